@@ -1,0 +1,161 @@
+/*
+ * pjx_attention.h -- C ABI of the sm_100a attention library.
+ *
+ * Everything probjax.nn's attention hot path lowers to on a GPU, as plain
+ * `extern "C"` entry points: caller-owned device buffers, sizes, a CUDA stream.
+ * No entry point allocates or frees device memory, synchronises the device
+ * (except the *_host and pjx_read_status helpers, which say so) or throws.
+ * All tensors are row-major and dense, laid out exactly as the reference
+ * passes them to its kernels (no transposes):
+ *
+ *   q   [B, Lq,  Hq,  D ]      k [B, Lkv, Hkv, D]      v [B, Lkv, Hkv, Dv]
+ *   o   [B, Lq,  Hq,  Dv]      lse [B, Hq, Lq] float32, natural log
+ *
+ * Query head h reads KV head h / (Hq / Hkv).  Rows without any valid key give
+ * o = 0 and lse = +inf.  Scores are (q.k) * sm_scale, then + bias, then the
+ * mask; the softmax is taken in fp32 and the probabilities are rounded to the
+ * input dtype before the product with V, as the reference does.
+ *
+ * Every function returns a pjx_status (0 = ok).  A message for the last failure
+ * on the calling thread is available from pjx_last_error().
+ *
+ * Citations give the reference interface each entry point replaces, as paths
+ * inside the probjax project.
+ */
+#ifndef PJX_ATTENTION_H_
+#define PJX_ATTENTION_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum pjx_status {
+  PJX_OK = 0,
+  PJX_ERR_BAD_ARG = 1,        /* shapes / pointers / dtypes the reference rejects with ValueError */
+  PJX_ERR_UNSUPPORTED = 2,    /* valid call that no kernel here computes */
+  PJX_ERR_WORKSPACE = 3,      /* workspace missing or too small */
+  PJX_ERR_DEVICE_TIMEOUT = 4, /* a bounded in-kernel wait expired (reported through the status word) */
+  PJX_ERR_CUDA = 5            /* a CUDA runtime / driver call failed */
+} pjx_status;
+
+typedef enum pjx_dtype { PJX_F32 = 0, PJX_BF16 = 1, PJX_F16 = 2 } pjx_dtype;
+
+/* Which forward kernel to run. AUTO picks the tcgen05 kernel whenever the call
+ * is one it computes and the generic one otherwise. */
+typedef enum pjx_impl { PJX_IMPL_AUTO = 0, PJX_IMPL_GENERIC = 1, PJX_IMPL_SM100 = 2 } pjx_impl;
+
+int pjx_version(void);
+const char* pjx_status_string(int status);
+const char* pjx_last_error(void);
+
+/*
+ * Flash-attention forward (MHA / GQA; optional causal mask, per-batch key
+ * lengths and dense additive bias).
+ *
+ * Replaces the `mha_fwd`, `mha_fwd_res` and their `_gqa` kernel primitives
+ * (probjax/nn/pallas_kernels/kernels/attention.py:2456-2490, 2537-2565; body
+ * `_mha_impl_raw` 2130-2278 launching `mha_forward_kernel` 377-533) for masks
+ * in {none, CausalMask, KVLenMask, their AND} and bias in {none, DenseBias}.
+ *
+ *   lse          may be NULL (the non-`_res` primitive).
+ *   kv_lengths   int32[B] or NULL: key j of batch b is valid iff j < kv_lengths[b].
+ *   bias         float32 [Bb, Hb, Lq, Lkv] with Bb in {1,B}, Hb in {1,Hq}, or NULL;
+ *                bias_batch_stride / bias_head_stride are element strides
+ *                (0 broadcasts that axis).
+ *   causal       nonzero: key j is valid for query i iff j <= i.
+ *   status       int32 device word or NULL; a kernel writes a nonzero pjx_status
+ *                there if a bounded wait expires. Read it with pjx_read_status.
+ */
+int pjx_attn_fwd(const void* q, const void* k, const void* v, void* o, float* lse,
+                 const int32_t* kv_lengths, const float* bias, int64_t bias_batch_stride,
+                 int64_t bias_head_stride, int B, int Lq, int Lkv, int Hq, int Hkv, int D, int Dv,
+                 int dtype, int causal, float sm_scale, int impl, int32_t* status, void* stream);
+
+/*
+ * Split-KV decode forward over a KV cache with per-sequence valid lengths,
+ * followed by the exact log-sum-exp combine of the per-split partials.
+ *
+ * Replaces `splitkv_forward` (probjax/nn/pallas_kernels/kernels/
+ * attention_splitkv.py:137-250: kernel 43-103, GQA row packing 121-134,
+ * combine 236-250) and, through kv_lengths, what `flex_attention(...,
+ * mask=KVLenMask(lengths))` computes for a decode step
+ * (probjax/nn/layers/attention.py:1426-1759).
+ *
+ *   k_cache, v_cache  [B, capacity, Hkv, D|Dv]; rows >= kv_lengths[b] are never read.
+ *   kv_lengths        int32[B] or NULL (= capacity everywhere).
+ *   o                 [B, Lq, Hq, Dv] in `dtype`, or float32 when o_is_f32 != 0
+ *                     (the per-rank partial of a sequence-sharded decode).
+ *   lse               [B, Hq, Lq] float32 natural log, or NULL.
+ *   split_len         keys per split (multiple of 64), 0 = choose.
+ *   workspace         pjx_attn_decode_workspace_bytes(...) bytes of device memory.
+ */
+int pjx_attn_decode_splitkv(const void* q, const void* k_cache, const void* v_cache,
+                            const int32_t* kv_lengths, void* o, float* lse, int B, int Lq, int Hq,
+                            int Hkv, int D, int Dv, int capacity, int dtype, float sm_scale,
+                            int split_len, int o_is_f32, void* workspace, size_t workspace_bytes,
+                            void* stream);
+size_t pjx_attn_decode_workspace_bytes(int B, int Lq, int Hq, int Hkv, int Dv, int capacity,
+                                       int split_len);
+/* The split length pjx_attn_decode_splitkv uses when given split_len = 0. */
+int pjx_attn_decode_default_split_len(int B, int Hkv, int capacity);
+
+/*
+ * Exact combine of n_parts normalised partial results, each with its natural-
+ * log LSE: m = max_p lse_p, w_p = exp(lse_p - m), o = sum w_p o_p / sum w_p,
+ * lse = m + log sum w_p (attention_splitkv.py:236-250, in natural log).  Used
+ * after the all-gather of a sequence-sharded decode.
+ *
+ *   o_parts   float32 [n_parts, n_rows, Dv]     lse_parts float32 [n_parts, n_rows]
+ *   o         [n_rows, Dv] in `dtype`           lse float32 [n_rows] or NULL
+ */
+int pjx_attn_combine(const float* o_parts, const float* lse_parts, int n_parts, int64_t n_rows,
+                     int Dv, void* o, float* lse, int dtype, void* stream);
+
+/*
+ * Latent attention forward: q over a shared latent cache with per-head
+ * up-projections (wk, wv both given) or with K = V = cache (both NULL).
+ *
+ * Replaces the `mla_fwd` / `mla_fwd_absorbed` primitives
+ * (probjax/nn/pallas_kernels/kernels/latent_attention.py:204-244, built by
+ * `_mla_build` 247-377 around `_mla_forward_kernel` 79-197).
+ *
+ *   q [B, Lq, H, Dqk]  cache [B, S, R]  wk [H, Dqk, R]  wv [H, Dv, R]  o [B, Lq, H, Dv]
+ *   workspace: pjx_mla_workspace_bytes(...) bytes; holds K = C.wk^T and V = C.wv^T.
+ */
+int pjx_mla_fwd(const void* q, const void* cache, const void* wk, const void* wv, void* o,
+                float* lse, const int32_t* kv_lengths, const float* bias,
+                int64_t bias_batch_stride, int64_t bias_head_stride, int B, int Lq, int S, int H,
+                int Dqk, int Dv, int R, int dtype, int causal, float sm_scale, int impl,
+                void* workspace, size_t workspace_bytes, int32_t* status, void* stream);
+size_t pjx_mla_workspace_bytes(int B, int S, int H, int Dqk, int Dv, int R, int dtype,
+                               int has_projections);
+
+/*
+ * The forward with HOST buffers: copies q, k, v (and kv_lengths, bias) to the
+ * device staging area, runs pjx_attn_fwd, copies o (and lse) back, and
+ * synchronises the stream before returning.  `staging` is device memory of
+ * pjx_attn_fwd_host_staging_bytes(...) bytes owned by the caller.  Same
+ * reference interface as pjx_attn_fwd; this is the call a host-side plugin
+ * makes when its arrays live in host memory.
+ */
+int pjx_attn_fwd_host(const void* q, const void* k, const void* v, void* o, float* lse,
+                      const int32_t* kv_lengths, const float* bias, int bias_batch, int bias_heads,
+                      int B, int Lq, int Lkv, int Hq, int Hkv, int D, int Dv, int dtype,
+                      int causal, float sm_scale, int impl, void* staging, size_t staging_bytes,
+                      void* stream);
+size_t pjx_attn_fwd_host_staging_bytes(int bias_batch, int bias_heads, int has_lse, int B, int Lq,
+                                       int Lkv, int Hq, int Hkv, int D, int Dv, int dtype);
+
+/* Synchronises `stream`, reads the device status word and returns it (0 = ok). */
+int pjx_read_status(const int32_t* status, void* stream);
+
+/* Number of this library's kernels launched by the calling process so far. */
+int64_t pjx_launch_count(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* PJX_ATTENTION_H_ */

@@ -1,0 +1,34 @@
+"""B200-native (sm_100a) implementation of probjax.nn's attention forward path.
+
+Public names mirror the reference: ``dot_product_attention``, ``flex_attention``,
+``mha``, ``splitkv_forward``, ``mla``, the mask / bias objects and the GPU dispatch
+route.  All computation happens in ``libpjx_attention.so`` (hand-written CUDA);
+build it with ``python -m probjax_b200.build``.
+"""
+
+from .attention import (  # noqa: F401
+    attention_forward,
+    check_status,
+    combine_partials,
+    decode_forward,
+    dot_product_attention,
+    flex_attention,
+    mha,
+    mla,
+    splitkv_forward,
+    use_splitkv,
+)
+from .dispatch import b200_attention_or_none, device_attention_defaults  # noqa: F401
+from .masks import (  # noqa: F401
+    AttentionBias,
+    AttentionMask,
+    CausalMask,
+    ComposeMask,
+    DenseBias,
+    KeyPaddingMask,
+    KVLenMask,
+    NoMask,
+    QKVLengthMask,
+)
+
+__version__ = "0.1.0"

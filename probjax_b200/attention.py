@@ -1,0 +1,432 @@
+"""probjax.nn's attention call signatures on top of the sm_100a CUDA library.
+
+``dot_product_attention`` / ``flex_attention`` (probjax/nn/layers/attention.py:
+1205-1319, 1426-1759), ``mha`` (probjax/nn/pallas_kernels/kernels/attention.py:
+2692-2984), ``splitkv_forward`` (.../attention_splitkv.py:137-250) and ``mla``
+(.../latent_attention.py:636-766) with the same argument names, defaults, layouts
+(``[..., T, H, D]``) and errors.  Arrays are torch tensors: CUDA tensors are used in
+place; CPU tensors and NumPy arrays go through the library's host-buffer call
+(copy in, compute on the GPU, copy out).  There is no CPU computation here: every
+function ends in a call into ``libpjx_attention.so`` and raises when that library
+or a GPU is missing.
+"""
+
+from __future__ import annotations
+
+import math
+from typing import Optional
+
+import numpy as np
+import torch
+
+from . import _lib
+from .masks import AttentionBias, AttentionMask, NoMask, lower_bias, lower_mask
+
+_DTYPES = {torch.float32: _lib.PJX_F32, torch.bfloat16: _lib.PJX_BF16, torch.float16: _lib.PJX_F16}
+_IMPL = {None: _lib.IMPL_AUTO, "b200": _lib.IMPL_AUTO, "b200:generic": _lib.IMPL_GENERIC,
+         "b200:tcgen05": _lib.IMPL_SM100}
+
+# kernels/attention.py:2649-2650
+_SPLITKV_MAX_Q_LEN = 64
+_SPLITKV_MIN_KV_LEN = 1024
+
+_status_words: dict = {}
+_scratch: dict = {}
+
+
+def _ptr(t) -> Optional[int]:
+    return None if t is None else t.data_ptr()
+
+
+def _stream(device) -> int:
+    return torch.cuda.current_stream(device).cuda_stream
+
+
+def _status_word(device) -> torch.Tensor:
+    key = torch.device(device).index or 0
+    if key not in _status_words:
+        _status_words[key] = torch.zeros(1, dtype=torch.int32, device=device)
+    return _status_words[key]
+
+
+def check_status(device=None) -> None:
+    """Synchronise and raise if a kernel on ``device`` reported a timed-out wait."""
+    device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    word = _status_word(device)
+    rc = _lib.lib().pjx_read_status(_ptr(word), _stream(device))
+    if rc:
+        word.zero_()
+    _lib.check(rc)
+
+
+def _scratch_bytes(device, tag: str, nbytes: int) -> torch.Tensor:
+    """A cached, growing device byte buffer (decode partials, projections, staging)."""
+    key = (torch.device(device).index or 0, tag)
+    buf = _scratch.get(key)
+    if buf is None or buf.numel() < nbytes:
+        buf = torch.empty(max(int(nbytes), 256), dtype=torch.uint8, device=device)
+        _scratch[key] = buf
+    return buf
+
+
+def _as_tensor(x):
+    if isinstance(x, torch.Tensor):
+        return x
+    if isinstance(x, np.ndarray):
+        return torch.from_numpy(np.ascontiguousarray(x))
+    raise TypeError(f"expected a torch.Tensor or numpy.ndarray, got {type(x).__name__}")
+
+
+def _require_gpu():
+    _lib.lib()  # raises when the library is not built
+    if not torch.cuda.is_available():
+        raise RuntimeError("probjax_b200 needs a CUDA device (sm_100a); there is no CPU path")
+
+
+def _gqa_group(hq: int, hkv: int) -> int:
+    # kernels/attention.py:2113-2120
+    if hq % hkv != 0:
+        raise ValueError(f"query heads ({hq}) must be a multiple of key/value heads ({hkv})")
+    return hq // hkv
+
+
+# ---------------------------------------------------------------------------
+# Raw calls (rank-4 tensors, structural mask)
+# ---------------------------------------------------------------------------
+
+
+def attention_forward(q, k, v, *, causal=False, kv_lengths=None, bias=None, sm_scale=1.0,
+                      return_lse=False, impl=None):
+    """One ``pjx_attn_fwd`` call. ``q [B,Lq,Hq,D]``, ``k [B,Lkv,Hkv,D]``,
+    ``v [B,Lkv,Hkv,Dv]``; CUDA tensors stay on the device, host tensors use the
+    host-buffer entry point.  Returns ``o`` or ``(o, lse)``."""
+    _require_gpu()
+    q, k, v = _as_tensor(q), _as_tensor(k), _as_tensor(v)
+    if q.dtype not in _DTYPES:
+        raise ValueError(f"unsupported dtype {q.dtype}; expected float32, bfloat16 or float16")
+    B, Lq, Hq, D = q.shape
+    Lkv, Hkv, Dv = k.shape[1], k.shape[2], v.shape[3]
+    if impl not in _IMPL:
+        raise ValueError(f"implementation must be one of {sorted(x for x in _IMPL if x)} or None, got {impl!r}")
+    on_device = q.is_cuda
+    if k.is_cuda != on_device or v.is_cuda != on_device:
+        raise ValueError("q, k and v must live on the same side (all CUDA or all host)")
+    L = _lib.lib()
+    if on_device:
+        dev = q.device
+        q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
+        o = torch.empty((B, Lq, Hq, Dv), dtype=q.dtype, device=dev)
+        lse = torch.empty((B, Hq, Lq), dtype=torch.float32, device=dev) if return_lse else None
+        kvl = None if kv_lengths is None else _as_tensor(kv_lengths).to(device=dev, dtype=torch.int32).contiguous()
+        bs = hs = 0
+        bt = None
+        if bias is not None:
+            bt = _as_tensor(bias).to(device=dev, dtype=torch.float32).contiguous()
+            bs = 0 if bt.shape[0] == 1 else bt.stride(0)
+            hs = 0 if bt.shape[1] == 1 else bt.stride(1)
+        with torch.cuda.device(dev):
+            rc = L.pjx_attn_fwd(_ptr(q), _ptr(k), _ptr(v), _ptr(o), _ptr(lse), _ptr(kvl), _ptr(bt), bs, hs,
+                                B, Lq, Lkv, Hq, Hkv, D, Dv, _DTYPES[q.dtype], int(bool(causal)), float(sm_scale),
+                                _IMPL[impl], _ptr(_status_word(dev)), _stream(dev))
+        _lib.check(rc)
+        return (o, lse) if return_lse else o
+    # host buffers
+    dev = torch.device("cuda", torch.cuda.current_device())
+    q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
+    pin = q.is_pinned()
+    o = torch.empty((B, Lq, Hq, Dv), dtype=q.dtype, pin_memory=pin)
+    lse = torch.empty((B, Hq, Lq), dtype=torch.float32, pin_memory=pin) if return_lse else None
+    kvl = None if kv_lengths is None else _as_tensor(kv_lengths).to(device="cpu", dtype=torch.int32).contiguous()
+    bt = None if bias is None else _as_tensor(bias).to(device="cpu", dtype=torch.float32).contiguous()
+    bb, bh = (bt.shape[0], bt.shape[1]) if bt is not None else (0, 0)
+    need = L.pjx_attn_fwd_host_staging_bytes(bb, bh, int(return_lse), B, Lq, Lkv, Hq, Hkv, D, Dv, _DTYPES[q.dtype])
+    staging = _scratch_bytes(dev, "staging", need)
+    with torch.cuda.device(dev):
+        rc = L.pjx_attn_fwd_host(_ptr(q), _ptr(k), _ptr(v), _ptr(o), _ptr(lse), _ptr(kvl), _ptr(bt), bb, bh,
+                                 B, Lq, Lkv, Hq, Hkv, D, Dv, _DTYPES[q.dtype], int(bool(causal)), float(sm_scale),
+                                 _IMPL[impl], _ptr(staging), staging.numel(), _stream(dev))
+    _lib.check(rc)
+    return (o, lse) if return_lse else o
+
+
+def decode_forward(q, k_cache, v_cache, *, kv_lengths=None, sm_scale, split_len=0, return_lse=False,
+                   partial_f32=False):
+    """One ``pjx_attn_decode_splitkv`` call on CUDA tensors (split-KV kernel +
+    combine).  ``partial_f32`` returns ``o`` in float32 (a rank's partial of a
+    sequence-sharded decode)."""
+    _require_gpu()
+    if not q.is_cuda:
+        raise ValueError("decode_forward takes CUDA tensors")
+    dev = q.device
+    q, k_cache, v_cache = q.contiguous(), k_cache.contiguous(), v_cache.contiguous()
+    B, Lq, Hq, D = q.shape
+    cap, Hkv, Dv = k_cache.shape[1], k_cache.shape[2], v_cache.shape[3]
+    L = _lib.lib()
+    o = torch.empty((B, Lq, Hq, Dv), dtype=torch.float32 if partial_f32 else q.dtype, device=dev)
+    lse = torch.empty((B, Hq, Lq), dtype=torch.float32, device=dev) if return_lse else None
+    kvl = None if kv_lengths is None else _as_tensor(kv_lengths).to(device=dev, dtype=torch.int32).contiguous()
+    need = L.pjx_attn_decode_workspace_bytes(B, Lq, Hq, Hkv, Dv, cap, int(split_len)) if Hq % Hkv == 0 else 0
+    ws = _scratch_bytes(dev, "decode", need)
+    with torch.cuda.device(dev):
+        rc = L.pjx_attn_decode_splitkv(_ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(kvl), _ptr(o), _ptr(lse),
+                                       B, Lq, Hq, Hkv, D, Dv, cap, _DTYPES[q.dtype], float(sm_scale),
+                                       int(split_len), int(partial_f32), _ptr(ws), ws.numel(), _stream(dev))
+    _lib.check(rc)
+    return (o, lse) if return_lse else o
+
+
+def combine_partials(o_parts, lse_parts, *, out_dtype=None):
+    """``pjx_attn_combine``: ``o_parts [P, N, Dv]`` fp32, ``lse_parts [P, N]`` natural
+    log (``+inf`` = no keys) -> ``(o [N, Dv], lse [N])``."""
+    _require_gpu()
+    o_parts, lse_parts = o_parts.contiguous().float(), lse_parts.contiguous().float()
+    P, N, Dv = o_parts.shape
+    out_dtype = out_dtype or torch.float32
+    o = torch.empty((N, Dv), dtype=out_dtype, device=o_parts.device)
+    lse = torch.empty((N,), dtype=torch.float32, device=o_parts.device)
+    with torch.cuda.device(o_parts.device):
+        rc = _lib.lib().pjx_attn_combine(_ptr(o_parts), _ptr(lse_parts), P, N, Dv, _ptr(o), _ptr(lse),
+                                         _DTYPES[out_dtype], _stream(o_parts.device))
+    _lib.check(rc)
+    return o, lse
+
+
+# ---------------------------------------------------------------------------
+# Reference call signatures
+# ---------------------------------------------------------------------------
+
+
+def _validate_qkv(query, key, value, enable_gqa):
+    # layers/attention.py:1490-1516
+    if (query.dtype != key.dtype) or (query.dtype != value.dtype):
+        raise ValueError(
+            "Expected query, key, and value to have the same dtype, "
+            f"but got query.dtype: {query.dtype}, key.dtype: {key.dtype}, "
+            f"and value.dtype: {value.dtype} instead."
+        )
+    if (query.dim() < 3) or (key.dim() < 3) or (value.dim() < 3):
+        raise ValueError(
+            "Expected query, key, and value to all be at least 3 dimensional, but got query.ndim: "
+            f"{query.dim()}, key.ndim: {key.dim()}, and value.ndim: {value.dim()} instead."
+        )
+    if (not enable_gqa) and query.shape[-2] != key.shape[-2]:
+        raise ValueError(
+            "Expect query and key/value to have the same number of heads "
+            f"but got Hq={query.shape[-2]} and Hkv={key.shape[-2]}. "
+            "Try setting enable_gqa=True for GQA."
+        )
+    if enable_gqa and query.shape[-2] % key.shape[-2] != 0:
+        raise ValueError(
+            "Expect number of query heads to be a multiple of kv heads for GQA "
+            f"but got Hq={query.shape[-2]} and Hkv={key.shape[-2]}."
+        )
+
+
+def use_splitkv(q, k, *, causal=False, bias=None, q_limit=None, dropout_rate=0.0, split_kv=None) -> bool:
+    """Whether the split-KV decode kernel runs (kernels/attention.py:2653-2689).
+    Unlike the reference's kernel this one takes per-batch key lengths, so a
+    ``KVLenMask`` does not disable it."""
+    if split_kv is False or causal or bias is not None or q_limit is not None or dropout_rate > 0:
+        return False
+    if q.dim() != 4 or not q.is_cuda or q.dtype not in (torch.bfloat16, torch.float16):
+        return False
+    hq, hkv = q.shape[2], k.shape[2]
+    if q.shape[-1] != k.shape[-1] or q.shape[-1] not in (64, 128) or (hq // hkv) * q.shape[1] > 16:
+        return False
+    if split_kv:
+        return True
+    return q.shape[1] <= _SPLITKV_MAX_Q_LEN and k.shape[1] >= _SPLITKV_MIN_KV_LEN
+
+
+def _apply_q_limit(out, lse, q_limit):
+    if q_limit is not None:
+        out[:, q_limit:] = 0
+        if lse is not None:
+            lse[:, :, q_limit:] = float("inf")
+    return out, lse
+
+
+def mha(q, k, v, mask: AttentionMask | None = None, bias: AttentionBias | None = None, rng=None,
+        sm_scale: float = 1.0, block_sizes=None, backward_pass_impl: str = "auto", num_warps=None,
+        num_stages: int = 2, grid=None, interpret: bool = False, debug: bool = False,
+        dropout_rate: float = 0.0, dropout_impl: str = "counter", diff_mode: str = "reverse",
+        split_kv: bool | None = None, *, return_lse: bool = False, implementation: str | None = None):
+    """``mha`` (kernels/attention.py:2692-2711): rank-4 ``[B, T, H, D]`` inputs,
+    default ``sm_scale=1.0``.  Tile-size / warp / stage arguments are accepted for
+    signature compatibility and ignored (the kernels pick their own tiling)."""
+    if diff_mode not in ("reverse", "forward"):
+        raise ValueError(f"diff_mode must be 'reverse' or 'forward', got {diff_mode!r}.")
+    q, k, v = _as_tensor(q), _as_tensor(k), _as_tensor(v)
+    _gqa_group(q.shape[-2], k.shape[-2])
+    if v.shape[-2] != k.shape[-2]:
+        raise ValueError(f"key and value need the same number of heads, got {k.shape[-2]} and {v.shape[-2]}.")
+    if dropout_rate > 0:
+        raise NotImplementedError("attention dropout is not implemented by the sm_100a forward kernels")
+    if interpret:
+        raise NotImplementedError("interpret mode belongs to the Pallas kernels; this library runs CUDA only")
+    B, Lq = q.shape[0], q.shape[1]
+    lm = lower_mask(mask, B, Lq, k.shape[1])
+    bt = lower_bias(bias, B, q.shape[2], Lq, k.shape[1])
+    if use_splitkv(q, k, causal=lm.causal, bias=bt, q_limit=lm.q_limit, dropout_rate=dropout_rate, split_kv=split_kv):
+        res = decode_forward(q, k, v, kv_lengths=lm.kv_lengths, sm_scale=sm_scale, return_lse=return_lse)
+    else:
+        res = attention_forward(q, k, v, causal=lm.causal, kv_lengths=lm.kv_lengths, bias=bt, sm_scale=sm_scale,
+                                return_lse=return_lse, impl=implementation)
+    out, lse = res if return_lse else (res, None)
+    out, lse = _apply_q_limit(out, lse, lm.q_limit)
+    return (out, lse) if return_lse else out
+
+
+def flex_attention(query, key, value, mask: AttentionMask | None = None, bias: AttentionBias | None = None,
+                   dropout_rng=None, dropout_rate: float = 0.0, broadcast_dropout: bool = False,
+                   deterministic=True, dtype=None, precision=None, module=None,
+                   sm_scale: Optional[float] = None, enable_gqa: bool = False, block_q: int = 128,
+                   block_k: int = 128, block_q_dkv: int = 64, block_kv_dkv: int = 64, block_q_dq: int = 64,
+                   block_kv_dq: int = 64, backward_pass_impl: str = "auto", num_warps=None, num_stages: int = 2,
+                   grid=None, interpret: bool = False, debug: bool = False, dropout_impl: str = "counter",
+                   diff_mode: str = "reverse", split_kv: bool | None = None, implementation: str | None = None,
+                   *, return_lse: bool = False):
+    """``flex_attention`` (layers/attention.py:1426-1457): ``[..., T, H, D]`` inputs,
+    default ``sm_scale = 1/sqrt(D)``; ``implementation`` is ``None`` or ``"b200"``."""
+    query, key, value = _as_tensor(query), _as_tensor(key), _as_tensor(value)
+    if dtype is not None:
+        query, key, value = query.to(dtype), key.to(dtype), value.to(dtype)
+    _validate_qkv(query, key, value, enable_gqa)
+    if sm_scale is None:
+        sm_scale = 1.0 / math.sqrt(query.shape[-1])
+    if implementation not in _IMPL:
+        raise ValueError(
+            f"implementation must be None or one of {sorted(x for x in _IMPL if x)}, got {implementation!r}"
+        )
+    active_dropout = dropout_rate if not deterministic and dropout_rate > 0 else 0.0
+    squeeze = query.dim() == 3
+    if squeeze:
+        query, key, value = query[None], key[None], value[None]
+    batch_shape = query.shape[:-3]
+    if key.shape[:-3] != batch_shape or value.shape[:-3] != batch_shape:
+        raise ValueError(f"batch dimensions differ: {tuple(query.shape)}, {tuple(key.shape)}, {tuple(value.shape)}")
+    q4, k4, v4 = (x.reshape((-1,) + tuple(x.shape[-3:])) for x in (query, key, value))
+    res = mha(q4, k4, v4, mask=mask, bias=bias, sm_scale=sm_scale, dropout_rate=active_dropout,
+              interpret=interpret, diff_mode=diff_mode, split_kv=split_kv, return_lse=return_lse,
+              implementation=implementation)
+    out, lse = res if return_lse else (res, None)
+    out = out.reshape(tuple(batch_shape) + tuple(out.shape[-3:]))
+    if squeeze:
+        out = out[0]
+    if return_lse:
+        lse = lse.reshape(tuple(batch_shape) + tuple(lse.shape[-2:]))
+        return out, (lse[0] if squeeze else lse)
+    return out
+
+
+def dot_product_attention(query, key, value, mask=None, bias=None, dropout_rng=None, dropout_rate: float = 0.0,
+                          broadcast_dropout: bool = False, deterministic=True, dtype=None, precision=None,
+                          module=None, sm_scale: Optional[float] = None, enable_gqa: bool = False,
+                          implementation: str | None = None):
+    """``dot_product_attention`` (layers/attention.py:1205-1221): the default
+    ``attention_fn`` of ``MultiHeadAttention``.  Like Flax, K/V may carry fewer
+    heads than Q.  Mask / bias must be the mask / bias objects of
+    :mod:`probjax_b200.masks` (dense arrays belong to the Flax einsum path of the
+    reference, which has no counterpart here)."""
+    if module is not None or precision is not None:
+        raise NotImplementedError("sowing (module=) and explicit precision belong to the Flax einsum path")
+    if mask is not None and not isinstance(mask, AttentionMask):
+        raise NotImplementedError("dense mask arrays are not supported; pass an AttentionMask object")
+    if bias is not None and not isinstance(bias, AttentionBias):
+        raise NotImplementedError("dense bias arrays are not supported; wrap them in DenseBias")
+    return flex_attention(query, key, value, mask=mask, bias=bias, dropout_rng=dropout_rng,
+                          dropout_rate=dropout_rate, deterministic=deterministic, dtype=dtype,
+                          sm_scale=sm_scale, enable_gqa=True, implementation=implementation)
+
+
+def splitkv_forward(q, k, v, *, sm_scale: float, num_splits: int | None = None, block_k: int | None = None,
+                    num_warps: int = 4, num_stages: int = 2, interpret: bool = False, return_lse: bool = False,
+                    kv_lengths=None):
+    """``splitkv_forward`` (attention_splitkv.py:137-149).  Returns
+    ``[B, Lq, Hq, Dv]`` in ``q.dtype`` and, with ``return_lse``, the natural-log LSE
+    ``[B, Hq, Lq]``.  ``num_splits`` fixes the number of KV splits (rounded so a
+    split is a multiple of 64 keys); ``kv_lengths [B]`` (an extension) gives
+    per-sequence valid lengths of the cache."""
+    if interpret:
+        raise NotImplementedError("interpret mode belongs to the Pallas kernels; this library runs CUDA only")
+    q, k, v = _as_tensor(q), _as_tensor(k), _as_tensor(v)
+    hq, hkv = q.shape[2], k.shape[2]
+    if hq % hkv:
+        raise ValueError(f"Hq={hq} must be a multiple of Hkv={hkv}.")
+    split_len = 0
+    if num_splits is not None:
+        if num_splits < 1:
+            raise ValueError("num_splits must be positive")
+        per_split = -(-k.shape[1] // num_splits)
+        split_len = max(64, -(-per_split // 64) * 64)
+    return decode_forward(q, k, v, kv_lengths=kv_lengths, sm_scale=sm_scale, split_len=split_len,
+                          return_lse=return_lse)
+
+
+def mla(q, cache, wk=None, wv=None, *, mask=None, bias=None, rng=None, sm_scale: float | None = None,
+        block_sizes=None, backward_pass_impl: str = "auto", num_warps=None, num_stages: int = 2,
+        interpret: bool = False, debug: bool = False, dropout_rate: float = 0.0, dropout_impl: str = "counter",
+        return_lse: bool = False, implementation: str | None = None):
+    """``mla`` (latent_attention.py:636-654): ``q [B,Q,H,Dqk]`` over a shared latent
+    ``cache [B,S,R]`` with per-head up-projections ``wk [H,Dqk,R]``, ``wv [H,Dv,R]``
+    (materialized) or none (absorbed, ``K = V = cache``)."""
+    q, cache = _as_tensor(q), _as_tensor(cache)
+    wk = None if wk is None else _as_tensor(wk)
+    wv = None if wv is None else _as_tensor(wv)
+    # latent_attention.py:668-696
+    if q.dim() != 4:
+        raise ValueError(f"q must be rank 4 [B,Q,H,D], got shape {tuple(q.shape)}")
+    if cache.dim() != 3:
+        raise ValueError(f"cache must be rank 3 [B,S,R], got shape {tuple(cache.shape)}")
+    if q.shape[0] != cache.shape[0]:
+        raise ValueError(f"batch mismatch: q has {q.shape[0]}, cache has {cache.shape[0]}")
+    H, Dqk, R = q.shape[-2], q.shape[-1], cache.shape[-1]
+    if (wk is None) != (wv is None):
+        raise ValueError(
+            "provide both wk and wv (materialized) or neither (absorbed); mixing the two is not supported"
+        )
+    if wk is None and Dqk != R:
+        raise ValueError(f"absorbed mode (wk=None) requires qk_head_dim == kv_lora_rank ({Dqk} != {R})")
+    if wk is not None and tuple(wk.shape) != (H, Dqk, R):
+        raise ValueError(f"wk must be {(H, Dqk, R)}, got {tuple(wk.shape)}")
+    if wv is not None and (wv.shape[0] != H or wv.shape[2] != R):
+        raise ValueError(f"wv must be [heads, v_head_dim, {R}], got {tuple(wv.shape)}")
+    if dropout_rate > 0:
+        raise NotImplementedError("attention dropout is not implemented by the sm_100a forward kernels")
+    if interpret:
+        raise NotImplementedError("interpret mode belongs to the Pallas kernels; this library runs CUDA only")
+    if sm_scale is None:
+        sm_scale = 1.0 / math.sqrt(Dqk)  # latent_attention.py:698-701
+    _require_gpu()
+    if not q.is_cuda:
+        raise NotImplementedError("mla takes CUDA tensors")
+    if implementation not in _IMPL:
+        raise ValueError(f"implementation must be None or one of {sorted(x for x in _IMPL if x)}")
+    dev = q.device
+    B, Lq, S = q.shape[0], q.shape[1], cache.shape[1]
+    Dv = R if wv is None else wv.shape[1]
+    lm = lower_mask(mask, B, Lq, S)
+    bt = lower_bias(bias, B, H, Lq, S)
+    q, cache = q.contiguous(), cache.contiguous()
+    wk = None if wk is None else wk.to(dev).contiguous()
+    wv = None if wv is None else wv.to(dev).contiguous()
+    if wk is not None and (wk.dtype != q.dtype or wv.dtype != q.dtype or cache.dtype != q.dtype):
+        raise ValueError("q, cache, wk and wv must share a dtype")
+    o = torch.empty((B, Lq, H, Dv), dtype=q.dtype, device=dev)
+    lse = torch.empty((B, H, Lq), dtype=torch.float32, device=dev) if return_lse else None
+    kvl = None if lm.kv_lengths is None else lm.kv_lengths.to(device=dev, dtype=torch.int32).contiguous()
+    bs = hs = 0
+    if bt is not None:
+        bt = bt.to(device=dev, dtype=torch.float32).contiguous()
+        bs = 0 if bt.shape[0] == 1 else bt.stride(0)
+        hs = 0 if bt.shape[1] == 1 else bt.stride(1)
+    L = _lib.lib()
+    need = L.pjx_mla_workspace_bytes(B, S, H, Dqk, Dv, R, _DTYPES[q.dtype], int(wk is not None))
+    ws = _scratch_bytes(dev, "mla", need)
+    with torch.cuda.device(dev):
+        rc = L.pjx_mla_fwd(_ptr(q), _ptr(cache), _ptr(wk), _ptr(wv), _ptr(o), _ptr(lse), _ptr(kvl), _ptr(bt), bs, hs,
+                           B, Lq, S, H, Dqk, Dv, R, _DTYPES[q.dtype], int(lm.causal), float(sm_scale),
+                           _IMPL[implementation], _ptr(ws), ws.numel(), _ptr(_status_word(dev)), _stream(dev))
+    _lib.check(rc)
+    o, lse = _apply_q_limit(o, lse, lm.q_limit)
+    return (o, lse) if return_lse else o

@@ -1,0 +1,435 @@
+// Split-KV decode forward and the exact (o, lse) combine.
+//
+// The decode step is bandwidth bound: every K and V byte of the valid part of
+// the cache is read once, and with GQA the G = Hq/Hkv query heads that share a
+// KV head are packed as rows of one small matrix so that the KV tile is read
+// once per group (the reference packs the same way,
+// probjax/nn/pallas_kernels/kernels/attention_splitkv.py:121-126).
+//
+// Grid (split, kv head, batch).  A CTA of four warps streams its split of the
+// cache through a cp.async ring of 64-key tiles (K and V, 16-byte vector copies,
+// XOR-swizzled rows); warp w owns keys 16w..16w+15 of every tile and keeps its
+// own running (max, sum, O) so that no CTA-wide exchange happens inside the
+// loop.  Scores and P.V use mma.sync m16n8k16 with the packed query rows padded
+// to 16 -- the tensor work is far below the memory time, so the padding is free.
+// The four warps are merged once at the end and the CTA writes one partial:
+// O normalised by its own sum (fp32) and a base-2 LSE, which is what the
+// reference kernel emits per split (attention_splitkv.py:97-103).  A second tiny
+// kernel combines the valid splits exactly (attention_splitkv.py:236-250).
+//
+// Unlike the reference kernel this one takes per-sequence valid lengths: keys at
+// positions >= kv_lengths[b] are neither read nor counted.
+#include "pjx_common.cuh"
+
+namespace pjx {
+namespace {
+
+constexpr int BK = 64;       // keys per tile
+constexpr int NWARP = 4;
+constexpr int NTHR = NWARP * 32;
+constexpr int NSTAGE = 3;
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+  return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, int src_bytes) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(dst), "l"(src), "r"(src_bytes));
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() {
+  asm volatile("cp.async.wait_group %0;\n" ::"n"(N));
+}
+__device__ __forceinline__ void ldsm_x4(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+               : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3)
+               : "r"(addr));
+}
+__device__ __forceinline__ void ldsm_x4_trans(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+               : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3)
+               : "r"(addr));
+}
+template <typename T>
+__device__ __forceinline__ void mma16816(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1);
+template <>
+__device__ __forceinline__ void mma16816<__nv_bfloat16>(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+      : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+template <>
+__device__ __forceinline__ void mma16816<__half>(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+      : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+template <typename T>
+__device__ __forceinline__ uint32_t pack2(float lo, float hi);
+template <>
+__device__ __forceinline__ uint32_t pack2<__nv_bfloat16>(float lo, float hi) {
+  __nv_bfloat162 t = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&t);
+}
+template <>
+__device__ __forceinline__ uint32_t pack2<__half>(float lo, float hi) {
+  __half2 t = __floats2half2_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&t);
+}
+
+// Byte offset of 16-byte chunk `c` of row `r` inside a swizzled [rows][HD] tile.
+template <int HD>
+__device__ __forceinline__ uint32_t swz(int r, int c) {
+  return static_cast<uint32_t>(r * (HD * 2) + ((c ^ (r & 7)) << 4));
+}
+
+template <typename T, int HD>
+__global__ void __launch_bounds__(NTHR, 2) decode_splitkv_kernel(const DecodeParams p) {
+  constexpr int CH = HD / 8;               // 16-byte chunks per row
+  constexpr int TILE_BYTES = BK * HD * 2;  // one K or V tile
+  constexpr int KS = HD / 16;              // k-steps of the score product
+  constexpr int NT_O = HD / 8;             // output n-tiles
+  extern __shared__ __align__(128) unsigned char smem_raw[];
+
+  const int split = blockIdx.x, hk = blockIdx.y, b = blockIdx.z;
+  int len = p.capacity;
+  if (p.kv_lengths) len = max(0, min(len, p.kv_lengths[b]));
+  const int start = split * p.split_len;
+  if (start >= len) return;  // nothing to do; the combine never reads this split
+  const int end = min(len, start + p.split_len);
+  const int n_tiles = (end - start + BK - 1) / BK;
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int G = p.Hq / p.Hkv;
+  const T* kbase = static_cast<const T*>(p.k) + ((int64_t)b * p.capacity * p.Hkv + hk) * HD;
+  const T* vbase = static_cast<const T*>(p.v) + ((int64_t)b * p.capacity * p.Hkv + hk) * HD;
+  const int64_t tok_stride = (int64_t)p.Hkv * HD;
+  const uint32_t smem_base = smem_u32(smem_raw);
+
+  auto load_tile = [&](int t) {
+    const int stage = t % NSTAGE;
+    const uint32_t ks = smem_base + stage * 2 * TILE_BYTES;
+    const uint32_t vs = ks + TILE_BYTES;
+    const int key0 = start + t * BK;
+#pragma unroll
+    for (int i = 0; i < BK * CH / NTHR; ++i) {
+      const int idx = tid + i * NTHR;
+      const int r = idx / CH, c = idx % CH;
+      const int key = key0 + r;
+      const bool ok = key < end;
+      const int64_t off = (int64_t)(ok ? key : start) * tok_stride + c * 8;
+      cp_async16(ks + swz<HD>(r, c), kbase + off, ok ? 16 : 0);
+      cp_async16(vs + swz<HD>(r, c), vbase + off, ok ? 16 : 0);
+    }
+  };
+
+#pragma unroll
+  for (int s = 0; s < NSTAGE - 1; ++s) {
+    if (s < n_tiles) load_tile(s);
+    cp_async_commit();
+  }
+
+  // Query fragments (A operand): packed row r = g * Lq + t of this KV head.
+  uint32_t qf[KS][4];
+  {
+    const T* q = static_cast<const T*>(p.q);
+    const int r0 = lane >> 2, cq = (lane & 3) * 2;
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+      const int r = r0 + half * 8;
+      const bool ok = r < p.rows;
+      const int g = ok ? r / p.Lq : 0, t = ok ? r % p.Lq : 0;
+      const T* qrow = q + (((int64_t)b * p.Lq + t) * p.Hq + hk * G + g) * HD;
+#pragma unroll
+      for (int ks = 0; ks < KS; ++ks) {
+        uint32_t lo = 0, hi = 0;
+        if (ok) {
+          lo = *reinterpret_cast<const uint32_t*>(qrow + ks * 16 + cq);
+          hi = *reinterpret_cast<const uint32_t*>(qrow + ks * 16 + cq + 8);
+        }
+        qf[ks][half] = lo;
+        qf[ks][half + 2] = hi;
+      }
+    }
+  }
+
+  const float c1 = p.sm_scale * kLog2e;
+  float m_ref[2] = {-INFINITY, -INFINITY};
+  float l_part[2] = {0.f, 0.f};
+  float oacc[NT_O][4];
+#pragma unroll
+  for (int n = 0; n < NT_O; ++n)
+#pragma unroll
+    for (int e = 0; e < 4; ++e) oacc[n][e] = 0.f;
+
+  for (int t = 0; t < n_tiles; ++t) {
+    cp_async_wait<NSTAGE - 2>();
+    __syncthreads();
+    if (t + NSTAGE - 1 < n_tiles) load_tile(t + NSTAGE - 1);
+    cp_async_commit();
+
+    const int stage = t % NSTAGE;
+    const uint32_t ks_addr = smem_base + stage * 2 * TILE_BYTES;
+    const uint32_t vs_addr = ks_addr + TILE_BYTES;
+    const int key_w = start + t * BK + warp * 16;  // first key of this warp's slice
+    if (key_w >= end) continue;                    // warp-uniform: slice has no valid key
+
+    // ---- scores: S[16 rows x 16 keys] ----
+    float s[2][4];
+#pragma unroll
+    for (int nt = 0; nt < 2; ++nt) {
+#pragma unroll
+      for (int e = 0; e < 4; ++e) s[nt][e] = 0.f;
+      const int row = warp * 16 + nt * 8 + (lane & 7);
+#pragma unroll
+      for (int kp = 0; kp < KS / 2; ++kp) {
+        uint32_t b0, b1, b2, b3;
+        ldsm_x4(ks_addr + swz<HD>(row, kp * 4 + (lane >> 3)), b0, b1, b2, b3);
+        mma16816<T>(s[nt], qf[2 * kp], b0, b1);
+        mma16816<T>(s[nt], qf[2 * kp + 1], b2, b3);
+      }
+    }
+
+    // ---- online softmax (exp2 domain) with lazy rescaling ----
+    float tmax[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+    for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int key = key_w + nt * 8 + (lane & 3) * 2 + (e & 1);
+        const float x = key < end ? s[nt][e] * c1 : -INFINITY;
+        s[nt][e] = x;
+        tmax[e >> 1] = fmaxf(tmax[e >> 1], x);
+      }
+#pragma unroll
+    for (int hrow = 0; hrow < 2; ++hrow) {
+      tmax[hrow] = fmaxf(tmax[hrow], __shfl_xor_sync(0xffffffffu, tmax[hrow], 1));
+      tmax[hrow] = fmaxf(tmax[hrow], __shfl_xor_sync(0xffffffffu, tmax[hrow], 2));
+    }
+    const bool need = (tmax[0] > m_ref[0] + 8.f) || (tmax[1] > m_ref[1] + 8.f) ||
+                      (m_ref[0] == -INFINITY && tmax[0] > -INFINITY) ||
+                      (m_ref[1] == -INFINITY && tmax[1] > -INFINITY);
+    if (__any_sync(0xffffffffu, need)) {
+      float corr[2];
+#pragma unroll
+      for (int hrow = 0; hrow < 2; ++hrow) {
+        const float m_new = fmaxf(m_ref[hrow], tmax[hrow]);
+        corr[hrow] = (m_new == -INFINITY) ? 1.f : exp2f(m_ref[hrow] - m_new);
+        m_ref[hrow] = m_new;
+        l_part[hrow] *= corr[hrow];
+      }
+#pragma unroll
+      for (int n = 0; n < NT_O; ++n) {
+        oacc[n][0] *= corr[0];
+        oacc[n][1] *= corr[0];
+        oacc[n][2] *= corr[1];
+        oacc[n][3] *= corr[1];
+      }
+    }
+    uint32_t pf[4];
+    {
+      const float mu0 = m_ref[0] == -INFINITY ? 0.f : m_ref[0];
+      const float mu1 = m_ref[1] == -INFINITY ? 0.f : m_ref[1];
+      float pr[2][4];
+#pragma unroll
+      for (int nt = 0; nt < 2; ++nt) {
+        pr[nt][0] = exp2f(s[nt][0] - mu0);
+        pr[nt][1] = exp2f(s[nt][1] - mu0);
+        pr[nt][2] = exp2f(s[nt][2] - mu1);
+        pr[nt][3] = exp2f(s[nt][3] - mu1);
+        l_part[0] += pr[nt][0] + pr[nt][1];
+        l_part[1] += pr[nt][2] + pr[nt][3];
+      }
+      pf[0] = pack2<T>(pr[0][0], pr[0][1]);
+      pf[1] = pack2<T>(pr[0][2], pr[0][3]);
+      pf[2] = pack2<T>(pr[1][0], pr[1][1]);
+      pf[3] = pack2<T>(pr[1][2], pr[1][3]);
+    }
+
+    // ---- O[16 x HD] += P[16 x 16 keys] . V[16 keys x HD] ----
+    {
+      const int row = warp * 16 + ((lane >> 3) & 1) * 8 + (lane & 7);
+#pragma unroll
+      for (int np = 0; np < NT_O / 2; ++np) {
+        uint32_t v0, v1, v2, v3;
+        ldsm_x4_trans(vs_addr + swz<HD>(row, np * 2 + (lane >> 4)), v0, v1, v2, v3);
+        mma16816<T>(oacc[2 * np], pf, v0, v1);
+        mma16816<T>(oacc[2 * np + 1], pf, v2, v3);
+      }
+    }
+  }
+
+  // ---- merge the four warps ----
+  cp_async_wait<0>();
+  __syncthreads();  // every warp is done with the ring: reuse it as fp32 scratch
+  float* sm_o = reinterpret_cast<float*>(smem_raw);          // [NWARP][16][HD]
+  float* sm_m = sm_o + NWARP * 16 * HD;                       // [NWARP][16]
+  float* sm_l = sm_m + NWARP * 16;                            // [NWARP][16]
+#pragma unroll
+  for (int hrow = 0; hrow < 2; ++hrow) {
+    float lsum = l_part[hrow];
+    lsum += __shfl_xor_sync(0xffffffffu, lsum, 1);
+    lsum += __shfl_xor_sync(0xffffffffu, lsum, 2);
+    if ((lane & 3) == 0) {
+      sm_m[warp * 16 + (lane >> 2) + hrow * 8] = m_ref[hrow];
+      sm_l[warp * 16 + (lane >> 2) + hrow * 8] = lsum;
+    }
+  }
+#pragma unroll
+  for (int n = 0; n < NT_O; ++n) {
+    const int col = n * 8 + (lane & 3) * 2;
+    float* r0 = sm_o + (warp * 16 + (lane >> 2)) * HD + col;
+    float* r1 = r0 + 8 * HD;
+    r0[0] = oacc[n][0];
+    r0[1] = oacc[n][1];
+    r1[0] = oacc[n][2];
+    r1[1] = oacc[n][3];
+  }
+  __syncthreads();
+
+  const int64_t part = (((int64_t)b * p.Hkv + hk) * p.num_splits + split) * p.rows;
+  for (int idx = tid; idx < p.rows * HD; idx += NTHR) {
+    const int r = idx / HD, d = idx % HD;
+    float mall = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < NWARP; ++w) mall = fmaxf(mall, sm_m[w * 16 + r]);
+    float lall = 0.f, o = 0.f;
+#pragma unroll
+    for (int w = 0; w < NWARP; ++w) {
+      const float mw = sm_m[w * 16 + r];
+      const float sc = (mw == -INFINITY) ? 0.f : exp2f(mw - mall);
+      lall += sm_l[w * 16 + r] * sc;
+      o += sm_o[(w * 16 + r) * HD + d] * sc;
+    }
+    p.o_part[(part + r) * HD + d] = lall > 0.f ? o / lall : 0.f;
+    if (d == 0) p.lse_part[part + r] = lall > 0.f ? mall + log2f(lall) : -INFINITY;
+  }
+}
+
+// One CTA per packed row (b, kv head, r): exact combine of the valid splits.
+template <typename TO>
+__global__ void combine_splits_kernel(const DecodeParams p) {
+  const int r = blockIdx.x, hk = blockIdx.y, b = blockIdx.z;
+  int len = p.capacity;
+  if (p.kv_lengths) len = max(0, min(len, p.kv_lengths[b]));
+  const int ns = (len + p.split_len - 1) / p.split_len;
+  const int64_t base = ((int64_t)b * p.Hkv + hk) * p.num_splits;
+  float m = -INFINITY;
+  for (int s = 0; s < ns; ++s) m = fmaxf(m, p.lse_part[(base + s) * p.rows + r]);
+  const float msafe = (m == -INFINITY) ? 0.f : m;
+  float denom = 0.f;
+  for (int s = 0; s < ns; ++s) denom += exp2f(p.lse_part[(base + s) * p.rows + r] - msafe);
+  const float inv = denom > 0.f ? 1.f / denom : 0.f;
+  const int G = p.Hq / p.Hkv;
+  const int g = r / p.Lq, t = r % p.Lq;
+  const int h = hk * G + g;
+  TO* o = static_cast<TO*>(p.o) + (((int64_t)b * p.Lq + t) * p.Hq + h) * p.Dv;
+  for (int d = threadIdx.x; d < p.Dv; d += blockDim.x) {
+    float acc = 0.f;
+    for (int s = 0; s < ns; ++s) {
+      const float w = exp2f(p.lse_part[(base + s) * p.rows + r] - msafe);
+      acc += w * p.o_part[((base + s) * p.rows + r) * p.Dv + d];
+    }
+    o[d] = Elem<TO>::from_f(acc * inv);
+  }
+  if (p.lse && threadIdx.x == 0)
+    p.lse[((int64_t)b * p.Hq + h) * p.Lq + t] = denom > 0.f ? (msafe + log2f(denom)) * kLn2 : INFINITY;
+}
+
+// Combine of n_parts partials laid out [n_parts, n_rows, Dv] with natural-log LSEs.
+template <typename TO>
+__global__ void combine_parts_kernel(const float* __restrict__ o_parts, const float* __restrict__ lse_parts,
+                                     int n_parts, int64_t n_rows, int Dv, TO* __restrict__ o,
+                                     float* __restrict__ lse) {
+  const int64_t row = blockIdx.x;
+  float m = -INFINITY;
+  for (int s = 0; s < n_parts; ++s) {
+    const float x = lse_parts[s * n_rows + row];
+    if (x != INFINITY) m = fmaxf(m, x);  // +inf marks a part without keys
+  }
+  const float msafe = (m == -INFINITY) ? 0.f : m;
+  float denom = 0.f;
+  for (int s = 0; s < n_parts; ++s) {
+    const float x = lse_parts[s * n_rows + row];
+    denom += (x == INFINITY) ? 0.f : expf(x - msafe);
+  }
+  const float inv = denom > 0.f ? 1.f / denom : 0.f;
+  for (int d = threadIdx.x; d < Dv; d += blockDim.x) {
+    float acc = 0.f;
+    for (int s = 0; s < n_parts; ++s) {
+      const float x = lse_parts[s * n_rows + row];
+      const float w = (x == INFINITY) ? 0.f : expf(x - msafe);
+      acc += w * o_parts[(s * n_rows + row) * Dv + d];
+    }
+    o[row * Dv + d] = Elem<TO>::from_f(acc * inv);
+  }
+  if (lse && threadIdx.x == 0) lse[row] = denom > 0.f ? msafe + logf(denom) : INFINITY;
+}
+
+template <typename T, int HD>
+int launch_decode_t(const DecodeParams& p, cudaStream_t stream) {
+  constexpr int smem = NSTAGE * 2 * BK * HD * 2;
+  static_assert(smem >= (NWARP * 16 * HD + 2 * NWARP * 16) * 4, "merge scratch must fit in the ring");
+  auto kern = decode_splitkv_kernel<T, HD>;
+  int rc = check_cuda(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem),
+                      "cudaFuncSetAttribute(decode)");
+  if (rc) return rc;
+  dim3 grid(p.num_splits, p.Hkv, p.B);
+  kern<<<grid, NTHR, smem, stream>>>(p);
+  count_launch();
+  rc = check_cuda(cudaGetLastError(), "decode launch");
+  if (rc) return rc;
+  dim3 cgrid(p.rows, p.Hkv, p.B);
+  const int cthr = p.Dv >= 128 ? 128 : 64;
+  if (p.o_is_f32)
+    combine_splits_kernel<float><<<cgrid, cthr, 0, stream>>>(p);
+  else
+    combine_splits_kernel<T><<<cgrid, cthr, 0, stream>>>(p);
+  count_launch();
+  return check_cuda(cudaGetLastError(), "decode combine launch");
+}
+
+}  // namespace
+
+bool decode_fast_supported(const DecodeParams& p, int dtype) {
+  if (dtype != PJX_BF16 && dtype != PJX_F16) return false;
+  if (p.D != p.Dv || (p.D != 64 && p.D != 128)) return false;
+  if (p.rows > 16) return false;
+  return true;
+}
+
+int launch_decode(const DecodeParams& p, int dtype, cudaStream_t stream) {
+  if (p.B == 0 || p.Hq == 0 || p.Lq == 0) return PJX_OK;
+  if (dtype == PJX_BF16) {
+    if (p.D == 128) return launch_decode_t<__nv_bfloat16, 128>(p, stream);
+    return launch_decode_t<__nv_bfloat16, 64>(p, stream);
+  }
+  if (p.D == 128) return launch_decode_t<__half, 128>(p, stream);
+  return launch_decode_t<__half, 64>(p, stream);
+}
+
+int launch_combine_parts(const float* o_parts, const float* lse_parts, int n_parts, int64_t n_rows,
+                         int Dv, void* o, float* lse, int dtype, cudaStream_t stream) {
+  if (n_rows == 0) return PJX_OK;
+  const int thr = Dv >= 128 ? 128 : 64;
+  const unsigned grid = static_cast<unsigned>(n_rows);
+  switch (dtype) {
+    case PJX_F32:
+      combine_parts_kernel<float><<<grid, thr, 0, stream>>>(o_parts, lse_parts, n_parts, n_rows, Dv, static_cast<float*>(o), lse);
+      break;
+    case PJX_BF16:
+      combine_parts_kernel<__nv_bfloat16><<<grid, thr, 0, stream>>>(o_parts, lse_parts, n_parts, n_rows, Dv, static_cast<__nv_bfloat16*>(o), lse);
+      break;
+    case PJX_F16:
+      combine_parts_kernel<__half><<<grid, thr, 0, stream>>>(o_parts, lse_parts, n_parts, n_rows, Dv, static_cast<__half*>(o), lse);
+      break;
+    default:
+      return fail(PJX_ERR_BAD_ARG, "unknown dtype %d", dtype);
+  }
+  count_launch();
+  return check_cuda(cudaGetLastError(), "combine launch");
+}
+
+}  // namespace pjx

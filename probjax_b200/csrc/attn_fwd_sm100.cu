@@ -1,0 +1,455 @@
+// Flash-attention forward for sm_100a: TMA-staged tiles, tcgen05 MMAs with
+// accumulators in tensor memory, warp-specialised roles.
+//
+// One CTA owns 256 query rows of one (batch, query head) as two 128-row tiles
+// that ping-pong on the tensor core: while the softmax warps of one tile work on
+// its scores, the MMAs of the other tile run.  K and V tiles are loaded once per
+// CTA and used by both query tiles.
+//
+//   warp 0      TMA producer (one lane): Q tiles, then a K ring and a V ring
+//   warp 1      MMA issuer (one lane): S_t = Q_t.K^T (both operands in shared
+//               memory), O_t += P_t.V (P_t read from tensor memory, V in shared
+//               memory, MN-major)
+//   warps 2-5   softmax of tile 0: one thread per query row
+//   warps 6-9   softmax of tile 1
+//
+// Tensor memory (columns): S0 | S1 | O0 | O1, 128 lanes = 128 query rows.  P_t is
+// written over S_t as packed 16-bit pairs, so the next S_t MMA is issued only
+// after the P_t.V MMAs (same issuing thread, executed in order).
+//
+// Softmax arithmetic is the reference kernel's
+// (probjax/nn/pallas_kernels/kernels/attention.py:456-529): fp32 scores, scale,
+// bias, mask, exp2 domain, P rounded to the input dtype, O divided by the row sum
+// at the end.  The running maximum is only advanced when it grew by more than 8
+// (a factor 256), which leaves the result unchanged and skips most rescales.
+//
+// Every barrier wait is bounded: on expiry the role raises the CTA abort flag,
+// all roles drain, tensor memory is freed and the status word gets
+// PJX_ERR_DEVICE_TIMEOUT.
+#include "pjx_common.cuh"
+#include "sm100_ptx.cuh"
+
+namespace pjx {
+namespace {
+
+using namespace sm100;
+
+constexpr int BM = 128;          // rows per query tile (= tensor-memory lanes)
+constexpr int NTHREADS = 320;    // 10 warps
+
+template <int DQK, int DV, int BN, int KST, int VST>
+struct Cfg {
+  static constexpr int Q_SUB = DQK / 64, V_SUB = DV / 64;
+  static constexpr int Q_TILE_BYTES = Q_SUB * BM * 128;
+  static constexpr int K_TILE_BYTES = Q_SUB * BN * 128;
+  static constexpr int V_TILE_BYTES = V_SUB * BN * 128;
+  static constexpr int OFF_Q = 0;
+  static constexpr int OFF_K = OFF_Q + 2 * Q_TILE_BYTES;
+  static constexpr int OFF_V = OFF_K + KST * K_TILE_BYTES;
+  static constexpr int OFF_BAR = OFF_V + VST * V_TILE_BYTES;
+  static constexpr int N_BAR = 2 + 2 * KST + 2 * VST + 6;
+  static constexpr int SMEM_BYTES = OFF_BAR + N_BAR * 8 + 16 + 1024;  // + alignment slack
+  static constexpr int TMEM_USED = 2 * BN + 2 * DV;
+  static constexpr int TMEM_COLS = TMEM_USED <= 128 ? 128 : (TMEM_USED <= 256 ? 256 : 512);
+  static_assert(TMEM_USED <= 512, "tensor memory has 512 columns");
+  static_assert(SMEM_BYTES <= 227 * 1024, "shared memory budget");
+};
+
+template <bool BF16>
+__device__ __forceinline__ uint32_t pack16(float lo, float hi) {
+  if constexpr (BF16) {
+    __nv_bfloat162 t = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&t);
+  } else {
+    __half2 t = __floats2half2_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&t);
+  }
+}
+
+template <int DQK, int DV, int BN, int KST, int VST, bool BF16>
+__global__ void __launch_bounds__(NTHREADS, 1)
+attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
+                      const __grid_constant__ CUtensorMap tm_v, const FwdParams p) {
+  using C = Cfg<DQK, DV, BN, KST, VST>;
+  extern __shared__ unsigned char smem_unaligned[];
+  unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_unaligned) + 1023) & ~uintptr_t(1023));
+  const uint32_t sbase = smem_u32(smem);
+  const uint32_t bar0 = sbase + C::OFF_BAR;
+  auto BAR = [&](int i) { return bar0 + 8u * i; };
+  // barrier indices
+  const int Q_FULL = 0;                   // [2]
+  const int K_FULL = 2;                   // [KST]
+  const int K_EMPTY = K_FULL + KST;       // [KST]
+  const int V_FULL = K_EMPTY + KST;       // [VST]
+  const int V_EMPTY = V_FULL + VST;       // [VST]
+  const int S_FULL = V_EMPTY + VST;       // [2]
+  const int P_FULL = S_FULL + 2;          // [2]
+  const int O_FULL = P_FULL + 2;          // [2]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + C::OFF_BAR + C::N_BAR * 8);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int qt = gridDim.x - 1 - blockIdx.x;  // longest causal tiles first
+  const int h = blockIdx.y, b = blockIdx.z;
+  const int hk = h / (p.Hq / p.Hkv);
+  const int q0 = qt * 2 * BM;
+
+  int kv_len = p.Lkv;
+  if (p.kv_lengths) kv_len = max(0, min(kv_len, p.kv_lengths[b]));
+  int n_t[2];
+#pragma unroll
+  for (int t = 0; t < 2; ++t) {
+    const int qs = q0 + t * BM;
+    if (qs >= p.Lq) {
+      n_t[t] = 0;
+    } else {
+      const int lim = p.causal ? min(kv_len, min(qs + BM, p.Lq)) : kv_len;
+      n_t[t] = (lim + BN - 1) / BN;
+    }
+  }
+  const int n = max(n_t[0], n_t[1]);
+
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < C::N_BAR; ++i) mbar_init(BAR(i), (i >= P_FULL && i < P_FULL + 2) ? 128u : 1u);
+    *abort_flag = 0;
+    fence_barrier_init();
+  }
+  if (warp == 0) {
+    tmem_alloc(smem_u32(tmem_slot), C::TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = *tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer
+    if (lane == 0 && n > 0) {
+      prefetch_tmap(&tm_q);
+      prefetch_tmap(&tm_k);
+      prefetch_tmap(&tm_v);
+#pragma unroll
+      for (int t = 0; t < 2; ++t) {
+        if (n_t[t] == 0) continue;
+        mbar_arrive_expect_tx(BAR(Q_FULL + t), C::Q_TILE_BYTES);
+#pragma unroll
+        for (int s = 0; s < C::Q_SUB; ++s)
+          tma_load_4d(sbase + C::OFF_Q + t * C::Q_TILE_BYTES + s * BM * 128, &tm_q, BAR(Q_FULL + t), s * 64, h,
+                      q0 + t * BM, b);
+      }
+      for (int j = 0; j < n; ++j) {
+        const int ks = j % KST, vs = j % VST;
+        if (!mbar_wait(BAR(K_EMPTY + ks), ((j / KST) & 1) ^ 1, abort_flag)) break;
+        mbar_arrive_expect_tx(BAR(K_FULL + ks), C::K_TILE_BYTES);
+#pragma unroll
+        for (int s = 0; s < C::Q_SUB; ++s)
+          tma_load_4d(sbase + C::OFF_K + ks * C::K_TILE_BYTES + s * BN * 128, &tm_k, BAR(K_FULL + ks), s * 64, hk,
+                      j * BN, b);
+        if (!mbar_wait(BAR(V_EMPTY + vs), ((j / VST) & 1) ^ 1, abort_flag)) break;
+        mbar_arrive_expect_tx(BAR(V_FULL + vs), C::V_TILE_BYTES);
+#pragma unroll
+        for (int s = 0; s < C::V_SUB; ++s)
+          tma_load_4d(sbase + C::OFF_V + vs * C::V_TILE_BYTES + s * BN * 128, &tm_v, BAR(V_FULL + vs), s * 64, hk,
+                      j * BN, b);
+      }
+    }
+  } else if (warp == 1) {
+    // -------------------------------------------------------------- MMA issuer
+    if (lane == 0 && n > 0) {
+      constexpr uint32_t idesc_s = make_idesc(BM, BN, BF16, false, false);
+      constexpr uint32_t idesc_o = make_idesc(BM, DV, BF16, false, true);
+      auto issue_s = [&](int t, int j) {
+        const uint32_t qa = sbase + C::OFF_Q + t * C::Q_TILE_BYTES;
+        const uint32_t ka = sbase + C::OFF_K + (j % KST) * C::K_TILE_BYTES;
+#pragma unroll
+        for (int s = 0; s < C::Q_SUB; ++s)
+#pragma unroll
+          for (int kk = 0; kk < 4; ++kk)
+            mma_ss(tmem + t * BN, make_smem_desc(qa + s * BM * 128 + kk * 32, 16, 1024),
+                   make_smem_desc(ka + s * BN * 128 + kk * 32, 16, 1024), idesc_s, (s | kk) != 0);
+      };
+      auto issue_pv = [&](int t, int j) {
+        const uint32_t va = sbase + C::OFF_V + (j % VST) * C::V_TILE_BYTES;
+#pragma unroll
+        for (int kk = 0; kk < BN / 16; ++kk)
+          mma_ts(tmem + 2 * BN + t * DV, tmem + t * BN + kk * 8, make_smem_desc(va + kk * 2048, BN * 128, 1024),
+                 idesc_o, (j | kk) != 0);
+      };
+      bool ok = true;
+#pragma unroll
+      for (int t = 0; t < 2; ++t)
+        if (ok && n_t[t] > 0) ok = mbar_wait(BAR(Q_FULL + t), 0, abort_flag);
+      if (ok) ok = mbar_wait(BAR(K_FULL + 0), 0, abort_flag);
+      if (ok) {
+        tc_fence_after();
+#pragma unroll
+        for (int t = 0; t < 2; ++t)
+          if (n_t[t] > 0) {
+            issue_s(t, 0);
+            mma_commit(BAR(S_FULL + t));
+          }
+        mma_commit(BAR(K_EMPTY + 0));
+      }
+      for (int j = 0; ok && j < n; ++j) {
+        const bool have_next = j + 1 < n;
+        ok = mbar_wait(BAR(V_FULL + j % VST), (j / VST) & 1, abort_flag);
+        if (ok && have_next) ok = mbar_wait(BAR(K_FULL + (j + 1) % KST), ((j + 1) / KST) & 1, abort_flag);
+        if (!ok) break;
+#pragma unroll
+        for (int t = 0; t < 2; ++t) {
+          if (j < n_t[t]) {
+            ok = mbar_wait(BAR(P_FULL + t), j & 1, abort_flag);
+            if (!ok) break;
+            tc_fence_after();
+            issue_pv(t, j);
+            if (j == n_t[t] - 1) mma_commit(BAR(O_FULL + t));
+          }
+          if (j + 1 < n_t[t]) {
+            issue_s(t, j + 1);
+            mma_commit(BAR(S_FULL + t));
+          }
+        }
+        if (!ok) break;
+        mma_commit(BAR(V_EMPTY + j % VST));
+        if (have_next) mma_commit(BAR(K_EMPTY + (j + 1) % KST));
+      }
+    }
+  } else {
+    // ------------------------------------------------------------ softmax warps
+    const int t = (warp - 2) >> 2;
+    const int quarter = warp & 3;  // tensor-memory lane quarter this warp may access
+    const int r_in = quarter * 32 + lane;
+    const int row = q0 + t * BM + r_in;
+    const bool row_ok = row < p.Lq;
+    const int my_n = n_t[t];
+    const uint32_t lane_sel = static_cast<uint32_t>(quarter * 32) << 16;
+    const uint32_t s_addr = tmem + lane_sel + t * BN;
+    const uint32_t o_addr = tmem + lane_sel + 2 * BN + t * DV;
+    const float c1 = p.sm_scale * kLog2e;
+    const float* bias_row = nullptr;
+    if (p.bias && row_ok) bias_row = p.bias + (int64_t)b * p.bias_bs + (int64_t)h * p.bias_hs + (int64_t)row * p.Lkv;
+    const bool bias_vec = p.bias && (p.Lkv % 4 == 0) && ((reinterpret_cast<uintptr_t>(p.bias) & 15) == 0) &&
+                          (p.bias_bs % 4 == 0) && (p.bias_hs % 4 == 0);
+    const float cs = p.bias ? 1.f : c1;
+
+    float m_ref = -INFINITY, l = 0.f;
+    bool ok = true;
+    for (int j = 0; j < my_n; ++j) {
+      ok = mbar_wait(BAR(S_FULL + t), j & 1, abort_flag);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      tc_fence_after();
+      float s[BN];
+#pragma unroll
+      for (int c = 0; c < BN / 32; ++c) tmem_ld32f(s_addr + c * 32, &s[c * 32]);
+      tmem_wait_ld();
+
+      const int k0 = j * BN;
+      if (p.bias) {
+        if (bias_row && bias_vec && k0 + BN <= p.Lkv) {
+          const float4* bp = reinterpret_cast<const float4*>(bias_row + k0);
+#pragma unroll
+          for (int c = 0; c < BN / 4; ++c) {
+            const float4 bv = __ldg(bp + c);
+            s[4 * c + 0] = fmaf(bv.x, kLog2e, s[4 * c + 0] * c1);
+            s[4 * c + 1] = fmaf(bv.y, kLog2e, s[4 * c + 1] * c1);
+            s[4 * c + 2] = fmaf(bv.z, kLog2e, s[4 * c + 2] * c1);
+            s[4 * c + 3] = fmaf(bv.w, kLog2e, s[4 * c + 3] * c1);
+          }
+        } else {
+#pragma unroll
+          for (int c = 0; c < BN; ++c) {
+            const float bv = (bias_row && k0 + c < p.Lkv) ? __ldg(bias_row + k0 + c) : 0.f;
+            s[c] = fmaf(bv, kLog2e, s[c] * c1);
+          }
+        }
+      }
+      const bool need_mask = (k0 + BN > kv_len) || (p.causal && k0 + BN - 1 > q0 + t * BM);
+      if (need_mask) {
+#pragma unroll
+        for (int c = 0; c < BN; ++c) {
+          const int key = k0 + c;
+          const bool keep = key < kv_len && (!p.causal || key <= row);
+          s[c] = keep ? s[c] : -INFINITY;
+        }
+      }
+      float mx = -INFINITY;
+#pragma unroll
+      for (int c = 0; c < BN; ++c) mx = fmaxf(mx, s[c]);
+      mx *= cs;  // cs > 0
+
+      // lazy running maximum: advance only when it grew by more than 8 (base 2)
+      const bool need = (mx > m_ref + 8.f) || (m_ref == -INFINITY && mx > -INFINITY);
+      if (__any_sync(0xffffffffu, need)) {
+        const float m_new = fmaxf(m_ref, mx);
+        const float corr = (m_new == -INFINITY) ? 1.f : exp2f(m_ref - m_new);
+        m_ref = m_new;
+        l *= corr;
+        if (j > 0) {
+#pragma unroll
+          for (int c = 0; c < DV / 32; ++c) {
+            float o[32];
+            tmem_ld32f(o_addr + c * 32, o);
+            tmem_wait_ld();
+#pragma unroll
+            for (int i = 0; i < 32; ++i) o[i] *= corr;
+            tmem_st32f(o_addr + c * 32, o);
+          }
+        }
+      }
+      const float neg_m = (m_ref == -INFINITY) ? 0.f : -m_ref;
+      float lsum = 0.f;
+#pragma unroll
+      for (int c = 0; c < BN / 64; ++c) {
+        uint32_t pk[32];
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          const float p0 = exp2f(fmaf(s[c * 64 + 2 * i], cs, neg_m));
+          const float p1 = exp2f(fmaf(s[c * 64 + 2 * i + 1], cs, neg_m));
+          lsum += p0 + p1;
+          pk[i] = pack16<BF16>(p0, p1);
+        }
+        tmem_st32(s_addr + c * 32, pk);
+      }
+      l += lsum;
+      tmem_wait_st();
+      tc_fence_before();
+      mbar_arrive(BAR(P_FULL + t));
+    }
+
+    if (ok && n_t[t] >= 0 && (q0 + t * BM) < p.Lq) {
+      const float inv = l > 0.f ? 1.f / l : 0.f;
+      if (my_n > 0) {
+        ok = mbar_wait(BAR(O_FULL + t), 0, abort_flag);
+        ok = __all_sync(0xffffffffu, ok);
+      }
+      if (ok) {
+        tc_fence_after();
+        unsigned char* orow = static_cast<unsigned char*>(p.o) + ((((int64_t)b * p.Lq + row) * p.Hq + h) * DV) * 2;
+#pragma unroll
+        for (int c = 0; c < DV / 32; ++c) {
+          float o[32];
+          if (my_n > 0) {
+            tmem_ld32f(o_addr + c * 32, o);
+            tmem_wait_ld();
+          } else {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) o[i] = 0.f;
+          }
+          if (row_ok) {
+            uint4* dst = reinterpret_cast<uint4*>(orow + c * 64);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              uint4 w;
+              w.x = pack16<BF16>(o[8 * i + 0] * inv, o[8 * i + 1] * inv);
+              w.y = pack16<BF16>(o[8 * i + 2] * inv, o[8 * i + 3] * inv);
+              w.z = pack16<BF16>(o[8 * i + 4] * inv, o[8 * i + 5] * inv);
+              w.w = pack16<BF16>(o[8 * i + 6] * inv, o[8 * i + 7] * inv);
+              dst[i] = w;
+            }
+          }
+        }
+        if (p.lse && row_ok)
+          p.lse[((int64_t)b * p.Hq + h) * p.Lq + row] = l > 0.f ? (m_ref + log2f(l)) * kLn2 : INFINITY;
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 0) {
+    __syncwarp();
+    tmem_dealloc(tmem, C::TMEM_COLS);
+    if (lane == 0 && *abort_flag && p.status) atomicExch(p.status, (int)PJX_ERR_DEVICE_TIMEOUT);
+  }
+}
+
+// ---------------------------------------------------------------------------
+// Host side: tensor maps and launch
+// ---------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = [] {
+    void* f = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &f, cudaEnableDefault, &q) != cudaSuccess ||
+        q != cudaDriverEntryPointSuccess)
+      f = nullptr;
+    return reinterpret_cast<EncodeTiledFn>(f);
+  }();
+  return fn;
+}
+
+}  // namespace
+
+// [B, L, H, Dim] row-major 16-bit tensor, box = 64 elements x 1 head x `rows` tokens.
+int make_tmap_blhd(CUtensorMap* m, const void* base, int dtype, int B, int L, int H, int Dim, int rows) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return fail(PJX_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
+  cuuint64_t dims[4] = {(cuuint64_t)Dim, (cuuint64_t)H, (cuuint64_t)L, (cuuint64_t)B};
+  cuuint64_t strides[3] = {(cuuint64_t)Dim * 2, (cuuint64_t)H * Dim * 2, (cuuint64_t)L * H * Dim * 2};
+  cuuint32_t box[4] = {64, 1, (cuuint32_t)rows, 1};
+  cuuint32_t estr[4] = {1, 1, 1, 1};
+  CUresult r = fn(m, dtype == PJX_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 4,
+                  const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                  CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail(PJX_ERR_CUDA, "cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
+  return PJX_OK;
+}
+
+namespace {
+
+template <int DQK, int DV, int BN, int KST, int VST, bool BF16>
+int launch_cfg(const FwdParams& p, int dtype, cudaStream_t stream) {
+  using C = Cfg<DQK, DV, BN, KST, VST>;
+  CUtensorMap tq, tk, tv;
+  int rc;
+  if ((rc = make_tmap_blhd(&tq, p.q, dtype, p.B, p.Lq, p.Hq, DQK, BM))) return rc;
+  if ((rc = make_tmap_blhd(&tk, p.k, dtype, p.B, p.Lkv, p.Hkv, DQK, BN))) return rc;
+  if ((rc = make_tmap_blhd(&tv, p.v, dtype, p.B, p.Lkv, p.Hkv, DV, BN))) return rc;
+  auto kern = attn_fwd_sm100_kernel<DQK, DV, BN, KST, VST, BF16>;
+  if ((rc = check_cuda(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES),
+                       "cudaFuncSetAttribute(sm100 fwd)")))
+    return rc;
+  dim3 grid((p.Lq + 2 * BM - 1) / (2 * BM), p.Hq, p.B);
+  kern<<<grid, NTHREADS, C::SMEM_BYTES, stream>>>(tq, tk, tv, p);
+  count_launch();
+  return check_cuda(cudaGetLastError(), "sm100 forward launch");
+}
+
+template <bool BF16>
+int launch_by_shape(const FwdParams& p, int dtype, cudaStream_t stream) {
+  if (p.D == 128 && p.Dv == 128) return launch_cfg<128, 128, 128, 2, 2, BF16>(p, dtype, stream);
+  if (p.D == 64 && p.Dv == 64) return launch_cfg<64, 64, 128, 3, 3, BF16>(p, dtype, stream);
+  if (p.D == 192 && p.Dv == 128) return launch_cfg<192, 128, 64, 2, 2, BF16>(p, dtype, stream);
+  return fail(PJX_ERR_UNSUPPORTED, "tcgen05 forward: head dims (%d, %d) not built", p.D, p.Dv);
+}
+
+}  // namespace
+
+bool fwd_sm100_supported(const FwdParams& p, int dtype, const char** why) {
+  const char* w = nullptr;
+  if (dtype != PJX_BF16 && dtype != PJX_F16) w = "dtype must be bf16 or fp16";
+  else if (!((p.D == 128 && p.Dv == 128) || (p.D == 64 && p.Dv == 64) || (p.D == 192 && p.Dv == 128)))
+    w = "head dims must be (64,64), (128,128) or (192,128)";
+  else if (!(p.sm_scale > 0.f)) w = "sm_scale must be positive";
+  else if (p.B < 1 || p.Lq < 1 || p.Lkv < 1) w = "empty problem";
+  else if (p.Hq > 65535 || p.B > 65535) w = "grid too large";
+  else if ((reinterpret_cast<uintptr_t>(p.q) | reinterpret_cast<uintptr_t>(p.k) | reinterpret_cast<uintptr_t>(p.v) |
+            reinterpret_cast<uintptr_t>(p.o)) & 15)
+    w = "q, k, v, o must be 16-byte aligned";
+  if (why) *why = w;
+  return w == nullptr;
+}
+
+int launch_fwd_sm100(const FwdParams& p, int dtype, cudaStream_t stream) {
+  const char* why = nullptr;
+  if (!fwd_sm100_supported(p, dtype, &why)) return fail(PJX_ERR_UNSUPPORTED, "tcgen05 forward: %s", why);
+  return dtype == PJX_BF16 ? launch_by_shape<true>(p, dtype, stream) : launch_by_shape<false>(p, dtype, stream);
+}
+
+}  // namespace pjx

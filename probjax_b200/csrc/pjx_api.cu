@@ -1,0 +1,282 @@
+// The C ABI: argument validation (mirroring the ValueErrors the reference raises
+// for the same mistakes), kernel selection and the host-buffer convenience call.
+#include <atomic>
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+
+#include "pjx_common.cuh"
+
+namespace pjx {
+
+static thread_local char g_err[512] = "";
+static std::atomic<int64_t> g_launches{0};
+
+int fail(int status, const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_err, sizeof(g_err), fmt, ap);
+  va_end(ap);
+  return status;
+}
+int check_cuda(cudaError_t e, const char* what) {
+  if (e == cudaSuccess) return PJX_OK;
+  return fail(PJX_ERR_CUDA, "%s: %s", what, cudaGetErrorString(e));
+}
+void count_launch(int n) { g_launches.fetch_add(n, std::memory_order_relaxed); }
+
+namespace {
+
+inline size_t align_up(size_t x, size_t a = 256) { return (x + a - 1) / a * a; }
+
+int validate_common(const void* q, const void* k, const void* v, const void* o, int B, int Lq, int Lkv,
+                    int Hq, int Hkv, int D, int Dv, int dtype) {
+  if (dtype != PJX_F32 && dtype != PJX_BF16 && dtype != PJX_F16)
+    return fail(PJX_ERR_BAD_ARG, "dtype must be float32, bfloat16 or float16 (got code %d)", dtype);
+  if (B < 0 || Lq < 0 || Lkv < 0 || Hq < 1 || Hkv < 1 || D < 1 || Dv < 1)
+    return fail(PJX_ERR_BAD_ARG, "negative or zero dimension (B=%d Lq=%d Lkv=%d Hq=%d Hkv=%d D=%d Dv=%d)", B, Lq,
+                Lkv, Hq, Hkv, D, Dv);
+  if (Hq % Hkv != 0)
+    return fail(PJX_ERR_BAD_ARG, "query heads %d must be a multiple of kv heads %d", Hq, Hkv);
+  if (B > 0 && Lq > 0 && (!q || !o)) return fail(PJX_ERR_BAD_ARG, "q and o must not be null");
+  if (B > 0 && Lkv > 0 && (!k || !v)) return fail(PJX_ERR_BAD_ARG, "k and v must not be null");
+  return PJX_OK;
+}
+
+}  // namespace
+}  // namespace pjx
+
+using namespace pjx;
+
+extern "C" {
+
+int pjx_version(void) { return 100; }
+
+const char* pjx_status_string(int status) {
+  switch (status) {
+    case PJX_OK: return "ok";
+    case PJX_ERR_BAD_ARG: return "bad argument";
+    case PJX_ERR_UNSUPPORTED: return "unsupported call";
+    case PJX_ERR_WORKSPACE: return "workspace missing or too small";
+    case PJX_ERR_DEVICE_TIMEOUT: return "a bounded wait inside a kernel expired";
+    case PJX_ERR_CUDA: return "CUDA call failed";
+  }
+  return "unknown status";
+}
+
+const char* pjx_last_error(void) { return g_err; }
+
+int64_t pjx_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
+
+int pjx_attn_fwd(const void* q, const void* k, const void* v, void* o, float* lse, const int32_t* kv_lengths,
+                 const float* bias, int64_t bias_batch_stride, int64_t bias_head_stride, int B, int Lq, int Lkv,
+                 int Hq, int Hkv, int D, int Dv, int dtype, int causal, float sm_scale, int impl, int32_t* status,
+                 void* stream) {
+  int rc = validate_common(q, k, v, o, B, Lq, Lkv, Hq, Hkv, D, Dv, dtype);
+  if (rc) return rc;
+  if (impl != PJX_IMPL_AUTO && impl != PJX_IMPL_GENERIC && impl != PJX_IMPL_SM100)
+    return fail(PJX_ERR_BAD_ARG, "impl must be 0 (auto), 1 (generic) or 2 (tcgen05), got %d", impl);
+  if (bias && (bias_batch_stride < 0 || bias_head_stride < 0))
+    return fail(PJX_ERR_BAD_ARG, "bias strides must be non-negative");
+  if (B == 0 || Lq == 0) return PJX_OK;
+  FwdParams p;
+  p.q = q; p.k = k; p.v = v; p.o = o; p.lse = lse;
+  p.kv_lengths = kv_lengths;
+  p.bias = bias; p.bias_bs = bias_batch_stride; p.bias_hs = bias_head_stride;
+  p.B = B; p.Lq = Lq; p.Lkv = Lkv; p.Hq = Hq; p.Hkv = Hkv; p.D = D; p.Dv = Dv;
+  p.causal = causal != 0;
+  p.sm_scale = sm_scale;
+  p.status = status;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (impl == PJX_IMPL_SM100) return launch_fwd_sm100(p, dtype, st);
+  if (impl == PJX_IMPL_AUTO && fwd_sm100_supported(p, dtype, nullptr)) return launch_fwd_sm100(p, dtype, st);
+  return launch_fwd_generic(p, dtype, st);
+}
+
+int pjx_attn_decode_default_split_len(int B, int Hkv, int capacity) {
+  if (B < 1 || Hkv < 1 || capacity < 1) return 64;
+  const long units = (long)B * Hkv;
+  const long target = 148L * 2 * 12;  // CTAs: a dozen waves of two CTAs per SM
+  long splits = (target + units - 1) / units;
+  if (splits < 1) splits = 1;
+  long len = (capacity + splits - 1) / splits;
+  len = (len + 63) / 64 * 64;
+  if (len < 256) len = 256;
+  const long cap64 = ((long)capacity + 63) / 64 * 64;
+  if (len > cap64) len = cap64;
+  return (int)len;
+}
+
+static int decode_geometry(int B, int Hkv, int capacity, int split_len, int* out_len, int* out_splits) {
+  if (split_len == 0) split_len = pjx_attn_decode_default_split_len(B, Hkv, capacity);
+  if (split_len < 64 || split_len % 64 != 0)
+    return fail(PJX_ERR_BAD_ARG, "split_len must be a positive multiple of 64 (got %d)", split_len);
+  *out_len = split_len;
+  *out_splits = capacity > 0 ? (capacity + split_len - 1) / split_len : 1;
+  return PJX_OK;
+}
+
+size_t pjx_attn_decode_workspace_bytes(int B, int Lq, int Hq, int Hkv, int Dv, int capacity, int split_len) {
+  int len, ns;
+  if (B < 1 || Hkv < 1 || Hq < 1 || Lq < 1 || Dv < 1 || Hq % Hkv) return 0;
+  if (decode_geometry(B, Hkv, capacity, split_len, &len, &ns)) return 0;
+  const size_t rows = (size_t)(Hq / Hkv) * Lq;
+  const size_t parts = (size_t)B * Hkv * ns * rows;
+  return align_up(parts * Dv * sizeof(float)) + align_up(parts * sizeof(float));
+}
+
+int pjx_attn_decode_splitkv(const void* q, const void* k_cache, const void* v_cache, const int32_t* kv_lengths,
+                            void* o, float* lse, int B, int Lq, int Hq, int Hkv, int D, int Dv, int capacity,
+                            int dtype, float sm_scale, int split_len, int o_is_f32, void* workspace,
+                            size_t workspace_bytes, void* stream) {
+  int rc = validate_common(q, k_cache, v_cache, o, B, Lq, capacity, Hq, Hkv, D, Dv, dtype);
+  if (rc) return rc;
+  if (B == 0 || Lq == 0) return PJX_OK;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  DecodeParams p;
+  p.q = q; p.k = k_cache; p.v = v_cache; p.kv_lengths = kv_lengths; p.o = o; p.lse = lse;
+  p.B = B; p.Lq = Lq; p.Hq = Hq; p.Hkv = Hkv; p.D = D; p.Dv = Dv; p.capacity = capacity;
+  p.rows = (Hq / Hkv) * Lq;
+  p.sm_scale = sm_scale;
+  p.o_is_f32 = o_is_f32 != 0;
+  const bool aligned =
+      ((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(k_cache) | reinterpret_cast<uintptr_t>(v_cache)) & 15) == 0;
+  if (!decode_fast_supported(p, dtype) || !aligned || capacity == 0) {
+    // Shapes the streaming kernel does not take: the generic forward with the
+    // key-length mask computes the same function.
+    if (o_is_f32 && dtype != PJX_F32)
+      return fail(PJX_ERR_UNSUPPORTED, "float32 partial output needs the split-KV kernel (bf16/fp16, D = Dv in {64,128}, (Hq/Hkv)*Lq <= 16)");
+    return pjx_attn_fwd(q, k_cache, v_cache, o, lse, kv_lengths, nullptr, 0, 0, B, Lq, capacity, Hq, Hkv, D, Dv,
+                        dtype, 0, sm_scale, PJX_IMPL_GENERIC, nullptr, stream);
+  }
+  if ((rc = decode_geometry(B, Hkv, capacity, split_len, &p.split_len, &p.num_splits))) return rc;
+  const size_t need = pjx_attn_decode_workspace_bytes(B, Lq, Hq, Hkv, Dv, capacity, p.split_len);
+  if (!workspace || workspace_bytes < need)
+    return fail(PJX_ERR_WORKSPACE, "decode workspace: need %zu bytes, got %zu", need, workspace ? workspace_bytes : (size_t)0);
+  const size_t parts = (size_t)B * Hkv * p.num_splits * p.rows;
+  p.o_part = static_cast<float*>(workspace);
+  p.lse_part = reinterpret_cast<float*>(static_cast<char*>(workspace) + align_up(parts * Dv * sizeof(float)));
+  return launch_decode(p, dtype, st);
+}
+
+int pjx_attn_combine(const float* o_parts, const float* lse_parts, int n_parts, int64_t n_rows, int Dv, void* o,
+                     float* lse, int dtype, void* stream) {
+  if (n_parts < 1 || n_rows < 0 || Dv < 1) return fail(PJX_ERR_BAD_ARG, "combine: n_parts=%d n_rows=%lld Dv=%d", n_parts, (long long)n_rows, Dv);
+  if (n_rows > 0 && (!o_parts || !lse_parts || !o)) return fail(PJX_ERR_BAD_ARG, "combine: null buffer");
+  if (n_rows > 2147483647LL) return fail(PJX_ERR_UNSUPPORTED, "combine: too many rows");
+  return launch_combine_parts(o_parts, lse_parts, n_parts, n_rows, Dv, o, lse, dtype, static_cast<cudaStream_t>(stream));
+}
+
+size_t pjx_mla_workspace_bytes(int B, int S, int H, int Dqk, int Dv, int R, int dtype, int has_projections) {
+  (void)R;
+  if (!has_projections) return 0;
+  const size_t es = dtype_size(dtype);
+  return align_up((size_t)B * S * H * Dqk * es) + align_up((size_t)B * S * H * Dv * es);
+}
+
+int pjx_mla_fwd(const void* q, const void* cache, const void* wk, const void* wv, void* o, float* lse,
+                const int32_t* kv_lengths, const float* bias, int64_t bias_batch_stride, int64_t bias_head_stride,
+                int B, int Lq, int S, int H, int Dqk, int Dv, int R, int dtype, int causal, float sm_scale, int impl,
+                void* workspace, size_t workspace_bytes, int32_t* status, void* stream) {
+  // probjax/nn/pallas_kernels/kernels/latent_attention.py:668-696
+  if ((wk == nullptr) != (wv == nullptr))
+    return fail(PJX_ERR_BAD_ARG, "provide both wk and wv (materialized) or neither (absorbed); mixing the two is not supported");
+  if (B < 0 || Lq < 0 || S < 0 || H < 1 || Dqk < 1 || Dv < 1 || R < 1)
+    return fail(PJX_ERR_BAD_ARG, "mla: bad dimension");
+  if (!wk && Dqk != R)
+    return fail(PJX_ERR_BAD_ARG, "absorbed mode (wk=None) requires qk_head_dim == kv_lora_rank (%d != %d)", Dqk, R);
+  if (!wk && Dv != R) return fail(PJX_ERR_BAD_ARG, "absorbed mode: the output width equals the latent width (%d != %d)", Dv, R);
+  if (B == 0 || Lq == 0) return PJX_OK;
+  if (!q || !cache || !o) return fail(PJX_ERR_BAD_ARG, "mla: null buffer");
+  if (!wk) {
+    // K = V = latent, one shared KV head (latent_attention.py:604-607).
+    return pjx_attn_fwd(q, cache, cache, o, lse, kv_lengths, bias, bias_batch_stride, bias_head_stride, B, Lq, S, H,
+                        1, R, R, dtype, causal, sm_scale, impl, status, stream);
+  }
+  const size_t need = pjx_mla_workspace_bytes(B, S, H, Dqk, Dv, R, dtype, 1);
+  if (!workspace || workspace_bytes < need)
+    return fail(PJX_ERR_WORKSPACE, "mla workspace: need %zu bytes, got %zu", need, workspace ? workspace_bytes : (size_t)0);
+  const size_t es = dtype_size(dtype);
+  void* kmat = workspace;
+  void* vmat = static_cast<char*>(workspace) + align_up((size_t)B * S * H * Dqk * es);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  int rc;
+  if ((rc = launch_gemm_tn(cache, wk, kmat, (int64_t)B * S, H * Dqk, R, dtype, impl, st))) return rc;
+  if ((rc = launch_gemm_tn(cache, wv, vmat, (int64_t)B * S, H * Dv, R, dtype, impl, st))) return rc;
+  return pjx_attn_fwd(q, kmat, vmat, o, lse, kv_lengths, bias, bias_batch_stride, bias_head_stride, B, Lq, S, H, H,
+                      Dqk, Dv, dtype, causal, sm_scale, impl, status, stream);
+}
+
+size_t pjx_attn_fwd_host_staging_bytes(int bias_batch, int bias_heads, int has_lse, int B, int Lq, int Lkv, int Hq,
+                                       int Hkv, int D, int Dv, int dtype) {
+  const size_t es = dtype_size(dtype);
+  size_t n = 0;
+  n += align_up((size_t)B * Lq * Hq * D * es);
+  n += align_up((size_t)B * Lkv * Hkv * D * es);
+  n += align_up((size_t)B * Lkv * Hkv * Dv * es);
+  n += align_up((size_t)B * Lq * Hq * Dv * es);
+  n += align_up((size_t)B * Hq * Lq * sizeof(float) * (has_lse ? 1 : 0));
+  n += align_up((size_t)B * sizeof(int32_t));
+  n += align_up((size_t)bias_batch * bias_heads * Lq * Lkv * sizeof(float));
+  n += align_up(sizeof(int32_t));
+  return n;
+}
+
+int pjx_attn_fwd_host(const void* q, const void* k, const void* v, void* o, float* lse, const int32_t* kv_lengths,
+                      const float* bias, int bias_batch, int bias_heads, int B, int Lq, int Lkv, int Hq, int Hkv,
+                      int D, int Dv, int dtype, int causal, float sm_scale, int impl, void* staging,
+                      size_t staging_bytes, void* stream) {
+  int rc = validate_common(q, k, v, o, B, Lq, Lkv, Hq, Hkv, D, Dv, dtype);
+  if (rc) return rc;
+  if (bias && !((bias_batch == 1 || bias_batch == B) && (bias_heads == 1 || bias_heads == Hq)))
+    return fail(PJX_ERR_BAD_ARG, "bias must be [B|1, H|1, Lq, Lkv]; got leading dims (%d, %d)", bias_batch, bias_heads);
+  if (!bias) bias_batch = bias_heads = 0;
+  const size_t need = pjx_attn_fwd_host_staging_bytes(bias_batch, bias_heads, lse != nullptr, B, Lq, Lkv, Hq, Hkv, D, Dv, dtype);
+  if (!staging || staging_bytes < need)
+    return fail(PJX_ERR_WORKSPACE, "host forward staging: need %zu bytes, got %zu", need, staging ? staging_bytes : (size_t)0);
+  if (B == 0 || Lq == 0) return PJX_OK;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const size_t es = dtype_size(dtype);
+  char* base = static_cast<char*>(staging);
+  size_t off = 0;
+  auto take = [&](size_t bytes) { char* ptr = base + off; off += align_up(bytes); return ptr; };
+  const size_t qb = (size_t)B * Lq * Hq * D * es, kb = (size_t)B * Lkv * Hkv * D * es,
+               vb = (size_t)B * Lkv * Hkv * Dv * es, ob = (size_t)B * Lq * Hq * Dv * es,
+               lb = lse ? (size_t)B * Hq * Lq * sizeof(float) : 0, nb = (size_t)B * sizeof(int32_t),
+               bb = (size_t)bias_batch * bias_heads * Lq * Lkv * sizeof(float);
+  char *dq = take(qb), *dk = take(kb), *dv = take(vb), *dout = take(ob), *dl = take(lb), *dn = take(nb), *db = take(bb),
+       *ds = take(sizeof(int32_t));
+  if ((rc = check_cuda(cudaMemcpyAsync(dq, q, qb, cudaMemcpyHostToDevice, st), "copy q to device"))) return rc;
+  if (kb && (rc = check_cuda(cudaMemcpyAsync(dk, k, kb, cudaMemcpyHostToDevice, st), "copy k to device"))) return rc;
+  if (vb && (rc = check_cuda(cudaMemcpyAsync(dv, v, vb, cudaMemcpyHostToDevice, st), "copy v to device"))) return rc;
+  if (kv_lengths && (rc = check_cuda(cudaMemcpyAsync(dn, kv_lengths, nb, cudaMemcpyHostToDevice, st), "copy kv_lengths to device"))) return rc;
+  if (bias && (rc = check_cuda(cudaMemcpyAsync(db, bias, bb, cudaMemcpyHostToDevice, st), "copy bias to device"))) return rc;
+  if ((rc = check_cuda(cudaMemsetAsync(ds, 0, sizeof(int32_t), st), "clear status"))) return rc;
+  const int64_t bhs = bias ? (bias_heads == 1 ? 0 : (int64_t)Lq * Lkv) : 0;
+  const int64_t bbs = bias ? (bias_batch == 1 ? 0 : (int64_t)bias_heads * Lq * Lkv) : 0;
+  rc = pjx_attn_fwd(dq, dk, dv, dout, lse ? reinterpret_cast<float*>(dl) : nullptr,
+                    kv_lengths ? reinterpret_cast<const int32_t*>(dn) : nullptr,
+                    bias ? reinterpret_cast<const float*>(db) : nullptr, bbs, bhs, B, Lq, Lkv, Hq, Hkv, D, Dv, dtype,
+                    causal, sm_scale, impl, reinterpret_cast<int32_t*>(ds), stream);
+  if (rc) return rc;
+  if ((rc = check_cuda(cudaMemcpyAsync(o, dout, ob, cudaMemcpyDeviceToHost, st), "copy o to host"))) return rc;
+  if (lse && (rc = check_cuda(cudaMemcpyAsync(lse, dl, lb, cudaMemcpyDeviceToHost, st), "copy lse to host"))) return rc;
+  int32_t hs = 0;
+  if ((rc = check_cuda(cudaMemcpyAsync(&hs, ds, sizeof(int32_t), cudaMemcpyDeviceToHost, st), "copy status to host"))) return rc;
+  if ((rc = check_cuda(cudaStreamSynchronize(st), "synchronise after host forward"))) return rc;
+  if (hs) return fail(hs, "the forward kernel reported status %d (%s)", hs, pjx_status_string(hs));
+  return PJX_OK;
+}
+
+int pjx_read_status(const int32_t* status, void* stream) {
+  if (!status) return PJX_OK;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  int32_t hs = 0;
+  int rc;
+  if ((rc = check_cuda(cudaMemcpyAsync(&hs, status, sizeof(int32_t), cudaMemcpyDeviceToHost, st), "read status"))) return rc;
+  if ((rc = check_cuda(cudaStreamSynchronize(st), "synchronise for status"))) return rc;
+  if (hs) return fail(hs, "kernel status %d (%s)", hs, pjx_status_string(hs));
+  return PJX_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,102 @@
+// Shared declarations of the attention library: element traits, the launch
+// parameter blocks, error plumbing and the internal launcher prototypes.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/pjx_attention.h"
+
+namespace pjx {
+
+constexpr float kLog2e = 1.4426950408889634f;
+constexpr float kLn2 = 0.6931471805599453f;
+
+// ---------------------------------------------------------------------------
+// Element traits
+// ---------------------------------------------------------------------------
+template <typename T>
+struct Elem;
+template <>
+struct Elem<float> {
+  static __device__ __forceinline__ float to_f(float x) { return x; }
+  static __device__ __forceinline__ float from_f(float x) { return x; }
+  static __device__ __forceinline__ float round(float x) { return x; }
+};
+template <>
+struct Elem<__nv_bfloat16> {
+  static __device__ __forceinline__ float to_f(__nv_bfloat16 x) { return __bfloat162float(x); }
+  static __device__ __forceinline__ __nv_bfloat16 from_f(float x) { return __float2bfloat16_rn(x); }
+  static __device__ __forceinline__ float round(float x) {
+    return __bfloat162float(__float2bfloat16_rn(x));
+  }
+};
+template <>
+struct Elem<__half> {
+  static __device__ __forceinline__ float to_f(__half x) { return __half2float(x); }
+  static __device__ __forceinline__ __half from_f(float x) { return __float2half_rn(x); }
+  static __device__ __forceinline__ float round(float x) {
+    return __half2float(__float2half_rn(x));
+  }
+};
+
+inline size_t dtype_size(int dtype) { return dtype == PJX_F32 ? 4 : 2; }
+
+// ---------------------------------------------------------------------------
+// Parameter block of the forward kernels
+// ---------------------------------------------------------------------------
+struct FwdParams {
+  const void* q;
+  const void* k;
+  const void* v;
+  void* o;
+  float* lse;                 // [B, Hq, Lq] or null
+  const int32_t* kv_lengths;  // [B] or null
+  const float* bias;          // [Bb, Hb, Lq, Lkv] or null
+  int64_t bias_bs, bias_hs;   // element strides of the bias batch / head axes (0 = broadcast)
+  int B, Lq, Lkv, Hq, Hkv, D, Dv;
+  int causal;
+  float sm_scale;
+  int32_t* status;  // device status word or null
+};
+
+struct DecodeParams {
+  const void* q;
+  const void* k;
+  const void* v;
+  const int32_t* kv_lengths;
+  void* o;
+  float* lse;
+  float* o_part;    // [B, Hkv, S, R, Dv] fp32
+  float* lse_part;  // [B, Hkv, S, R] fp32, base 2, -inf for a split without keys
+  int B, Lq, Hq, Hkv, D, Dv, capacity;
+  int split_len, num_splits, rows;  // rows = (Hq / Hkv) * Lq
+  float sm_scale;
+  int o_is_f32;
+};
+
+// ---------------------------------------------------------------------------
+// Error plumbing (host)
+// ---------------------------------------------------------------------------
+int fail(int status, const char* fmt, ...);
+int check_cuda(cudaError_t e, const char* what);
+void count_launch(int n = 1);
+
+// ---------------------------------------------------------------------------
+// Launchers implemented in the kernel translation units. Each returns a
+// pjx_status and enqueues on `stream` only.
+// ---------------------------------------------------------------------------
+int launch_fwd_generic(const FwdParams& p, int dtype, cudaStream_t stream);
+bool fwd_sm100_supported(const FwdParams& p, int dtype, const char** why);
+int launch_fwd_sm100(const FwdParams& p, int dtype, cudaStream_t stream);
+bool decode_fast_supported(const DecodeParams& p, int dtype);
+int launch_decode(const DecodeParams& p, int dtype, cudaStream_t stream);
+int launch_combine_parts(const float* o_parts, const float* lse_parts, int n_parts, int64_t n_rows,
+                         int Dv, void* o, float* lse, int dtype, cudaStream_t stream);
+// C[M, N] = A[M, K] . B[N, K]^T, all row-major, fp32 accumulation, C in `dtype`.
+int launch_gemm_tn(const void* A, const void* Bm, void* C, int64_t M, int N, int K, int dtype,
+                   int impl, cudaStream_t stream);
+
+}  // namespace pjx

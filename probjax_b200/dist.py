@@ -1,0 +1,90 @@
+"""Sequence-sharded decode: the KV cache of every sequence is split across the
+ranks of a process group, each rank runs the split-KV decode on its part, and the
+per-rank ``(o, lse)`` partials are exchanged with one all-gather and combined
+exactly.
+
+The reference never shards the sequence axis (probjax/nn/sharding.py:70, 97); its
+single-GPU split-KV combine (probjax/nn/pallas_kernels/kernels/
+attention_splitkv.py:236-250) is the same log-sum-exp algebra applied across
+ranks here.
+
+Placement is block-cyclic by pages of ``page`` tokens: page ``p`` of a sequence
+lives on rank ``p % world``, compacted in order on that rank.  With ragged lengths
+a contiguous split would leave the last ranks nearly empty; block-cyclic keeps
+every rank within one page of ``len / world``.  Attention over a set of keys does
+not depend on their order, so a rank only needs its local valid length.
+
+The exchange is an all-gather of one fp32 record per (sequence, query head):
+``Dv`` output values plus the LSE.  Records land in this rank's own memory first
+and the combine kernel reads them with ordinary loads.
+"""
+
+from __future__ import annotations
+
+import torch
+import torch.distributed as dist
+
+from . import attention as _att
+
+
+def local_lengths(kv_lengths: torch.Tensor, rank: int, world: int, page: int) -> torch.Tensor:
+    """Valid tokens rank ``rank`` holds of sequences with global ``kv_lengths``."""
+    kv_lengths = kv_lengths.to(torch.int64)
+    full_pages = kv_lengths // page
+    tail = kv_lengths - full_pages * page
+    mine_full = (full_pages - rank + world - 1) // world  # pages p < full_pages with p % world == rank
+    mine_full = torch.clamp(mine_full, min=0)
+    has_tail = (full_pages % world) == rank
+    return (mine_full * page + torch.where(has_tail, tail, torch.zeros_like(tail))).to(torch.int32)
+
+
+def local_capacity(capacity: int, rank: int, world: int, page: int) -> int:
+    """Rows rank ``rank`` needs for a cache of ``capacity`` tokens."""
+    return int(local_lengths(torch.tensor([capacity]), rank, world, page)[0])
+
+
+def shard_cache(cache: torch.Tensor, rank: int, world: int, page: int) -> torch.Tensor:
+    """The pages of ``cache [B, cap, H, D]`` that live on ``rank``, compacted."""
+    B, cap, H, D = cache.shape
+    idx = torch.arange(cap, device=cache.device)
+    mine = idx[(idx // page) % world == rank]
+    return cache.index_select(1, mine).contiguous()
+
+
+def decode_sharded(q, k_local, v_local, kv_lengths, *, page: int, sm_scale: float, group=None,
+                   return_lse: bool = False, _local_fn=None, _combine_fn=None):
+    """Decode step with the KV sequence split across ``group``.
+
+    ``q [B, Lq, Hq, D]`` is replicated; ``k_local`` / ``v_local`` are this rank's
+    shards (:func:`shard_cache`); ``kv_lengths [B]`` are the *global* valid
+    lengths.  Every rank returns the full result ``[B, Lq, Hq, Dv]`` in
+    ``q.dtype`` (and the natural-log LSE ``[B, Hq, Lq]``).
+
+    ``_local_fn`` / ``_combine_fn`` replace the two kernel calls; they exist so the
+    exchange and the partition arithmetic can be exercised on CPU ranks.
+    """
+    world = dist.get_world_size(group) if dist.is_initialized() else 1
+    rank = dist.get_rank(group) if dist.is_initialized() else 0
+    lens = local_lengths(torch.as_tensor(kv_lengths).cpu(), rank, world, page).to(q.device)
+    local_fn = _local_fn or (lambda q_, k_, v_, l_: _att.decode_forward(
+        q_, k_, v_, kv_lengths=l_, sm_scale=sm_scale, return_lse=True, partial_f32=True))
+    combine_fn = _combine_fn or (lambda o_, l_: _att.combine_partials(o_, l_, out_dtype=q.dtype))
+    o_loc, lse_loc = local_fn(q, k_local, v_local, lens)  # [B,Lq,Hq,Dv] fp32, [B,Hq,Lq]
+    B, Lq, Hq, Dv = o_loc.shape
+    # one record per (b, t, h): Dv outputs + the LSE, rows in [B, Lq, Hq] order
+    rec = torch.empty((B, Lq, Hq, Dv + 1), dtype=torch.float32, device=o_loc.device)
+    rec[..., :Dv] = o_loc
+    rec[..., Dv] = lse_loc.permute(0, 2, 1)
+    if world > 1:
+        gathered = torch.empty((world,) + tuple(rec.shape), dtype=torch.float32, device=rec.device)
+        dist.all_gather([gathered[r] for r in range(world)], rec, group=group)
+    else:
+        gathered = rec[None]
+    n = B * Lq * Hq
+    o_parts = gathered[..., :Dv].reshape(world, n, Dv)
+    lse_parts = gathered[..., Dv].reshape(world, n)
+    o, lse = combine_fn(o_parts, lse_parts)
+    o = o.reshape(B, Lq, Hq, Dv)
+    if return_lse:
+        return o, lse.reshape(B, Lq, Hq).permute(0, 2, 1).contiguous()
+    return o

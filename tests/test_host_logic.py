@@ -1,0 +1,250 @@
+"""Host-side logic that needs no GPU: the C-ABI library loads and exports every
+declared symbol, argument validation mirrors the reference's errors, mask
+lowering, the dispatch seam, and the partition arithmetic of the sharded decode
+(including a two-rank gloo run of the exchange)."""
+
+import ctypes
+import os
+import re
+import socket
+import sys
+
+import numpy as np
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _header_functions():
+    text = open(os.path.join(ROOT, "include", "pjx_attention.h")).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(pjx_[a-z0-9_]+)\s*\(", text)))
+
+
+def test_library_exports_every_declared_symbol(built_lib):
+    from probjax_b200 import _lib
+
+    handle = ctypes.CDLL(os.fspath(built_lib))
+    names = _header_functions()
+    assert len(names) >= 12
+    for name in names:
+        assert hasattr(handle, name), f"{name} is declared in the header but not exported"
+    # the ctypes table binds exactly the declared functions
+    assert sorted(_lib.SIGNATURES) == names
+    L = _lib.lib()
+    assert L.pjx_version() >= 100
+    assert L.pjx_status_string(0) == b"ok"
+
+
+def test_abi_validation_without_a_gpu(built_lib):
+    """Argument errors are reported before anything touches the device."""
+    from probjax_b200 import _lib
+
+    L = _lib.lib()
+    # Hq not a multiple of Hkv -> bad argument mentioning "multiple"
+    rc = L.pjx_attn_fwd(None, None, None, None, None, None, None, 0, 0, 1, 4, 4, 3, 2, 8, 8, 0, 0, 1.0, 0, None, None)
+    assert rc == _lib.PJX_ERR_BAD_ARG and "multiple" in _lib.last_error()
+    with pytest.raises(ValueError, match="multiple"):
+        _lib.check(rc)
+    # unknown dtype
+    assert L.pjx_attn_fwd(None, None, None, None, None, None, None, 0, 0, 1, 4, 4, 2, 2, 8, 8, 7, 0, 1.0, 0, None, None) == _lib.PJX_ERR_BAD_ARG
+    # empty batch is a no-op
+    assert L.pjx_attn_fwd(None, None, None, None, None, None, None, 0, 0, 0, 4, 4, 2, 2, 8, 8, 1, 0, 1.0, 0, None, None) == 0
+    # mla: one projection without the other
+    rc = L.pjx_mla_fwd(1, 1, 1, None, 1, None, None, None, 0, 0, 1, 4, 4, 2, 8, 8, 8, 1, 0, 1.0, 0, None, 0, None, None)
+    assert rc == _lib.PJX_ERR_BAD_ARG and "both wk and wv" in _lib.last_error()
+    # absorbed form needs Dqk == R
+    rc = L.pjx_mla_fwd(1, 1, None, None, 1, None, None, None, 0, 0, 1, 4, 4, 2, 16, 8, 8, 1, 0, 1.0, 0, None, 0, None, None)
+    assert rc == _lib.PJX_ERR_BAD_ARG and "qk_head_dim == kv_lora_rank" in _lib.last_error()
+    # decode workspace query and split-length rule
+    assert L.pjx_attn_decode_default_split_len(16, 8, 32768) % 64 == 0
+    need = L.pjx_attn_decode_workspace_bytes(16, 1, 32, 8, 128, 32768, 1024)
+    assert need >= 16 * 8 * 32 * 4 * 129 * 4
+    rc = L.pjx_attn_decode_splitkv(16, 16, 16, None, 16, None, 1, 1, 8, 2, 128, 128, 4096, 1, 1.0, 100, 0, None, 0, None)
+    assert rc == _lib.PJX_ERR_BAD_ARG and "multiple of 64" in _lib.last_error()
+    rc = L.pjx_attn_decode_splitkv(16, 16, 16, None, 16, None, 1, 1, 8, 2, 128, 128, 4096, 1, 1.0, 256, 0, None, 0, None)
+    assert rc == _lib.PJX_ERR_WORKSPACE
+    assert L.pjx_launch_count() == 0
+
+
+def test_python_api_validation_errors():
+    import probjax_b200 as pj
+
+    q = torch.zeros(2, 8, 4, 16)
+    k = torch.zeros(2, 8, 2, 16)
+    # layers/attention.py:1503-1508: heads differ without enable_gqa
+    with pytest.raises(ValueError, match="enable_gqa=True"):
+        pj.flex_attention(q, k, k)
+    # layers/attention.py:1490-1495: dtypes differ
+    with pytest.raises(ValueError, match="same dtype"):
+        pj.flex_attention(q, k.half(), k, enable_gqa=True)
+    # kernels/attention.py:2113-2120
+    with pytest.raises(ValueError, match="multiple"):
+        pj.mha(torch.zeros(1, 4, 3, 8), torch.zeros(1, 4, 2, 8), torch.zeros(1, 4, 2, 8))
+    with pytest.raises(ValueError, match="implementation"):
+        pj.flex_attention(q, q, q, implementation="cudnn")
+    # latent_attention.py:668-696
+    with pytest.raises(ValueError, match="rank 4"):
+        pj.mla(torch.zeros(8, 4, 16), torch.zeros(8, 4, 16))
+    with pytest.raises(ValueError, match="rank 3"):
+        pj.mla(torch.zeros(1, 8, 4, 16), torch.zeros(1, 8, 4, 16))
+    with pytest.raises(ValueError, match="batch mismatch"):
+        pj.mla(torch.zeros(1, 8, 4, 16), torch.zeros(2, 8, 16))
+    with pytest.raises(ValueError, match="both wk and wv"):
+        pj.mla(torch.zeros(1, 8, 4, 16), torch.zeros(1, 8, 16), wk=torch.zeros(4, 16, 16))
+    with pytest.raises(ValueError, match="qk_head_dim == kv_lora_rank"):
+        pj.mla(torch.zeros(1, 8, 4, 16), torch.zeros(1, 8, 8))
+    with pytest.raises(ValueError, match="wk must be"):
+        pj.mla(torch.zeros(1, 8, 4, 16), torch.zeros(1, 8, 8), wk=torch.zeros(4, 8, 8), wv=torch.zeros(4, 8, 8))
+
+
+@pytest.mark.skipif(torch.cuda.is_available(), reason="checks the no-GPU behaviour")
+def test_no_cpu_fallback():
+    """Without a GPU every compute call raises; nothing is computed on the host."""
+    import probjax_b200 as pj
+
+    q = torch.zeros(1, 8, 2, 16)
+    with pytest.raises(RuntimeError, match="no CPU path"):
+        pj.flex_attention(q, q, q)
+    with pytest.raises(RuntimeError, match="no CPU path"):
+        pj.mla(torch.zeros(1, 8, 2, 16), torch.zeros(1, 8, 16))
+    assert pj.device_attention_defaults() is None
+    assert pj.b200_attention_or_none(q, q, q, sm_scale=1.0) is None
+    with pytest.raises(ValueError, match="cannot compute"):
+        pj.b200_attention_or_none(q, q, q, sm_scale=1.0, force=True)
+
+
+def test_mask_truth_tables():
+    """tests/test_attention_mask_bias.py:62-67, 130-135, 152-162, 182-188 restated."""
+    from probjax_b200 import CausalMask, KeyPaddingMask, KVLenMask, NoMask, QKVLengthMask
+
+    def idx(n):
+        return torch.arange(n, dtype=torch.int32)
+
+    assert NoMask()(idx(5), idx(7)).shape == (5, 7) and NoMask()(idx(5), idx(7)).all()
+    got = CausalMask()(idx(6), idx(6))
+    assert torch.equal(got, idx(6)[:, None] >= idx(6)[None, :])
+    got = QKVLengthMask(q_length=4, kv_length=6)(idx(7), idx(9))
+    assert torch.equal(got, (idx(7)[:, None] < 4) & (idx(9)[None, :] < 6))
+    lengths = torch.tensor([2, 4, 6], dtype=torch.int32)
+    dense = KVLenMask(lengths).dense(5, 6, batch_size=3, num_heads=2)
+    want = (idx(6)[None, :] < lengths[:, None])[:, None, None, :].expand(3, 2, 5, 6)
+    assert torch.equal(dense, want)
+    with pytest.raises(ValueError, match="does not match"):
+        KVLenMask(lengths).dense(5, 6, batch_size=2)
+    seg_q = torch.tensor([1, 3, 5, 6], dtype=torch.int32)
+    got = KeyPaddingMask(torch.tensor([6]))(idx(4), idx(6), seg_q=seg_q)
+    assert torch.equal(got, idx(6)[None, :] < seg_q[:, None])
+    both = (CausalMask() & KVLenMask(lengths)).dense(6, 6, batch_size=3)
+    assert torch.equal(both, CausalMask().dense(6, 6, batch_size=3) & KVLenMask(lengths).dense(6, 6, batch_size=3))
+
+
+def test_mask_lowering():
+    from probjax_b200 import CausalMask, ComposeMask, DenseBias, KeyPaddingMask, KVLenMask, NoMask, QKVLengthMask
+    from probjax_b200.masks import lower_bias, lower_mask
+
+    assert lower_mask(None, 2, 8, 8).causal is False
+    assert lower_mask(NoMask(), 2, 8, 8).kv_lengths is None
+    assert lower_mask(CausalMask(), 2, 8, 8).causal is True
+    lm = lower_mask(CausalMask() & KVLenMask([3, 8]), 2, 8, 8)
+    assert lm.causal and lm.kv_lengths.tolist() == [3, 8]
+    lm = lower_mask(KVLenMask([3, 8]) & QKVLengthMask(q_length=5, kv_length=6), 2, 8, 8)
+    assert lm.kv_lengths.tolist() == [3, 6] and lm.q_limit == 5
+    assert lower_mask(KeyPaddingMask(torch.tensor([4, 7])), 2, 1, 8).kv_lengths.tolist() == [4, 7]
+    with pytest.raises(NotImplementedError):
+        lower_mask(KeyPaddingMask(torch.tensor([4, 7])), 2, 4, 8)
+    with pytest.raises(NotImplementedError):
+        lower_mask(ComposeMask("or", CausalMask(), NoMask()), 2, 8, 8)
+    with pytest.raises(ValueError):
+        lower_mask(KVLenMask([1, 2, 3]), 2, 8, 8)
+    with pytest.raises(ValueError):  # attention_mask_bias.py:1815-1823
+        DenseBias(torch.zeros(8, 8))
+    b = DenseBias(torch.zeros(1, 4, 8, 8))
+    assert lower_bias(b, 2, 4, 8, 8).shape == (1, 4, 8, 8)
+    with pytest.raises(ValueError, match="shape mismatch"):
+        lower_bias(b, 2, 4, 8, 9)
+    with pytest.raises(ValueError, match="head dim"):
+        lower_bias(b, 2, 2, 8, 8)
+
+
+def test_block_cyclic_partition():
+    from probjax_b200.dist import local_capacity, local_lengths, shard_cache
+
+    rng = np.random.default_rng(0)
+    for world in (1, 2, 4, 8):
+        for page in (1, 16, 256):
+            lens = torch.from_numpy(rng.integers(0, 5000, size=32))
+            per_rank = torch.stack([local_lengths(lens, r, world, page) for r in range(world)])
+            assert torch.equal(per_rank.sum(0).to(torch.int64), lens)  # every token lives on exactly one rank
+            # brute force
+            for b in range(4):
+                t = torch.arange(int(lens[b]))
+                for r in range(world):
+                    assert int(per_rank[r, b]) == int((((t // page) % world) == r).sum())
+            assert int((per_rank.max(0).values - per_rank.min(0).values).max()) <= page
+    cache = torch.arange(2 * 40 * 1 * 1).reshape(2, 40, 1, 1)
+    parts = [shard_cache(cache, r, 4, 8) for r in range(4)]
+    assert [p.shape[1] for p in parts] == [16, 8, 8, 8]
+    assert [local_capacity(40, r, 4, 8) for r in range(4)] == [16, 8, 8, 8]
+    assert parts[1][0, :, 0, 0].tolist() == list(range(8, 16))
+    # the first local_lengths rows of a shard are exactly the valid tokens of that rank
+    lens = torch.tensor([19, 40])
+    for r in range(4):
+        ll = local_lengths(lens, r, 4, 8)
+        valid = parts[r][0, : int(ll[0]), 0, 0]
+        assert (valid < 19).all() and int(ll.sum()) > 0 or int(ll[0]) == 0
+
+
+def _free_port():
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    port = s.getsockname()[1]
+    s.close()
+    return port
+
+
+def _sharded_worker(rank, world, port, page, out_dir):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    sys.path.insert(0, ROOT)
+    import oracle
+    from probjax_b200.dist import decode_sharded, shard_cache
+
+    c = oracle.make_config(4, B=3, Hq=8, Hkv=2, D=32, cap=700, dtype="f32")
+    q, k, v, lens = c["q"], c["k"], c["v"], c["kv_lengths"]
+    lens[0] = 5  # shorter than one page: most ranks hold nothing of this sequence
+    k_loc, v_loc = shard_cache(k, rank, world, page), shard_cache(v, rank, world, page)
+
+    def local_fn(q_, k_, v_, l_):  # CPU stand-in for the decode kernel
+        o, lse = oracle.xla_attention(q_, k_, v_, kv_lengths=l_, sm_scale=c["sm_scale"], return_lse=True)
+        return o.float(), lse
+
+    def combine_fn(o_parts, lse_parts):  # CPU stand-in for pjx_attn_combine (natural log, +inf = empty)
+        neg = torch.where(torch.isinf(lse_parts) & (lse_parts > 0), torch.tensor(-float("inf")), lse_parts)
+        m = neg.max(0).values
+        m = torch.where(torch.isfinite(m), m, torch.zeros_like(m))
+        w = torch.exp(neg - m)
+        den = w.sum(0)
+        o = (w[..., None] * o_parts).sum(0) / torch.where(den > 0, den, torch.ones_like(den))[..., None]
+        return o, torch.where(den > 0, m + torch.log(den), torch.tensor(float("inf")))
+
+    o, lse = decode_sharded(q, k_loc, v_loc, lens, page=page, sm_scale=c["sm_scale"], return_lse=True,
+                            _local_fn=local_fn, _combine_fn=combine_fn)
+    want, want_lse = oracle.xla_attention(q, k, v, kv_lengths=lens, sm_scale=c["sm_scale"], return_lse=True)
+    err = float((o - want).abs().max())
+    err_lse = float((lse - want_lse).abs().max())
+    torch.save({"err": err, "err_lse": err_lse}, os.path.join(out_dir, f"r{rank}.pt"))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_sharded_decode_two_ranks_gloo(tmp_path):
+    """World size 2 on CPU: partition, all-gather and combine reproduce the unsharded answer."""
+    world, page = 2, 64
+    mp.spawn(_sharded_worker, args=(world, _free_port(), page, str(tmp_path)), nprocs=world, join=True)
+    for r in range(world):
+        res = torch.load(os.path.join(str(tmp_path), f"r{r}.pt"))
+        assert res["err"] < 1e-5 and res["err_lse"] < 1e-5
