@@ -1,0 +1,387 @@
+#!/usr/bin/env python
+"""Benchmark of the attention forward hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+Headline (``value``): GQA prefill forward, bf16, B=4 Hq=32 Hkv=8 S=4096 D=128,
+non-causal, in TFLOP/s with the inputs resident in HBM.  One step is one forward
+over the whole batch.  With N > 1 (launched by torchrun, one rank per GPU) every
+rank runs the same per-GPU batch (weak scaling, no collective on the data path)
+and ``value`` is the aggregate over all ranks divided by the slowest rank's time.
+
+The same JSON line also carries the end-to-end number through the public API with
+pinned host buffers (``e2e``), the roofline of the dominant kernel, the CPU
+baseline (the oracle port on the host cores, bounded sample) and, as additional
+objects, the other configurations: causal prefill, masked + biased attention,
+latent attention, split-KV decode (HBM GB/s) and -- with N > 1 -- the decode with
+the KV sequence sharded over the ranks plus its all-gather and combine.
+
+``--impl reference`` times the reference's CPU attention path (the oracle port:
+the reference itself needs jax, which is not installable offline) on the host
+cores.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+import torch  # noqa: E402
+
+C2 = dict(B=4, Hq=32, Hkv=8, S=4096, D=128)
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}
+
+
+def peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    try:
+        with open(path) as f:
+            p = json.load(f)
+        return {"hbm_gbs": float(p["hbm_gbs"]), "bf16_tflops": float(p["bf16_tflops"]),
+                "bf16_tflops_sustained": float(p.get("bf16_tflops_sustained", p["bf16_tflops"])), "source": "measured"}
+    except Exception:
+        return dict(FALLBACK_PEAKS, bf16_tflops_sustained=1400.0, source="fallback")
+
+
+def prefill_flops(B, Hq, Lq, Lkv, D, Dv, causal):
+    if causal:  # sum over rows of (i + 1) keys, rows beyond Lkv see Lkv keys
+        pairs = sum(min(i + 1, Lkv) for i in range(Lq))
+    else:
+        pairs = Lq * Lkv
+    return 2.0 * B * Hq * pairs * (D + Dv)
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while a region runs."""
+
+    Q = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index=0):
+        self.index, self.rows, self.proc = index, [], None
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "100"],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.th = threading.Thread(target=self._read, daemon=True)
+            self.th.start()
+        except Exception:
+            self.proc = None
+        return self
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([x.strip() for x in line.split(",")])
+
+    def __exit__(self, *a):
+        if self.proc:
+            time.sleep(0.15)
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=2)
+            except Exception:
+                self.proc.kill()
+
+    def summary(self):
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for r in self.rows:
+            try:
+                sm.append(float(r[0]))
+                mx.append(float(r[1]))
+                for nm, val in zip(names, r[4:8]):
+                    if val.lower().startswith("active"):
+                        reasons.add(nm)
+            except Exception:
+                continue
+        if not sm:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        busy = sorted(sm)[len(sm) // 2:]  # upper half: samples taken under load
+        return {"sm_mhz": statistics.median(busy), "sm_max_mhz": max(mx), "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def time_steps(fn, steps, warmup, dist_on=False):
+    """W untimed steps, then exactly K steps between CUDA events on the launching
+    stream, bracketed by barrier + synchronize. Returns total milliseconds."""
+    import torch.distributed as dist
+
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    if dist_on:
+        dist.barrier()
+        torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    if dist_on:
+        dist.barrier()
+        torch.cuda.synchronize()
+    return e0.elapsed_time(e1)
+
+
+def max_over_ranks(ms, dist_on):
+    if not dist_on:
+        return ms
+    import torch.distributed as dist
+
+    t = torch.tensor([ms], dtype=torch.float64, device="cuda")
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return float(t.item())
+
+
+def cpu_baseline(budget_s=12.0, threads=None):
+    """The oracle port on the host cores: configuration 2 (non-causal) one batch
+    row at a time until about `budget_s` seconds are spent (at least one row)."""
+    import oracle
+
+    threads = threads or os.cpu_count() or 1
+    torch.set_num_threads(threads)
+    c = oracle.make_config(2, B=1)
+    oracle.xla_attention(c["q"][:, :512], c["k"][:, :512], c["v"][:, :512], sm_scale=c["sm_scale"])  # warm the pool
+    done, t0 = 0, time.perf_counter()
+    while done < C2["B"] and (done == 0 or time.perf_counter() - t0 < budget_s):
+        oracle.xla_attention(c["q"], c["k"], c["v"], sm_scale=c["sm_scale"])
+        done += 1
+    dt = time.perf_counter() - t0
+    fl = prefill_flops(done, C2["Hq"], C2["S"], C2["S"], C2["D"], C2["D"], False)
+    return {"value": fl / dt / 1e12, "unit": "TFLOP/s", "cores": threads, "kind": "port",
+            "sample": f"{done} of {C2['B']} batch rows of the workload (B={done} Hq=32 Hkv=8 S=4096 D=128, non-causal), "
+                      f"{dt:.1f} s, torch CPU fp32 restatement of the reference's XLA path"}
+
+
+def run_reference(args, rank):
+    """--impl reference: the reference's CPU attention path on the host cores."""
+    if rank != 0:
+        return
+    import oracle
+
+    threads = os.cpu_count() or 1
+    torch.set_num_threads(threads)
+    c = oracle.make_config(2, B=1)
+    for _ in range(min(args.warmup, 1)):
+        oracle.xla_attention(c["q"], c["k"], c["v"], sm_scale=c["sm_scale"])
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        oracle.xla_attention(c["q"], c["k"], c["v"], sm_scale=c["sm_scale"])
+    dt = time.perf_counter() - t0
+    fl = prefill_flops(1, C2["Hq"], C2["S"], C2["S"], C2["D"], C2["D"], False) * args.steps
+    val = fl / dt / 1e12
+    sample = "each step = 1 of 4 batch rows of the workload (B=1 Hq=32 Hkv=8 S=4096 D=128, non-causal)"
+    print(json.dumps({
+        "impl": "reference", "metric": "attn_fwd_tflops", "value": val, "unit": "TFLOP/s", "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": min(args.warmup, 1), "ms_per_step": dt / args.steps * 1e3,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": "GQA prefill fwd bf16 B4 Hq32 Hkv8 S4096 D128 non-causal", "sample": sample},
+        "cpu_baseline": {"value": val, "unit": "TFLOP/s", "cores": threads, "kind": "port", "sample": sample},
+        "e2e": {"value": val, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "note": "oracle port of probjax's XLA CPU attention path (the reference needs jax, not installable offline)",
+    }), flush=True)
+
+
+def bench_extra(name, fn, steps, warmup, work, unit, peak, bound, pk_note):
+    """Time one secondary configuration; returns a small dict (never raises)."""
+    try:
+        ms = time_steps(fn, steps, warmup) / steps
+        ach = work / (ms * 1e-3)
+        return {"ms": ms, "value": ach, "unit": unit, "roofline": {"bound": bound, "achieved": ach, "peak": peak,
+                                                                   "unit": unit, "frac": ach / peak, "of": pk_note}}
+    except Exception as e:  # keep the headline line alive
+        return {"error": f"{type(e).__name__}: {e}"[:300]}
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--skip-extras", action="store_true", help="headline only (used for profiling captures)")
+    ap.add_argument("--skip-cpu", action="store_true", help="do not time the CPU baseline")
+    ap.add_argument("--kernel", default=None, choices=[None, "b200:generic", "b200:tcgen05"],
+                    help="force one forward kernel for the headline (default: the library's own choice)")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if args.impl == "reference":
+        run_reference(args, rank)
+        return
+
+    import oracle
+    import probjax_b200 as pj
+    from probjax_b200 import _lib
+
+    _lib.lib()  # raises if the CUDA library is not built: there is no other path
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    dist_on = world > 1
+    if dist_on:
+        import torch.distributed as dist
+
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=dev)
+    pk = peaks()
+
+    # ---------------------------------------------------------------- headline
+    c = oracle.make_config(2)
+    q, k, v = c["q"].to(dev), c["k"].to(dev), c["v"].to(dev)
+    sc = c["sm_scale"]
+    flops = prefill_flops(C2["B"], C2["Hq"], C2["S"], C2["S"], C2["D"], C2["D"], False)
+
+    def step():
+        return pj.attention_forward(q, k, v, sm_scale=sc, impl=args.kernel)
+
+    n0 = _lib.launch_count()
+    step()
+    launches_per_step = _lib.launch_count() - n0  # kernels of this library per step
+    with ClockSampler(local_rank) as cs:
+        ms_total = time_steps(step, args.steps, args.warmup, dist_on)
+    pj.check_status(dev)
+    ms_total = max_over_ranks(ms_total, dist_on)
+    ms = ms_total / args.steps
+    value = flops * world / (ms * 1e-3) / 1e12
+    per_gpu = flops / (ms * 1e-3) / 1e12
+    clocks = cs.summary()
+
+    # ------------------------------------------------------------- end to end
+    qh, kh, vh = c["q"].pin_memory(), c["k"].pin_memory(), c["v"].pin_memory()
+    e2e_steps = max(3, min(args.steps, 10))
+
+    oh = torch.empty(tuple(q.shape), dtype=q.dtype, pin_memory=True)
+
+    def step_host():  # H2D q,k,v + kernel + D2H o; returns after the result is in host memory
+        return pj.attention_forward(qh, kh, vh, sm_scale=sc, out=oh)
+
+    ms_e2e = max_over_ranks(time_steps(step_host, e2e_steps, 3, dist_on), dist_on) / e2e_steps
+    h2d = sum(t.numel() * t.element_size() for t in (qh, kh, vh))
+    d2h = q.numel() * q.element_size()
+    e2e = {"value": flops * world / (ms_e2e * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": ms_e2e,
+           "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+           "call": "probjax_b200.attention_forward on pinned host tensors (pjx_attn_fwd_host)"}
+
+    out = {
+        "metric": "attn_fwd_tflops", "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": "GQA prefill fwd bf16 B4 Hq32 Hkv8 S4096 D128 non-causal (per GPU)",
+                   "l2": "inputs+outputs 335 MB per step exceed the 126 MB L2; no flush needed",
+                   "parallelism": f"batch-sharded x{world}, no collective" if world > 1 else "single GPU"},
+        "roofline": {"bound": "tensor", "achieved": per_gpu, "peak": pk["bf16_tflops"], "unit": "TFLOP/s",
+                     "frac": per_gpu / pk["bf16_tflops"], "traffic": None,
+                     "of": f"{pk['source']} burst bf16 peak", "kernel": "attn_fwd_sm100_kernel<128,128,128,2,2,bf16>",
+                     "frac_of_sustained": per_gpu / pk["bf16_tflops_sustained"]},
+        "e2e": e2e, "gpu_launches": int(launches_per_step * args.steps), "clocks": clocks,
+    }
+
+    # ------------------------------------------------- other configurations
+    if not args.skip_extras:
+        xs, xw = max(5, min(args.steps, 20)), 3
+        extras = {}
+        fl_c = prefill_flops(C2["B"], C2["Hq"], C2["S"], C2["S"], C2["D"], C2["D"], True)
+        extras["prefill_causal"] = bench_extra(
+            "causal", lambda: pj.attention_forward(q, k, v, causal=True, sm_scale=sc), xs, xw, fl_c / 1e12,
+            "TFLOP/s", pk["bf16_tflops"], "tensor", pk["source"])
+        try:
+            c3 = oracle.make_config(3)
+            q3, k3, v3 = c3["q"].to(dev), c3["k"].to(dev), c3["v"].to(dev)
+            l3, b3 = c3["kv_lengths"].to(dev), c3["bias"].to(dev)
+            fl3 = 4.0 * 16 * 1024 * 64 * float(c3["kv_lengths"].sum())
+            extras["masked_bias"] = bench_extra(
+                "c3", lambda: pj.attention_forward(q3, k3, v3, kv_lengths=l3, bias=b3, sm_scale=c3["sm_scale"]), xs, xw,
+                fl3 / 1e12, "TFLOP/s", pk["bf16_tflops"], "tensor", pk["source"])
+            by3 = 2 * q3.numel() * 2 + 2 * 16 * 64 * 2 * float(c3["kv_lengths"].sum()) + 4.0 * 16 * 1024 * float(c3["kv_lengths"].max())
+            if "ms" in extras["masked_bias"]:
+                extras["masked_bias"]["hbm_gbs"] = by3 / (extras["masked_bias"]["ms"] * 1e-3) / 1e9
+            del q3, k3, v3, b3
+        except Exception as e:
+            extras["masked_bias"] = {"error": str(e)[:300]}
+        try:
+            c5 = oracle.make_config(5)
+            q5, ch5, wk5, wv5 = c5["q"].to(dev), c5["cache"].to(dev), c5["wk"].to(dev), c5["wv"].to(dev)
+            fl5 = 2.0 * 8 * 2048 * 512 * 16 * 256 + prefill_flops(8, 16, 2048, 2048, 192, 128, True)
+            extras["latent"] = bench_extra(
+                "c5", lambda: pj.mla(q5, ch5, wk5, wv5, mask=pj.CausalMask(), sm_scale=c5["sm_scale"]), xs, xw,
+                fl5 / 1e12, "TFLOP/s", pk["bf16_tflops"], "tensor", pk["source"])
+            del q5, ch5
+        except Exception as e:
+            extras["latent"] = {"error": str(e)[:300]}
+        try:
+            for tag, full in (("decode_32k", True), ("decode_ragged", False)):
+                c4 = oracle.make_config(4, full=full)
+                q4, k4, v4, l4 = c4["q"].to(dev), c4["k"].to(dev), c4["v"].to(dev), c4["kv_lengths"].to(dev)
+                by4 = 4096.0 * float(c4["kv_lengths"].sum()) + 2 * q4.numel() * 2 + 16 * 32 * 4
+                extras[tag] = bench_extra(
+                    tag, lambda: pj.decode_forward(q4, k4, v4, kv_lengths=l4, sm_scale=c4["sm_scale"], return_lse=True),
+                    xs, xw, by4 / 1e9, "GB/s", pk["hbm_gbs"], "hbm", pk["source"])
+                if "roofline" in extras[tag]:
+                    extras[tag]["roofline"]["frac_of_nominal_8TBs"] = extras[tag]["value"] / 8000.0
+                if dist_on and full:
+                    extras["decode_32k_seq_sharded"] = sharded_decode_bench(c4, dev, rank, world, xs, xw, pk)
+                del q4, k4, v4
+        except Exception as e:
+            extras["decode"] = {"error": str(e)[:300]}
+        out["extras"] = extras
+
+    if rank == 0 and not args.skip_cpu and world == 1:
+        try:
+            out["cpu_baseline"] = cpu_baseline()
+        except Exception as e:
+            out["cpu_baseline"] = {"error": str(e)[:300]}
+    if rank == 0:
+        print(json.dumps(out), flush=True)
+    if dist_on:
+        import torch.distributed as dist
+
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def sharded_decode_bench(c4, dev, rank, world, steps, warmup, pk):
+    """Decode at 32k context with the KV sequence block-cyclically sharded over
+    the ranks: local split-KV kernel, all-gather of (o, lse), combine."""
+    import probjax_b200 as pj
+    from probjax_b200 import dist as pjd
+
+    try:
+        page = 256
+        kl = pjd.shard_cache(c4["k"], rank, world, page).to(dev)
+        vl = pjd.shard_cache(c4["v"], rank, world, page).to(dev)
+        q4 = c4["q"].to(dev)
+        lens = c4["kv_lengths"].to(dev)
+
+        def fn():
+            return pjd.decode_sharded(q4, kl, vl, lens, page=page, sm_scale=c4["sm_scale"], return_lse=True)
+
+        ms = max_over_ranks(time_steps(fn, steps, warmup, True), True) / steps
+        by = 4096.0 * float(lens.sum())
+        ach = by / (ms * 1e-3) / 1e9
+        return {"ms": ms, "value": ach, "unit": "GB/s aggregate", "page": page,
+                "roofline": {"bound": "hbm", "achieved": ach / world, "peak": pk["hbm_gbs"], "unit": "GB/s per GPU",
+                             "frac": ach / world / pk["hbm_gbs"], "of": pk["source"]}}
+    except Exception as e:
+        return {"error": f"{type(e).__name__}: {e}"[:300]}
+
+
+if __name__ == "__main__":
+    main()

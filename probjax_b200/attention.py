@@ -77,6 +77,18 @@ def _as_tensor(x):
     raise TypeError(f"expected a torch.Tensor or numpy.ndarray, got {type(x).__name__}")
 
 
+def _result(given, shape, dtype, device, pin=False):
+    """The caller's result tensor if it fits (contiguous, right shape / dtype / side), else a new one."""
+    if given is not None:
+        if tuple(given.shape) != tuple(shape) or given.dtype != dtype or given.device.type != torch.device(device).type \
+                or not given.is_contiguous():
+            raise ValueError(f"result tensor must be contiguous {tuple(shape)} {dtype} on {device}")
+        return given
+    if torch.device(device).type == "cpu":
+        return torch.empty(shape, dtype=dtype, pin_memory=pin)
+    return torch.empty(shape, dtype=dtype, device=device)
+
+
 def _require_gpu():
     _lib.lib()  # raises when the library is not built
     if not torch.cuda.is_available():
@@ -96,10 +108,11 @@ def _gqa_group(hq: int, hkv: int) -> int:
 
 
 def attention_forward(q, k, v, *, causal=False, kv_lengths=None, bias=None, sm_scale=1.0,
-                      return_lse=False, impl=None):
+                      return_lse=False, impl=None, out=None, lse_out=None):
     """One ``pjx_attn_fwd`` call. ``q [B,Lq,Hq,D]``, ``k [B,Lkv,Hkv,D]``,
     ``v [B,Lkv,Hkv,Dv]``; CUDA tensors stay on the device, host tensors use the
-    host-buffer entry point.  Returns ``o`` or ``(o, lse)``."""
+    host-buffer entry point.  ``out`` / ``lse_out`` are optional preallocated result
+    tensors (same side as the inputs).  Returns ``o`` or ``(o, lse)``."""
     _require_gpu()
     q, k, v = _as_tensor(q), _as_tensor(k), _as_tensor(v)
     if q.dtype not in _DTYPES:
@@ -115,8 +128,8 @@ def attention_forward(q, k, v, *, causal=False, kv_lengths=None, bias=None, sm_s
     if on_device:
         dev = q.device
         q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
-        o = torch.empty((B, Lq, Hq, Dv), dtype=q.dtype, device=dev)
-        lse = torch.empty((B, Hq, Lq), dtype=torch.float32, device=dev) if return_lse else None
+        o = _result(out, (B, Lq, Hq, Dv), q.dtype, dev)
+        lse = _result(lse_out, (B, Hq, Lq), torch.float32, dev) if return_lse else None
         kvl = None if kv_lengths is None else _as_tensor(kv_lengths).to(device=dev, dtype=torch.int32).contiguous()
         bs = hs = 0
         bt = None
@@ -134,8 +147,8 @@ def attention_forward(q, k, v, *, causal=False, kv_lengths=None, bias=None, sm_s
     dev = torch.device("cuda", torch.cuda.current_device())
     q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
     pin = q.is_pinned()
-    o = torch.empty((B, Lq, Hq, Dv), dtype=q.dtype, pin_memory=pin)
-    lse = torch.empty((B, Hq, Lq), dtype=torch.float32, pin_memory=pin) if return_lse else None
+    o = _result(out, (B, Lq, Hq, Dv), q.dtype, torch.device("cpu"), pin)
+    lse = _result(lse_out, (B, Hq, Lq), torch.float32, torch.device("cpu"), pin) if return_lse else None
     kvl = None if kv_lengths is None else _as_tensor(kv_lengths).to(device="cpu", dtype=torch.int32).contiguous()
     bt = None if bias is None else _as_tensor(bias).to(device="cpu", dtype=torch.float32).contiguous()
     bb, bh = (bt.shape[0], bt.shape[1]) if bt is not None else (0, 0)

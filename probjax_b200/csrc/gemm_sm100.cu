@@ -237,11 +237,11 @@ int make_tmap_2d(CUtensorMap* m, const void* base, int dtype, int64_t rows, int6
 int launch_gemm_tn(const void* A, const void* Bm, void* C, int64_t M, int N, int K, int dtype, int impl,
                    cudaStream_t stream) {
   if (M == 0 || N == 0) return PJX_OK;
-  const bool tc_ok = (dtype == PJX_BF16 || dtype == PJX_F16) && K % 8 == 0 && K >= 8 &&
+  const bool tc_ok = (dtype == PJX_BF16 || dtype == PJX_F16) && K % 8 == 0 && K >= 64 &&
                      ((reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(Bm)) & 15) == 0 &&
                      (M + TM - 1) / TM <= 65535;
   if (impl == PJX_IMPL_SM100 && !tc_ok)
-    return fail(PJX_ERR_UNSUPPORTED, "tcgen05 projection needs 16-bit inputs, K %% 8 == 0 and 16-byte aligned operands");
+    return fail(PJX_ERR_UNSUPPORTED, "tcgen05 projection needs 16-bit inputs, K %% 8 == 0, K >= 64 and 16-byte aligned operands");
   if (impl != PJX_IMPL_GENERIC && tc_ok) {
     CUtensorMap ta, tb;
     int rc;

@@ -57,7 +57,7 @@ def decode_sharded(q, k_local, v_local, kv_lengths, *, page: int, sm_scale: floa
 
     ``q [B, Lq, Hq, D]`` is replicated; ``k_local`` / ``v_local`` are this rank's
     shards (:func:`shard_cache`); ``kv_lengths [B]`` are the *global* valid
-    lengths.  Every rank returns the full result ``[B, Lq, Hq, Dv]`` in
+    lengths (pass them on ``q``'s device to keep the call free of host copies).  Every rank returns the full result ``[B, Lq, Hq, Dv]`` in
     ``q.dtype`` (and the natural-log LSE ``[B, Hq, Lq]``).
 
     ``_local_fn`` / ``_combine_fn`` replace the two kernel calls; they exist so the
@@ -65,7 +65,7 @@ def decode_sharded(q, k_local, v_local, kv_lengths, *, page: int, sm_scale: floa
     """
     world = dist.get_world_size(group) if dist.is_initialized() else 1
     rank = dist.get_rank(group) if dist.is_initialized() else 0
-    lens = local_lengths(torch.as_tensor(kv_lengths).cpu(), rank, world, page).to(q.device)
+    lens = local_lengths(torch.as_tensor(kv_lengths), rank, world, page).to(q.device)
     local_fn = _local_fn or (lambda q_, k_, v_, l_: _att.decode_forward(
         q_, k_, v_, kv_lengths=l_, sm_scale=sm_scale, return_lse=True, partial_f32=True))
     combine_fn = _combine_fn or (lambda o_, l_: _att.combine_partials(o_, l_, out_dtype=q.dtype))

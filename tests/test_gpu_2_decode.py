@@ -1,0 +1,145 @@
+"""Parity of the split-KV decode kernel, its combine and the sharded decode."""
+
+import math
+
+import pytest
+import torch
+
+import oracle
+import probjax_b200 as pj
+from probjax_b200 import dist as pjd
+from _gpu_util import assert_close, cases, dev, load_golden, oracle_fwd, randn
+
+pytestmark = pytest.mark.gpu
+
+
+def _decode(q, k, v, lens, sc, **kw):
+    d = dev()
+    out, lse = pj.decode_forward(q.to(d), k.to(d), v.to(d), kv_lengths=None if lens is None else lens.to(d),
+                                 sm_scale=sc, return_lse=True, **kw)
+    torch.cuda.synchronize()
+    return out, lse
+
+
+def test_golden():
+    inp = cases.make_inputs("c4_small")
+    out, lse = _decode(inp["q"], inp["k"], inp["v"], inp["kv_lengths"], inp["sm_scale"])
+    want, want_lse = load_golden("c4_small")
+    assert_close(out, lse, want, want_lse, torch.bfloat16, "c4_small")
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize(
+    "b,lq,lkv,hq,hkv,d,split_len",
+    [
+        (1, 1, 200, 4, 4, 64, 0),       # tests/test_attention_gqa_splitkv.py:175-183 shapes, widened to a kernel head dim
+        (2, 3, 130, 4, 2, 64, 64),
+        (1, 4, 96, 8, 2, 128, 0),
+        (1, 2, 50, 2, 1, 64, 0),
+        (3, 1, 2100, 32, 8, 128, 256),  # the benchmark's head geometry
+        (2, 1, 1, 8, 2, 128, 0),        # a single key
+        (2, 2, 777, 16, 2, 128, 128),   # 16 packed rows: the most the kernel takes
+    ],
+)
+def test_shapes(dtype, b, lq, lkv, hq, hkv, d, split_len):
+    q, k, v = randn((b, lq, hq, d), dtype, 1), randn((b, lkv, hkv, d), dtype, 2), randn((b, lkv, hkv, d), dtype, 3)
+    lens = torch.randint(1, lkv + 1, (b,), generator=torch.Generator().manual_seed(lkv), dtype=torch.int32)
+    lens[0] = lkv
+    sc = 1 / math.sqrt(d)
+    out, lse = _decode(q, k, v, lens, sc, split_len=split_len)
+    want, want_lse = oracle_fwd(q, k, v, kv_lengths=lens, sm_scale=sc)
+    assert_close(out, lse, want, want_lse, dtype, f"{(b, lq, lkv, hq, hkv, d, split_len)}")
+    # without lengths the whole cache counts
+    out, lse = _decode(q, k, v, None, sc, split_len=split_len)
+    want, want_lse = oracle_fwd(q, k, v, sm_scale=sc)
+    assert_close(out, lse, want, want_lse, dtype, "full cache")
+
+
+def test_garbage_past_the_valid_length_is_never_read():
+    b, cap, hq, hkv, d = 2, 700, 8, 2, 128
+    q, k, v = randn((b, 1, hq, d), torch.bfloat16, 1), randn((b, cap, hkv, d), torch.bfloat16, 2), randn((b, cap, hkv, d), torch.bfloat16, 3)
+    lens = torch.tensor([130, 401], dtype=torch.int32)
+    want, want_lse = oracle_fwd(q, k, v, kv_lengths=lens, sm_scale=0.1)
+    for i in range(b):
+        k[i, int(lens[i]):] = float("nan")
+        v[i, int(lens[i]):] = float("inf")
+    out, lse = _decode(q, k, v, lens, 0.1, split_len=64)
+    assert_close(out, lse, want, want_lse, torch.bfloat16, "poisoned tail")
+
+
+def test_zero_length_sequences():
+    q, k, v = randn((3, 1, 8, 128), torch.bfloat16, 1), randn((3, 300, 2, 128), torch.bfloat16, 2), randn((3, 300, 2, 128), torch.bfloat16, 3)
+    lens = torch.tensor([0, 300, 0], dtype=torch.int32)
+    out, lse = _decode(q, k, v, lens, 0.2)
+    assert (out[0] == 0).all() and (out[2] == 0).all()
+    assert torch.isinf(lse[0]).all() and (lse[0] > 0).all()
+    want, want_lse = oracle_fwd(q, k, v, kv_lengths=lens, sm_scale=0.2)
+    assert_close(out, lse, want, want_lse, torch.bfloat16, "zero lengths")
+
+
+def test_shapes_outside_the_streaming_kernel_use_the_generic_forward():
+    # D = 32 and fp32 are not streaming-kernel cases (tests/test_attention_gqa_splitkv.py:235-243 shapes)
+    for dtype, d, lq, lkv in [(torch.float32, 32, 1, 300), (torch.bfloat16, 32, 4, 1000), (torch.float32, 128, 1, 500)]:
+        q, k, v = randn((1, lq, 8, d), dtype, 1), randn((1, lkv, 2, d), dtype, 2), randn((1, lkv, 2, d), dtype, 3)
+        lens = torch.tensor([lkv - 17], dtype=torch.int32)
+        out, lse = _decode(q, k, v, lens, 0.3)
+        want, want_lse = oracle_fwd(q, k, v, kv_lengths=lens, sm_scale=0.3)
+        assert_close(out, lse, want, want_lse, dtype, f"fallback {dtype} {d}")
+
+
+def test_splitkv_forward_signature():
+    # attention_splitkv.py:137-149: num_splits fixes the split count; LSE is natural log [B, Hq, Lq]
+    d = dev()
+    q, k, v = randn((2, 3, 4, 64), torch.bfloat16, 1), randn((2, 130, 2, 64), torch.bfloat16, 2), randn((2, 130, 2, 64), torch.bfloat16, 3)
+    out, lse = pj.splitkv_forward(q.to(d), k.to(d), v.to(d), sm_scale=0.125, num_splits=3, return_lse=True)
+    want, want_lse, _, _ = oracle.splitkv_reference(q, k, v, sm_scale=0.125, num_splits=3)
+    assert lse.shape == (2, 4, 3)
+    assert_close(out, lse, want, want_lse, torch.bfloat16, "splitkv_forward")
+    with pytest.raises(ValueError, match="multiple"):
+        pj.splitkv_forward(q.to(d)[:, :, :3], k.to(d), v.to(d), sm_scale=1.0)
+
+
+def test_combine_entry_point():
+    g = torch.Generator().manual_seed(0)
+    P, N, Dv = 5, 37, 128
+    o_parts = torch.randn(P, N, Dv, generator=g)
+    lse_parts = torch.randn(P, N, generator=g) * 3
+    lse_parts[2] = float("inf")          # a part without keys
+    lse_parts[:, 5] = float("inf")       # a row no part has keys for
+    o, lse = pj.combine_partials(o_parts.to(dev()), lse_parts.to(dev()))
+    neg = torch.where(torch.isinf(lse_parts), torch.tensor(-float("inf")), lse_parts)
+    w = torch.softmax(neg.double(), dim=0)
+    w = torch.where(torch.isnan(w), torch.zeros_like(w), w)
+    want = (w[..., None] * o_parts.double()).sum(0)
+    want_lse = torch.logsumexp(neg.double(), 0)
+    assert float((o.cpu().double() - want).abs().max()) < 1e-5
+    assert (o.cpu()[5] == 0).all() and torch.isinf(lse.cpu()[5]) and lse.cpu()[5] > 0
+    fin = torch.isfinite(want_lse)
+    assert float((lse.cpu().double()[fin] - want_lse[fin]).abs().max()) < 1e-5
+
+
+@pytest.mark.parametrize("world,page", [(2, 64), (4, 256), (8, 128)])
+def test_sharded_decode_emulated_on_one_gpu(world, page):
+    """Every rank's shard is run in turn on this GPU and the partials are combined
+    with the same kernel the multi-GPU path uses: the result must equal the
+    unsharded decode and the oracle."""
+    d = dev()
+    b, cap, hq, hkv, dd = 4, 3000, 32, 8, 128
+    q, k, v = randn((b, 1, hq, dd), torch.bfloat16, 1), randn((b, cap, hkv, dd), torch.bfloat16, 2), randn((b, cap, hkv, dd), torch.bfloat16, 3)
+    lens = torch.tensor([3000, 17, 1500, 640], dtype=torch.int32)
+    sc = 1 / math.sqrt(dd)
+    recs_o, recs_l = [], []
+    for r in range(world):
+        kl, vl = pjd.shard_cache(k, r, world, page).to(d), pjd.shard_cache(v, r, world, page).to(d)
+        ll = pjd.local_lengths(lens, r, world, page).to(d)
+        o, lse = pj.decode_forward(q.to(d), kl, vl, kv_lengths=ll, sm_scale=sc, return_lse=True, partial_f32=True)
+        assert o.dtype == torch.float32
+        recs_o.append(o.reshape(-1, dd))
+        recs_l.append(lse.permute(0, 2, 1).reshape(-1))
+    o, lse = pj.combine_partials(torch.stack(recs_o), torch.stack(recs_l), out_dtype=torch.bfloat16)
+    o, lse = o.reshape(b, 1, hq, dd), lse.reshape(b, 1, hq).permute(0, 2, 1)
+    want, want_lse = oracle_fwd(q, k, v, kv_lengths=lens, sm_scale=sc)
+    assert_close(o, lse, want, want_lse, torch.bfloat16, f"sharded x{world}")
+    # world size 1 through the public function (no process group)
+    o1, lse1 = pjd.decode_sharded(q.to(d), k.to(d), v.to(d), lens, page=page, sm_scale=sc, return_lse=True)
+    assert_close(o1, lse1, want, want_lse, torch.bfloat16, "decode_sharded world=1")

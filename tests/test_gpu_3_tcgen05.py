@@ -1,0 +1,166 @@
+"""Parity of the tcgen05 forward kernel and the tcgen05 projection with the oracle."""
+
+import math
+
+import pytest
+import torch
+
+import oracle
+import probjax_b200 as pj
+from _gpu_util import assert_close, cases, dev, load_golden, oracle_fwd, randn
+
+pytestmark = pytest.mark.gpu
+TC = "b200:tcgen05"
+
+
+def _run(q, k, v, impl=TC, **kw):
+    d = dev()
+    args = {n: (t.to(d) if isinstance(t, torch.Tensor) else t) for n, t in kw.items()}
+    out, lse = pj.attention_forward(q.to(d), k.to(d), v.to(d), return_lse=True, impl=impl, **args)
+    pj.check_status(d)  # a timed-out wait inside the kernel raises here
+    return out, lse
+
+
+def test_one_tile_identity_values():
+    """Smallest case: one 128x128 tile, V = identity-like, so O = P and every row of
+    O sums to 1; catches descriptor / layout mistakes before the real cases."""
+    q, k = randn((1, 128, 1, 128), torch.bfloat16, 1), randn((1, 128, 1, 128), torch.bfloat16, 2)
+    v = torch.eye(128, dtype=torch.bfloat16).reshape(1, 128, 1, 128)
+    sc = 1 / math.sqrt(128)
+    out, lse = _run(q, k, v, sm_scale=sc)
+    want, want_lse = oracle_fwd(q, k, v, sm_scale=sc)
+    assert_close(out, lse, want, want_lse, torch.bfloat16, "identity V")
+    assert torch.allclose(out.float().sum(-1).cpu(), torch.ones(1, 128, 1), atol=2e-2)
+
+
+@pytest.mark.parametrize("name", ["c2_small", "c2_small_causal", "c3_small"])
+def test_golden(name):
+    inp = cases.make_inputs(name)
+    kw = {n: inp[n] for n in ("causal", "sm_scale", "kv_lengths", "bias") if n in inp}
+    out, lse = _run(inp["q"], inp["k"], inp["v"], **kw)
+    want, want_lse = load_golden(name)
+    assert_close(out, lse, want, want_lse, inp["q"].dtype, name)
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize(
+    "b,lq,lkv,hq,hkv,d,dv,causal",
+    [
+        (1, 256, 256, 1, 1, 128, 128, False),
+        (2, 512, 512, 4, 2, 128, 128, True),
+        (1, 200, 333, 2, 1, 128, 128, False),   # ragged: tails on both axes
+        (1, 333, 200, 2, 2, 128, 128, True),    # more queries than keys, causal
+        (2, 100, 1000, 4, 4, 64, 64, False),
+        (1, 640, 640, 2, 1, 64, 64, True),
+        (1, 1, 300, 2, 2, 128, 128, False),     # a single query row
+        (1, 300, 300, 2, 2, 192, 128, True),    # latent-attention head shape
+        (1, 130, 70, 3, 1, 192, 128, False),
+    ],
+)
+def test_shapes(dtype, b, lq, lkv, hq, hkv, d, dv, causal):
+    q, k, v = randn((b, lq, hq, d), dtype, 1), randn((b, lkv, hkv, d), dtype, 2), randn((b, lkv, hkv, dv), dtype, 3)
+    sc = 1 / math.sqrt(d)
+    out, lse = _run(q, k, v, causal=causal, sm_scale=sc)
+    want, want_lse = oracle_fwd(q, k, v, causal=causal, sm_scale=sc)
+    assert_close(out, lse, want, want_lse, dtype, f"{(b, lq, lkv, hq, hkv, d, dv, causal)}")
+
+
+@pytest.mark.parametrize("bshape", [(1, 4), (2, 4), (1, 1)])
+@pytest.mark.parametrize("lkv", [384, 331])  # 331: the bias rows are not 16-byte aligned
+def test_key_lengths_and_bias(bshape, lkv):
+    b, lq, h, d = 2, 300, 4, 64
+    q, k, v = randn((b, lq, h, d), torch.bfloat16, 4), randn((b, lkv, h, d), torch.bfloat16, 5), randn((b, lkv, h, d), torch.bfloat16, 6)
+    bias = randn((*bshape, lq, lkv), torch.float32, 7)
+    lens = torch.tensor([77, lkv], dtype=torch.int32)
+    for causal in (False, True):
+        out, lse = _run(q, k, v, causal=causal, kv_lengths=lens, bias=bias, sm_scale=0.125)
+        want, want_lse = oracle_fwd(q, k, v, causal=causal, kv_lengths=lens, bias=bias, sm_scale=0.125)
+        assert_close(out, lse, want, want_lse, torch.bfloat16, f"bias{bshape} lkv={lkv} causal={causal}")
+
+
+def test_zero_length_batch_rows():
+    q, k, v = randn((3, 140, 2, 128), torch.bfloat16, 1), randn((3, 256, 2, 128), torch.bfloat16, 2), randn((3, 256, 2, 128), torch.bfloat16, 3)
+    lens = torch.tensor([0, 256, 5], dtype=torch.int32)
+    out, lse = _run(q, k, v, kv_lengths=lens, sm_scale=0.1)
+    assert (out[0] == 0).all() and torch.isinf(lse[0]).all() and (lse[0] > 0).all()
+    want, want_lse = oracle_fwd(q, k, v, kv_lengths=lens, sm_scale=0.1)
+    assert_close(out, lse, want, want_lse, torch.bfloat16, "zero length")
+
+
+def test_large_scores_do_not_overflow():
+    # scores spread over hundreds of units: the running maximum must keep up
+    q, k, v = randn((1, 256, 1, 128), torch.bfloat16, 1) * 6, randn((1, 512, 1, 128), torch.bfloat16, 2) * 6, randn((1, 512, 1, 128), torch.bfloat16, 3)
+    out, lse = _run(q, k, v, sm_scale=1.0)
+    want, want_lse = oracle_fwd(q, k, v, sm_scale=1.0)
+    assert_close(out, None, want, None, torch.bfloat16, "large scores")
+    assert float(((lse.cpu() - want_lse) / want_lse.abs().clamp_min(1)).abs().max()) < 1e-3
+
+
+def test_repeatable_bit_for_bit_and_equal_to_generic():
+    q, k, v = randn((2, 512, 4, 128), torch.bfloat16, 1), randn((2, 512, 2, 128), torch.bfloat16, 2), randn((2, 512, 2, 128), torch.bfloat16, 3)
+    a, la = _run(q, k, v, causal=True, sm_scale=0.09)
+    b, lb = _run(q, k, v, causal=True, sm_scale=0.09)
+    assert torch.equal(a, b) and torch.equal(la, lb)
+    g, lg = _run(q, k, v, impl="b200:generic", causal=True, sm_scale=0.09)
+    assert float((a.float() - g.float()).abs().max()) <= 2e-2
+    assert float((la - lg).abs().max()) <= 1e-3
+
+
+def test_auto_dispatch_picks_the_kernel_by_shape():
+    from probjax_b200 import _lib
+
+    d = dev()
+    q = randn((1, 128, 2, 128), torch.bfloat16, 1).to(d)
+    n0 = _lib.launch_count()
+    pj.attention_forward(q, q, q, sm_scale=0.1)
+    assert _lib.launch_count() == n0 + 1
+    with pytest.raises(NotImplementedError, match="tcgen05"):
+        pj.attention_forward(q.float(), q.float(), q.float(), impl=TC)
+    q24 = randn((1, 50, 2, 24), torch.bfloat16, 1).to(d)
+    with pytest.raises(NotImplementedError, match="head dims"):
+        pj.attention_forward(q24, q24, q24, impl=TC)
+    out = pj.attention_forward(q24, q24, q24, sm_scale=0.2)  # auto falls to the generic kernel
+    want, _ = oracle_fwd(q24, q24, q24, sm_scale=0.2)
+    assert_close(out, None, want, None, torch.bfloat16, "auto generic")
+
+
+@pytest.mark.parametrize("impl", [TC, "b200:generic", None])
+def test_latent_attention_golden(impl):
+    inp = cases.make_inputs("c5_small")
+    d = dev()
+    out, lse = pj.mla(inp["q"].to(d), inp["cache"].to(d), inp["wk"].to(d), inp["wv"].to(d),
+                      mask=pj.CausalMask(), sm_scale=inp["sm_scale"], return_lse=True, implementation=impl)
+    pj.check_status(d)
+    want, want_lse = load_golden("c5_small")
+    assert_close(out, lse, want, want_lse, torch.bfloat16, f"c5_small {impl}")
+
+
+@pytest.mark.parametrize("impl", [TC, "b200:generic"])
+@pytest.mark.parametrize("s_len,dh,r", [(128, 128, 64), (300, 64, 136), (64, 128, 8), (700, 192, 576)])
+def test_projection_product(impl, s_len, dh, r):
+    """The up-projection K = C.W_K^T, V = C.W_V^T (ragged tile tails on every axis),
+    checked through the whole latent-attention call against the oracle."""
+    d = dev()
+    dv = 128 if dh == 192 else dh
+    cache = randn((1, s_len, r), torch.bfloat16, 1)
+    wk, wv = randn((2, dh, r), torch.bfloat16, 2) * 0.2, randn((2, dv, r), torch.bfloat16, 3) * 0.2
+    q = randn((1, 40, 2, dh), torch.bfloat16, 4)
+    if impl == TC and r < 64:  # the tensor-map path needs at least one full 64-wide K slice
+        with pytest.raises(NotImplementedError, match="projection"):
+            pj.mla(q.to(d), cache.to(d), wk.to(d), wv.to(d), sm_scale=0.05, implementation=impl)
+        return
+    got = pj.mla(q.to(d), cache.to(d), wk.to(d), wv.to(d), sm_scale=0.05, implementation=impl)
+    pj.check_status(d)
+    want = oracle.mla_reference(q, cache, wk, wv, sm_scale=0.05, factorisation="materialized")
+    assert_close(got, None, want, None, torch.bfloat16, f"projection {(s_len, dh, r)}")
+
+
+def test_host_buffer_call_matches_device_call():
+    inp = cases.make_inputs("c2_small_causal")
+    q, k, v = (inp[n].pin_memory() for n in ("q", "k", "v"))
+    out, lse = pj.attention_forward(q, k, v, causal=True, sm_scale=inp["sm_scale"], return_lse=True)
+    assert not out.is_cuda and out.is_pinned()
+    want, want_lse = load_golden("c2_small_causal")
+    assert_close(out, lse, want, want_lse, torch.bfloat16, "host buffers")
+    out2 = pj.attention_forward(q.numpy() if q.dtype != torch.bfloat16 else q, k, v, causal=True, sm_scale=inp["sm_scale"])
+    assert torch.equal(out, out2)

@@ -1,0 +1,182 @@
+"""The reference call signatures end to end on the GPU, and size-independent
+properties at the benchmark's full sizes."""
+
+import math
+
+import pytest
+import torch
+
+import oracle
+import probjax_b200 as pj
+from _gpu_util import assert_close, dev, oracle_fwd, randn
+
+pytestmark = pytest.mark.gpu
+
+
+def test_flex_attention_masks_and_bias_objects():
+    d = dev()
+    b, t, h, dd = 2, 32, 2, 16  # tests/test_attention_xla.py:91-147 (B2 T32 H2 D16, scale 0.25)
+    q, k, v = (randn((b, t, h, dd), torch.float32, s) for s in (1, 2, 3))
+    lens = torch.tensor([20, 32], dtype=torch.int32)
+    bias = randn((b, h, t, t), torch.float32, 4)
+    for mask, kw in [
+        (None, {}),
+        (pj.NoMask(), {}),
+        (pj.CausalMask(), dict(causal=True)),
+        (pj.KVLenMask(lens), dict(kv_lengths=lens)),
+        (pj.KVLenMask(lens) & pj.CausalMask(), dict(kv_lengths=lens, causal=True)),
+    ]:
+        for bobj, bkw in [(None, {}), (pj.DenseBias(bias), dict(bias=bias)), (pj.DenseBias(bias[:1, :1]), dict(bias=bias[:1, :1]))]:
+            got, lse = pj.flex_attention(q.to(d), k.to(d), v.to(d), mask=mask, bias=bobj, sm_scale=0.25, return_lse=True)
+            want, want_lse = oracle_fwd(q, k, v, sm_scale=0.25, **kw, **bkw)
+            assert_close(got, lse, want, want_lse, torch.float32, f"{type(mask).__name__} {bool(bobj)}")
+
+
+def test_default_scale_rank3_and_extra_batch_dims():
+    d = dev()
+    q, k, v = (randn((40, 4, 16), torch.float32, s) for s in (1, 2, 3))
+    got = pj.flex_attention(q.to(d), k.to(d), v.to(d), mask=pj.CausalMask())
+    want, _ = oracle_fwd(q[None], k[None], v[None], causal=True, sm_scale=1 / 4.0)  # layers/attention.py:1524-1525
+    assert got.shape == (40, 4, 16)
+    assert_close(got[None], None, want, None, torch.float32, "rank 3")
+    q5 = randn((2, 3, 20, 4, 16), torch.float32, 5)
+    got = pj.dot_product_attention(q5.to(d), q5.to(d)[..., :2, :], q5.to(d)[..., :2, :])  # GQA like Flax
+    want, _ = oracle_fwd(q5.reshape(6, 20, 4, 16), q5.reshape(6, 20, 4, 16)[..., :2, :], q5.reshape(6, 20, 4, 16)[..., :2, :], sm_scale=0.25)
+    assert got.shape == q5.shape
+    assert_close(got.reshape(6, 20, 4, 16), None, want, None, torch.float32, "rank 5")
+
+
+def test_mha_defaults_and_padding_mask():
+    d = dev()
+    q, k, v = (randn((1, 50, 2, 24), torch.float32, s) for s in (1, 2, 3))
+    got = pj.mha(q.to(d), k.to(d), v.to(d))  # default sm_scale = 1.0 (kernels/attention.py:2699)
+    want, _ = oracle_fwd(q, k, v, sm_scale=1.0)
+    assert_close(got, None, want, None, torch.float32, "mha default scale")
+    # QKVLengthMask: rows past q_length see nothing, keys past kv_length are masked
+    m = pj.QKVLengthMask(q_length=30, kv_length=41)
+    got, lse = pj.mha(q.to(d), k.to(d), v.to(d), mask=m, sm_scale=0.2, return_lse=True)
+    keep = m.dense(50, 50)
+    want, want_lse = oracle_fwd(q, k, v, keep=keep, sm_scale=0.2)
+    assert_close(got, lse, want, want_lse, torch.float32, "QKVLengthMask")
+    with pytest.raises(NotImplementedError):
+        pj.mha(q.to(d), k.to(d), v.to(d), dropout_rate=0.1)
+
+
+def test_dispatch_route():
+    d = dev()
+    assert pj.device_attention_defaults(d)["route"] == "b200"
+    q, k = randn((2, 64, 4, 64), torch.bfloat16, 1), randn((2, 64, 2, 64), torch.bfloat16, 2)
+    got = pj.b200_attention_or_none(q.to(d), k.to(d), k.to(d), mask=pj.CausalMask(), sm_scale=0.125)
+    want, _ = oracle_fwd(q, k, k, causal=True, sm_scale=0.125)
+    assert_close(got, None, want, None, torch.bfloat16, "route")
+    # a mask the kernels do not implement: "not mine", or ValueError when forced
+    kp = pj.KeyPaddingMask(torch.tensor([3, 9]))
+    assert pj.b200_attention_or_none(q.to(d), k.to(d), k.to(d), mask=kp, sm_scale=1.0) is None
+    with pytest.raises(ValueError, match="cannot compute"):
+        pj.b200_attention_or_none(q.to(d), k.to(d), k.to(d), mask=kp, sm_scale=1.0, force=True)
+    assert pj.b200_attention_or_none(q.to(d), k.to(d), k.to(d), dropout_rate=0.1, sm_scale=1.0) is None
+
+
+def test_split_kv_routing_rule():
+    # kernels/attention.py:2649-2689: Lq <= 64 and Lkv >= 1024 picks split-KV; KVLenMask keeps it
+    from probjax_b200 import _lib
+
+    d = dev()
+    q = randn((2, 1, 8, 128), torch.bfloat16, 1).to(d)
+    k = randn((2, 1100, 2, 128), torch.bfloat16, 2).to(d)
+    assert pj.use_splitkv(q, k) and not pj.use_splitkv(q, k[:, :1000]) and pj.use_splitkv(q, k[:, :1000], split_kv=True)
+    assert not pj.use_splitkv(q, k, causal=True) and not pj.use_splitkv(q, k, split_kv=False)
+    lens = torch.tensor([1100, 300], dtype=torch.int32)
+    n0 = _lib.launch_count()
+    got, lse = pj.flex_attention(q, k, k, mask=pj.KVLenMask(lens), enable_gqa=True, return_lse=True)
+    assert _lib.launch_count() == n0 + 2  # split kernel + combine
+    want, want_lse = oracle_fwd(q, k, k, kv_lengths=lens, sm_scale=1 / math.sqrt(128))
+    assert_close(got, lse, want, want_lse, torch.bfloat16, "split-KV route")
+    # decode step as MultiHeadAttention issues it: KeyPaddingMask with one query row (layers/attention.py:658-673)
+    got = pj.flex_attention(q, k, k, mask=pj.KeyPaddingMask(lens), enable_gqa=True)
+    assert_close(got, None, want, None, torch.bfloat16, "KeyPaddingMask decode")
+
+
+def test_mla_absorbed_and_small_shapes():
+    d = dev()
+    g = torch.Generator().manual_seed(21)  # tests/test_latent_attention.py:234-258 (b2 s32 h4 d16 r8 dv12)
+    b, s, h, dd, r, dv = 2, 32, 4, 16, 8, 12
+    q, cache = torch.randn(b, s, h, dd, generator=g), torch.randn(b, s, r, generator=g)
+    wk, wv = torch.randn(h, dd, r, generator=g) * 0.3, torch.randn(h, dv, r, generator=g) * 0.3
+    for mask, kw in [(None, {}), (pj.CausalMask(), dict(causal=True)), (pj.KVLenMask(torch.tensor([20, 32])), dict(kv_lengths=torch.tensor([20, 32])))]:
+        got = pj.mla(q.to(d), cache.to(d), wk.to(d), wv.to(d), mask=mask)
+        want = oracle.mla_reference(q, cache, wk, wv, **kw)
+        assert got.shape == (b, s, h, dv)
+        assert float((got.cpu() - want).abs().max()) < 1e-4
+    q2 = torch.randn(b, s, h, r, generator=g)
+    got = pj.mla(q2.to(d), cache.to(d), mask=pj.CausalMask())
+    want = oracle.mla_reference(q2, cache, causal=True)
+    assert float((got.cpu() - want).abs().max()) < 1e-4
+
+
+def _row_sample_check(q, k, v, out, lse, rows, causal, sc, kv_lengths=None, bias=None):
+    """Oracle comparison on a sample of query rows of a large problem."""
+    qs = q[:, rows].cpu()
+    lkv = k.shape[1]
+    keep = torch.ones(1, 1, len(rows), lkv, dtype=torch.bool)
+    if causal:
+        keep = keep & (torch.arange(lkv)[None, :] <= torch.tensor(rows)[:, None])[None, None]
+    if kv_lengths is not None:
+        keep = keep & (torch.arange(lkv)[None, :] < kv_lengths.cpu()[:, None])[:, None, None, :]
+    b = None if bias is None else bias[:, :, rows].cpu()
+    want, want_lse = oracle.dense_formula(qs, k.cpu(), v.cpu(), sm_scale=sc, keep=keep, bias=b)
+    assert_close(out[:, rows], lse[:, :, rows], want.float(), want_lse.float(), q.dtype, "row sample")
+
+
+@pytest.mark.parametrize("causal", [False, True])
+def test_full_size_gqa_prefill_properties(causal):
+    """Configuration 2 at full size (B4 Hq32 Hkv8 S4096 D128): normalisation
+    (V = 1 gives exactly 1), linearity in V, and oracle parity on sampled rows."""
+    d = dev()
+    c = oracle.make_config(2, causal=causal)
+    q, k, v = c["q"].to(d), c["k"].to(d), c["v"].to(d)
+    out, lse = pj.attention_forward(q, k, v, causal=causal, sm_scale=c["sm_scale"], return_lse=True)
+    pj.check_status(d)
+    ones = pj.attention_forward(q, k, torch.ones_like(v), causal=causal, sm_scale=c["sm_scale"])
+    assert float((ones.float() - 1).abs().max()) <= 8e-3  # bf16 rounding of P and of the output
+    twice = pj.attention_forward(q, k, v * 2, causal=causal, sm_scale=c["sm_scale"])
+    assert torch.equal(twice, out * 2)  # scaling V by a power of two is exact
+    rows = [0, 1, 127, 128, 129, 255, 256, 1000, 2047, 2048, 3000, 4095]
+    _row_sample_check(q[:1], k[:1], v[:1], out[:1], lse[:1], rows, causal, c["sm_scale"])
+    _row_sample_check(q[3:], k[3:], v[3:], out[3:], lse[3:], rows, causal, c["sm_scale"])
+
+
+def test_full_size_masked_biased_attention():
+    """Configuration 3 at full size (B8 H16 S1024 D64, key lengths + fp32 bias)."""
+    d = dev()
+    c = oracle.make_config(3)
+    q, k, v = c["q"].to(d), c["k"].to(d), c["v"].to(d)
+    out, lse = pj.flex_attention(q, k, v, mask=pj.KVLenMask(c["kv_lengths"]), bias=pj.DenseBias(c["bias"]),
+                                 sm_scale=c["sm_scale"], return_lse=True)
+    pj.check_status(d)
+    rows = [0, 63, 64, 500, 1023]
+    _row_sample_check(q, k, v, out, lse, rows, False, c["sm_scale"], kv_lengths=c["kv_lengths"], bias=c["bias"])
+
+
+def test_full_size_decode():
+    """Configuration 4 at full size (B16 Hq32 Hkv8 D128, capacity 32768, ragged):
+    oracle parity for every row (one query row per sequence keeps the oracle cheap)."""
+    d = dev()
+    c = oracle.make_config(4)
+    q, k, v = c["q"].to(d), c["k"].to(d), c["v"].to(d)
+    out, lse = pj.flex_attention(q, k, v, mask=pj.KVLenMask(c["kv_lengths"]), enable_gqa=True, return_lse=True)
+    want, want_lse = oracle_fwd(c["q"], c["k"], c["v"], kv_lengths=c["kv_lengths"], sm_scale=c["sm_scale"])
+    assert_close(out, lse, want, want_lse, torch.bfloat16, "config 4")
+
+
+def test_full_size_latent_attention():
+    """Configuration 5 at full size (B8 H16 S2048, rank 512 + rotary 64): sampled rows
+    against the dense formula over the materialised keys and values of one batch row."""
+    d = dev()
+    c = oracle.make_config(5)
+    out, lse = pj.mla(c["q"].to(d), c["cache"].to(d), c["wk"].to(d), c["wv"].to(d), mask=pj.CausalMask(),
+                      sm_scale=c["sm_scale"], return_lse=True)
+    pj.check_status(d)
+    key, value = oracle.materialize_kv(c["cache"][:1], c["wk"], c["wv"], 16)
+    rows = [0, 1, 127, 128, 700, 2047]
+    _row_sample_check(c["q"][:1], key, value, out[:1], lse[:1], rows, True, c["sm_scale"])
