@@ -214,6 +214,9 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--skip-extras", action="store_true", help="headline only (used for profiling captures)")
     ap.add_argument("--skip-cpu", action="store_true", help="do not time the CPU baseline")
+    ap.add_argument("--batch", type=int, default=C2["B"], help="batch rows of the headline workload (profiling captures use a smaller one)")
+    ap.add_argument("--skip-e2e", action="store_true", help="do not time the host-buffer path")
+    ap.add_argument("--only-decode", action="store_true", help="time only the decode configuration (profiling captures)")
     ap.add_argument("--kernel", default=None, choices=[None, "b200:generic", "b200:tcgen05"],
                     help="force one forward kernel for the headline (default: the library's own choice)")
     args = ap.parse_args()
@@ -243,11 +246,15 @@ def main():
         dist.init_process_group("nccl", device_id=dev)
     pk = peaks()
 
+    if args.only_decode:
+        only_decode(args, dev, pk)
+        return
+
     # ---------------------------------------------------------------- headline
-    c = oracle.make_config(2)
+    c = oracle.make_config(2, B=args.batch)
     q, k, v = c["q"].to(dev), c["k"].to(dev), c["v"].to(dev)
     sc = c["sm_scale"]
-    flops = prefill_flops(C2["B"], C2["Hq"], C2["S"], C2["S"], C2["D"], C2["D"], False)
+    flops = prefill_flops(args.batch, C2["Hq"], C2["S"], C2["S"], C2["D"], C2["D"], False)
 
     def step():
         return pj.attention_forward(q, k, v, sm_scale=sc, impl=args.kernel)
@@ -284,7 +291,7 @@ def main():
         "metric": "attn_fwd_tflops", "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "bf16", "data": "synthetic",
-        "config": {"workload": "GQA prefill fwd bf16 B4 Hq32 Hkv8 S4096 D128 non-causal (per GPU)",
+        "config": {"workload": f"GQA prefill fwd bf16 B{args.batch} Hq32 Hkv8 S4096 D128 non-causal (per GPU)",
                    "l2": "inputs+outputs 335 MB per step exceed the 126 MB L2; no flush needed",
                    "parallelism": f"batch-sharded x{world}, no collective" if world > 1 else "single GPU"},
         "roofline": {"bound": "tensor", "achieved": per_gpu, "peak": pk["bf16_tflops"], "unit": "TFLOP/s",
@@ -355,6 +362,21 @@ def main():
 
         dist.barrier()
         dist.destroy_process_group()
+
+
+def only_decode(args, dev, pk):
+    """Decode at full context on `--batch` sequences, nothing else: the command
+    profiling captures of the split-KV kernel run."""
+    import oracle
+    import probjax_b200 as pj
+
+    c4 = oracle.make_config(4, B=args.batch, full=True)
+    q4, k4, v4, l4 = c4["q"].to(dev), c4["k"].to(dev), c4["v"].to(dev), c4["kv_lengths"].to(dev)
+    by4 = 4096.0 * float(c4["kv_lengths"].sum()) + 2 * q4.numel() * 2 + args.batch * 32 * 4
+    res = bench_extra("decode", lambda: pj.decode_forward(q4, k4, v4, kv_lengths=l4, sm_scale=c4["sm_scale"], return_lse=True),
+                      args.steps, args.warmup, by4 / 1e9, "GB/s", pk["hbm_gbs"], "hbm", pk["source"])
+    res["config"] = {"workload": f"GQA split-KV decode bf16 B{args.batch} Hq32 Hkv8 D128, 32768 keys each"}
+    print(json.dumps(res), flush=True)
 
 
 def sharded_decode_bench(c4, dev, rank, world, steps, warmup, pk):
