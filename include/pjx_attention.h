@@ -103,6 +103,34 @@ size_t pjx_attn_decode_workspace_bytes(int B, int Lq, int Hq, int Hkv, int Dv, i
 int pjx_attn_decode_default_split_len(int B, int Hkv, int capacity);
 
 /*
+ * The same decode for callers that cannot allocate device memory and are given
+ * none to pass on: a serving loop inside a compiler-planned custom call (the
+ * runtime hands it its operand and result buffers only and forbids cudaMalloc
+ * there), or code running while the device allocator is locked or exhausted.
+ * The per-split partials live in a fixed 16 MiB array inside the library
+ * (pjx_attn_decode_static_scratch_bytes(); every GPU that loads the library
+ * holds it until the process exits) instead of a workspace argument.  This entry
+ * point has no counterpart in the reference.
+ *
+ *   - Takes what the streaming kernel takes: bf16/fp16, D = Dv in {64, 128},
+ *     (Hq/Hkv)*Lq <= 16, 16-byte aligned q/k/v; anything else is
+ *     PJX_ERR_UNSUPPORTED.  A call whose partials exceed the array is refused
+ *     with PJX_ERR_WORKSPACE (choose a larger split_len, or use
+ *     pjx_attn_decode_splitkv).  o is written in `dtype`.
+ *   - It calls no cudaMalloc / cudaFree and no allocating library routine.
+ *   - The first call on each device looks up the array's device address; make
+ *     that first call before starting any stream capture.
+ *   - All calls share the array.  Nothing in it needs clearing between calls,
+ *     but two calls whose kernels overlap on the GPU (different streams or
+ *     threads) corrupt each other: order them on one stream.
+ */
+int pjx_attn_decode_splitkv_static(const void* q, const void* k_cache, const void* v_cache,
+                                   const int32_t* kv_lengths, void* o, float* lse, int B, int Lq,
+                                   int Hq, int Hkv, int D, int Dv, int capacity, int dtype,
+                                   float sm_scale, int split_len, void* stream);
+size_t pjx_attn_decode_static_scratch_bytes(void);
+
+/*
  * Exact combine of n_parts normalised partial results, each with its natural-
  * log LSE: m = max_p lse_p, w_p = exp(lse_p - m), o = sum w_p o_p / sum w_p,
  * lse = m + log sum w_p (attention_splitkv.py:236-250, in natural log).  Used

@@ -30,6 +30,8 @@ SIGNATURES = {
                                      _i, _i, _vp, _sz, _vp]),
     "pjx_attn_decode_workspace_bytes": (_sz, [_i, _i, _i, _i, _i, _i, _i]),
     "pjx_attn_decode_default_split_len": (_i, [_i, _i, _i]),
+    "pjx_attn_decode_splitkv_static": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _f, _i, _vp]),
+    "pjx_attn_decode_static_scratch_bytes": (_sz, []),
     "pjx_attn_combine": (_i, [_vp, _vp, _i, _i64, _i, _vp, _vp, _i, _vp]),
     "pjx_mla_fwd": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64,
                          _i, _i, _i, _i, _i, _i, _i, _i, _i, _f, _i, _vp, _sz, _vp, _vp]),

@@ -432,4 +432,107 @@ int launch_combine_parts(const float* o_parts, const float* lse_parts, int n_par
   return check_cuda(cudaGetLastError(), "combine launch");
 }
 
+
+// ---------------------------------------------------------------------------
+// Split-KV decode without any allocation by anyone.
+//
+// Some callers hold no allocator they may use at the moment they need a decode
+// step: a serving loop that runs inside a framework's custom-call handler is
+// handed its operand and result buffers only (XLA plans every byte ahead of time
+// and forbids cudaMalloc inside the handler), and so is code that runs while the
+// device allocator is locked or exhausted.  For them the per-split partials live
+// in the fixed device array below instead of a workspace argument.
+//
+// Every device that loads the library reserves the array until the process
+// exits, so it is kept modest: 16 MiB holds the partials of the benchmark's
+// decode (16 sequences x 8 KV heads x 27 splits x 4 packed rows x 129 floats =
+// 7.1 MB) twice over.  Larger calls are rejected, not truncated.
+//
+// All calls share the one array.  Nothing in it has to start at zero: the combine
+// kernel reads exactly the partials that the split kernel of the same call wrote
+// (splits past a sequence's length are neither written nor read), so leftovers of
+// an earlier call are never looked at.  Two calls whose kernels overlap on the
+// GPU (different streams, or different host threads) would overwrite each other's
+// partials: callers must order them on one stream.
+// ---------------------------------------------------------------------------
+namespace {
+
+constexpr size_t kStaticScratchFloats = 4u * 1024u * 1024u;  // 16 MiB
+static __device__ __align__(256) float g_decode_scratch[kStaticScratchFloats];
+
+constexpr int kMaxDevices = 64;
+float* g_scratch_ptr[kMaxDevices] = {};  // device address of g_decode_scratch, per device
+
+inline size_t round256(size_t x) { return (x + 255) / 256 * 256; }
+
+// The array's name is only a host-side handle; kernels need its device address,
+// which differs per device and is looked up once per device with that device
+// current.
+int static_scratch_address(float** out) {
+  int dev = -1;
+  int rc = check_cuda(cudaGetDevice(&dev), "cudaGetDevice");
+  if (rc) return rc;
+  if (dev < 0 || dev >= kMaxDevices) return fail(PJX_ERR_UNSUPPORTED, "device index %d is beyond the %d supported", dev, kMaxDevices);
+  float* p = __atomic_load_n(&g_scratch_ptr[dev], __ATOMIC_ACQUIRE);
+  if (!p) {
+    void* sym = nullptr;
+    rc = check_cuda(cudaGetSymbolAddress(&sym, g_decode_scratch), "cudaGetSymbolAddress(decode scratch)");
+    if (rc) return rc;
+    if (!sym) return fail(PJX_ERR_CUDA, "cudaGetSymbolAddress returned a null address for the decode scratch");
+    p = static_cast<float*>(sym);
+    __atomic_store_n(&g_scratch_ptr[dev], p, __ATOMIC_RELEASE);  // every thread computes the same value
+  }
+  *out = p;
+  return PJX_OK;
+}
+
+}  // namespace
 }  // namespace pjx
+
+extern "C" {
+
+size_t pjx_attn_decode_static_scratch_bytes(void) { return pjx::kStaticScratchFloats * sizeof(float); }
+
+int pjx_attn_decode_splitkv_static(const void* q, const void* k_cache, const void* v_cache,
+                                   const int32_t* kv_lengths, void* o, float* lse, int B, int Lq, int Hq,
+                                   int Hkv, int D, int Dv, int capacity, int dtype, float sm_scale,
+                                   int split_len, void* stream) {
+  using namespace pjx;
+  if (B < 0 || Lq < 0 || capacity < 0 || Hq < 1 || Hkv < 1 || D < 1 || Dv < 1)
+    return fail(PJX_ERR_BAD_ARG, "negative or zero dimension (B=%d Lq=%d capacity=%d Hq=%d Hkv=%d D=%d Dv=%d)", B, Lq, capacity, Hq, Hkv, D, Dv);
+  if (Hq % Hkv != 0) return fail(PJX_ERR_BAD_ARG, "query heads %d must be a multiple of kv heads %d", Hq, Hkv);
+  if (B == 0 || Lq == 0) return PJX_OK;
+  if (!q || !k_cache || !v_cache || !o) return fail(PJX_ERR_BAD_ARG, "q, k_cache, v_cache and o must not be null");
+  DecodeParams p;
+  p.q = q; p.k = k_cache; p.v = v_cache; p.kv_lengths = kv_lengths; p.o = o; p.lse = lse;
+  p.B = B; p.Lq = Lq; p.Hq = Hq; p.Hkv = Hkv; p.D = D; p.Dv = Dv; p.capacity = capacity;
+  p.rows = (Hq / Hkv) * Lq;
+  p.sm_scale = sm_scale;
+  p.o_is_f32 = 0;
+  const bool aligned =
+      ((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(k_cache) | reinterpret_cast<uintptr_t>(v_cache)) & 15) == 0;
+  if (!decode_fast_supported(p, dtype) || !aligned || capacity == 0)
+    return fail(PJX_ERR_UNSUPPORTED,
+                "the allocation-free decode takes bf16/fp16, D = Dv in {64,128}, (Hq/Hkv)*Lq <= 16, capacity > 0 and 16-byte aligned q/k/v");
+  if (split_len == 0) split_len = pjx_attn_decode_default_split_len(B, Hkv, capacity);
+  if (split_len < 64 || split_len % 64 != 0)
+    return fail(PJX_ERR_BAD_ARG, "split_len must be a positive multiple of 64 (got %d)", split_len);
+  p.split_len = split_len;
+  p.num_splits = (capacity + split_len - 1) / split_len;
+  const size_t parts = (size_t)B * Hkv * p.num_splits * p.rows;
+  const size_t o_bytes = round256(parts * Dv * sizeof(float));
+  const size_t need = o_bytes + round256(parts * sizeof(float));
+  if (need > kStaticScratchFloats * sizeof(float))
+    return fail(PJX_ERR_WORKSPACE,
+                "the allocation-free decode holds %zu bytes of partials; this call needs %zu (B=%d Hkv=%d splits=%d rows=%d Dv=%d): "
+                "use a larger split_len or pjx_attn_decode_splitkv with a workspace",
+                kStaticScratchFloats * sizeof(float), need, B, Hkv, p.num_splits, p.rows, Dv);
+  float* scratch = nullptr;
+  int rc = static_scratch_address(&scratch);
+  if (rc) return rc;
+  p.o_part = scratch;
+  p.lse_part = reinterpret_cast<float*>(reinterpret_cast<char*>(scratch) + o_bytes);
+  return launch_decode(p, dtype, static_cast<cudaStream_t>(stream));
+}
+
+}  // extern "C"
