@@ -10,7 +10,9 @@
 //   warp 1      MMA issuer (one lane): S_t = Q_t.K^T (both operands in shared
 //               memory), O_t += P_t.V (P_t read from tensor memory, V in shared
 //               memory, MN-major)
-//   warps 2-5   softmax of tile 0: one thread per query row
+//   warps 2-5   softmax of tile 0: one thread per query row, two passes over the
+//               row's scores in tensor memory (maximum, then exp2 / sum / pack) in
+//               32-column chunks with the next chunk's load in flight
 //   warps 6-9   softmax of tile 1
 //
 // Tensor memory (columns): S0 | S1 | O0 | O1, 128 lanes = 128 query rows.  P_t is
@@ -36,6 +38,17 @@ using namespace sm100;
 
 constexpr int BM = 128;          // rows per query tile (= tensor-memory lanes)
 constexpr int NTHREADS = 320;    // 10 warps
+
+__device__ __forceinline__ float ex2_approx(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+__device__ __forceinline__ float fmax3(float a, float b, float c) {
+  float y;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(y) : "f"(a), "f"(b), "f"(c));
+  return y;
+}
 
 template <int DQK, int DV, int BN, int KST, int VST>
 struct Cfg {
@@ -222,7 +235,7 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
     const int r_in = quarter * 32 + lane;
     const int row = q0 + t * BM + r_in;
     const bool row_ok = row < p.Lq;
-    const int my_n = n_t[t];
+    const int my_n = t ? n_t[1] : n_t[0];
     const uint32_t lane_sel = static_cast<uint32_t>(quarter * 32) << 16;
     const uint32_t s_addr = tmem + lane_sel + t * BN;
     const uint32_t o_addr = tmem + lane_sel + 2 * BN + t * DV;
@@ -240,43 +253,62 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       tc_fence_after();
-      float s[BN];
-#pragma unroll
-      for (int c = 0; c < BN / 32; ++c) tmem_ld32f(s_addr + c * 32, &s[c * 32]);
-      tmem_wait_ld();
-
+      constexpr int NCH = BN / 32;
       const int k0 = j * BN;
-      if (p.bias) {
-        if (bias_row && bias_vec && k0 + BN <= p.Lkv) {
-          const float4* bp = reinterpret_cast<const float4*>(bias_row + k0);
-#pragma unroll
-          for (int c = 0; c < BN / 4; ++c) {
-            const float4 bv = __ldg(bp + c);
-            s[4 * c + 0] = fmaf(bv.x, kLog2e, s[4 * c + 0] * c1);
-            s[4 * c + 1] = fmaf(bv.y, kLog2e, s[4 * c + 1] * c1);
-            s[4 * c + 2] = fmaf(bv.z, kLog2e, s[4 * c + 2] * c1);
-            s[4 * c + 3] = fmaf(bv.w, kLog2e, s[4 * c + 3] * c1);
-          }
-        } else {
-#pragma unroll
-          for (int c = 0; c < BN; ++c) {
-            const float bv = (bias_row && k0 + c < p.Lkv) ? __ldg(bias_row + k0 + c) : 0.f;
-            s[c] = fmaf(bv, kLog2e, s[c] * c1);
-          }
-        }
-      }
       const bool need_mask = (k0 + BN > kv_len) || (p.causal && k0 + BN - 1 > q0 + t * BM);
-      if (need_mask) {
+      const bool rewrite = (p.bias != nullptr) || need_mask;  // uniform over the CTA tile
+      float buf[2][32];
+
+      // ---- pass 1: bias and mask (written back when present), row maximum ----
+      float m0 = -INFINITY, m1 = -INFINITY, m2 = -INFINITY, m3 = -INFINITY;  // independent chains
+      tmem_ld32f(s_addr, buf[0]);
+      tmem_wait_ld();
 #pragma unroll
-        for (int c = 0; c < BN; ++c) {
-          const int key = k0 + c;
-          const bool keep = key < kv_len && (!p.causal || key <= row);
-          s[c] = keep ? s[c] : -INFINITY;
+      for (int c = 0; c < NCH; ++c) {
+        float* cur = buf[c & 1];
+        if (c + 1 < NCH) tmem_ld32f(s_addr + (c + 1) * 32, buf[(c + 1) & 1]);
+        if (rewrite) {
+          const int kc = k0 + c * 32;
+          if (p.bias) {
+            if (bias_row && bias_vec && kc + 32 <= p.Lkv) {
+              const float4* bp = reinterpret_cast<const float4*>(bias_row + kc);
+#pragma unroll
+              for (int i = 0; i < 8; ++i) {
+                const float4 bv = __ldg(bp + i);
+                cur[4 * i + 0] = fmaf(bv.x, kLog2e, cur[4 * i + 0] * c1);
+                cur[4 * i + 1] = fmaf(bv.y, kLog2e, cur[4 * i + 1] * c1);
+                cur[4 * i + 2] = fmaf(bv.z, kLog2e, cur[4 * i + 2] * c1);
+                cur[4 * i + 3] = fmaf(bv.w, kLog2e, cur[4 * i + 3] * c1);
+              }
+            } else {
+#pragma unroll
+              for (int i = 0; i < 32; ++i) {
+                const float bv = (bias_row && kc + i < p.Lkv) ? __ldg(bias_row + kc + i) : 0.f;
+                cur[i] = fmaf(bv, kLog2e, cur[i] * c1);
+              }
+            }
+          }
+          if (need_mask) {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) {
+              const int key = kc + i;
+              const bool keep = key < kv_len && (!p.causal || key <= row);
+              cur[i] = keep ? cur[i] : -INFINITY;
+            }
+          }
+          tmem_st32f(s_addr + c * 32, cur);
         }
-      }
-      float mx = -INFINITY;
 #pragma unroll
-      for (int c = 0; c < BN; ++c) mx = fmaxf(mx, s[c]);
+        for (int i = 0; i < 4; ++i) {
+          m0 = fmax3(m0, cur[8 * i + 0], cur[8 * i + 1]);
+          m1 = fmax3(m1, cur[8 * i + 2], cur[8 * i + 3]);
+          m2 = fmax3(m2, cur[8 * i + 4], cur[8 * i + 5]);
+          m3 = fmax3(m3, cur[8 * i + 6], cur[8 * i + 7]);
+        }
+        if (c + 1 < NCH) tmem_wait_ld();
+      }
+      if (rewrite) tmem_wait_st();
+      float mx = fmaxf(fmaxf(m0, m1), fmaxf(m2, m3));
       mx *= cs;  // cs > 0
 
       // lazy running maximum: advance only when it grew by more than 8 (base 2)
@@ -289,36 +321,48 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
         if (j > 0) {
 #pragma unroll
           for (int c = 0; c < DV / 32; ++c) {
-            float o[32];
-            tmem_ld32f(o_addr + c * 32, o);
+            tmem_ld32f(o_addr + c * 32, buf[0]);
             tmem_wait_ld();
 #pragma unroll
-            for (int i = 0; i < 32; ++i) o[i] *= corr;
-            tmem_st32f(o_addr + c * 32, o);
+            for (int i = 0; i < 32; ++i) buf[0][i] *= corr;
+            tmem_st32f(o_addr + c * 32, buf[0]);
           }
         }
       }
+
+      // ---- pass 2: p = exp2(x * cs - m), row sum, pack to 16 bits, store over S ----
       const float neg_m = (m_ref == -INFINITY) ? 0.f : -m_ref;
-      float lsum = 0.f;
+      const float2 cs2 = make_float2(cs, cs), nm2 = make_float2(neg_m, neg_m);
+      float2 sum0 = make_float2(0.f, 0.f), sum1 = make_float2(0.f, 0.f);
+      tmem_ld32f(s_addr, buf[0]);
+      tmem_wait_ld();
 #pragma unroll
-      for (int c = 0; c < BN / 64; ++c) {
-        uint32_t pk[32];
+      for (int c = 0; c < NCH; ++c) {
+        const float* cur = buf[c & 1];
+        if (c + 1 < NCH) tmem_ld32f(s_addr + (c + 1) * 32, buf[(c + 1) & 1]);
+        uint32_t pk[16];
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          const float p0 = exp2f(fmaf(s[c * 64 + 2 * i], cs, neg_m));
-          const float p1 = exp2f(fmaf(s[c * 64 + 2 * i + 1], cs, neg_m));
-          lsum += p0 + p1;
-          pk[i] = pack16<BF16>(p0, p1);
+        for (int i = 0; i < 16; i += 2) {
+          const float2 x0 = __ffma2_rn(make_float2(cur[2 * i], cur[2 * i + 1]), cs2, nm2);
+          const float2 x1 = __ffma2_rn(make_float2(cur[2 * i + 2], cur[2 * i + 3]), cs2, nm2);
+          const float2 p0 = make_float2(ex2_approx(x0.x), ex2_approx(x0.y));
+          const float2 p1 = make_float2(ex2_approx(x1.x), ex2_approx(x1.y));
+          sum0 = __fadd2_rn(sum0, p0);
+          sum1 = __fadd2_rn(sum1, p1);
+          pk[i] = pack16<BF16>(p0.x, p0.y);
+          pk[i + 1] = pack16<BF16>(p1.x, p1.y);
         }
-        tmem_st32(s_addr + c * 32, pk);
+        if (c + 1 < NCH) tmem_wait_ld();  // chunk c + 1 covers the columns written next: it has landed
+        tmem_st16(s_addr + c * 16, pk);
       }
+      const float lsum = (sum0.x + sum0.y) + (sum1.x + sum1.y);
       l += lsum;
       tmem_wait_st();
       tc_fence_before();
       mbar_arrive(BAR(P_FULL + t));
     }
 
-    if (ok && n_t[t] >= 0 && (q0 + t * BM) < p.Lq) {
+    if (ok && (q0 + t * BM) < p.Lq) {
       const float inv = l > 0.f ? 1.f / l : 0.f;
       if (my_n > 0) {
         ok = mbar_wait(BAR(O_FULL + t), 0, abort_flag);
