@@ -62,55 +62,72 @@ def prefill_flops(B, Hq, Lq, Lkv, D, Dv, causal):
 
 
 class ClockSampler:
-    """Samples SM clocks and throttle reasons with nvidia-smi while a region runs."""
+    """Samples SM clocks and clock-event reasons through NVML (read-only) every
+    couple of milliseconds while a region runs; falls back to nvidia-smi."""
 
-    Q = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
-         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
-         "clocks_event_reasons.sw_power_cap")
+    REASONS = {0x8: "hw_slowdown", 0x40: "hw_thermal_slowdown", 0x20: "sw_thermal_slowdown", 0x4: "sw_power_cap"}
 
     def __init__(self, index=0):
-        self.index, self.rows, self.proc = index, [], None
+        self.index, self.sm, self.bits, self.max_mhz = index, [], 0, None
+        self.stop, self.th, self.proc = threading.Event(), None, None
+
+    def _nvml_loop(self, nv, handle):
+        getr = getattr(nv, "nvmlDeviceGetCurrentClocksEventReasons", None) or nv.nvmlDeviceGetCurrentClocksThrottleReasons
+        while not self.stop.is_set():
+            try:
+                self.sm.append(float(nv.nvmlDeviceGetClockInfo(handle, nv.NVML_CLOCK_SM)))
+                self.bits |= int(getr(handle))
+            except Exception:
+                pass
+            time.sleep(0.002)
 
     def __enter__(self):
         try:
-            self.proc = subprocess.Popen(
-                ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "100"],
-                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
-            self.th = threading.Thread(target=self._read, daemon=True)
+            import pynvml as nv
+
+            nv.nvmlInit()
+            uuid = str(torch.cuda.get_device_properties(self.index).uuid)
+            uuid = uuid if uuid.startswith("GPU-") else "GPU-" + uuid
+            try:
+                handle = nv.nvmlDeviceGetHandleByUUID(uuid.encode())
+            except Exception:
+                handle = nv.nvmlDeviceGetHandleByIndex(self.index)
+            self.max_mhz = float(nv.nvmlDeviceGetMaxClockInfo(handle, nv.NVML_CLOCK_SM))
+            self.th = threading.Thread(target=self._nvml_loop, args=(nv, handle), daemon=True)
             self.th.start()
         except Exception:
-            self.proc = None
+            self.th = None
+            try:
+                q = "clocks.sm,clocks.max.sm,clocks_event_reasons.active"
+                self.proc = subprocess.Popen(["nvidia-smi", f"--id={self.index}", f"--query-gpu={q}",
+                                              "--format=csv,noheader,nounits", "-lms", "50"],
+                                             stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            except Exception:
+                self.proc = None
         return self
 
-    def _read(self):
-        for line in self.proc.stdout:
-            self.rows.append([x.strip() for x in line.split(",")])
-
     def __exit__(self, *a):
+        self.stop.set()
+        if self.th:
+            self.th.join(timeout=1)
         if self.proc:
-            time.sleep(0.15)
+            time.sleep(0.1)
             self.proc.terminate()
             try:
-                self.proc.wait(timeout=2)
+                out, _ = self.proc.communicate(timeout=2)
+                for line in out.splitlines():
+                    f = [x.strip() for x in line.split(",")]
+                    self.sm.append(float(f[0]))
+                    self.max_mhz = float(f[1])
+                    self.bits |= int(f[2], 16)
             except Exception:
-                self.proc.kill()
+                pass
 
     def summary(self):
-        sm, mx, reasons = [], [], set()
-        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        for r in self.rows:
-            try:
-                sm.append(float(r[0]))
-                mx.append(float(r[1]))
-                for nm, val in zip(names, r[4:8]):
-                    if val.lower().startswith("active"):
-                        reasons.add(nm)
-            except Exception:
-                continue
-        if not sm:
-            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
-        busy = sorted(sm)[len(sm) // 2:]  # upper half: samples taken under load
-        return {"sm_mhz": statistics.median(busy), "sm_max_mhz": max(mx), "reasons": sorted(reasons), "samples": len(sm)}
+        if not self.sm:
+            return {"sm_mhz": None, "sm_max_mhz": self.max_mhz, "reasons": [], "samples": 0}
+        return {"sm_mhz": statistics.median(self.sm), "sm_min_mhz": min(self.sm), "sm_max_mhz": self.max_mhz,
+                "reasons": sorted(n for b, n in self.REASONS.items() if self.bits & b), "samples": len(self.sm)}
 
 
 def time_steps(fn, steps, warmup, dist_on=False):

@@ -164,7 +164,9 @@ size_t pjx_mla_workspace_bytes(int B, int S, int H, int Dqk, int Dv, int R, int 
 /*
  * The forward with HOST buffers: copies q, k, v (and kv_lengths, bias) to the
  * device staging area, runs pjx_attn_fwd, copies o (and lse) back, and
- * synchronises the stream before returning.  `staging` is device memory of
+ * synchronises the stream before returning.  The batch is processed in chunks so
+ * that uploads, kernels and downloads overlap (two internal copy streams per
+ * device, created on first use).  `staging` is device memory of
  * pjx_attn_fwd_host_staging_bytes(...) bytes owned by the caller.  Same
  * reference interface as pjx_attn_fwd; this is the call a host-side plugin
  * makes when its arrays live in host memory.

@@ -23,10 +23,10 @@ namespace {
 
 using namespace sm100;
 
-constexpr int TM = 128, TN = 128, TK = 64, ST = 4;
+constexpr int TM = 128, TN = 256, TK = 64, ST = 4;
 constexpr int A_BYTES = TM * TK * 2, B_BYTES = TN * TK * 2;
 constexpr int G_OFF_BAR = ST * (A_BYTES + B_BYTES);
-constexpr int G_NBAR = 2 * ST + 1;
+constexpr int G_NBAR = 2 * ST + 4;
 constexpr int G_SMEM = G_OFF_BAR + G_NBAR * 8 + 16 + 1024;
 constexpr int G_THREADS = 192;
 
@@ -41,29 +41,49 @@ __device__ __forceinline__ uint32_t gpack(float lo, float hi) {
   }
 }
 
+// Up to two products that share A run in one launch: C0 = A.B0^T [M, N0] and
+// C1 = A.B1^T [M, N1] (keys and values of latent attention).  Persistent CTAs walk
+// the 128 x 256 output tiles of both; the accumulator is double buffered in tensor
+// memory (2 x 256 columns) so the epilogue of one tile overlaps the MMAs of the next.
+struct GemmArgs {
+  void* c0;
+  void* c1;
+  int64_t M;
+  int n0, n1, K;
+  int32_t* status;
+};
+
 template <bool BF16>
 __global__ void __launch_bounds__(G_THREADS, 1)
-gemm_tn_sm100_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
-                     void* __restrict__ Cout, int64_t M, int N, int K, int32_t* status) {
+gemm_tn_sm100_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b0,
+                     const __grid_constant__ CUtensorMap tm_b1, const GemmArgs g) {
   extern __shared__ unsigned char smem_unaligned[];
   unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_unaligned) + 1023) & ~uintptr_t(1023));
   const uint32_t sbase = smem_u32(smem);
   auto BAR = [&](int i) { return sbase + G_OFF_BAR + 8u * i; };
-  const int FULL = 0, EMPTY = ST, ACC = 2 * ST;
+  const int FULL = 0, EMPTY = ST, ACC_FULL = 2 * ST, ACC_EMPTY = 2 * ST + 2;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + G_OFF_BAR + G_NBAR * 8);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int n0 = blockIdx.x * TN;
-  const int64_t m0 = (int64_t)blockIdx.y * TM;
-  const int nk = (K + TK - 1) / TK;
+  const int nk = (g.K + TK - 1) / TK;
+  const int mt = (int)((g.M + TM - 1) / TM);
+  const int nt0 = (g.n0 + TN - 1) / TN, nt1 = (g.n1 + TN - 1) / TN;
+  const int ntiles = mt * (nt0 + nt1);
+  // tile id -> (which product, m tile, n tile); consecutive ids share the B tile
+  auto decode = [&](int tile, int& which, int& m_idx, int& n_idx) {
+    int col = tile / mt;
+    m_idx = tile - col * mt;
+    which = col >= nt0;
+    n_idx = which ? col - nt0 : col;
+  };
 
   if (threadIdx.x == 0) {
-    for (int i = 0; i < G_NBAR; ++i) mbar_init(BAR(i), 1);
+    for (int i = 0; i < G_NBAR; ++i) mbar_init(BAR(i), (i >= ACC_EMPTY) ? 128u : 1u);
     *abort_flag = 0;
     fence_barrier_init();
   }
   if (warp == 0) {
-    tmem_alloc(smem_u32(tmem_slot), 128);
+    tmem_alloc(smem_u32(tmem_slot), 512);
     tmem_relinquish();
   }
   tc_fence_before();
@@ -74,78 +94,107 @@ gemm_tn_sm100_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_cons
   if (warp == 0) {
     if (lane == 0) {
       prefetch_tmap(&tm_a);
-      prefetch_tmap(&tm_b);
-      for (int k = 0; k < nk; ++k) {
-        const int s = k % ST;
-        if (!mbar_wait(BAR(EMPTY + s), ((k / ST) & 1) ^ 1, abort_flag)) break;
-        mbar_arrive_expect_tx(BAR(FULL + s), A_BYTES + B_BYTES);
-        tma_load_2d(sbase + s * (A_BYTES + B_BYTES), &tm_a, BAR(FULL + s), k * TK, (int)m0);
-        tma_load_2d(sbase + s * (A_BYTES + B_BYTES) + A_BYTES, &tm_b, BAR(FULL + s), k * TK, n0);
+      prefetch_tmap(&tm_b0);
+      if (nt1) prefetch_tmap(&tm_b1);
+      int it = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; ok && tile < ntiles; tile += gridDim.x) {
+        int which, m_idx, n_idx;
+        decode(tile, which, m_idx, n_idx);
+        const CUtensorMap* tb = which ? &tm_b1 : &tm_b0;
+        for (int k = 0; k < nk; ++k, ++it) {
+          const int s = it % ST;
+          ok = mbar_wait(BAR(EMPTY + s), ((it / ST) & 1) ^ 1, abort_flag);
+          if (!ok) break;
+          mbar_arrive_expect_tx(BAR(FULL + s), A_BYTES + B_BYTES);
+          const uint32_t a = sbase + s * (A_BYTES + B_BYTES);
+          tma_load_2d(a, &tm_a, BAR(FULL + s), k * TK, m_idx * TM);
+          // the B tile is 256 rows: two 128-row boxes
+          tma_load_2d(a + A_BYTES, tb, BAR(FULL + s), k * TK, n_idx * TN);
+          tma_load_2d(a + A_BYTES + B_BYTES / 2, tb, BAR(FULL + s), k * TK, n_idx * TN + 128);
+        }
       }
     }
   } else if (warp == 1) {
     if (lane == 0) {
       constexpr uint32_t idesc = make_idesc(TM, TN, BF16, false, false);
+      int it = 0, local = 0;
       bool ok = true;
-      for (int k = 0; k < nk; ++k) {
-        const int s = k % ST;
-        ok = mbar_wait(BAR(FULL + s), (k / ST) & 1, abort_flag);
+      for (int tile = blockIdx.x; ok && tile < ntiles; tile += gridDim.x, ++local) {
+        const int acc = local & 1;
+        ok = mbar_wait(BAR(ACC_EMPTY + acc), ((local >> 1) & 1) ^ 1, abort_flag);
         if (!ok) break;
         tc_fence_after();
-        const uint32_t a = sbase + s * (A_BYTES + B_BYTES), bb = a + A_BYTES;
+        for (int k = 0; k < nk; ++k, ++it) {
+          const int s = it % ST;
+          ok = mbar_wait(BAR(FULL + s), (it / ST) & 1, abort_flag);
+          if (!ok) break;
+          tc_fence_after();
+          const uint32_t a = sbase + s * (A_BYTES + B_BYTES), bb = a + A_BYTES;
 #pragma unroll
-        for (int kk = 0; kk < TK / 16; ++kk)
-          mma_ss(tmem, make_smem_desc(a + kk * 32, 16, 1024), make_smem_desc(bb + kk * 32, 16, 1024), idesc,
-                 (k | kk) != 0);
-        mma_commit(BAR(EMPTY + s));
+          for (int kk = 0; kk < TK / 16; ++kk)
+            mma_ss(tmem + acc * TN, make_smem_desc(a + kk * 32, 16, 1024), make_smem_desc(bb + kk * 32, 16, 1024),
+                   idesc, (k | kk) != 0);
+          mma_commit(BAR(EMPTY + s));
+        }
+        if (ok) mma_commit(BAR(ACC_FULL + acc));
       }
-      if (ok) mma_commit(BAR(ACC));
     }
   } else {
     const int quarter = warp & 3;
-    bool ok = mbar_wait(BAR(ACC), 0, abort_flag);
-    ok = __all_sync(0xffffffffu, ok);
-    if (ok) {
+    int local = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; ok && tile < ntiles; tile += gridDim.x, ++local) {
+      const int acc = local & 1;
+      int which, m_idx, n_idx;
+      decode(tile, which, m_idx, n_idx);
+      const int N = which ? g.n1 : g.n0;
+      void* Cout = which ? g.c1 : g.c0;
+      ok = mbar_wait(BAR(ACC_FULL + acc), (local >> 1) & 1, abort_flag);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
       tc_fence_after();
-      const int64_t row = m0 + quarter * 32 + lane;
-      const uint32_t taddr = tmem + (static_cast<uint32_t>(quarter * 32) << 16);
+      const int64_t row = (int64_t)m_idx * TM + quarter * 32 + lane;
+      const uint32_t taddr = tmem + (static_cast<uint32_t>(quarter * 32) << 16) + acc * TN;
       const bool vec_ok = (N % 8 == 0) && ((reinterpret_cast<uintptr_t>(Cout) & 15) == 0);
-#pragma unroll
+#pragma unroll 2
       for (int c = 0; c < TN / 32; ++c) {
-        float acc[32];
-        tmem_ld32f(taddr + c * 32, acc);
+        float accv[32];
+        tmem_ld32f(taddr + c * 32, accv);
         tmem_wait_ld();
-        const int col0 = n0 + c * 32;
-        if (row < M && col0 < N) {
+        const int col0 = n_idx * TN + c * 32;
+        if (row < g.M && col0 < N) {
           unsigned char* dst = static_cast<unsigned char*>(Cout) + (row * N + col0) * 2;
           if (vec_ok && col0 + 32 <= N) {
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
               uint4 w;
-              w.x = gpack<BF16>(acc[8 * i + 0], acc[8 * i + 1]);
-              w.y = gpack<BF16>(acc[8 * i + 2], acc[8 * i + 3]);
-              w.z = gpack<BF16>(acc[8 * i + 4], acc[8 * i + 5]);
-              w.w = gpack<BF16>(acc[8 * i + 6], acc[8 * i + 7]);
+              w.x = gpack<BF16>(accv[8 * i + 0], accv[8 * i + 1]);
+              w.y = gpack<BF16>(accv[8 * i + 2], accv[8 * i + 3]);
+              w.z = gpack<BF16>(accv[8 * i + 4], accv[8 * i + 5]);
+              w.w = gpack<BF16>(accv[8 * i + 6], accv[8 * i + 7]);
               reinterpret_cast<uint4*>(dst)[i] = w;
             }
           } else {
 #pragma unroll
             for (int i = 0; i < 32; ++i)
               if (col0 + i < N) {
-                if constexpr (BF16) reinterpret_cast<__nv_bfloat16*>(dst)[i] = __float2bfloat16_rn(acc[i]);
-                else reinterpret_cast<__half*>(dst)[i] = __float2half_rn(acc[i]);
+                if constexpr (BF16) reinterpret_cast<__nv_bfloat16*>(dst)[i] = __float2bfloat16_rn(accv[i]);
+                else reinterpret_cast<__half*>(dst)[i] = __float2half_rn(accv[i]);
               }
           }
         }
       }
+      tc_fence_before();
+      mbar_arrive(BAR(ACC_EMPTY + acc));
     }
   }
   tc_fence_before();
   __syncthreads();
   if (warp == 0) {
     __syncwarp();
-    tmem_dealloc(tmem, 128);
-    if (lane == 0 && *abort_flag && status) atomicExch(status, (int)PJX_ERR_DEVICE_TIMEOUT);
+    tmem_dealloc(tmem, 512);
+    if (lane == 0 && *abort_flag && g.status) atomicExch(g.status, (int)PJX_ERR_DEVICE_TIMEOUT);
   }
 }
 
@@ -234,38 +283,64 @@ int make_tmap_2d(CUtensorMap* m, const void* base, int dtype, int64_t rows, int6
   return PJX_OK;
 }
 
-int launch_gemm_tn(const void* A, const void* Bm, void* C, int64_t M, int N, int K, int dtype, int impl,
-                   cudaStream_t stream) {
-  if (M == 0 || N == 0) return PJX_OK;
-  const bool tc_ok = (dtype == PJX_BF16 || dtype == PJX_F16) && K % 8 == 0 && K >= 64 &&
-                     ((reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(Bm)) & 15) == 0 &&
-                     (M + TM - 1) / TM <= 65535;
-  if (impl == PJX_IMPL_SM100 && !tc_ok)
-    return fail(PJX_ERR_UNSUPPORTED, "tcgen05 projection needs 16-bit inputs, K %% 8 == 0, K >= 64 and 16-byte aligned operands");
-  if (impl != PJX_IMPL_GENERIC && tc_ok) {
-    CUtensorMap ta, tb;
-    int rc;
-    if ((rc = make_tmap_2d(&ta, A, dtype, M, K, TM))) return rc;
-    if ((rc = make_tmap_2d(&tb, Bm, dtype, N, K, TN))) return rc;
-    dim3 grid((N + TN - 1) / TN, (unsigned)((M + TM - 1) / TM));
-    if (dtype == PJX_BF16) {
-      auto kern = gemm_tn_sm100_kernel<true>;
-      if ((rc = check_cuda(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, G_SMEM), "cudaFuncSetAttribute(projection)"))) return rc;
-      kern<<<grid, G_THREADS, G_SMEM, stream>>>(ta, tb, C, M, N, K, nullptr);
-    } else {
-      auto kern = gemm_tn_sm100_kernel<false>;
-      if ((rc = check_cuda(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, G_SMEM), "cudaFuncSetAttribute(projection)"))) return rc;
-      kern<<<grid, G_THREADS, G_SMEM, stream>>>(ta, tb, C, M, N, K, nullptr);
-    }
-    count_launch();
-    return check_cuda(cudaGetLastError(), "projection (tcgen05) launch");
-  }
+namespace {
+
+int simt_by_dtype(const void* A, const void* Bm, void* C, int64_t M, int N, int K, int dtype, cudaStream_t stream) {
   switch (dtype) {
     case PJX_F32: return launch_simt<float>(A, Bm, C, M, N, K, stream);
     case PJX_BF16: return launch_simt<__nv_bfloat16>(A, Bm, C, M, N, K, stream);
     case PJX_F16: return launch_simt<__half>(A, Bm, C, M, N, K, stream);
   }
   return fail(PJX_ERR_BAD_ARG, "unknown dtype %d", dtype);
+}
+
+}  // namespace
+
+int launch_gemm_tn2(const void* A, const void* B0, void* C0, int N0, const void* B1, void* C1, int N1, int64_t M,
+                    int K, int dtype, int impl, int32_t* status, cudaStream_t stream) {
+  if (M == 0 || (N0 == 0 && N1 == 0)) return PJX_OK;
+  uintptr_t al = reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(B0);
+  if (N1) al |= reinterpret_cast<uintptr_t>(B1);
+  const bool tc_ok = (dtype == PJX_BF16 || dtype == PJX_F16) && K % 8 == 0 && K >= 64 && (al & 15) == 0 &&
+                     M <= 2147483647LL - TM;
+  if (impl == PJX_IMPL_SM100 && !tc_ok)
+    return fail(PJX_ERR_UNSUPPORTED, "tcgen05 projection needs 16-bit inputs, K %% 8 == 0, K >= 64 and 16-byte aligned operands");
+  if (impl != PJX_IMPL_GENERIC && tc_ok) {
+    CUtensorMap ta, tb0, tb1;
+    int rc;
+    if ((rc = make_tmap_2d(&ta, A, dtype, M, K, TM))) return rc;
+    if ((rc = make_tmap_2d(&tb0, B0, dtype, N0, K, 128))) return rc;
+    if (N1) {
+      if ((rc = make_tmap_2d(&tb1, B1, dtype, N1, K, 128))) return rc;
+    } else {
+      tb1 = tb0;
+    }
+    GemmArgs g;
+    g.c0 = C0; g.c1 = C1; g.M = M; g.n0 = N0; g.n1 = N1; g.K = K; g.status = status;
+    const int64_t tiles = ((M + TM - 1) / TM) * ((N0 + TN - 1) / TN + (N1 + TN - 1) / TN);
+    int dev = 0, sms = 148;
+    if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    const unsigned grid = (unsigned)(tiles < sms ? tiles : sms);
+    if (dtype == PJX_BF16) {
+      auto kern = gemm_tn_sm100_kernel<true>;
+      if ((rc = check_cuda(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, G_SMEM), "cudaFuncSetAttribute(projection)"))) return rc;
+      kern<<<grid, G_THREADS, G_SMEM, stream>>>(ta, tb0, tb1, g);
+    } else {
+      auto kern = gemm_tn_sm100_kernel<false>;
+      if ((rc = check_cuda(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, G_SMEM), "cudaFuncSetAttribute(projection)"))) return rc;
+      kern<<<grid, G_THREADS, G_SMEM, stream>>>(ta, tb0, tb1, g);
+    }
+    count_launch();
+    return check_cuda(cudaGetLastError(), "projection (tcgen05) launch");
+  }
+  int rc = simt_by_dtype(A, B0, C0, M, N0, K, dtype, stream);
+  if (rc || !N1) return rc;
+  return simt_by_dtype(A, B1, C1, M, N1, K, dtype, stream);
+}
+
+int launch_gemm_tn(const void* A, const void* Bm, void* C, int64_t M, int N, int K, int dtype, int impl,
+                   cudaStream_t stream) {
+  return launch_gemm_tn2(A, Bm, C, N, nullptr, nullptr, 0, M, K, dtype, impl, nullptr, stream);
 }
 
 }  // namespace pjx

@@ -4,6 +4,7 @@
 #include <cstdarg>
 #include <cstdio>
 #include <cstring>
+#include <mutex>
 
 #include "pjx_common.cuh"
 
@@ -40,6 +41,38 @@ int validate_common(const void* q, const void* k, const void* v, const void* o, 
     return fail(PJX_ERR_BAD_ARG, "query heads %d must be a multiple of kv heads %d", Hq, Hkv);
   if (B > 0 && Lq > 0 && (!q || !o)) return fail(PJX_ERR_BAD_ARG, "q and o must not be null");
   if (B > 0 && Lkv > 0 && (!k || !v)) return fail(PJX_ERR_BAD_ARG, "k and v must not be null");
+  return PJX_OK;
+}
+
+// Streams and events of the host-buffer call, one set per device, created on first use.
+constexpr int kHostChunks = 8;
+struct HostPipe {
+  cudaStream_t in = nullptr, out = nullptr;
+  cudaEvent_t start = nullptr, finish = nullptr, up[kHostChunks] = {}, done[kHostChunks] = {};
+  bool ready = false;
+};
+std::mutex g_pipe_mu;
+HostPipe g_pipes[64];
+
+int host_pipe(HostPipe** out) {
+  int dev = 0;
+  int rc = check_cuda(cudaGetDevice(&dev), "cudaGetDevice");
+  if (rc) return rc;
+  if (dev < 0 || dev >= 64) return fail(PJX_ERR_UNSUPPORTED, "device index %d out of range", dev);
+  std::lock_guard<std::mutex> lock(g_pipe_mu);
+  HostPipe& p = g_pipes[dev];
+  if (!p.ready) {
+    if ((rc = check_cuda(cudaStreamCreateWithFlags(&p.in, cudaStreamNonBlocking), "create upload stream"))) return rc;
+    if ((rc = check_cuda(cudaStreamCreateWithFlags(&p.out, cudaStreamNonBlocking), "create download stream"))) return rc;
+    if ((rc = check_cuda(cudaEventCreateWithFlags(&p.start, cudaEventDisableTiming), "create event"))) return rc;
+    if ((rc = check_cuda(cudaEventCreateWithFlags(&p.finish, cudaEventDisableTiming), "create event"))) return rc;
+    for (int i = 0; i < kHostChunks; ++i) {
+      if ((rc = check_cuda(cudaEventCreateWithFlags(&p.up[i], cudaEventDisableTiming), "create event"))) return rc;
+      if ((rc = check_cuda(cudaEventCreateWithFlags(&p.done[i], cudaEventDisableTiming), "create event"))) return rc;
+    }
+    p.ready = true;
+  }
+  *out = &p;
   return PJX_OK;
 }
 
@@ -201,8 +234,7 @@ int pjx_mla_fwd(const void* q, const void* cache, const void* wk, const void* wv
   void* vmat = static_cast<char*>(workspace) + align_up((size_t)B * S * H * Dqk * es);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   int rc;
-  if ((rc = launch_gemm_tn(cache, wk, kmat, (int64_t)B * S, H * Dqk, R, dtype, impl, st))) return rc;
-  if ((rc = launch_gemm_tn(cache, wv, vmat, (int64_t)B * S, H * Dv, R, dtype, impl, st))) return rc;
+  if ((rc = launch_gemm_tn2(cache, wk, kmat, H * Dqk, wv, vmat, H * Dv, (int64_t)B * S, R, dtype, impl, status, st))) return rc;
   return pjx_attn_fwd(q, kmat, vmat, o, lse, kv_lengths, bias, bias_batch_stride, bias_head_stride, B, Lq, S, H, H,
                       Dqk, Dv, dtype, causal, sm_scale, impl, status, stream);
 }
@@ -236,6 +268,8 @@ int pjx_attn_fwd_host(const void* q, const void* k, const void* v, void* o, floa
     return fail(PJX_ERR_WORKSPACE, "host forward staging: need %zu bytes, got %zu", need, staging ? staging_bytes : (size_t)0);
   if (B == 0 || Lq == 0) return PJX_OK;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
+  HostPipe* hp = nullptr;
+  if ((rc = host_pipe(&hp))) return rc;
   const size_t es = dtype_size(dtype);
   char* base = static_cast<char*>(staging);
   size_t off = 0;
@@ -246,23 +280,48 @@ int pjx_attn_fwd_host(const void* q, const void* k, const void* v, void* o, floa
                bb = (size_t)bias_batch * bias_heads * Lq * Lkv * sizeof(float);
   char *dq = take(qb), *dk = take(kb), *dv = take(vb), *dout = take(ob), *dl = take(lb), *dn = take(nb), *db = take(bb),
        *ds = take(sizeof(int32_t));
-  if ((rc = check_cuda(cudaMemcpyAsync(dq, q, qb, cudaMemcpyHostToDevice, st), "copy q to device"))) return rc;
-  if (kb && (rc = check_cuda(cudaMemcpyAsync(dk, k, kb, cudaMemcpyHostToDevice, st), "copy k to device"))) return rc;
-  if (vb && (rc = check_cuda(cudaMemcpyAsync(dv, v, vb, cudaMemcpyHostToDevice, st), "copy v to device"))) return rc;
-  if (kv_lengths && (rc = check_cuda(cudaMemcpyAsync(dn, kv_lengths, nb, cudaMemcpyHostToDevice, st), "copy kv_lengths to device"))) return rc;
-  if (bias && (rc = check_cuda(cudaMemcpyAsync(db, bias, bb, cudaMemcpyHostToDevice, st), "copy bias to device"))) return rc;
-  if ((rc = check_cuda(cudaMemsetAsync(ds, 0, sizeof(int32_t), st), "clear status"))) return rc;
   const int64_t bhs = bias ? (bias_heads == 1 ? 0 : (int64_t)Lq * Lkv) : 0;
   const int64_t bbs = bias ? (bias_batch == 1 ? 0 : (int64_t)bias_heads * Lq * Lkv) : 0;
-  rc = pjx_attn_fwd(dq, dk, dv, dout, lse ? reinterpret_cast<float*>(dl) : nullptr,
-                    kv_lengths ? reinterpret_cast<const int32_t*>(dn) : nullptr,
-                    bias ? reinterpret_cast<const float*>(db) : nullptr, bbs, bhs, B, Lq, Lkv, Hq, Hkv, D, Dv, dtype,
-                    causal, sm_scale, impl, reinterpret_cast<int32_t*>(ds), stream);
-  if (rc) return rc;
-  if ((rc = check_cuda(cudaMemcpyAsync(o, dout, ob, cudaMemcpyDeviceToHost, st), "copy o to host"))) return rc;
-  if (lse && (rc = check_cuda(cudaMemcpyAsync(lse, dl, lb, cudaMemcpyDeviceToHost, st), "copy lse to host"))) return rc;
+
+  // Three streams: copies in, kernels (the caller's stream), copies out. The batch is
+  // cut into chunks so that the upload of chunk c + 1 and the download of chunk c - 1
+  // overlap the kernel of chunk c (PCIe is full duplex).
+  const int nchunk = B < kHostChunks ? B : kHostChunks;
+  const int per = (B + nchunk - 1) / nchunk;
+  if ((rc = check_cuda(cudaEventRecord(hp->start, st), "record start"))) return rc;
+  if ((rc = check_cuda(cudaStreamWaitEvent(hp->in, hp->start, 0), "order upload stream"))) return rc;
+  if ((rc = check_cuda(cudaStreamWaitEvent(hp->out, hp->start, 0), "order download stream"))) return rc;
+  if (kv_lengths && (rc = check_cuda(cudaMemcpyAsync(dn, kv_lengths, nb, cudaMemcpyHostToDevice, hp->in), "copy kv_lengths to device"))) return rc;
+  if (bias && (rc = check_cuda(cudaMemcpyAsync(db, bias, bb, cudaMemcpyHostToDevice, hp->in), "copy bias to device"))) return rc;
+  if ((rc = check_cuda(cudaMemsetAsync(ds, 0, sizeof(int32_t), hp->in), "clear status"))) return rc;
+  const size_t q1 = (size_t)Lq * Hq * D * es, k1 = (size_t)Lkv * Hkv * D * es, v1 = (size_t)Lkv * Hkv * Dv * es,
+               o1 = (size_t)Lq * Hq * Dv * es, l1 = (size_t)Hq * Lq * sizeof(float);
+  int c = 0;
+  for (int b0 = 0; b0 < B; b0 += per, ++c) {
+    const int nb_c = (b0 + per <= B) ? per : B - b0;
+    const char* hq = static_cast<const char*>(q) + b0 * q1;
+    const char* hk = static_cast<const char*>(k) + b0 * k1;
+    const char* hv = static_cast<const char*>(v) + b0 * v1;
+    if ((rc = check_cuda(cudaMemcpyAsync(dq + b0 * q1, hq, nb_c * q1, cudaMemcpyHostToDevice, hp->in), "copy q to device"))) return rc;
+    if (k1 && (rc = check_cuda(cudaMemcpyAsync(dk + b0 * k1, hk, nb_c * k1, cudaMemcpyHostToDevice, hp->in), "copy k to device"))) return rc;
+    if (v1 && (rc = check_cuda(cudaMemcpyAsync(dv + b0 * v1, hv, nb_c * v1, cudaMemcpyHostToDevice, hp->in), "copy v to device"))) return rc;
+    if ((rc = check_cuda(cudaEventRecord(hp->up[c], hp->in), "record upload"))) return rc;
+    if ((rc = check_cuda(cudaStreamWaitEvent(st, hp->up[c], 0), "wait for upload"))) return rc;
+    rc = pjx_attn_fwd(dq + b0 * q1, dk + b0 * k1, dv + b0 * v1, dout + b0 * o1,
+                      lse ? reinterpret_cast<float*>(dl + b0 * l1) : nullptr,
+                      kv_lengths ? reinterpret_cast<const int32_t*>(dn) + b0 : nullptr,
+                      bias ? reinterpret_cast<const float*>(db) + (int64_t)b0 * bbs : nullptr, bbs, bhs, nb_c, Lq, Lkv, Hq,
+                      Hkv, D, Dv, dtype, causal, sm_scale, impl, reinterpret_cast<int32_t*>(ds), stream);
+    if (rc) return rc;
+    if ((rc = check_cuda(cudaEventRecord(hp->done[c], st), "record kernel"))) return rc;
+    if ((rc = check_cuda(cudaStreamWaitEvent(hp->out, hp->done[c], 0), "wait for kernel"))) return rc;
+    if ((rc = check_cuda(cudaMemcpyAsync(static_cast<char*>(o) + b0 * o1, dout + b0 * o1, nb_c * o1, cudaMemcpyDeviceToHost, hp->out), "copy o to host"))) return rc;
+    if (lse && (rc = check_cuda(cudaMemcpyAsync(reinterpret_cast<char*>(lse) + b0 * l1, dl + b0 * l1, nb_c * l1, cudaMemcpyDeviceToHost, hp->out), "copy lse to host"))) return rc;
+  }
   int32_t hs = 0;
-  if ((rc = check_cuda(cudaMemcpyAsync(&hs, ds, sizeof(int32_t), cudaMemcpyDeviceToHost, st), "copy status to host"))) return rc;
+  if ((rc = check_cuda(cudaMemcpyAsync(&hs, ds, sizeof(int32_t), cudaMemcpyDeviceToHost, hp->out), "copy status to host"))) return rc;
+  if ((rc = check_cuda(cudaEventRecord(hp->finish, hp->out), "record finish"))) return rc;
+  if ((rc = check_cuda(cudaStreamWaitEvent(st, hp->finish, 0), "join download stream"))) return rc;
   if ((rc = check_cuda(cudaStreamSynchronize(st), "synchronise after host forward"))) return rc;
   if (hs) return fail(hs, "the forward kernel reported status %d (%s)", hs, pjx_status_string(hs));
   return PJX_OK;
