@@ -10,9 +10,8 @@
 //   warp 1      MMA issuer (one lane): S_t = Q_t.K^T (both operands in shared
 //               memory), O_t += P_t.V (P_t read from tensor memory, V in shared
 //               memory, MN-major)
-//   warps 2-5   softmax of tile 0: one thread per query row, two passes over the
-//               row's scores in tensor memory (maximum, then exp2 / sum / pack) in
-//               32-column chunks with the next chunk's load in flight
+//   warps 2-5   softmax of tile 0: one thread per query row, the row's scores held
+//               in registers (all tensor-memory loads in flight at once)
 //   warps 6-9   softmax of tile 1
 //
 // Tensor memory (columns): S0 | S1 | O0 | O1, 128 lanes = 128 query rows.  P_t is
@@ -79,7 +78,7 @@ __device__ __forceinline__ uint32_t pack16(float lo, float hi) {
   }
 }
 
-template <int DQK, int DV, int BN, int KST, int VST, bool BF16>
+template <int DQK, int DV, int BN, int KST, int VST, bool BF16, bool HAS_BIAS>
 __global__ void __launch_bounds__(NTHREADS, 1)
 attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                       const __grid_constant__ CUtensorMap tm_v, const FwdParams p) {
@@ -241,10 +240,10 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
     const uint32_t o_addr = tmem + lane_sel + 2 * BN + t * DV;
     const float c1 = p.sm_scale * kLog2e;
     const float* bias_row = nullptr;
-    if (p.bias && row_ok) bias_row = p.bias + (int64_t)b * p.bias_bs + (int64_t)h * p.bias_hs + (int64_t)row * p.Lkv;
-    const bool bias_vec = p.bias && (p.Lkv % 4 == 0) && ((reinterpret_cast<uintptr_t>(p.bias) & 15) == 0) &&
+    if (HAS_BIAS && row_ok) bias_row = p.bias + (int64_t)b * p.bias_bs + (int64_t)h * p.bias_hs + (int64_t)row * p.Lkv;
+    const bool bias_vec = HAS_BIAS && (p.Lkv % 4 == 0) && ((reinterpret_cast<uintptr_t>(p.bias) & 15) == 0) &&
                           (p.bias_bs % 4 == 0) && (p.bias_hs % 4 == 0);
-    const float cs = p.bias ? 1.f : c1;
+    const float cs = HAS_BIAS ? 1.f : c1;
 
     float m_ref = -INFINITY, l = 0.f;
     bool ok = true;
@@ -256,95 +255,81 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
       constexpr int NCH = BN / 32;
       const int k0 = j * BN;
       const bool need_mask = (k0 + BN > kv_len) || (p.causal && k0 + BN - 1 > q0 + t * BM);
-      const bool rewrite = (p.bias != nullptr) || need_mask;  // uniform over the CTA tile
-      float buf[2][32];
 
-      // ---- pass 1: bias and mask (written back when present), row maximum ----
-      float m0 = -INFINITY, m1 = -INFINITY, m2 = -INFINITY, m3 = -INFINITY;  // independent chains
-      tmem_ld32f(s_addr, buf[0]);
+      // The whole row of scores in registers: all loads in flight at once.
+      float s[BN];
+#pragma unroll
+      for (int c = 0; c < NCH; ++c) tmem_ld32f(s_addr + c * 32, &s[c * 32]);
       tmem_wait_ld();
+
+      if constexpr (HAS_BIAS) {
 #pragma unroll
-      for (int c = 0; c < NCH; ++c) {
-        float* cur = buf[c & 1];
-        if (c + 1 < NCH) tmem_ld32f(s_addr + (c + 1) * 32, buf[(c + 1) & 1]);
-        if (rewrite) {
+        for (int c = 0; c < NCH; ++c) {
           const int kc = k0 + c * 32;
-          if (p.bias) {
-            if (bias_row && bias_vec && kc + 32 <= p.Lkv) {
-              const float4* bp = reinterpret_cast<const float4*>(bias_row + kc);
+          if (bias_row && bias_vec && kc + 32 <= p.Lkv) {
+            const float4* bp = reinterpret_cast<const float4*>(bias_row + kc);
 #pragma unroll
-              for (int i = 0; i < 8; ++i) {
-                const float4 bv = __ldg(bp + i);
-                cur[4 * i + 0] = fmaf(bv.x, kLog2e, cur[4 * i + 0] * c1);
-                cur[4 * i + 1] = fmaf(bv.y, kLog2e, cur[4 * i + 1] * c1);
-                cur[4 * i + 2] = fmaf(bv.z, kLog2e, cur[4 * i + 2] * c1);
-                cur[4 * i + 3] = fmaf(bv.w, kLog2e, cur[4 * i + 3] * c1);
-              }
-            } else {
-#pragma unroll
-              for (int i = 0; i < 32; ++i) {
-                const float bv = (bias_row && kc + i < p.Lkv) ? __ldg(bias_row + kc + i) : 0.f;
-                cur[i] = fmaf(bv, kLog2e, cur[i] * c1);
-              }
+            for (int i = 0; i < 8; ++i) {
+              const float4 bv = __ldg(bp + i);
+              s[c * 32 + 4 * i + 0] = fmaf(bv.x, kLog2e, s[c * 32 + 4 * i + 0] * c1);
+              s[c * 32 + 4 * i + 1] = fmaf(bv.y, kLog2e, s[c * 32 + 4 * i + 1] * c1);
+              s[c * 32 + 4 * i + 2] = fmaf(bv.z, kLog2e, s[c * 32 + 4 * i + 2] * c1);
+              s[c * 32 + 4 * i + 3] = fmaf(bv.w, kLog2e, s[c * 32 + 4 * i + 3] * c1);
             }
-          }
-          if (need_mask) {
+          } else {
 #pragma unroll
             for (int i = 0; i < 32; ++i) {
-              const int key = kc + i;
-              const bool keep = key < kv_len && (!p.causal || key <= row);
-              cur[i] = keep ? cur[i] : -INFINITY;
+              const float bv = (bias_row && kc + i < p.Lkv) ? __ldg(bias_row + kc + i) : 0.f;
+              s[c * 32 + i] = fmaf(bv, kLog2e, s[c * 32 + i] * c1);
             }
           }
-          tmem_st32f(s_addr + c * 32, cur);
         }
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          m0 = fmax3(m0, cur[8 * i + 0], cur[8 * i + 1]);
-          m1 = fmax3(m1, cur[8 * i + 2], cur[8 * i + 3]);
-          m2 = fmax3(m2, cur[8 * i + 4], cur[8 * i + 5]);
-          m3 = fmax3(m3, cur[8 * i + 6], cur[8 * i + 7]);
-        }
-        if (c + 1 < NCH) tmem_wait_ld();
       }
-      if (rewrite) tmem_wait_st();
-      float mx = fmaxf(fmaxf(m0, m1), fmaxf(m2, m3));
+      if (need_mask) {
+#pragma unroll
+        for (int i = 0; i < BN; ++i) {
+          const int key = k0 + i;
+          const bool keep = key < kv_len && (!p.causal || key <= row);
+          s[i] = keep ? s[i] : -INFINITY;
+        }
+      }
+
+      float mx;
+      {
+        float m0 = -INFINITY, m1 = -INFINITY, m2 = -INFINITY, m3 = -INFINITY;  // independent chains
+#pragma unroll
+        for (int i = 0; i < BN / 8; ++i) {
+          m0 = fmax3(m0, s[8 * i + 0], s[8 * i + 1]);
+          m1 = fmax3(m1, s[8 * i + 2], s[8 * i + 3]);
+          m2 = fmax3(m2, s[8 * i + 4], s[8 * i + 5]);
+          m3 = fmax3(m3, s[8 * i + 6], s[8 * i + 7]);
+        }
+        mx = fmaxf(fmaxf(m0, m1), fmaxf(m2, m3));
+      }
       mx *= cs;  // cs > 0
 
       // lazy running maximum: advance only when it grew by more than 8 (base 2)
       const bool need = (mx > m_ref + 8.f) || (m_ref == -INFINITY && mx > -INFINITY);
-      if (__any_sync(0xffffffffu, need)) {
+      const bool rescale = __any_sync(0xffffffffu, need);
+      float corr = 1.f;
+      if (rescale) {
         const float m_new = fmaxf(m_ref, mx);
-        const float corr = (m_new == -INFINITY) ? 1.f : exp2f(m_ref - m_new);
+        corr = (m_new == -INFINITY) ? 1.f : exp2f(m_ref - m_new);
         m_ref = m_new;
         l *= corr;
-        if (j > 0) {
-#pragma unroll
-          for (int c = 0; c < DV / 32; ++c) {
-            tmem_ld32f(o_addr + c * 32, buf[0]);
-            tmem_wait_ld();
-#pragma unroll
-            for (int i = 0; i < 32; ++i) buf[0][i] *= corr;
-            tmem_st32f(o_addr + c * 32, buf[0]);
-          }
-        }
       }
 
-      // ---- pass 2: p = exp2(x * cs - m), row sum, pack to 16 bits, store over S ----
+      // p = exp2(x * cs - m), row sum, pack to 16 bits, store over S
       const float neg_m = (m_ref == -INFINITY) ? 0.f : -m_ref;
       const float2 cs2 = make_float2(cs, cs), nm2 = make_float2(neg_m, neg_m);
       float2 sum0 = make_float2(0.f, 0.f), sum1 = make_float2(0.f, 0.f);
-      tmem_ld32f(s_addr, buf[0]);
-      tmem_wait_ld();
 #pragma unroll
       for (int c = 0; c < NCH; ++c) {
-        const float* cur = buf[c & 1];
-        if (c + 1 < NCH) tmem_ld32f(s_addr + (c + 1) * 32, buf[(c + 1) & 1]);
         uint32_t pk[16];
 #pragma unroll
         for (int i = 0; i < 16; i += 2) {
-          const float2 x0 = __ffma2_rn(make_float2(cur[2 * i], cur[2 * i + 1]), cs2, nm2);
-          const float2 x1 = __ffma2_rn(make_float2(cur[2 * i + 2], cur[2 * i + 3]), cs2, nm2);
+          const float2 x0 = __ffma2_rn(make_float2(s[c * 32 + 2 * i], s[c * 32 + 2 * i + 1]), cs2, nm2);
+          const float2 x1 = __ffma2_rn(make_float2(s[c * 32 + 2 * i + 2], s[c * 32 + 2 * i + 3]), cs2, nm2);
           const float2 p0 = make_float2(ex2_approx(x0.x), ex2_approx(x0.y));
           const float2 p1 = make_float2(ex2_approx(x1.x), ex2_approx(x1.y));
           sum0 = __fadd2_rn(sum0, p0);
@@ -352,10 +337,23 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
           pk[i] = pack16<BF16>(p0.x, p0.y);
           pk[i + 1] = pack16<BF16>(p1.x, p1.y);
         }
-        if (c + 1 < NCH) tmem_wait_ld();  // chunk c + 1 covers the columns written next: it has landed
         tmem_st16(s_addr + c * 16, pk);
       }
       const float lsum = (sum0.x + sum0.y) + (sum1.x + sum1.y);
+
+      // rescale O only now: the score registers are free again (the previous P.V of this
+      // tile completed before these scores became visible)
+      if (rescale && j > 0) {
+#pragma unroll
+        for (int c = 0; c < DV / 32; ++c) {
+          float o[32];
+          tmem_ld32f(o_addr + c * 32, o);
+          tmem_wait_ld();
+#pragma unroll
+          for (int i = 0; i < 32; ++i) o[i] *= corr;
+          tmem_st32f(o_addr + c * 32, o);
+        }
+      }
       l += lsum;
       tmem_wait_st();
       tc_fence_before();
@@ -455,7 +453,8 @@ int launch_cfg(const FwdParams& p, int dtype, cudaStream_t stream) {
   if ((rc = make_tmap_blhd(&tq, p.q, dtype, p.B, p.Lq, p.Hq, DQK, BM))) return rc;
   if ((rc = make_tmap_blhd(&tk, p.k, dtype, p.B, p.Lkv, p.Hkv, DQK, BN))) return rc;
   if ((rc = make_tmap_blhd(&tv, p.v, dtype, p.B, p.Lkv, p.Hkv, DV, BN))) return rc;
-  auto kern = attn_fwd_sm100_kernel<DQK, DV, BN, KST, VST, BF16>;
+  auto kern = p.bias ? attn_fwd_sm100_kernel<DQK, DV, BN, KST, VST, BF16, true>
+                     : attn_fwd_sm100_kernel<DQK, DV, BN, KST, VST, BF16, false>;
   if ((rc = check_cuda(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES),
                        "cudaFuncSetAttribute(sm100 fwd)")))
     return rc;
