@@ -38,6 +38,21 @@ using namespace sm100;
 constexpr int BM = 128;          // rows per query tile (= tensor-memory lanes)
 constexpr int NTHREADS = 320;    // 10 warps
 
+// Optional phase timeline of one CTA (debug builds only, -DPJX_TRACE): role r
+// (0/1 = softmax of tile 0/1, 2 = MMA issuer) stamps clock64() at point `pt` of KV
+// iteration j.
+#ifdef PJX_TRACE
+__device__ long long g_trace[3][64][8];
+#define PJX_TRACE_AT(r, j, pt)                                                                   \
+  do {                                                                                           \
+    if (blockIdx.x == gridDim.x / 2 && blockIdx.y == 1 && blockIdx.z == 0 && (j) < 64 &&         \
+        ((r) == 2 || (threadIdx.x & 127) == 64))                                                 \
+      g_trace[(r)][(j)][(pt)] = clock64();                                                       \
+  } while (0)
+#else
+#define PJX_TRACE_AT(r, j, pt) do {} while (0)
+#endif
+
 __device__ __forceinline__ float ex2_approx(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
@@ -76,6 +91,29 @@ __device__ __forceinline__ uint32_t pack16(float lo, float hi) {
     __half2 t = __floats2half2_rn(lo, hi);
     return *reinterpret_cast<uint32_t*>(&t);
   }
+}
+
+// p = exp2(x * cs - m) for one row of BN scores, running sums, pack to 16 bits and
+// store over the scores in tensor memory. All exponentials of the row form one
+// straight-line block (the stores come last) so that the scheduler can overlap the
+// latencies of independent elements.
+template <int BN, bool BF16>
+__device__ __forceinline__ void exp_pack_store(const float (&s)[BN], float2 cs2, float2 nm2, float2& sum0,
+                                               float2& sum1, uint32_t s_addr) {
+  uint32_t pk[BN / 2];
+#pragma unroll
+  for (int i = 0; i < BN / 2; i += 2) {
+    const float2 x0 = __ffma2_rn(make_float2(s[2 * i], s[2 * i + 1]), cs2, nm2);
+    const float2 x1 = __ffma2_rn(make_float2(s[2 * i + 2], s[2 * i + 3]), cs2, nm2);
+    const float2 p0 = make_float2(ex2_approx(x0.x), ex2_approx(x0.y));
+    const float2 p1 = make_float2(ex2_approx(x1.x), ex2_approx(x1.y));
+    sum0 = __fadd2_rn(sum0, p0);
+    sum1 = __fadd2_rn(sum1, p1);
+    pk[i] = pack16<BF16>(p0.x, p0.y);
+    pk[i + 1] = pack16<BF16>(p1.x, p1.y);
+  }
+#pragma unroll
+  for (int c = 0; c < BN / 64; ++c) tmem_st32(s_addr + c * 32, *reinterpret_cast<const uint32_t(*)[32]>(&pk[c * 32]));
 }
 
 template <int DQK, int DV, int BN, int KST, int VST, bool BF16, bool HAS_BIAS>
@@ -211,15 +249,19 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
 #pragma unroll
         for (int t = 0; t < 2; ++t) {
           if (j < n_t[t]) {
+            PJX_TRACE_AT(2, j, 4 * t + 0);
             ok = mbar_wait(BAR(P_FULL + t), j & 1, abort_flag);
             if (!ok) break;
             tc_fence_after();
+            PJX_TRACE_AT(2, j, 4 * t + 1);
             issue_pv(t, j);
+            PJX_TRACE_AT(2, j, 4 * t + 2);
             if (j == n_t[t] - 1) mma_commit(BAR(O_FULL + t));
           }
           if (j + 1 < n_t[t]) {
             issue_s(t, j + 1);
             mma_commit(BAR(S_FULL + t));
+            PJX_TRACE_AT(2, j, 4 * t + 3);
           }
         }
         if (!ok) break;
@@ -248,10 +290,12 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
     float m_ref = -INFINITY, l = 0.f;
     bool ok = true;
     for (int j = 0; j < my_n; ++j) {
+      PJX_TRACE_AT(t, j, 0);
       ok = mbar_wait(BAR(S_FULL + t), j & 1, abort_flag);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       tc_fence_after();
+      PJX_TRACE_AT(t, j, 1);
       constexpr int NCH = BN / 32;
       const int k0 = j * BN;
       const bool need_mask = (k0 + BN > kv_len) || (p.causal && k0 + BN - 1 > q0 + t * BM);
@@ -261,6 +305,7 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
 #pragma unroll
       for (int c = 0; c < NCH; ++c) tmem_ld32f(s_addr + c * 32, &s[c * 32]);
       tmem_wait_ld();
+      PJX_TRACE_AT(t, j, 2);
 
       if constexpr (HAS_BIAS) {
 #pragma unroll
@@ -296,15 +341,14 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
 
       float mx;
       {
-        float m0 = -INFINITY, m1 = -INFINITY, m2 = -INFINITY, m3 = -INFINITY;  // independent chains
+        float m[8];  // independent chains
 #pragma unroll
-        for (int i = 0; i < BN / 8; ++i) {
-          m0 = fmax3(m0, s[8 * i + 0], s[8 * i + 1]);
-          m1 = fmax3(m1, s[8 * i + 2], s[8 * i + 3]);
-          m2 = fmax3(m2, s[8 * i + 4], s[8 * i + 5]);
-          m3 = fmax3(m3, s[8 * i + 6], s[8 * i + 7]);
-        }
-        mx = fmaxf(fmaxf(m0, m1), fmaxf(m2, m3));
+        for (int i = 0; i < 8; ++i) m[i] = fmaxf(s[2 * i], s[2 * i + 1]);
+#pragma unroll
+        for (int i = 1; i < BN / 16; ++i)
+#pragma unroll
+          for (int u = 0; u < 8; ++u) m[u] = fmax3(m[u], s[16 * i + 2 * u], s[16 * i + 2 * u + 1]);
+        mx = fmaxf(fmaxf(fmaxf(m[0], m[1]), fmaxf(m[2], m[3])), fmaxf(fmaxf(m[4], m[5]), fmaxf(m[6], m[7])));
       }
       mx *= cs;  // cs > 0
 
@@ -323,22 +367,9 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
       const float neg_m = (m_ref == -INFINITY) ? 0.f : -m_ref;
       const float2 cs2 = make_float2(cs, cs), nm2 = make_float2(neg_m, neg_m);
       float2 sum0 = make_float2(0.f, 0.f), sum1 = make_float2(0.f, 0.f);
-#pragma unroll
-      for (int c = 0; c < NCH; ++c) {
-        uint32_t pk[16];
-#pragma unroll
-        for (int i = 0; i < 16; i += 2) {
-          const float2 x0 = __ffma2_rn(make_float2(s[c * 32 + 2 * i], s[c * 32 + 2 * i + 1]), cs2, nm2);
-          const float2 x1 = __ffma2_rn(make_float2(s[c * 32 + 2 * i + 2], s[c * 32 + 2 * i + 3]), cs2, nm2);
-          const float2 p0 = make_float2(ex2_approx(x0.x), ex2_approx(x0.y));
-          const float2 p1 = make_float2(ex2_approx(x1.x), ex2_approx(x1.y));
-          sum0 = __fadd2_rn(sum0, p0);
-          sum1 = __fadd2_rn(sum1, p1);
-          pk[i] = pack16<BF16>(p0.x, p0.y);
-          pk[i + 1] = pack16<BF16>(p1.x, p1.y);
-        }
-        tmem_st16(s_addr + c * 16, pk);
-      }
+      PJX_TRACE_AT(t, j, 3);
+      exp_pack_store<BN, BF16>(s, cs2, nm2, sum0, sum1, s_addr);
+      PJX_TRACE_AT(t, j, 4);
       const float lsum = (sum0.x + sum0.y) + (sum1.x + sum1.y);
 
       // rescale O only now: the score registers are free again (the previous P.V of this
@@ -358,6 +389,7 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
       tmem_wait_st();
       tc_fence_before();
       mbar_arrive(BAR(P_FULL + t));
+      PJX_TRACE_AT(t, j, 5);
     }
 
     if (ok && (q0 + t * BM) < p.Lq) {
@@ -488,6 +520,12 @@ bool fwd_sm100_supported(const FwdParams& p, int dtype, const char** why) {
   if (why) *why = w;
   return w == nullptr;
 }
+
+#ifdef PJX_TRACE
+extern "C" int pjx_debug_read_trace(long long* host_out) {
+  return (int)cudaMemcpyFromSymbol(host_out, g_trace, sizeof(long long) * 3 * 64 * 8);
+}
+#endif
 
 int launch_fwd_sm100(const FwdParams& p, int dtype, cudaStream_t stream) {
   const char* why = nullptr;
