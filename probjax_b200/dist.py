@@ -88,3 +88,95 @@ def decode_sharded(q, k_local, v_local, kv_lengths, *, page: int, sm_scale: floa
     if return_lse:
         return o, lse.reshape(B, Lq, Hq).permute(0, 2, 1).contiguous()
     return o
+
+
+class ShardedDecoder:
+    """Repeated decode steps over one sequence-sharded cache with every buffer
+    allocated once: the local split-KV decode writes its fp32 partial and LSE, two
+    ``all_gather_into_tensor`` calls land all ranks' partials in local memory, and the
+    combine kernel writes the result.  With ``use_graph`` the four launches of a
+    step are captured in one CUDA graph (a decode step is a few tens of
+    microseconds, so launch overhead matters).
+
+    ``kv_lengths`` are the global valid lengths; call :meth:`set_lengths` when they
+    change.  ``q`` is read from the tensor passed at construction (copy new queries
+    into ``decoder.q``).
+    """
+
+    def __init__(self, q, k_local, v_local, kv_lengths, *, page: int, sm_scale: float, group=None,
+                 use_graph: bool = False):
+        from . import _lib
+
+        self.group = group
+        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+        self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+        self.page, self.sm_scale = page, float(sm_scale)
+        self.q, self.k, self.v = q.contiguous(), k_local.contiguous(), v_local.contiguous()
+        dev = q.device
+        B, Lq, Hq, D = q.shape
+        self.cap, Hkv, Dv = self.k.shape[1], self.k.shape[2], self.v.shape[3]
+        self.shape = (B, Lq, Hq, Hkv, D, Dv)
+        n = B * Lq * Hq
+        self.o_loc = torch.empty((n, Dv), dtype=torch.float32, device=dev)
+        self.lse_loc = torch.empty((B, Hq, Lq), dtype=torch.float32, device=dev)
+        self.o_all = torch.empty((self.world, n, Dv), dtype=torch.float32, device=dev)
+        self.lse_all = torch.empty((self.world, n), dtype=torch.float32, device=dev)
+        self.out = torch.empty((B, Lq, Hq, Dv), dtype=q.dtype, device=dev)
+        self.lse = torch.empty((n,), dtype=torch.float32, device=dev)
+        self.lens = torch.empty((B,), dtype=torch.int32, device=dev)
+        self.set_lengths(kv_lengths)
+        L = _lib.lib()
+        need = L.pjx_attn_decode_workspace_bytes(B, Lq, Hq, Hkv, Dv, self.cap, 0)
+        self.ws = torch.empty(max(need, 256), dtype=torch.uint8, device=dev)
+        self._L, self._dt = L, _att._DTYPES[q.dtype]
+        self.graph = None
+        if use_graph:
+            self._capture()
+
+    def set_lengths(self, kv_lengths):
+        self.lens.copy_(local_lengths(torch.as_tensor(kv_lengths), self.rank, self.world, self.page))
+
+    def _step(self):
+        from . import _lib
+
+        B, Lq, Hq, Hkv, D, Dv = self.shape
+        dev = self.q.device
+        stream = torch.cuda.current_stream(dev).cuda_stream
+        rc = self._L.pjx_attn_decode_splitkv(
+            self.q.data_ptr(), self.k.data_ptr(), self.v.data_ptr(), self.lens.data_ptr(), self.o_loc.data_ptr(),
+            self.lse_loc.data_ptr(), B, Lq, Hq, Hkv, D, Dv, self.cap, self._dt, self.sm_scale, 0, 1,
+            self.ws.data_ptr(), self.ws.numel(), stream)
+        _lib.check(rc)
+        lse_rows = self.lse_loc.reshape(-1) if Lq == 1 else self.lse_loc.permute(0, 2, 1).reshape(-1)
+        if self.world > 1:
+            dist.all_gather_into_tensor(self.o_all.view(-1), self.o_loc.view(-1), group=self.group)
+            dist.all_gather_into_tensor(self.lse_all.view(-1), lse_rows.contiguous(), group=self.group)
+        else:
+            self.o_all[0].copy_(self.o_loc)
+            self.lse_all[0].copy_(lse_rows)
+        rc = self._L.pjx_attn_combine(self.o_all.data_ptr(), self.lse_all.data_ptr(), self.world, B * Lq * Hq, Dv,
+                                      self.out.data_ptr(), self.lse.data_ptr(), self._dt, stream)
+        _lib.check(rc)
+
+    def _capture(self):
+        side = torch.cuda.Stream(self.q.device)
+        side.wait_stream(torch.cuda.current_stream(self.q.device))
+        with torch.cuda.stream(side):
+            for _ in range(3):
+                self._step()
+        torch.cuda.current_stream(self.q.device).wait_stream(side)
+        torch.cuda.synchronize(self.q.device)
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            self._step()
+        self.graph = graph
+
+    def __call__(self, return_lse: bool = False):
+        if self.graph is not None:
+            self.graph.replay()
+        else:
+            self._step()
+        if return_lse:
+            B, Lq, Hq = self.shape[:3]
+            return self.out, self.lse.reshape(B, Lq, Hq).permute(0, 2, 1)
+        return self.out

@@ -143,3 +143,25 @@ def test_sharded_decode_emulated_on_one_gpu(world, page):
     # world size 1 through the public function (no process group)
     o1, lse1 = pjd.decode_sharded(q.to(d), k.to(d), v.to(d), lens, page=page, sm_scale=sc, return_lse=True)
     assert_close(o1, lse1, want, want_lse, torch.bfloat16, "decode_sharded world=1")
+
+
+@pytest.mark.parametrize("use_graph", [False, True])
+def test_sharded_decoder_object_single_rank(use_graph):
+    """The preallocated decoder (optionally replaying one CUDA graph per step)
+    gives the same answer as the oracle, also after the lengths change."""
+    d = dev()
+    b, cap, hq, hkv, dd = 3, 2000, 32, 8, 128
+    q, k, v = randn((b, 1, hq, dd), torch.bfloat16, 1), randn((b, cap, hkv, dd), torch.bfloat16, 2), randn((b, cap, hkv, dd), torch.bfloat16, 3)
+    lens = torch.tensor([2000, 900, 33], dtype=torch.int32)
+    sc = 1 / math.sqrt(dd)
+    dec = pjd.ShardedDecoder(q.to(d), k.to(d), v.to(d), lens, page=128, sm_scale=sc, use_graph=use_graph)
+    o, lse = dec(return_lse=True)
+    torch.cuda.synchronize()
+    want, want_lse = oracle_fwd(q, k, v, kv_lengths=lens, sm_scale=sc)
+    assert_close(o, lse, want, want_lse, torch.bfloat16, "ShardedDecoder")
+    lens2 = torch.tensor([5, 2000, 1000], dtype=torch.int32)
+    dec.set_lengths(lens2)
+    o, lse = dec(return_lse=True)
+    torch.cuda.synchronize()
+    want, want_lse = oracle_fwd(q, k, v, kv_lengths=lens2, sm_scale=sc)
+    assert_close(o, lse, want, want_lse, torch.bfloat16, "ShardedDecoder after set_lengths")
