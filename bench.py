@@ -398,8 +398,9 @@ def only_decode(args, dev, pk):
 
 def sharded_decode_bench(c4, dev, rank, world, steps, warmup, pk):
     """Decode at 32k context with the KV sequence block-cyclically sharded over
-    the ranks: local split-KV kernel, all-gather of (o, lse), combine.  Timed as
-    eager launches and as one captured CUDA graph per step."""
+    the ranks.  Timed three ways: the fused exchange (peer stores and flags inside
+    the kernels), NCCL all-gathers between the kernels, and the latter as one CUDA
+    graph per step."""
     from probjax_b200 import dist as pjd
 
     out = {}
@@ -410,9 +411,13 @@ def sharded_decode_bench(c4, dev, rank, world, steps, warmup, pk):
         q4 = c4["q"].to(dev)
         lens = c4["kv_lengths"]
         by = 4096.0 * float(lens.sum())
-        for mode in ("eager", "graph"):
+        for mode in ("fused", "nccl", "nccl_graph"):
             try:
-                dec = pjd.ShardedDecoder(q4, kl, vl, lens, page=page, sm_scale=c4["sm_scale"], use_graph=(mode == "graph"))
+                if mode == "fused":  # peer stores + flags inside the kernels, no library collective
+                    dec = pjd.FusedShardedDecoder(q4, kl, vl, lens, page=page, sm_scale=c4["sm_scale"])
+                else:
+                    dec = pjd.ShardedDecoder(q4, kl, vl, lens, page=page, sm_scale=c4["sm_scale"],
+                                             use_graph=(mode == "nccl_graph"))
                 ms = max_over_ranks(time_steps(dec, steps * 5, warmup, True), True) / (steps * 5)
                 ach = by / (ms * 1e-3) / 1e9
                 out[mode] = {"ms": ms, "value": ach, "unit": "GB/s aggregate",

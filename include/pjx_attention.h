@@ -131,6 +131,35 @@ int pjx_attn_decode_splitkv_static(const void* q, const void* k_cache, const voi
 size_t pjx_attn_decode_static_scratch_bytes(void);
 
 /*
+ * Decode step with the KV sequence sharded over `world` GPUs (one process per
+ * GPU).  Each rank passes its own shard (`k_local`, `v_local`, `local_lengths` =
+ * valid tokens this rank holds per sequence) and the replicated q; every rank
+ * gets the full result.  The exchange is fused into the kernels: after the local
+ * split-KV pass a kernel writes this rank's (o, lse) partial straight into every
+ * rank's exchange buffer with peer stores over NVLink and raises a flag; a second
+ * kernel waits (bounded, about two seconds, then PJX_ERR_DEVICE_TIMEOUT in
+ * `status`) for all ranks' flags and combines the partials out of local memory.
+ * It generalises the split combine of attention_splitkv.py:236-250 across GPUs;
+ * the reference itself never shards the sequence axis (probjax/nn/sharding.py:70, 97).
+ *
+ *   exchange_buffers  host array of `world` device pointers: entry r is rank r's
+ *                     exchange buffer (pjx_attn_decode_sharded_buffer_bytes bytes,
+ *                     zero-filled before the first step, mapped into this process,
+ *                     e.g. a torch symmetric-memory allocation).  All ranks pass the
+ *                     same list.
+ *   step              1, 2, 3, ... : every rank must make the same sequence of calls
+ *                     with the same step numbers.
+ *   o, lse            as pjx_attn_decode_splitkv (o in `dtype`).
+ */
+int pjx_attn_decode_sharded(const void* q, const void* k_local, const void* v_local,
+                            const int32_t* local_lengths, void* o, float* lse, int B, int Lq, int Hq,
+                            int Hkv, int D, int Dv, int capacity_local, int dtype, float sm_scale,
+                            int split_len, void* workspace, size_t workspace_bytes, int rank,
+                            int world, void* const* exchange_buffers, uint32_t step, int32_t* status,
+                            void* stream);
+size_t pjx_attn_decode_sharded_buffer_bytes(int B, int Lq, int Hq, int Dv, int world);
+
+/*
  * Exact combine of n_parts normalised partial results, each with its natural-
  * log LSE: m = max_p lse_p, w_p = exp(lse_p - m), o = sum w_p o_p / sum w_p,
  * lse = m + log sum w_p (attention_splitkv.py:236-250, in natural log).  Used

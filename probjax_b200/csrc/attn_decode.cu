@@ -368,6 +368,131 @@ __global__ void combine_parts_kernel(const float* __restrict__ o_parts, const fl
   if (lse && threadIdx.x == 0) lse[row] = denom > 0.f ? msafe + logf(denom) : INFINITY;
 }
 
+// ---------------------------------------------------------------------------
+// Sequence-sharded decode: the exchange of per-rank partials is done by the
+// kernels themselves with plain stores into the peers' memory over NVLink (no
+// library collective): the message is one (Dv + 1)-float record per (sequence,
+// query head), a few hundred KB, so its cost is latency, not bandwidth.
+//
+//   publish_partials_kernel   combines this rank's splits and writes the fp32
+//                             partial + natural-log LSE into slot [rank] of every
+//                             rank's exchange buffer; the last CTA to finish then
+//                             raises this rank's flag on every rank (release, system scope).
+//   gather_combine_kernel     waits (bounded) until all ranks' flags show this
+//                             step, then combines the partials out of local memory.
+//
+// Buffers are double buffered by step parity: a rank can run at most one step
+// ahead of a peer, because its next combine needs that peer's next flag.
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ void st_release_sys_u32(uint32_t* p, uint32_t v) {
+  asm volatile("st.release.sys.global.u32 [%0], %1;\n" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ uint32_t ld_acquire_sys_u32(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];\n" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+
+__global__ void publish_partials_kernel(const DecodeParams p) {
+  const int r = blockIdx.x, hk = blockIdx.y, b = blockIdx.z;
+  int len = p.capacity;
+  if (p.kv_lengths) len = max(0, min(len, p.kv_lengths[b]));
+  const int ns = (len + p.split_len - 1) / p.split_len;
+  const int64_t base = ((int64_t)b * p.Hkv + hk) * p.num_splits;
+  float m = -INFINITY;
+  for (int s = 0; s < ns; ++s) m = fmaxf(m, p.lse_part[(base + s) * p.rows + r]);
+  const float msafe = (m == -INFINITY) ? 0.f : m;
+  float denom = 0.f;
+  for (int s = 0; s < ns; ++s) denom += exp2f(p.lse_part[(base + s) * p.rows + r] - msafe);
+  const float inv = denom > 0.f ? 1.f / denom : 0.f;
+  const int G = p.Hq / p.Hkv;
+  const int g = r / p.Lq, t = r % p.Lq;
+  const int h = hk * G + g;
+  const int64_t N = (int64_t)p.B * p.Lq * p.Hq;
+  const int64_t n = ((int64_t)b * p.Lq + t) * p.Hq + h;
+  const size_t half = exchange_record_floats(p.ex_world, N, p.Dv);
+  const size_t o_off = (p.ex_step & 1) * half + ((size_t)p.ex_rank * N + n) * p.Dv;
+  const size_t l_off = (p.ex_step & 1) * half + (size_t)p.ex_world * N * p.Dv + (size_t)p.ex_rank * N + n;
+  for (int d = threadIdx.x; d < p.Dv; d += blockDim.x) {
+    float acc = 0.f;
+    for (int s = 0; s < ns; ++s) {
+      const float w = exp2f(p.lse_part[(base + s) * p.rows + r] - msafe);
+      acc += w * p.o_part[((base + s) * p.rows + r) * p.Dv + d];
+    }
+    acc *= inv;
+    for (int q = 0; q < p.ex_world; ++q) reinterpret_cast<float*>(p.ex_buf[q])[o_off + d] = acc;
+  }
+  if (threadIdx.x == 0) {
+    const float lse = denom > 0.f ? (msafe + log2f(denom)) * kLn2 : INFINITY;
+    for (int q = 0; q < p.ex_world; ++q) reinterpret_cast<float*>(p.ex_buf[q])[l_off] = lse;
+  }
+  __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    uint32_t* flags = reinterpret_cast<uint32_t*>(p.ex_buf[p.ex_rank] + 2 * half * sizeof(float));
+    uint32_t* counter = flags + kMaxExchangeRanks;
+    const uint32_t total = gridDim.x * gridDim.y * gridDim.z;
+    if (atomicAdd(counter, 1u) == total - 1) {
+      *counter = 0;
+      __threadfence_system();
+      for (int q = 0; q < p.ex_world; ++q)
+        st_release_sys_u32(reinterpret_cast<uint32_t*>(p.ex_buf[q] + 2 * half * sizeof(float)) + p.ex_rank, p.ex_step);
+    }
+  }
+}
+
+template <typename TO>
+__global__ void gather_combine_kernel(const DecodeParams p) {
+  const int64_t N = (int64_t)p.B * p.Lq * p.Hq;
+  const int64_t n = blockIdx.x;
+  const size_t half = exchange_record_floats(p.ex_world, N, p.Dv);
+  const unsigned char* mine = p.ex_buf[p.ex_rank];
+  __shared__ int timed_out;
+  if (threadIdx.x == 0) {
+    timed_out = 0;
+    const uint32_t* flags = reinterpret_cast<const uint32_t*>(mine + 2 * half * sizeof(float));
+    const long long t0 = clock64();
+    for (int q = 0; q < p.ex_world && !timed_out; ++q) {
+      while (static_cast<int32_t>(ld_acquire_sys_u32(flags + q) - p.ex_step) < 0) {
+        if (clock64() - t0 > 4000000000LL) {  // about two seconds: a peer never published
+          timed_out = 1;
+          if (p.status) atomicExch(p.status, (int)PJX_ERR_DEVICE_TIMEOUT);
+          break;
+        }
+      }
+    }
+  }
+  __syncthreads();
+  const float* o_parts = reinterpret_cast<const float*>(mine) + (p.ex_step & 1) * half;
+  const float* lse_parts = o_parts + (size_t)p.ex_world * N * p.Dv;
+  float m = -INFINITY;
+  for (int s = 0; s < p.ex_world; ++s) {
+    const float x = __ldcg(lse_parts + s * N + n);
+    if (x != INFINITY) m = fmaxf(m, x);
+  }
+  const float msafe = (m == -INFINITY) ? 0.f : m;
+  float denom = 0.f;
+  for (int s = 0; s < p.ex_world; ++s) {
+    const float x = __ldcg(lse_parts + s * N + n);
+    denom += (x == INFINITY) ? 0.f : expf(x - msafe);
+  }
+  const float inv = denom > 0.f ? 1.f / denom : 0.f;
+  TO* o = static_cast<TO*>(p.o);
+  for (int d = threadIdx.x; d < p.Dv; d += blockDim.x) {
+    float acc = 0.f;
+    for (int s = 0; s < p.ex_world; ++s) {
+      const float x = __ldcg(lse_parts + s * N + n);
+      const float w = (x == INFINITY) ? 0.f : expf(x - msafe);
+      acc += w * __ldcg(o_parts + (s * N + n) * p.Dv + d);
+    }
+    o[n * p.Dv + d] = Elem<TO>::from_f(acc * inv);
+  }
+  if (p.lse && threadIdx.x == 0) {
+    const int h = n % p.Hq, t = (n / p.Hq) % p.Lq, b = n / ((int64_t)p.Hq * p.Lq);
+    p.lse[((int64_t)b * p.Hq + h) * p.Lq + t] = denom > 0.f ? msafe + logf(denom) : INFINITY;
+  }
+}
+
 template <typename T, int HD>
 int launch_decode_t(const DecodeParams& p, cudaStream_t stream) {
   constexpr int smem = NSTAGE * 2 * BK * HD * 2;
@@ -383,6 +508,18 @@ int launch_decode_t(const DecodeParams& p, cudaStream_t stream) {
   if (rc) return rc;
   dim3 cgrid(p.rows, p.Hkv, p.B);
   const int cthr = p.Dv >= 128 ? 128 : 64;
+  if (p.ex_world > 0) {
+    publish_partials_kernel<<<cgrid, cthr, 0, stream>>>(p);
+    count_launch();
+    if ((rc = check_cuda(cudaGetLastError(), "decode publish launch"))) return rc;
+    const unsigned rows = (unsigned)((int64_t)p.B * p.Lq * p.Hq);
+    if (p.o_is_f32)
+      gather_combine_kernel<float><<<rows, cthr, 0, stream>>>(p);
+    else
+      gather_combine_kernel<T><<<rows, cthr, 0, stream>>>(p);
+    count_launch();
+    return check_cuda(cudaGetLastError(), "decode gather-combine launch");
+  }
   if (p.o_is_f32)
     combine_splits_kernel<float><<<cgrid, cthr, 0, stream>>>(p);
   else

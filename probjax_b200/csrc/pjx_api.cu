@@ -127,17 +127,22 @@ int pjx_attn_fwd(const void* q, const void* k, const void* v, void* o, float* ls
 }
 
 int pjx_attn_decode_default_split_len(int B, int Hkv, int capacity) {
+  // Measured on B200 (B=16, Hkv=8, caches of 4k..32k keys): CTAs that stream at least
+  // ~2048 keys amortise their pipeline fill and merge; more than ~3.5 waves of the 296
+  // CTA slots (2 per SM) buys nothing. Small problems get shorter splits so that one
+  // wave is still filled.
   if (B < 1 || Hkv < 1 || capacity < 1) return 64;
-  const long units = (long)B * Hkv;
-  const long target = 148L * 2 * 12;  // CTAs: a dozen waves of two CTAs per SM
-  long splits = (target + units - 1) / units;
-  if (splits < 1) splits = 1;
-  long len = (capacity + splits - 1) / splits;
-  len = (len + 63) / 64 * 64;
-  if (len < 256) len = 256;
+  const double total = (double)B * Hkv * capacity;
+  const double slots = 148.0 * 2;
+  const double len_fill = total / slots;
+  const double len_waves = total / (slots * 3.5);
+  double len = len_fill < 2048.0 ? len_fill : 2048.0;
+  if (len_waves > len) len = len_waves;
+  long l64 = ((long)len + 63) / 64 * 64;
+  if (l64 < 256) l64 = 256;
   const long cap64 = ((long)capacity + 63) / 64 * 64;
-  if (len > cap64) len = cap64;
-  return (int)len;
+  if (l64 > cap64) l64 = cap64;
+  return (int)l64;
 }
 
 static int decode_geometry(int B, int Hkv, int capacity, int split_len, int* out_len, int* out_splits) {
@@ -190,6 +195,49 @@ int pjx_attn_decode_splitkv(const void* q, const void* k_cache, const void* v_ca
   p.o_part = static_cast<float*>(workspace);
   p.lse_part = reinterpret_cast<float*>(static_cast<char*>(workspace) + align_up(parts * Dv * sizeof(float)));
   return launch_decode(p, dtype, st);
+}
+
+size_t pjx_attn_decode_sharded_buffer_bytes(int B, int Lq, int Hq, int Dv, int world) {
+  if (B < 1 || Lq < 1 || Hq < 1 || Dv < 1 || world < 1 || world > kMaxExchangeRanks) return 0;
+  return align_up(exchange_buffer_bytes(world, (int64_t)B * Lq * Hq, Dv));
+}
+
+int pjx_attn_decode_sharded(const void* q, const void* k_local, const void* v_local, const int32_t* local_lengths,
+                            void* o, float* lse, int B, int Lq, int Hq, int Hkv, int D, int Dv, int capacity_local,
+                            int dtype, float sm_scale, int split_len, void* workspace, size_t workspace_bytes,
+                            int rank, int world, void* const* exchange_buffers, uint32_t step, int32_t* status,
+                            void* stream) {
+  int rc = validate_common(q, k_local, v_local, o, B, Lq, capacity_local, Hq, Hkv, D, Dv, dtype);
+  if (rc) return rc;
+  if (world < 1 || world > kMaxExchangeRanks || rank < 0 || rank >= world)
+    return fail(PJX_ERR_BAD_ARG, "rank %d / world %d out of range (at most %d ranks)", rank, world, kMaxExchangeRanks);
+  if (!exchange_buffers) return fail(PJX_ERR_BAD_ARG, "exchange_buffers must hold one device pointer per rank");
+  for (int i = 0; i < world; ++i)
+    if (!exchange_buffers[i] || (reinterpret_cast<uintptr_t>(exchange_buffers[i]) & 15))
+      return fail(PJX_ERR_BAD_ARG, "exchange buffer of rank %d is null or not 16-byte aligned", i);
+  if (step == 0) return fail(PJX_ERR_BAD_ARG, "step counts from 1 and must grow by one per call");
+  if (B == 0 || Lq == 0) return PJX_OK;
+  DecodeParams p;
+  p.q = q; p.k = k_local; p.v = v_local; p.kv_lengths = local_lengths; p.o = o; p.lse = lse;
+  p.B = B; p.Lq = Lq; p.Hq = Hq; p.Hkv = Hkv; p.D = D; p.Dv = Dv; p.capacity = capacity_local;
+  p.rows = (Hq / Hkv) * Lq;
+  p.sm_scale = sm_scale;
+  p.o_is_f32 = 0;
+  const bool aligned =
+      ((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(k_local) | reinterpret_cast<uintptr_t>(v_local)) & 15) == 0;
+  if (!decode_fast_supported(p, dtype) || !aligned || capacity_local == 0)
+    return fail(PJX_ERR_UNSUPPORTED,
+                "the sharded decode takes bf16/fp16, D = Dv in {64,128}, (Hq/Hkv)*Lq <= 16, a non-empty local cache and 16-byte aligned q/k/v");
+  if ((rc = decode_geometry(B, Hkv, capacity_local, split_len, &p.split_len, &p.num_splits))) return rc;
+  const size_t need = pjx_attn_decode_workspace_bytes(B, Lq, Hq, Hkv, Dv, capacity_local, p.split_len);
+  if (!workspace || workspace_bytes < need)
+    return fail(PJX_ERR_WORKSPACE, "decode workspace: need %zu bytes, got %zu", need, workspace ? workspace_bytes : (size_t)0);
+  const size_t parts = (size_t)B * Hkv * p.num_splits * p.rows;
+  p.o_part = static_cast<float*>(workspace);
+  p.lse_part = reinterpret_cast<float*>(static_cast<char*>(workspace) + align_up(parts * Dv * sizeof(float)));
+  p.ex_world = world; p.ex_rank = rank; p.ex_step = step; p.status = status;
+  for (int i = 0; i < world; ++i) p.ex_buf[i] = static_cast<unsigned char*>(exchange_buffers[i]);
+  return launch_decode(p, dtype, static_cast<cudaStream_t>(stream));
 }
 
 int pjx_attn_combine(const float* o_parts, const float* lse_parts, int n_parts, int64_t n_rows, int Dv, void* o,

@@ -75,7 +75,22 @@ struct DecodeParams {
   int split_len, num_splits, rows;  // rows = (Hq / Hkv) * Lq
   float sm_scale;
   int o_is_f32;
+  // Sequence-sharded decode (ex_world > 0): instead of the local combine, every
+  // rank publishes its partial into all ranks' exchange buffers and then combines
+  // the partials of all ranks. Buffer layout (identical on every rank), N = B*Lq*Hq:
+  //   2 x { float o[world][N][Dv]; float lse[world][N]; }   (double buffered by step parity)
+  //   uint32 flags[16]; uint32 counter;
+  int ex_world = 0, ex_rank = 0;
+  uint32_t ex_step = 0;
+  unsigned char* ex_buf[16] = {};
+  int32_t* status = nullptr;
 };
+
+constexpr int kMaxExchangeRanks = 16;
+__host__ __device__ inline size_t exchange_record_floats(int world, int64_t n_rows, int Dv) { return (size_t)world * n_rows * (Dv + 1); }
+inline size_t exchange_buffer_bytes(int world, int64_t n_rows, int Dv) {
+  return 2 * exchange_record_floats(world, n_rows, Dv) * sizeof(float) + (kMaxExchangeRanks + 1) * sizeof(uint32_t);
+}
 
 // ---------------------------------------------------------------------------
 // Error plumbing (host)

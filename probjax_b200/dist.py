@@ -180,3 +180,80 @@ class ShardedDecoder:
             B, Lq, Hq = self.shape[:3]
             return self.out, self.lse.reshape(B, Lq, Hq).permute(0, 2, 1)
         return self.out
+
+
+class FusedShardedDecoder:
+    """Sequence-sharded decode whose exchange is done by the kernels themselves
+    (``pjx_attn_decode_sharded``): peer stores over NVLink into every rank's
+    exchange buffer plus a flag, no library collective on the data path.  The
+    exchange buffers are one torch symmetric-memory allocation per rank, mapped
+    into every process of ``group``.
+
+    One process per GPU; every rank must construct the decoder and call it the same
+    number of times.  ``decoder.q`` holds the queries of the step.
+    """
+
+    def __init__(self, q, k_local, v_local, kv_lengths, *, page: int, sm_scale: float, group=None):
+        import ctypes
+
+        from . import _lib
+
+        self.group = group
+        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+        self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+        self.page, self.sm_scale = page, float(sm_scale)
+        self.q, self.k, self.v = q.contiguous(), k_local.contiguous(), v_local.contiguous()
+        dev = q.device
+        B, Lq, Hq, D = q.shape
+        self.cap, Hkv, Dv = self.k.shape[1], self.k.shape[2], self.v.shape[3]
+        self.shape = (B, Lq, Hq, Hkv, D, Dv)
+        self.out = torch.empty((B, Lq, Hq, Dv), dtype=q.dtype, device=dev)
+        self.lse = torch.empty((B, Hq, Lq), dtype=torch.float32, device=dev)
+        self.lens = torch.empty((B,), dtype=torch.int32, device=dev)
+        self.set_lengths(kv_lengths)
+        L = _lib.lib()
+        self.ws = torch.empty(max(L.pjx_attn_decode_workspace_bytes(B, Lq, Hq, Hkv, Dv, self.cap, 0), 256),
+                              dtype=torch.uint8, device=dev)
+        nbytes = L.pjx_attn_decode_sharded_buffer_bytes(B, Lq, Hq, Dv, self.world)
+        if nbytes == 0:
+            raise ValueError(f"unsupported exchange geometry (world={self.world})")
+        if self.world > 1:
+            import torch.distributed._symmetric_memory as symm
+
+            self.xbuf = symm.empty(nbytes, dtype=torch.uint8, device=dev)
+            self.xbuf.zero_()
+            torch.cuda.synchronize(dev)
+            self._handle = symm.rendezvous(self.xbuf, group if group is not None else dist.group.WORLD)
+            ptrs = [int(x) for x in self._handle.buffer_ptrs]
+            dist.barrier(group)  # every rank has zeroed its flags before anyone publishes
+        else:
+            self.xbuf = torch.zeros(nbytes, dtype=torch.uint8, device=dev)
+            ptrs = [self.xbuf.data_ptr()]
+        self._ptrs = (ctypes.c_void_p * self.world)(*ptrs)
+        self._status = torch.zeros(1, dtype=torch.int32, device=dev)
+        self._L, self._dt, self.step = L, _att._DTYPES[q.dtype], 0
+
+    def set_lengths(self, kv_lengths):
+        self.lens.copy_(local_lengths(torch.as_tensor(kv_lengths), self.rank, self.world, self.page))
+
+    def __call__(self, return_lse: bool = False):
+        from . import _lib
+
+        B, Lq, Hq, Hkv, D, Dv = self.shape
+        self.step += 1
+        rc = self._L.pjx_attn_decode_sharded(
+            self.q.data_ptr(), self.k.data_ptr(), self.v.data_ptr(), self.lens.data_ptr(), self.out.data_ptr(),
+            self.lse.data_ptr(), B, Lq, Hq, Hkv, D, Dv, self.cap, self._dt, self.sm_scale, 0,
+            self.ws.data_ptr(), self.ws.numel(), self.rank, self.world, self._ptrs, self.step,
+            self._status.data_ptr(), torch.cuda.current_stream(self.q.device).cuda_stream)
+        _lib.check(rc)
+        return (self.out, self.lse) if return_lse else self.out
+
+    def check_status(self):
+        """Synchronise and raise if a wait on a peer's flag expired."""
+        from . import _lib
+
+        rc = self._L.pjx_read_status(self._status.data_ptr(), torch.cuda.current_stream(self.q.device).cuda_stream)
+        if rc:
+            self._status.zero_()
+        _lib.check(rc)
