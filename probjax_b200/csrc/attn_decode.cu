@@ -387,11 +387,6 @@ __global__ void combine_parts_kernel(const float* __restrict__ o_parts, const fl
 __device__ __forceinline__ void st_release_sys_u32(uint32_t* p, uint32_t v) {
   asm volatile("st.release.sys.global.u32 [%0], %1;\n" ::"l"(p), "r"(v) : "memory");
 }
-__device__ __forceinline__ uint32_t ld_acquire_sys_u32(const uint32_t* p) {
-  uint32_t v;
-  asm volatile("ld.acquire.sys.global.u32 %0, [%1];\n" : "=r"(v) : "l"(p) : "memory");
-  return v;
-}
 
 __global__ void publish_partials_kernel(const DecodeParams p) {
   const int r = blockIdx.x, hk = blockIdx.y, b = blockIdx.z;
@@ -426,9 +421,9 @@ __global__ void publish_partials_kernel(const DecodeParams p) {
     const float lse = denom > 0.f ? (msafe + log2f(denom)) * kLn2 : INFINITY;
     for (int q = 0; q < p.ex_world; ++q) reinterpret_cast<float*>(p.ex_buf[q])[l_off] = lse;
   }
-  __threadfence_system();
-  __syncthreads();
+  __syncthreads();  // the CTA's stores are ordered before thread 0's fence (cumulativity)
   if (threadIdx.x == 0) {
+    __threadfence_system();
     uint32_t* flags = reinterpret_cast<uint32_t*>(p.ex_buf[p.ex_rank] + 2 * half * sizeof(float));
     uint32_t* counter = flags + kMaxExchangeRanks;
     const uint32_t total = gridDim.x * gridDim.y * gridDim.z;
@@ -447,20 +442,16 @@ __global__ void gather_combine_kernel(const DecodeParams p) {
   const int64_t n = blockIdx.x;
   const size_t half = exchange_record_floats(p.ex_world, N, p.Dv);
   const unsigned char* mine = p.ex_buf[p.ex_rank];
-  __shared__ int timed_out;
-  if (threadIdx.x == 0) {
-    timed_out = 0;
-    const uint32_t* flags = reinterpret_cast<const uint32_t*>(mine + 2 * half * sizeof(float));
+  if (threadIdx.x < p.ex_world) {  // one thread per peer flag, polled in parallel
+    const volatile uint32_t* flag = reinterpret_cast<const volatile uint32_t*>(mine + 2 * half * sizeof(float)) + threadIdx.x;
     const long long t0 = clock64();
-    for (int q = 0; q < p.ex_world && !timed_out; ++q) {
-      while (static_cast<int32_t>(ld_acquire_sys_u32(flags + q) - p.ex_step) < 0) {
-        if (clock64() - t0 > 4000000000LL) {  // about two seconds: a peer never published
-          timed_out = 1;
-          if (p.status) atomicExch(p.status, (int)PJX_ERR_DEVICE_TIMEOUT);
-          break;
-        }
+    while (static_cast<int32_t>(*flag - p.ex_step) < 0) {
+      if (clock64() - t0 > 4000000000LL) {  // about two seconds: a peer never published
+        if (p.status) atomicExch(p.status, (int)PJX_ERR_DEVICE_TIMEOUT);
+        break;
       }
     }
+    __threadfence_system();  // acquire: the peers' records are visible after their flags
   }
   __syncthreads();
   const float* o_parts = reinterpret_cast<const float*>(mine) + (p.ex_step & 1) * half;
