@@ -64,7 +64,7 @@ __device__ __forceinline__ float fmax3(float a, float b, float c) {
   return y;
 }
 
-template <int DQK, int DV, int BN, int KST, int VST>
+template <int DQK, int DV, int BN, int KST, int VST, bool BIAS_STAGED = false>
 struct Cfg {
   static constexpr int Q_SUB = DQK / 64, V_SUB = DV / 64;
   static constexpr int Q_TILE_BYTES = Q_SUB * BM * 128;
@@ -73,8 +73,11 @@ struct Cfg {
   static constexpr int OFF_Q = 0;
   static constexpr int OFF_K = OFF_Q + 2 * Q_TILE_BYTES;
   static constexpr int OFF_V = OFF_K + KST * K_TILE_BYTES;
-  static constexpr int OFF_BAR = OFF_V + VST * V_TILE_BYTES;
-  static constexpr int N_BAR = 2 + 2 * KST + 2 * VST + 6;
+  // staged bias: per query tile one fp32 [128 rows x BN keys] tile as BN/32 boxes of 128 x 32 (128-byte rows)
+  static constexpr int BIAS_TILE_BYTES = BIAS_STAGED ? (BN / 32) * BM * 128 : 0;
+  static constexpr int OFF_BIAS = OFF_V + VST * V_TILE_BYTES;
+  static constexpr int OFF_BAR = OFF_BIAS + 2 * BIAS_TILE_BYTES;
+  static constexpr int N_BAR = 2 + 2 * KST + 2 * VST + 6 + 4;
   static constexpr int SMEM_BYTES = OFF_BAR + N_BAR * 8 + 16 + 1024;  // + alignment slack
   static constexpr int TMEM_USED = 2 * BN + 2 * DV;
   static constexpr int TMEM_COLS = TMEM_USED <= 128 ? 128 : (TMEM_USED <= 256 ? 256 : 512);
@@ -116,11 +119,16 @@ __device__ __forceinline__ void exp_pack_store(const float (&s)[BN], float2 cs2,
   for (int c = 0; c < BN / 64; ++c) tmem_st32(s_addr + c * 32, *reinterpret_cast<const uint32_t(*)[32]>(&pk[c * 32]));
 }
 
-template <int DQK, int DV, int BN, int KST, int VST, bool BF16, bool HAS_BIAS>
+// BIAS: 0 = no bias, 1 = bias read by each thread from global memory, 2 = bias tiles
+// staged in shared memory by TMA (one row per thread out of global memory costs one
+// L1 transaction per lane and instruction; the staged tile is read conflict-free).
+template <int DQK, int DV, int BN, int KST, int VST, bool BF16, int BIAS>
 __global__ void __launch_bounds__(NTHREADS, 1)
 attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
-                      const __grid_constant__ CUtensorMap tm_v, const FwdParams p) {
-  using C = Cfg<DQK, DV, BN, KST, VST>;
+                      const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_b,
+                      const FwdParams p) {
+  constexpr bool HAS_BIAS = BIAS != 0;
+  using C = Cfg<DQK, DV, BN, KST, VST, BIAS == 2>;
   extern __shared__ unsigned char smem_unaligned[];
   unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_unaligned) + 1023) & ~uintptr_t(1023));
   const uint32_t sbase = smem_u32(smem);
@@ -135,6 +143,8 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
   const int S_FULL = V_EMPTY + VST;       // [2]
   const int P_FULL = S_FULL + 2;          // [2]
   const int O_FULL = P_FULL + 2;          // [2]
+  const int B_FULL = O_FULL + 2;          // [2] staged bias tile landed
+  const int B_EMPTY = B_FULL + 2;         // [2] staged bias tile consumed (128 arrivals)
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + C::OFF_BAR + C::N_BAR * 8);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
@@ -160,7 +170,8 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
   const int n = max(n_t[0], n_t[1]);
 
   if (threadIdx.x == 0) {
-    for (int i = 0; i < C::N_BAR; ++i) mbar_init(BAR(i), (i >= P_FULL && i < P_FULL + 2) ? 128u : 1u);
+    for (int i = 0; i < C::N_BAR; ++i)
+      mbar_init(BAR(i), ((i >= P_FULL && i < P_FULL + 2) || i >= B_EMPTY) ? 128u : 1u);
     *abort_flag = 0;
     fence_barrier_init();
   }
@@ -179,6 +190,7 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
       prefetch_tmap(&tm_q);
       prefetch_tmap(&tm_k);
       prefetch_tmap(&tm_v);
+      if constexpr (BIAS == 2) prefetch_tmap(&tm_b);
 #pragma unroll
       for (int t = 0; t < 2; ++t) {
         if (n_t[t] == 0) continue;
@@ -202,6 +214,21 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
         for (int s = 0; s < C::V_SUB; ++s)
           tma_load_4d(sbase + C::OFF_V + vs * C::V_TILE_BYTES + s * BN * 128, &tm_v, BAR(V_FULL + vs), s * 64, hk,
                       j * BN, b);
+        if constexpr (BIAS == 2) {
+          bool okb = true;
+#pragma unroll
+          for (int t = 0; t < 2; ++t) {
+            if (j >= n_t[t]) continue;
+            okb = mbar_wait(BAR(B_EMPTY + t), (j & 1) ^ 1, abort_flag);
+            if (!okb) break;
+            mbar_arrive_expect_tx(BAR(B_FULL + t), C::BIAS_TILE_BYTES);
+#pragma unroll
+            for (int c = 0; c < BN / 32; ++c)
+              tma_load_4d(sbase + C::OFF_BIAS + t * C::BIAS_TILE_BYTES + c * BM * 128, &tm_b, BAR(B_FULL + t),
+                          j * BN + c * 32, q0 + t * BM, p.bias_hs ? h : 0, p.bias_bs ? b : 0);
+          }
+          if (!okb) break;
+        }
       }
     }
   } else if (warp == 1) {
@@ -282,8 +309,8 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
     const uint32_t o_addr = tmem + lane_sel + 2 * BN + t * DV;
     const float c1 = p.sm_scale * kLog2e;
     const float* bias_row = nullptr;
-    if (HAS_BIAS && row_ok) bias_row = p.bias + (int64_t)b * p.bias_bs + (int64_t)h * p.bias_hs + (int64_t)row * p.Lkv;
-    const bool bias_vec = HAS_BIAS && (p.Lkv % 4 == 0) && ((reinterpret_cast<uintptr_t>(p.bias) & 15) == 0) &&
+    if (BIAS == 1 && row_ok) bias_row = p.bias + (int64_t)b * p.bias_bs + (int64_t)h * p.bias_hs + (int64_t)row * p.Lkv;
+    const bool bias_vec = BIAS == 1 && (p.Lkv % 4 == 0) && ((reinterpret_cast<uintptr_t>(p.bias) & 15) == 0) &&
                           (p.bias_bs % 4 == 0) && (p.bias_hs % 4 == 0);
     const float cs = HAS_BIAS ? 1.f : c1;
 
@@ -307,7 +334,27 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
       tmem_wait_ld();
       PJX_TRACE_AT(t, j, 2);
 
-      if constexpr (HAS_BIAS) {
+      if constexpr (BIAS == 2) {
+        ok = mbar_wait(BAR(B_FULL + t), j & 1, abort_flag);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
+        const uint32_t brow = sbase + C::OFF_BIAS + t * C::BIAS_TILE_BYTES + r_in * 128;
+#pragma unroll
+        for (int c = 0; c < NCH; ++c) {
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            float4 bv;
+            asm volatile("ld.shared.v4.f32 {%0,%1,%2,%3}, [%4];\n"
+                         : "=f"(bv.x), "=f"(bv.y), "=f"(bv.z), "=f"(bv.w)
+                         : "r"(brow + c * BM * 128 + ((i ^ (r_in & 7)) << 4)));
+            s[c * 32 + 4 * i + 0] = fmaf(bv.x, kLog2e, s[c * 32 + 4 * i + 0] * c1);
+            s[c * 32 + 4 * i + 1] = fmaf(bv.y, kLog2e, s[c * 32 + 4 * i + 1] * c1);
+            s[c * 32 + 4 * i + 2] = fmaf(bv.z, kLog2e, s[c * 32 + 4 * i + 2] * c1);
+            s[c * 32 + 4 * i + 3] = fmaf(bv.w, kLog2e, s[c * 32 + 4 * i + 3] * c1);
+          }
+        }
+        mbar_arrive(BAR(B_EMPTY + t));
+      } else if constexpr (BIAS == 1) {
 #pragma unroll
         for (int c = 0; c < NCH; ++c) {
           const int kc = k0 + c * 32;
@@ -477,29 +524,66 @@ int make_tmap_blhd(CUtensorMap* m, const void* base, int dtype, int B, int L, in
 
 namespace {
 
-template <int DQK, int DV, int BN, int KST, int VST, bool BF16>
-int launch_cfg(const FwdParams& p, int dtype, cudaStream_t stream) {
-  using C = Cfg<DQK, DV, BN, KST, VST>;
-  CUtensorMap tq, tk, tv;
+// fp32 bias [Bb, Hb, Lq, Lkv] (strides in elements, 0 = broadcast): box = 32 keys x 128 rows.
+int make_tmap_bias(CUtensorMap* m, const FwdParams& p) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return fail(PJX_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
+  const cuuint64_t hb = p.bias_hs ? p.Hq : 1, bb = p.bias_bs ? p.B : 1;
+  const cuuint64_t plane = (cuuint64_t)p.Lq * p.Lkv;
+  cuuint64_t dims[4] = {(cuuint64_t)p.Lkv, (cuuint64_t)p.Lq, hb, bb};
+  cuuint64_t strides[3] = {(cuuint64_t)p.Lkv * 4, (p.bias_hs ? (cuuint64_t)p.bias_hs : plane) * 4,
+                           (p.bias_bs ? (cuuint64_t)p.bias_bs : plane * hb) * 4};
+  cuuint32_t box[4] = {32, (cuuint32_t)BM, 1, 1};
+  cuuint32_t estr[4] = {1, 1, 1, 1};
+  CUresult r = fn(m, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, const_cast<float*>(p.bias), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail(PJX_ERR_CUDA, "cuTensorMapEncodeTiled (bias) failed with CUresult %d", (int)r);
+  return PJX_OK;
+}
+
+bool bias_can_be_staged(const FwdParams& p) {
+  return p.bias && p.Lkv % 4 == 0 && (reinterpret_cast<uintptr_t>(p.bias) & 15) == 0 && p.bias_hs % 4 == 0 &&
+         p.bias_bs % 4 == 0;
+}
+
+template <int DQK, int DV, int BN, int KST, int VST, bool BF16, int BIAS>
+int launch_one(const FwdParams& p, int dtype, cudaStream_t stream) {
+  using C = Cfg<DQK, DV, BN, KST, VST, BIAS == 2>;
+  CUtensorMap tq, tk, tv, tb;
   int rc;
   if ((rc = make_tmap_blhd(&tq, p.q, dtype, p.B, p.Lq, p.Hq, DQK, BM))) return rc;
   if ((rc = make_tmap_blhd(&tk, p.k, dtype, p.B, p.Lkv, p.Hkv, DQK, BN))) return rc;
   if ((rc = make_tmap_blhd(&tv, p.v, dtype, p.B, p.Lkv, p.Hkv, DV, BN))) return rc;
-  auto kern = p.bias ? attn_fwd_sm100_kernel<DQK, DV, BN, KST, VST, BF16, true>
-                     : attn_fwd_sm100_kernel<DQK, DV, BN, KST, VST, BF16, false>;
+  if (BIAS == 2) {
+    if ((rc = make_tmap_bias(&tb, p))) return rc;
+  } else {
+    tb = tq;  // unused
+  }
+  auto kern = attn_fwd_sm100_kernel<DQK, DV, BN, KST, VST, BF16, BIAS>;
   if ((rc = check_cuda(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES),
                        "cudaFuncSetAttribute(sm100 fwd)")))
     return rc;
   dim3 grid((p.Lq + 2 * BM - 1) / (2 * BM), p.Hq, p.B);
-  kern<<<grid, NTHREADS, C::SMEM_BYTES, stream>>>(tq, tk, tv, p);
+  kern<<<grid, NTHREADS, C::SMEM_BYTES, stream>>>(tq, tk, tv, tb, p);
   count_launch();
   return check_cuda(cudaGetLastError(), "sm100 forward launch");
+}
+
+template <int DQK, int DV, int BN, int KST, int VST, bool BF16>
+int launch_cfg(const FwdParams& p, int dtype, cudaStream_t stream) {
+  if (!p.bias) return launch_one<DQK, DV, BN, KST, VST, BF16, 0>(p, dtype, stream);
+  return launch_one<DQK, DV, BN, KST, VST, BF16, 1>(p, dtype, stream);
 }
 
 template <bool BF16>
 int launch_by_shape(const FwdParams& p, int dtype, cudaStream_t stream) {
   if (p.D == 128 && p.Dv == 128) return launch_cfg<128, 128, 128, 2, 2, BF16>(p, dtype, stream);
-  if (p.D == 64 && p.Dv == 64) return launch_cfg<64, 64, 128, 3, 3, BF16>(p, dtype, stream);
+  if (p.D == 64 && p.Dv == 64) {
+    // with a bias that TMA can address, two K/V stages leave room for the staged bias tiles
+    if (bias_can_be_staged(p)) return launch_one<64, 64, 128, 2, 2, BF16, 2>(p, dtype, stream);
+    return launch_cfg<64, 64, 128, 3, 3, BF16>(p, dtype, stream);
+  }
   if (p.D == 192 && p.Dv == 128) return launch_cfg<192, 128, 128, 2, 1, BF16>(p, dtype, stream);
   return fail(PJX_ERR_UNSUPPORTED, "tcgen05 forward: head dims (%d, %d) not built", p.D, p.Dv);
 }
