@@ -11,7 +11,8 @@ import os
 from pathlib import Path
 
 _PKG = Path(__file__).resolve().parent
-LIB_PATH = _PKG / "libpjx_attention.so"
+# PJX_ATTENTION_LIB points at another build of the same library (e.g. a debug build).
+LIB_PATH = Path(os.environ.get("PJX_ATTENTION_LIB", _PKG / "libpjx_attention.so"))
 
 PJX_OK, PJX_ERR_BAD_ARG, PJX_ERR_UNSUPPORTED, PJX_ERR_WORKSPACE, PJX_ERR_DEVICE_TIMEOUT, PJX_ERR_CUDA = range(6)
 PJX_F32, PJX_BF16, PJX_F16 = 0, 1, 2
