@@ -14,6 +14,7 @@ from .attention import (  # noqa: F401
     dot_product_attention,
     flex_attention,
     mha,
+    mha_flash,
     mla,
     splitkv_forward,
     use_splitkv,

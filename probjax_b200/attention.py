@@ -352,6 +352,36 @@ def dot_product_attention(query, key, value, mask=None, bias=None, dropout_rng=N
                           sm_scale=sm_scale, enable_gqa=True, implementation=implementation)
 
 
+def mha_flash(query, key, value, mask=None, bias=None, dropout_rng=None, dropout_rate: float = 0.0,
+              broadcast_dropout: bool = True, deterministic: bool = True, dtype=None, precision=None, module=None,
+              sm_scale: Optional[float] = None, enable_gqa: bool = False, block_q=None, block_k=None, block_kv=None,
+              max_concurrent_steps: int = 2, use_schedule_barrier: bool = True, causal: bool = False,
+              compute_wgs_bwd=None, block_q_dkv=None, block_kv_dkv=None, block_q_dq=None, block_kv_dq=None,
+              save_residuals: bool = False, use_pipeline_emitter: bool = False):
+    """``mha_flash`` (probjax/nn/pallas_kernels/kernels/flash_attention3.py:344-372), the
+    reference's warp-specialised Hopper kernel, with the same restrictions so call
+    sites behave alike: ``mask`` is ``None`` / ``NoMask`` / ``KVLenMask``, causal
+    attention is asked for with ``causal=True``, no bias, no dropout.  With
+    ``save_residuals`` it also returns the natural-log LSE ``[B, Hq, Lq]`` (the
+    reference returns its base-2 residual; multiply by ``log2(e)`` to compare)."""
+    from .masks import CausalMask, KVLenMask
+
+    if mask is not None and type(mask) is not NoMask and type(mask) is not KVLenMask:
+        raise NotImplementedError(
+            "mha_flash supports mask=None, NoMask or KVLenMask (use causal=True for "
+            f"causal attention), got {type(mask).__name__}."
+        )
+    if bias is not None:
+        raise NotImplementedError("mha_flash does not support additive attention bias.")
+    if not deterministic and dropout_rate != 0.0:
+        raise NotImplementedError("mha_flash does not support dropout.")
+    full = mask
+    if causal:
+        full = CausalMask() if not isinstance(mask, KVLenMask) else (mask & CausalMask())
+    return flex_attention(query, key, value, mask=full, dtype=dtype, sm_scale=sm_scale, enable_gqa=enable_gqa,
+                          split_kv=False, return_lse=save_residuals)
+
+
 def splitkv_forward(q, k, v, *, sm_scale: float, num_splits: int | None = None, block_k: int | None = None,
                     num_warps: int = 4, num_stages: int = 2, interpret: bool = False, return_lse: bool = False,
                     kv_lengths=None):

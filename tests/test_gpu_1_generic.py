@@ -90,3 +90,27 @@ def test_empty_batch_and_single_row():
     out, lse = _run(q, k, v, sm_scale=1.0)
     assert torch.allclose(out.cpu(), v, atol=1e-6)  # one key: the output is its value
     assert torch.allclose(lse.cpu().reshape(()), (q * k).sum(), atol=1e-5)
+
+
+def test_seeded_random_shape_sweep():
+    """Thirty seeded random problems (ragged lengths, odd head widths, GQA ratios,
+    masks and biases in every combination) against the oracle."""
+    import numpy as np
+
+    rng = np.random.default_rng(2024)
+    for case in range(30):
+        hkv = int(rng.integers(1, 4))
+        hq = hkv * int(rng.integers(1, 4))
+        b, lq, lkv = int(rng.integers(1, 4)), int(rng.integers(1, 150)), int(rng.integers(1, 200))
+        d, dv = int(rng.integers(1, 80)), int(rng.integers(1, 80))
+        dtype = [torch.float32, torch.bfloat16, torch.float16][case % 3]
+        causal = bool(rng.integers(0, 2))
+        q, k, v = randn((b, lq, hq, d), dtype, 3 * case), randn((b, lkv, hkv, d), dtype, 3 * case + 1), randn((b, lkv, hkv, dv), dtype, 3 * case + 2)
+        kw = dict(causal=causal, sm_scale=float(rng.uniform(0.05, 0.5)))
+        if rng.integers(0, 2):
+            kw["kv_lengths"] = torch.from_numpy(rng.integers(0, lkv + 1, size=b).astype(np.int32))
+        if rng.integers(0, 2):
+            kw["bias"] = randn((1 if rng.integers(0, 2) else b, 1 if rng.integers(0, 2) else hq, lq, lkv), torch.float32, 1000 + case)
+        out, lse = _run(q, k, v, **kw)
+        want, want_lse = oracle_fwd(q, k, v, **kw)
+        assert_close(out, lse, want, want_lse, dtype, f"case {case}: {(b, lq, lkv, hq, hkv, d, dv)} {sorted(kw)}")

@@ -165,3 +165,41 @@ def test_sharded_decoder_object_single_rank(use_graph):
     torch.cuda.synchronize()
     want, want_lse = oracle_fwd(q, k, v, kv_lengths=lens2, sm_scale=sc)
     assert_close(o, lse, want, want_lse, torch.bfloat16, "ShardedDecoder after set_lengths")
+
+
+def test_missing_peer_is_reported_not_waited_for_forever():
+    """Failure detection of the fused sharded decode: rank 0 of a two-rank exchange
+    whose peer never publishes.  The wait on the peer's flag is bounded: the kernel
+    gives up after about two seconds, the status word reads DEVICE_TIMEOUT, and the
+    device stays usable."""
+    import ctypes
+
+    from probjax_b200 import _lib
+
+    L = _lib.lib()
+    d = dev()
+    b, cap, hq, hkv, dd = 1, 256, 8, 2, 128
+    q, k, v = randn((b, 1, hq, dd), torch.bfloat16, 1).to(d), randn((b, cap, hkv, dd), torch.bfloat16, 2).to(d), randn((b, cap, hkv, dd), torch.bfloat16, 3).to(d)
+    nbytes = L.pjx_attn_decode_sharded_buffer_bytes(b, 1, hq, dd, 2)
+    mine = torch.zeros(nbytes, dtype=torch.uint8, device=d)
+    absent_peer = torch.zeros(nbytes, dtype=torch.uint8, device=d)  # nobody ever raises rank 1's flag
+    ptrs = (ctypes.c_void_p * 2)(mine.data_ptr(), absent_peer.data_ptr())
+    ws = torch.empty(L.pjx_attn_decode_workspace_bytes(b, 1, hq, hkv, dd, cap, 0), dtype=torch.uint8, device=d)
+    o = torch.empty(b, 1, hq, dd, dtype=torch.bfloat16, device=d)
+    status = torch.zeros(1, dtype=torch.int32, device=d)
+    stream = torch.cuda.current_stream(d).cuda_stream
+    rc = L.pjx_attn_decode_sharded(q.data_ptr(), k.data_ptr(), v.data_ptr(), None, o.data_ptr(), None, b, 1, hq, hkv, dd, dd,
+                                   cap, _lib.PJX_BF16, 0.1, 0, ws.data_ptr(), ws.numel(), 0, 2, ptrs, 1, status.data_ptr(), stream)
+    assert rc == 0
+    assert L.pjx_read_status(status.data_ptr(), stream) == _lib.PJX_ERR_DEVICE_TIMEOUT
+    with pytest.raises(_lib.KernelTimeout):
+        _lib.check(_lib.PJX_ERR_DEVICE_TIMEOUT)
+    # the context is intact: the same call as a one-rank exchange completes and is correct
+    status.zero_()
+    mine.zero_()
+    one = (ctypes.c_void_p * 1)(mine.data_ptr())
+    rc = L.pjx_attn_decode_sharded(q.data_ptr(), k.data_ptr(), v.data_ptr(), None, o.data_ptr(), None, b, 1, hq, hkv, dd, dd,
+                                   cap, _lib.PJX_BF16, 0.1, 0, ws.data_ptr(), ws.numel(), 0, 1, one, 1, status.data_ptr(), stream)
+    assert rc == 0 and L.pjx_read_status(status.data_ptr(), stream) == 0
+    want, _ = oracle_fwd(q, k, v, sm_scale=0.1)
+    assert_close(o, None, want, None, torch.bfloat16, "after a timed-out exchange")

@@ -165,3 +165,27 @@ def test_host_buffer_call_matches_device_call():
     assert_close(out, lse, want, want_lse, torch.bfloat16, "host buffers")
     out2 = pj.attention_forward(q.numpy() if q.dtype != torch.bfloat16 else q, k, v, causal=True, sm_scale=inp["sm_scale"])
     assert torch.equal(out, out2)
+
+
+def test_seeded_random_shape_sweep():
+    """Twenty seeded random problems on the tcgen05 kernel: ragged lengths on both
+    axes, every head shape it is built for, GQA ratios, masks and biases."""
+    import numpy as np
+
+    rng = np.random.default_rng(7)
+    shapes = [(64, 64), (128, 128), (192, 128)]
+    for case in range(20):
+        d, dv = shapes[case % 3]
+        hkv = int(rng.integers(1, 3))
+        hq = hkv * int(rng.integers(1, 5))
+        b, lq, lkv = int(rng.integers(1, 3)), int(rng.integers(1, 700)), int(rng.integers(1, 900))
+        dtype = torch.bfloat16 if case % 2 else torch.float16
+        q, k, v = randn((b, lq, hq, d), dtype, 5 * case), randn((b, lkv, hkv, d), dtype, 5 * case + 1), randn((b, lkv, hkv, dv), dtype, 5 * case + 2)
+        kw = dict(causal=bool(rng.integers(0, 2)), sm_scale=1 / math.sqrt(d))
+        if rng.integers(0, 2):
+            kw["kv_lengths"] = torch.from_numpy(rng.integers(0, lkv + 1, size=b).astype(np.int32))
+        if rng.integers(0, 3) == 0:
+            kw["bias"] = randn((1, hq, lq, lkv), torch.float32, 2000 + case)
+        out, lse = _run(q, k, v, **kw)
+        want, want_lse = oracle_fwd(q, k, v, **kw)
+        assert_close(out, lse, want, want_lse, dtype, f"case {case}: {(b, lq, lkv, hq, hkv, d, dv)} {sorted(kw)}")

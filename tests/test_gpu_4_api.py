@@ -62,6 +62,21 @@ def test_mha_defaults_and_padding_mask():
         pj.mha(q.to(d), k.to(d), v.to(d), dropout_rate=0.1)
 
 
+def test_mha_flash_signature():
+    # flash_attention3.py:344-397: KVLenMask or none, causal flag, no bias / other masks
+    d = dev()
+    q, k = randn((2, 200, 4, 128), torch.bfloat16, 1), randn((2, 200, 2, 128), torch.bfloat16, 2)
+    lens = torch.tensor([200, 77], dtype=torch.int32)
+    got, lse = pj.mha_flash(q.to(d), k.to(d), k.to(d), mask=pj.KVLenMask(lens), causal=True, enable_gqa=True,
+                            save_residuals=True)
+    want, want_lse = oracle_fwd(q, k, k, causal=True, kv_lengths=lens, sm_scale=1 / math.sqrt(128))
+    assert_close(got, lse, want, want_lse, torch.bfloat16, "mha_flash")
+    with pytest.raises(NotImplementedError, match="causal=True"):
+        pj.mha_flash(q.to(d), k.to(d), k.to(d), mask=pj.CausalMask(), enable_gqa=True)
+    with pytest.raises(NotImplementedError, match="bias"):
+        pj.mha_flash(q.to(d), k.to(d), k.to(d), bias=pj.DenseBias(torch.zeros(1, 1, 200, 200)), enable_gqa=True)
+
+
 def test_dispatch_route():
     d = dev()
     assert pj.device_attention_defaults(d)["route"] == "b200"
