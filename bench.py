@@ -368,6 +368,7 @@ def main():
                 del q4, k4, v4
         except Exception as e:
             extras["decode"] = {"error": str(e)[:300]}
+        extras["decode_128k"] = long_context_decode_bench(dev, rank, world, xs, xw, pk, dist_on)
         out["extras"] = extras
 
     if rank == 0 and not args.skip_cpu and world == 1:
@@ -397,6 +398,41 @@ def only_decode(args, dev, pk):
                       args.steps, args.warmup, by4 / 1e9, "GB/s", pk["hbm_gbs"], "hbm", pk["source"])
     res["config"] = {"workload": f"GQA split-KV decode bf16 B{args.batch} Hq32 Hkv8 D128, 32768 keys each"}
     print(json.dumps(res), flush=True)
+
+
+def long_context_decode_bench(dev, rank, world, steps, warmup, pk, dist_on, context=131072):
+    """The decode geometry of configuration 4 at a 128k context (device-generated
+    N(0,1) cache, all keys valid): on one GPU the whole cache, on N GPUs the KV
+    sequence sharded with the fused exchange.  At 8 GPUs each rank still streams 16k
+    keys per sequence, so the fixed cost of the exchange is amortised."""
+    import probjax_b200 as pj
+    from probjax_b200 import dist as pjd
+
+    try:
+        B, Hq, Hkv, D, page = 16, 32, 8, 128, 256
+        local = context // world
+        g = torch.Generator(device=dev).manual_seed(1234 + rank)
+        q = torch.randn((B, 1, Hq, D), generator=torch.Generator(device=dev).manual_seed(99), device=dev).bfloat16()
+        k = torch.randn((B, local, Hkv, D), generator=g, device=dev, dtype=torch.float16).bfloat16()
+        v = torch.randn((B, local, Hkv, D), generator=g, device=dev, dtype=torch.float16).bfloat16()
+        lens = torch.full((B,), context, dtype=torch.int32)
+        sc = 1.0 / (D ** 0.5)
+        if dist_on:
+            fn = pjd.FusedShardedDecoder(q, k, v, lens, page=page, sm_scale=sc)
+        else:
+            ll = lens.to(dev)
+
+            def fn():
+                return pj.decode_forward(q, k, v, kv_lengths=ll, sm_scale=sc, return_lse=True)
+
+        ms = max_over_ranks(time_steps(fn, steps, warmup, dist_on), dist_on) / steps
+        by = 4096.0 * B * context
+        ach = by / (ms * 1e-3) / 1e9
+        return {"ms": ms, "value": ach, "unit": "GB/s aggregate", "context": context, "n_gpus": world,
+                "roofline": {"bound": "hbm", "achieved": ach / world, "peak": pk["hbm_gbs"], "unit": "GB/s per GPU",
+                             "frac": ach / world / pk["hbm_gbs"], "of": pk["source"]}}
+    except Exception as e:
+        return {"error": f"{type(e).__name__}: {e}"[:300]}
 
 
 def sharded_decode_bench(c4, dev, rank, world, steps, warmup, pk):
