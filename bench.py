@@ -329,6 +329,18 @@ def main():
         extras["prefill_causal"] = bench_extra(
             "causal", lambda: pj.attention_forward(q, k, v, causal=True, sm_scale=sc), xs, xw, fl_c / 1e12,
             "TFLOP/s", pk["bf16_tflops"], "tensor", pk["source"])
+        try:  # configuration 1: exact fp32 causal MHA, latency-bound (time and parity only)
+            c1 = oracle.make_config(1)
+            q1, k1, v1 = c1["q"].to(dev), c1["k"].to(dev), c1["v"].to(dev)
+            fl1 = prefill_flops(2, 4, 256, 256, 64, 64, True)
+            extras["fp32_causal_small"] = bench_extra(
+                "c1", lambda: pj.attention_forward(q1, k1, v1, causal=True, sm_scale=c1["sm_scale"]), xs * 5, xw,
+                fl1 / 1e12, "TFLOP/s", 72.0, "fp32 FMA (nominal, for scale only)", "nominal")
+            got = pj.attention_forward(q1, k1, v1, causal=True, sm_scale=c1["sm_scale"]).cpu()
+            want = oracle.xla_attention(c1["q"], c1["k"], c1["v"], causal=True, sm_scale=c1["sm_scale"])
+            extras["fp32_causal_small"]["max_abs_error_vs_oracle"] = float((got - want).abs().max())
+        except Exception as e:
+            extras["fp32_causal_small"] = {"error": str(e)[:300]}
         try:
             c3 = oracle.make_config(3)
             q3, k3, v3 = c3["q"].to(dev), c3["k"].to(dev), c3["v"].to(dev)
