@@ -75,6 +75,27 @@ int pjx_attn_fwd(const void* q, const void* k, const void* v, void* o, float* ls
                  int dtype, int causal, float sm_scale, int impl, int32_t* status, void* stream);
 
 /*
+ * Backward of pjx_attn_fwd: dq, dk, dv from q, k, v, o, d_o and the forward's
+ * natural-log lse, for the same masks and bias (the bias itself gets no gradient
+ * here).  First correct path: exact fp32 arithmetic on CUDA cores for every dtype.
+ *
+ * Replaces the `mha_bwd` primitive (probjax/nn/pallas_kernels/kernels/
+ * attention.py:2509-2534; kernels `_preprocess_backward_kernel` 853-906,
+ * `mha_backward_kernel_split_dkdv` 1189 and `_split_dq` 1364).  With GQA, dk and dv
+ * of a KV head are summed over its group's query heads.
+ *
+ *   d_o        [B, Lq, Hq, Dv] gradient of o, in `dtype`
+ *   dq, dk, dv like q, k, v, in `dtype`
+ *   workspace  pjx_attn_bwd_workspace_bytes(B, Lq, Hq) bytes
+ */
+int pjx_attn_bwd(const void* q, const void* k, const void* v, const void* o, const float* lse,
+                 const void* d_o, void* dq, void* dk, void* dv, const int32_t* kv_lengths,
+                 const float* bias, int64_t bias_batch_stride, int64_t bias_head_stride, int B, int Lq,
+                 int Lkv, int Hq, int Hkv, int D, int Dv, int dtype, int causal, float sm_scale,
+                 void* workspace, size_t workspace_bytes, void* stream);
+size_t pjx_attn_bwd_workspace_bytes(int B, int Lq, int Hq);
+
+/*
  * Split-KV decode forward over a KV cache with per-sequence valid lengths,
  * followed by the exact log-sum-exp combine of the per-split partials.
  *

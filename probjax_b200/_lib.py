@@ -27,6 +27,9 @@ SIGNATURES = {
     "pjx_last_error": (C.c_char_p, []),
     "pjx_attn_fwd": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64,
                           _i, _i, _i, _i, _i, _i, _i, _i, _i, _f, _i, _vp, _vp]),
+    "pjx_attn_bwd": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64,
+                          _i, _i, _i, _i, _i, _i, _i, _i, _i, _f, _vp, _sz, _vp]),
+    "pjx_attn_bwd_workspace_bytes": (_sz, [_i, _i, _i]),
     "pjx_attn_decode_splitkv": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _f,
                                      _i, _i, _vp, _sz, _vp]),
     "pjx_attn_decode_workspace_bytes": (_sz, [_i, _i, _i, _i, _i, _i, _i]),

@@ -162,6 +162,60 @@ def attention_forward(q, k, v, *, causal=False, kv_lengths=None, bias=None, sm_s
     return (o, lse) if return_lse else o
 
 
+def attention_backward(q, k, v, o, lse, d_o, *, causal=False, kv_lengths=None, bias=None, sm_scale=1.0):
+    """One ``pjx_attn_bwd`` call on CUDA tensors: ``(dq, dk, dv)`` for the forward that
+    produced ``o`` and ``lse`` from the same arguments."""
+    _require_gpu()
+    dev = q.device
+    q, k, v, o, d_o = (x.contiguous() for x in (q, k, v, o, d_o))
+    lse = lse.contiguous().float()
+    B, Lq, Hq, D = q.shape
+    Lkv, Hkv, Dv = k.shape[1], k.shape[2], v.shape[3]
+    dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
+    kvl = None if kv_lengths is None else _as_tensor(kv_lengths).to(device=dev, dtype=torch.int32).contiguous()
+    bs = hs = 0
+    bt = None
+    if bias is not None:
+        bt = _as_tensor(bias).to(device=dev, dtype=torch.float32).contiguous()
+        bs = 0 if bt.shape[0] == 1 else bt.stride(0)
+        hs = 0 if bt.shape[1] == 1 else bt.stride(1)
+    L = _lib.lib()
+    ws = _scratch_bytes(dev, "bwd", L.pjx_attn_bwd_workspace_bytes(B, Lq, Hq))
+    with torch.cuda.device(dev):
+        rc = L.pjx_attn_bwd(_ptr(q), _ptr(k), _ptr(v), _ptr(o), _ptr(lse), _ptr(d_o), _ptr(dq), _ptr(dk), _ptr(dv),
+                            _ptr(kvl), _ptr(bt), bs, hs, B, Lq, Lkv, Hq, Hkv, D, Dv, _DTYPES[q.dtype],
+                            int(bool(causal)), float(sm_scale), _ptr(ws), ws.numel(), _stream(dev))
+    _lib.check(rc)
+    return dq, dk, dv
+
+
+class _AttentionFunction(torch.autograd.Function):
+    """Differentiable forward: the regular forward kernels with the LSE kept as the
+    residual, and ``pjx_attn_bwd`` for the gradients of q, k and v (the reference wires
+    its kernels the same way, kernels/attention.py:3156-3270)."""
+
+    @staticmethod
+    def forward(ctx, q, k, v, causal, kv_lengths, bias, sm_scale, impl):
+        o, lse = attention_forward(q, k, v, causal=causal, kv_lengths=kv_lengths, bias=bias, sm_scale=sm_scale,
+                                   return_lse=True, impl=impl)
+        ctx.save_for_backward(q, k, v, o, lse)
+        ctx.args = (causal, kv_lengths, bias, sm_scale)
+        ctx.mark_non_differentiable(lse)
+        return o, lse
+
+    @staticmethod
+    def backward(ctx, d_o, _d_lse):
+        q, k, v, o, lse = ctx.saved_tensors
+        causal, kv_lengths, bias, sm_scale = ctx.args
+        dq, dk, dv = attention_backward(q, k, v, o, lse, d_o, causal=causal, kv_lengths=kv_lengths, bias=bias,
+                                        sm_scale=sm_scale)
+        return dq, dk, dv, None, None, None, None, None
+
+
+def _wants_grad(*tensors) -> bool:
+    return torch.is_grad_enabled() and any(isinstance(t, torch.Tensor) and t.requires_grad for t in tensors)
+
+
 def decode_forward(q, k_cache, v_cache, *, kv_lengths=None, sm_scale, split_len=0, return_lse=False,
                    partial_f32=False):
     """One ``pjx_attn_decode_splitkv`` call on CUDA tensors (split-KV kernel +
@@ -280,7 +334,17 @@ def mha(q, k, v, mask: AttentionMask | None = None, bias: AttentionBias | None =
     B, Lq = q.shape[0], q.shape[1]
     lm = lower_mask(mask, B, Lq, k.shape[1])
     bt = lower_bias(bias, B, q.shape[2], Lq, k.shape[1])
-    if use_splitkv(q, k, causal=lm.causal, bias=bt, q_limit=lm.q_limit, dropout_rate=dropout_rate, split_kv=split_kv):
+    if _wants_grad(q, k, v):
+        # differentiation always runs the regular kernels (attention_splitkv.py:253-272)
+        if bt is not None and bt.requires_grad:
+            raise NotImplementedError("gradients of a DenseBias are not implemented")
+        if not q.is_cuda:
+            raise NotImplementedError("differentiable attention takes CUDA tensors")
+        if lm.q_limit is not None:
+            raise NotImplementedError("gradients under a query-length mask are not implemented")
+        out, lse = _AttentionFunction.apply(q, k, v, lm.causal, lm.kv_lengths, bt, float(sm_scale), implementation)
+        res = (out, lse) if return_lse else out
+    elif use_splitkv(q, k, causal=lm.causal, bias=bt, q_limit=lm.q_limit, dropout_rate=dropout_rate, split_kv=split_kv):
         res = decode_forward(q, k, v, kv_lengths=lm.kv_lengths, sm_scale=sm_scale, return_lse=return_lse)
     else:
         res = attention_forward(q, k, v, causal=lm.causal, kv_lengths=lm.kv_lengths, bias=bt, sm_scale=sm_scale,

@@ -21,6 +21,7 @@ LIB = PKG / "libpjx_attention.so"
 SOURCES = [
     "pjx_api.cu",
     "attn_fwd_generic.cu",
+    "attn_bwd_generic.cu",
     "attn_fwd_sm100.cu",
     "attn_decode.cu",
     "gemm_sm100.cu",

@@ -1,0 +1,376 @@
+// Flash-attention backward on CUDA cores (exact fp32 arithmetic), any shape the
+// generic forward takes: dQ, dK, dV from Q, K, V, O, dO and the forward's natural-log
+// LSE, recomputing the probabilities tile by tile (nothing of size Lq x Lkv is stored).
+//
+// Math of the reference's backward kernels
+// (probjax/nn/pallas_kernels/kernels/attention.py:853-906 `_preprocess_backward_kernel`,
+// 1189-1483 the split dK/dV and dQ kernels):
+//   delta_i = sum_d dO_id O_id
+//   P_ij    = exp(s_ij - lse_i),  s_ij = sm_scale q_i.k_j + bias_ij, masked entries 0
+//   dV_j   += sum_i P_ij dO_i
+//   dS_ij   = P_ij (dO_i.v_j - delta_i)
+//   dQ_i   += sm_scale sum_j dS_ij k_j        dK_j += sm_scale sum_i dS_ij q_i
+// With GQA, dK and dV of a KV head are summed over the query heads of its group
+// (attention.py:2537-2542 restricts the GQA primitives the same way).
+//
+// Three launches without atomics: delta; dQ (one CTA per 32-query tile, walking the KV
+// tiles); dK/dV (one CTA per 32-key tile of a KV head, walking the group's query heads
+// and their query tiles).  Threads form a 16 x 16 grid with 2 x 2 micro-tiles of the
+// 32 x 32 score tile.
+#include "pjx_common.cuh"
+
+namespace pjx {
+namespace {
+
+constexpr int T = 32;     // tile edge (queries and keys)
+constexpr int NT = 256;   // threads per CTA
+
+struct BwdParams {
+  const void* q;
+  const void* k;
+  const void* v;
+  const void* o;
+  const void* d_o;
+  const float* lse;     // [B, Hq, Lq] natural log, +inf for rows without keys
+  float* delta;         // [B, Hq, Lq] workspace
+  void* dq;
+  void* dk;
+  void* dv;
+  const int32_t* kv_lengths;
+  const float* bias;
+  int64_t bias_bs, bias_hs;
+  int B, Lq, Lkv, Hq, Hkv, D, Dv;
+  int causal;
+  float sm_scale;
+};
+
+template <typename T_>
+__global__ void bwd_delta_kernel(const BwdParams p) {
+  const int64_t row = (int64_t)blockIdx.x * (blockDim.x / 32) + (threadIdx.x >> 5);  // (b, i, h) flattened
+  const int lane = threadIdx.x & 31;
+  const int64_t rows = (int64_t)p.B * p.Lq * p.Hq;
+  if (row >= rows) return;
+  const T_* o = static_cast<const T_*>(p.o) + row * p.Dv;
+  const T_* d_o = static_cast<const T_*>(p.d_o) + row * p.Dv;
+  float acc = 0.f;
+  for (int d = lane; d < p.Dv; d += 32) acc = fmaf(Elem<T_>::to_f(o[d]), Elem<T_>::to_f(d_o[d]), acc);
+#pragma unroll
+  for (int off = 16; off >= 1; off >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);
+  if (lane == 0) {
+    const int h = row % p.Hq;
+    const int64_t bi = row / p.Hq;
+    const int i = bi % p.Lq, b = bi / p.Lq;
+    p.delta[((int64_t)b * p.Hq + h) * p.Lq + i] = acc;
+  }
+}
+
+// Shared-memory views of one tile step.
+struct Tiles {
+  float *Qs, *dOs, *Ks, *Vs, *Ps, *dSs, *lse_s, *delta_s;
+  int Dp, Dvp;
+};
+
+__device__ __forceinline__ Tiles carve(float* smem, int D, int Dv) {
+  Tiles t;
+  t.Dp = D | 1;
+  t.Dvp = Dv | 1;
+  t.Qs = smem;
+  t.dOs = t.Qs + T * t.Dp;
+  t.Ks = t.dOs + T * t.Dvp;
+  t.Vs = t.Ks + T * t.Dp;
+  t.Ps = t.Vs + T * t.Dvp;
+  t.dSs = t.Ps + T * (T + 1);
+  t.lse_s = t.dSs + T * (T + 1);
+  t.delta_s = t.lse_s + T;
+  return t;
+}
+inline size_t bwd_smem_bytes(int D, int Dv) {
+  return sizeof(float) * ((size_t)2 * T * (D | 1) + (size_t)2 * T * (Dv | 1) + 2 * T * (T + 1) + 2 * T);
+}
+
+template <typename T_>
+__device__ __forceinline__ void load_rows(float* dst, int pitch, const T_* src, int64_t row_stride, int first, int limit,
+                                          int width) {
+  for (int idx = threadIdx.x; idx < T * width; idx += NT) {
+    const int r = idx / width, d = idx - r * width;
+    const int g = first + r;
+    dst[r * pitch + d] = g < limit ? Elem<T_>::to_f(src[(int64_t)g * row_stride + d]) : 0.f;
+  }
+}
+
+// P and dS of the 32 x 32 tile (queries q0.., keys k0..) of head h into shared memory.
+// Expects Qs, dOs, Ks, Vs, lse_s, delta_s loaded and a barrier passed.
+__device__ __forceinline__ void tile_p_ds(const BwdParams& p, const Tiles& t, int b, int h, int q0, int k0, int kv_len) {
+  const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
+  float s[2][2] = {}, dp[2][2] = {};
+  for (int d = 0; d < p.D; ++d) {
+    const float q0v = t.Qs[(ty * 2) * t.Dp + d], q1v = t.Qs[(ty * 2 + 1) * t.Dp + d];
+    const float k0v = t.Ks[tx * t.Dp + d], k1v = t.Ks[(tx + 16) * t.Dp + d];
+    s[0][0] = fmaf(q0v, k0v, s[0][0]);
+    s[0][1] = fmaf(q0v, k1v, s[0][1]);
+    s[1][0] = fmaf(q1v, k0v, s[1][0]);
+    s[1][1] = fmaf(q1v, k1v, s[1][1]);
+  }
+  for (int d = 0; d < p.Dv; ++d) {
+    const float a0 = t.dOs[(ty * 2) * t.Dvp + d], a1 = t.dOs[(ty * 2 + 1) * t.Dvp + d];
+    const float v0 = t.Vs[tx * t.Dvp + d], v1 = t.Vs[(tx + 16) * t.Dvp + d];
+    dp[0][0] = fmaf(a0, v0, dp[0][0]);
+    dp[0][1] = fmaf(a0, v1, dp[0][1]);
+    dp[1][0] = fmaf(a1, v0, dp[1][0]);
+    dp[1][1] = fmaf(a1, v1, dp[1][1]);
+  }
+  const float* bias = p.bias ? p.bias + (int64_t)b * p.bias_bs + (int64_t)h * p.bias_hs : nullptr;
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    const int r = ty * 2 + i, qi = q0 + r;
+    const float lse = t.lse_s[r], delta = t.delta_s[r];
+#pragma unroll
+    for (int c = 0; c < 2; ++c) {
+      const int col = tx + 16 * c, kj = k0 + col;
+      float x = s[i][c] * p.sm_scale;
+      if (bias && qi < p.Lq && kj < p.Lkv) x += bias[(int64_t)qi * p.Lkv + kj];
+      const bool keep = qi < p.Lq && kj < kv_len && (!p.causal || kj <= qi) && lse != INFINITY;
+      const float pr = keep ? exp2f((x - lse) * kLog2e) : 0.f;
+      t.Ps[r * (T + 1) + col] = pr;
+      t.dSs[r * (T + 1) + col] = pr * (dp[i][c] - delta);
+    }
+  }
+}
+
+template <typename T_, int NC>  // NC: per-thread columns = ceil(D / 16)
+__global__ void __launch_bounds__(NT) bwd_dq_kernel(const BwdParams p) {
+  extern __shared__ float smem[];
+  const Tiles t = carve(smem, p.D, p.Dv);
+  const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
+  const int q0 = blockIdx.x * T, h = blockIdx.y, b = blockIdx.z;
+  const int hk = h / (p.Hq / p.Hkv);
+  int kv_len = p.Lkv;
+  if (p.kv_lengths) kv_len = max(0, min(kv_len, p.kv_lengths[b]));
+  const int kv_end = p.causal ? min(kv_len, q0 + T) : kv_len;
+  const int64_t qstride = (int64_t)p.Hq * p.D, ostride = (int64_t)p.Hq * p.Dv;
+  const int64_t kstride = (int64_t)p.Hkv * p.D, vstride = (int64_t)p.Hkv * p.Dv;
+  const T_* q = static_cast<const T_*>(p.q) + ((int64_t)b * p.Lq * p.Hq + h) * p.D;
+  const T_* d_o = static_cast<const T_*>(p.d_o) + ((int64_t)b * p.Lq * p.Hq + h) * p.Dv;
+  const T_* k = static_cast<const T_*>(p.k) + ((int64_t)b * p.Lkv * p.Hkv + hk) * p.D;
+  const T_* v = static_cast<const T_*>(p.v) + ((int64_t)b * p.Lkv * p.Hkv + hk) * p.Dv;
+  load_rows<T_>(t.Qs, t.Dp, q, qstride, q0, p.Lq, p.D);
+  load_rows<T_>(t.dOs, t.Dvp, d_o, ostride, q0, p.Lq, p.Dv);
+  if (threadIdx.x < T) {
+    const int qi = q0 + threadIdx.x;
+    const int64_t at = ((int64_t)b * p.Hq + h) * p.Lq + qi;
+    t.lse_s[threadIdx.x] = qi < p.Lq ? p.lse[at] : INFINITY;
+    t.delta_s[threadIdx.x] = qi < p.Lq ? p.delta[at] : 0.f;
+  }
+  float acc[2][NC];
+#pragma unroll
+  for (int i = 0; i < 2; ++i)
+#pragma unroll
+    for (int c = 0; c < NC; ++c) acc[i][c] = 0.f;
+  for (int k0 = 0; k0 < kv_end; k0 += T) {
+    __syncthreads();
+    load_rows<T_>(t.Ks, t.Dp, k, kstride, k0, kv_len, p.D);
+    load_rows<T_>(t.Vs, t.Dvp, v, vstride, k0, kv_len, p.Dv);
+    __syncthreads();
+    tile_p_ds(p, t, b, h, q0, k0, kv_len);
+    __syncthreads();
+    for (int c = 0; c < T; ++c) {
+      const float d0 = t.dSs[(ty * 2) * (T + 1) + c], d1 = t.dSs[(ty * 2 + 1) * (T + 1) + c];
+#pragma unroll
+      for (int cc = 0; cc < NC; ++cc) {
+        const int d = tx + 16 * cc;
+        const float kv = d < p.D ? t.Ks[c * t.Dp + d] : 0.f;
+        acc[0][cc] = fmaf(d0, kv, acc[0][cc]);
+        acc[1][cc] = fmaf(d1, kv, acc[1][cc]);
+      }
+    }
+  }
+  T_* dq = static_cast<T_*>(p.dq) + ((int64_t)b * p.Lq * p.Hq + h) * p.D;
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    const int qi = q0 + ty * 2 + i;
+    if (qi >= p.Lq) continue;
+#pragma unroll
+    for (int cc = 0; cc < NC; ++cc) {
+      const int d = tx + 16 * cc;
+      if (d < p.D) dq[(int64_t)qi * qstride + d] = Elem<T_>::from_f(acc[i][cc] * p.sm_scale);
+    }
+  }
+}
+
+template <typename T_, int NCK, int NCV>  // per-thread columns of dK (D) and dV (Dv)
+__global__ void __launch_bounds__(NT) bwd_dkdv_kernel(const BwdParams p) {
+  extern __shared__ float smem[];
+  const Tiles t = carve(smem, p.D, p.Dv);
+  const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
+  const int k0 = blockIdx.x * T, hk = blockIdx.y, b = blockIdx.z;
+  const int G = p.Hq / p.Hkv;
+  int kv_len = p.Lkv;
+  if (p.kv_lengths) kv_len = max(0, min(kv_len, p.kv_lengths[b]));
+  const int64_t qstride = (int64_t)p.Hq * p.D, ostride = (int64_t)p.Hq * p.Dv;
+  const int64_t kstride = (int64_t)p.Hkv * p.D, vstride = (int64_t)p.Hkv * p.Dv;
+  const T_* k = static_cast<const T_*>(p.k) + ((int64_t)b * p.Lkv * p.Hkv + hk) * p.D;
+  const T_* v = static_cast<const T_*>(p.v) + ((int64_t)b * p.Lkv * p.Hkv + hk) * p.Dv;
+  float acck[2][NCK], accv[2][NCV];
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+#pragma unroll
+    for (int c = 0; c < NCK; ++c) acck[i][c] = 0.f;
+#pragma unroll
+    for (int c = 0; c < NCV; ++c) accv[i][c] = 0.f;
+  }
+  if (k0 < kv_len) {  // keys past the valid length get zero gradients
+    load_rows<T_>(t.Ks, t.Dp, k, kstride, k0, kv_len, p.D);
+    load_rows<T_>(t.Vs, t.Dvp, v, vstride, k0, kv_len, p.Dv);
+    const int q_first = p.causal ? (k0 / T) * T : 0;  // queries before the tile's first key never see it
+    for (int g = 0; g < G; ++g) {
+      const int h = hk * G + g;
+      const T_* q = static_cast<const T_*>(p.q) + ((int64_t)b * p.Lq * p.Hq + h) * p.D;
+      const T_* d_o = static_cast<const T_*>(p.d_o) + ((int64_t)b * p.Lq * p.Hq + h) * p.Dv;
+      for (int q0 = q_first; q0 < p.Lq; q0 += T) {
+        __syncthreads();
+        load_rows<T_>(t.Qs, t.Dp, q, qstride, q0, p.Lq, p.D);
+        load_rows<T_>(t.dOs, t.Dvp, d_o, ostride, q0, p.Lq, p.Dv);
+        if (threadIdx.x < T) {
+          const int qi = q0 + threadIdx.x;
+          const int64_t at = ((int64_t)b * p.Hq + h) * p.Lq + qi;
+          t.lse_s[threadIdx.x] = qi < p.Lq ? p.lse[at] : INFINITY;
+          t.delta_s[threadIdx.x] = qi < p.Lq ? p.delta[at] : 0.f;
+        }
+        __syncthreads();
+        tile_p_ds(p, t, b, h, q0, k0, kv_len);
+        __syncthreads();
+        for (int r = 0; r < T; ++r) {
+          const float p0 = t.Ps[r * (T + 1) + ty * 2], p1 = t.Ps[r * (T + 1) + ty * 2 + 1];
+          const float s0 = t.dSs[r * (T + 1) + ty * 2], s1 = t.dSs[r * (T + 1) + ty * 2 + 1];
+#pragma unroll
+          for (int cc = 0; cc < NCV; ++cc) {
+            const int d = tx + 16 * cc;
+            const float g_o = d < p.Dv ? t.dOs[r * t.Dvp + d] : 0.f;
+            accv[0][cc] = fmaf(p0, g_o, accv[0][cc]);
+            accv[1][cc] = fmaf(p1, g_o, accv[1][cc]);
+          }
+#pragma unroll
+          for (int cc = 0; cc < NCK; ++cc) {
+            const int d = tx + 16 * cc;
+            const float qv = d < p.D ? t.Qs[r * t.Dp + d] : 0.f;
+            acck[0][cc] = fmaf(s0, qv, acck[0][cc]);
+            acck[1][cc] = fmaf(s1, qv, acck[1][cc]);
+          }
+        }
+      }
+    }
+  }
+  T_* dk = static_cast<T_*>(p.dk) + ((int64_t)b * p.Lkv * p.Hkv + hk) * p.D;
+  T_* dv = static_cast<T_*>(p.dv) + ((int64_t)b * p.Lkv * p.Hkv + hk) * p.Dv;
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    const int kj = k0 + ty * 2 + i;
+    if (kj >= p.Lkv) continue;
+#pragma unroll
+    for (int cc = 0; cc < NCK; ++cc) {
+      const int d = tx + 16 * cc;
+      if (d < p.D) dk[(int64_t)kj * kstride + d] = Elem<T_>::from_f(acck[i][cc] * p.sm_scale);
+    }
+#pragma unroll
+    for (int cc = 0; cc < NCV; ++cc) {
+      const int d = tx + 16 * cc;
+      if (d < p.Dv) dv[(int64_t)kj * vstride + d] = Elem<T_>::from_f(accv[i][cc]);
+    }
+  }
+}
+
+template <typename K>
+int set_smem(K kern, size_t bytes, const char* what) {
+  if (bytes <= 48 * 1024) return PJX_OK;
+  return check_cuda(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes), what);
+}
+
+template <typename T_, int NCK, int NCV>
+int launch_widths(const BwdParams& p, cudaStream_t stream) {
+  const size_t smem = bwd_smem_bytes(p.D, p.Dv);
+  int rc;
+  const int64_t rows = (int64_t)p.B * p.Lq * p.Hq;
+  bwd_delta_kernel<T_><<<(unsigned)((rows + 7) / 8), 256, 0, stream>>>(p);
+  count_launch();
+  if ((rc = check_cuda(cudaGetLastError(), "backward delta launch"))) return rc;
+  auto kq = bwd_dq_kernel<T_, NCK>;
+  if ((rc = set_smem(kq, smem, "cudaFuncSetAttribute(backward dq)"))) return rc;
+  kq<<<dim3((p.Lq + T - 1) / T, p.Hq, p.B), NT, smem, stream>>>(p);
+  count_launch();
+  if ((rc = check_cuda(cudaGetLastError(), "backward dq launch"))) return rc;
+  if (p.Lkv == 0) return PJX_OK;
+  auto kk = bwd_dkdv_kernel<T_, NCK, NCV>;
+  if ((rc = set_smem(kk, smem, "cudaFuncSetAttribute(backward dk/dv)"))) return rc;
+  kk<<<dim3((p.Lkv + T - 1) / T, p.Hkv, p.B), NT, smem, stream>>>(p);
+  count_launch();
+  return check_cuda(cudaGetLastError(), "backward dk/dv launch");
+}
+
+template <typename T_>
+int launch_dtype(const BwdParams& p, cudaStream_t stream) {
+  const int nk = p.D <= 64 ? 4 : (p.D <= 128 ? 8 : 16);
+  const int nv = p.Dv <= 64 ? 4 : (p.Dv <= 128 ? 8 : 16);
+  switch (nk * 100 + nv) {
+    case 404: return launch_widths<T_, 4, 4>(p, stream);
+    case 408: return launch_widths<T_, 4, 8>(p, stream);
+    case 416: return launch_widths<T_, 4, 16>(p, stream);
+    case 804: return launch_widths<T_, 8, 4>(p, stream);
+    case 808: return launch_widths<T_, 8, 8>(p, stream);
+    case 816: return launch_widths<T_, 8, 16>(p, stream);
+    case 1604: return launch_widths<T_, 16, 4>(p, stream);
+    case 1608: return launch_widths<T_, 16, 8>(p, stream);
+    default: return launch_widths<T_, 16, 16>(p, stream);
+  }
+}
+
+}  // namespace
+}  // namespace pjx
+
+using namespace pjx;
+
+extern "C" {
+
+size_t pjx_attn_bwd_workspace_bytes(int B, int Lq, int Hq) {
+  if (B < 0 || Lq < 0 || Hq < 1) return 0;
+  return ((size_t)B * Hq * Lq * sizeof(float) + 255) / 256 * 256;
+}
+
+int pjx_attn_bwd(const void* q, const void* k, const void* v, const void* o, const float* lse, const void* d_o,
+                 void* dq, void* dk, void* dv, const int32_t* kv_lengths, const float* bias,
+                 int64_t bias_batch_stride, int64_t bias_head_stride, int B, int Lq, int Lkv, int Hq, int Hkv, int D,
+                 int Dv, int dtype, int causal, float sm_scale, void* workspace, size_t workspace_bytes, void* stream) {
+  if (dtype != PJX_F32 && dtype != PJX_BF16 && dtype != PJX_F16)
+    return fail(PJX_ERR_BAD_ARG, "dtype must be float32, bfloat16 or float16 (got code %d)", dtype);
+  if (B < 0 || Lq < 0 || Lkv < 0 || Hq < 1 || Hkv < 1 || D < 1 || Dv < 1)
+    return fail(PJX_ERR_BAD_ARG, "negative or zero dimension");
+  if (Hq % Hkv != 0) return fail(PJX_ERR_BAD_ARG, "query heads %d must be a multiple of kv heads %d", Hq, Hkv);
+  if (D > 256 || Dv > 256) return fail(PJX_ERR_UNSUPPORTED, "head dims above 256 are not supported (D=%d, Dv=%d)", D, Dv);
+  if (B == 0 || Hq == 0) return PJX_OK;
+  if (Lq > 0 && (!q || !o || !d_o || !lse || !dq)) return fail(PJX_ERR_BAD_ARG, "backward: null query-side buffer");
+  if (Lkv > 0 && (!k || !v || !dk || !dv)) return fail(PJX_ERR_BAD_ARG, "backward: null key-side buffer");
+  const size_t need = pjx_attn_bwd_workspace_bytes(B, Lq, Hq);
+  if (Lq > 0 && (!workspace || workspace_bytes < need))
+    return fail(PJX_ERR_WORKSPACE, "backward workspace: need %zu bytes, got %zu", need, workspace ? workspace_bytes : (size_t)0);
+  if (Lq == 0 && Lkv == 0) return PJX_OK;
+  BwdParams p;
+  p.q = q; p.k = k; p.v = v; p.o = o; p.d_o = d_o; p.lse = lse;
+  p.delta = static_cast<float*>(workspace);
+  p.dq = dq; p.dk = dk; p.dv = dv;
+  p.kv_lengths = kv_lengths; p.bias = bias; p.bias_bs = bias_batch_stride; p.bias_hs = bias_head_stride;
+  p.B = B; p.Lq = Lq; p.Lkv = Lkv; p.Hq = Hq; p.Hkv = Hkv; p.D = D; p.Dv = Dv;
+  p.causal = causal != 0;
+  p.sm_scale = sm_scale;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (Lq == 0) {  // no queries: the key-side gradients are zero
+    int rc = check_cuda(cudaMemsetAsync(dk, 0, (size_t)B * Lkv * Hkv * D * dtype_size(dtype), st), "clear dk");
+    if (rc) return rc;
+    return check_cuda(cudaMemsetAsync(dv, 0, (size_t)B * Lkv * Hkv * Dv * dtype_size(dtype), st), "clear dv");
+  }
+  switch (dtype) {
+    case PJX_F32: return launch_dtype<float>(p, st);
+    case PJX_BF16: return launch_dtype<__nv_bfloat16>(p, st);
+    default: return launch_dtype<__half>(p, st);
+  }
+}
+
+}  // extern "C"
