@@ -45,12 +45,20 @@ constexpr int NTHREADS = 320;    // 10 warps
 __device__ long long g_trace[3][64][8];
 #define PJX_TRACE_AT(r, j, pt)                                                                   \
   do {                                                                                           \
-    if (blockIdx.x == gridDim.x / 2 && blockIdx.y == 1 && blockIdx.z == 0 && (j) < 64 &&         \
+    if (blockIdx.x == gridDim.x / 2 && (j) < 64 &&                                               \
         ((r) == 2 || (threadIdx.x & 127) == 64))                                                 \
       g_trace[(r)][(j)][(pt)] = clock64();                                                       \
   } while (0)
+// Per-CTA timeline: [0] SM id, then clock64 at [1] entry, [2] first S MMA issued, [3] last MMA
+// issued, [4] epilogue of tile 1 begins, [5] exit; [6] globaltimer at entry.
+__device__ long long g_cta[8192][8];
+#define PJX_CTA_AT(slot)                                                        \
+  do {                                                                          \
+    if (blockIdx.x < 8192) g_cta[blockIdx.x][(slot)] = clock64();               \
+  } while (0)
 #else
 #define PJX_TRACE_AT(r, j, pt) do {} while (0)
+#define PJX_CTA_AT(slot) do {} while (0)
 #endif
 
 __device__ __forceinline__ float ex2_approx(float x) {
@@ -126,7 +134,7 @@ template <int DQK, int DV, int BN, int KST, int VST, bool BF16, int BIAS>
 __global__ void __launch_bounds__(NTHREADS, 1)
 attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                       const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_b,
-                      const FwdParams p) {
+                      const FwdParams p, const int order_w) {
   constexpr bool HAS_BIAS = BIAS != 0;
   using C = Cfg<DQK, DV, BN, KST, VST, BIAS == 2>;
   extern __shared__ unsigned char smem_unaligned[];
@@ -149,8 +157,19 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int qt = gridDim.x - 1 - blockIdx.x;  // longest causal tiles first
-  const int h = blockIdx.y, b = blockIdx.z;
+  // Work order: the (batch, head) pairs are taken in blocks of `order_w`; inside a block the
+  // query-tile index is the slow, descending axis. Under a causal mask the long CTAs of a
+  // block therefore start first and its short ones fill the gaps (a block of 16 pairs gets
+  // within a few per cent of a global longest-first order), while the CTAs in flight still
+  // share few K/V heads, which keeps their tiles in the near L2 partition.
+  const int n_bh = p.Hq * p.B;
+  const int n_qt = (p.Lq + 2 * BM - 1) / (2 * BM);
+  const int blk = blockIdx.x / (order_w * n_qt);
+  const int rem = blockIdx.x - blk * (order_w * n_qt);
+  const int wc = min(order_w, n_bh - blk * order_w);
+  const int qt = n_qt - 1 - rem / wc;
+  const int bh = blk * order_w + rem % wc;
+  const int h = bh % p.Hq, b = bh / p.Hq;
   const int hk = h / (p.Hq / p.Hkv);
   const int q0 = qt * 2 * BM;
 
@@ -170,6 +189,17 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
   const int n = max(n_t[0], n_t[1]);
 
   if (threadIdx.x == 0) {
+#ifdef PJX_TRACE
+    if (blockIdx.x < 8192) {
+      unsigned smid;
+      unsigned long long gt;
+      asm volatile("mov.u32 %0, %%smid;" : "=r"(smid));
+      asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(gt));
+      g_cta[blockIdx.x][0] = smid;
+      g_cta[blockIdx.x][6] = (long long)gt;
+    }
+#endif
+    PJX_CTA_AT(1);
     for (int i = 0; i < C::N_BAR; ++i)
       mbar_init(BAR(i), ((i >= P_FULL && i < P_FULL + 2) || i >= B_EMPTY) ? 128u : 1u);
     *abort_flag = 0;
@@ -267,6 +297,7 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
             mma_commit(BAR(S_FULL + t));
           }
         mma_commit(BAR(K_EMPTY + 0));
+        PJX_CTA_AT(2);
       }
       for (int j = 0; ok && j < n; ++j) {
         const bool have_next = j + 1 < n;
@@ -295,6 +326,7 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
         mma_commit(BAR(V_EMPTY + j % VST));
         if (have_next) mma_commit(BAR(K_EMPTY + (j + 1) % KST));
       }
+      PJX_CTA_AT(3);
     }
   } else {
     // ------------------------------------------------------------ softmax warps
@@ -447,6 +479,7 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
       }
       if (ok) {
         tc_fence_after();
+        if (threadIdx.x == 320 - 128) PJX_CTA_AT(4);
         unsigned char* orow = static_cast<unsigned char*>(p.o) + ((((int64_t)b * p.Lq + row) * p.Hq + h) * DV) * 2;
 #pragma unroll
         for (int c = 0; c < DV / 32; ++c) {
@@ -482,6 +515,7 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
   if (warp == 0) {
     __syncwarp();
     tmem_dealloc(tmem, C::TMEM_COLS);
+    if (lane == 0) PJX_CTA_AT(5);
     if (lane == 0 && *abort_flag && p.status) atomicExch(p.status, (int)PJX_ERR_DEVICE_TIMEOUT);
   }
 }
@@ -564,8 +598,9 @@ int launch_one(const FwdParams& p, int dtype, cudaStream_t stream) {
   if ((rc = check_cuda(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES),
                        "cudaFuncSetAttribute(sm100 fwd)")))
     return rc;
-  dim3 grid((p.Lq + 2 * BM - 1) / (2 * BM), p.Hq, p.B);
-  kern<<<grid, NTHREADS, C::SMEM_BYTES, stream>>>(tq, tk, tv, tb, p);
+  dim3 grid((unsigned)(((p.Lq + 2 * BM - 1) / (2 * BM)) * (int64_t)p.Hq * p.B));
+  const int order_w = p.causal ? 16 : 1;
+  kern<<<grid, NTHREADS, C::SMEM_BYTES, stream>>>(tq, tk, tv, tb, p, order_w);
   count_launch();
   return check_cuda(cudaGetLastError(), "sm100 forward launch");
 }
@@ -597,7 +632,7 @@ bool fwd_sm100_supported(const FwdParams& p, int dtype, const char** why) {
     w = "head dims must be (64,64), (128,128) or (192,128)";
   else if (!(p.sm_scale > 0.f)) w = "sm_scale must be positive";
   else if (p.B < 1 || p.Lq < 1 || p.Lkv < 1) w = "empty problem";
-  else if (p.Hq > 65535 || p.B > 65535) w = "grid too large";
+  else if (((p.Lq + 2 * BM - 1) / (2 * BM)) * (int64_t)p.Hq * p.B > 0x7fffffffLL) w = "grid too large";
   else if ((reinterpret_cast<uintptr_t>(p.q) | reinterpret_cast<uintptr_t>(p.k) | reinterpret_cast<uintptr_t>(p.v) |
             reinterpret_cast<uintptr_t>(p.o)) & 15)
     w = "q, k, v, o must be 16-byte aligned";
@@ -608,6 +643,9 @@ bool fwd_sm100_supported(const FwdParams& p, int dtype, const char** why) {
 #ifdef PJX_TRACE
 extern "C" int pjx_debug_read_trace(long long* host_out) {
   return (int)cudaMemcpyFromSymbol(host_out, g_trace, sizeof(long long) * 3 * 64 * 8);
+}
+extern "C" int pjx_debug_read_cta(long long* host_out) {
+  return (int)cudaMemcpyFromSymbol(host_out, g_cta, sizeof(long long) * 8192 * 8);
 }
 #endif
 
