@@ -75,6 +75,27 @@ int pjx_attn_fwd(const void* q, const void* k, const void* v, void* o, float* ls
                  int dtype, int causal, float sm_scale, int impl, int32_t* status, void* stream);
 
 /*
+ * pjx_attn_fwd with a band of visible keys instead of the causal flag: key j is
+ * valid for query i iff i + band_lo <= j <= i + band_hi.  PJX_BAND_NO_LOWER /
+ * PJX_BAND_NO_UPPER leave a side open; (NO_LOWER, 0) is the causal mask.
+ *
+ * Covers the index masks the reference's default dispatch sends to its fused kernel
+ * (probjax/nn/layers/attention.py:1167-1202): `LocalWindowMask(l, r)` -> (-l, r),
+ * `CausalLocalWindowMask(l)` -> (-l, 0), `CausalFromBottomRightMask` -> (NO_LOWER,
+ * Lkv - Lq) (probjax/nn/pallas_kernels/attention_mask_bias.py:651-782), and their AND
+ * with each other and with key lengths.  KV tiles wholly outside the band of a query
+ * tile are skipped, as the reference's block-sparse iteration does
+ * (`fast_blockmask_local_window`).
+ */
+#define PJX_BAND_NO_LOWER (-(1 << 30))
+#define PJX_BAND_NO_UPPER (1 << 30)
+int pjx_attn_fwd_band(const void* q, const void* k, const void* v, void* o, float* lse,
+                      const int32_t* kv_lengths, const float* bias, int64_t bias_batch_stride,
+                      int64_t bias_head_stride, int B, int Lq, int Lkv, int Hq, int Hkv, int D, int Dv,
+                      int dtype, int band_lo, int band_hi, float sm_scale, int impl, int32_t* status,
+                      void* stream);
+
+/*
  * Backward of pjx_attn_fwd: dq, dk, dv from q, k, v, o, d_o and the forward's
  * natural-log lse, for the same masks and bias (the bias itself gets no gradient
  * here).  First correct path: exact fp32 arithmetic on CUDA cores for every dtype.
@@ -93,6 +114,12 @@ int pjx_attn_bwd(const void* q, const void* k, const void* v, const void* o, con
                  const float* bias, int64_t bias_batch_stride, int64_t bias_head_stride, int B, int Lq,
                  int Lkv, int Hq, int Hkv, int D, int Dv, int dtype, int causal, float sm_scale,
                  void* workspace, size_t workspace_bytes, void* stream);
+/* The same for the band form of the mask (see pjx_attn_fwd_band). */
+int pjx_attn_bwd_band(const void* q, const void* k, const void* v, const void* o, const float* lse,
+                      const void* d_o, void* dq, void* dk, void* dv, const int32_t* kv_lengths,
+                      const float* bias, int64_t bias_batch_stride, int64_t bias_head_stride, int B,
+                      int Lq, int Lkv, int Hq, int Hkv, int D, int Dv, int dtype, int band_lo,
+                      int band_hi, float sm_scale, void* workspace, size_t workspace_bytes, void* stream);
 size_t pjx_attn_bwd_workspace_bytes(int B, int Lq, int Hq);
 
 /*

@@ -7,6 +7,7 @@ build it with ``python -m probjax_b200.build``.
 """
 
 from .attention import (  # noqa: F401
+    attention_backward,
     attention_forward,
     check_status,
     combine_partials,
@@ -23,11 +24,14 @@ from .dispatch import b200_attention_or_none, device_attention_defaults  # noqa:
 from .masks import (  # noqa: F401
     AttentionBias,
     AttentionMask,
+    CausalFromBottomRightMask,
+    CausalLocalWindowMask,
     CausalMask,
     ComposeMask,
     DenseBias,
     KeyPaddingMask,
     KVLenMask,
+    LocalWindowMask,
     NoMask,
     QKVLengthMask,
 )

@@ -107,13 +107,31 @@ def _gqa_group(hq: int, hkv: int) -> int:
 # ---------------------------------------------------------------------------
 
 
-def attention_forward(q, k, v, *, causal=False, kv_lengths=None, bias=None, sm_scale=1.0,
+_BAND_NO_LOWER, _BAND_NO_UPPER = -(1 << 30), 1 << 30
+
+
+def _band_args(causal, band):
+    """(band_lo, band_hi) C arguments from the ``causal`` flag and an optional
+    ``(lo, hi)`` pair (``None`` = open side): key ``j`` is visible to query ``i`` iff
+    ``i + lo <= j <= i + hi``."""
+    lo, hi = (None, None) if band is None else band
+    if causal:
+        hi = 0 if hi is None else min(int(hi), 0)
+    lo = _BAND_NO_LOWER if lo is None else max(int(lo), _BAND_NO_LOWER)
+    hi = _BAND_NO_UPPER if hi is None else min(int(hi), _BAND_NO_UPPER)
+    return lo, hi
+
+
+def attention_forward(q, k, v, *, causal=False, band=None, kv_lengths=None, bias=None, sm_scale=1.0,
                       return_lse=False, impl=None, out=None, lse_out=None):
-    """One ``pjx_attn_fwd`` call. ``q [B,Lq,Hq,D]``, ``k [B,Lkv,Hkv,D]``,
+    """One ``pjx_attn_fwd_band`` call. ``q [B,Lq,Hq,D]``, ``k [B,Lkv,Hkv,D]``,
     ``v [B,Lkv,Hkv,Dv]``; CUDA tensors stay on the device, host tensors use the
-    host-buffer entry point.  ``out`` / ``lse_out`` are optional preallocated result
-    tensors (same side as the inputs).  Returns ``o`` or ``(o, lse)``."""
+    host-buffer entry point.  ``band = (lo, hi)`` limits query ``i`` to keys
+    ``i + lo .. i + hi`` (``None`` leaves a side open; ``causal`` is ``(None, 0)``).
+    ``out`` / ``lse_out`` are optional preallocated result tensors (same side as the
+    inputs).  Returns ``o`` or ``(o, lse)``."""
     _require_gpu()
+    band_lo, band_hi = _band_args(causal, band)
     q, k, v = _as_tensor(q), _as_tensor(k), _as_tensor(v)
     if q.dtype not in _DTYPES:
         raise ValueError(f"unsupported dtype {q.dtype}; expected float32, bfloat16 or float16")
@@ -138,12 +156,15 @@ def attention_forward(q, k, v, *, causal=False, kv_lengths=None, bias=None, sm_s
             bs = 0 if bt.shape[0] == 1 else bt.stride(0)
             hs = 0 if bt.shape[1] == 1 else bt.stride(1)
         with torch.cuda.device(dev):
-            rc = L.pjx_attn_fwd(_ptr(q), _ptr(k), _ptr(v), _ptr(o), _ptr(lse), _ptr(kvl), _ptr(bt), bs, hs,
-                                B, Lq, Lkv, Hq, Hkv, D, Dv, _DTYPES[q.dtype], int(bool(causal)), float(sm_scale),
-                                _IMPL[impl], _ptr(_status_word(dev)), _stream(dev))
+            rc = L.pjx_attn_fwd_band(_ptr(q), _ptr(k), _ptr(v), _ptr(o), _ptr(lse), _ptr(kvl), _ptr(bt), bs, hs,
+                                     B, Lq, Lkv, Hq, Hkv, D, Dv, _DTYPES[q.dtype], band_lo, band_hi,
+                                     float(sm_scale), _IMPL[impl], _ptr(_status_word(dev)), _stream(dev))
         _lib.check(rc)
         return (o, lse) if return_lse else o
     # host buffers
+    is_causal = band_lo == _BAND_NO_LOWER and band_hi == 0
+    if not is_causal and (band_lo != _BAND_NO_LOWER or band_hi != _BAND_NO_UPPER):
+        raise NotImplementedError("the host-buffer entry point takes no mask band other than the causal one")
     dev = torch.device("cuda", torch.cuda.current_device())
     q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
     pin = q.is_pinned()
@@ -156,16 +177,18 @@ def attention_forward(q, k, v, *, causal=False, kv_lengths=None, bias=None, sm_s
     staging = _scratch_bytes(dev, "staging", need)
     with torch.cuda.device(dev):
         rc = L.pjx_attn_fwd_host(_ptr(q), _ptr(k), _ptr(v), _ptr(o), _ptr(lse), _ptr(kvl), _ptr(bt), bb, bh,
-                                 B, Lq, Lkv, Hq, Hkv, D, Dv, _DTYPES[q.dtype], int(bool(causal)), float(sm_scale),
+                                 B, Lq, Lkv, Hq, Hkv, D, Dv, _DTYPES[q.dtype], int(is_causal), float(sm_scale),
                                  _IMPL[impl], _ptr(staging), staging.numel(), _stream(dev))
     _lib.check(rc)
     return (o, lse) if return_lse else o
 
 
-def attention_backward(q, k, v, o, lse, d_o, *, causal=False, kv_lengths=None, bias=None, sm_scale=1.0):
-    """One ``pjx_attn_bwd`` call on CUDA tensors: ``(dq, dk, dv)`` for the forward that
-    produced ``o`` and ``lse`` from the same arguments."""
+def attention_backward(q, k, v, o, lse, d_o, *, causal=False, band=None, kv_lengths=None, bias=None,
+                       sm_scale=1.0):
+    """One ``pjx_attn_bwd_band`` call on CUDA tensors: ``(dq, dk, dv)`` for the forward
+    that produced ``o`` and ``lse`` from the same arguments."""
     _require_gpu()
+    band_lo, band_hi = _band_args(causal, band)
     dev = q.device
     q, k, v, o, d_o = (x.contiguous() for x in (q, k, v, o, d_o))
     lse = lse.contiguous().float()
@@ -182,9 +205,10 @@ def attention_backward(q, k, v, o, lse, d_o, *, causal=False, kv_lengths=None, b
     L = _lib.lib()
     ws = _scratch_bytes(dev, "bwd", L.pjx_attn_bwd_workspace_bytes(B, Lq, Hq))
     with torch.cuda.device(dev):
-        rc = L.pjx_attn_bwd(_ptr(q), _ptr(k), _ptr(v), _ptr(o), _ptr(lse), _ptr(d_o), _ptr(dq), _ptr(dk), _ptr(dv),
-                            _ptr(kvl), _ptr(bt), bs, hs, B, Lq, Lkv, Hq, Hkv, D, Dv, _DTYPES[q.dtype],
-                            int(bool(causal)), float(sm_scale), _ptr(ws), ws.numel(), _stream(dev))
+        rc = L.pjx_attn_bwd_band(_ptr(q), _ptr(k), _ptr(v), _ptr(o), _ptr(lse), _ptr(d_o), _ptr(dq), _ptr(dk),
+                                 _ptr(dv), _ptr(kvl), _ptr(bt), bs, hs, B, Lq, Lkv, Hq, Hkv, D, Dv,
+                                 _DTYPES[q.dtype], band_lo, band_hi, float(sm_scale), _ptr(ws), ws.numel(),
+                                 _stream(dev))
     _lib.check(rc)
     return dq, dk, dv
 
@@ -195,19 +219,19 @@ class _AttentionFunction(torch.autograd.Function):
     its kernels the same way, kernels/attention.py:3156-3270)."""
 
     @staticmethod
-    def forward(ctx, q, k, v, causal, kv_lengths, bias, sm_scale, impl):
-        o, lse = attention_forward(q, k, v, causal=causal, kv_lengths=kv_lengths, bias=bias, sm_scale=sm_scale,
+    def forward(ctx, q, k, v, band, kv_lengths, bias, sm_scale, impl):
+        o, lse = attention_forward(q, k, v, band=band, kv_lengths=kv_lengths, bias=bias, sm_scale=sm_scale,
                                    return_lse=True, impl=impl)
         ctx.save_for_backward(q, k, v, o, lse)
-        ctx.args = (causal, kv_lengths, bias, sm_scale)
+        ctx.args = (band, kv_lengths, bias, sm_scale)
         ctx.mark_non_differentiable(lse)
         return o, lse
 
     @staticmethod
     def backward(ctx, d_o, _d_lse):
         q, k, v, o, lse = ctx.saved_tensors
-        causal, kv_lengths, bias, sm_scale = ctx.args
-        dq, dk, dv = attention_backward(q, k, v, o, lse, d_o, causal=causal, kv_lengths=kv_lengths, bias=bias,
+        band, kv_lengths, bias, sm_scale = ctx.args
+        dq, dk, dv = attention_backward(q, k, v, o, lse, d_o, band=band, kv_lengths=kv_lengths, bias=bias,
                                         sm_scale=sm_scale)
         return dq, dk, dv, None, None, None, None, None
 
@@ -342,12 +366,12 @@ def mha(q, k, v, mask: AttentionMask | None = None, bias: AttentionBias | None =
             raise NotImplementedError("differentiable attention takes CUDA tensors")
         if lm.q_limit is not None:
             raise NotImplementedError("gradients under a query-length mask are not implemented")
-        out, lse = _AttentionFunction.apply(q, k, v, lm.causal, lm.kv_lengths, bt, float(sm_scale), implementation)
+        out, lse = _AttentionFunction.apply(q, k, v, lm.band, lm.kv_lengths, bt, float(sm_scale), implementation)
         res = (out, lse) if return_lse else out
-    elif use_splitkv(q, k, causal=lm.causal, bias=bt, q_limit=lm.q_limit, dropout_rate=dropout_rate, split_kv=split_kv):
+    elif use_splitkv(q, k, causal=lm.banded, bias=bt, q_limit=lm.q_limit, dropout_rate=dropout_rate, split_kv=split_kv):
         res = decode_forward(q, k, v, kv_lengths=lm.kv_lengths, sm_scale=sm_scale, return_lse=return_lse)
     else:
-        res = attention_forward(q, k, v, causal=lm.causal, kv_lengths=lm.kv_lengths, bias=bt, sm_scale=sm_scale,
+        res = attention_forward(q, k, v, band=lm.band, kv_lengths=lm.kv_lengths, bias=bt, sm_scale=sm_scale,
                                 return_lse=return_lse, impl=implementation)
     out, lse = res if return_lse else (res, None)
     out, lse = _apply_q_limit(out, lse, lm.q_limit)
@@ -513,6 +537,8 @@ def mla(q, cache, wk=None, wv=None, *, mask=None, bias=None, rng=None, sm_scale:
     B, Lq, S = q.shape[0], q.shape[1], cache.shape[1]
     Dv = R if wv is None else wv.shape[1]
     lm = lower_mask(mask, B, Lq, S)
+    if lm.banded and not lm.causal:
+        raise NotImplementedError("mla takes no mask band other than the causal one")
     bt = lower_bias(bias, B, H, Lq, S)
     q, cache = q.contiguous(), cache.contiguous()
     wk = None if wk is None else wk.to(dev).contiguous()

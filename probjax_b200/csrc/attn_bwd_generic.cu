@@ -40,7 +40,7 @@ struct BwdParams {
   const float* bias;
   int64_t bias_bs, bias_hs;
   int B, Lq, Lkv, Hq, Hkv, D, Dv;
-  int causal;
+  int band_lo, band_hi;  // key j is visible to query i iff i + band_lo <= j <= i + band_hi
   float sm_scale;
 };
 
@@ -129,7 +129,7 @@ __device__ __forceinline__ void tile_p_ds(const BwdParams& p, const Tiles& t, in
       const int col = tx + 16 * c, kj = k0 + col;
       float x = s[i][c] * p.sm_scale;
       if (bias && qi < p.Lq && kj < p.Lkv) x += bias[(int64_t)qi * p.Lkv + kj];
-      const bool keep = qi < p.Lq && kj < kv_len && (!p.causal || kj <= qi) && lse != INFINITY;
+      const bool keep = qi < p.Lq && kj < kv_len && kj <= qi + p.band_hi && kj >= qi + p.band_lo && lse != INFINITY;
       const float pr = keep ? exp2f((x - lse) * kLog2e) : 0.f;
       t.Ps[r * (T + 1) + col] = pr;
       t.dSs[r * (T + 1) + col] = pr * (dp[i][c] - delta);
@@ -146,7 +146,8 @@ __global__ void __launch_bounds__(NT) bwd_dq_kernel(const BwdParams p) {
   const int hk = h / (p.Hq / p.Hkv);
   int kv_len = p.Lkv;
   if (p.kv_lengths) kv_len = max(0, min(kv_len, p.kv_lengths[b]));
-  const int kv_end = p.causal ? min(kv_len, q0 + T) : kv_len;
+  const int kv_end = max(0, min(kv_len, min(q0 + T, p.Lq) + p.band_hi));  // keys past the band of the tile's last row
+  const int kv_begin = (max(0, q0 + p.band_lo) / T) * T;                  // keys before the band of its first row
   const int64_t qstride = (int64_t)p.Hq * p.D, ostride = (int64_t)p.Hq * p.Dv;
   const int64_t kstride = (int64_t)p.Hkv * p.D, vstride = (int64_t)p.Hkv * p.Dv;
   const T_* q = static_cast<const T_*>(p.q) + ((int64_t)b * p.Lq * p.Hq + h) * p.D;
@@ -166,7 +167,7 @@ __global__ void __launch_bounds__(NT) bwd_dq_kernel(const BwdParams p) {
   for (int i = 0; i < 2; ++i)
 #pragma unroll
     for (int c = 0; c < NC; ++c) acc[i][c] = 0.f;
-  for (int k0 = 0; k0 < kv_end; k0 += T) {
+  for (int k0 = kv_begin; k0 < kv_end; k0 += T) {
     __syncthreads();
     load_rows<T_>(t.Ks, t.Dp, k, kstride, k0, kv_len, p.D);
     load_rows<T_>(t.Vs, t.Dvp, v, vstride, k0, kv_len, p.Dv);
@@ -221,12 +222,14 @@ __global__ void __launch_bounds__(NT) bwd_dkdv_kernel(const BwdParams p) {
   if (k0 < kv_len) {  // keys past the valid length get zero gradients
     load_rows<T_>(t.Ks, t.Dp, k, kstride, k0, kv_len, p.D);
     load_rows<T_>(t.Vs, t.Dvp, v, vstride, k0, kv_len, p.Dv);
-    const int q_first = p.causal ? (k0 / T) * T : 0;  // queries before the tile's first key never see it
+    // queries outside [first key - band_hi, last key - band_lo] never see a key of this tile
+    const int q_first = (max(0, k0 - p.band_hi) / T) * T;
+    const int q_end = min(p.Lq, k0 + T - p.band_lo);
     for (int g = 0; g < G; ++g) {
       const int h = hk * G + g;
       const T_* q = static_cast<const T_*>(p.q) + ((int64_t)b * p.Lq * p.Hq + h) * p.D;
       const T_* d_o = static_cast<const T_*>(p.d_o) + ((int64_t)b * p.Lq * p.Hq + h) * p.Dv;
-      for (int q0 = q_first; q0 < p.Lq; q0 += T) {
+      for (int q0 = q_first; q0 < q_end; q0 += T) {
         __syncthreads();
         load_rows<T_>(t.Qs, t.Dp, q, qstride, q0, p.Lq, p.D);
         load_rows<T_>(t.dOs, t.Dvp, d_o, ostride, q0, p.Lq, p.Dv);
@@ -335,16 +338,19 @@ size_t pjx_attn_bwd_workspace_bytes(int B, int Lq, int Hq) {
   return ((size_t)B * Hq * Lq * sizeof(float) + 255) / 256 * 256;
 }
 
-int pjx_attn_bwd(const void* q, const void* k, const void* v, const void* o, const float* lse, const void* d_o,
-                 void* dq, void* dk, void* dv, const int32_t* kv_lengths, const float* bias,
-                 int64_t bias_batch_stride, int64_t bias_head_stride, int B, int Lq, int Lkv, int Hq, int Hkv, int D,
-                 int Dv, int dtype, int causal, float sm_scale, void* workspace, size_t workspace_bytes, void* stream) {
+int pjx_attn_bwd_band(const void* q, const void* k, const void* v, const void* o, const float* lse, const void* d_o,
+                      void* dq, void* dk, void* dv, const int32_t* kv_lengths, const float* bias,
+                      int64_t bias_batch_stride, int64_t bias_head_stride, int B, int Lq, int Lkv, int Hq, int Hkv,
+                      int D, int Dv, int dtype, int band_lo, int band_hi, float sm_scale, void* workspace,
+                      size_t workspace_bytes, void* stream) {
   if (dtype != PJX_F32 && dtype != PJX_BF16 && dtype != PJX_F16)
     return fail(PJX_ERR_BAD_ARG, "dtype must be float32, bfloat16 or float16 (got code %d)", dtype);
   if (B < 0 || Lq < 0 || Lkv < 0 || Hq < 1 || Hkv < 1 || D < 1 || Dv < 1)
     return fail(PJX_ERR_BAD_ARG, "negative or zero dimension");
   if (Hq % Hkv != 0) return fail(PJX_ERR_BAD_ARG, "query heads %d must be a multiple of kv heads %d", Hq, Hkv);
   if (D > 256 || Dv > 256) return fail(PJX_ERR_UNSUPPORTED, "head dims above 256 are not supported (D=%d, Dv=%d)", D, Dv);
+  if (Lq >= PJX_BAND_NO_UPPER || Lkv >= PJX_BAND_NO_UPPER)
+    return fail(PJX_ERR_BAD_ARG, "sequence lengths must be below 2^30");
   if (B == 0 || Hq == 0) return PJX_OK;
   if (Lq > 0 && (!q || !o || !d_o || !lse || !dq)) return fail(PJX_ERR_BAD_ARG, "backward: null query-side buffer");
   if (Lkv > 0 && (!k || !v || !dk || !dv)) return fail(PJX_ERR_BAD_ARG, "backward: null key-side buffer");
@@ -358,7 +364,8 @@ int pjx_attn_bwd(const void* q, const void* k, const void* v, const void* o, con
   p.dq = dq; p.dk = dk; p.dv = dv;
   p.kv_lengths = kv_lengths; p.bias = bias; p.bias_bs = bias_batch_stride; p.bias_hs = bias_head_stride;
   p.B = B; p.Lq = Lq; p.Lkv = Lkv; p.Hq = Hq; p.Hkv = Hkv; p.D = D; p.Dv = Dv;
-  p.causal = causal != 0;
+  p.band_lo = band_lo < PJX_BAND_NO_LOWER ? PJX_BAND_NO_LOWER : (band_lo > PJX_BAND_NO_UPPER ? PJX_BAND_NO_UPPER : band_lo);
+  p.band_hi = band_hi > PJX_BAND_NO_UPPER ? PJX_BAND_NO_UPPER : (band_hi < PJX_BAND_NO_LOWER ? PJX_BAND_NO_LOWER : band_hi);
   p.sm_scale = sm_scale;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   if (Lq == 0) {  // no queries: the key-side gradients are zero
@@ -371,6 +378,15 @@ int pjx_attn_bwd(const void* q, const void* k, const void* v, const void* o, con
     case PJX_BF16: return launch_dtype<__nv_bfloat16>(p, st);
     default: return launch_dtype<__half>(p, st);
   }
+}
+
+int pjx_attn_bwd(const void* q, const void* k, const void* v, const void* o, const float* lse, const void* d_o,
+                 void* dq, void* dk, void* dv, const int32_t* kv_lengths, const float* bias,
+                 int64_t bias_batch_stride, int64_t bias_head_stride, int B, int Lq, int Lkv, int Hq, int Hkv, int D,
+                 int Dv, int dtype, int causal, float sm_scale, void* workspace, size_t workspace_bytes, void* stream) {
+  return pjx_attn_bwd_band(q, k, v, o, lse, d_o, dq, dk, dv, kv_lengths, bias, bias_batch_stride, bias_head_stride, B,
+                           Lq, Lkv, Hq, Hkv, D, Dv, dtype, PJX_BAND_NO_LOWER, causal ? 0 : PJX_BAND_NO_UPPER, sm_scale,
+                           workspace, workspace_bytes, stream);
 }
 
 }  // extern "C"

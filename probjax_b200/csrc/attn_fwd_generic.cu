@@ -43,8 +43,9 @@ __global__ void __launch_bounds__(NT) attn_fwd_generic_kernel(const FwdParams p)
 
   int kv_len = p.Lkv;
   if (p.kv_lengths) kv_len = max(0, min(kv_len, p.kv_lengths[b]));
-  int kv_end = kv_len;
-  if (p.causal) kv_end = min(kv_end, q0 + BM);  // keys beyond the tile's last query are masked
+  // keys outside [first query + band_lo, last query + band_hi] of the tile are masked for all its rows
+  const int kv_end = max(0, min(kv_len, min(q0 + BM, p.Lq) + p.band_hi));
+  const int kv_begin = (max(0, q0 + p.band_lo) / BN) * BN;
 
   for (int idx = tid; idx < BM * D; idx += NT) {
     int r = idx / D, d = idx - r * D;
@@ -66,7 +67,7 @@ __global__ void __launch_bounds__(NT) attn_fwd_generic_kernel(const FwdParams p)
   const float* bias = nullptr;
   if (p.bias) bias = p.bias + (int64_t)b * p.bias_bs + (int64_t)h * p.bias_hs;
 
-  for (int k0 = 0; k0 < kv_end; k0 += BN) {
+  for (int k0 = kv_begin; k0 < kv_end; k0 += BN) {
     __syncthreads();  // previous tile fully consumed (also orders the Q staging)
     for (int idx = tid; idx < BN * D; idx += NT) {
       int r = idx / D, d = idx - r * D;
@@ -111,7 +112,7 @@ __global__ void __launch_bounds__(NT) attn_fwd_generic_kernel(const FwdParams p)
         const int kj = k0 + tx + 16 * c;
         float x = s[i][c] * c1;
         if (bias && qi < p.Lq && kj < p.Lkv) x = fmaf(bias[(int64_t)qi * p.Lkv + kj], kLog2e, x);
-        const bool keep = (kj < kv_len) && (!p.causal || kj <= qi);
+        const bool keep = (kj < kv_len) && kj <= qi + p.band_hi && kj >= qi + p.band_lo;
         x = keep ? x : -INFINITY;
         s[i][c] = x;
         tmax = fmaxf(tmax, x);

@@ -130,7 +130,12 @@ __device__ __forceinline__ void exp_pack_store(const float (&s)[BN], float2 cs2,
 // BIAS: 0 = no bias, 1 = bias read by each thread from global memory, 2 = bias tiles
 // staged in shared memory by TMA (one row per thread out of global memory costs one
 // L1 transaction per lane and instruction; the staged tile is read conflict-free).
-template <int DQK, int DV, int BN, int KST, int VST, bool BF16, int BIAS>
+//
+// BAND: the mask is a band of visible keys around each query row (row + band_lo <= key <=
+// row + band_hi) instead of the causal flag.  The KV loop then starts at the first tile that
+// any row of the CTA can see; a query tile whose band begins later meets leading tiles it
+// masks completely, which leaves its running state untouched.
+template <int DQK, int DV, int BN, int KST, int VST, bool BF16, int BIAS, bool BAND>
 __global__ void __launch_bounds__(NTHREADS, 1)
 attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                       const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_b,
@@ -176,14 +181,37 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
   int kv_len = p.Lkv;
   if (p.kv_lengths) kv_len = max(0, min(kv_len, p.kv_lengths[b]));
   int n_t[2];
+  int j_base = 0;  // first KV tile of the loop (BAND only)
+  if constexpr (BAND) {
+    int lo_t[2], hi_t[2];
+    j_base = 0x7fffffff;
 #pragma unroll
-  for (int t = 0; t < 2; ++t) {
-    const int qs = q0 + t * BM;
-    if (qs >= p.Lq) {
-      n_t[t] = 0;
-    } else {
-      const int lim = p.causal ? min(kv_len, min(qs + BM, p.Lq)) : kv_len;
-      n_t[t] = (lim + BN - 1) / BN;
+    for (int t = 0; t < 2; ++t) {
+      const int qs = q0 + t * BM;
+      lo_t[t] = hi_t[t] = 0;
+      if (qs < p.Lq) {
+        const int end = max(0, min(kv_len, min(qs + BM, p.Lq) + p.band_hi));
+        const int begin = max(0, qs + p.band_lo);
+        if (begin < end) {
+          lo_t[t] = begin / BN;
+          hi_t[t] = (end + BN - 1) / BN;
+          j_base = min(j_base, lo_t[t]);
+        }
+      }
+    }
+#pragma unroll
+    for (int t = 0; t < 2; ++t) n_t[t] = hi_t[t] > 0 ? hi_t[t] - j_base : 0;
+    if (j_base == 0x7fffffff) j_base = 0;
+  } else {
+#pragma unroll
+    for (int t = 0; t < 2; ++t) {
+      const int qs = q0 + t * BM;
+      if (qs >= p.Lq) {
+        n_t[t] = 0;
+      } else {
+        const int lim = p.causal ? min(kv_len, min(qs + BM, p.Lq)) : kv_len;
+        n_t[t] = (lim + BN - 1) / BN;
+      }
     }
   }
   const int n = max(n_t[0], n_t[1]);
@@ -237,13 +265,13 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
 #pragma unroll
         for (int s = 0; s < C::Q_SUB; ++s)
           tma_load_4d(sbase + C::OFF_K + ks * C::K_TILE_BYTES + s * BN * 128, &tm_k, BAR(K_FULL + ks), s * 64, hk,
-                      j * BN, b);
+                      (j_base + j) * BN, b);
         if (!mbar_wait(BAR(V_EMPTY + vs), ((j / VST) & 1) ^ 1, abort_flag)) break;
         mbar_arrive_expect_tx(BAR(V_FULL + vs), C::V_TILE_BYTES);
 #pragma unroll
         for (int s = 0; s < C::V_SUB; ++s)
           tma_load_4d(sbase + C::OFF_V + vs * C::V_TILE_BYTES + s * BN * 128, &tm_v, BAR(V_FULL + vs), s * 64, hk,
-                      j * BN, b);
+                      (j_base + j) * BN, b);
         if constexpr (BIAS == 2) {
           bool okb = true;
 #pragma unroll
@@ -255,7 +283,7 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
 #pragma unroll
             for (int c = 0; c < BN / 32; ++c)
               tma_load_4d(sbase + C::OFF_BIAS + t * C::BIAS_TILE_BYTES + c * BM * 128, &tm_b, BAR(B_FULL + t),
-                          j * BN + c * 32, q0 + t * BM, p.bias_hs ? h : 0, p.bias_bs ? b : 0);
+                          (j_base + j) * BN + c * 32, q0 + t * BM, p.bias_hs ? h : 0, p.bias_bs ? b : 0);
           }
           if (!okb) break;
         }
@@ -356,8 +384,14 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
       tc_fence_after();
       PJX_TRACE_AT(t, j, 1);
       constexpr int NCH = BN / 32;
-      const int k0 = j * BN;
-      const bool need_mask = (k0 + BN > kv_len) || (p.causal && k0 + BN - 1 > q0 + t * BM);
+      const int k0 = (j_base + j) * BN;
+      bool need_mask;
+      if constexpr (BAND) {
+        need_mask = (k0 + BN > kv_len) || (k0 + BN - 1 > q0 + t * BM + p.band_hi) ||
+                    (k0 < q0 + t * BM + BM - 1 + p.band_lo);
+      } else {
+        need_mask = (k0 + BN > kv_len) || (p.causal && k0 + BN - 1 > q0 + t * BM);
+      }
 
       // The whole row of scores in registers: all loads in flight at once.
       float s[BN];
@@ -413,7 +447,12 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
 #pragma unroll
         for (int i = 0; i < BN; ++i) {
           const int key = k0 + i;
-          const bool keep = key < kv_len && (!p.causal || key <= row);
+          bool keep;
+          if constexpr (BAND) {
+            keep = key < kv_len && key <= row + p.band_hi && key >= row + p.band_lo;
+          } else {
+            keep = key < kv_len && (!p.causal || key <= row);
+          }
           s[i] = keep ? s[i] : -INFINITY;
         }
       }
@@ -581,7 +620,7 @@ bool bias_can_be_staged(const FwdParams& p) {
          p.bias_bs % 4 == 0;
 }
 
-template <int DQK, int DV, int BN, int KST, int VST, bool BF16, int BIAS>
+template <int DQK, int DV, int BN, int KST, int VST, bool BF16, int BIAS, bool BAND = false>
 int launch_one(const FwdParams& p, int dtype, cudaStream_t stream) {
   using C = Cfg<DQK, DV, BN, KST, VST, BIAS == 2>;
   CUtensorMap tq, tk, tv, tb;
@@ -594,12 +633,13 @@ int launch_one(const FwdParams& p, int dtype, cudaStream_t stream) {
   } else {
     tb = tq;  // unused
   }
-  auto kern = attn_fwd_sm100_kernel<DQK, DV, BN, KST, VST, BF16, BIAS>;
+  auto kern = attn_fwd_sm100_kernel<DQK, DV, BN, KST, VST, BF16, BIAS, BAND>;
   if ((rc = check_cuda(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES),
                        "cudaFuncSetAttribute(sm100 fwd)")))
     return rc;
   dim3 grid((unsigned)(((p.Lq + 2 * BM - 1) / (2 * BM)) * (int64_t)p.Hq * p.B));
-  const int order_w = p.causal ? 16 : 1;
+  // triangular work (an upper bound on the keys only): heavy-first order in blocks of 16 pairs
+  const int order_w = (p.band_hi < PJX_BAND_NO_UPPER && p.band_lo == PJX_BAND_NO_LOWER) ? 16 : 1;
   kern<<<grid, NTHREADS, C::SMEM_BYTES, stream>>>(tq, tk, tv, tb, p, order_w);
   count_launch();
   return check_cuda(cudaGetLastError(), "sm100 forward launch");
@@ -607,6 +647,10 @@ int launch_one(const FwdParams& p, int dtype, cudaStream_t stream) {
 
 template <int DQK, int DV, int BN, int KST, int VST, bool BF16>
 int launch_cfg(const FwdParams& p, int dtype, cudaStream_t stream) {
+  if (p.banded()) {
+    if (!p.bias) return launch_one<DQK, DV, BN, KST, VST, BF16, 0, true>(p, dtype, stream);
+    return launch_one<DQK, DV, BN, KST, VST, BF16, 1, true>(p, dtype, stream);
+  }
   if (!p.bias) return launch_one<DQK, DV, BN, KST, VST, BF16, 0>(p, dtype, stream);
   return launch_one<DQK, DV, BN, KST, VST, BF16, 1>(p, dtype, stream);
 }
@@ -616,7 +660,7 @@ int launch_by_shape(const FwdParams& p, int dtype, cudaStream_t stream) {
   if (p.D == 128 && p.Dv == 128) return launch_cfg<128, 128, 128, 2, 2, BF16>(p, dtype, stream);
   if (p.D == 64 && p.Dv == 64) {
     // with a bias that TMA can address, two K/V stages leave room for the staged bias tiles
-    if (bias_can_be_staged(p)) return launch_one<64, 64, 128, 2, 2, BF16, 2>(p, dtype, stream);
+    if (bias_can_be_staged(p) && !p.banded()) return launch_one<64, 64, 128, 2, 2, BF16, 2>(p, dtype, stream);
     return launch_cfg<64, 64, 128, 3, 3, BF16>(p, dtype, stream);
   }
   if (p.D == 192 && p.Dv == 128) return launch_cfg<192, 128, 128, 2, 1, BF16>(p, dtype, stream);

@@ -101,29 +101,44 @@ const char* pjx_last_error(void) { return g_err; }
 
 int64_t pjx_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
 
-int pjx_attn_fwd(const void* q, const void* k, const void* v, void* o, float* lse, const int32_t* kv_lengths,
-                 const float* bias, int64_t bias_batch_stride, int64_t bias_head_stride, int B, int Lq, int Lkv,
-                 int Hq, int Hkv, int D, int Dv, int dtype, int causal, float sm_scale, int impl, int32_t* status,
-                 void* stream) {
+int pjx_attn_fwd_band(const void* q, const void* k, const void* v, void* o, float* lse, const int32_t* kv_lengths,
+                      const float* bias, int64_t bias_batch_stride, int64_t bias_head_stride, int B, int Lq, int Lkv,
+                      int Hq, int Hkv, int D, int Dv, int dtype, int band_lo, int band_hi, float sm_scale, int impl,
+                      int32_t* status, void* stream) {
   int rc = validate_common(q, k, v, o, B, Lq, Lkv, Hq, Hkv, D, Dv, dtype);
   if (rc) return rc;
   if (impl != PJX_IMPL_AUTO && impl != PJX_IMPL_GENERIC && impl != PJX_IMPL_SM100)
     return fail(PJX_ERR_BAD_ARG, "impl must be 0 (auto), 1 (generic) or 2 (tcgen05), got %d", impl);
   if (bias && (bias_batch_stride < 0 || bias_head_stride < 0))
     return fail(PJX_ERR_BAD_ARG, "bias strides must be non-negative");
+  if (Lq >= PJX_BAND_NO_UPPER || Lkv >= PJX_BAND_NO_UPPER)
+    return fail(PJX_ERR_BAD_ARG, "sequence lengths must be below 2^30");
   if (B == 0 || Lq == 0) return PJX_OK;
   FwdParams p;
   p.q = q; p.k = k; p.v = v; p.o = o; p.lse = lse;
   p.kv_lengths = kv_lengths;
   p.bias = bias; p.bias_bs = bias_batch_stride; p.bias_hs = bias_head_stride;
   p.B = B; p.Lq = Lq; p.Lkv = Lkv; p.Hq = Hq; p.Hkv = Hkv; p.D = D; p.Dv = Dv;
-  p.causal = causal != 0;
+  p.band_lo = band_lo <= PJX_BAND_NO_LOWER ? PJX_BAND_NO_LOWER : band_lo;
+  p.band_hi = band_hi >= PJX_BAND_NO_UPPER ? PJX_BAND_NO_UPPER : band_hi;
+  if (p.band_lo > PJX_BAND_NO_UPPER) p.band_lo = PJX_BAND_NO_UPPER;  // nothing visible; keeps row + band in range
+  if (p.band_hi < PJX_BAND_NO_LOWER) p.band_hi = PJX_BAND_NO_LOWER;
+  p.causal = p.band_hi == 0 && p.band_lo == PJX_BAND_NO_LOWER;
   p.sm_scale = sm_scale;
   p.status = status;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   if (impl == PJX_IMPL_SM100) return launch_fwd_sm100(p, dtype, st);
   if (impl == PJX_IMPL_AUTO && fwd_sm100_supported(p, dtype, nullptr)) return launch_fwd_sm100(p, dtype, st);
   return launch_fwd_generic(p, dtype, st);
+}
+
+int pjx_attn_fwd(const void* q, const void* k, const void* v, void* o, float* lse, const int32_t* kv_lengths,
+                 const float* bias, int64_t bias_batch_stride, int64_t bias_head_stride, int B, int Lq, int Lkv,
+                 int Hq, int Hkv, int D, int Dv, int dtype, int causal, float sm_scale, int impl, int32_t* status,
+                 void* stream) {
+  return pjx_attn_fwd_band(q, k, v, o, lse, kv_lengths, bias, bias_batch_stride, bias_head_stride, B, Lq, Lkv, Hq,
+                           Hkv, D, Dv, dtype, PJX_BAND_NO_LOWER, causal ? 0 : PJX_BAND_NO_UPPER, sm_scale, impl,
+                           status, stream);
 }
 
 int pjx_attn_decode_default_split_len(int B, int Hkv, int capacity) {

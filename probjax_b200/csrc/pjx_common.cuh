@@ -57,9 +57,14 @@ struct FwdParams {
   const float* bias;          // [Bb, Hb, Lq, Lkv] or null
   int64_t bias_bs, bias_hs;   // element strides of the bias batch / head axes (0 = broadcast)
   int B, Lq, Lkv, Hq, Hkv, D, Dv;
-  int causal;
+  int causal;   // shorthand for band_hi == 0 with no lower bound (the kernels' fast path)
+  // Band of visible keys around each query row: row + band_lo <= key <= row + band_hi.
+  // PJX_BAND_NO_LOWER / PJX_BAND_NO_UPPER leave a side open.
+  int band_lo = PJX_BAND_NO_LOWER, band_hi = PJX_BAND_NO_UPPER;
   float sm_scale;
   int32_t* status;  // device status word or null
+
+  bool banded() const { return !causal && (band_lo > PJX_BAND_NO_LOWER || band_hi < PJX_BAND_NO_UPPER); }
 };
 
 struct DecodeParams {

@@ -2,15 +2,17 @@
 
 Host-side mirror of the part of the reference's object model the kernels take
 (probjax/nn/pallas_kernels/attention_mask_bias.py): ``NoMask`` (585),
-``CausalMask`` (617), ``QKVLengthMask`` (1079), ``KeyPaddingMask`` (1132),
-``KVLenMask`` (1401), ``ComposeMask`` (326) and ``DenseBias`` (1808).  A mask is a
+``CausalMask`` (617), ``LocalWindowMask`` (651), ``CausalLocalWindowMask`` (707),
+``CausalFromBottomRightMask`` (753), ``QKVLengthMask`` (1079), ``KeyPaddingMask``
+(1132), ``KVLenMask`` (1401), ``ComposeMask`` (326) and ``DenseBias`` (1808).  A mask is a
 callable ``mask(q_idx, k_idx, seg_q=None, seg_k=None) -> [Q, K] bool`` and can be
 materialised with ``dense``; masks combine with ``&``.
 
 The kernels do not evaluate these callables.  :func:`lower_mask` reduces a mask
-expression to the three things the kernels implement natively -- a causal flag,
-per-batch key lengths and a query-row limit -- and raises ``NotImplementedError``
-for anything else, which the dispatcher reports as "not mine".
+expression to the three things the kernels implement natively -- a band of visible
+keys around each query row (``i + lo <= j <= i + hi``; the causal mask is the band
+``(-inf, 0)``), per-batch key lengths and a query-row limit -- and raises
+``NotImplementedError`` for anything else, which the dispatcher reports as "not mine".
 """
 
 from __future__ import annotations
@@ -69,6 +71,44 @@ class CausalMask(AttentionMask):
 
     def __call__(self, q_idx, k_idx, seg_q=None, seg_k=None):
         return q_idx[:, None] >= k_idx[None, :]
+
+
+@dataclass(frozen=True)
+class LocalWindowMask(AttentionMask):
+    """``-right_window <= i - j <= left_window`` (attention_mask_bias.py:651-704);
+    ``right_window=None`` means 0."""
+
+    left_window: int
+    right_window: Optional[int] = None
+
+    def __call__(self, q_idx, k_idx, seg_q=None, seg_k=None):
+        dqk = q_idx[:, None].to(torch.int64) - k_idx[None, :].to(torch.int64)
+        rw = 0 if self.right_window is None else int(self.right_window)
+        return (dqk >= -rw) & (dqk <= int(self.left_window))
+
+
+@dataclass(frozen=True)
+class CausalLocalWindowMask(AttentionMask):
+    """Query ``i`` sees keys ``[i - left_window, i]`` (attention_mask_bias.py:707-750)."""
+
+    left_window: int
+
+    def __call__(self, q_idx, k_idx, seg_q=None, seg_k=None):
+        dqk = q_idx[:, None].to(torch.int64) - k_idx[None, :].to(torch.int64)
+        return (dqk >= 0) & (dqk <= int(self.left_window))
+
+
+@dataclass(frozen=True)
+class CausalFromBottomRightMask(AttentionMask):
+    """Causal mask aligned to the last key: ``i + (kv_length - q_length) >= j``
+    (attention_mask_bias.py:753-782)."""
+
+    q_length: int
+    kv_length: int
+
+    def __call__(self, q_idx, k_idx, seg_q=None, seg_k=None):
+        shift = int(self.kv_length) - int(self.q_length)
+        return (q_idx[:, None].to(torch.int64) + shift) >= k_idx[None, :].to(torch.int64)
 
 
 @dataclass(frozen=True)
@@ -183,9 +223,23 @@ class DenseBias(AttentionBias):
 
 @dataclass
 class LoweredMask:
-    causal: bool = False
+    band_lo: Optional[int] = None     # key j visible to query i iff i + band_lo <= j (None: no bound)
+    band_hi: Optional[int] = None     # ... and j <= i + band_hi (None: no bound)
     kv_lengths: Optional[Any] = None  # int32 tensor [B] or None
     q_limit: Optional[int] = None     # query rows >= q_limit see no key
+
+    @property
+    def causal(self) -> bool:
+        """The band is exactly the causal mask."""
+        return self.band_hi == 0 and self.band_lo is None
+
+    @property
+    def band(self):
+        return (self.band_lo, self.band_hi)
+
+    @property
+    def banded(self) -> bool:
+        return self.band_lo is not None or self.band_hi is not None
 
 
 def lower_mask(mask, batch: int, q_len: int, kv_len: int) -> LoweredMask:
@@ -194,7 +248,14 @@ def lower_mask(mask, batch: int, q_len: int, kv_len: int) -> LoweredMask:
     if mask is None or isinstance(mask, NoMask):
         return LoweredMask()
     if isinstance(mask, CausalMask):
-        return LoweredMask(causal=True)
+        return LoweredMask(band_hi=0)
+    if isinstance(mask, LocalWindowMask):
+        rw = 0 if mask.right_window is None else int(mask.right_window)
+        return LoweredMask(band_lo=-int(mask.left_window), band_hi=rw)
+    if isinstance(mask, CausalLocalWindowMask):
+        return LoweredMask(band_lo=-int(mask.left_window), band_hi=0)
+    if isinstance(mask, CausalFromBottomRightMask):
+        return LoweredMask(band_hi=int(mask.kv_length) - int(mask.q_length))
     if isinstance(mask, KVLenMask):
         lengths = mask.kv_lengths.reshape(-1)
         if lengths.shape[0] != batch:
@@ -218,7 +279,11 @@ def lower_mask(mask, batch: int, q_len: int, kv_len: int) -> LoweredMask:
     if isinstance(mask, ComposeMask) and mask.op == "and":
         a = lower_mask(mask.lhs, batch, q_len, kv_len)
         b = lower_mask(mask.rhs, batch, q_len, kv_len)
-        out = LoweredMask(causal=a.causal or b.causal)
+        out = LoweredMask()
+        los = [x for x in (a.band_lo, b.band_lo) if x is not None]
+        his = [x for x in (a.band_hi, b.band_hi) if x is not None]
+        out.band_lo = max(los) if los else None
+        out.band_hi = min(his) if his else None
         if a.kv_lengths is not None and b.kv_lengths is not None:
             out.kv_lengths = torch.minimum(a.kv_lengths.cpu(), b.kv_lengths.cpu()) \
                 if a.kv_lengths.device != b.kv_lengths.device else torch.minimum(a.kv_lengths, b.kv_lengths)

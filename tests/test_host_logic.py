@@ -248,3 +248,23 @@ def test_sharded_decode_two_ranks_gloo(tmp_path):
     for r in range(world):
         res = torch.load(os.path.join(str(tmp_path), f"r{r}.pt"))
         assert res["err"] < 1e-5 and res["err_lse"] < 1e-5
+
+
+def test_window_masks_lower_to_bands_and_compose():
+    import torch
+    from probjax_b200.masks import (CausalFromBottomRightMask, CausalLocalWindowMask, CausalMask, KVLenMask,
+                                    LocalWindowMask, lower_mask)
+
+    lm = lower_mask(LocalWindowMask(7, 3), 2, 16, 16)
+    assert (lm.band_lo, lm.band_hi, lm.causal, lm.banded) == (-7, 3, False, True)
+    assert lower_mask(LocalWindowMask(7), 2, 16, 16).band == (-7, 0)
+    assert lower_mask(CausalLocalWindowMask(5), 2, 16, 16).band == (-5, 0)
+    assert lower_mask(CausalFromBottomRightMask(4, 10), 2, 4, 10).band == (None, 6)
+    assert lower_mask(CausalMask(), 2, 16, 16).causal
+    both = lower_mask(CausalMask() & LocalWindowMask(9, 9) & KVLenMask(torch.tensor([3, 16])), 2, 16, 16)
+    assert both.band == (-9, 0) and both.kv_lengths.tolist() == [3, 16] and not both.causal
+    # dense forms follow the reference's predicates (attention_mask_bias.py:651-782)
+    i, j = torch.arange(6)[:, None], torch.arange(8)[None, :]
+    assert torch.equal(LocalWindowMask(2, 1).dense(6, 8)[0, 0], (i - j >= -1) & (i - j <= 2))
+    assert torch.equal(CausalLocalWindowMask(2).dense(6, 8)[0, 0], (i - j >= 0) & (i - j <= 2))
+    assert torch.equal(CausalFromBottomRightMask(6, 8).dense(6, 8)[0, 0], i + 2 >= j)
