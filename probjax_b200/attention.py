@@ -184,7 +184,7 @@ def attention_forward(q, k, v, *, causal=False, band=None, kv_lengths=None, bias
 
 
 def attention_backward(q, k, v, o, lse, d_o, *, causal=False, band=None, kv_lengths=None, bias=None,
-                       sm_scale=1.0):
+                       sm_scale=1.0, impl=None):
     """One ``pjx_attn_bwd_band`` call on CUDA tensors: ``(dq, dk, dv)`` for the forward
     that produced ``o`` and ``lse`` from the same arguments."""
     _require_gpu()
@@ -207,8 +207,8 @@ def attention_backward(q, k, v, o, lse, d_o, *, causal=False, band=None, kv_leng
     with torch.cuda.device(dev):
         rc = L.pjx_attn_bwd_band(_ptr(q), _ptr(k), _ptr(v), _ptr(o), _ptr(lse), _ptr(d_o), _ptr(dq), _ptr(dk),
                                  _ptr(dv), _ptr(kvl), _ptr(bt), bs, hs, B, Lq, Lkv, Hq, Hkv, D, Dv,
-                                 _DTYPES[q.dtype], band_lo, band_hi, float(sm_scale), _ptr(ws), ws.numel(),
-                                 _stream(dev))
+                                 _DTYPES[q.dtype], band_lo, band_hi, float(sm_scale), _IMPL[impl], _ptr(ws),
+                                 ws.numel(), _ptr(_status_word(dev)), _stream(dev))
     _lib.check(rc)
     return dq, dk, dv
 
@@ -223,16 +223,16 @@ class _AttentionFunction(torch.autograd.Function):
         o, lse = attention_forward(q, k, v, band=band, kv_lengths=kv_lengths, bias=bias, sm_scale=sm_scale,
                                    return_lse=True, impl=impl)
         ctx.save_for_backward(q, k, v, o, lse)
-        ctx.args = (band, kv_lengths, bias, sm_scale)
+        ctx.args = (band, kv_lengths, bias, sm_scale, impl)
         ctx.mark_non_differentiable(lse)
         return o, lse
 
     @staticmethod
     def backward(ctx, d_o, _d_lse):
         q, k, v, o, lse = ctx.saved_tensors
-        band, kv_lengths, bias, sm_scale = ctx.args
+        band, kv_lengths, bias, sm_scale, impl = ctx.args
         dq, dk, dv = attention_backward(q, k, v, o, lse, d_o, band=band, kv_lengths=kv_lengths, bias=bias,
-                                        sm_scale=sm_scale)
+                                        sm_scale=sm_scale, impl=impl)
         return dq, dk, dv, None, None, None, None, None
 
 

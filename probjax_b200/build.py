@@ -22,6 +22,7 @@ SOURCES = [
     "pjx_api.cu",
     "attn_fwd_generic.cu",
     "attn_bwd_generic.cu",
+    "attn_bwd_sm100.cu",
     "attn_fwd_sm100.cu",
     "attn_decode.cu",
     "gemm_sm100.cu",

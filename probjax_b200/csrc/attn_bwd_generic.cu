@@ -25,24 +25,6 @@ namespace {
 constexpr int T = 32;     // tile edge (queries and keys)
 constexpr int NT = 256;   // threads per CTA
 
-struct BwdParams {
-  const void* q;
-  const void* k;
-  const void* v;
-  const void* o;
-  const void* d_o;
-  const float* lse;     // [B, Hq, Lq] natural log, +inf for rows without keys
-  float* delta;         // [B, Hq, Lq] workspace
-  void* dq;
-  void* dk;
-  void* dv;
-  const int32_t* kv_lengths;
-  const float* bias;
-  int64_t bias_bs, bias_hs;
-  int B, Lq, Lkv, Hq, Hkv, D, Dv;
-  int band_lo, band_hi;  // key j is visible to query i iff i + band_lo <= j <= i + band_hi
-  float sm_scale;
-};
 
 template <typename T_>
 __global__ void bwd_delta_kernel(const BwdParams p) {
@@ -296,6 +278,7 @@ int launch_widths(const BwdParams& p, cudaStream_t stream) {
   bwd_delta_kernel<T_><<<(unsigned)((rows + 7) / 8), 256, 0, stream>>>(p);
   count_launch();
   if ((rc = check_cuda(cudaGetLastError(), "backward delta launch"))) return rc;
+  if (p.use_sm100) return launch_bwd_sm100(p, stream);
   auto kq = bwd_dq_kernel<T_, NCK>;
   if ((rc = set_smem(kq, smem, "cudaFuncSetAttribute(backward dq)"))) return rc;
   kq<<<dim3((p.Lq + T - 1) / T, p.Hq, p.B), NT, smem, stream>>>(p);
@@ -341,8 +324,10 @@ size_t pjx_attn_bwd_workspace_bytes(int B, int Lq, int Hq) {
 int pjx_attn_bwd_band(const void* q, const void* k, const void* v, const void* o, const float* lse, const void* d_o,
                       void* dq, void* dk, void* dv, const int32_t* kv_lengths, const float* bias,
                       int64_t bias_batch_stride, int64_t bias_head_stride, int B, int Lq, int Lkv, int Hq, int Hkv,
-                      int D, int Dv, int dtype, int band_lo, int band_hi, float sm_scale, void* workspace,
-                      size_t workspace_bytes, void* stream) {
+                      int D, int Dv, int dtype, int band_lo, int band_hi, float sm_scale, int impl, void* workspace,
+                      size_t workspace_bytes, int32_t* status, void* stream) {
+  if (impl != PJX_IMPL_AUTO && impl != PJX_IMPL_GENERIC && impl != PJX_IMPL_SM100)
+    return fail(PJX_ERR_BAD_ARG, "impl must be 0 (auto), 1 (generic) or 2 (tcgen05), got %d", impl);
   if (dtype != PJX_F32 && dtype != PJX_BF16 && dtype != PJX_F16)
     return fail(PJX_ERR_BAD_ARG, "dtype must be float32, bfloat16 or float16 (got code %d)", dtype);
   if (B < 0 || Lq < 0 || Lkv < 0 || Hq < 1 || Hkv < 1 || D < 1 || Dv < 1)
@@ -367,12 +352,18 @@ int pjx_attn_bwd_band(const void* q, const void* k, const void* v, const void* o
   p.band_lo = band_lo < PJX_BAND_NO_LOWER ? PJX_BAND_NO_LOWER : (band_lo > PJX_BAND_NO_UPPER ? PJX_BAND_NO_UPPER : band_lo);
   p.band_hi = band_hi > PJX_BAND_NO_UPPER ? PJX_BAND_NO_UPPER : (band_hi < PJX_BAND_NO_LOWER ? PJX_BAND_NO_LOWER : band_hi);
   p.sm_scale = sm_scale;
+  p.dtype = dtype;
+  p.status = status;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   if (Lq == 0) {  // no queries: the key-side gradients are zero
     int rc = check_cuda(cudaMemsetAsync(dk, 0, (size_t)B * Lkv * Hkv * D * dtype_size(dtype), st), "clear dk");
     if (rc) return rc;
     return check_cuda(cudaMemsetAsync(dv, 0, (size_t)B * Lkv * Hkv * Dv * dtype_size(dtype), st), "clear dv");
   }
+  const char* why = nullptr;
+  const bool tc_ok = bwd_sm100_supported(p, &why);
+  if (impl == PJX_IMPL_SM100 && !tc_ok) return fail(PJX_ERR_UNSUPPORTED, "tcgen05 backward: %s", why);
+  p.use_sm100 = impl != PJX_IMPL_GENERIC && tc_ok;
   switch (dtype) {
     case PJX_F32: return launch_dtype<float>(p, st);
     case PJX_BF16: return launch_dtype<__nv_bfloat16>(p, st);
@@ -386,7 +377,7 @@ int pjx_attn_bwd(const void* q, const void* k, const void* v, const void* o, con
                  int Dv, int dtype, int causal, float sm_scale, void* workspace, size_t workspace_bytes, void* stream) {
   return pjx_attn_bwd_band(q, k, v, o, lse, d_o, dq, dk, dv, kv_lengths, bias, bias_batch_stride, bias_head_stride, B,
                            Lq, Lkv, Hq, Hkv, D, Dv, dtype, PJX_BAND_NO_LOWER, causal ? 0 : PJX_BAND_NO_UPPER, sm_scale,
-                           workspace, workspace_bytes, stream);
+                           PJX_IMPL_AUTO, workspace, workspace_bytes, nullptr, stream);
 }
 
 }  // extern "C"

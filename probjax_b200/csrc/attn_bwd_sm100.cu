@@ -1,0 +1,573 @@
+// Flash-attention backward for sm_100a: TMA-staged tiles, tcgen05 MMAs with accumulators in
+// tensor memory.  Two kernels without atomics (the reference splits its backward the same way,
+// probjax/nn/pallas_kernels/kernels/attention.py:1189-1483 `mha_backward_kernel_split_dkdv` and
+// `_split_dq`), both recomputing P = exp(s - lse) from the forward's log-sum-exp:
+//
+//   dQ kernel     one CTA per 128-row query tile of a (batch, query head), walking the KV tiles:
+//                   S = Q.K^T, dP = dO.V^T            (both operands in shared memory)
+//                   dS = P o (dP - delta)              (compute warps, one thread per query row)
+//                   dQ += dS.K                         (dS read from tensor memory, K MN-major)
+//   dK/dV kernel  one CTA per 128-key tile of a (batch, KV head), walking the query tiles of all
+//                 query heads of the group (GQA gradients are summed inside the CTA):
+//                   S^T = K.Q^T, dP^T = V.dO^T
+//                   P^T, dS^T                          (compute warps, one thread per key row)
+//                   dV += P^T.dO,  dK += dS^T.Q       (A from tensor memory, dO / Q MN-major)
+//
+// Transposed scores in the dK/dV kernel put the keys on the tensor-memory lanes, so P^T and dS^T
+// are already laid out as the A operand of the two accumulating products.  P and dS are rounded
+// to the input dtype before those products, as the reference does.  Scaling by sm_scale is
+// applied once, when dQ and dK leave tensor memory.
+//
+// Warps: 0 = TMA producer, 1 = MMA issuer (one lane), 2-5 = compute.  Every barrier wait is
+// bounded; on expiry the CTA drains, frees tensor memory and reports PJX_ERR_DEVICE_TIMEOUT.
+#include "pjx_common.cuh"
+#include "sm100_ptx.cuh"
+
+namespace pjx {
+
+int make_tmap_blhd(CUtensorMap* m, const void* base, int dtype, int B, int L, int H, int Dim, int rows);
+
+namespace {
+
+using namespace sm100;
+
+constexpr int BM = 128;        // query rows per tile
+constexpr int BN = 128;        // keys per tile
+constexpr int NTHREADS = 192;  // 6 warps
+
+__device__ __forceinline__ float ex2_approx(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+template <bool BF16>
+__device__ __forceinline__ uint32_t pack16(float lo, float hi) {
+  if constexpr (BF16) {
+    __nv_bfloat162 t = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&t);
+  } else {
+    __half2 t = __floats2half2_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&t);
+  }
+}
+
+// Rows of `Dh` 16-bit elements leave tensor memory (32 columns at a time), are scaled and
+// written to a [.., rows, heads, Dh] tensor; `dst` points at this thread's row.
+template <int Dh, bool BF16>
+__device__ __forceinline__ void store_row(uint32_t taddr, unsigned char* dst, float scale, bool have_acc, bool row_ok) {
+#pragma unroll
+  for (int c = 0; c < Dh / 32; ++c) {
+    float o[32];
+    if (have_acc) {
+      tmem_ld32f(taddr + c * 32, o);
+      tmem_wait_ld();
+    } else {
+#pragma unroll
+      for (int i = 0; i < 32; ++i) o[i] = 0.f;
+    }
+    if (row_ok) {
+      uint4* d4 = reinterpret_cast<uint4*>(dst + c * 64);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        uint4 w;
+        w.x = pack16<BF16>(o[8 * i + 0] * scale, o[8 * i + 1] * scale);
+        w.y = pack16<BF16>(o[8 * i + 2] * scale, o[8 * i + 3] * scale);
+        w.z = pack16<BF16>(o[8 * i + 4] * scale, o[8 * i + 5] * scale);
+        w.w = pack16<BF16>(o[8 * i + 6] * scale, o[8 * i + 7] * scale);
+        d4[i] = w;
+      }
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// dQ kernel
+// ---------------------------------------------------------------------------------------------
+template <int D>
+struct DqCfg {
+  static constexpr int SUB = D / 64;               // 64-element (128-byte) column blocks of a row
+  static constexpr int TILE = SUB * 128 * 128;     // bytes of a 128-row tile
+  static constexpr int OFF_Q = 0;
+  static constexpr int OFF_DO = TILE;
+  static constexpr int OFF_K = 2 * TILE;           // 2 stages
+  static constexpr int OFF_V = 4 * TILE;           // 2 stages
+  static constexpr int OFF_BAR = 6 * TILE;
+  // barriers: QDO_FULL, K_FULL[2], K_EMPTY[2], V_FULL[2], V_EMPTY[2], SP_FULL, DS_FULL, DQ_FULL
+  static constexpr int N_BAR = 12;
+  static constexpr int SMEM_BYTES = OFF_BAR + N_BAR * 8 + 16 + 1024;
+  static constexpr int TMEM_COLS = 512;            // S 128 | dP 128 | dQ D
+  static_assert(SMEM_BYTES <= 227 * 1024, "shared memory budget");
+};
+
+template <int D, bool BF16>
+__global__ void __launch_bounds__(NTHREADS, 1)
+bwd_dq_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_do,
+                    const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v,
+                    const BwdParams p) {
+  using C = DqCfg<D>;
+  extern __shared__ unsigned char smem_unaligned[];
+  unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_unaligned) + 1023) & ~uintptr_t(1023));
+  const uint32_t sbase = smem_u32(smem);
+  const uint32_t bar0 = sbase + C::OFF_BAR;
+  auto BAR = [&](int i) { return bar0 + 8u * i; };
+  const int QDO_FULL = 0, K_FULL = 1, K_EMPTY = 3, V_FULL = 5, V_EMPTY = 7, SP_FULL = 9, DS_FULL = 10, DQ_FULL = 11;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + C::OFF_BAR + C::N_BAR * 8);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int qt = gridDim.x - 1 - blockIdx.x;  // longest tiles of a causal band first
+  const int h = blockIdx.y, b = blockIdx.z;
+  const int hk = h / (p.Hq / p.Hkv);
+  const int q0 = qt * BM;
+
+  int kv_len = p.Lkv;
+  if (p.kv_lengths) kv_len = max(0, min(kv_len, p.kv_lengths[b]));
+  // KV tiles any row of this query tile can see
+  const int kv_end = max(0, min(kv_len, min(q0 + BM, p.Lq) + p.band_hi));
+  const int kv_begin = max(0, q0 + p.band_lo);
+  const int j_lo = kv_begin / BN;
+  const int n = kv_begin < kv_end ? (kv_end + BN - 1) / BN - j_lo : 0;
+
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < C::N_BAR; ++i) mbar_init(BAR(i), i == DS_FULL ? 128u : 1u);
+    *abort_flag = 0;
+    fence_barrier_init();
+  }
+  if (warp == 0) {
+    tmem_alloc(smem_u32(tmem_slot), C::TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = *tmem_slot;
+  const uint32_t T_S = tmem, T_DP = tmem + BN, T_DQ = tmem + 2 * BN;
+
+  if (warp == 0) {
+    // ---------------------------------------------------------------- TMA producer
+    if (lane == 0 && n > 0) {
+      prefetch_tmap(&tm_q);
+      prefetch_tmap(&tm_do);
+      prefetch_tmap(&tm_k);
+      prefetch_tmap(&tm_v);
+      mbar_arrive_expect_tx(BAR(QDO_FULL), 2 * C::TILE);
+#pragma unroll
+      for (int s = 0; s < C::SUB; ++s) {
+        tma_load_4d(sbase + C::OFF_Q + s * BM * 128, &tm_q, BAR(QDO_FULL), s * 64, h, q0, b);
+        tma_load_4d(sbase + C::OFF_DO + s * BM * 128, &tm_do, BAR(QDO_FULL), s * 64, h, q0, b);
+      }
+      for (int j = 0; j < n; ++j) {
+        const int st = j & 1;
+        if (!mbar_wait(BAR(K_EMPTY + st), ((j >> 1) & 1) ^ 1, abort_flag)) break;
+        mbar_arrive_expect_tx(BAR(K_FULL + st), C::TILE);
+#pragma unroll
+        for (int s = 0; s < C::SUB; ++s)
+          tma_load_4d(sbase + C::OFF_K + st * C::TILE + s * BN * 128, &tm_k, BAR(K_FULL + st), s * 64, hk,
+                      (j_lo + j) * BN, b);
+        if (!mbar_wait(BAR(V_EMPTY + st), ((j >> 1) & 1) ^ 1, abort_flag)) break;
+        mbar_arrive_expect_tx(BAR(V_FULL + st), C::TILE);
+#pragma unroll
+        for (int s = 0; s < C::SUB; ++s)
+          tma_load_4d(sbase + C::OFF_V + st * C::TILE + s * BN * 128, &tm_v, BAR(V_FULL + st), s * 64, hk,
+                      (j_lo + j) * BN, b);
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (lane == 0 && n > 0) {
+      constexpr uint32_t idesc_s = make_idesc(BM, BN, BF16, false, false);
+      constexpr uint32_t idesc_q = make_idesc(BM, D, BF16, false, true);
+      const uint32_t qa = sbase + C::OFF_Q, doa = sbase + C::OFF_DO;
+      bool ok = mbar_wait(BAR(QDO_FULL), 0, abort_flag);
+      for (int j = 0; ok && j < n; ++j) {
+        const int st = j & 1;
+        const uint32_t ka = sbase + C::OFF_K + st * C::TILE, va = sbase + C::OFF_V + st * C::TILE;
+        ok = mbar_wait(BAR(K_FULL + st), (j >> 1) & 1, abort_flag);
+        if (ok) ok = mbar_wait(BAR(V_FULL + st), (j >> 1) & 1, abort_flag);
+        if (!ok) break;
+        tc_fence_after();
+        // S = Q.K^T and dP = dO.V^T; they overwrite dS of the previous step, which the dQ MMAs
+        // issued before them have consumed (MMAs of one issuer execute in order)
+#pragma unroll
+        for (int s = 0; s < C::SUB; ++s)
+#pragma unroll
+          for (int kk = 0; kk < 4; ++kk)
+            mma_ss(T_S, make_smem_desc(qa + s * BM * 128 + kk * 32, 16, 1024),
+                   make_smem_desc(ka + s * BN * 128 + kk * 32, 16, 1024), idesc_s, (s | kk) != 0);
+#pragma unroll
+        for (int s = 0; s < C::SUB; ++s)
+#pragma unroll
+          for (int kk = 0; kk < 4; ++kk)
+            mma_ss(T_DP, make_smem_desc(doa + s * BM * 128 + kk * 32, 16, 1024),
+                   make_smem_desc(va + s * BN * 128 + kk * 32, 16, 1024), idesc_s, (s | kk) != 0);
+        mma_commit(BAR(SP_FULL));
+        mma_commit(BAR(V_EMPTY + st));
+        ok = mbar_wait(BAR(DS_FULL), j & 1, abort_flag);
+        if (!ok) break;
+        tc_fence_after();
+        // dQ += dS.K : A = dS (16-bit pairs over S), B = the K tile read MN-major
+#pragma unroll
+        for (int kk = 0; kk < BN / 16; ++kk)
+          mma_ts(T_DQ, T_S + kk * 8, make_smem_desc(ka + kk * 2048, BN * 128, 1024), idesc_q, (j | kk) != 0);
+        mma_commit(BAR(K_EMPTY + st));
+      }
+      if (ok) mma_commit(BAR(DQ_FULL));
+    }
+  } else {
+    // --------------------------------------------------------------- compute warps
+    const int quarter = warp & 3;
+    const int r_in = quarter * 32 + lane;
+    const int row = q0 + r_in;
+    const bool row_ok = row < p.Lq;
+    const uint32_t lane_sel = static_cast<uint32_t>(quarter * 32) << 16;
+    const float c1 = p.sm_scale * kLog2e;
+    float lse2 = INFINITY, delta = 0.f;
+    if (row_ok) {
+      const int64_t at = ((int64_t)b * p.Hq + h) * p.Lq + row;
+      lse2 = p.lse[at] * kLog2e;  // +inf stays +inf: rows without keys get P = 0
+      delta = p.delta[at];
+    }
+    bool ok = true;
+    for (int j = 0; j < n; ++j) {
+      ok = mbar_wait(BAR(SP_FULL), j & 1, abort_flag);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      tc_fence_after();
+      const int k0 = (j_lo + j) * BN;
+      const bool need_mask = (k0 + BN > kv_len) || (k0 + BN - 1 > q0 + p.band_hi) || (k0 < q0 + BM - 1 + p.band_lo);
+#pragma unroll
+      for (int half = 0; half < 2; ++half) {
+        float s[64], dp[64];
+        tmem_ld32f(T_S + lane_sel + half * 64, s);
+        tmem_ld32f(T_S + lane_sel + half * 64 + 32, s + 32);
+        tmem_ld32f(T_DP + lane_sel + half * 64, dp);
+        tmem_ld32f(T_DP + lane_sel + half * 64 + 32, dp + 32);
+        tmem_wait_ld();
+        uint32_t pk[32];
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          float d0 = ex2_approx(fmaf(s[2 * i], c1, -lse2)) * (dp[2 * i] - delta);
+          float d1 = ex2_approx(fmaf(s[2 * i + 1], c1, -lse2)) * (dp[2 * i + 1] - delta);
+          if (need_mask) {  // selects, not products: masked scores may be anything
+            const int key = k0 + half * 64 + 2 * i;
+            const bool keep0 = key < kv_len && key <= row + p.band_hi && key >= row + p.band_lo;
+            const bool keep1 = key + 1 < kv_len && key + 1 <= row + p.band_hi && key + 1 >= row + p.band_lo;
+            d0 = keep0 ? d0 : 0.f;
+            d1 = keep1 ? d1 : 0.f;
+          }
+          pk[i] = pack16<BF16>(d0, d1);
+        }
+        // dS of this half goes over S columns that were read already (half 0: 0-31, half 1: 32-63)
+        tmem_st32(T_S + lane_sel + half * 32, pk);
+      }
+      tmem_wait_st();
+      tc_fence_before();
+      mbar_arrive(BAR(DS_FULL));
+    }
+    if (ok && q0 < p.Lq) {
+      if (n > 0) {
+        ok = mbar_wait(BAR(DQ_FULL), 0, abort_flag);
+        ok = __all_sync(0xffffffffu, ok);
+      }
+      if (ok) {
+        tc_fence_after();
+        unsigned char* dst = static_cast<unsigned char*>(p.dq) + ((((int64_t)b * p.Lq + row) * p.Hq + h) * D) * 2;
+        store_row<D, BF16>(T_DQ + lane_sel, dst, p.sm_scale, n > 0, row_ok);
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 0) {
+    __syncwarp();
+    tmem_dealloc(tmem, C::TMEM_COLS);
+    if (lane == 0 && *abort_flag && p.status) atomicExch(p.status, (int)PJX_ERR_DEVICE_TIMEOUT);
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// dK/dV kernel
+// ---------------------------------------------------------------------------------------------
+template <int D>
+struct DkvCfg {
+  static constexpr int SUB = D / 64;
+  static constexpr int TILE = SUB * 128 * 128;
+  static constexpr int OFF_K = 0;
+  static constexpr int OFF_V = TILE;
+  static constexpr int OFF_Q = 2 * TILE;            // 2 stages
+  static constexpr int OFF_DO = 4 * TILE;           // 2 stages
+  static constexpr int OFF_ROW = 6 * TILE;          // 2 stages x { float lse2[128]; float delta[128]; }
+  static constexpr int OFF_BAR = OFF_ROW + 2 * 2 * BM * 4;
+  // barriers: KV_FULL, QDO_FULL[2], QDO_EMPTY[2], ROW_FULL[2], SP_FULL, PDS_FULL, ACC_FULL
+  static constexpr int N_BAR = 10;
+  static constexpr int SMEM_BYTES = OFF_BAR + N_BAR * 8 + 16 + 1024;
+  static constexpr int TMEM_COLS = 512;             // S^T 128 | dP^T 128 | dV D | dK D
+  static_assert(SMEM_BYTES <= 227 * 1024, "shared memory budget");
+  static_assert(2 * BM + 2 * D <= 512, "tensor memory has 512 columns");
+};
+
+template <int D, bool BF16>
+__global__ void __launch_bounds__(NTHREADS, 1)
+bwd_dkdv_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_do,
+                      const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v,
+                      const BwdParams p) {
+  using C = DkvCfg<D>;
+  extern __shared__ unsigned char smem_unaligned[];
+  unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_unaligned) + 1023) & ~uintptr_t(1023));
+  const uint32_t sbase = smem_u32(smem);
+  const uint32_t bar0 = sbase + C::OFF_BAR;
+  auto BAR = [&](int i) { return bar0 + 8u * i; };
+  const int KV_FULL = 0, QDO_FULL = 1, QDO_EMPTY = 3, ROW_FULL = 5, SP_FULL = 7, PDS_FULL = 8, ACC_FULL = 9;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + C::OFF_BAR + C::N_BAR * 8);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  float* row_s = reinterpret_cast<float*>(smem + C::OFF_ROW);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int kt = blockIdx.x, hk = blockIdx.y, b = blockIdx.z;
+  const int G = p.Hq / p.Hkv;
+  const int k0 = kt * BN;
+
+  int kv_len = p.Lkv;
+  if (p.kv_lengths) kv_len = max(0, min(kv_len, p.kv_lengths[b]));
+  // query tiles that see a key of this tile: rows in [first key - band_hi, last valid key - band_lo]
+  const int q_begin = max(0, k0 - p.band_hi);
+  const int q_end = min(p.Lq, min(k0 + BN, kv_len) - p.band_lo);
+  const int t_lo = q_begin / BM;
+  const int n_t = (k0 < kv_len && q_begin < q_end) ? (q_end + BM - 1) / BM - t_lo : 0;
+  const int n = n_t * G;  // steps: query heads of the group outer, query tiles inner
+
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < C::N_BAR; ++i)
+      mbar_init(BAR(i), i == PDS_FULL ? 128u : ((i >= ROW_FULL && i < ROW_FULL + 2) ? 32u : 1u));
+    *abort_flag = 0;
+    fence_barrier_init();
+  }
+  if (warp == 0) {
+    tmem_alloc(smem_u32(tmem_slot), C::TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = *tmem_slot;
+  const uint32_t T_S = tmem, T_DP = tmem + BM, T_DV = tmem + 2 * BM, T_DK = tmem + 2 * BM + D;
+
+  if (warp == 0) {
+    // ------------------------------------------- producer: TMA by lane 0, row vectors by the warp
+    if (n > 0) {
+      if (lane == 0) {
+        prefetch_tmap(&tm_q);
+        prefetch_tmap(&tm_do);
+        prefetch_tmap(&tm_k);
+        prefetch_tmap(&tm_v);
+        mbar_arrive_expect_tx(BAR(KV_FULL), 2 * C::TILE);
+#pragma unroll
+        for (int s = 0; s < C::SUB; ++s) {
+          tma_load_4d(sbase + C::OFF_K + s * BN * 128, &tm_k, BAR(KV_FULL), s * 64, hk, k0, b);
+          tma_load_4d(sbase + C::OFF_V + s * BN * 128, &tm_v, BAR(KV_FULL), s * 64, hk, k0, b);
+        }
+      }
+      for (int it = 0; it < n; ++it) {
+        const int st = it & 1;
+        const int h = hk * G + it / n_t;
+        const int q0 = (t_lo + it % n_t) * BM;
+        int ok = 1;
+        if (lane == 0) ok = mbar_wait(BAR(QDO_EMPTY + st), ((it >> 1) & 1) ^ 1, abort_flag) ? 1 : 0;
+        ok = __shfl_sync(0xffffffffu, ok, 0);
+        if (!ok) break;
+        if (lane == 0) {
+          mbar_arrive_expect_tx(BAR(QDO_FULL + st), 2 * C::TILE);
+#pragma unroll
+          for (int s = 0; s < C::SUB; ++s) {
+            tma_load_4d(sbase + C::OFF_Q + st * C::TILE + s * BM * 128, &tm_q, BAR(QDO_FULL + st), s * 64, h, q0, b);
+            tma_load_4d(sbase + C::OFF_DO + st * C::TILE + s * BM * 128, &tm_do, BAR(QDO_FULL + st), s * 64, h, q0, b);
+          }
+        }
+        // per-row log-sum-exp (base 2) and delta of the 128 query rows; rows past Lq get P = 0
+        float* dst = row_s + st * 2 * BM;
+        const int64_t base = ((int64_t)b * p.Hq + h) * p.Lq;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const int r = lane + 32 * i, row = q0 + r;
+          dst[r] = row < p.Lq ? p.lse[base + row] * kLog2e : INFINITY;
+          dst[BM + r] = row < p.Lq ? p.delta[base + row] : 0.f;
+        }
+        mbar_arrive(BAR(ROW_FULL + st));
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (lane == 0 && n > 0) {
+      constexpr uint32_t idesc_s = make_idesc(BN, BM, BF16, false, false);
+      constexpr uint32_t idesc_acc = make_idesc(BN, D, BF16, false, true);
+      const uint32_t ka = sbase + C::OFF_K, va = sbase + C::OFF_V;
+      bool ok = mbar_wait(BAR(KV_FULL), 0, abort_flag);
+      for (int it = 0; ok && it < n; ++it) {
+        const int st = it & 1;
+        const uint32_t qa = sbase + C::OFF_Q + st * C::TILE, doa = sbase + C::OFF_DO + st * C::TILE;
+        ok = mbar_wait(BAR(QDO_FULL + st), (it >> 1) & 1, abort_flag);
+        if (!ok) break;
+        tc_fence_after();
+        // S^T = K.Q^T and dP^T = V.dO^T (keys on the lanes, query rows on the columns)
+#pragma unroll
+        for (int s = 0; s < C::SUB; ++s)
+#pragma unroll
+          for (int kk = 0; kk < 4; ++kk)
+            mma_ss(T_S, make_smem_desc(ka + s * BN * 128 + kk * 32, 16, 1024),
+                   make_smem_desc(qa + s * BM * 128 + kk * 32, 16, 1024), idesc_s, (s | kk) != 0);
+#pragma unroll
+        for (int s = 0; s < C::SUB; ++s)
+#pragma unroll
+          for (int kk = 0; kk < 4; ++kk)
+            mma_ss(T_DP, make_smem_desc(va + s * BN * 128 + kk * 32, 16, 1024),
+                   make_smem_desc(doa + s * BM * 128 + kk * 32, 16, 1024), idesc_s, (s | kk) != 0);
+        mma_commit(BAR(SP_FULL));
+        ok = mbar_wait(BAR(PDS_FULL), it & 1, abort_flag);
+        if (!ok) break;
+        tc_fence_after();
+        // dV += P^T.dO and dK += dS^T.Q : A from tensor memory, dO / Q tiles read MN-major
+#pragma unroll
+        for (int kk = 0; kk < BM / 16; ++kk)
+          mma_ts(T_DV, T_S + kk * 8, make_smem_desc(doa + kk * 2048, BM * 128, 1024), idesc_acc, (it | kk) != 0);
+#pragma unroll
+        for (int kk = 0; kk < BM / 16; ++kk)
+          mma_ts(T_DK, T_DP + kk * 8, make_smem_desc(qa + kk * 2048, BM * 128, 1024), idesc_acc, (it | kk) != 0);
+        mma_commit(BAR(QDO_EMPTY + st));
+      }
+      if (ok) mma_commit(BAR(ACC_FULL));
+    }
+  } else {
+    // --------------------------------------------------------------- compute warps
+    const int quarter = warp & 3;
+    const int r_in = quarter * 32 + lane;
+    const int key = k0 + r_in;
+    const bool key_ok = key < kv_len;
+    const uint32_t lane_sel = static_cast<uint32_t>(quarter * 32) << 16;
+    const float c1 = p.sm_scale * kLog2e;
+    bool ok = true;
+    for (int it = 0; it < n; ++it) {
+      const int st = it & 1;
+      const int q0 = (t_lo + it % n_t) * BM;
+      ok = mbar_wait(BAR(SP_FULL), it & 1, abort_flag);
+      if (ok) ok = mbar_wait(BAR(ROW_FULL + st), (it >> 1) & 1, abort_flag);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      tc_fence_after();
+      const float* lse2_s = row_s + st * 2 * BM;
+      const float* delta_s = lse2_s + BM;
+      // this key row against query rows q0 .. q0+127: visible iff q + band_lo <= key <= q + band_hi
+      const bool need_mask = !key_ok || (key > q0 + p.band_hi) || (key < q0 + BM - 1 + p.band_lo);
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {  // 32 query columns at a time
+        float s[32], dp[32];
+        tmem_ld32f(T_S + lane_sel + c * 32, s);
+        tmem_ld32f(T_DP + lane_sel + c * 32, dp);
+        tmem_wait_ld();
+        uint32_t pkp[16], pkd[16];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const float4 l4 = *reinterpret_cast<const float4*>(lse2_s + c * 32 + 4 * i);
+          const float4 d4 = *reinterpret_cast<const float4*>(delta_s + c * 32 + 4 * i);
+          const float lv[4] = {l4.x, l4.y, l4.z, l4.w}, dv[4] = {d4.x, d4.y, d4.z, d4.w};
+          float pr[4], ds[4];
+#pragma unroll
+          for (int u = 0; u < 4; ++u) {
+            const int col = 4 * i + u;
+            pr[u] = ex2_approx(fmaf(s[col], c1, -lv[u]));
+            ds[u] = pr[u] * (dp[col] - dv[u]);
+            if (need_mask) {  // selects, not products: masked scores may be anything
+              const int qrow = q0 + c * 32 + col;
+              const bool keep = key_ok && key <= qrow + p.band_hi && key >= qrow + p.band_lo;
+              pr[u] = keep ? pr[u] : 0.f;
+              ds[u] = keep ? ds[u] : 0.f;
+            }
+          }
+          pkp[2 * i] = pack16<BF16>(pr[0], pr[1]);
+          pkp[2 * i + 1] = pack16<BF16>(pr[2], pr[3]);
+          pkd[2 * i] = pack16<BF16>(ds[0], ds[1]);
+          pkd[2 * i + 1] = pack16<BF16>(ds[2], ds[3]);
+        }
+        // 16-bit pairs of these 32 columns go over columns that were read already
+        tmem_st16(T_S + lane_sel + c * 16, pkp);
+        tmem_st16(T_DP + lane_sel + c * 16, pkd);
+      }
+      tmem_wait_st();
+      tc_fence_before();
+      mbar_arrive(BAR(PDS_FULL));
+    }
+    if (ok && k0 < p.Lkv) {
+      if (n > 0) {
+        ok = mbar_wait(BAR(ACC_FULL), 0, abort_flag);
+        ok = __all_sync(0xffffffffu, ok);
+      }
+      if (ok) {
+        tc_fence_after();
+        const bool row_ok = key < p.Lkv;
+        const int64_t at = (((int64_t)b * p.Lkv + key) * p.Hkv + hk) * D * 2;
+        store_row<D, BF16>(T_DV + lane_sel, static_cast<unsigned char*>(p.dv) + at, 1.f, n > 0, row_ok);
+        store_row<D, BF16>(T_DK + lane_sel, static_cast<unsigned char*>(p.dk) + at, p.sm_scale, n > 0, row_ok);
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 0) {
+    __syncwarp();
+    tmem_dealloc(tmem, C::TMEM_COLS);
+    if (lane == 0 && *abort_flag && p.status) atomicExch(p.status, (int)PJX_ERR_DEVICE_TIMEOUT);
+  }
+}
+
+template <int D, bool BF16>
+int launch_both(const BwdParams& p, cudaStream_t stream) {
+  CUtensorMap tq, tdo, tk, tv;
+  int rc;
+  if ((rc = make_tmap_blhd(&tq, p.q, p.dtype, p.B, p.Lq, p.Hq, D, BM))) return rc;
+  if ((rc = make_tmap_blhd(&tdo, p.d_o, p.dtype, p.B, p.Lq, p.Hq, D, BM))) return rc;
+  if ((rc = make_tmap_blhd(&tk, p.k, p.dtype, p.B, p.Lkv, p.Hkv, D, BN))) return rc;
+  if ((rc = make_tmap_blhd(&tv, p.v, p.dtype, p.B, p.Lkv, p.Hkv, D, BN))) return rc;
+  auto kq = bwd_dq_sm100_kernel<D, BF16>;
+  if ((rc = check_cuda(cudaFuncSetAttribute(kq, cudaFuncAttributeMaxDynamicSharedMemorySize, DqCfg<D>::SMEM_BYTES),
+                       "cudaFuncSetAttribute(sm100 dq)")))
+    return rc;
+  kq<<<dim3((p.Lq + BM - 1) / BM, p.Hq, p.B), NTHREADS, DqCfg<D>::SMEM_BYTES, stream>>>(tq, tdo, tk, tv, p);
+  count_launch();
+  if ((rc = check_cuda(cudaGetLastError(), "sm100 dq launch"))) return rc;
+  auto kk = bwd_dkdv_sm100_kernel<D, BF16>;
+  if ((rc = check_cuda(cudaFuncSetAttribute(kk, cudaFuncAttributeMaxDynamicSharedMemorySize, DkvCfg<D>::SMEM_BYTES),
+                       "cudaFuncSetAttribute(sm100 dk/dv)")))
+    return rc;
+  kk<<<dim3((p.Lkv + BN - 1) / BN, p.Hkv, p.B), NTHREADS, DkvCfg<D>::SMEM_BYTES, stream>>>(tq, tdo, tk, tv, p);
+  count_launch();
+  return check_cuda(cudaGetLastError(), "sm100 dk/dv launch");
+}
+
+}  // namespace
+
+bool bwd_sm100_supported(const BwdParams& p, const char** why) {
+  const char* w = nullptr;
+  if (p.dtype != PJX_BF16 && p.dtype != PJX_F16) w = "dtype must be bf16 or fp16";
+  else if (!(p.D == p.Dv && (p.D == 64 || p.D == 128))) w = "head dims must be (64,64) or (128,128)";
+  else if (p.bias) w = "a dense bias is taken by the CUDA-core kernels only";
+  else if (p.B < 1 || p.Lq < 1 || p.Lkv < 1) w = "empty problem";
+  else if (p.Hq > 65535 || p.B > 65535) w = "grid too large";
+  else if ((reinterpret_cast<uintptr_t>(p.q) | reinterpret_cast<uintptr_t>(p.k) | reinterpret_cast<uintptr_t>(p.v) |
+            reinterpret_cast<uintptr_t>(p.d_o) | reinterpret_cast<uintptr_t>(p.dq) | reinterpret_cast<uintptr_t>(p.dk) |
+            reinterpret_cast<uintptr_t>(p.dv)) & 15)
+    w = "q, k, v, d_o, dq, dk, dv must be 16-byte aligned";
+  if (why) *why = w;
+  return w == nullptr;
+}
+
+int launch_bwd_sm100(const BwdParams& p, cudaStream_t stream) {
+  const char* why = nullptr;
+  if (!bwd_sm100_supported(p, &why)) return fail(PJX_ERR_UNSUPPORTED, "tcgen05 backward: %s", why);
+  const bool bf16 = p.dtype == PJX_BF16;
+  if (p.D == 128) return bf16 ? launch_both<128, true>(p, stream) : launch_both<128, false>(p, stream);
+  return bf16 ? launch_both<64, true>(p, stream) : launch_both<64, false>(p, stream);
+}
+
+}  // namespace pjx

@@ -91,6 +91,29 @@ struct DecodeParams {
   int32_t* status = nullptr;
 };
 
+// Parameter block of the backward kernels
+struct BwdParams {
+  const void* q;
+  const void* k;
+  const void* v;
+  const void* o;
+  const void* d_o;
+  const float* lse;     // [B, Hq, Lq] natural log, +inf for rows without keys
+  float* delta;         // [B, Hq, Lq] workspace
+  void* dq;
+  void* dk;
+  void* dv;
+  const int32_t* kv_lengths;
+  const float* bias;
+  int64_t bias_bs, bias_hs;
+  int B, Lq, Lkv, Hq, Hkv, D, Dv;
+  int band_lo, band_hi;  // key j is visible to query i iff i + band_lo <= j <= i + band_hi
+  float sm_scale;
+  int dtype = PJX_F32;
+  int32_t* status = nullptr;  // device status word or null
+  bool use_sm100 = false;     // dQ and dK/dV by the tcgen05 kernels instead of the CUDA-core ones
+};
+
 constexpr int kMaxExchangeRanks = 16;
 __host__ __device__ inline size_t exchange_record_floats(int world, int64_t n_rows, int Dv) { return (size_t)world * n_rows * (Dv + 1); }
 inline size_t exchange_buffer_bytes(int world, int64_t n_rows, int Dv) {
@@ -111,6 +134,9 @@ void count_launch(int n = 1);
 int launch_fwd_generic(const FwdParams& p, int dtype, cudaStream_t stream);
 bool fwd_sm100_supported(const FwdParams& p, int dtype, const char** why);
 int launch_fwd_sm100(const FwdParams& p, int dtype, cudaStream_t stream);
+// tcgen05 backward (dQ kernel and dK/dV kernel); expects p.delta filled.
+bool bwd_sm100_supported(const BwdParams& p, const char** why);
+int launch_bwd_sm100(const BwdParams& p, cudaStream_t stream);
 bool decode_fast_supported(const DecodeParams& p, int dtype);
 int launch_decode(const DecodeParams& p, int dtype, cudaStream_t stream);
 int launch_combine_parts(const float* o_parts, const float* lse_parts, int n_parts, int64_t n_rows,

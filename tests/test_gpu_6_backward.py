@@ -97,3 +97,72 @@ def test_zero_length_rows_and_no_grad_paths():
     with pytest.raises(NotImplementedError, match="DenseBias"):
         bias = torch.zeros(1, 2, 9, 9, device=dvc, requires_grad=True)
         pj.flex_attention(qd, kd, vd, bias=pj.DenseBias(bias), sm_scale=0.25)
+
+
+def _grads64(q, k, v, g, keep, sc):
+    q64, k64, v64 = (x.double().requires_grad_(True) for x in (q, k, v))
+    rep = q.shape[2] // k.shape[2]
+    kk, vv = k64.repeat_interleave(rep, dim=2), v64.repeat_interleave(rep, dim=2)
+    s = torch.einsum("bqhd,bkhd->bhqk", q64, kk) * sc
+    s = s.masked_fill(~keep, -math.inf)
+    m = s.amax(-1, keepdim=True)
+    m = torch.where(torch.isfinite(m), m, torch.zeros_like(m))
+    e = torch.exp(s - m)
+    den = e.sum(-1, keepdim=True)
+    out = torch.einsum("bhqk,bkhd->bqhd", e / torch.where(den > 0, den, torch.ones_like(den)), vv)
+    out.backward(g.double())
+    return q64.grad, k64.grad, v64.grad
+
+
+@pytest.mark.parametrize(
+    "dtype,b,lq,lkv,hq,hkv,d,band,lengths",
+    [
+        (torch.bfloat16, 1, 128, 128, 1, 1, 128, (None, None), False),   # one tile, no mask
+        (torch.bfloat16, 2, 256, 384, 4, 2, 128, (None, None), False),   # GQA, several tiles
+        (torch.bfloat16, 2, 300, 300, 4, 1, 128, (None, 0), False),      # causal, ragged tails, MQA
+        (torch.float16, 2, 200, 333, 2, 2, 64, (None, 0), True),         # key lengths
+        (torch.bfloat16, 1, 520, 391, 2, 2, 64, (-100, 30), True),       # window band
+        (torch.bfloat16, 2, 257, 700, 6, 3, 128, (None, 443), False),    # bottom-right causal
+        (torch.float16, 3, 130, 260, 2, 2, 128, (-64, 0), True),         # a sequence without keys
+    ],
+)
+def test_tcgen05_backward_matches_dense_autograd_and_generic(dtype, b, lq, lkv, hq, hkv, d, band, lengths):
+    dvc = dev()
+    q, k, v = randn((b, lq, hq, d), dtype, 11), randn((b, lkv, hkv, d), dtype, 12), randn((b, lkv, hkv, d), dtype, 13)
+    g = randn((b, lq, hq, d), dtype, 14)
+    sc = 1 / math.sqrt(d)
+    lens = None
+    if lengths:
+        lens = torch.tensor([lkv, max(1, lkv // 3), 0][:b], dtype=torch.int32)
+    i, j = torch.arange(lq)[:, None], torch.arange(lkv)[None, :]
+    keep = torch.ones(lq, lkv, dtype=torch.bool)
+    if band[0] is not None:
+        keep &= j >= i + band[0]
+    if band[1] is not None:
+        keep &= j <= i + band[1]
+    keep = keep[None, None].expand(b, 1, lq, lkv).clone()
+    if lens is not None:
+        keep &= (torch.arange(lkv)[None, :] < lens[:, None])[:, None, None, :]
+    qd, kd, vd, gd = (x.to(dvc) for x in (q, k, v, g))
+    o, lse = pj.attention_forward(qd, kd, vd, band=band, kv_lengths=lens, sm_scale=sc, return_lse=True)
+    got = pj.attention_backward(qd, kd, vd, o, lse, gd, band=band, kv_lengths=lens, sm_scale=sc, impl="b200:tcgen05")
+    gen = pj.attention_backward(qd, kd, vd, o, lse, gd, band=band, kv_lengths=lens, sm_scale=sc, impl="b200:generic")
+    pj.check_status()
+    want = _grads64(q, k, v, g, keep, sc)
+    for name, a, c, w in zip(("dq", "dk", "dv"), got, gen, want):
+        assert torch.isfinite(a).all(), name
+        assert _rel(a, w) < 2e-2, (name, _rel(a, w))
+        assert _rel(a, c.double().cpu()) < 2e-2, (name, "vs generic", _rel(a, c.double().cpu()))
+    if lens is not None and b == 3:  # the sequence without keys has zero gradients everywhere
+        assert all((x[2] == 0).all() for x in got)
+
+
+def test_tcgen05_backward_refuses_what_it_does_not_compute():
+    dvc = dev()
+    q = randn((1, 64, 2, 96), torch.bfloat16, 1).to(dvc)
+    o, lse = pj.attention_forward(q, q, q, sm_scale=0.1, return_lse=True)
+    with pytest.raises(NotImplementedError, match="head dims"):
+        pj.attention_backward(q, q, q, o, lse, q, sm_scale=0.1, impl="b200:tcgen05")
+    # auto falls back to the CUDA-core kernels
+    dq, dk, dv = pj.attention_backward(q, q, q, o, lse, q, sm_scale=0.1)
+    assert torch.isfinite(dq).all()
