@@ -329,6 +329,29 @@ def main():
         extras["prefill_causal"] = bench_extra(
             "causal", lambda: pj.attention_forward(q, k, v, causal=True, sm_scale=sc), xs, xw, fl_c / 1e12,
             "TFLOP/s", pk["bf16_tflops"], "tensor", pk["source"])
+        try:  # sliding window of 1024 keys (the band form of the mask): keys j with i-1023 <= j <= i
+            win = 1024
+            rows = torch.arange(C2["S"], dtype=torch.float64)
+            fl_w = 4.0 * C2["B"] * C2["Hq"] * C2["D"] * float(torch.clamp(rows + 1, max=win).sum())
+            extras["prefill_window_1024"] = bench_extra(
+                "window", lambda: pj.attention_forward(q, k, v, band=(-(win - 1), 0), sm_scale=sc), xs, xw, fl_w / 1e12,
+                "TFLOP/s", pk["bf16_tflops"], "tensor", pk["source"])
+        except Exception as e:
+            extras["prefill_window_1024"] = {"error": str(e)[:300]}
+        try:  # backward of the headline shape (tcgen05 dQ and dK/dV kernels + the delta kernel);
+            # FLOPs counted as 2.5 x the forward (five products), although the split design computes seven
+            o_b, lse_b = pj.attention_forward(q, k, v, sm_scale=sc, return_lse=True)
+            g_b = torch.randn_like(o_b)
+            extras["backward"] = bench_extra(
+                "bwd", lambda: pj.attention_backward(q, k, v, o_b, lse_b, g_b, sm_scale=sc), xs, xw,
+                2.5 * flops / 1e12, "TFLOP/s", pk["bf16_tflops"], "tensor", pk["source"])
+            o_c, lse_c = pj.attention_forward(q, k, v, causal=True, sm_scale=sc, return_lse=True)
+            extras["backward_causal"] = bench_extra(
+                "bwd_causal", lambda: pj.attention_backward(q, k, v, o_c, lse_c, g_b, causal=True, sm_scale=sc), xs, xw,
+                2.5 * fl_c / 1e12, "TFLOP/s", pk["bf16_tflops"], "tensor", pk["source"])
+            del o_b, lse_b, g_b, o_c, lse_c
+        except Exception as e:
+            extras["backward"] = {"error": str(e)[:300]}
         try:  # configuration 1: exact fp32 causal MHA, latency-bound (time and parity only)
             c1 = oracle.make_config(1)
             q1, k1, v1 = c1["q"].to(dev), c1["k"].to(dev), c1["v"].to(dev)

@@ -28,21 +28,32 @@ constexpr int NT = 256;   // threads per CTA
 
 template <typename T_>
 __global__ void bwd_delta_kernel(const BwdParams p) {
-  const int64_t row = (int64_t)blockIdx.x * (blockDim.x / 32) + (threadIdx.x >> 5);  // (b, i, h) flattened
+  // one warp per (b, i, h) with i running over the padded length
+  const int64_t row = (int64_t)blockIdx.x * (blockDim.x / 32) + (threadIdx.x >> 5);
   const int lane = threadIdx.x & 31;
-  const int64_t rows = (int64_t)p.B * p.Lq * p.Hq;
+  const int64_t rows = (int64_t)p.B * p.Lq_pad * p.Hq;
   if (row >= rows) return;
-  const T_* o = static_cast<const T_*>(p.o) + row * p.Dv;
-  const T_* d_o = static_cast<const T_*>(p.d_o) + row * p.Dv;
+  const int h = row % p.Hq;
+  const int64_t bi = row / p.Hq;
+  const int i = bi % p.Lq_pad, b = bi / p.Lq_pad;
+  const int64_t at = ((int64_t)b * p.Hq + h) * p.Lq_pad + i;
+  if (i >= p.Lq) {  // padding: rows that contribute nothing
+    if (lane == 0) {
+      p.delta[at] = 0.f;
+      p.lse2[at] = INFINITY;
+    }
+    return;
+  }
+  const int64_t src = ((int64_t)b * p.Lq + i) * p.Hq + h;
+  const T_* o = static_cast<const T_*>(p.o) + src * p.Dv;
+  const T_* d_o = static_cast<const T_*>(p.d_o) + src * p.Dv;
   float acc = 0.f;
   for (int d = lane; d < p.Dv; d += 32) acc = fmaf(Elem<T_>::to_f(o[d]), Elem<T_>::to_f(d_o[d]), acc);
 #pragma unroll
   for (int off = 16; off >= 1; off >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);
   if (lane == 0) {
-    const int h = row % p.Hq;
-    const int64_t bi = row / p.Hq;
-    const int i = bi % p.Lq, b = bi / p.Lq;
-    p.delta[((int64_t)b * p.Hq + h) * p.Lq + i] = acc;
+    p.delta[at] = acc;
+    p.lse2[at] = p.lse[((int64_t)b * p.Hq + h) * p.Lq + i] * kLog2e;  // +inf (row without keys) stays +inf
   }
 }
 
@@ -142,7 +153,7 @@ __global__ void __launch_bounds__(NT) bwd_dq_kernel(const BwdParams p) {
     const int qi = q0 + threadIdx.x;
     const int64_t at = ((int64_t)b * p.Hq + h) * p.Lq + qi;
     t.lse_s[threadIdx.x] = qi < p.Lq ? p.lse[at] : INFINITY;
-    t.delta_s[threadIdx.x] = qi < p.Lq ? p.delta[at] : 0.f;
+    t.delta_s[threadIdx.x] = qi < p.Lq ? p.delta[((int64_t)b * p.Hq + h) * p.Lq_pad + qi] : 0.f;
   }
   float acc[2][NC];
 #pragma unroll
@@ -219,7 +230,7 @@ __global__ void __launch_bounds__(NT) bwd_dkdv_kernel(const BwdParams p) {
           const int qi = q0 + threadIdx.x;
           const int64_t at = ((int64_t)b * p.Hq + h) * p.Lq + qi;
           t.lse_s[threadIdx.x] = qi < p.Lq ? p.lse[at] : INFINITY;
-          t.delta_s[threadIdx.x] = qi < p.Lq ? p.delta[at] : 0.f;
+          t.delta_s[threadIdx.x] = qi < p.Lq ? p.delta[((int64_t)b * p.Hq + h) * p.Lq_pad + qi] : 0.f;
         }
         __syncthreads();
         tile_p_ds(p, t, b, h, q0, k0, kv_len);
@@ -274,7 +285,7 @@ template <typename T_, int NCK, int NCV>
 int launch_widths(const BwdParams& p, cudaStream_t stream) {
   const size_t smem = bwd_smem_bytes(p.D, p.Dv);
   int rc;
-  const int64_t rows = (int64_t)p.B * p.Lq * p.Hq;
+  const int64_t rows = (int64_t)p.B * p.Lq_pad * p.Hq;
   bwd_delta_kernel<T_><<<(unsigned)((rows + 7) / 8), 256, 0, stream>>>(p);
   count_launch();
   if ((rc = check_cuda(cudaGetLastError(), "backward delta launch"))) return rc;
@@ -318,7 +329,8 @@ extern "C" {
 
 size_t pjx_attn_bwd_workspace_bytes(int B, int Lq, int Hq) {
   if (B < 0 || Lq < 0 || Hq < 1) return 0;
-  return ((size_t)B * Hq * Lq * sizeof(float) + 255) / 256 * 256;
+  const size_t lq_pad = ((size_t)Lq + 127) / 128 * 128;  // two float arrays [B, Hq, lq_pad]
+  return 2 * (size_t)B * Hq * lq_pad * sizeof(float);
 }
 
 int pjx_attn_bwd_band(const void* q, const void* k, const void* v, const void* o, const float* lse, const void* d_o,
@@ -345,7 +357,9 @@ int pjx_attn_bwd_band(const void* q, const void* k, const void* v, const void* o
   if (Lq == 0 && Lkv == 0) return PJX_OK;
   BwdParams p;
   p.q = q; p.k = k; p.v = v; p.o = o; p.d_o = d_o; p.lse = lse;
+  p.Lq_pad = (Lq + 127) / 128 * 128;
   p.delta = static_cast<float*>(workspace);
+  p.lse2 = p.delta + (size_t)B * Hq * p.Lq_pad;
   p.dq = dq; p.dk = dk; p.dv = dv;
   p.kv_lengths = kv_lengths; p.bias = bias; p.bias_bs = bias_batch_stride; p.bias_hs = bias_head_stride;
   p.B = B; p.Lq = Lq; p.Lkv = Lkv; p.Hq = Hq; p.Hkv = Hkv; p.D = D; p.Dv = Dv;

@@ -18,8 +18,11 @@
 // to the input dtype before those products, as the reference does.  Scaling by sm_scale is
 // applied once, when dQ and dK leave tensor memory.
 //
-// Warps: 0 = TMA producer, 1 = MMA issuer (one lane), 2-5 = compute.  Every barrier wait is
-// bounded; on expiry the CTA drains, frees tensor memory and reports PJX_ERR_DEVICE_TIMEOUT.
+// Warps: 0 = TMA producer, 1 = MMA issuer (one lane), 2-5 and 6-9 = two compute groups; a group
+// has one thread per tensor-memory lane (query row, or key row in the dK/dV kernel) and takes
+// one half of the 128 score columns, so that every scheduler has two compute warps to
+// interleave.  A group writes its 16-bit results over the first 32 columns of its own half,
+// which it has read already.  Every barrier wait is bounded; on expiry the CTA drains, frees tensor memory and reports PJX_ERR_DEVICE_TIMEOUT.
 #include "pjx_common.cuh"
 #include "sm100_ptx.cuh"
 
@@ -33,7 +36,26 @@ using namespace sm100;
 
 constexpr int BM = 128;        // query rows per tile
 constexpr int BN = 128;        // keys per tile
-constexpr int NTHREADS = 192;  // 6 warps
+constexpr int NTHREADS = 320;  // 10 warps
+constexpr int NCOMPUTE = 256;  // threads of the two compute groups
+
+// Optional phase timeline of one CTA of the dQ kernel (debug builds only, -DPJX_TRACE).
+#ifdef PJX_TRACE
+__device__ long long g_btrace[4][64][8];
+#define PJX_BTRACE(r, j, pt)                                                                     \
+  do {                                                                                           \
+    if (blockIdx.x == gridDim.x / 2 && blockIdx.y == 1 && blockIdx.z == 0 && (j) < 64)           \
+      g_btrace[(r)][(j)][(pt)] = clock64();                                                      \
+  } while (0)
+#define PJX_KTRACE(r, j, pt)                                                                     \
+  do {                                                                                           \
+    if (blockIdx.x == gridDim.x / 2 && blockIdx.y == 1 && blockIdx.z == 0 && (j) < 64)           \
+      g_btrace[2 + (r)][(j)][(pt)] = clock64();                                                  \
+  } while (0)
+#else
+#define PJX_BTRACE(r, j, pt) do {} while (0)
+#define PJX_KTRACE(r, j, pt) do {} while (0)
+#endif
 
 __device__ __forceinline__ float ex2_approx(float x) {
   float y;
@@ -49,6 +71,28 @@ __device__ __forceinline__ uint32_t pack16(float lo, float hi) {
   } else {
     __half2 t = __floats2half2_rn(lo, hi);
     return *reinterpret_cast<uint32_t*>(&t);
+  }
+}
+
+// dS of 32 score columns of one query row: p = exp2(s c1 - lse2), dS = p (dP - delta), packed to
+// 16 bits.  Straight-line over independent elements so that the scheduler can overlap them.
+template <bool BF16>
+__device__ __forceinline__ void ds_row_chunk(const float (&s)[32], const float (&dp)[32], float c1, float neg_lse2,
+                                             float neg_delta, float (&d)[32]) {
+  const float2 c2 = make_float2(c1, c1), nl2 = make_float2(neg_lse2, neg_lse2), nd2 = make_float2(neg_delta, neg_delta);
+#pragma unroll
+  for (int i = 0; i < 16; i += 2) {
+    const float2 x0 = __ffma2_rn(make_float2(s[2 * i], s[2 * i + 1]), c2, nl2);
+    const float2 x1 = __ffma2_rn(make_float2(s[2 * i + 2], s[2 * i + 3]), c2, nl2);
+    const float2 p0 = make_float2(ex2_approx(x0.x), ex2_approx(x0.y));
+    const float2 p1 = make_float2(ex2_approx(x1.x), ex2_approx(x1.y));
+    const float2 e0 = __fadd2_rn(make_float2(dp[2 * i], dp[2 * i + 1]), nd2);
+    const float2 e1 = __fadd2_rn(make_float2(dp[2 * i + 2], dp[2 * i + 3]), nd2);
+    const float2 d0 = __fmul2_rn(p0, e0), d1 = __fmul2_rn(p1, e1);
+    d[2 * i] = d0.x;
+    d[2 * i + 1] = d0.y;
+    d[2 * i + 2] = d1.x;
+    d[2 * i + 3] = d1.y;
   }
 }
 
@@ -130,7 +174,7 @@ bwd_dq_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
   const int n = kv_begin < kv_end ? (kv_end + BN - 1) / BN - j_lo : 0;
 
   if (threadIdx.x == 0) {
-    for (int i = 0; i < C::N_BAR; ++i) mbar_init(BAR(i), i == DS_FULL ? 128u : 1u);
+    for (int i = 0; i < C::N_BAR; ++i) mbar_init(BAR(i), i == DS_FULL ? (uint32_t)NCOMPUTE : 1u);
     *abort_flag = 0;
     fence_barrier_init();
   }
@@ -187,6 +231,7 @@ bwd_dq_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
         if (ok) ok = mbar_wait(BAR(V_FULL + st), (j >> 1) & 1, abort_flag);
         if (!ok) break;
         tc_fence_after();
+        PJX_BTRACE(0, j, 0);
         // S = Q.K^T and dP = dO.V^T; they overwrite dS of the previous step, which the dQ MMAs
         // issued before them have consumed (MMAs of one issuer execute in order)
 #pragma unroll
@@ -203,67 +248,72 @@ bwd_dq_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
                    make_smem_desc(va + s * BN * 128 + kk * 32, 16, 1024), idesc_s, (s | kk) != 0);
         mma_commit(BAR(SP_FULL));
         mma_commit(BAR(V_EMPTY + st));
+        PJX_BTRACE(0, j, 1);
         ok = mbar_wait(BAR(DS_FULL), j & 1, abort_flag);
         if (!ok) break;
         tc_fence_after();
-        // dQ += dS.K : A = dS (16-bit pairs over S), B = the K tile read MN-major
+        PJX_BTRACE(0, j, 2);
+        // dQ += dS.K : A = dS (16-bit pairs, keys 0-63 at S columns 0-31, keys 64-127 at 64-95),
+        // B = the K tile read MN-major
 #pragma unroll
         for (int kk = 0; kk < BN / 16; ++kk)
-          mma_ts(T_DQ, T_S + kk * 8, make_smem_desc(ka + kk * 2048, BN * 128, 1024), idesc_q, (j | kk) != 0);
+          mma_ts(T_DQ, T_S + (kk >> 2) * 64 + (kk & 3) * 8, make_smem_desc(ka + kk * 2048, BN * 128, 1024), idesc_q,
+                 (j | kk) != 0);
         mma_commit(BAR(K_EMPTY + st));
+        PJX_BTRACE(0, j, 3);
       }
       if (ok) mma_commit(BAR(DQ_FULL));
     }
   } else {
     // --------------------------------------------------------------- compute warps
+    const int grp = (warp - 2) >> 2;  // which half of the score columns
     const int quarter = warp & 3;
     const int r_in = quarter * 32 + lane;
     const int row = q0 + r_in;
     const bool row_ok = row < p.Lq;
     const uint32_t lane_sel = static_cast<uint32_t>(quarter * 32) << 16;
     const float c1 = p.sm_scale * kLog2e;
-    float lse2 = INFINITY, delta = 0.f;
-    if (row_ok) {
-      const int64_t at = ((int64_t)b * p.Hq + h) * p.Lq + row;
-      lse2 = p.lse[at] * kLog2e;  // +inf stays +inf: rows without keys get P = 0
-      delta = p.delta[at];
-    }
+    // padded per-row vectors: +inf / 0 for rows past Lq and +inf for rows without keys, so P = 0 there
+    const int64_t at = ((int64_t)b * p.Hq + h) * p.Lq_pad + row;
+    const float lse2 = p.lse2[at], delta = p.delta[at];
+    const uint32_t s_addr = T_S + lane_sel + grp * 64, dp_addr = T_DP + lane_sel + grp * 64;
     bool ok = true;
     for (int j = 0; j < n; ++j) {
+      if (r_in == 64 && grp == 0) PJX_BTRACE(1, j, 0);
       ok = mbar_wait(BAR(SP_FULL), j & 1, abort_flag);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       tc_fence_after();
-      const int k0 = (j_lo + j) * BN;
-      const bool need_mask = (k0 + BN > kv_len) || (k0 + BN - 1 > q0 + p.band_hi) || (k0 < q0 + BM - 1 + p.band_lo);
+      if (r_in == 64 && grp == 0) PJX_BTRACE(1, j, 1);
+      const int k0 = (j_lo + j) * BN + grp * 64;  // first key of this group's columns
+      const bool need_mask = (k0 + 64 > kv_len) || (k0 + 63 > q0 + p.band_hi) || (k0 < q0 + BM - 1 + p.band_lo);
 #pragma unroll
-      for (int half = 0; half < 2; ++half) {
-        float s[64], dp[64];
-        tmem_ld32f(T_S + lane_sel + half * 64, s);
-        tmem_ld32f(T_S + lane_sel + half * 64 + 32, s + 32);
-        tmem_ld32f(T_DP + lane_sel + half * 64, dp);
-        tmem_ld32f(T_DP + lane_sel + half * 64 + 32, dp + 32);
+      for (int c = 0; c < 2; ++c) {
+        float s[32], dp[32], d[32];
+        tmem_ld32f(s_addr + c * 32, s);
+        tmem_ld32f(dp_addr + c * 32, dp);
         tmem_wait_ld();
-        uint32_t pk[32];
+        if (r_in == 64 && grp == 0) PJX_BTRACE(1, j, 2 + 2 * c);
+        ds_row_chunk<BF16>(s, dp, c1, -lse2, -delta, d);
+        if (need_mask) {  // selects, not products: masked scores may be anything
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          float d0 = ex2_approx(fmaf(s[2 * i], c1, -lse2)) * (dp[2 * i] - delta);
-          float d1 = ex2_approx(fmaf(s[2 * i + 1], c1, -lse2)) * (dp[2 * i + 1] - delta);
-          if (need_mask) {  // selects, not products: masked scores may be anything
-            const int key = k0 + half * 64 + 2 * i;
-            const bool keep0 = key < kv_len && key <= row + p.band_hi && key >= row + p.band_lo;
-            const bool keep1 = key + 1 < kv_len && key + 1 <= row + p.band_hi && key + 1 >= row + p.band_lo;
-            d0 = keep0 ? d0 : 0.f;
-            d1 = keep1 ? d1 : 0.f;
+          for (int i = 0; i < 32; ++i) {
+            const int key = k0 + c * 32 + i;
+            const bool keep = key < kv_len && key <= row + p.band_hi && key >= row + p.band_lo;
+            d[i] = keep ? d[i] : 0.f;
           }
-          pk[i] = pack16<BF16>(d0, d1);
         }
-        // dS of this half goes over S columns that were read already (half 0: 0-31, half 1: 32-63)
-        tmem_st32(T_S + lane_sel + half * 32, pk);
+        uint32_t pk[16];
+#pragma unroll
+        for (int i = 0; i < 16; ++i) pk[i] = pack16<BF16>(d[2 * i], d[2 * i + 1]);
+        // over columns of this group's half that were read already (chunk 0: 0-15, chunk 1: 16-31)
+        tmem_st16(s_addr + c * 16, pk);
+        if (r_in == 64 && grp == 0) PJX_BTRACE(1, j, 3 + 2 * c);
       }
       tmem_wait_st();
       tc_fence_before();
       mbar_arrive(BAR(DS_FULL));
+      if (r_in == 64 && grp == 0) PJX_BTRACE(1, j, 6);
     }
     if (ok && q0 < p.Lq) {
       if (n > 0) {
@@ -272,8 +322,9 @@ bwd_dq_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
       }
       if (ok) {
         tc_fence_after();
+        // each group stores one half of the row's D columns
         unsigned char* dst = static_cast<unsigned char*>(p.dq) + ((((int64_t)b * p.Lq + row) * p.Hq + h) * D) * 2;
-        store_row<D, BF16>(T_DQ + lane_sel, dst, p.sm_scale, n > 0, row_ok);
+        store_row<D / 2, BF16>(T_DQ + lane_sel + grp * (D / 2), dst + grp * D, p.sm_scale, n > 0, row_ok);
       }
     }
   }
@@ -300,8 +351,8 @@ struct DkvCfg {
   static constexpr int OFF_DO = 4 * TILE;           // 2 stages
   static constexpr int OFF_ROW = 6 * TILE;          // 2 stages x { float lse2[128]; float delta[128]; }
   static constexpr int OFF_BAR = OFF_ROW + 2 * 2 * BM * 4;
-  // barriers: KV_FULL, QDO_FULL[2], QDO_EMPTY[2], ROW_FULL[2], SP_FULL, PDS_FULL, ACC_FULL
-  static constexpr int N_BAR = 10;
+  // barriers: KV_FULL, QDO_FULL[2], QDO_EMPTY[2], SP_FULL, PDS_FULL, ACC_FULL
+  static constexpr int N_BAR = 8;
   static constexpr int SMEM_BYTES = OFF_BAR + N_BAR * 8 + 16 + 1024;
   static constexpr int TMEM_COLS = 512;             // S^T 128 | dP^T 128 | dV D | dK D
   static_assert(SMEM_BYTES <= 227 * 1024, "shared memory budget");
@@ -319,7 +370,7 @@ bwd_dkdv_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
   const uint32_t sbase = smem_u32(smem);
   const uint32_t bar0 = sbase + C::OFF_BAR;
   auto BAR = [&](int i) { return bar0 + 8u * i; };
-  const int KV_FULL = 0, QDO_FULL = 1, QDO_EMPTY = 3, ROW_FULL = 5, SP_FULL = 7, PDS_FULL = 8, ACC_FULL = 9;
+  const int KV_FULL = 0, QDO_FULL = 1, QDO_EMPTY = 3, SP_FULL = 5, PDS_FULL = 6, ACC_FULL = 7;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + C::OFF_BAR + C::N_BAR * 8);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   float* row_s = reinterpret_cast<float*>(smem + C::OFF_ROW);
@@ -340,7 +391,7 @@ bwd_dkdv_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
 
   if (threadIdx.x == 0) {
     for (int i = 0; i < C::N_BAR; ++i)
-      mbar_init(BAR(i), i == PDS_FULL ? 128u : ((i >= ROW_FULL && i < ROW_FULL + 2) ? 32u : 1u));
+      mbar_init(BAR(i), i == PDS_FULL ? (uint32_t)NCOMPUTE : 1u);
     *abort_flag = 0;
     fence_barrier_init();
   }
@@ -355,46 +406,33 @@ bwd_dkdv_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
   const uint32_t T_S = tmem, T_DP = tmem + BM, T_DV = tmem + 2 * BM, T_DK = tmem + 2 * BM + D;
 
   if (warp == 0) {
-    // ------------------------------------------- producer: TMA by lane 0, row vectors by the warp
-    if (n > 0) {
-      if (lane == 0) {
-        prefetch_tmap(&tm_q);
-        prefetch_tmap(&tm_do);
-        prefetch_tmap(&tm_k);
-        prefetch_tmap(&tm_v);
-        mbar_arrive_expect_tx(BAR(KV_FULL), 2 * C::TILE);
+    // ------------------------------------------------------------------- TMA producer
+    if (lane == 0 && n > 0) {
+      prefetch_tmap(&tm_q);
+      prefetch_tmap(&tm_do);
+      prefetch_tmap(&tm_k);
+      prefetch_tmap(&tm_v);
+      mbar_arrive_expect_tx(BAR(KV_FULL), 2 * C::TILE);
 #pragma unroll
-        for (int s = 0; s < C::SUB; ++s) {
-          tma_load_4d(sbase + C::OFF_K + s * BN * 128, &tm_k, BAR(KV_FULL), s * 64, hk, k0, b);
-          tma_load_4d(sbase + C::OFF_V + s * BN * 128, &tm_v, BAR(KV_FULL), s * 64, hk, k0, b);
-        }
+      for (int s = 0; s < C::SUB; ++s) {
+        tma_load_4d(sbase + C::OFF_K + s * BN * 128, &tm_k, BAR(KV_FULL), s * 64, hk, k0, b);
+        tma_load_4d(sbase + C::OFF_V + s * BN * 128, &tm_v, BAR(KV_FULL), s * 64, hk, k0, b);
       }
       for (int it = 0; it < n; ++it) {
         const int st = it & 1;
         const int h = hk * G + it / n_t;
         const int q0 = (t_lo + it % n_t) * BM;
-        int ok = 1;
-        if (lane == 0) ok = mbar_wait(BAR(QDO_EMPTY + st), ((it >> 1) & 1) ^ 1, abort_flag) ? 1 : 0;
-        ok = __shfl_sync(0xffffffffu, ok, 0);
-        if (!ok) break;
-        if (lane == 0) {
-          mbar_arrive_expect_tx(BAR(QDO_FULL + st), 2 * C::TILE);
+        if (!mbar_wait(BAR(QDO_EMPTY + st), ((it >> 1) & 1) ^ 1, abort_flag)) break;
+        mbar_arrive_expect_tx(BAR(QDO_FULL + st), 2 * C::TILE + 2 * BM * 4);
 #pragma unroll
-          for (int s = 0; s < C::SUB; ++s) {
-            tma_load_4d(sbase + C::OFF_Q + st * C::TILE + s * BM * 128, &tm_q, BAR(QDO_FULL + st), s * 64, h, q0, b);
-            tma_load_4d(sbase + C::OFF_DO + st * C::TILE + s * BM * 128, &tm_do, BAR(QDO_FULL + st), s * 64, h, q0, b);
-          }
+        for (int s = 0; s < C::SUB; ++s) {
+          tma_load_4d(sbase + C::OFF_Q + st * C::TILE + s * BM * 128, &tm_q, BAR(QDO_FULL + st), s * 64, h, q0, b);
+          tma_load_4d(sbase + C::OFF_DO + st * C::TILE + s * BM * 128, &tm_do, BAR(QDO_FULL + st), s * 64, h, q0, b);
         }
-        // per-row log-sum-exp (base 2) and delta of the 128 query rows; rows past Lq get P = 0
-        float* dst = row_s + st * 2 * BM;
-        const int64_t base = ((int64_t)b * p.Hq + h) * p.Lq;
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          const int r = lane + 32 * i, row = q0 + r;
-          dst[r] = row < p.Lq ? p.lse[base + row] * kLog2e : INFINITY;
-          dst[BM + r] = row < p.Lq ? p.delta[base + row] : 0.f;
-        }
-        mbar_arrive(BAR(ROW_FULL + st));
+        // the 128 query rows' log-sum-exp (base 2) and delta out of the padded workspace arrays
+        const int64_t at = ((int64_t)b * p.Hq + h) * p.Lq_pad + q0;
+        bulk_load(sbase + C::OFF_ROW + st * 2 * BM * 4, p.lse2 + at, BM * 4, BAR(QDO_FULL + st));
+        bulk_load(sbase + C::OFF_ROW + st * 2 * BM * 4 + BM * 4, p.delta + at, BM * 4, BAR(QDO_FULL + st));
       }
     }
   } else if (warp == 1) {
@@ -410,6 +448,7 @@ bwd_dkdv_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
         ok = mbar_wait(BAR(QDO_FULL + st), (it >> 1) & 1, abort_flag);
         if (!ok) break;
         tc_fence_after();
+        PJX_KTRACE(0, it, 0);
         // S^T = K.Q^T and dP^T = V.dO^T (keys on the lanes, query rows on the columns)
 #pragma unroll
         for (int s = 0; s < C::SUB; ++s)
@@ -424,78 +463,98 @@ bwd_dkdv_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
             mma_ss(T_DP, make_smem_desc(va + s * BN * 128 + kk * 32, 16, 1024),
                    make_smem_desc(doa + s * BM * 128 + kk * 32, 16, 1024), idesc_s, (s | kk) != 0);
         mma_commit(BAR(SP_FULL));
+        PJX_KTRACE(0, it, 1);
         ok = mbar_wait(BAR(PDS_FULL), it & 1, abort_flag);
         if (!ok) break;
         tc_fence_after();
+        PJX_KTRACE(0, it, 2);
         // dV += P^T.dO and dK += dS^T.Q : A from tensor memory, dO / Q tiles read MN-major
+        // (16-bit pairs of query rows 0-63 sit at columns 0-31 of their region, rows 64-127 at 64-95)
 #pragma unroll
         for (int kk = 0; kk < BM / 16; ++kk)
-          mma_ts(T_DV, T_S + kk * 8, make_smem_desc(doa + kk * 2048, BM * 128, 1024), idesc_acc, (it | kk) != 0);
+          mma_ts(T_DV, T_S + (kk >> 2) * 64 + (kk & 3) * 8, make_smem_desc(doa + kk * 2048, BM * 128, 1024), idesc_acc,
+                 (it | kk) != 0);
 #pragma unroll
         for (int kk = 0; kk < BM / 16; ++kk)
-          mma_ts(T_DK, T_DP + kk * 8, make_smem_desc(qa + kk * 2048, BM * 128, 1024), idesc_acc, (it | kk) != 0);
+          mma_ts(T_DK, T_DP + (kk >> 2) * 64 + (kk & 3) * 8, make_smem_desc(qa + kk * 2048, BM * 128, 1024), idesc_acc,
+                 (it | kk) != 0);
         mma_commit(BAR(QDO_EMPTY + st));
+        PJX_KTRACE(0, it, 3);
       }
       if (ok) mma_commit(BAR(ACC_FULL));
     }
   } else {
     // --------------------------------------------------------------- compute warps
+    const int grp = (warp - 2) >> 2;  // which half of the query columns
     const int quarter = warp & 3;
     const int r_in = quarter * 32 + lane;
     const int key = k0 + r_in;
     const bool key_ok = key < kv_len;
     const uint32_t lane_sel = static_cast<uint32_t>(quarter * 32) << 16;
     const float c1 = p.sm_scale * kLog2e;
+    const float2 c2 = make_float2(c1, c1);
+    const uint32_t s_addr = T_S + lane_sel + grp * 64, dp_addr = T_DP + lane_sel + grp * 64;
     bool ok = true;
     for (int it = 0; it < n; ++it) {
       const int st = it & 1;
-      const int q0 = (t_lo + it % n_t) * BM;
+      const int q0 = (t_lo + it % n_t) * BM + grp * 64;  // first query row of this group's columns
+      if (r_in == 64 && grp == 0) PJX_KTRACE(1, it, 0);
       ok = mbar_wait(BAR(SP_FULL), it & 1, abort_flag);
-      if (ok) ok = mbar_wait(BAR(ROW_FULL + st), (it >> 1) & 1, abort_flag);
+      if (r_in == 64 && grp == 0) PJX_KTRACE(1, it, 1);
+      if (ok) ok = mbar_wait(BAR(QDO_FULL + st), (it >> 1) & 1, abort_flag);  // the row vectors landed with Q and dO
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       tc_fence_after();
-      const float* lse2_s = row_s + st * 2 * BM;
+      if (r_in == 64 && grp == 0) PJX_KTRACE(1, it, 2);
+      const float* lse2_s = row_s + st * 2 * BM + grp * 64;
       const float* delta_s = lse2_s + BM;
-      // this key row against query rows q0 .. q0+127: visible iff q + band_lo <= key <= q + band_hi
-      const bool need_mask = !key_ok || (key > q0 + p.band_hi) || (key < q0 + BM - 1 + p.band_lo);
+      // this key row against query rows q0 .. q0+63: visible iff q + band_lo <= key <= q + band_hi
+      const bool need_mask = !key_ok || (key > q0 + p.band_hi) || (key < q0 + 63 + p.band_lo);
 #pragma unroll
-      for (int c = 0; c < 4; ++c) {  // 32 query columns at a time
+      for (int c = 0; c < 2; ++c) {  // 32 query columns at a time
         float s[32], dp[32];
-        tmem_ld32f(T_S + lane_sel + c * 32, s);
-        tmem_ld32f(T_DP + lane_sel + c * 32, dp);
+        tmem_ld32f(s_addr + c * 32, s);
+        tmem_ld32f(dp_addr + c * 32, dp);
         tmem_wait_ld();
-        uint32_t pkp[16], pkd[16];
+        float pr[32], ds[32];
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
           const float4 l4 = *reinterpret_cast<const float4*>(lse2_s + c * 32 + 4 * i);
           const float4 d4 = *reinterpret_cast<const float4*>(delta_s + c * 32 + 4 * i);
-          const float lv[4] = {l4.x, l4.y, l4.z, l4.w}, dv[4] = {d4.x, d4.y, d4.z, d4.w};
-          float pr[4], ds[4];
-#pragma unroll
-          for (int u = 0; u < 4; ++u) {
-            const int col = 4 * i + u;
-            pr[u] = ex2_approx(fmaf(s[col], c1, -lv[u]));
-            ds[u] = pr[u] * (dp[col] - dv[u]);
-            if (need_mask) {  // selects, not products: masked scores may be anything
-              const int qrow = q0 + c * 32 + col;
-              const bool keep = key_ok && key <= qrow + p.band_hi && key >= qrow + p.band_lo;
-              pr[u] = keep ? pr[u] : 0.f;
-              ds[u] = keep ? ds[u] : 0.f;
-            }
-          }
-          pkp[2 * i] = pack16<BF16>(pr[0], pr[1]);
-          pkp[2 * i + 1] = pack16<BF16>(pr[2], pr[3]);
-          pkd[2 * i] = pack16<BF16>(ds[0], ds[1]);
-          pkd[2 * i + 1] = pack16<BF16>(ds[2], ds[3]);
+          const float2 x0 = __ffma2_rn(make_float2(s[4 * i], s[4 * i + 1]), c2, make_float2(-l4.x, -l4.y));
+          const float2 x1 = __ffma2_rn(make_float2(s[4 * i + 2], s[4 * i + 3]), c2, make_float2(-l4.z, -l4.w));
+          const float2 p0 = make_float2(ex2_approx(x0.x), ex2_approx(x0.y));
+          const float2 p1 = make_float2(ex2_approx(x1.x), ex2_approx(x1.y));
+          const float2 e0 = __fadd2_rn(make_float2(dp[4 * i], dp[4 * i + 1]), make_float2(-d4.x, -d4.y));
+          const float2 e1 = __fadd2_rn(make_float2(dp[4 * i + 2], dp[4 * i + 3]), make_float2(-d4.z, -d4.w));
+          const float2 g0 = __fmul2_rn(p0, e0), g1 = __fmul2_rn(p1, e1);
+          pr[4 * i] = p0.x; pr[4 * i + 1] = p0.y; pr[4 * i + 2] = p1.x; pr[4 * i + 3] = p1.y;
+          ds[4 * i] = g0.x; ds[4 * i + 1] = g0.y; ds[4 * i + 2] = g1.x; ds[4 * i + 3] = g1.y;
         }
-        // 16-bit pairs of these 32 columns go over columns that were read already
-        tmem_st16(T_S + lane_sel + c * 16, pkp);
-        tmem_st16(T_DP + lane_sel + c * 16, pkd);
+        if (need_mask) {  // selects, not products: masked scores may be anything
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            const int qrow = q0 + c * 32 + i;
+            const bool keep = key_ok && key <= qrow + p.band_hi && key >= qrow + p.band_lo;
+            pr[i] = keep ? pr[i] : 0.f;
+            ds[i] = keep ? ds[i] : 0.f;
+          }
+        }
+        uint32_t pkp[16], pkd[16];
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+          pkp[i] = pack16<BF16>(pr[2 * i], pr[2 * i + 1]);
+          pkd[i] = pack16<BF16>(ds[2 * i], ds[2 * i + 1]);
+        }
+        // over columns of this group's half that were read already (chunk 0: 0-15, chunk 1: 16-31)
+        tmem_st16(s_addr + c * 16, pkp);
+        tmem_st16(dp_addr + c * 16, pkd);
+        if (r_in == 64 && grp == 0) PJX_KTRACE(1, it, 3 + c);
       }
       tmem_wait_st();
       tc_fence_before();
       mbar_arrive(BAR(PDS_FULL));
+      if (r_in == 64 && grp == 0) PJX_KTRACE(1, it, 5);
     }
     if (ok && k0 < p.Lkv) {
       if (n > 0) {
@@ -506,8 +565,9 @@ bwd_dkdv_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
         tc_fence_after();
         const bool row_ok = key < p.Lkv;
         const int64_t at = (((int64_t)b * p.Lkv + key) * p.Hkv + hk) * D * 2;
-        store_row<D, BF16>(T_DV + lane_sel, static_cast<unsigned char*>(p.dv) + at, 1.f, n > 0, row_ok);
-        store_row<D, BF16>(T_DK + lane_sel, static_cast<unsigned char*>(p.dk) + at, p.sm_scale, n > 0, row_ok);
+        // group 0 stores the dV row, group 1 the dK row
+        if (grp == 0) store_row<D, BF16>(T_DV + lane_sel, static_cast<unsigned char*>(p.dv) + at, 1.f, n > 0, row_ok);
+        else store_row<D, BF16>(T_DK + lane_sel, static_cast<unsigned char*>(p.dk) + at, p.sm_scale, n > 0, row_ok);
       }
     }
   }
@@ -558,9 +618,16 @@ bool bwd_sm100_supported(const BwdParams& p, const char** why) {
             reinterpret_cast<uintptr_t>(p.d_o) | reinterpret_cast<uintptr_t>(p.dq) | reinterpret_cast<uintptr_t>(p.dk) |
             reinterpret_cast<uintptr_t>(p.dv)) & 15)
     w = "q, k, v, d_o, dq, dk, dv must be 16-byte aligned";
+  else if (reinterpret_cast<uintptr_t>(p.delta) & 15) w = "the workspace must be 16-byte aligned";
   if (why) *why = w;
   return w == nullptr;
 }
+
+#ifdef PJX_TRACE
+extern "C" int pjx_debug_read_bwd_trace(long long* host_out) {
+  return (int)cudaMemcpyFromSymbol(host_out, g_btrace, sizeof(long long) * 4 * 64 * 8);
+}
+#endif
 
 int launch_bwd_sm100(const BwdParams& p, cudaStream_t stream) {
   const char* why = nullptr;

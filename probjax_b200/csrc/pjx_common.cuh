@@ -99,7 +99,9 @@ struct BwdParams {
   const void* o;
   const void* d_o;
   const float* lse;     // [B, Hq, Lq] natural log, +inf for rows without keys
-  float* delta;         // [B, Hq, Lq] workspace
+  float* delta;         // [B, Hq, Lq_pad] workspace: rowsum(o * d_o), 0 in the padding
+  float* lse2;          // [B, Hq, Lq_pad] workspace: lse * log2(e), +inf in the padding
+  int Lq_pad;           // Lq rounded up to a multiple of 128 (row pitch of the two arrays)
   void* dq;
   void* dk;
   void* dv;
