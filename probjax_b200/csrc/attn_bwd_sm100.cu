@@ -22,7 +22,10 @@
 // has one thread per tensor-memory lane (query row, or key row in the dK/dV kernel) and takes
 // one half of the 128 score columns, so that every scheduler has two compute warps to
 // interleave.  A group writes its 16-bit results over the first 32 columns of its own half,
-// which it has read already.  Every barrier wait is bounded; on expiry the CTA drains, frees tensor memory and reports PJX_ERR_DEVICE_TIMEOUT.
+// which it has read already.  The MMA issuer works in half steps: the score products of half A of
+// the next step are issued as soon as half A of this step has been accumulated, so the tensor
+// core works on one half while a compute group works on the other.  Every barrier wait is
+// bounded; on expiry the CTA drains, frees tensor memory and reports PJX_ERR_DEVICE_TIMEOUT.
 #include "pjx_common.cuh"
 #include "sm100_ptx.cuh"
 
@@ -37,7 +40,6 @@ using namespace sm100;
 constexpr int BM = 128;        // query rows per tile
 constexpr int BN = 128;        // keys per tile
 constexpr int NTHREADS = 320;  // 10 warps
-constexpr int NCOMPUTE = 256;  // threads of the two compute groups
 
 // Optional phase timeline of one CTA of the dQ kernel (debug builds only, -DPJX_TRACE).
 #ifdef PJX_TRACE
@@ -137,8 +139,8 @@ struct DqCfg {
   static constexpr int OFF_K = 2 * TILE;           // 2 stages
   static constexpr int OFF_V = 4 * TILE;           // 2 stages
   static constexpr int OFF_BAR = 6 * TILE;
-  // barriers: QDO_FULL, K_FULL[2], K_EMPTY[2], V_FULL[2], V_EMPTY[2], SP_FULL, DS_FULL, DQ_FULL
-  static constexpr int N_BAR = 12;
+  // barriers: QDO_FULL, K_FULL[2], K_EMPTY[2], V_FULL[2], V_EMPTY[2], SP_FULL[2], DS_FULL[2], DQ_FULL
+  static constexpr int N_BAR = 14;
   static constexpr int SMEM_BYTES = OFF_BAR + N_BAR * 8 + 16 + 1024;
   static constexpr int TMEM_COLS = 512;            // S 128 | dP 128 | dQ D
   static_assert(SMEM_BYTES <= 227 * 1024, "shared memory budget");
@@ -155,7 +157,7 @@ bwd_dq_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
   const uint32_t sbase = smem_u32(smem);
   const uint32_t bar0 = sbase + C::OFF_BAR;
   auto BAR = [&](int i) { return bar0 + 8u * i; };
-  const int QDO_FULL = 0, K_FULL = 1, K_EMPTY = 3, V_FULL = 5, V_EMPTY = 7, SP_FULL = 9, DS_FULL = 10, DQ_FULL = 11;
+  const int QDO_FULL = 0, K_FULL = 1, K_EMPTY = 3, V_FULL = 5, V_EMPTY = 7, SP_FULL = 9, DS_FULL = 11, DQ_FULL = 13;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + C::OFF_BAR + C::N_BAR * 8);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
@@ -174,7 +176,7 @@ bwd_dq_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
   const int n = kv_begin < kv_end ? (kv_end + BN - 1) / BN - j_lo : 0;
 
   if (threadIdx.x == 0) {
-    for (int i = 0; i < C::N_BAR; ++i) mbar_init(BAR(i), i == DS_FULL ? (uint32_t)NCOMPUTE : 1u);
+    for (int i = 0; i < C::N_BAR; ++i) mbar_init(BAR(i), (i == DS_FULL || i == DS_FULL + 1) ? 128u : 1u);
     *abort_flag = 0;
     fence_barrier_init();
   }
@@ -220,46 +222,71 @@ bwd_dq_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer
     if (lane == 0 && n > 0) {
-      constexpr uint32_t idesc_s = make_idesc(BM, BN, BF16, false, false);
+      constexpr uint32_t idesc_s = make_idesc(BM, BN / 2, BF16, false, false);
       constexpr uint32_t idesc_q = make_idesc(BM, D, BF16, false, true);
       const uint32_t qa = sbase + C::OFF_Q, doa = sbase + C::OFF_DO;
-      bool ok = mbar_wait(BAR(QDO_FULL), 0, abort_flag);
-      for (int j = 0; ok && j < n; ++j) {
-        const int st = j & 1;
-        const uint32_t ka = sbase + C::OFF_K + st * C::TILE, va = sbase + C::OFF_V + st * C::TILE;
-        ok = mbar_wait(BAR(K_FULL + st), (j >> 1) & 1, abort_flag);
-        if (ok) ok = mbar_wait(BAR(V_FULL + st), (j >> 1) & 1, abort_flag);
-        if (!ok) break;
-        tc_fence_after();
-        PJX_BTRACE(0, j, 0);
-        // S = Q.K^T and dP = dO.V^T; they overwrite dS of the previous step, which the dQ MMAs
-        // issued before them have consumed (MMAs of one issuer execute in order)
+      // S and dP of one half (64 keys) of KV tile j: the B operands start 64 rows into the tiles
+      auto issue_sdp = [&](int half, int j) {
+        const uint32_t ka = sbase + C::OFF_K + (j & 1) * C::TILE + half * 64 * 128;
+        const uint32_t va = sbase + C::OFF_V + (j & 1) * C::TILE + half * 64 * 128;
 #pragma unroll
         for (int s = 0; s < C::SUB; ++s)
 #pragma unroll
           for (int kk = 0; kk < 4; ++kk)
-            mma_ss(T_S, make_smem_desc(qa + s * BM * 128 + kk * 32, 16, 1024),
+            mma_ss(T_S + half * 64, make_smem_desc(qa + s * BM * 128 + kk * 32, 16, 1024),
                    make_smem_desc(ka + s * BN * 128 + kk * 32, 16, 1024), idesc_s, (s | kk) != 0);
 #pragma unroll
         for (int s = 0; s < C::SUB; ++s)
 #pragma unroll
           for (int kk = 0; kk < 4; ++kk)
-            mma_ss(T_DP, make_smem_desc(doa + s * BM * 128 + kk * 32, 16, 1024),
+            mma_ss(T_DP + half * 64, make_smem_desc(doa + s * BM * 128 + kk * 32, 16, 1024),
                    make_smem_desc(va + s * BN * 128 + kk * 32, 16, 1024), idesc_s, (s | kk) != 0);
-        mma_commit(BAR(SP_FULL));
-        mma_commit(BAR(V_EMPTY + st));
-        PJX_BTRACE(0, j, 1);
-        ok = mbar_wait(BAR(DS_FULL), j & 1, abort_flag);
+        mma_commit(BAR(SP_FULL + half));
+      };
+      // dQ += dS.K over one half: A = dS (16-bit pairs at the first 32 columns of the half of S),
+      // B = the K tile read MN-major
+      auto issue_acc = [&](int half, int j) {
+        const uint32_t ka = sbase + C::OFF_K + (j & 1) * C::TILE;
+#pragma unroll
+        for (int kk = 0; kk < 4; ++kk)
+          mma_ts(T_DQ, T_S + half * 64 + kk * 8, make_smem_desc(ka + (half * 4 + kk) * 2048, BN * 128, 1024), idesc_q,
+                 (j | half | kk) != 0);
+      };
+      bool ok = mbar_wait(BAR(QDO_FULL), 0, abort_flag);
+      if (ok) ok = mbar_wait(BAR(K_FULL), 0, abort_flag);
+      if (ok) ok = mbar_wait(BAR(V_FULL), 0, abort_flag);
+      if (ok) {
+        tc_fence_after();
+        issue_sdp(0, 0);
+        issue_sdp(1, 0);
+        mma_commit(BAR(V_EMPTY));
+      }
+      for (int j = 0; ok && j < n; ++j) {
+        const int st = j & 1;
+        const bool next = j + 1 < n;
+        PJX_BTRACE(0, j, 0);
+        ok = mbar_wait(BAR(DS_FULL + 0), j & 1, abort_flag);
         if (!ok) break;
         tc_fence_after();
+        PJX_BTRACE(0, j, 1);
+        issue_acc(0, j);
+        if (next) {
+          ok = mbar_wait(BAR(K_FULL + (st ^ 1)), ((j + 1) >> 1) & 1, abort_flag);
+          if (ok) ok = mbar_wait(BAR(V_FULL + (st ^ 1)), ((j + 1) >> 1) & 1, abort_flag);
+          if (!ok) break;
+          tc_fence_after();
+          issue_sdp(0, j + 1);  // over dS of half 0, which the MMAs just issued consume first
+        }
         PJX_BTRACE(0, j, 2);
-        // dQ += dS.K : A = dS (16-bit pairs, keys 0-63 at S columns 0-31, keys 64-127 at 64-95),
-        // B = the K tile read MN-major
-#pragma unroll
-        for (int kk = 0; kk < BN / 16; ++kk)
-          mma_ts(T_DQ, T_S + (kk >> 2) * 64 + (kk & 3) * 8, make_smem_desc(ka + kk * 2048, BN * 128, 1024), idesc_q,
-                 (j | kk) != 0);
+        ok = mbar_wait(BAR(DS_FULL + 1), j & 1, abort_flag);
+        if (!ok) break;
+        tc_fence_after();
+        issue_acc(1, j);
         mma_commit(BAR(K_EMPTY + st));
+        if (next) {
+          issue_sdp(1, j + 1);
+          mma_commit(BAR(V_EMPTY + (st ^ 1)));
+        }
         PJX_BTRACE(0, j, 3);
       }
       if (ok) mma_commit(BAR(DQ_FULL));
@@ -280,7 +307,7 @@ bwd_dq_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
     bool ok = true;
     for (int j = 0; j < n; ++j) {
       if (r_in == 64 && grp == 0) PJX_BTRACE(1, j, 0);
-      ok = mbar_wait(BAR(SP_FULL), j & 1, abort_flag);
+      ok = mbar_wait(BAR(SP_FULL + grp), j & 1, abort_flag);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       tc_fence_after();
@@ -312,7 +339,7 @@ bwd_dq_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
       }
       tmem_wait_st();
       tc_fence_before();
-      mbar_arrive(BAR(DS_FULL));
+      mbar_arrive(BAR(DS_FULL + grp));
       if (r_in == 64 && grp == 0) PJX_BTRACE(1, j, 6);
     }
     if (ok && q0 < p.Lq) {
@@ -351,8 +378,8 @@ struct DkvCfg {
   static constexpr int OFF_DO = 4 * TILE;           // 2 stages
   static constexpr int OFF_ROW = 6 * TILE;          // 2 stages x { float lse2[128]; float delta[128]; }
   static constexpr int OFF_BAR = OFF_ROW + 2 * 2 * BM * 4;
-  // barriers: KV_FULL, QDO_FULL[2], QDO_EMPTY[2], SP_FULL, PDS_FULL, ACC_FULL
-  static constexpr int N_BAR = 8;
+  // barriers: KV_FULL, QDO_FULL[2], QDO_EMPTY[2], SP_FULL[2], PDS_FULL[2], ACC_FULL
+  static constexpr int N_BAR = 10;
   static constexpr int SMEM_BYTES = OFF_BAR + N_BAR * 8 + 16 + 1024;
   static constexpr int TMEM_COLS = 512;             // S^T 128 | dP^T 128 | dV D | dK D
   static_assert(SMEM_BYTES <= 227 * 1024, "shared memory budget");
@@ -370,7 +397,7 @@ bwd_dkdv_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
   const uint32_t sbase = smem_u32(smem);
   const uint32_t bar0 = sbase + C::OFF_BAR;
   auto BAR = [&](int i) { return bar0 + 8u * i; };
-  const int KV_FULL = 0, QDO_FULL = 1, QDO_EMPTY = 3, SP_FULL = 5, PDS_FULL = 6, ACC_FULL = 7;
+  const int KV_FULL = 0, QDO_FULL = 1, QDO_EMPTY = 3, SP_FULL = 5, PDS_FULL = 7, ACC_FULL = 9;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + C::OFF_BAR + C::N_BAR * 8);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   float* row_s = reinterpret_cast<float*>(smem + C::OFF_ROW);
@@ -391,7 +418,7 @@ bwd_dkdv_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
 
   if (threadIdx.x == 0) {
     for (int i = 0; i < C::N_BAR; ++i)
-      mbar_init(BAR(i), i == PDS_FULL ? (uint32_t)NCOMPUTE : 1u);
+      mbar_init(BAR(i), (i == PDS_FULL || i == PDS_FULL + 1) ? 128u : 1u);
     *abort_flag = 0;
     fence_barrier_init();
   }
@@ -438,47 +465,70 @@ bwd_dkdv_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer
     if (lane == 0 && n > 0) {
-      constexpr uint32_t idesc_s = make_idesc(BN, BM, BF16, false, false);
+      constexpr uint32_t idesc_s = make_idesc(BN, BM / 2, BF16, false, false);
       constexpr uint32_t idesc_acc = make_idesc(BN, D, BF16, false, true);
       const uint32_t ka = sbase + C::OFF_K, va = sbase + C::OFF_V;
-      bool ok = mbar_wait(BAR(KV_FULL), 0, abort_flag);
-      for (int it = 0; ok && it < n; ++it) {
-        const int st = it & 1;
-        const uint32_t qa = sbase + C::OFF_Q + st * C::TILE, doa = sbase + C::OFF_DO + st * C::TILE;
-        ok = mbar_wait(BAR(QDO_FULL + st), (it >> 1) & 1, abort_flag);
-        if (!ok) break;
-        tc_fence_after();
-        PJX_KTRACE(0, it, 0);
-        // S^T = K.Q^T and dP^T = V.dO^T (keys on the lanes, query rows on the columns)
+      // S^T and dP^T of one half (64 query rows) of step `it`: keys on the lanes, query rows on
+      // the columns; the B operands start 64 rows into the Q / dO tiles
+      auto issue_sdp = [&](int half, int it) {
+        const uint32_t qa = sbase + C::OFF_Q + (it & 1) * C::TILE + half * 64 * 128;
+        const uint32_t doa = sbase + C::OFF_DO + (it & 1) * C::TILE + half * 64 * 128;
 #pragma unroll
         for (int s = 0; s < C::SUB; ++s)
 #pragma unroll
           for (int kk = 0; kk < 4; ++kk)
-            mma_ss(T_S, make_smem_desc(ka + s * BN * 128 + kk * 32, 16, 1024),
+            mma_ss(T_S + half * 64, make_smem_desc(ka + s * BN * 128 + kk * 32, 16, 1024),
                    make_smem_desc(qa + s * BM * 128 + kk * 32, 16, 1024), idesc_s, (s | kk) != 0);
 #pragma unroll
         for (int s = 0; s < C::SUB; ++s)
 #pragma unroll
           for (int kk = 0; kk < 4; ++kk)
-            mma_ss(T_DP, make_smem_desc(va + s * BN * 128 + kk * 32, 16, 1024),
+            mma_ss(T_DP + half * 64, make_smem_desc(va + s * BN * 128 + kk * 32, 16, 1024),
                    make_smem_desc(doa + s * BM * 128 + kk * 32, 16, 1024), idesc_s, (s | kk) != 0);
-        mma_commit(BAR(SP_FULL));
-        PJX_KTRACE(0, it, 1);
-        ok = mbar_wait(BAR(PDS_FULL), it & 1, abort_flag);
+        mma_commit(BAR(SP_FULL + half));
+      };
+      // dV += P^T.dO and dK += dS^T.Q over one half: A from tensor memory (16-bit pairs at the
+      // first 32 columns of the half), dO / Q tiles read MN-major
+      auto issue_acc = [&](int half, int it) {
+        const uint32_t qa = sbase + C::OFF_Q + (it & 1) * C::TILE, doa = sbase + C::OFF_DO + (it & 1) * C::TILE;
+#pragma unroll
+        for (int kk = 0; kk < 4; ++kk)
+          mma_ts(T_DV, T_S + half * 64 + kk * 8, make_smem_desc(doa + (half * 4 + kk) * 2048, BM * 128, 1024), idesc_acc,
+                 (it | half | kk) != 0);
+#pragma unroll
+        for (int kk = 0; kk < 4; ++kk)
+          mma_ts(T_DK, T_DP + half * 64 + kk * 8, make_smem_desc(qa + (half * 4 + kk) * 2048, BM * 128, 1024), idesc_acc,
+                 (it | half | kk) != 0);
+      };
+      bool ok = mbar_wait(BAR(KV_FULL), 0, abort_flag);
+      if (ok) ok = mbar_wait(BAR(QDO_FULL), 0, abort_flag);
+      if (ok) {
+        tc_fence_after();
+        issue_sdp(0, 0);
+        issue_sdp(1, 0);
+      }
+      for (int it = 0; ok && it < n; ++it) {
+        const int st = it & 1;
+        const bool next = it + 1 < n;
+        PJX_KTRACE(0, it, 0);
+        ok = mbar_wait(BAR(PDS_FULL + 0), it & 1, abort_flag);
         if (!ok) break;
         tc_fence_after();
+        PJX_KTRACE(0, it, 1);
+        issue_acc(0, it);
+        if (next) {
+          ok = mbar_wait(BAR(QDO_FULL + (st ^ 1)), ((it + 1) >> 1) & 1, abort_flag);
+          if (!ok) break;
+          tc_fence_after();
+          issue_sdp(0, it + 1);  // over P^T / dS^T of half 0, which the MMAs just issued consume first
+        }
         PJX_KTRACE(0, it, 2);
-        // dV += P^T.dO and dK += dS^T.Q : A from tensor memory, dO / Q tiles read MN-major
-        // (16-bit pairs of query rows 0-63 sit at columns 0-31 of their region, rows 64-127 at 64-95)
-#pragma unroll
-        for (int kk = 0; kk < BM / 16; ++kk)
-          mma_ts(T_DV, T_S + (kk >> 2) * 64 + (kk & 3) * 8, make_smem_desc(doa + kk * 2048, BM * 128, 1024), idesc_acc,
-                 (it | kk) != 0);
-#pragma unroll
-        for (int kk = 0; kk < BM / 16; ++kk)
-          mma_ts(T_DK, T_DP + (kk >> 2) * 64 + (kk & 3) * 8, make_smem_desc(qa + kk * 2048, BM * 128, 1024), idesc_acc,
-                 (it | kk) != 0);
+        ok = mbar_wait(BAR(PDS_FULL + 1), it & 1, abort_flag);
+        if (!ok) break;
+        tc_fence_after();
+        issue_acc(1, it);
         mma_commit(BAR(QDO_EMPTY + st));
+        if (next) issue_sdp(1, it + 1);
         PJX_KTRACE(0, it, 3);
       }
       if (ok) mma_commit(BAR(ACC_FULL));
@@ -499,7 +549,7 @@ bwd_dkdv_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
       const int st = it & 1;
       const int q0 = (t_lo + it % n_t) * BM + grp * 64;  // first query row of this group's columns
       if (r_in == 64 && grp == 0) PJX_KTRACE(1, it, 0);
-      ok = mbar_wait(BAR(SP_FULL), it & 1, abort_flag);
+      ok = mbar_wait(BAR(SP_FULL + grp), it & 1, abort_flag);
       if (r_in == 64 && grp == 0) PJX_KTRACE(1, it, 1);
       if (ok) ok = mbar_wait(BAR(QDO_FULL + st), (it >> 1) & 1, abort_flag);  // the row vectors landed with Q and dO
       ok = __all_sync(0xffffffffu, ok);
@@ -553,7 +603,7 @@ bwd_dkdv_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
       }
       tmem_wait_st();
       tc_fence_before();
-      mbar_arrive(BAR(PDS_FULL));
+      mbar_arrive(BAR(PDS_FULL + grp));
       if (r_in == 64 && grp == 0) PJX_KTRACE(1, it, 5);
     }
     if (ok && k0 < p.Lkv) {
