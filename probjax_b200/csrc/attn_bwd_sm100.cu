@@ -46,12 +46,12 @@ constexpr int NTHREADS = 320;  // 10 warps
 __device__ long long g_btrace[4][64][8];
 #define PJX_BTRACE(r, j, pt)                                                                     \
   do {                                                                                           \
-    if (blockIdx.x == gridDim.x / 2 && blockIdx.y == 1 && blockIdx.z == 0 && (j) < 64)           \
+    if (blockIdx.x == gridDim.x / 2 && (j) < 64)                                                 \
       g_btrace[(r)][(j)][(pt)] = clock64();                                                      \
   } while (0)
 #define PJX_KTRACE(r, j, pt)                                                                     \
   do {                                                                                           \
-    if (blockIdx.x == gridDim.x / 2 && blockIdx.y == 1 && blockIdx.z == 0 && (j) < 64)           \
+    if (blockIdx.x == gridDim.x / 2 && (j) < 64)                                                 \
       g_btrace[2 + (r)][(j)][(pt)] = clock64();                                                  \
   } while (0)
 #else
@@ -74,6 +74,18 @@ __device__ __forceinline__ uint32_t pack16(float lo, float hi) {
     __half2 t = __floats2half2_rn(lo, hi);
     return *reinterpret_cast<uint32_t*>(&t);
   }
+}
+
+// Work order of a 1-D grid over (tile, pair) with `n_tiles` tiles per pair and `n_pairs` pairs
+// (a pair is a (batch, head)): pairs are taken in blocks of `order_w`; inside a block the tile
+// index is the slow axis, so that under a causal band the long CTAs of a block start first
+// (callers number the tiles heaviest-first) while the CTAs in flight share few K/V heads.
+__device__ __forceinline__ void work_item(int id, int n_tiles, int n_pairs, int order_w, int& tile, int& pair) {
+  const int blk = id / (order_w * n_tiles);
+  const int rem = id - blk * (order_w * n_tiles);
+  const int wc = min(order_w, n_pairs - blk * order_w);
+  tile = rem / wc;
+  pair = blk * order_w + rem % wc;
 }
 
 // dS of 32 score columns of one query row: p = exp2(s c1 - lse2), dS = p (dP - delta), packed to
@@ -150,7 +162,7 @@ template <int D, bool BF16>
 __global__ void __launch_bounds__(NTHREADS, 1)
 bwd_dq_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_do,
                     const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v,
-                    const BwdParams p) {
+                    const BwdParams p, const int order_w) {
   using C = DqCfg<D>;
   extern __shared__ unsigned char smem_unaligned[];
   unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_unaligned) + 1023) & ~uintptr_t(1023));
@@ -162,8 +174,11 @@ bwd_dq_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int qt = gridDim.x - 1 - blockIdx.x;  // longest tiles of a causal band first
-  const int h = blockIdx.y, b = blockIdx.z;
+  const int n_qt = (p.Lq + BM - 1) / BM;
+  int tile, pair;
+  work_item(blockIdx.x, n_qt, p.Hq * p.B, order_w, tile, pair);
+  const int qt = n_qt - 1 - tile;  // the last query tiles see the most keys under a causal band
+  const int h = pair % p.Hq, b = pair / p.Hq;
   const int hk = h / (p.Hq / p.Hkv);
   const int q0 = qt * BM;
 
@@ -390,7 +405,7 @@ template <int D, bool BF16>
 __global__ void __launch_bounds__(NTHREADS, 1)
 bwd_dkdv_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_do,
                       const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v,
-                      const BwdParams p) {
+                      const BwdParams p, const int order_w) {
   using C = DkvCfg<D>;
   extern __shared__ unsigned char smem_unaligned[];
   unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_unaligned) + 1023) & ~uintptr_t(1023));
@@ -403,7 +418,9 @@ bwd_dkdv_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
   float* row_s = reinterpret_cast<float*>(smem + C::OFF_ROW);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int kt = blockIdx.x, hk = blockIdx.y, b = blockIdx.z;
+  int kt, pair;  // the first key tiles are seen by the most queries under a causal band
+  work_item(blockIdx.x, (p.Lkv + BN - 1) / BN, p.Hkv * p.B, order_w, kt, pair);
+  const int hk = pair % p.Hkv, b = pair / p.Hkv;
   const int G = p.Hq / p.Hkv;
   const int k0 = kt * BN;
 
@@ -643,14 +660,18 @@ int launch_both(const BwdParams& p, cudaStream_t stream) {
   if ((rc = check_cuda(cudaFuncSetAttribute(kq, cudaFuncAttributeMaxDynamicSharedMemorySize, DqCfg<D>::SMEM_BYTES),
                        "cudaFuncSetAttribute(sm100 dq)")))
     return rc;
-  kq<<<dim3((p.Lq + BM - 1) / BM, p.Hq, p.B), NTHREADS, DqCfg<D>::SMEM_BYTES, stream>>>(tq, tdo, tk, tv, p);
+  // triangular work (an upper bound on the keys only): heavy-first order in blocks of 16 pairs
+  const int order_w = (p.band_hi < PJX_BAND_NO_UPPER && p.band_lo == PJX_BAND_NO_LOWER) ? 16 : 1;
+  const int64_t n_dq = (int64_t)((p.Lq + BM - 1) / BM) * p.Hq * p.B;
+  kq<<<dim3((unsigned)n_dq), NTHREADS, DqCfg<D>::SMEM_BYTES, stream>>>(tq, tdo, tk, tv, p, order_w);
   count_launch();
   if ((rc = check_cuda(cudaGetLastError(), "sm100 dq launch"))) return rc;
   auto kk = bwd_dkdv_sm100_kernel<D, BF16>;
   if ((rc = check_cuda(cudaFuncSetAttribute(kk, cudaFuncAttributeMaxDynamicSharedMemorySize, DkvCfg<D>::SMEM_BYTES),
                        "cudaFuncSetAttribute(sm100 dk/dv)")))
     return rc;
-  kk<<<dim3((p.Lkv + BN - 1) / BN, p.Hkv, p.B), NTHREADS, DkvCfg<D>::SMEM_BYTES, stream>>>(tq, tdo, tk, tv, p);
+  const int64_t n_dkv = (int64_t)((p.Lkv + BN - 1) / BN) * p.Hkv * p.B;
+  kk<<<dim3((unsigned)n_dkv), NTHREADS, DkvCfg<D>::SMEM_BYTES, stream>>>(tq, tdo, tk, tv, p, order_w);
   count_launch();
   return check_cuda(cudaGetLastError(), "sm100 dk/dv launch");
 }
@@ -663,7 +684,9 @@ bool bwd_sm100_supported(const BwdParams& p, const char** why) {
   else if (!(p.D == p.Dv && (p.D == 64 || p.D == 128))) w = "head dims must be (64,64) or (128,128)";
   else if (p.bias) w = "a dense bias is taken by the CUDA-core kernels only";
   else if (p.B < 1 || p.Lq < 1 || p.Lkv < 1) w = "empty problem";
-  else if (p.Hq > 65535 || p.B > 65535) w = "grid too large";
+  else if ((int64_t)((p.Lq + BM - 1) / BM) * p.Hq * p.B > 0x7fffffffLL ||
+           (int64_t)((p.Lkv + BN - 1) / BN) * p.Hkv * p.B > 0x7fffffffLL)
+    w = "grid too large";
   else if ((reinterpret_cast<uintptr_t>(p.q) | reinterpret_cast<uintptr_t>(p.k) | reinterpret_cast<uintptr_t>(p.v) |
             reinterpret_cast<uintptr_t>(p.d_o) | reinterpret_cast<uintptr_t>(p.dq) | reinterpret_cast<uintptr_t>(p.dk) |
             reinterpret_cast<uintptr_t>(p.dv)) & 15)
