@@ -234,6 +234,8 @@ def main():
     ap.add_argument("--batch", type=int, default=C2["B"], help="batch rows of the headline workload (profiling captures use a smaller one)")
     ap.add_argument("--skip-e2e", action="store_true", help="do not time the host-buffer path")
     ap.add_argument("--only-decode", action="store_true", help="time only the decode configuration (profiling captures)")
+    ap.add_argument("--only-backward", action="store_true",
+                    help="time only the backward of the headline shape on --batch rows (profiling captures)")
     ap.add_argument("--kernel", default=None, choices=[None, "b200:generic", "b200:tcgen05"],
                     help="force one forward kernel for the headline (default: the library's own choice)")
     args = ap.parse_args()
@@ -265,6 +267,9 @@ def main():
 
     if args.only_decode:
         only_decode(args, dev, pk)
+        return
+    if args.only_backward:
+        only_backward(args, dev, pk)
         return
 
     # ---------------------------------------------------------------- headline
@@ -432,6 +437,24 @@ def only_decode(args, dev, pk):
     res = bench_extra("decode", lambda: pj.decode_forward(q4, k4, v4, kv_lengths=l4, sm_scale=c4["sm_scale"], return_lse=True),
                       args.steps, args.warmup, by4 / 1e9, "GB/s", pk["hbm_gbs"], "hbm", pk["source"])
     res["config"] = {"workload": f"GQA split-KV decode bf16 B{args.batch} Hq32 Hkv8 D128, 32768 keys each"}
+    print(json.dumps(res), flush=True)
+
+
+def only_backward(args, dev, pk):
+    """Backward of the headline shape on `--batch` batch rows, nothing else: the command
+    profiling captures of the dQ and dK/dV kernels run."""
+    import oracle
+    import probjax_b200 as pj
+
+    c = oracle.make_config(2, B=args.batch)
+    q, k, v = c["q"].to(dev), c["k"].to(dev), c["v"].to(dev)
+    o, lse = pj.attention_forward(q, k, v, sm_scale=c["sm_scale"], return_lse=True)
+    g = torch.randn_like(o)
+    fl = 2.5 * prefill_flops(args.batch, C2["Hq"], C2["S"], C2["S"], C2["D"], C2["D"], False)
+    res = bench_extra("backward", lambda: pj.attention_backward(q, k, v, o, lse, g, sm_scale=c["sm_scale"]), args.steps,
+                      args.warmup, fl / 1e12, "TFLOP/s", pk["bf16_tflops"], "tensor", pk["source"])
+    res["config"] = {"workload": f"GQA attention backward bf16 B{args.batch} Hq32 Hkv8 S4096 D128 non-causal "
+                                 "(FLOPs counted as 2.5 x forward)"}
     print(json.dumps(res), flush=True)
 
 
