@@ -127,6 +127,20 @@ int pjx_attn_bwd_band(const void* q, const void* k, const void* v, const void* o
 size_t pjx_attn_bwd_workspace_bytes(int B, int Lq, int Hq);
 
 /*
+ * Forward-mode derivative of pjx_attn_fwd_band: the tangent t_o of o for tangents tq, tk, tv of
+ * q, k, v (each may be NULL = zero), from the forward's natural-log lse.  Exact fp32 arithmetic
+ * on CUDA cores, one pass over the keys.
+ *
+ * Replaces `mha_jvp_from_lse_kernel` (probjax/nn/pallas_kernels/kernels/attention.py:536-660),
+ * the forward-mode path behind `diff_mode="forward"` (`jax.custom_jvp` wiring at 3303-3330).
+ */
+int pjx_attn_jvp_band(const void* q, const void* k, const void* v, const void* tq, const void* tk,
+                      const void* tv, const float* lse, void* t_o, const int32_t* kv_lengths,
+                      const float* bias, int64_t bias_batch_stride, int64_t bias_head_stride, int B,
+                      int Lq, int Lkv, int Hq, int Hkv, int D, int Dv, int dtype, int band_lo,
+                      int band_hi, float sm_scale, void* stream);
+
+/*
  * Split-KV decode forward over a KV cache with per-sequence valid lengths,
  * followed by the exact log-sum-exp combine of the per-split partials.
  *

@@ -9,6 +9,7 @@ build it with ``python -m probjax_b200.build``.
 from .attention import (  # noqa: F401
     attention_backward,
     attention_forward,
+    attention_jvp,
     check_status,
     combine_partials,
     decode_forward,
@@ -24,16 +25,29 @@ from .dispatch import b200_attention_or_none, device_attention_defaults  # noqa:
 from .masks import (  # noqa: F401
     AttentionBias,
     AttentionMask,
+    BlockDiagonalCausalMask,
+    BlockDiagonalMask,
+    CausalAlibiBias,
     CausalFromBottomRightMask,
     CausalLocalWindowMask,
     CausalMask,
     ComposeMask,
+    ConstantBias,
     DenseBias,
+    DistanceDecayBias,
     KeyPaddingMask,
     KVLenMask,
     LocalWindowMask,
+    LowRankBias,
+    MarginalizationMask,
     NoMask,
+    NotMask,
+    PrefixLMMask,
     QKVLengthMask,
+    SameSegmentMask,
+    SeqLenMask,
+    SumBias,
+    SymmetricAlibiBias,
 )
 
 __version__ = "0.1.0"

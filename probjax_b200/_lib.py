@@ -31,6 +31,8 @@ SIGNATURES = {
                                _i, _i, _i, _i, _i, _i, _i, _i, _i, _i, _f, _i, _vp, _vp]),
     "pjx_attn_bwd_band": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64,
                                _i, _i, _i, _i, _i, _i, _i, _i, _i, _i, _f, _i, _vp, _sz, _vp, _vp]),
+    "pjx_attn_jvp_band": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64,
+                               _i, _i, _i, _i, _i, _i, _i, _i, _i, _i, _f, _vp]),
     "pjx_attn_bwd": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64,
                           _i, _i, _i, _i, _i, _i, _i, _i, _i, _f, _vp, _sz, _vp]),
     "pjx_attn_bwd_workspace_bytes": (_sz, [_i, _i, _i]),

@@ -20,7 +20,7 @@ import numpy as np
 import torch
 
 from . import _lib
-from .masks import AttentionBias, AttentionMask, NoMask, lower_bias, lower_mask
+from .masks import AttentionBias, AttentionMask, NoMask, lower_bias, lower_dense, lower_mask, split_mask
 
 _DTYPES = {torch.float32: _lib.PJX_F32, torch.bfloat16: _lib.PJX_BF16, torch.float16: _lib.PJX_F16}
 _IMPL = {None: _lib.IMPL_AUTO, "b200": _lib.IMPL_AUTO, "b200:generic": _lib.IMPL_GENERIC,
@@ -213,6 +213,34 @@ def attention_backward(q, k, v, o, lse, d_o, *, causal=False, band=None, kv_leng
     return dq, dk, dv
 
 
+def attention_jvp(q, k, v, lse, tq=None, tk=None, tv=None, *, causal=False, band=None, kv_lengths=None, bias=None,
+                  sm_scale=1.0):
+    """One ``pjx_attn_jvp_band`` call on CUDA tensors: the tangent of ``o`` for tangents
+    ``tq, tk, tv`` (``None`` = zero) of the forward that produced ``lse``."""
+    _require_gpu()
+    band_lo, band_hi = _band_args(causal, band)
+    dev = q.device
+    q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
+    tq, tk, tv = (None if t is None else t.to(q.dtype).contiguous() for t in (tq, tk, tv))
+    lse = lse.contiguous().float()
+    B, Lq, Hq, D = q.shape
+    Lkv, Hkv, Dv = k.shape[1], k.shape[2], v.shape[3]
+    t_o = torch.empty((B, Lq, Hq, Dv), dtype=q.dtype, device=dev)
+    kvl = None if kv_lengths is None else _as_tensor(kv_lengths).to(device=dev, dtype=torch.int32).contiguous()
+    bs = hs = 0
+    bt = None
+    if bias is not None:
+        bt = _as_tensor(bias).to(device=dev, dtype=torch.float32).contiguous()
+        bs = 0 if bt.shape[0] == 1 else bt.stride(0)
+        hs = 0 if bt.shape[1] == 1 else bt.stride(1)
+    with torch.cuda.device(dev):
+        rc = _lib.lib().pjx_attn_jvp_band(_ptr(q), _ptr(k), _ptr(v), _ptr(tq), _ptr(tk), _ptr(tv), _ptr(lse), _ptr(t_o),
+                                          _ptr(kvl), _ptr(bt), bs, hs, B, Lq, Lkv, Hq, Hkv, D, Dv, _DTYPES[q.dtype],
+                                          band_lo, band_hi, float(sm_scale), _stream(dev))
+    _lib.check(rc)
+    return t_o
+
+
 class _AttentionFunction(torch.autograd.Function):
     """Differentiable forward: the regular forward kernels with the LSE kept as the
     residual, and ``pjx_attn_bwd`` for the gradients of q, k and v (the reference wires
@@ -223,21 +251,41 @@ class _AttentionFunction(torch.autograd.Function):
         o, lse = attention_forward(q, k, v, band=band, kv_lengths=kv_lengths, bias=bias, sm_scale=sm_scale,
                                    return_lse=True, impl=impl)
         ctx.save_for_backward(q, k, v, o, lse)
+        ctx.save_for_forward(q, k, v, lse)
         ctx.args = (band, kv_lengths, bias, sm_scale, impl)
         ctx.mark_non_differentiable(lse)
         return o, lse
 
     @staticmethod
+    def jvp(ctx, tq, tk, tv, *_):
+        # forward-mode: the reference's diff_mode="forward" path (kernels/attention.py:3303-3330)
+        q, k, v, lse = ctx.saved_tensors
+        band, kv_lengths, bias, sm_scale, _impl = ctx.args
+        t_o = attention_jvp(q, k, v, lse, tq, tk, tv, band=band, kv_lengths=kv_lengths, bias=bias, sm_scale=sm_scale)
+        return t_o, None
+
+    @staticmethod
     def backward(ctx, d_o, _d_lse):
         q, k, v, o, lse = ctx.saved_tensors
         band, kv_lengths, bias, sm_scale, impl = ctx.args
+        # a forced tensor-core forward does not force the tensor-core backward, which takes fewer shapes
         dq, dk, dv = attention_backward(q, k, v, o, lse, d_o, band=band, kv_lengths=kv_lengths, bias=bias,
-                                        sm_scale=sm_scale, impl=impl)
+                                        sm_scale=sm_scale, impl=impl if impl == "b200:generic" else None)
         return dq, dk, dv, None, None, None, None, None
 
 
 def _wants_grad(*tensors) -> bool:
-    return torch.is_grad_enabled() and any(isinstance(t, torch.Tensor) and t.requires_grad for t in tensors)
+    """Reverse-mode (requires_grad) or forward-mode (a dual tensor) differentiation is active."""
+    import torch.autograd.forward_ad as fwd_ad
+
+    for t in tensors:
+        if not isinstance(t, torch.Tensor):
+            continue
+        if torch.is_grad_enabled() and t.requires_grad:
+            return True
+        if fwd_ad.unpack_dual(t).tangent is not None:
+            return True
+    return False
 
 
 def decode_forward(q, k_cache, v_cache, *, kv_lengths=None, sm_scale, split_len=0, return_lse=False,
@@ -356,8 +404,11 @@ def mha(q, k, v, mask: AttentionMask | None = None, bias: AttentionBias | None =
     if interpret:
         raise NotImplementedError("interpret mode belongs to the Pallas kernels; this library runs CUDA only")
     B, Lq = q.shape[0], q.shape[1]
-    lm = lower_mask(mask, B, Lq, k.shape[1])
-    bt = lower_bias(bias, B, q.shape[2], Lq, k.shape[1])
+    lm, residual = split_mask(mask, B, Lq, k.shape[1])
+    if residual is None:
+        bt = lower_bias(bias, B, q.shape[2], Lq, k.shape[1])
+    else:  # mask classes without a native form: their dense -inf tensor rides on the bias
+        bt = lower_dense(residual, bias, B, q.shape[2], Lq, k.shape[1])
     if _wants_grad(q, k, v):
         # differentiation always runs the regular kernels (attention_splitkv.py:253-272)
         if bt is not None and bt.requires_grad:
@@ -545,6 +596,21 @@ def mla(q, cache, wk=None, wv=None, *, mask=None, bias=None, rng=None, sm_scale:
     wv = None if wv is None else wv.to(dev).contiguous()
     if wk is not None and (wk.dtype != q.dtype or wv.dtype != q.dtype or cache.dtype != q.dtype):
         raise ValueError("q, cache, wk and wv must share a dtype")
+    if _wants_grad(q, cache, wk, wv):
+        # Differentiation goes through the materialized K and V and the regular attention kernels, as
+        # in the reference (latent_attention.py:554-585); the up-projections and their gradients are
+        # plain library matrix products here.
+        if bt is not None and bt.requires_grad:
+            raise NotImplementedError("gradients of a DenseBias are not implemented")
+        if lm.q_limit is not None:
+            raise NotImplementedError("gradients under a query-length mask are not implemented")
+        if wk is not None:
+            kmat = torch.matmul(cache, wk.reshape(H * Dqk, R).t()).view(B, S, H, Dqk)
+            vmat = torch.matmul(cache, wv.reshape(H * Dv, R).t()).view(B, S, H, Dv)
+        else:
+            kmat = vmat = cache[:, :, None, :]  # one shared KV head
+        out, lse = _AttentionFunction.apply(q, kmat, vmat, lm.band, lm.kv_lengths, bt, float(sm_scale), implementation)
+        return (out, lse) if return_lse else out
     o = torch.empty((B, Lq, H, Dv), dtype=q.dtype, device=dev)
     lse = torch.empty((B, H, Lq), dtype=torch.float32, device=dev) if return_lse else None
     kvl = None if lm.kv_lengths is None else lm.kv_lengths.to(device=dev, dtype=torch.int32).contiguous()

@@ -320,6 +320,174 @@ int launch_dtype(const BwdParams& p, cudaStream_t stream) {
   }
 }
 
+
+// ---------------------------------------------------------------------------------------------
+// Forward-mode derivative (JVP) from the saved log-sum-exp, the reference's
+// `mha_jvp_from_lse_kernel` (kernels/attention.py:536-660): with tangents tq, tk, tv,
+//   ds_ij = sm_scale (tq_i.k_j + q_i.tk_j)            (masked entries 0)
+//   to_i  = sum_j P_ij ds_ij v_j + sum_j P_ij tv_j - (sum_j P_ij ds_ij) o_i,   o_i = sum_j P_ij v_j
+// One CTA per 32-query tile of a (batch, head), walking the KV tiles once; P and P ds are rounded
+// to the input dtype before the products with v / tv, as the reference does.
+// ---------------------------------------------------------------------------------------------
+struct JvpParams {
+  const void *q, *k, *v, *tq, *tk, *tv;  // tangents may be null (zero)
+  const float* lse;
+  void* t_o;
+  const int32_t* kv_lengths;
+  const float* bias;
+  int64_t bias_bs, bias_hs;
+  int B, Lq, Lkv, Hq, Hkv, D, Dv;
+  int band_lo, band_hi;
+  float sm_scale;
+};
+
+inline size_t jvp_smem_bytes(int D, int Dv) {
+  return sizeof(float) * ((size_t)4 * T * (D | 1) + (size_t)2 * T * (Dv | 1) + 2 * T * (T + 1) + T);
+}
+
+template <typename T_>
+__device__ __forceinline__ void load_rows_or_zero(float* dst, int pitch, const T_* src, int64_t row_stride, int first,
+                                                  int limit, int width) {
+  if (src) {
+    load_rows<T_>(dst, pitch, src, row_stride, first, limit, width);
+  } else {
+    for (int idx = threadIdx.x; idx < T * width; idx += NT) dst[(idx / width) * pitch + idx % width] = 0.f;
+  }
+}
+
+template <typename T_, int NC>  // NC: per-thread output columns = ceil(Dv / 16)
+__global__ void __launch_bounds__(NT) jvp_kernel(const JvpParams p) {
+  extern __shared__ float smem[];
+  const int Dp = p.D | 1, Dvp = p.Dv | 1;
+  float* Qs = smem;                 // [T][Dp]
+  float* tQs = Qs + T * Dp;
+  float* Ks = tQs + T * Dp;
+  float* tKs = Ks + T * Dp;
+  float* Vs = tKs + T * Dp;         // [T][Dvp]
+  float* tVs = Vs + T * Dvp;
+  float* Ps = tVs + T * Dvp;        // [T][T + 1]  P
+  float* PDs = Ps + T * (T + 1);    // [T][T + 1]  P ds
+  float* lse_s = PDs + T * (T + 1);
+  const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
+  const int q0 = blockIdx.x * T, h = blockIdx.y, b = blockIdx.z;
+  const int hk = h / (p.Hq / p.Hkv);
+  int kv_len = p.Lkv;
+  if (p.kv_lengths) kv_len = max(0, min(kv_len, p.kv_lengths[b]));
+  const int kv_end = max(0, min(kv_len, min(q0 + T, p.Lq) + p.band_hi));
+  const int kv_begin = (max(0, q0 + p.band_lo) / T) * T;
+  const int64_t qstride = (int64_t)p.Hq * p.D, ostride = (int64_t)p.Hq * p.Dv;
+  const int64_t kstride = (int64_t)p.Hkv * p.D, vstride = (int64_t)p.Hkv * p.Dv;
+  const int64_t qoff = ((int64_t)b * p.Lq * p.Hq + h) * p.D;
+  const int64_t koff = ((int64_t)b * p.Lkv * p.Hkv + hk) * p.D, voff = ((int64_t)b * p.Lkv * p.Hkv + hk) * p.Dv;
+  const T_* q = static_cast<const T_*>(p.q) + qoff;
+  const T_* tq = p.tq ? static_cast<const T_*>(p.tq) + qoff : nullptr;
+  const T_* k = static_cast<const T_*>(p.k) + koff;
+  const T_* tk = p.tk ? static_cast<const T_*>(p.tk) + koff : nullptr;
+  const T_* v = static_cast<const T_*>(p.v) + voff;
+  const T_* tv = p.tv ? static_cast<const T_*>(p.tv) + voff : nullptr;
+  load_rows<T_>(Qs, Dp, q, qstride, q0, p.Lq, p.D);
+  load_rows_or_zero<T_>(tQs, Dp, tq, qstride, q0, p.Lq, p.D);
+  if (threadIdx.x < T) {
+    const int qi = q0 + threadIdx.x;
+    lse_s[threadIdx.x] = qi < p.Lq ? p.lse[((int64_t)b * p.Hq + h) * p.Lq + qi] : INFINITY;
+  }
+  const float* bias = p.bias ? p.bias + (int64_t)b * p.bias_bs + (int64_t)h * p.bias_hs : nullptr;
+  float acc[2][NC], out[2][NC], mu[2] = {0.f, 0.f};
+#pragma unroll
+  for (int i = 0; i < 2; ++i)
+#pragma unroll
+    for (int c = 0; c < NC; ++c) acc[i][c] = out[i][c] = 0.f;
+
+  for (int k0 = kv_begin; k0 < kv_end; k0 += T) {
+    __syncthreads();
+    load_rows<T_>(Ks, Dp, k, kstride, k0, kv_len, p.D);
+    load_rows_or_zero<T_>(tKs, Dp, tk, kstride, k0, kv_len, p.D);
+    load_rows<T_>(Vs, Dvp, v, vstride, k0, kv_len, p.Dv);
+    load_rows_or_zero<T_>(tVs, Dvp, tv, vstride, k0, kv_len, p.Dv);
+    __syncthreads();
+    float s[2][2] = {}, ds[2][2] = {};
+    for (int d = 0; d < p.D; ++d) {
+      const float qa = Qs[(ty * 2) * Dp + d], qb = Qs[(ty * 2 + 1) * Dp + d];
+      const float ta = tQs[(ty * 2) * Dp + d], tb = tQs[(ty * 2 + 1) * Dp + d];
+      const float ka = Ks[tx * Dp + d], kb = Ks[(tx + 16) * Dp + d];
+      const float ua = tKs[tx * Dp + d], ub = tKs[(tx + 16) * Dp + d];
+      s[0][0] = fmaf(qa, ka, s[0][0]);
+      s[0][1] = fmaf(qa, kb, s[0][1]);
+      s[1][0] = fmaf(qb, ka, s[1][0]);
+      s[1][1] = fmaf(qb, kb, s[1][1]);
+      ds[0][0] = fmaf(ta, ka, fmaf(qa, ua, ds[0][0]));
+      ds[0][1] = fmaf(ta, kb, fmaf(qa, ub, ds[0][1]));
+      ds[1][0] = fmaf(tb, ka, fmaf(qb, ua, ds[1][0]));
+      ds[1][1] = fmaf(tb, kb, fmaf(qb, ub, ds[1][1]));
+    }
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      const int r = ty * 2 + i, qi = q0 + r;
+      const float lse = lse_s[r];
+      float part = 0.f;
+#pragma unroll
+      for (int c = 0; c < 2; ++c) {
+        const int col = tx + 16 * c, kj = k0 + col;
+        float x = s[i][c] * p.sm_scale;
+        if (bias && qi < p.Lq && kj < p.Lkv) x += bias[(int64_t)qi * p.Lkv + kj];
+        const bool keep = qi < p.Lq && kj < kv_len && kj <= qi + p.band_hi && kj >= qi + p.band_lo && lse != INFINITY;
+        const float pr = keep ? exp2f((x - lse) * kLog2e) : 0.f;
+        const float pd = keep ? pr * ds[i][c] * p.sm_scale : 0.f;
+        part += pd;
+        Ps[r * (T + 1) + col] = Elem<T_>::round(pr);
+        PDs[r * (T + 1) + col] = Elem<T_>::round(pd);
+      }
+#pragma unroll
+      for (int off = 8; off >= 1; off >>= 1) part += __shfl_xor_sync(0xffffffffu, part, off);
+      mu[i] += part;  // the 16 threads of a row hold the same sum
+    }
+    __syncthreads();
+    for (int c = 0; c < T; ++c) {
+      const float p0 = Ps[(ty * 2) * (T + 1) + c], p1 = Ps[(ty * 2 + 1) * (T + 1) + c];
+      const float e0 = PDs[(ty * 2) * (T + 1) + c], e1 = PDs[(ty * 2 + 1) * (T + 1) + c];
+#pragma unroll
+      for (int cc = 0; cc < NC; ++cc) {
+        const int d = tx + 16 * cc;
+        const float vv = d < p.Dv ? Vs[c * Dvp + d] : 0.f;
+        const float tvv = d < p.Dv ? tVs[c * Dvp + d] : 0.f;
+        acc[0][cc] = fmaf(e0, vv, fmaf(p0, tvv, acc[0][cc]));
+        acc[1][cc] = fmaf(e1, vv, fmaf(p1, tvv, acc[1][cc]));
+        out[0][cc] = fmaf(p0, vv, out[0][cc]);
+        out[1][cc] = fmaf(p1, vv, out[1][cc]);
+      }
+    }
+  }
+  T_* t_o = static_cast<T_*>(p.t_o) + ((int64_t)b * p.Lq * p.Hq + h) * p.Dv;
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    const int qi = q0 + ty * 2 + i;
+    if (qi >= p.Lq) continue;
+#pragma unroll
+    for (int cc = 0; cc < NC; ++cc) {
+      const int d = tx + 16 * cc;
+      if (d < p.Dv) t_o[(int64_t)qi * ostride + d] = Elem<T_>::from_f(acc[i][cc] - mu[i] * out[i][cc]);
+    }
+  }
+}
+
+template <typename T_, int NC>
+int launch_jvp_width(const JvpParams& p, cudaStream_t stream) {
+  const size_t smem = jvp_smem_bytes(p.D, p.Dv);
+  auto kern = jvp_kernel<T_, NC>;
+  int rc;
+  if ((rc = set_smem(kern, smem, "cudaFuncSetAttribute(jvp)"))) return rc;
+  kern<<<dim3((p.Lq + T - 1) / T, p.Hq, p.B), NT, smem, stream>>>(p);
+  count_launch();
+  return check_cuda(cudaGetLastError(), "jvp launch");
+}
+
+template <typename T_>
+int launch_jvp(const JvpParams& p, cudaStream_t stream) {
+  if (p.Dv <= 64) return launch_jvp_width<T_, 4>(p, stream);
+  if (p.Dv <= 128) return launch_jvp_width<T_, 8>(p, stream);
+  return launch_jvp_width<T_, 16>(p, stream);
+}
+
 }  // namespace
 }  // namespace pjx
 
@@ -392,6 +560,35 @@ int pjx_attn_bwd(const void* q, const void* k, const void* v, const void* o, con
   return pjx_attn_bwd_band(q, k, v, o, lse, d_o, dq, dk, dv, kv_lengths, bias, bias_batch_stride, bias_head_stride, B,
                            Lq, Lkv, Hq, Hkv, D, Dv, dtype, PJX_BAND_NO_LOWER, causal ? 0 : PJX_BAND_NO_UPPER, sm_scale,
                            PJX_IMPL_AUTO, workspace, workspace_bytes, nullptr, stream);
+}
+
+int pjx_attn_jvp_band(const void* q, const void* k, const void* v, const void* tq, const void* tk, const void* tv,
+                      const float* lse, void* t_o, const int32_t* kv_lengths, const float* bias,
+                      int64_t bias_batch_stride, int64_t bias_head_stride, int B, int Lq, int Lkv, int Hq, int Hkv,
+                      int D, int Dv, int dtype, int band_lo, int band_hi, float sm_scale, void* stream) {
+  if (dtype != PJX_F32 && dtype != PJX_BF16 && dtype != PJX_F16)
+    return fail(PJX_ERR_BAD_ARG, "dtype must be float32, bfloat16 or float16 (got code %d)", dtype);
+  if (B < 0 || Lq < 0 || Lkv < 0 || Hq < 1 || Hkv < 1 || D < 1 || Dv < 1)
+    return fail(PJX_ERR_BAD_ARG, "negative or zero dimension");
+  if (Hq % Hkv != 0) return fail(PJX_ERR_BAD_ARG, "query heads %d must be a multiple of kv heads %d", Hq, Hkv);
+  if (D > 256 || Dv > 256) return fail(PJX_ERR_UNSUPPORTED, "head dims above 256 are not supported (D=%d, Dv=%d)", D, Dv);
+  if (Lq >= PJX_BAND_NO_UPPER || Lkv >= PJX_BAND_NO_UPPER)
+    return fail(PJX_ERR_BAD_ARG, "sequence lengths must be below 2^30");
+  if (B == 0 || Lq == 0) return PJX_OK;
+  if (!q || !lse || !t_o || (Lkv > 0 && (!k || !v))) return fail(PJX_ERR_BAD_ARG, "jvp: null buffer");
+  JvpParams p;
+  p.q = q; p.k = k; p.v = v; p.tq = tq; p.tk = tk; p.tv = tv; p.lse = lse; p.t_o = t_o;
+  p.kv_lengths = kv_lengths; p.bias = bias; p.bias_bs = bias_batch_stride; p.bias_hs = bias_head_stride;
+  p.B = B; p.Lq = Lq; p.Lkv = Lkv; p.Hq = Hq; p.Hkv = Hkv; p.D = D; p.Dv = Dv;
+  p.band_lo = band_lo < PJX_BAND_NO_LOWER ? PJX_BAND_NO_LOWER : (band_lo > PJX_BAND_NO_UPPER ? PJX_BAND_NO_UPPER : band_lo);
+  p.band_hi = band_hi > PJX_BAND_NO_UPPER ? PJX_BAND_NO_UPPER : (band_hi < PJX_BAND_NO_LOWER ? PJX_BAND_NO_LOWER : band_hi);
+  p.sm_scale = sm_scale;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  switch (dtype) {
+    case PJX_F32: return launch_jvp<float>(p, st);
+    case PJX_BF16: return launch_jvp<__nv_bfloat16>(p, st);
+    default: return launch_jvp<__half>(p, st);
+  }
 }
 
 }  // extern "C"

@@ -8,6 +8,15 @@ Host-side mirror of the part of the reference's object model the kernels take
 callable ``mask(q_idx, k_idx, seg_q=None, seg_k=None) -> [Q, K] bool`` and can be
 materialised with ``dense``; masks combine with ``&``.
 
+Further classes are carried with their dense definition only -- ``NotMask`` (530),
+``PrefixLMMask`` (785), ``BlockDiagonalMask`` (871), ``BlockDiagonalCausalMask`` (984),
+``SeqLenMask`` (1239), ``SameSegmentMask`` (1537), ``MarginalizationMask`` (1671), ``or`` /
+``xor`` compositions, and the additive biases ``ConstantBias`` (1781), ``SumBias`` (553),
+``CausalAlibiBias`` (2230), ``SymmetricAlibiBias`` (2355), ``DistanceDecayBias`` (2387),
+``LowRankBias`` (1926): :func:`lower_dense` turns them into one additive float32 tensor
+(``-inf`` where masked) that the kernels take as a dense bias.  That costs ``O(H Q K)``
+memory; it widens what runs on the kernels, it is not a fused implementation.
+
 The kernels do not evaluate these callables.  :func:`lower_mask` reduces a mask
 expression to the three things the kernels implement natively -- a band of visible
 keys around each query row (``i + lo <= j <= i + hi``; the causal mask is the band
@@ -191,6 +200,124 @@ class ComposeMask(AttentionMask):
         return {"and": a & b, "or": a | b, "xor": a ^ b}[self.op]
 
 
+class NotMask(AttentionMask):
+    """Logical complement (attention_mask_bias.py:530-548)."""
+
+    def __init__(self, inner: AttentionMask):
+        self.inner = inner
+        self.stateful = inner.stateful
+
+    def __call__(self, q_idx, k_idx, seg_q=None, seg_k=None):
+        return ~self.inner(q_idx, k_idx, seg_q, seg_k)
+
+    def dense(self, q_len, kv_len, *, batch_size=1, num_heads=1, seg_q=None, seg_k=None):
+        return ~self.inner.dense(q_len, kv_len, batch_size=batch_size, num_heads=num_heads)
+
+
+class _PerBatchMask(AttentionMask):
+    """Masks whose data is per batch element: ``dense`` evaluates ``pair(b)`` -> ``[Q, K]`` bool."""
+
+    stateful = True
+
+    def _pair(self, b, q_len, kv_len):
+        raise NotImplementedError
+
+    def dense(self, q_len, kv_len, *, batch_size=1, num_heads=1, seg_q=None, seg_k=None):
+        rows = [self._pair(b, q_len, kv_len).expand(num_heads, q_len, kv_len) for b in range(batch_size)]
+        return torch.stack(rows)
+
+
+def _row(data, b):
+    """Batch element ``b`` of ``[B, T]`` data, or shared ``[T]`` data."""
+    data = torch.as_tensor(data)
+    return data[b] if data.dim() >= 2 else data
+
+
+class PrefixLMMask(_PerBatchMask):
+    """Keys in ``[0, prefix_length)`` visible to all queries, causal elsewhere
+    (attention_mask_bias.py:785-866); ``prefix_lengths`` scalar or ``[B]``."""
+
+    def __init__(self, prefix_lengths):
+        self.prefix_lengths = torch.as_tensor(prefix_lengths)
+
+    def __call__(self, q_idx, k_idx, seg_q=None, seg_k=None):
+        p = self.prefix_lengths if seg_q is None else torch.as_tensor(seg_q)
+        p = p.reshape(-1)[0]
+        return (k_idx[None, :] < p) | (q_idx[:, None] >= k_idx[None, :])
+
+    def _pair(self, b, q_len, kv_len):
+        p = self.prefix_lengths.reshape(-1)
+        return self(_idx(q_len), _idx(kv_len), p[b if p.shape[0] > 1 else 0])
+
+
+class BlockDiagonalMask(_PerBatchMask):
+    """Same block id (attention_mask_bias.py:871-980); ids ``[T]`` or ``[B, T]``."""
+
+    def __init__(self, query_block_ids, key_block_ids=None):
+        self.query_block_ids = torch.as_tensor(query_block_ids)
+        self.key_block_ids = None if key_block_ids is None else torch.as_tensor(key_block_ids)
+
+    def __call__(self, q_idx, k_idx, seg_q=None, seg_k=None):
+        qids = self.query_block_ids if seg_q is None else torch.as_tensor(seg_q)
+        kids = torch.as_tensor(seg_k) if seg_k is not None else (self.key_block_ids if self.key_block_ids is not None else qids)
+        return qids[..., :, None] == kids[..., None, :]
+
+    def _pair(self, b, q_len, kv_len):
+        qids = _row(self.query_block_ids, b)[:q_len]
+        kids = _row(self.key_block_ids if self.key_block_ids is not None else self.query_block_ids, b)[:kv_len]
+        return qids[:, None] == kids[None, :]
+
+
+class BlockDiagonalCausalMask(BlockDiagonalMask):
+    """Causal inside each block id (attention_mask_bias.py:984-1075)."""
+
+    def __call__(self, q_idx, k_idx, seg_q=None, seg_k=None):
+        return super().__call__(q_idx, k_idx, seg_q, seg_k) & (q_idx[:, None] >= k_idx[None, :])
+
+    def _pair(self, b, q_len, kv_len):
+        return super()._pair(b, q_len, kv_len) & (_idx(q_len)[:, None] >= _idx(kv_len)[None, :])
+
+
+class SameSegmentMask(BlockDiagonalMask):
+    """Same segment id (attention_mask_bias.py:1537-1667)."""
+
+    def __init__(self, query_segment_ids, key_segment_ids=None):
+        super().__init__(query_segment_ids, key_segment_ids)
+
+
+class SeqLenMask(_PerBatchMask):
+    """Per-batch sequence length ``L``: full attention inside ``[0, L)`` on both axes, only the
+    diagonal outside (attention_mask_bias.py:1239-1396)."""
+
+    def __init__(self, seq_lengths):
+        self.seq_lengths = torch.as_tensor(seq_lengths)
+
+    def _pair(self, b, q_len, kv_len):
+        length = self.seq_lengths.reshape(-1)[b]
+        q_idx, k_idx = _idx(q_len), _idx(kv_len)
+        rect = (q_idx[:, None] < length) & (k_idx[None, :] < length)
+        return rect | (q_idx[:, None] == k_idx[None, :])
+
+    def dense(self, q_len, kv_len, *, batch_size=1, num_heads=1, seg_q=None, seg_k=None):
+        if batch_size != self.seq_lengths.reshape(-1).shape[0]:
+            raise ValueError(
+                f"SeqLenMask.dense batch_size={batch_size} does not match stored lengths "
+                f"{self.seq_lengths.reshape(-1).shape[0]}"
+            )
+        return super().dense(q_len, kv_len, batch_size=batch_size, num_heads=num_heads)
+
+
+class MarginalizationMask(_PerBatchMask):
+    """Keep-mask on tokens with the diagonal always kept (attention_mask_bias.py:1671-1777)."""
+
+    def __init__(self, mask):
+        self.mask = torch.as_tensor(mask).bool()
+
+    def _pair(self, b, q_len, kv_len):
+        m = _row(self.mask, b)
+        return (m[:q_len, None] & m[None, :kv_len]) | (_idx(q_len)[:, None] == _idx(kv_len)[None, :])
+
+
 class AttentionBias:
     """Base class (attention_mask_bias.py:233-318): ``bias(scores, h, q_idx, k_idx, data)``."""
 
@@ -221,6 +348,90 @@ class DenseBias(AttentionBias):
         return b.expand(batch_size, num_heads, q_len, kv_len)
 
 
+class ConstantBias(AttentionBias):
+    """``scores + value`` (attention_mask_bias.py:1781-1804)."""
+
+    def __init__(self, value: float):
+        self.value = float(value)
+
+    def dense(self, q_len, kv_len, *, batch_size=1, num_heads=1):
+        return torch.full((1, 1, q_len, kv_len), self.value, dtype=torch.float32)
+
+
+class SumBias(AttentionBias):
+    """Sum of two additive biases (attention_mask_bias.py:553-579)."""
+
+    def __init__(self, lhs: AttentionBias, rhs: AttentionBias):
+        self.lhs, self.rhs = lhs, rhs
+
+    def dense(self, q_len, kv_len, *, batch_size=1, num_heads=1):
+        a = self.lhs.dense(q_len, kv_len, batch_size=batch_size, num_heads=num_heads)
+        b = self.rhs.dense(q_len, kv_len, batch_size=batch_size, num_heads=num_heads)
+        return a.float().cpu() + b.float().cpu() if a.device != b.device else a.float() + b.float()
+
+
+def _alibi_slopes(num_heads):
+    # attention_mask_bias.py:2223-2227: slope(h) = 2^-(h+1)
+    return torch.exp2(-(torch.arange(num_heads, dtype=torch.float32) + 1.0))
+
+
+class CausalAlibiBias(AttentionBias):
+    """``-slope(h) * relu(i - j)`` (attention_mask_bias.py:2230-2254)."""
+
+    def dense(self, q_len, kv_len, *, batch_size=1, num_heads=1):
+        dist = (_idx(q_len)[:, None] - _idx(kv_len)[None, :]).clamp_min(0).float()
+        return -(_alibi_slopes(num_heads)[None, :, None, None] * dist[None, None])
+
+
+class SymmetricAlibiBias(AttentionBias):
+    """``-slope(h) * |i - j|`` (attention_mask_bias.py:2355-2379)."""
+
+    def dense(self, q_len, kv_len, *, batch_size=1, num_heads=1):
+        dist = (_idx(q_len)[:, None] - _idx(kv_len)[None, :]).abs().float()
+        return -(_alibi_slopes(num_heads)[None, :, None, None] * dist[None, None])
+
+
+class DistanceDecayBias(AttentionBias):
+    """``-alpha * |i - j|`` (attention_mask_bias.py:2387-2414)."""
+
+    def __init__(self, alpha: float = 1.0):
+        self.alpha = float(alpha)
+
+    def dense(self, q_len, kv_len, *, batch_size=1, num_heads=1):
+        dist = (_idx(q_len)[:, None] - _idx(kv_len)[None, :]).abs().float()
+        return (-self.alpha * dist)[None, None]
+
+
+class LowRankBias(AttentionBias):
+    """``scale * query_factors @ key_factors^T`` with factors ``[H|1, max_length, rank]``
+    (attention_mask_bias.py:1926-2024).  Lowered densely here; the reference folds the factors
+    into Q and K instead."""
+
+    def __init__(self, query_factors, key_factors, *, scale: float = 1.0):
+        qf, kf = torch.as_tensor(query_factors), torch.as_tensor(key_factors)
+        qf = qf[None] if qf.dim() == 2 else qf
+        kf = kf[None] if kf.dim() == 2 else kf
+        if qf.dim() != 3 or kf.dim() != 3:
+            raise ValueError("factors must have shape [H|1, length, rank]")
+        if qf.shape[-1] != kf.shape[-1]:
+            raise ValueError("query and key factors must have the same rank")
+        if qf.shape[0] != kf.shape[0]:
+            raise ValueError("query and key factors must have the same head count")
+        if scale < 0:
+            raise ValueError("scale must be non-negative")
+        self.query_factors, self.key_factors, self.scale = qf, kf, float(scale)
+
+    def dense(self, q_len, kv_len, *, batch_size=1, num_heads=1):
+        if q_len > self.query_factors.shape[1]:
+            raise ValueError(f"q_len={q_len} exceeds maximum {self.query_factors.shape[1]}")
+        if kv_len > self.key_factors.shape[1]:
+            raise ValueError(f"kv_len={kv_len} exceeds maximum {self.key_factors.shape[1]}")
+        if self.query_factors.shape[0] not in (1, num_heads):
+            raise ValueError(f"Cannot broadcast factor head dim {self.query_factors.shape[0]} to {num_heads}")
+        qf, kf = self.query_factors[:, :q_len].float(), self.key_factors[:, :kv_len].float()
+        return (self.scale * torch.einsum("hqr,hkr->hqk", qf, kf))[None]
+
+
 @dataclass
 class LoweredMask:
     band_lo: Optional[int] = None     # key j visible to query i iff i + band_lo <= j (None: no bound)
@@ -240,6 +451,38 @@ class LoweredMask:
     @property
     def banded(self) -> bool:
         return self.band_lo is not None or self.band_hi is not None
+
+
+def _merge_lowered(a: LoweredMask, b: LoweredMask) -> LoweredMask:
+    """AND of two lowered masks: the tighter band, the shorter key lengths, the lower query limit."""
+    out = LoweredMask()
+    los = [x for x in (a.band_lo, b.band_lo) if x is not None]
+    his = [x for x in (a.band_hi, b.band_hi) if x is not None]
+    out.band_lo = max(los) if los else None
+    out.band_hi = min(his) if his else None
+    if a.kv_lengths is not None and b.kv_lengths is not None:
+        out.kv_lengths = torch.minimum(a.kv_lengths.cpu(), b.kv_lengths.cpu()) \
+            if a.kv_lengths.device != b.kv_lengths.device else torch.minimum(a.kv_lengths, b.kv_lengths)
+    else:
+        out.kv_lengths = a.kv_lengths if a.kv_lengths is not None else b.kv_lengths
+    limits = [x for x in (a.q_limit, b.q_limit) if x is not None]
+    out.q_limit = min(limits) if limits else None
+    return out
+
+
+def split_mask(mask, batch: int, q_len: int, kv_len: int):
+    """``(LoweredMask, residual)``: the part of an AND-expression the kernels implement natively,
+    and the rest (``None`` if nothing is left) for :func:`lower_dense`."""
+    try:
+        return lower_mask(mask, batch, q_len, kv_len), None
+    except NotImplementedError:
+        pass
+    if isinstance(mask, ComposeMask) and mask.op == "and":
+        la, ra = split_mask(mask.lhs, batch, q_len, kv_len)
+        lb, rb = split_mask(mask.rhs, batch, q_len, kv_len)
+        residual = ra if rb is None else (rb if ra is None else ComposeMask("and", ra, rb))
+        return _merge_lowered(la, lb), residual
+    return LoweredMask(), mask
 
 
 def lower_mask(mask, batch: int, q_len: int, kv_len: int) -> LoweredMask:
@@ -277,29 +520,35 @@ def lower_mask(mask, batch: int, q_len: int, kv_len: int) -> LoweredMask:
             "lowers to the kernels (use KVLenMask for per-batch key lengths)"
         )
     if isinstance(mask, ComposeMask) and mask.op == "and":
-        a = lower_mask(mask.lhs, batch, q_len, kv_len)
-        b = lower_mask(mask.rhs, batch, q_len, kv_len)
-        out = LoweredMask()
-        los = [x for x in (a.band_lo, b.band_lo) if x is not None]
-        his = [x for x in (a.band_hi, b.band_hi) if x is not None]
-        out.band_lo = max(los) if los else None
-        out.band_hi = min(his) if his else None
-        if a.kv_lengths is not None and b.kv_lengths is not None:
-            out.kv_lengths = torch.minimum(a.kv_lengths.cpu(), b.kv_lengths.cpu()) \
-                if a.kv_lengths.device != b.kv_lengths.device else torch.minimum(a.kv_lengths, b.kv_lengths)
-        else:
-            out.kv_lengths = a.kv_lengths if a.kv_lengths is not None else b.kv_lengths
-        limits = [x for x in (a.q_limit, b.q_limit) if x is not None]
-        out.q_limit = min(limits) if limits else None
-        return out
+        return _merge_lowered(lower_mask(mask.lhs, batch, q_len, kv_len), lower_mask(mask.rhs, batch, q_len, kv_len))
     raise NotImplementedError(f"mask {type(mask).__name__} is not implemented by the sm_100a kernels")
 
 
 def lower_bias(bias, batch: int, heads: int, q_len: int, kv_len: int):
-    """``DenseBias`` -> float32 ``[Bb, Hb, Q, K]`` tensor, or None."""
+    """Additive bias -> float32 ``[Bb, Hb, Q, K]`` tensor, or None.  ``DenseBias`` passes
+    through; the other additive classes are evaluated densely."""
     if bias is None:
         return None
     if isinstance(bias, DenseBias):
         bias.dense(q_len, kv_len, batch_size=batch, num_heads=heads)  # shape validation
         return bias.bias
+    if isinstance(bias, (ConstantBias, SumBias, CausalAlibiBias, SymmetricAlibiBias, DistanceDecayBias, LowRankBias)):
+        return bias.dense(q_len, kv_len, batch_size=batch, num_heads=heads).float()
     raise NotImplementedError(f"bias {type(bias).__name__} is not implemented by the sm_100a kernels")
+
+
+def lower_dense(mask, bias, batch: int, heads: int, q_len: int, kv_len: int):
+    """Fallback lowering for masks :func:`lower_mask` refuses: the mask's dense boolean form
+    becomes ``-inf`` entries of one additive float32 ``[B|1, H|1, Q, K]`` tensor, summed with
+    the bias.  Rows without a visible key come out as zeros, as with the structural masks."""
+    if not isinstance(mask, AttentionMask):
+        raise NotImplementedError(f"mask {type(mask).__name__} is not implemented by the sm_100a kernels")
+    try:
+        keep = mask.dense(q_len, kv_len, batch_size=batch, num_heads=1)
+    except NotImplementedError as e:
+        raise NotImplementedError(f"mask {type(mask).__name__} has no dense form here") from e
+    add = torch.zeros(keep.shape, dtype=torch.float32).masked_fill_(~keep.cpu(), float("-inf"))
+    bt = lower_bias(bias, batch, heads, q_len, kv_len)
+    if bt is not None:
+        add = add.to(bt.device) + bt.float()
+    return add

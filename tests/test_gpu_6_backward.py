@@ -166,3 +166,87 @@ def test_tcgen05_backward_refuses_what_it_does_not_compute():
     # auto falls back to the CUDA-core kernels
     dq, dk, dv = pj.attention_backward(q, q, q, o, lse, q, sm_scale=0.1)
     assert torch.isfinite(dq).all()
+
+
+@pytest.mark.parametrize(
+    "dtype,b,lq,lkv,hq,hkv,d,dv,mask_kind",
+    [
+        (torch.float32, 2, 45, 70, 4, 2, 24, 40, "causal_len"),
+        (torch.float32, 1, 64, 64, 2, 2, 100, 100, "window"),
+        (torch.bfloat16, 2, 130, 200, 4, 1, 128, 128, "none"),
+        (torch.float16, 1, 96, 96, 2, 2, 64, 64, "causal_len"),
+    ],
+)
+def test_forward_mode_tangent_matches_dense_jvp(dtype, b, lq, lkv, hq, hkv, d, dv, mask_kind):
+    """pjx_attn_jvp_band through torch forward-mode AD against torch.func.jvp of the float64 dense
+    formula (the reference tests diff_mode="forward" against jax.jvp of its dense path)."""
+    import torch.autograd.forward_ad as fwd_ad
+
+    dvc = dev()
+    q, k, v = randn((b, lq, hq, d), dtype, 1), randn((b, lkv, hkv, d), dtype, 2), randn((b, lkv, hkv, dv), dtype, 3)
+    tq, tk, tv = randn((b, lq, hq, d), dtype, 4), randn((b, lkv, hkv, d), dtype, 5), randn((b, lkv, hkv, dv), dtype, 6)
+    sc = 1 / math.sqrt(d)
+    lens = torch.tensor([lkv, max(1, lkv // 3)][:b], dtype=torch.int32)
+    if mask_kind == "causal_len":
+        mask = pj.CausalMask() & pj.KVLenMask(lens)
+    elif mask_kind == "window":
+        mask = pj.LocalWindowMask(9, 4)
+    else:
+        mask = None
+    keep = torch.ones(b, 1, lq, lkv, dtype=torch.bool) if mask is None else mask.dense(lq, lkv, batch_size=b)
+
+    def dense(q_, k_, v_):
+        rep = hq // hkv
+        kk, vv = k_.repeat_interleave(rep, dim=2), v_.repeat_interleave(rep, dim=2)
+        s = torch.einsum("bqhd,bkhd->bhqk", q_, kk) * sc
+        s = s.masked_fill(~keep, -math.inf)
+        return torch.einsum("bhqk,bkhd->bqhd", torch.softmax(s, dim=-1), vv)
+
+    _, want = torch.func.jvp(dense, (q.double(), k.double(), v.double()), (tq.double(), tk.double(), tv.double()))
+    with fwd_ad.dual_level():
+        qd, kd, vd = (fwd_ad.make_dual(x.to(dvc), t.to(dvc)) for x, t in ((q, tq), (k, tk), (v, tv)))
+        out = pj.flex_attention(qd, kd, vd, mask=mask, sm_scale=sc, enable_gqa=True)
+        primal, tangent = fwd_ad.unpack_dual(out)
+    assert tangent is not None
+    tol = 1e-4 if dtype == torch.float32 else 2e-2
+    assert _rel(tangent, want) < tol, _rel(tangent, want)
+    # a missing tangent is a zero tangent
+    got_q_only = pj.attention_jvp(q.to(dvc), k.to(dvc), v.to(dvc),
+                                  pj.attention_forward(q.to(dvc), k.to(dvc), v.to(dvc), band=pj.masks.lower_mask(mask, b, lq, lkv).band,
+                                                       kv_lengths=pj.masks.lower_mask(mask, b, lq, lkv).kv_lengths, sm_scale=sc,
+                                                       return_lse=True)[1],
+                                  tq.to(dvc), None, None, band=pj.masks.lower_mask(mask, b, lq, lkv).band,
+                                  kv_lengths=pj.masks.lower_mask(mask, b, lq, lkv).kv_lengths, sm_scale=sc)
+    _, want_q = torch.func.jvp(lambda q_: dense(q_, k.double(), v.double()), (q.double(),), (tq.double(),))
+    assert _rel(got_q_only, want_q) < tol
+
+
+@pytest.mark.parametrize("absorbed", [False, True])
+def test_latent_attention_gradients(absorbed):
+    """mla differentiates through the materialized K, V and the attention kernels
+    (latent_attention.py:554-585); reference: float64 autograd of the same composition."""
+    dvc = dev()
+    dtype = torch.bfloat16
+    b, lq, s_len, h, r = 2, 70, 90, 4, 64
+    dqk, dv_ = (r, r) if absorbed else (48, 32)
+    q, cache = randn((b, lq, h, dqk), dtype, 1), randn((b, s_len, r), dtype, 2)
+    wk = None if absorbed else (randn((h, dqk, r), dtype, 3) / math.sqrt(r)).to(dtype)
+    wv = None if absorbed else (randn((h, dv_, r), dtype, 4) / math.sqrt(r)).to(dtype)
+    g = randn((b, lq, h, dv_), dtype, 5)
+    sc = 1 / math.sqrt(dqk)
+    leaves = [x.to(dvc).requires_grad_(True) for x in (q, cache) + (() if absorbed else (wk, wv))]
+    out = pj.mla(leaves[0], leaves[1], *(leaves[2:] if not absorbed else (None, None)), mask=pj.CausalMask(), sm_scale=sc)
+    out.backward(g.to(dvc))
+    ref = [x.double().requires_grad_(True) for x in (q, cache) + (() if absorbed else (wk, wv))]
+    if absorbed:
+        k64 = v64 = ref[1][:, :, None, :].expand(b, s_len, h, r)
+    else:
+        k64 = torch.einsum("bsr,hdr->bshd", ref[1], ref[2])
+        v64 = torch.einsum("bsr,hdr->bshd", ref[1], ref[3])
+    sco = torch.einsum("bqhd,bkhd->bhqk", ref[0], k64) * sc
+    sco = sco.masked_fill(~torch.tril(torch.ones(lq, s_len, dtype=torch.bool))[None, None], -math.inf)
+    o64 = torch.einsum("bhqk,bkhd->bqhd", torch.softmax(sco, -1), v64)
+    o64.backward(g.double())
+    assert _rel(out.detach(), o64.detach()) < 2e-2
+    for name, a, w in zip(("dq", "dcache", "dwk", "dwv"), leaves, ref):
+        assert _rel(a.grad, w.grad) < 3e-2, (name, _rel(a.grad, w.grad))

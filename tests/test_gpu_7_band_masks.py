@@ -91,3 +91,26 @@ def test_band_gradients(dtype):
         for name, a, r in (("dq", qd.grad, q64.grad), ("dk", kd.grad, k64.grad), ("dv", vd.grad, v64.grad)):
             rel = float((a.double().cpu() - r).norm() / r.norm())
             assert rel < tol, (str(mask), name, rel)
+
+
+def test_masks_and_biases_without_a_native_form_run_through_the_dense_lowering():
+    """Segment / prefix masks and ALiBi-style biases reach the kernels as one additive tensor
+    (-inf where masked), while the causal part of the expression stays native."""
+    b, lq, h, d = 2, 200, 4, 64
+    dtype = torch.bfloat16
+    q, k, v = (randn((b, lq, h, d), dtype, s) for s in (1, 2, 3))
+    seg = torch.stack([torch.arange(lq) // 50, torch.arange(lq) // 70])
+    sc = 1 / math.sqrt(d)
+    cases = [
+        (pj.CausalMask() & pj.SameSegmentMask(seg), None),
+        (pj.PrefixLMMask(torch.tensor([30, 120])), pj.CausalAlibiBias()),
+        (pj.SeqLenMask(torch.tensor([200, 77])), pj.SumBias(pj.ConstantBias(0.5), pj.DistanceDecayBias(0.01))),
+        (None, pj.SymmetricAlibiBias()),
+    ]
+    for mask, bias in cases:
+        out, lse = pj.flex_attention(q.to(dev()), k.to(dev()), v.to(dev()), mask=mask, bias=bias, sm_scale=sc,
+                                     return_lse=True)
+        keep = None if mask is None else mask.dense(lq, lq, batch_size=b)
+        bt = None if bias is None else bias.dense(lq, lq, batch_size=b, num_heads=h)
+        want, want_lse = oracle_fwd(q, k, v, sm_scale=sc, keep=keep, bias=bt)
+        assert_close(out, lse, want, want_lse, dtype, f"{type(mask).__name__} + {type(bias).__name__}")

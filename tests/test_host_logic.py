@@ -268,3 +268,46 @@ def test_window_masks_lower_to_bands_and_compose():
     assert torch.equal(LocalWindowMask(2, 1).dense(6, 8)[0, 0], (i - j >= -1) & (i - j <= 2))
     assert torch.equal(CausalLocalWindowMask(2).dense(6, 8)[0, 0], (i - j >= 0) & (i - j <= 2))
     assert torch.equal(CausalFromBottomRightMask(6, 8).dense(6, 8)[0, 0], i + 2 >= j)
+
+
+def test_dense_lowered_masks_and_biases_follow_the_reference_predicates():
+    """Classes without a native kernel form: dense semantics of attention_mask_bias.py and the
+    split of an AND-expression into a native part and a dense residual."""
+    import math
+
+    import torch
+    from probjax_b200 import masks as M
+
+    i, j = torch.arange(6)[:, None], torch.arange(7)[None, :]
+    ids_q, ids_k = torch.tensor([0, 0, 1, 1, 2, 2]), torch.tensor([0, 0, 0, 1, 1, 2, 2])
+    assert torch.equal(M.PrefixLMMask(torch.tensor([3, 1])).dense(6, 7, batch_size=2)[1, 0], (j < 1) | (i >= j))
+    assert torch.equal(M.BlockDiagonalMask(ids_q, ids_k).dense(6, 7)[0, 0], ids_q[:, None] == ids_k[None, :])
+    assert torch.equal(M.BlockDiagonalCausalMask(ids_q, ids_k).dense(6, 7)[0, 0],
+                       (ids_q[:, None] == ids_k[None, :]) & (i >= j))
+    assert torch.equal(M.SameSegmentMask(torch.stack([ids_q, ids_q + 1])).dense(6, 6, batch_size=2)[1, 0],
+                       ids_q[:, None] == ids_q[None, :])
+    sl = M.SeqLenMask(torch.tensor([4, 6])).dense(6, 7, batch_size=2)
+    assert torch.equal(sl[0, 0], ((i < 4) & (j < 4)) | (i == j))
+    keep = torch.tensor([True, False, True, True, False, True, True])
+    assert torch.equal(M.MarginalizationMask(keep).dense(6, 7)[0, 0], (keep[:6, None] & keep[None, :]) | (i == j))
+    assert torch.equal(M.NotMask(M.CausalMask()).dense(6, 7)[0, 0], ~(i >= j))
+    assert torch.equal((M.ComposeMask("or", M.CausalMask(), M.LocalWindowMask(0, 2))).dense(6, 7)[0, 0],
+                       (i >= j) | ((i - j >= -2) & (i - j <= 0)))
+    # biases
+    slopes = torch.exp2(-(torch.arange(4.0) + 1))
+    assert torch.allclose(M.CausalAlibiBias().dense(6, 7, num_heads=4)[0], -slopes[:, None, None] * (i - j).clamp_min(0))
+    assert torch.allclose(M.SymmetricAlibiBias().dense(6, 7, num_heads=4)[0], -slopes[:, None, None] * (i - j).abs())
+    assert torch.allclose(M.DistanceDecayBias(0.5).dense(6, 7)[0, 0], -0.5 * (i - j).abs().float())
+    qf, kf = torch.randn(2, 8, 3), torch.randn(2, 9, 3)
+    assert torch.allclose(M.LowRankBias(qf, kf, scale=2.0).dense(6, 7, num_heads=2)[0],
+                          2.0 * torch.einsum("hqr,hkr->hqk", qf[:, :6], kf[:, :7]))
+    both = M.SumBias(M.ConstantBias(1.5), M.DistanceDecayBias(1.0)).dense(6, 7)
+    assert torch.allclose(both[0, 0], 1.5 - (i - j).abs().float())
+    # an AND-expression keeps its native part native
+    lm, residual = M.split_mask(M.CausalMask() & M.SameSegmentMask(ids_q) & M.KVLenMask(torch.tensor([5])), 1, 6, 6)
+    assert lm.causal and lm.kv_lengths.tolist() == [5] and isinstance(residual, M.SameSegmentMask)
+    add = M.lower_dense(residual, M.ConstantBias(2.0), 1, 2, 6, 6)
+    want = torch.where(ids_q[:, None] == ids_q[None, :], torch.tensor(2.0), torch.tensor(-math.inf))
+    assert torch.equal(add[0, 0], want)
+    lm2, res2 = M.split_mask(M.CausalMask(), 1, 6, 6)
+    assert res2 is None and lm2.causal
