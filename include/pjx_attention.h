@@ -238,6 +238,25 @@ int pjx_attn_combine(const float* o_parts, const float* lse_parts, int n_parts, 
                      int Dv, void* o, float* lse, int dtype, void* stream);
 
 /*
+ * Decode KV-cache update: writes k_new [B, n_new, Hkv, D] and v_new [B, n_new, Hkv, Dv] into
+ * the caches [B, capacity, Hkv, D|Dv] at rows positions[b] .. positions[b] + n_new - 1 and, if
+ * `advance` is nonzero, adds n_new to positions[b] in the same launch (no host round trip:
+ * append + pjx_attn_decode_splitkv with kv_lengths = positions is one graph-capturable step).
+ *
+ * Replaces the cache update of the attention layer's decode branch (probjax/nn/layers/
+ * attention.py:631-643: dynamic_update_slice of cached_key / cached_value at cache_index, then
+ * cache_index += 1), with one position per sequence instead of one shared index.
+ *
+ *   positions  int32 device array of 2 * B entries: [0, B) the positions, [B, 2B) scratch
+ *              counters that must be zero on entry and are zero again on exit.
+ *   overflow   optional int32 device word set to 1 if a sequence ran past `capacity` (its
+ *              excess rows are dropped and its position saturates).
+ */
+int pjx_kv_cache_append(void* k_cache, void* v_cache, const void* k_new, const void* v_new,
+                        int32_t* positions, int B, int capacity, int n_new, int Hkv, int D, int Dv,
+                        int dtype, int advance, int32_t* overflow, void* stream);
+
+/*
  * Latent attention forward: q over a shared latent cache with per-head
  * up-projections (wk, wv both given) or with K = V = cache (both NULL).
  *

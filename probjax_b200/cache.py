@@ -1,0 +1,90 @@
+"""Autoregressive KV cache for decode steps.
+
+Host-side mirror of the cache the reference's attention layer keeps
+(probjax/nn/layers/attention.py: ``init_cache`` 727-757, decode branch 603-675):
+``cached_key`` / ``cached_value`` ``[B, capacity, Hkv, D]`` and a write position.  The
+reference shares one ``cache_index`` across the batch and masks with
+``KeyPaddingMask(cur_index + 1)``; here every sequence has its own position (a ragged
+batch), the update is one kernel launch (``pjx_kv_cache_append``) that also advances the
+positions on the device, and attention over the filled prefix is the split-KV decode
+kernel with ``kv_lengths = positions``.
+"""
+
+from __future__ import annotations
+
+import math
+
+import torch
+
+from . import _lib
+from .attention import _DTYPES, _ptr, _require_gpu, _stream, mha
+from .masks import CausalFromBottomRightMask, KVLenMask
+
+
+class DecodeCache:
+    def __init__(self, batch: int, capacity: int, num_kv_heads: int, head_dim: int, v_head_dim: int | None = None,
+                 dtype=torch.bfloat16, device=None):
+        _require_gpu()
+        device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+        v_head_dim = head_dim if v_head_dim is None else v_head_dim
+        self.batch, self.capacity = int(batch), int(capacity)
+        self.cached_key = torch.zeros((batch, capacity, num_kv_heads, head_dim), dtype=dtype, device=device)
+        self.cached_value = torch.zeros((batch, capacity, num_kv_heads, v_head_dim), dtype=dtype, device=device)
+        # [0, B): positions; [B, 2B): scratch counters of the append kernel (zero between launches)
+        self._positions = torch.zeros((2 * batch,), dtype=torch.int32, device=device)
+        self._overflow = torch.zeros((1,), dtype=torch.int32, device=device)
+
+    @property
+    def cache_index(self) -> torch.Tensor:
+        """``int32 [B]``: number of valid tokens per sequence (a view, updated on the device)."""
+        return self._positions[: self.batch]
+
+    def reset(self, lengths=None):
+        self._positions.zero_()
+        self._overflow.zero_()
+        if lengths is not None:
+            self._positions[: self.batch] = torch.as_tensor(lengths, dtype=torch.int32, device=self._positions.device)
+
+    def overflowed(self) -> bool:
+        """Whether an update ran past the capacity (synchronises)."""
+        return bool(self._overflow.item())
+
+    def update(self, key: torch.Tensor, value: torch.Tensor, advance: bool = True):
+        """Append ``key [B, n, Hkv, D]`` / ``value [B, n, Hkv, Dv]`` at each sequence's position."""
+        ck, cv = self.cached_key, self.cached_value
+        if key.shape[0] != self.batch or key.shape[2:] != ck.shape[2:] or value.shape[2:] != cv.shape[2:] \
+                or value.shape[:2] != key.shape[:2]:
+            raise ValueError(
+                f"Autoregressive cache shape error, expected key [B={self.batch}, n, {ck.shape[2]}, {ck.shape[3]}] and "
+                f"value [B, n, {cv.shape[2]}, {cv.shape[3]}], got {tuple(key.shape)} and {tuple(value.shape)}."
+            )
+        if key.dtype != ck.dtype or value.dtype != cv.dtype:
+            raise ValueError("key / value dtype differs from the cache dtype")
+        key, value = key.contiguous(), value.contiguous()
+        dev = ck.device
+        with torch.cuda.device(dev):
+            rc = _lib.lib().pjx_kv_cache_append(_ptr(ck), _ptr(cv), _ptr(key), _ptr(value), _ptr(self._positions),
+                                                self.batch, self.capacity, key.shape[1], ck.shape[2], ck.shape[3],
+                                                cv.shape[3], _DTYPES[ck.dtype], int(advance), _ptr(self._overflow),
+                                                _stream(dev))
+        _lib.check(rc)
+
+    def attend(self, query: torch.Tensor, *, sm_scale: float | None = None, return_lse: bool = False,
+               prefix_length: int | None = None):
+        """Attention of ``query [B, n, Hq, D]`` over the filled prefix.  One query token per
+        sequence is a decode step (split-KV kernel, ragged positions).  Several query tokens
+        (a prefill chunk just appended) need ``prefix_length``: the common number of valid
+        tokens after the append, for the bottom-right causal mask."""
+        if sm_scale is None:
+            sm_scale = 1.0 / math.sqrt(query.shape[-1])
+        mask = KVLenMask(self.cache_index)
+        if query.shape[1] > 1:
+            if prefix_length is None:
+                raise ValueError("attend with several query tokens needs prefix_length (tokens valid after the append)")
+            mask = mask & CausalFromBottomRightMask(query.shape[1], int(prefix_length))
+        return mha(query, self.cached_key, self.cached_value, mask=mask, sm_scale=sm_scale, return_lse=return_lse)
+
+    def step(self, query, key, value, *, sm_scale: float | None = None):
+        """One decode step: append the token's key / value, then attend over the prefix."""
+        self.update(key, value)
+        return self.attend(query, sm_scale=sm_scale)

@@ -203,3 +203,34 @@ def test_missing_peer_is_reported_not_waited_for_forever():
     assert rc == 0 and L.pjx_read_status(status.data_ptr(), stream) == 0
     want, _ = oracle_fwd(q, k, v, sm_scale=0.1)
     assert_close(o, None, want, None, torch.bfloat16, "after a timed-out exchange")
+
+
+def test_decode_cache_steps_match_causal_attention():
+    """A ragged batch decoded token by token through DecodeCache (append kernel + split-KV
+    decode) equals attention over each sequence's prefix (the reference's decode branch,
+    layers/attention.py:603-675, checks its cache the same way in tests/test_attention.py)."""
+    import oracle
+
+    b, hq, hkv, d, cap = 3, 8, 2, 64, 256
+    dtype = torch.bfloat16
+    start = torch.tensor([0, 17, 100], dtype=torch.int32)
+    steps = 5
+    k_all, v_all = randn((b, cap, hkv, d), dtype, 1), randn((b, cap, hkv, d), dtype, 2)
+    q_all = randn((b, steps, hq, d), dtype, 3)
+    cache = pj.DecodeCache(b, cap, hkv, d, dtype=dtype, device=dev())
+    # prefill each sequence's prefix in one append of the longest length, then fix the positions
+    cache.update(k_all[:, :100].to(dev()), v_all[:, :100].to(dev()), advance=False)
+    cache.reset(start)
+    for t in range(steps):
+        pos = start + t
+        kn = torch.stack([k_all[i, pos[i]] for i in range(b)])[:, None].to(dev())
+        vn = torch.stack([v_all[i, pos[i]] for i in range(b)])[:, None].to(dev())
+        out = cache.step(q_all[:, t : t + 1].to(dev()), kn, vn)
+        assert cache.cache_index.tolist() == (pos + 1).tolist()
+        want = oracle.xla_attention(q_all[:, t : t + 1], k_all, v_all, kv_lengths=pos + 1, sm_scale=1 / math.sqrt(d))
+        assert float((out.float().cpu() - want.float()).abs().max()) <= 2e-2
+    assert not cache.overflowed()
+    # running past the capacity is reported, not written
+    cache.reset(torch.tensor([cap, 0, 0]))
+    cache.update(k_all[:, :1].to(dev()), v_all[:, :1].to(dev()))
+    assert cache.overflowed() and cache.cache_index.tolist() == [cap, 1, 1]
