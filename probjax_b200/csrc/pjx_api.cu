@@ -45,10 +45,12 @@ int validate_common(const void* q, const void* k, const void* v, const void* o, 
 }
 
 // Streams and events of the host-buffer call, one set per device, created on first use.
-constexpr int kHostChunks = 8;
+constexpr int kHostChunks = 8;        // batch chunks of the host-buffer pipeline
+constexpr int kHostQueryChunks = 4;   // query-row chunks inside a batch chunk
+constexpr int kHostEvents = kHostChunks * kHostQueryChunks;
 struct HostPipe {
   cudaStream_t in = nullptr, out = nullptr;
-  cudaEvent_t start = nullptr, finish = nullptr, up[kHostChunks] = {}, done[kHostChunks] = {};
+  cudaEvent_t start = nullptr, finish = nullptr, up[kHostEvents] = {}, done[kHostEvents] = {};
   bool ready = false;
 };
 std::mutex g_pipe_mu;
@@ -66,7 +68,7 @@ int host_pipe(HostPipe** out) {
     if ((rc = check_cuda(cudaStreamCreateWithFlags(&p.out, cudaStreamNonBlocking), "create download stream"))) return rc;
     if ((rc = check_cuda(cudaEventCreateWithFlags(&p.start, cudaEventDisableTiming), "create event"))) return rc;
     if ((rc = check_cuda(cudaEventCreateWithFlags(&p.finish, cudaEventDisableTiming), "create event"))) return rc;
-    for (int i = 0; i < kHostChunks; ++i) {
+    for (int i = 0; i < kHostEvents; ++i) {
       if ((rc = check_cuda(cudaEventCreateWithFlags(&p.up[i], cudaEventDisableTiming), "create event"))) return rc;
       if ((rc = check_cuda(cudaEventCreateWithFlags(&p.done[i], cudaEventDisableTiming), "create event"))) return rc;
     }
@@ -347,10 +349,15 @@ int pjx_attn_fwd_host(const void* q, const void* k, const void* v, void* o, floa
   const int64_t bbs = bias ? (bias_batch == 1 ? 0 : (int64_t)bias_heads * Lq * Lkv) : 0;
 
   // Three streams: copies in, kernels (the caller's stream), copies out. The batch is
-  // cut into chunks so that the upload of chunk c + 1 and the download of chunk c - 1
-  // overlap the kernel of chunk c (PCIe is full duplex).
+  // cut into chunks, and without a bias or an LSE result the query rows of a chunk are cut
+  // again (K and V go up once, then each block of query rows is uploaded, computed with the
+  // mask band shifted by its first row, and downloaded), so that uploads, kernels and
+  // downloads overlap (PCIe is full duplex) and only one small block trails the last upload.
   const int nchunk = B < kHostChunks ? B : kHostChunks;
   const int per = (B + nchunk - 1) / nchunk;
+  int nq = 1;
+  if (!bias && !lse) nq = Lq / 1024 < 1 ? 1 : (Lq / 1024 > kHostQueryChunks ? kHostQueryChunks : Lq / 1024);
+  const int rows_per = ((Lq + nq - 1) / nq + 255) / 256 * 256;  // whole 256-row CTAs
   if ((rc = check_cuda(cudaEventRecord(hp->start, st), "record start"))) return rc;
   if ((rc = check_cuda(cudaStreamWaitEvent(hp->in, hp->start, 0), "order upload stream"))) return rc;
   if ((rc = check_cuda(cudaStreamWaitEvent(hp->out, hp->start, 0), "order download stream"))) return rc;
@@ -359,27 +366,51 @@ int pjx_attn_fwd_host(const void* q, const void* k, const void* v, void* o, floa
   if ((rc = check_cuda(cudaMemsetAsync(ds, 0, sizeof(int32_t), hp->in), "clear status"))) return rc;
   const size_t q1 = (size_t)Lq * Hq * D * es, k1 = (size_t)Lkv * Hkv * D * es, v1 = (size_t)Lkv * Hkv * Dv * es,
                o1 = (size_t)Lq * Hq * Dv * es, l1 = (size_t)Hq * Lq * sizeof(float);
+  const size_t qrow = (size_t)Hq * D * es, orow = (size_t)Hq * Dv * es;
   int c = 0;
-  for (int b0 = 0; b0 < B; b0 += per, ++c) {
+  for (int b0 = 0; b0 < B; b0 += per) {
     const int nb_c = (b0 + per <= B) ? per : B - b0;
-    const char* hq = static_cast<const char*>(q) + b0 * q1;
     const char* hk = static_cast<const char*>(k) + b0 * k1;
     const char* hv = static_cast<const char*>(v) + b0 * v1;
-    if ((rc = check_cuda(cudaMemcpyAsync(dq + b0 * q1, hq, nb_c * q1, cudaMemcpyHostToDevice, hp->in), "copy q to device"))) return rc;
     if (k1 && (rc = check_cuda(cudaMemcpyAsync(dk + b0 * k1, hk, nb_c * k1, cudaMemcpyHostToDevice, hp->in), "copy k to device"))) return rc;
     if (v1 && (rc = check_cuda(cudaMemcpyAsync(dv + b0 * v1, hv, nb_c * v1, cudaMemcpyHostToDevice, hp->in), "copy v to device"))) return rc;
-    if ((rc = check_cuda(cudaEventRecord(hp->up[c], hp->in), "record upload"))) return rc;
-    if ((rc = check_cuda(cudaStreamWaitEvent(st, hp->up[c], 0), "wait for upload"))) return rc;
-    rc = pjx_attn_fwd(dq + b0 * q1, dk + b0 * k1, dv + b0 * v1, dout + b0 * o1,
-                      lse ? reinterpret_cast<float*>(dl + b0 * l1) : nullptr,
-                      kv_lengths ? reinterpret_cast<const int32_t*>(dn) + b0 : nullptr,
-                      bias ? reinterpret_cast<const float*>(db) + (int64_t)b0 * bbs : nullptr, bbs, bhs, nb_c, Lq, Lkv, Hq,
-                      Hkv, D, Dv, dtype, causal, sm_scale, impl, reinterpret_cast<int32_t*>(ds), stream);
-    if (rc) return rc;
-    if ((rc = check_cuda(cudaEventRecord(hp->done[c], st), "record kernel"))) return rc;
-    if ((rc = check_cuda(cudaStreamWaitEvent(hp->out, hp->done[c], 0), "wait for kernel"))) return rc;
-    if ((rc = check_cuda(cudaMemcpyAsync(static_cast<char*>(o) + b0 * o1, dout + b0 * o1, nb_c * o1, cudaMemcpyDeviceToHost, hp->out), "copy o to host"))) return rc;
-    if (lse && (rc = check_cuda(cudaMemcpyAsync(reinterpret_cast<char*>(lse) + b0 * l1, dl + b0 * l1, nb_c * l1, cudaMemcpyDeviceToHost, hp->out), "copy lse to host"))) return rc;
+    for (int l0 = 0; l0 < Lq; l0 += (nq > 1 ? rows_per : Lq), ++c) {
+      const int rows = nq > 1 ? (l0 + rows_per <= Lq ? rows_per : Lq - l0) : Lq;
+      // rows l0 .. l0+rows of every batch row of the chunk (one strided copy when the chunk holds several)
+      const char* hq = static_cast<const char*>(q) + b0 * q1 + l0 * qrow;
+      if (nq == 1) {
+        if ((rc = check_cuda(cudaMemcpyAsync(dq + b0 * q1, hq, nb_c * q1, cudaMemcpyHostToDevice, hp->in), "copy q to device"))) return rc;
+      } else if ((rc = check_cuda(cudaMemcpy2DAsync(dq + b0 * q1 + l0 * qrow, q1, hq, q1, rows * qrow, nb_c, cudaMemcpyHostToDevice, hp->in), "copy q rows to device"))) {
+        return rc;
+      }
+      if ((rc = check_cuda(cudaEventRecord(hp->up[c], hp->in), "record upload"))) return rc;
+      if ((rc = check_cuda(cudaStreamWaitEvent(st, hp->up[c], 0), "wait for upload"))) return rc;
+      if (nq == 1) {
+        rc = pjx_attn_fwd(dq + b0 * q1, dk + b0 * k1, dv + b0 * v1, dout + b0 * o1,
+                          lse ? reinterpret_cast<float*>(dl + b0 * l1) : nullptr,
+                          kv_lengths ? reinterpret_cast<const int32_t*>(dn) + b0 : nullptr,
+                          bias ? reinterpret_cast<const float*>(db) + (int64_t)b0 * bbs : nullptr, bbs, bhs, nb_c, Lq, Lkv,
+                          Hq, Hkv, D, Dv, dtype, causal, sm_scale, impl, reinterpret_cast<int32_t*>(ds), stream);
+      } else {
+        // a block of query rows per batch row: the batch rows of the chunk are launched one by one
+        // (their row blocks are not adjacent in memory)
+        for (int bi = 0; bi < nb_c && !rc; ++bi)
+          rc = pjx_attn_fwd_band(dq + (b0 + bi) * q1 + l0 * qrow, dk + (b0 + bi) * k1, dv + (b0 + bi) * v1,
+                                 dout + (b0 + bi) * o1 + l0 * orow, nullptr,
+                                 kv_lengths ? reinterpret_cast<const int32_t*>(dn) + b0 + bi : nullptr, nullptr, 0, 0, 1,
+                                 rows, Lkv, Hq, Hkv, D, Dv, dtype, PJX_BAND_NO_LOWER, causal ? l0 : PJX_BAND_NO_UPPER,
+                                 sm_scale, impl, reinterpret_cast<int32_t*>(ds), stream);
+      }
+      if (rc) return rc;
+      if ((rc = check_cuda(cudaEventRecord(hp->done[c], st), "record kernel"))) return rc;
+      if ((rc = check_cuda(cudaStreamWaitEvent(hp->out, hp->done[c], 0), "wait for kernel"))) return rc;
+      if (nq == 1) {
+        if ((rc = check_cuda(cudaMemcpyAsync(static_cast<char*>(o) + b0 * o1, dout + b0 * o1, nb_c * o1, cudaMemcpyDeviceToHost, hp->out), "copy o to host"))) return rc;
+        if (lse && (rc = check_cuda(cudaMemcpyAsync(reinterpret_cast<char*>(lse) + b0 * l1, dl + b0 * l1, nb_c * l1, cudaMemcpyDeviceToHost, hp->out), "copy lse to host"))) return rc;
+      } else if ((rc = check_cuda(cudaMemcpy2DAsync(static_cast<char*>(o) + b0 * o1 + l0 * orow, o1, dout + b0 * o1 + l0 * orow, o1, rows * orow, nb_c, cudaMemcpyDeviceToHost, hp->out), "copy o rows to host"))) {
+        return rc;
+      }
+    }
   }
   int32_t hs = 0;
   if ((rc = check_cuda(cudaMemcpyAsync(&hs, ds, sizeof(int32_t), cudaMemcpyDeviceToHost, hp->out), "copy status to host"))) return rc;

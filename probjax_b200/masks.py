@@ -537,18 +537,33 @@ def lower_bias(bias, batch: int, heads: int, q_len: int, kv_len: int):
     raise NotImplementedError(f"bias {type(bias).__name__} is not implemented by the sm_100a kernels")
 
 
+_DENSE_LEAVES = ()  # filled below, once the classes exist
+
+
+def _dense_lowerable(mask) -> bool:
+    """Mask expressions whose ``dense`` form is defined for a whole batch here (``KeyPaddingMask``
+    with per-query-row data, for one, is not)."""
+    if isinstance(mask, ComposeMask):
+        return _dense_lowerable(mask.lhs) and _dense_lowerable(mask.rhs)
+    if isinstance(mask, NotMask):
+        return _dense_lowerable(mask.inner)
+    return isinstance(mask, _DENSE_LEAVES)
+
+
 def lower_dense(mask, bias, batch: int, heads: int, q_len: int, kv_len: int):
     """Fallback lowering for masks :func:`lower_mask` refuses: the mask's dense boolean form
     becomes ``-inf`` entries of one additive float32 ``[B|1, H|1, Q, K]`` tensor, summed with
     the bias.  Rows without a visible key come out as zeros, as with the structural masks."""
-    if not isinstance(mask, AttentionMask):
+    if not _dense_lowerable(mask):
         raise NotImplementedError(f"mask {type(mask).__name__} is not implemented by the sm_100a kernels")
-    try:
-        keep = mask.dense(q_len, kv_len, batch_size=batch, num_heads=1)
-    except NotImplementedError as e:
-        raise NotImplementedError(f"mask {type(mask).__name__} has no dense form here") from e
+    keep = mask.dense(q_len, kv_len, batch_size=batch, num_heads=1)
     add = torch.zeros(keep.shape, dtype=torch.float32).masked_fill_(~keep.cpu(), float("-inf"))
     bt = lower_bias(bias, batch, heads, q_len, kv_len)
     if bt is not None:
         add = add.to(bt.device) + bt.float()
     return add
+
+
+_DENSE_LEAVES = (NoMask, CausalMask, LocalWindowMask, CausalLocalWindowMask, CausalFromBottomRightMask, QKVLengthMask,
+                 KVLenMask, PrefixLMMask, BlockDiagonalMask, BlockDiagonalCausalMask, SameSegmentMask, SeqLenMask,
+                 MarginalizationMask)
