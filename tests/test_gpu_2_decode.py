@@ -234,3 +234,44 @@ def test_decode_cache_steps_match_causal_attention():
     cache.reset(torch.tensor([cap, 0, 0]))
     cache.update(k_all[:, :1].to(dev()), v_all[:, :1].to(dev()))
     assert cache.overflowed() and cache.cache_index.tolist() == [cap, 1, 1]
+
+
+def test_decode_step_replays_as_a_cuda_graph():
+    """Append + decode is two launches without a host round trip, so a step can be captured once
+    and replayed: positions advance on the device between replays."""
+    import oracle
+
+    b, hq, hkv, d, cap = 2, 8, 2, 128, 512
+    dtype = torch.bfloat16
+    k_all, v_all = randn((b, cap, hkv, d), dtype, 1), randn((b, cap, hkv, d), dtype, 2)
+    q_all = randn((b, 8, hq, d), dtype, 3)
+    start = torch.tensor([300, 5], dtype=torch.int32)
+    cache = pj.DecodeCache(b, cap, hkv, d, dtype=dtype, device=dev())
+    cache.update(k_all[:, :300].to(dev()), v_all[:, :300].to(dev()), advance=False)
+    cache.reset(start)
+    q_in = torch.empty((b, 1, hq, d), dtype=dtype, device=dev())
+    k_in, v_in = (torch.empty((b, 1, hkv, d), dtype=dtype, device=dev()) for _ in range(2))
+
+    def feed(t):
+        pos = start + t
+        q_in.copy_(q_all[:, t : t + 1])
+        k_in.copy_(torch.stack([k_all[i, pos[i]] for i in range(b)])[:, None])
+        v_in.copy_(torch.stack([v_all[i, pos[i]] for i in range(b)])[:, None])
+
+    side = torch.cuda.Stream()
+    feed(0)
+    with torch.cuda.stream(side):  # warm-up outside the capture (workspaces, status word)
+        cache.step(q_in, k_in, v_in)
+    side.synchronize()
+    cache.reset(start)
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph, stream=side):
+        out = cache.step(q_in, k_in, v_in)
+    cache.reset(start)  # the capture itself does not run the kernels
+    for t in range(4):
+        feed(t)
+        graph.replay()
+        torch.cuda.synchronize()
+        assert cache.cache_index.tolist() == (start + t + 1).tolist()
+        want = oracle.xla_attention(q_all[:, t : t + 1], k_all, v_all, kv_lengths=start + t + 1, sm_scale=1 / math.sqrt(d))
+        assert float((out.float().cpu() - want.float()).abs().max()) <= 2e-2
