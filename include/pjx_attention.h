@@ -117,13 +117,15 @@ int pjx_attn_bwd(const void* q, const void* k, const void* v, const void* o, con
 /* The same for the band form of the mask (see pjx_attn_fwd_band).  `impl` picks the
  * kernels as in the forward: AUTO runs the tcgen05 dQ and dK/dV kernels for 16-bit
  * inputs with D = Dv in {64, 128} and no bias, the CUDA-core kernels otherwise;
- * `status` as in pjx_attn_fwd. */
+ * `status` as in pjx_attn_fwd.  `dbias` (float32, shape and strides of `bias`, or NULL) receives
+ * the gradient of a learnable dense bias, summed over the axes the bias broadcasts (with
+ * atomic adds there, so that sum is not bit-repeatable). */
 int pjx_attn_bwd_band(const void* q, const void* k, const void* v, const void* o, const float* lse,
                       const void* d_o, void* dq, void* dk, void* dv, const int32_t* kv_lengths,
-                      const float* bias, int64_t bias_batch_stride, int64_t bias_head_stride, int B,
-                      int Lq, int Lkv, int Hq, int Hkv, int D, int Dv, int dtype, int band_lo,
-                      int band_hi, float sm_scale, int impl, void* workspace, size_t workspace_bytes,
-                      int32_t* status, void* stream);
+                      const float* bias, int64_t bias_batch_stride, int64_t bias_head_stride,
+                      float* dbias, int B, int Lq, int Lkv, int Hq, int Hkv, int D, int Dv, int dtype,
+                      int band_lo, int band_hi, float sm_scale, int impl, void* workspace,
+                      size_t workspace_bytes, int32_t* status, void* stream);
 size_t pjx_attn_bwd_workspace_bytes(int B, int Lq, int Hq);
 
 /*

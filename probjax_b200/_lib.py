@@ -29,7 +29,7 @@ SIGNATURES = {
                           _i, _i, _i, _i, _i, _i, _i, _i, _i, _f, _i, _vp, _vp]),
     "pjx_attn_fwd_band": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64,
                                _i, _i, _i, _i, _i, _i, _i, _i, _i, _i, _f, _i, _vp, _vp]),
-    "pjx_attn_bwd_band": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64,
+    "pjx_attn_bwd_band": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _vp,
                                _i, _i, _i, _i, _i, _i, _i, _i, _i, _i, _f, _i, _vp, _sz, _vp, _vp]),
     "pjx_attn_jvp_band": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64,
                                _i, _i, _i, _i, _i, _i, _i, _i, _i, _i, _f, _vp]),

@@ -184,9 +184,10 @@ def attention_forward(q, k, v, *, causal=False, band=None, kv_lengths=None, bias
 
 
 def attention_backward(q, k, v, o, lse, d_o, *, causal=False, band=None, kv_lengths=None, bias=None,
-                       sm_scale=1.0, impl=None):
+                       sm_scale=1.0, impl=None, bias_grad=False):
     """One ``pjx_attn_bwd_band`` call on CUDA tensors: ``(dq, dk, dv)`` for the forward
-    that produced ``o`` and ``lse`` from the same arguments."""
+    that produced ``o`` and ``lse`` from the same arguments; with ``bias_grad`` also the
+    gradient of the dense bias (float32, the bias' shape)."""
     _require_gpu()
     band_lo, band_hi = _band_args(causal, band)
     dev = q.device
@@ -202,15 +203,20 @@ def attention_backward(q, k, v, o, lse, d_o, *, causal=False, band=None, kv_leng
         bt = _as_tensor(bias).to(device=dev, dtype=torch.float32).contiguous()
         bs = 0 if bt.shape[0] == 1 else bt.stride(0)
         hs = 0 if bt.shape[1] == 1 else bt.stride(1)
+    dbias = None
+    if bias_grad:
+        if bt is None:
+            raise ValueError("bias_grad needs a bias")
+        dbias = torch.empty_like(bt)
     L = _lib.lib()
     ws = _scratch_bytes(dev, "bwd", L.pjx_attn_bwd_workspace_bytes(B, Lq, Hq))
     with torch.cuda.device(dev):
         rc = L.pjx_attn_bwd_band(_ptr(q), _ptr(k), _ptr(v), _ptr(o), _ptr(lse), _ptr(d_o), _ptr(dq), _ptr(dk),
-                                 _ptr(dv), _ptr(kvl), _ptr(bt), bs, hs, B, Lq, Lkv, Hq, Hkv, D, Dv,
+                                 _ptr(dv), _ptr(kvl), _ptr(bt), bs, hs, _ptr(dbias), B, Lq, Lkv, Hq, Hkv, D, Dv,
                                  _DTYPES[q.dtype], band_lo, band_hi, float(sm_scale), _IMPL[impl], _ptr(ws),
                                  ws.numel(), _ptr(_status_word(dev)), _stream(dev))
     _lib.check(rc)
-    return dq, dk, dv
+    return (dq, dk, dv, dbias) if bias_grad else (dq, dk, dv)
 
 
 def attention_jvp(q, k, v, lse, tq=None, tk=None, tv=None, *, causal=False, band=None, kv_lengths=None, bias=None,
@@ -268,10 +274,12 @@ class _AttentionFunction(torch.autograd.Function):
     def backward(ctx, d_o, _d_lse):
         q, k, v, o, lse = ctx.saved_tensors
         band, kv_lengths, bias, sm_scale, impl = ctx.args
+        want_dbias = bias is not None and ctx.needs_input_grad[5]
         # a forced tensor-core forward does not force the tensor-core backward, which takes fewer shapes
-        dq, dk, dv = attention_backward(q, k, v, o, lse, d_o, band=band, kv_lengths=kv_lengths, bias=bias,
-                                        sm_scale=sm_scale, impl=impl if impl == "b200:generic" else None)
-        return dq, dk, dv, None, None, None, None, None
+        grads = attention_backward(q, k, v, o, lse, d_o, band=band, kv_lengths=kv_lengths, bias=bias, sm_scale=sm_scale,
+                                   impl=impl if impl == "b200:generic" else None, bias_grad=want_dbias)
+        dbias = grads[3].to(bias.dtype) if want_dbias else None
+        return grads[0], grads[1], grads[2], None, None, dbias, None, None
 
 
 def _wants_grad(*tensors) -> bool:
@@ -409,10 +417,8 @@ def mha(q, k, v, mask: AttentionMask | None = None, bias: AttentionBias | None =
         bt = lower_bias(bias, B, q.shape[2], Lq, k.shape[1])
     else:  # mask classes without a native form: their dense -inf tensor rides on the bias
         bt = lower_dense(residual, bias, B, q.shape[2], Lq, k.shape[1])
-    if _wants_grad(q, k, v):
+    if _wants_grad(q, k, v, bt):
         # differentiation always runs the regular kernels (attention_splitkv.py:253-272)
-        if bt is not None and bt.requires_grad:
-            raise NotImplementedError("gradients of a DenseBias are not implemented")
         if not q.is_cuda:
             raise NotImplementedError("differentiable attention takes CUDA tensors")
         if lm.q_limit is not None:
@@ -600,8 +606,6 @@ def mla(q, cache, wk=None, wv=None, *, mask=None, bias=None, rng=None, sm_scale:
         # Differentiation goes through the materialized K and V and the regular attention kernels, as
         # in the reference (latent_attention.py:554-585); the up-projections and their gradients are
         # plain library matrix products here.
-        if bt is not None and bt.requires_grad:
-            raise NotImplementedError("gradients of a DenseBias are not implemented")
         if lm.q_limit is not None:
             raise NotImplementedError("gradients under a query-length mask are not implemented")
         if wk is not None:

@@ -167,6 +167,21 @@ __global__ void __launch_bounds__(NT) bwd_dq_kernel(const BwdParams p) {
     __syncthreads();
     tile_p_ds(p, t, b, h, q0, k0, kv_len);
     __syncthreads();
+    if (p.dbias) {  // d(loss)/d(bias_ij) = dS_ij (the bias enters the score unscaled)
+      float* db = p.dbias + (int64_t)b * p.bias_bs + (int64_t)h * p.bias_hs;
+#pragma unroll
+      for (int i = 0; i < 2; ++i)
+#pragma unroll
+        for (int c = 0; c < 2; ++c) {
+          const int r = ty * 2 + i, col = tx + 16 * c;
+          const int qi = q0 + r, kj = k0 + col;
+          if (qi < p.Lq && kj < p.Lkv) {
+            const float g = t.dSs[r * (T + 1) + col];
+            if (p.dbias_atomic) atomicAdd(&db[(int64_t)qi * p.Lkv + kj], g);
+            else db[(int64_t)qi * p.Lkv + kj] = g;
+          }
+        }
+    }
     for (int c = 0; c < T; ++c) {
       const float d0 = t.dSs[(ty * 2) * (T + 1) + c], d1 = t.dSs[(ty * 2 + 1) * (T + 1) + c];
 #pragma unroll
@@ -503,9 +518,9 @@ size_t pjx_attn_bwd_workspace_bytes(int B, int Lq, int Hq) {
 
 int pjx_attn_bwd_band(const void* q, const void* k, const void* v, const void* o, const float* lse, const void* d_o,
                       void* dq, void* dk, void* dv, const int32_t* kv_lengths, const float* bias,
-                      int64_t bias_batch_stride, int64_t bias_head_stride, int B, int Lq, int Lkv, int Hq, int Hkv,
-                      int D, int Dv, int dtype, int band_lo, int band_hi, float sm_scale, int impl, void* workspace,
-                      size_t workspace_bytes, int32_t* status, void* stream) {
+                      int64_t bias_batch_stride, int64_t bias_head_stride, float* dbias, int B, int Lq, int Lkv, int Hq,
+                      int Hkv, int D, int Dv, int dtype, int band_lo, int band_hi, float sm_scale, int impl,
+                      void* workspace, size_t workspace_bytes, int32_t* status, void* stream) {
   if (impl != PJX_IMPL_AUTO && impl != PJX_IMPL_GENERIC && impl != PJX_IMPL_SM100)
     return fail(PJX_ERR_BAD_ARG, "impl must be 0 (auto), 1 (generic) or 2 (tcgen05), got %d", impl);
   if (dtype != PJX_F32 && dtype != PJX_BF16 && dtype != PJX_F16)
@@ -537,6 +552,16 @@ int pjx_attn_bwd_band(const void* q, const void* k, const void* v, const void* o
   p.dtype = dtype;
   p.status = status;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (dbias) {
+    if (!bias) return fail(PJX_ERR_BAD_ARG, "backward: dbias given without a bias");
+    if (bias_batch_stride < 0 || bias_head_stride < 0) return fail(PJX_ERR_BAD_ARG, "bias strides must be non-negative");
+    // the bias is [Bb, Hb, Lq, Lkv] with Bb in {1, B}, Hb in {1, Hq}: its extent follows from the strides
+    const int64_t hb = bias_head_stride ? Hq : 1, bbn = bias_batch_stride ? B : 1;
+    int rc0 = check_cuda(cudaMemsetAsync(dbias, 0, (size_t)bbn * hb * Lq * Lkv * sizeof(float), st), "clear dbias");
+    if (rc0) return rc0;
+    p.dbias = dbias;
+    p.dbias_atomic = (bias_batch_stride == 0 && B > 1) || (bias_head_stride == 0 && Hq > 1);
+  }
   if (Lq == 0) {  // no queries: the key-side gradients are zero
     int rc = check_cuda(cudaMemsetAsync(dk, 0, (size_t)B * Lkv * Hkv * D * dtype_size(dtype), st), "clear dk");
     if (rc) return rc;
@@ -557,8 +582,8 @@ int pjx_attn_bwd(const void* q, const void* k, const void* v, const void* o, con
                  void* dq, void* dk, void* dv, const int32_t* kv_lengths, const float* bias,
                  int64_t bias_batch_stride, int64_t bias_head_stride, int B, int Lq, int Lkv, int Hq, int Hkv, int D,
                  int Dv, int dtype, int causal, float sm_scale, void* workspace, size_t workspace_bytes, void* stream) {
-  return pjx_attn_bwd_band(q, k, v, o, lse, d_o, dq, dk, dv, kv_lengths, bias, bias_batch_stride, bias_head_stride, B,
-                           Lq, Lkv, Hq, Hkv, D, Dv, dtype, PJX_BAND_NO_LOWER, causal ? 0 : PJX_BAND_NO_UPPER, sm_scale,
+  return pjx_attn_bwd_band(q, k, v, o, lse, d_o, dq, dk, dv, kv_lengths, bias, bias_batch_stride, bias_head_stride,
+                           nullptr, B, Lq, Lkv, Hq, Hkv, D, Dv, dtype, PJX_BAND_NO_LOWER, causal ? 0 : PJX_BAND_NO_UPPER, sm_scale,
                            PJX_IMPL_AUTO, workspace, workspace_bytes, nullptr, stream);
 }
 

@@ -85,7 +85,7 @@ struct Cfg {
   static constexpr int BIAS_TILE_BYTES = BIAS_STAGED ? (BN / 32) * BM * 128 : 0;
   static constexpr int OFF_BIAS = OFF_V + VST * V_TILE_BYTES;
   static constexpr int OFF_BAR = OFF_BIAS + 2 * BIAS_TILE_BYTES;
-  static constexpr int N_BAR = 2 + 2 * KST + 2 * VST + 6 + 4;
+  static constexpr int N_BAR = 2 + 2 * KST + 2 * VST + 6 + 4 + 2;
   static constexpr int SMEM_BYTES = OFF_BAR + N_BAR * 8 + 16 + 1024;  // + alignment slack
   static constexpr int TMEM_USED = 2 * BN + 2 * DV;
   static constexpr int TMEM_COLS = TMEM_USED <= 128 ? 128 : (TMEM_USED <= 256 ? 256 : 512);
@@ -139,7 +139,7 @@ template <int DQK, int DV, int BN, int KST, int VST, bool BF16, int BIAS, bool B
 __global__ void __launch_bounds__(NTHREADS, 1)
 attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                       const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_b,
-                      const FwdParams p, const int order_w) {
+                      const __grid_constant__ CUtensorMap tm_o, const FwdParams p, const int order_w) {
   constexpr bool HAS_BIAS = BIAS != 0;
   using C = Cfg<DQK, DV, BN, KST, VST, BIAS == 2>;
   extern __shared__ unsigned char smem_unaligned[];
@@ -158,6 +158,7 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
   const int O_FULL = P_FULL + 2;          // [2]
   const int B_FULL = O_FULL + 2;          // [2] staged bias tile landed
   const int B_EMPTY = B_FULL + 2;         // [2] staged bias tile consumed (128 arrivals)
+  const int O_STAGED = B_EMPTY + 2;       // [2] output tile written to shared memory (128 arrivals)
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + C::OFF_BAR + C::N_BAR * 8);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
@@ -229,7 +230,7 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
 #endif
     PJX_CTA_AT(1);
     for (int i = 0; i < C::N_BAR; ++i)
-      mbar_init(BAR(i), ((i >= P_FULL && i < P_FULL + 2) || i >= B_EMPTY) ? 128u : 1u);
+      mbar_init(BAR(i), ((i >= P_FULL && i < P_FULL + 2) || i >= B_EMPTY) ? 128u : 1u);  // B_EMPTY, O_STAGED: 128
     *abort_flag = 0;
     fence_barrier_init();
   }
@@ -519,7 +520,11 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
       if (ok) {
         tc_fence_after();
         if (threadIdx.x == 320 - 128) PJX_CTA_AT(4);
-        unsigned char* orow = static_cast<unsigned char*>(p.o) + ((((int64_t)b * p.Lq + row) * p.Hq + h) * DV) * 2;
+        // O leaves through shared memory: every thread writes its row (16-bit, 128-byte-swizzled
+        // like the tensor map expects) over the query tile, which the MMAs no longer read, and one
+        // thread hands the tile to a TMA store, which clips rows past Lq. Stores straight from the
+        // registers would touch 32 separate rows per instruction.
+        const uint32_t stage = sbase + C::OFF_Q + t * C::Q_TILE_BYTES;
 #pragma unroll
         for (int c = 0; c < DV / 32; ++c) {
           float o[32];
@@ -530,18 +535,26 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
 #pragma unroll
             for (int i = 0; i < 32; ++i) o[i] = 0.f;
           }
-          if (row_ok) {
-            uint4* dst = reinterpret_cast<uint4*>(orow + c * 64);
+          // columns 32c .. 32c+31 = 16-byte units 4(c%2) .. 4(c%2)+3 of the 128-byte row in block c/2
+          const uint32_t rbase = stage + (c >> 1) * (BM * 128) + r_in * 128;
 #pragma unroll
-            for (int i = 0; i < 4; ++i) {
-              uint4 w;
-              w.x = pack16<BF16>(o[8 * i + 0] * inv, o[8 * i + 1] * inv);
-              w.y = pack16<BF16>(o[8 * i + 2] * inv, o[8 * i + 3] * inv);
-              w.z = pack16<BF16>(o[8 * i + 4] * inv, o[8 * i + 5] * inv);
-              w.w = pack16<BF16>(o[8 * i + 6] * inv, o[8 * i + 7] * inv);
-              dst[i] = w;
-            }
+          for (int i = 0; i < 4; ++i) {
+            const uint32_t unit = static_cast<uint32_t>((c & 1) * 4 + i) ^ static_cast<uint32_t>(r_in & 7);
+            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};\n" ::"r"(rbase + unit * 16),
+                         "r"(pack16<BF16>(o[8 * i + 0] * inv, o[8 * i + 1] * inv)),
+                         "r"(pack16<BF16>(o[8 * i + 2] * inv, o[8 * i + 3] * inv)),
+                         "r"(pack16<BF16>(o[8 * i + 4] * inv, o[8 * i + 5] * inv)),
+                         "r"(pack16<BF16>(o[8 * i + 6] * inv, o[8 * i + 7] * inv))
+                         : "memory");
           }
+        }
+        fence_proxy_async();
+        mbar_arrive(BAR(O_STAGED + t));
+        if (r_in == 0 && mbar_wait(BAR(O_STAGED + t), 0, abort_flag)) {
+#pragma unroll
+          for (int s = 0; s < DV / 64; ++s) tma_store_4d(&tm_o, stage + s * (BM * 128), s * 64, h, q0 + t * BM, b);
+          tma_store_commit();
+          tma_store_wait_read();
         }
         if (p.lse && row_ok)
           p.lse[((int64_t)b * p.Hq + h) * p.Lq + row] = l > 0.f ? (m_ref + log2f(l)) * kLn2 : INFINITY;
@@ -633,6 +646,8 @@ int launch_one(const FwdParams& p, int dtype, cudaStream_t stream) {
   } else {
     tb = tq;  // unused
   }
+  CUtensorMap to;
+  if ((rc = make_tmap_blhd(&to, p.o, dtype, p.B, p.Lq, p.Hq, DV, BM))) return rc;
   auto kern = attn_fwd_sm100_kernel<DQK, DV, BN, KST, VST, BF16, BIAS, BAND>;
   if ((rc = check_cuda(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES),
                        "cudaFuncSetAttribute(sm100 fwd)")))
@@ -640,7 +655,7 @@ int launch_one(const FwdParams& p, int dtype, cudaStream_t stream) {
   dim3 grid((unsigned)(((p.Lq + 2 * BM - 1) / (2 * BM)) * (int64_t)p.Hq * p.B));
   // triangular work (an upper bound on the keys only): heavy-first order in blocks of 16 pairs
   const int order_w = (p.band_hi < PJX_BAND_NO_UPPER && p.band_lo == PJX_BAND_NO_LOWER) ? 16 : 1;
-  kern<<<grid, NTHREADS, C::SMEM_BYTES, stream>>>(tq, tk, tv, tb, p, order_w);
+  kern<<<grid, NTHREADS, C::SMEM_BYTES, stream>>>(tq, tk, tv, tb, to, p, order_w);
   count_launch();
   return check_cuda(cudaGetLastError(), "sm100 forward launch");
 }

@@ -108,6 +108,8 @@ struct BwdParams {
   const int32_t* kv_lengths;
   const float* bias;
   int64_t bias_bs, bias_hs;
+  float* dbias = nullptr;     // gradient of the bias, same shape and strides, zeroed by the caller; or null
+  bool dbias_atomic = false;  // a broadcast axis: several (batch, head) pairs add into one entry
   int B, Lq, Lkv, Hq, Hkv, D, Dv;
   int band_lo, band_hi;  // key j is visible to query i iff i + band_lo <= j <= i + band_hi
   float sm_scale;

@@ -94,9 +94,36 @@ def test_zero_length_rows_and_no_grad_paths():
     with torch.no_grad():
         out2 = pj.flex_attention(qd, kd, vd, mask=pj.KVLenMask(lens), sm_scale=0.25)
     assert not out2.requires_grad and torch.equal(out2, out.detach())
-    with pytest.raises(NotImplementedError, match="DenseBias"):
-        bias = torch.zeros(1, 2, 9, 9, device=dvc, requires_grad=True)
-        pj.flex_attention(qd, kd, vd, bias=pj.DenseBias(bias), sm_scale=0.25)
+
+
+@pytest.mark.parametrize("bshape", [(1, 4, 40, 56), (2, 1, 40, 56), (2, 4, 40, 56), (1, 1, 40, 56)])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_gradient_of_a_learnable_dense_bias(bshape, dtype):
+    """d(loss)/d(bias) = dS, summed over the axes the bias broadcasts (configuration 3 of the
+    benchmark set has a learnable fp32 bias [H, Sq, Skv])."""
+    dvc = dev()
+    b, hq, hkv, lq, lkv, d = 2, 4, 2, 40, 56, 32
+    q, k, v = randn((b, lq, hq, d), dtype, 1), randn((b, lkv, hkv, d), dtype, 2), randn((b, lkv, hkv, d), dtype, 3)
+    g = randn((b, lq, hq, d), dtype, 4)
+    bias = randn(bshape, torch.float32, 5)
+    lens = torch.tensor([lkv, 30], dtype=torch.int32)
+    sc = 1 / math.sqrt(d)
+    qd, kd, vd = (x.to(dvc).requires_grad_(True) for x in (q, k, v))
+    bd = bias.to(dvc).requires_grad_(True)
+    out = pj.flex_attention(qd, kd, vd, mask=pj.CausalMask() & pj.KVLenMask(lens), bias=pj.DenseBias(bd), sm_scale=sc,
+                            enable_gqa=True)
+    out.backward(g.to(dvc))
+    q64, k64, v64, b64 = (x.double().requires_grad_(True) for x in (q, k, v, bias))
+    ref = _dense(q64, k64, v64, True, lens, b64, sc)
+    ref.backward(g.double())
+    tol = 1e-4 if dtype == torch.float32 else 2e-2
+    assert bd.grad is not None and bd.grad.shape == bias.shape
+    assert _rel(bd.grad, b64.grad) < tol, _rel(bd.grad, b64.grad)
+    assert _rel(qd.grad, q64.grad) < tol and _rel(kd.grad, k64.grad) < tol and _rel(vd.grad, v64.grad) < tol
+    # only the bias asks for a gradient
+    bd2 = bias.to(dvc).requires_grad_(True)
+    pj.flex_attention(q.to(dvc), k.to(dvc), v.to(dvc), bias=pj.DenseBias(bd2), sm_scale=sc, enable_gqa=True).sum().backward()
+    assert bd2.grad is not None and torch.isfinite(bd2.grad).all()
 
 
 def _grads64(q, k, v, g, keep, sc):
