@@ -262,6 +262,8 @@ def main():
         import torch.distributed as dist
 
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        if os.environ.get("NCCL_DEBUG", "").upper() in ("", "VERSION"):
+            os.environ["NCCL_DEBUG"] = "WARN"  # no version banner on stdout: rank 0 prints one JSON line
         dist.init_process_group("nccl", device_id=dev)
     pk = peaks()
 
