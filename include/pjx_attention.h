@@ -259,6 +259,18 @@ int pjx_kv_cache_append(void* k_cache, void* v_cache, const void* k_new, const v
                         int dtype, int advance, int32_t* overflow, void* stream);
 
 /*
+ * Interleaved rotary position embedding of x [outer, T, H, D] into y (may alias x): pairs
+ * (x[2i], x[2i+1]) with 2i < rotary_dim are rotated by pos * base^(-2i / rotary_dim); pos is
+ * positions[t] (float32 [T]) or t + offset when positions is NULL.
+ *
+ * Replaces the rotary layer applied to queries / keys and to the latent layer's decoupled
+ * rotary key (probjax/nn/layers/encoding.py:171-211, probjax/nn/layers/latent_attention.py:
+ * 424-481).
+ */
+int pjx_rope_interleaved(const void* x, void* y, const float* positions, float offset, int64_t outer,
+                         int T, int H, int D, int rotary_dim, float base, int dtype, void* stream);
+
+/*
  * Latent attention forward: q over a shared latent cache with per-head
  * up-projections (wk, wv both given) or with K = V = cache (both NULL).
  *

@@ -26,6 +26,7 @@ SOURCES = [
     "attn_fwd_sm100.cu",
     "attn_decode.cu",
     "kv_cache.cu",
+    "rope.cu",
     "gemm_sm100.cu",
 ]
 

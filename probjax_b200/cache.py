@@ -88,3 +88,26 @@ class DecodeCache:
         """One decode step: append the token's key / value, then attend over the prefix."""
         self.update(key, value)
         return self.attend(query, sm_scale=sm_scale)
+
+
+def rope_interleaved(x: torch.Tensor, positions=None, *, base: float = 10_000.0, rotary_dim: int | None = None,
+                     offset: float = 0.0, out: torch.Tensor | None = None) -> torch.Tensor:
+    """Interleaved rotary embedding of ``x [..., T, H, D]`` on the device (``pjx_rope_interleaved``):
+    the reference's rotary layer (layers/encoding.py:171-211) with its ``rotary_dim`` / ``offset``
+    options; ``positions`` is ``[T]`` or ``None`` (= ``arange(T) + offset``)."""
+    _require_gpu()
+    if not x.is_cuda or x.dim() < 3:
+        raise ValueError("rope_interleaved takes a CUDA tensor [..., T, H, D]")
+    x = x.contiguous()
+    T, H, D = x.shape[-3:]
+    outer = x.numel() // max(T * H * D, 1)
+    rotary_dim = D if rotary_dim is None else int(rotary_dim)
+    y = torch.empty_like(x) if out is None else out
+    pos = None if positions is None else torch.as_tensor(positions).to(device=x.device, dtype=torch.float32).contiguous()
+    if pos is not None and pos.numel() != T:
+        raise ValueError(f"positions must have {T} entries, got {pos.numel()}")
+    with torch.cuda.device(x.device):
+        rc = _lib.lib().pjx_rope_interleaved(_ptr(x), _ptr(y), _ptr(pos), float(offset), outer, T, H, D, rotary_dim,
+                                             float(base), _DTYPES[x.dtype], _stream(x.device))
+    _lib.check(rc)
+    return y

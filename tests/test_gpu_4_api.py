@@ -195,3 +195,27 @@ def test_full_size_latent_attention():
     key, value = oracle.materialize_kv(c["cache"][:1], c["wk"], c["wv"], 16)
     rows = [0, 1, 127, 128, 700, 2047]
     _row_sample_check(c["q"][:1], key, value, out[:1], lse[:1], rows, True, c["sm_scale"])
+
+
+@pytest.mark.parametrize("dtype,shape,rot", [
+    (torch.float32, (2, 300, 3, 64), None),
+    (torch.bfloat16, (1, 2048, 1, 64), None),      # the decoupled rotary key of the latent configuration
+    (torch.float16, (2, 100, 4, 128), 64),         # partial rotary width: the tail is copied
+])
+def test_rope_interleaved_matches_the_oracle(dtype, shape, rot):
+    """pjx_rope_interleaved against the oracle's restatement of layers/encoding.py:171-211."""
+    x = randn(shape, dtype, 7)
+    got = pj.rope_interleaved(x.to(dev()), rotary_dim=rot)
+    want = x.clone().float()
+    r = shape[-1] if rot is None else rot
+    want[..., :r] = oracle.rope_interleaved(x[..., :r].float())
+    # fp32 angles of a few thousand radians: the device's sin / cos arguments differ from the host's in the last bits
+    tol = 2e-3 if dtype == torch.float32 else 3e-2
+    assert float((got.float().cpu() - want).abs().max()) <= tol
+    if rot is not None:
+        assert torch.equal(got[..., r:].cpu(), x[..., r:])
+    # explicit positions and an offset agree with each other
+    pos = torch.arange(shape[1], dtype=torch.float32) + 5.0
+    a = pj.rope_interleaved(x.to(dev()), positions=pos, rotary_dim=rot)
+    b = pj.rope_interleaved(x.to(dev()), offset=5.0, rotary_dim=rot)
+    assert torch.equal(a, b)
