@@ -359,6 +359,17 @@ def main():
             del o_b, lse_b, g_b, o_c, lse_c
         except Exception as e:
             extras["backward"] = {"error": str(e)[:300]}
+        try:  # fused QKV projection of the headline shape: [B*S, d_model] x [(Hq + 2 Hkv) * D, d_model]^T
+            d_model = 4096
+            m_rows, n_out = args.batch * C2["S"], (C2["Hq"] + 2 * C2["Hkv"]) * C2["D"]
+            xg = torch.randn((m_rows, d_model), device=dev).bfloat16()
+            wg = (torch.randn((n_out, d_model), device=dev) / 64).bfloat16()
+            extras["qkv_projection"] = bench_extra(
+                "linear", lambda: pj.linear(xg, wg), xs, xw, 2.0 * m_rows * n_out * d_model / 1e12, "TFLOP/s",
+                pk["bf16_tflops"], "tensor", pk["source"])
+            del xg, wg
+        except Exception as e:
+            extras["qkv_projection"] = {"error": str(e)[:300]}
         try:  # configuration 1: exact fp32 causal MHA, latency-bound (time and parity only)
             c1 = oracle.make_config(1)
             q1, k1, v1 = c1["q"].to(dev), c1["k"].to(dev), c1["v"].to(dev)

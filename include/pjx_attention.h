@@ -259,6 +259,18 @@ int pjx_kv_cache_append(void* k_cache, void* v_cache, const void* k_new, const v
                         int dtype, int advance, int32_t* overflow, void* stream);
 
 /*
+ * y [M, N] = x [M, K] . w [N, K]^T, fp32 accumulation, y in `dtype`: a bias-free linear layer
+ * with the weight stored [out, in].  16-bit inputs with K >= 64, K % 8 == 0 and 16-byte aligned
+ * operands run the persistent tcgen05 kernel (the one behind pjx_mla_fwd's up-projections),
+ * anything else a CUDA-core kernel.
+ *
+ * Replaces the query / key / value / output projections around the attention call
+ * (probjax/nn/layers/attention.py:591-594 and the output projection at the end of `__call__`).
+ */
+int pjx_linear(const void* x, const void* w, void* y, int64_t M, int N, int K, int dtype, int impl,
+               int32_t* status, void* stream);
+
+/*
  * Interleaved rotary position embedding of x [outer, T, H, D] into y (may alias x): pairs
  * (x[2i], x[2i+1]) with 2i < rotary_dim are rotated by pos * base^(-2i / rotary_dim); pos is
  * positions[t] (float32 [T]) or t + offset when positions is NULL.

@@ -17,7 +17,7 @@ import math
 import torch
 
 from . import _lib
-from .attention import _DTYPES, _ptr, _require_gpu, _stream, mha
+from .attention import _DTYPES, _IMPL, _ptr, _require_gpu, _status_word, _stream, mha
 from .masks import CausalFromBottomRightMask, KVLenMask
 
 
@@ -111,3 +111,22 @@ def rope_interleaved(x: torch.Tensor, positions=None, *, base: float = 10_000.0,
                                              float(base), _DTYPES[x.dtype], _stream(x.device))
     _lib.check(rc)
     return y
+
+
+def linear(x: torch.Tensor, weight: torch.Tensor, *, implementation: str | None = None) -> torch.Tensor:
+    """``x [..., K] @ weight[N, K]^T`` on the device (``pjx_linear``): the bias-free query / key /
+    value / output projections around the attention call (layers/attention.py:591-594).  A fused
+    QKV projection is one call with the three weights concatenated along ``N``."""
+    _require_gpu()
+    if not x.is_cuda or x.dtype != weight.dtype or x.shape[-1] != weight.shape[-1] or weight.dim() != 2:
+        raise ValueError("linear takes CUDA tensors x [..., K] and weight [N, K] of one dtype")
+    if implementation not in _IMPL:
+        raise ValueError(f"implementation must be None or one of {sorted(k for k in _IMPL if k)}")
+    x2 = x.contiguous().view(-1, x.shape[-1])
+    w = weight.to(x.device).contiguous()
+    y = torch.empty((x2.shape[0], w.shape[0]), dtype=x.dtype, device=x.device)
+    with torch.cuda.device(x.device):
+        rc = _lib.lib().pjx_linear(_ptr(x2), _ptr(w), _ptr(y), x2.shape[0], w.shape[0], w.shape[1], _DTYPES[x.dtype],
+                                   _IMPL[implementation], _ptr(_status_word(x.device)), _stream(x.device))
+    _lib.check(rc)
+    return y.view(*x.shape[:-1], w.shape[0])

@@ -143,6 +143,18 @@ int pjx_attn_fwd(const void* q, const void* k, const void* v, void* o, float* ls
                            status, stream);
 }
 
+int pjx_linear(const void* x, const void* w, void* y, int64_t M, int N, int K, int dtype, int impl, int32_t* status,
+               void* stream) {
+  if (dtype != PJX_F32 && dtype != PJX_BF16 && dtype != PJX_F16)
+    return fail(PJX_ERR_BAD_ARG, "dtype must be float32, bfloat16 or float16 (got code %d)", dtype);
+  if (M < 0 || N < 0 || K < 1) return fail(PJX_ERR_BAD_ARG, "linear: negative dimension or K < 1");
+  if (impl != PJX_IMPL_AUTO && impl != PJX_IMPL_GENERIC && impl != PJX_IMPL_SM100)
+    return fail(PJX_ERR_BAD_ARG, "impl must be 0 (auto), 1 (generic) or 2 (tcgen05), got %d", impl);
+  if (M == 0 || N == 0) return PJX_OK;
+  if (!x || !w || !y) return fail(PJX_ERR_BAD_ARG, "linear: null buffer");
+  return launch_gemm_tn2(x, w, y, N, nullptr, nullptr, 0, M, K, dtype, impl, status, static_cast<cudaStream_t>(stream));
+}
+
 int pjx_attn_decode_default_split_len(int B, int Hkv, int capacity) {
   // Measured on B200 (B=16, Hkv=8, caches of 4k..32k keys): CTAs that stream at least
   // ~2048 keys amortise their pipeline fill and merge; more than ~3.5 waves of the 296

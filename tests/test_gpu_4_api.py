@@ -219,3 +219,15 @@ def test_rope_interleaved_matches_the_oracle(dtype, shape, rot):
     a = pj.rope_interleaved(x.to(dev()), positions=pos, rotary_dim=rot)
     b = pj.rope_interleaved(x.to(dev()), offset=5.0, rotary_dim=rot)
     assert torch.equal(a, b)
+
+
+@pytest.mark.parametrize("dtype,m,n,k", [(torch.bfloat16, 300, 520, 192), (torch.float16, 1000, 256, 64), (torch.float32, 70, 33, 20)])
+def test_linear_projection(dtype, m, n, k):
+    """pjx_linear (the projections around the attention call) against a float64 product."""
+    x, w = randn((2, m // 2, k), dtype, 1), (randn((n, k), dtype, 2) / math.sqrt(k)).to(dtype)
+    got = pj.linear(x.to(dev()), w.to(dev()))
+    pj.check_status()
+    want = x.double() @ w.double().t()
+    assert got.shape == (2, m // 2, n)
+    tol = 1e-5 if dtype == torch.float32 else 2e-2
+    assert float((got.double().cpu() - want).abs().max()) <= tol
