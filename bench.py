@@ -320,9 +320,9 @@ def main():
                    "parallelism": f"batch-sharded x{world}, no collective" if world > 1 else "single GPU"},
         "roofline": {"bound": "tensor", "achieved": per_gpu, "peak": pk["bf16_tflops"], "unit": "TFLOP/s",
                      "frac": per_gpu / pk["bf16_tflops"],
-                     # DRAM bytes per launch from the ncu capture summarised under profiles/ (133 MB at B=2,
+                     # DRAM bytes per launch from the ncu capture summarised under profiles/ (135 MB at B=2,
                      # proportional to the batch)
-                     "traffic": 66.5e6 * args.batch, "traffic_unit": "bytes per launch (ncu dram read+write, scaled from B=2)",
+                     "traffic": 67.5e6 * args.batch, "traffic_unit": "bytes per launch (ncu dram read+write, scaled from B=2)",
                      "of": f"{pk['source']} burst bf16 peak", "kernel": "attn_fwd_sm100_kernel<128,128,128,2,2,bf16>",
                      "frac_of_sustained": per_gpu / pk["bf16_tflops_sustained"]},
         "e2e": e2e, "gpu_launches": int(launches_per_step * args.steps), "clocks": clocks,

@@ -67,6 +67,25 @@ def test_abi_validation_without_a_gpu(built_lib):
     assert rc == _lib.PJX_ERR_BAD_ARG and "multiple of 64" in _lib.last_error()
     rc = L.pjx_attn_decode_splitkv(16, 16, 16, None, 16, None, 1, 1, 8, 2, 128, 128, 4096, 1, 1.0, 256, 0, None, 0, None)
     assert rc == _lib.PJX_ERR_WORKSPACE
+    # backward / forward-mode / band entry points validate the same way
+    rc = L.pjx_attn_bwd_band(1, 1, 1, 1, 1, 1, 1, 1, 1, None, None, 0, 0, None, 1, 4, 4, 3, 2, 8, 8, 1, -5, 0, 1.0, 0,
+                             None, 0, None, None)
+    assert rc == _lib.PJX_ERR_BAD_ARG and "multiple" in _lib.last_error()
+    rc = L.pjx_attn_bwd_band(1, 1, 1, 1, 1, 1, 1, 1, 1, None, None, 0, 0, None, 1, 4, 4, 2, 2, 8, 8, 1, -5, 0, 1.0, 0,
+                             None, 0, None, None)
+    assert rc == _lib.PJX_ERR_WORKSPACE
+    assert L.pjx_attn_bwd_workspace_bytes(2, 130, 4) == 2 * 2 * 4 * 256 * 4  # two padded float arrays
+    rc = L.pjx_attn_jvp_band(1, 1, 1, None, None, None, 1, 1, None, None, 0, 0, 1, 4, 4, 3, 2, 8, 8, 1, 0, 0, 1.0, None)
+    assert rc == _lib.PJX_ERR_BAD_ARG and "multiple" in _lib.last_error()
+    assert L.pjx_attn_fwd_band(None, None, None, None, None, None, None, 0, 0, 1, 4, 4, 2, 2, 8, 8, 7, 0, 0, 1.0, 0, None, None) \
+        == _lib.PJX_ERR_BAD_ARG
+    # projections, rotary embedding, cache update
+    assert L.pjx_linear(1, 1, 1, 4, 4, 0, 1, 0, None, None) == _lib.PJX_ERR_BAD_ARG
+    assert L.pjx_linear(None, None, None, 0, 4, 8, 1, 0, None, None) == 0
+    rc = L.pjx_rope_interleaved(1, 1, None, 0.0, 1, 4, 2, 64, 7, 10000.0, 1, None)
+    assert rc == _lib.PJX_ERR_BAD_ARG and "rotary_dim" in _lib.last_error()
+    rc = L.pjx_kv_cache_append(None, None, None, None, None, 2, 16, 1, 2, 64, 64, 1, 1, None, None)
+    assert rc == _lib.PJX_ERR_BAD_ARG and "null" in _lib.last_error()
     assert L.pjx_launch_count() == 0
 
 
