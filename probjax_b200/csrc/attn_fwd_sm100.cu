@@ -85,7 +85,7 @@ struct Cfg {
   static constexpr int BIAS_TILE_BYTES = BIAS_STAGED ? (BN / 32) * BM * 128 : 0;
   static constexpr int OFF_BIAS = OFF_V + VST * V_TILE_BYTES;
   static constexpr int OFF_BAR = OFF_BIAS + 2 * BIAS_TILE_BYTES;
-  static constexpr int N_BAR = 2 + 2 * KST + 2 * VST + 6 + 4 + 2;
+  static constexpr int N_BAR = 2 + 2 * KST + 2 * VST + 6 + 4 + 2 + 1;
   static constexpr int SMEM_BYTES = OFF_BAR + N_BAR * 8 + 16 + 1024;  // + alignment slack
   static constexpr int TMEM_USED = 2 * BN + 2 * DV;
   static constexpr int TMEM_COLS = TMEM_USED <= 128 ? 128 : (TMEM_USED <= 256 ? 256 : 512);
@@ -159,6 +159,7 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
   const int B_FULL = O_FULL + 2;          // [2] staged bias tile landed
   const int B_EMPTY = B_FULL + 2;         // [2] staged bias tile consumed (128 arrivals)
   const int O_STAGED = B_EMPTY + 2;       // [2] output tile written to shared memory (128 arrivals)
+  const int V_CLEAN = O_STAGED + 2;       // rows past the valid length cleared in the last V tile (32 arrivals)
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + C::OFF_BAR + C::N_BAR * 8);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
@@ -216,6 +217,11 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
     }
   }
   const int n = max(n_t[0], n_t[1]);
+  // The last KV tile of the loop may reach past the valid length. Probabilities are exactly 0
+  // there, but those rows may hold anything (a cache tail that was never written) and 0 x NaN
+  // inside the P.V product is not 0: the producer warp clears them in shared memory once the
+  // tile has landed, and the MMA issuer waits for that before the tile's P.V.
+  const int clean_j = (n > 0 && (j_base + n) * BN > kv_len) ? n - 1 : -1;
 
   if (threadIdx.x == 0) {
 #ifdef PJX_TRACE
@@ -230,7 +236,7 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
 #endif
     PJX_CTA_AT(1);
     for (int i = 0; i < C::N_BAR; ++i)
-      mbar_init(BAR(i), ((i >= P_FULL && i < P_FULL + 2) || i >= B_EMPTY) ? 128u : 1u);  // B_EMPTY, O_STAGED: 128
+      mbar_init(BAR(i), i == V_CLEAN ? 32u : (((i >= P_FULL && i < P_FULL + 2) || i >= B_EMPTY) ? 128u : 1u));
     *abort_flag = 0;
     fence_barrier_init();
   }
@@ -290,6 +296,22 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
         }
       }
     }
+    __syncwarp();
+    if (clean_j >= 0) {
+      const int vs = clean_j % VST;
+      if (mbar_wait(BAR(V_FULL + vs), (clean_j / VST) & 1, abort_flag)) {
+        for (int r = kv_len - (j_base + clean_j) * BN + lane; r < BN; r += 32) {
+          const uint32_t vrow = sbase + C::OFF_V + vs * C::V_TILE_BYTES + r * 128;
+#pragma unroll
+          for (int sub = 0; sub < C::V_SUB; ++sub)
+#pragma unroll
+            for (int u = 0; u < 8; ++u)
+              asm volatile("st.shared.v4.b32 [%0], {%1, %1, %1, %1};\n" ::"r"(vrow + sub * BN * 128 + u * 16), "r"(0) : "memory");
+        }
+        fence_proxy_async();
+      }
+      mbar_arrive(BAR(V_CLEAN));
+    }
   } else if (warp == 1) {
     // -------------------------------------------------------------- MMA issuer
     if (lane == 0 && n > 0) {
@@ -331,6 +353,7 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
       for (int j = 0; ok && j < n; ++j) {
         const bool have_next = j + 1 < n;
         ok = mbar_wait(BAR(V_FULL + j % VST), (j / VST) & 1, abort_flag);
+        if (ok && j == clean_j) ok = mbar_wait(BAR(V_CLEAN), 0, abort_flag);
         if (ok && have_next) ok = mbar_wait(BAR(K_FULL + (j + 1) % KST), ((j + 1) / KST) & 1, abort_flag);
         if (!ok) break;
 #pragma unroll

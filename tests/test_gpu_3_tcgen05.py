@@ -203,3 +203,27 @@ def test_host_buffer_call_with_query_row_chunks(causal):
     assert not out_host.is_cuda
     out_dev = pj.attention_forward(q.to(dev()), k.to(dev()), v.to(dev()), causal=causal, kv_lengths=lens, sm_scale=sc)
     assert torch.equal(out_host, out_dev.cpu())
+
+
+@pytest.mark.parametrize("d,dv", [(128, 128), (64, 64), (192, 128)])
+def test_rows_past_the_valid_length_may_hold_anything(d, dv):
+    """K / V rows between kv_lengths[b] and Lkv (a cache tail that was never written) must not
+    reach the result: NaN and inf there give the same bits as zeros."""
+    b, lq, lkv, hq, hkv = 2, 300, 700, 4, 2
+    q, k, v = randn((b, lq, hq, d), torch.bfloat16, 1), randn((b, lkv, hkv, d), torch.bfloat16, 2), randn((b, lkv, hkv, dv), torch.bfloat16, 3)
+    lens = torch.tensor([517, 130], dtype=torch.int32)
+    clean_k, clean_v = k.clone(), v.clone()
+    for i in range(b):
+        clean_k[i, lens[i]:] = 0
+        clean_v[i, lens[i]:] = 0
+        k[i, lens[i]:] = float("nan")
+        v[i, lens[i]:] = float("nan")
+        v[i, lens[i] + 1] = float("inf")
+    sc = 1 / math.sqrt(d)
+    for causal in (False, True):
+        got, lse = pj.attention_forward(q.to(dev()), k.to(dev()), v.to(dev()), causal=causal, kv_lengths=lens, sm_scale=sc,
+                                        return_lse=True, impl="b200:tcgen05")
+        ref, lse_ref = pj.attention_forward(q.to(dev()), clean_k.to(dev()), clean_v.to(dev()), causal=causal, kv_lengths=lens,
+                                            sm_scale=sc, return_lse=True, impl="b200:tcgen05")
+        assert torch.isfinite(got).all()
+        assert torch.equal(got, ref) and torch.equal(lse, lse_ref)
