@@ -151,8 +151,8 @@ struct DqCfg {
   static constexpr int OFF_K = 2 * TILE;           // 2 stages
   static constexpr int OFF_V = 4 * TILE;           // 2 stages
   static constexpr int OFF_BAR = 6 * TILE;
-  // barriers: QDO_FULL, K_FULL[2], K_EMPTY[2], V_FULL[2], V_EMPTY[2], SP_FULL[2], DS_FULL[2], DQ_FULL
-  static constexpr int N_BAR = 14;
+  // barriers: QDO_FULL, K_FULL[2], K_EMPTY[2], V_FULL[2], V_EMPTY[2], SP_FULL[2], DS_FULL[2], DQ_FULL, K_CLEAN
+  static constexpr int N_BAR = 15;
   static constexpr int SMEM_BYTES = OFF_BAR + N_BAR * 8 + 16 + 1024;
   static constexpr int TMEM_COLS = 512;            // S 128 | dP 128 | dQ D
   static_assert(SMEM_BYTES <= 227 * 1024, "shared memory budget");
@@ -169,7 +169,8 @@ bwd_dq_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
   const uint32_t sbase = smem_u32(smem);
   const uint32_t bar0 = sbase + C::OFF_BAR;
   auto BAR = [&](int i) { return bar0 + 8u * i; };
-  const int QDO_FULL = 0, K_FULL = 1, K_EMPTY = 3, V_FULL = 5, V_EMPTY = 7, SP_FULL = 9, DS_FULL = 11, DQ_FULL = 13;
+  const int QDO_FULL = 0, K_FULL = 1, K_EMPTY = 3, V_FULL = 5, V_EMPTY = 7, SP_FULL = 9, DS_FULL = 11, DQ_FULL = 13,
+            K_CLEAN = 14;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + C::OFF_BAR + C::N_BAR * 8);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
@@ -189,9 +190,14 @@ bwd_dq_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
   const int kv_begin = max(0, q0 + p.band_lo);
   const int j_lo = kv_begin / BN;
   const int n = kv_begin < kv_end ? (kv_end + BN - 1) / BN - j_lo : 0;
+  // The last KV tile may reach past the valid length: dS is exactly 0 there, but those K rows may
+  // hold anything and 0 x NaN inside dQ += dS.K is not 0. The producer warp clears them in shared
+  // memory once the tile has landed; the MMA issuer waits for that before it uses the tile.
+  const int clean_j = (n > 0 && (j_lo + n) * BN > kv_len) ? n - 1 : -1;
 
   if (threadIdx.x == 0) {
-    for (int i = 0; i < C::N_BAR; ++i) mbar_init(BAR(i), (i == DS_FULL || i == DS_FULL + 1) ? 128u : 1u);
+    for (int i = 0; i < C::N_BAR; ++i)
+      mbar_init(BAR(i), i == K_CLEAN ? 32u : ((i == DS_FULL || i == DS_FULL + 1) ? 128u : 1u));
     *abort_flag = 0;
     fence_barrier_init();
   }
@@ -234,6 +240,22 @@ bwd_dq_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
                       (j_lo + j) * BN, b);
       }
     }
+    __syncwarp();
+    if (clean_j >= 0) {
+      const int st = clean_j & 1;
+      if (mbar_wait(BAR(K_FULL + st), (clean_j >> 1) & 1, abort_flag)) {
+        for (int r = kv_len - (j_lo + clean_j) * BN + lane; r < BN; r += 32) {
+          const uint32_t krow = sbase + C::OFF_K + st * C::TILE + r * 128;
+#pragma unroll
+          for (int sub = 0; sub < C::SUB; ++sub)
+#pragma unroll
+            for (int u = 0; u < 8; ++u)
+              asm volatile("st.shared.v4.b32 [%0], {%1, %1, %1, %1};\n" ::"r"(krow + sub * BN * 128 + u * 16), "r"(0) : "memory");
+        }
+        fence_proxy_async();
+      }
+      mbar_arrive(BAR(K_CLEAN));
+    }
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer
     if (lane == 0 && n > 0) {
@@ -269,6 +291,7 @@ bwd_dq_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
       };
       bool ok = mbar_wait(BAR(QDO_FULL), 0, abort_flag);
       if (ok) ok = mbar_wait(BAR(K_FULL), 0, abort_flag);
+      if (ok && clean_j == 0) ok = mbar_wait(BAR(K_CLEAN), 0, abort_flag);
       if (ok) ok = mbar_wait(BAR(V_FULL), 0, abort_flag);
       if (ok) {
         tc_fence_after();
@@ -287,6 +310,7 @@ bwd_dq_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
         issue_acc(0, j);
         if (next) {
           ok = mbar_wait(BAR(K_FULL + (st ^ 1)), ((j + 1) >> 1) & 1, abort_flag);
+          if (ok && j + 1 == clean_j) ok = mbar_wait(BAR(K_CLEAN), 0, abort_flag);
           if (ok) ok = mbar_wait(BAR(V_FULL + (st ^ 1)), ((j + 1) >> 1) & 1, abort_flag);
           if (!ok) break;
           tc_fence_after();

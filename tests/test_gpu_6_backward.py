@@ -277,3 +277,29 @@ def test_latent_attention_gradients(absorbed):
     assert _rel(out.detach(), o64.detach()) < 2e-2
     for name, a, w in zip(("dq", "dcache", "dwk", "dwv"), leaves, ref):
         assert _rel(a.grad, w.grad) < 3e-2, (name, _rel(a.grad, w.grad))
+
+
+def test_backward_ignores_rows_past_the_valid_length():
+    """K / V rows between kv_lengths[b] and Lkv may hold anything (NaN here): the gradients equal
+    those of zero-filled tails bit for bit, and the tails themselves get zero gradients."""
+    dvc = dev()
+    b, lq, lkv, hq, hkv, d = 2, 300, 700, 4, 2, 128
+    q, k, v = randn((b, lq, hq, d), torch.bfloat16, 1), randn((b, lkv, hkv, d), torch.bfloat16, 2), randn((b, lkv, hkv, d), torch.bfloat16, 3)
+    g = randn((b, lq, hq, d), torch.bfloat16, 4)
+    lens = torch.tensor([517, 130], dtype=torch.int32)
+    clean_k, clean_v = k.clone(), v.clone()
+    for i in range(b):
+        clean_k[i, lens[i]:] = 0
+        clean_v[i, lens[i]:] = 0
+        k[i, lens[i]:] = float("nan")
+        v[i, lens[i]:] = float("nan")
+    sc = 1 / math.sqrt(d)
+    res = []
+    for kk, vv in ((k, v), (clean_k, clean_v)):
+        qd, kd, vd, gd = (x.to(dvc) for x in (q, kk, vv, g))
+        o, lse = pj.attention_forward(qd, kd, vd, causal=True, kv_lengths=lens, sm_scale=sc, return_lse=True)
+        res.append(pj.attention_backward(qd, kd, vd, o, lse, gd, causal=True, kv_lengths=lens, sm_scale=sc, impl="b200:tcgen05"))
+    for a, c in zip(*res):
+        assert torch.isfinite(a).all() and torch.equal(a, c)
+    for i in range(b):
+        assert (res[0][1][i, lens[i]:] == 0).all() and (res[0][2][i, lens[i]:] == 0).all()
