@@ -7,10 +7,10 @@
 // (probjax/nn/pallas_kernels/kernels/latent_attention.py:396-410), and what its
 // fused kernel recomputes per query tile (:143-145, :177).
 //
-// tcgen05 kernel: one 128 x 128 output tile per CTA; a TMA producer lane fills a
-// 4-stage ring of 128 x 64 A and B tiles (both K-major, 128-byte swizzle), an MMA
-// lane accumulates in tensor memory, four epilogue warps read the accumulator
-// (one 32-lane quarter each), convert and store.  A plain CUDA-core kernel covers
+// tcgen05 kernel: persistent CTAs walk 128 x 256 output tiles; a TMA producer lane fills a
+// 4-stage ring of 128 x 64 A and 256 x 64 B tiles (both K-major, 128-byte swizzle), an MMA
+// lane accumulates in tensor memory (double buffered), four epilogue warps read the
+// accumulator (one 32-lane quarter each), convert and store.  A plain CUDA-core kernel covers
 // fp32 inputs and shapes the tensor-map rules exclude.
 #include "pjx_common.cuh"
 #include "sm100_ptx.cuh"
@@ -69,10 +69,20 @@ gemm_tn_sm100_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_cons
   const int mt = (int)((g.M + TM - 1) / TM);
   const int nt0 = (g.n0 + TN - 1) / TN, nt1 = (g.n1 + TN - 1) / TN;
   const int ntiles = mt * (nt0 + nt1);
-  // tile id -> (which product, m tile, n tile); consecutive ids share the B tile
+  // tile id -> (which product, m tile, n tile).  Tiles are walked in groups of kGroupM row tiles:
+  // inside a group the row tile is the fast axis and the column tile the slow one, so the CTAs in
+  // flight share a few B column tiles and at most kGroupM A row tiles, which stay in L2 while the
+  // group sweeps all columns (a plain column-major walk streams all of A once per column tile,
+  // out of HBM as soon as A is larger than L2).
+  constexpr int kGroupM = 16;
+  const int ncols = nt0 + nt1;
   auto decode = [&](int tile, int& which, int& m_idx, int& n_idx) {
-    int col = tile / mt;
-    m_idx = tile - col * mt;
+    const int grp = tile / (kGroupM * ncols);
+    const int first_m = grp * kGroupM;
+    const int gm = min(kGroupM, mt - first_m);
+    const int r = tile - grp * (kGroupM * ncols);
+    const int col = r / gm;
+    m_idx = first_m + (r - col * gm);
     which = col >= nt0;
     n_idx = which ? col - nt0 : col;
   };
