@@ -236,6 +236,8 @@ def main():
     ap.add_argument("--only-decode", action="store_true", help="time only the decode configuration (profiling captures)")
     ap.add_argument("--only-backward", action="store_true",
                     help="time only the backward of the headline shape on --batch rows (profiling captures)")
+    ap.add_argument("--only-linear", action="store_true",
+                    help="time only the fused QKV projection of the headline shape (profiling captures)")
     ap.add_argument("--kernel", default=None, choices=[None, "b200:generic", "b200:tcgen05"],
                     help="force one forward kernel for the headline (default: the library's own choice)")
     args = ap.parse_args()
@@ -272,6 +274,9 @@ def main():
         return
     if args.only_backward:
         only_backward(args, dev, pk)
+        return
+    if args.only_linear:
+        only_linear(args, dev, pk)
         return
 
     # ---------------------------------------------------------------- headline
@@ -468,6 +473,21 @@ def only_backward(args, dev, pk):
                       args.warmup, fl / 1e12, "TFLOP/s", pk["bf16_tflops"], "tensor", pk["source"])
     res["config"] = {"workload": f"GQA attention backward bf16 B{args.batch} Hq32 Hkv8 S4096 D128 non-causal "
                                  "(FLOPs counted as 2.5 x forward)"}
+    print(json.dumps(res), flush=True)
+
+
+def only_linear(args, dev, pk):
+    """The fused QKV projection of the headline shape, [batch * 4096, 4096] x [6144, 4096]^T, nothing
+    else: the command profiling captures of the projection GEMM run."""
+    import probjax_b200 as pj
+
+    d_model = 4096
+    m_rows, n_out = args.batch * C2["S"], (C2["Hq"] + 2 * C2["Hkv"]) * C2["D"]
+    xg = torch.randn((m_rows, d_model), device=dev).bfloat16()
+    wg = (torch.randn((n_out, d_model), device=dev) / 64).bfloat16()
+    res = bench_extra("linear", lambda: pj.linear(xg, wg), args.steps, args.warmup, 2.0 * m_rows * n_out * d_model / 1e12,
+                      "TFLOP/s", pk["bf16_tflops"], "tensor", pk["source"])
+    res["config"] = {"workload": f"QKV projection bf16 [{m_rows}, {d_model}] x [{n_out}, {d_model}]^T"}
     print(json.dumps(res), flush=True)
 
 
