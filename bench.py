@@ -426,6 +426,24 @@ def main():
                 del q4, k4, v4
         except Exception as e:
             extras["decode"] = {"error": str(e)[:300]}
+        try:  # the all-32768 decode over a paged cache (pages of 256 keys, shuffled in the pool)
+            c4 = oracle.make_config(4, full=True)
+            q4, l4 = c4["q"].to(dev), c4["kv_lengths"].to(dev)
+            page, Bc, cap = 256, c4["k"].shape[0], c4["k"].shape[1]
+            mp = cap // page
+            perm = torch.randperm(Bc * mp, generator=torch.Generator().manual_seed(1)).view(Bc, mp).to(torch.int32)
+            kp = torch.empty((Bc * mp, page) + tuple(c4["k"].shape[2:]), dtype=c4["k"].dtype, device=dev)
+            vp = torch.empty_like(kp)
+            kp[perm.view(-1).long().to(dev)] = c4["k"].to(dev).view(Bc * mp, page, *c4["k"].shape[2:])
+            vp[perm.view(-1).long().to(dev)] = c4["v"].to(dev).view(Bc * mp, page, *c4["v"].shape[2:])
+            permd = perm.to(dev)
+            by4p = 4096.0 * float(c4["kv_lengths"].sum()) + 2 * q4.numel() * 2 + 16 * 32 * 4
+            extras["decode_32k_paged"] = bench_extra(
+                "decode_paged", lambda: pj.decode_paged(q4, kp, vp, permd, l4, sm_scale=c4["sm_scale"]), xs, xw,
+                by4p / 1e9, "GB/s", pk["hbm_gbs"], "hbm", pk["source"])
+            del kp, vp
+        except Exception as e:
+            extras["decode_32k_paged"] = {"error": str(e)[:300]}
         extras["decode_128k"] = long_context_decode_bench(dev, rank, world, xs, xw, pk, dist_on)
         out["extras"] = extras
 

@@ -240,6 +240,22 @@ int pjx_attn_combine(const float* o_parts, const float* lse_parts, int n_parts, 
                      int Dv, void* o, float* lse, int dtype, void* stream);
 
 /*
+ * pjx_attn_decode_splitkv over a paged cache: k_pool / v_pool are [num_pages, page_size, Hkv, D|Dv]
+ * and logical key j of sequence b lives in page block_table[b * max_pages + j / page_size]
+ * (int32 device array [B, max_pages]) at row j % page_size.  page_size is a multiple of 64 (the
+ * kernel's key tile, so a tile never straddles a page); kv_lengths is required.  The workspace is
+ * pjx_attn_decode_workspace_bytes(..., capacity = max_pages * page_size, split_len) bytes.
+ *
+ * No counterpart in the reference, whose caches are contiguous per sequence
+ * (probjax/nn/layers/attention.py:727-757); it is the cache format a serving stack hands over.
+ */
+int pjx_attn_decode_paged(const void* q, const void* k_pool, const void* v_pool,
+                          const int32_t* block_table, const int32_t* kv_lengths, void* o, float* lse,
+                          int B, int Lq, int Hq, int Hkv, int D, int Dv, int page_size, int max_pages,
+                          int dtype, float sm_scale, int split_len, void* workspace,
+                          size_t workspace_bytes, void* stream);
+
+/*
  * Decode KV-cache update: writes k_new [B, n_new, Hkv, D] and v_new [B, n_new, Hkv, Dv] into
  * the caches [B, capacity, Hkv, D|Dv] at rows positions[b] .. positions[b] + n_new - 1 and, if
  * `advance` is nonzero, adds n_new to positions[b] in the same launch (no host round trip:

@@ -21,7 +21,7 @@ from .attention import (  # noqa: F401
     splitkv_forward,
     use_splitkv,
 )
-from .cache import DecodeCache, linear, rope_interleaved  # noqa: F401
+from .cache import DecodeCache, decode_paged, linear, rope_interleaved  # noqa: F401
 from .dispatch import b200_attention_or_none, device_attention_defaults  # noqa: F401
 from .masks import (  # noqa: F401
     AttentionBias,

@@ -47,6 +47,8 @@ SIGNATURES = {
     "pjx_attn_decode_sharded_buffer_bytes": (_sz, [_i, _i, _i, _i, _i]),
     "pjx_linear": (_i, [_vp, _vp, _vp, _i64, _i, _i, _i, _i, _vp, _vp]),
     "pjx_rope_interleaved": (_i, [_vp, _vp, _vp, _f, _i64, _i, _i, _i, _i, _f, _i, _vp]),
+    "pjx_attn_decode_paged": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _i, _f, _i,
+                                   _vp, _sz, _vp]),
     "pjx_kv_cache_append": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _vp, _vp]),
     "pjx_attn_combine": (_i, [_vp, _vp, _i, _i64, _i, _vp, _vp, _i, _vp]),
     "pjx_mla_fwd": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64,

@@ -17,7 +17,7 @@ import math
 import torch
 
 from . import _lib
-from .attention import _DTYPES, _IMPL, _ptr, _require_gpu, _status_word, _stream, mha
+from .attention import _DTYPES, _IMPL, _ptr, _require_gpu, _scratch_bytes, _status_word, _stream, mha
 from .masks import CausalFromBottomRightMask, KVLenMask
 
 
@@ -130,3 +130,35 @@ def linear(x: torch.Tensor, weight: torch.Tensor, *, implementation: str | None 
                                    _IMPL[implementation], _ptr(_status_word(x.device)), _stream(x.device))
     _lib.check(rc)
     return y.view(*x.shape[:-1], w.shape[0])
+
+
+def decode_paged(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, block_table: torch.Tensor, kv_lengths,
+                 *, sm_scale: float | None = None, split_len: int = 0, return_lse: bool = False):
+    """Split-KV decode over a paged cache (``pjx_attn_decode_paged``): ``k_pool`` / ``v_pool``
+    ``[num_pages, page_size, Hkv, D]``, ``block_table int32 [B, max_pages]`` (page of every logical
+    block of a sequence), ``kv_lengths [B]``.  ``page_size`` must be a multiple of 64."""
+    _require_gpu()
+    if not q.is_cuda:
+        raise ValueError("decode_paged takes CUDA tensors")
+    dev = q.device
+    q, k_pool, v_pool = q.contiguous(), k_pool.contiguous(), v_pool.contiguous()
+    B, Lq, Hq, D = q.shape
+    page_size, Hkv, Dv = k_pool.shape[1], k_pool.shape[2], v_pool.shape[3]
+    bt = torch.as_tensor(block_table).to(device=dev, dtype=torch.int32).contiguous()
+    if bt.dim() != 2 or bt.shape[0] != B:
+        raise ValueError(f"block_table must be [B={B}, max_pages], got {tuple(bt.shape)}")
+    max_pages = bt.shape[1]
+    if sm_scale is None:
+        sm_scale = 1.0 / math.sqrt(D)
+    kvl = torch.as_tensor(kv_lengths).to(device=dev, dtype=torch.int32).contiguous()
+    L = _lib.lib()
+    o = torch.empty((B, Lq, Hq, Dv), dtype=q.dtype, device=dev)
+    lse = torch.empty((B, Hq, Lq), dtype=torch.float32, device=dev) if return_lse else None
+    need = L.pjx_attn_decode_workspace_bytes(B, Lq, Hq, Hkv, Dv, max_pages * page_size, int(split_len)) if Hq % Hkv == 0 else 0
+    ws = _scratch_bytes(dev, "decode", need)
+    with torch.cuda.device(dev):
+        rc = L.pjx_attn_decode_paged(_ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(bt), _ptr(kvl), _ptr(o), _ptr(lse), B, Lq, Hq,
+                                     Hkv, D, Dv, page_size, max_pages, _DTYPES[q.dtype], float(sm_scale), int(split_len),
+                                     _ptr(ws), ws.numel(), _stream(dev))
+    _lib.check(rc)
+    return (o, lse) if return_lse else o

@@ -85,7 +85,7 @@ __device__ __forceinline__ uint32_t swz(int r, int c) {
   return static_cast<uint32_t>(r * (HD * 2) + ((c ^ (r & 7)) << 4));
 }
 
-template <typename T, int HD>
+template <typename T, int HD, bool PAGED>
 __global__ void __launch_bounds__(NTHR, 2) decode_splitkv_kernel(const DecodeParams p) {
   constexpr int CH = HD / 8;               // 16-byte chunks per row
   constexpr int TILE_BYTES = BK * HD * 2;  // one K or V tile
@@ -103,8 +103,10 @@ __global__ void __launch_bounds__(NTHR, 2) decode_splitkv_kernel(const DecodePar
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int G = p.Hq / p.Hkv;
-  const T* kbase = static_cast<const T*>(p.k) + ((int64_t)b * p.capacity * p.Hkv + hk) * HD;
-  const T* vbase = static_cast<const T*>(p.v) + ((int64_t)b * p.capacity * p.Hkv + hk) * HD;
+  // contiguous cache: the sequence's rows; paged cache: the pool (rows are found per tile)
+  const int64_t seq_row0 = PAGED ? 0 : (int64_t)b * p.capacity;
+  const T* kbase = static_cast<const T*>(p.k) + (seq_row0 * p.Hkv + hk) * HD;
+  const T* vbase = static_cast<const T*>(p.v) + (seq_row0 * p.Hkv + hk) * HD;
   const int64_t tok_stride = (int64_t)p.Hkv * HD;
   const uint32_t smem_base = smem_u32(smem_raw);
 
@@ -113,13 +115,16 @@ __global__ void __launch_bounds__(NTHR, 2) decode_splitkv_kernel(const DecodePar
     const uint32_t ks = smem_base + stage * 2 * TILE_BYTES;
     const uint32_t vs = ks + TILE_BYTES;
     const int key0 = start + t * BK;
+    // pool row of the tile's first key: a 64-key tile never straddles a page
+    int64_t row0 = key0;
+    if constexpr (PAGED)
+      row0 = (int64_t)p.block_table[(int64_t)b * p.max_pages + key0 / p.page_size] * p.page_size + key0 % p.page_size;
 #pragma unroll
     for (int i = 0; i < BK * CH / NTHR; ++i) {
       const int idx = tid + i * NTHR;
       const int r = idx / CH, c = idx % CH;
-      const int key = key0 + r;
-      const bool ok = key < end;
-      const int64_t off = (int64_t)(ok ? key : start) * tok_stride + c * 8;
+      const bool ok = key0 + r < end;
+      const int64_t off = (row0 + (ok ? r : 0)) * tok_stride + c * 8;
       cp_async16(ks + swz<HD>(r, c), kbase + off, ok ? 16 : 0);
       cp_async16(vs + swz<HD>(r, c), vbase + off, ok ? 16 : 0);
     }
@@ -488,7 +493,7 @@ template <typename T, int HD>
 int launch_decode_t(const DecodeParams& p, cudaStream_t stream) {
   constexpr int smem = NSTAGE * 2 * BK * HD * 2;
   static_assert(smem >= (NWARP * 16 * HD + 2 * NWARP * 16) * 4, "merge scratch must fit in the ring");
-  auto kern = decode_splitkv_kernel<T, HD>;
+  auto kern = p.block_table ? decode_splitkv_kernel<T, HD, true> : decode_splitkv_kernel<T, HD, false>;
   int rc = check_cuda(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem),
                       "cudaFuncSetAttribute(decode)");
   if (rc) return rc;

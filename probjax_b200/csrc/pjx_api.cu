@@ -226,6 +226,41 @@ int pjx_attn_decode_splitkv(const void* q, const void* k_cache, const void* v_ca
   return launch_decode(p, dtype, st);
 }
 
+int pjx_attn_decode_paged(const void* q, const void* k_pool, const void* v_pool, const int32_t* block_table,
+                          const int32_t* kv_lengths, void* o, float* lse, int B, int Lq, int Hq, int Hkv, int D, int Dv,
+                          int page_size, int max_pages, int dtype, float sm_scale, int split_len, void* workspace,
+                          size_t workspace_bytes, void* stream) {
+  if (page_size < 64 || page_size % 64 != 0)
+    return fail(PJX_ERR_BAD_ARG, "page_size must be a positive multiple of 64 (got %d)", page_size);
+  if (max_pages < 0 || (int64_t)max_pages * page_size >= PJX_BAND_NO_UPPER)
+    return fail(PJX_ERR_BAD_ARG, "max_pages * page_size must be below 2^30");
+  const int capacity = max_pages * page_size;
+  int rc = validate_common(q, k_pool, v_pool, o, B, Lq, capacity, Hq, Hkv, D, Dv, dtype);
+  if (rc) return rc;
+  if (B == 0 || Lq == 0) return PJX_OK;
+  if (!block_table || !kv_lengths) return fail(PJX_ERR_BAD_ARG, "paged decode needs a block table and key lengths");
+  DecodeParams p;
+  p.q = q; p.k = k_pool; p.v = v_pool; p.kv_lengths = kv_lengths; p.o = o; p.lse = lse;
+  p.B = B; p.Lq = Lq; p.Hq = Hq; p.Hkv = Hkv; p.D = D; p.Dv = Dv; p.capacity = capacity;
+  p.rows = (Hq / Hkv) * Lq;
+  p.sm_scale = sm_scale;
+  p.o_is_f32 = 0;
+  p.block_table = block_table; p.page_size = page_size; p.max_pages = max_pages;
+  const bool aligned =
+      ((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(k_pool) | reinterpret_cast<uintptr_t>(v_pool)) & 15) == 0;
+  if (!decode_fast_supported(p, dtype) || !aligned || capacity == 0)
+    return fail(PJX_ERR_UNSUPPORTED,
+                "the paged decode takes bf16/fp16, D = Dv in {64,128}, (Hq/Hkv)*Lq <= 16, at least one page and 16-byte aligned q/k/v");
+  if ((rc = decode_geometry(B, Hkv, capacity, split_len, &p.split_len, &p.num_splits))) return rc;
+  const size_t need = pjx_attn_decode_workspace_bytes(B, Lq, Hq, Hkv, Dv, capacity, p.split_len);
+  if (!workspace || workspace_bytes < need)
+    return fail(PJX_ERR_WORKSPACE, "decode workspace: need %zu bytes, got %zu", need, workspace ? workspace_bytes : (size_t)0);
+  const size_t parts = (size_t)B * Hkv * p.num_splits * p.rows;
+  p.o_part = static_cast<float*>(workspace);
+  p.lse_part = reinterpret_cast<float*>(static_cast<char*>(workspace) + align_up(parts * Dv * sizeof(float)));
+  return launch_decode(p, dtype, static_cast<cudaStream_t>(stream));
+}
+
 size_t pjx_attn_decode_sharded_buffer_bytes(int B, int Lq, int Hq, int Dv, int world) {
   if (B < 1 || Lq < 1 || Hq < 1 || Dv < 1 || world < 1 || world > kMaxExchangeRanks) return 0;
   return align_up(exchange_buffer_bytes(world, (int64_t)B * Lq * Hq, Dv));

@@ -89,6 +89,11 @@ struct DecodeParams {
   uint32_t ex_step = 0;
   unsigned char* ex_buf[16] = {};
   int32_t* status = nullptr;
+  // Paged cache (block_table != null): k and v are page pools [num_pages, page_size, Hkv, D];
+  // logical key j of sequence b lives in page block_table[b * max_pages + j / page_size] at row
+  // j % page_size. page_size is a multiple of the 64-key tile, capacity = max_pages * page_size.
+  const int32_t* block_table = nullptr;
+  int page_size = 0, max_pages = 0;
 };
 
 // Parameter block of the backward kernels

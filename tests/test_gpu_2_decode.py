@@ -275,3 +275,33 @@ def test_decode_step_replays_as_a_cuda_graph():
         assert cache.cache_index.tolist() == (start + t + 1).tolist()
         want = oracle.xla_attention(q_all[:, t : t + 1], k_all, v_all, kv_lengths=start + t + 1, sm_scale=1 / math.sqrt(d))
         assert float((out.float().cpu() - want.float()).abs().max()) <= 2e-2
+
+
+@pytest.mark.parametrize("dtype,d,page", [(torch.bfloat16, 128, 256), (torch.float16, 64, 64)])
+def test_paged_cache_decode_equals_contiguous_decode(dtype, d, page):
+    """The same keys scattered over shuffled pages of a pool give the bits of the contiguous
+    decode (same tiles, same order), which is checked against the oracle elsewhere."""
+    b, hq, hkv, cap = 3, 8, 2, 1024
+    lens = torch.tensor([1024, 333, 65], dtype=torch.int32)
+    q = randn((b, 1, hq, d), dtype, 1)
+    k, v = randn((b, cap, hkv, d), dtype, 2), randn((b, cap, hkv, d), dtype, 3)
+    max_pages = cap // page
+    n_pages = b * max_pages + 5
+    perm = torch.randperm(n_pages, generator=torch.Generator().manual_seed(0))[: b * max_pages].view(b, max_pages)
+    k_pool = torch.full((n_pages, page, hkv, d), float("nan"), dtype=dtype)
+    v_pool = torch.full((n_pages, page, hkv, d), float("nan"), dtype=dtype)
+    for i in range(b):
+        for pg in range(max_pages):
+            k_pool[perm[i, pg]] = k[i, pg * page : (pg + 1) * page]
+            v_pool[perm[i, pg]] = v[i, pg * page : (pg + 1) * page]
+    sc = 1 / math.sqrt(d)
+    got, lse = pj.decode_paged(q.to(dev()), k_pool.to(dev()), v_pool.to(dev()), perm.to(torch.int32), lens, sm_scale=sc,
+                               return_lse=True)
+    want, want_lse = pj.decode_forward(q.to(dev()), k.to(dev()), v.to(dev()), kv_lengths=lens, sm_scale=sc, return_lse=True)
+    assert torch.isfinite(got).all()
+    assert torch.equal(got, want) and torch.equal(lse, want_lse)
+    ref, ref_lse = oracle_fwd(q, k, v, kv_lengths=lens, sm_scale=sc)
+    assert_close(got, lse, ref, ref_lse, dtype, "paged decode")
+    with pytest.raises(ValueError, match="multiple of 64"):
+        pj.decode_paged(q.to(dev()), k_pool[:, :48].contiguous().to(dev()), v_pool[:, :48].contiguous().to(dev()),
+                        perm.to(torch.int32), lens, sm_scale=sc)
