@@ -201,7 +201,7 @@ def run_reference(args, rank):
     fl = prefill_flops(1, C2["Hq"], C2["S"], C2["S"], C2["D"], C2["D"], False) * args.steps
     val = fl / dt / 1e12
     sample = "each step = 1 of 4 batch rows of the workload (B=1 Hq=32 Hkv=8 S=4096 D=128, non-causal)"
-    print(json.dumps({
+    _emit({
         "impl": "reference", "metric": "attn_fwd_tflops", "value": val, "unit": "TFLOP/s", "n_gpus": args.gpus,
         "steps": args.steps, "warmup": min(args.warmup, 1), "ms_per_step": dt / args.steps * 1e3,
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
@@ -209,7 +209,7 @@ def run_reference(args, rank):
         "cpu_baseline": {"value": val, "unit": "TFLOP/s", "cores": threads, "kind": "port", "sample": sample},
         "e2e": {"value": val, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "note": "oracle port of probjax's XLA CPU attention path (the reference needs jax, not installable offline)",
-    }), flush=True)
+    })
 
 
 def bench_extra(name, fn, steps, warmup, work, unit, peak, bound, pk_note):
@@ -264,8 +264,6 @@ def main():
         import torch.distributed as dist
 
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
-        if os.environ.get("NCCL_DEBUG", "").upper() in ("", "VERSION"):
-            os.environ["NCCL_DEBUG"] = "WARN"  # no version banner on stdout: rank 0 prints one JSON line
         dist.init_process_group("nccl", device_id=dev)
     pk = peaks()
 
@@ -453,7 +451,7 @@ def main():
         except Exception as e:
             out["cpu_baseline"] = {"error": str(e)[:300]}
     if rank == 0:
-        print(json.dumps(out), flush=True)
+        _emit(out)
     if dist_on:
         import torch.distributed as dist
 
@@ -473,7 +471,7 @@ def only_decode(args, dev, pk):
     res = bench_extra("decode", lambda: pj.decode_forward(q4, k4, v4, kv_lengths=l4, sm_scale=c4["sm_scale"], return_lse=True),
                       args.steps, args.warmup, by4 / 1e9, "GB/s", pk["hbm_gbs"], "hbm", pk["source"])
     res["config"] = {"workload": f"GQA split-KV decode bf16 B{args.batch} Hq32 Hkv8 D128, 32768 keys each"}
-    print(json.dumps(res), flush=True)
+    _emit(res)
 
 
 def only_backward(args, dev, pk):
@@ -491,7 +489,7 @@ def only_backward(args, dev, pk):
                       args.warmup, fl / 1e12, "TFLOP/s", pk["bf16_tflops"], "tensor", pk["source"])
     res["config"] = {"workload": f"GQA attention backward bf16 B{args.batch} Hq32 Hkv8 S4096 D128 non-causal "
                                  "(FLOPs counted as 2.5 x forward)"}
-    print(json.dumps(res), flush=True)
+    _emit(res)
 
 
 def only_linear(args, dev, pk):
@@ -506,7 +504,7 @@ def only_linear(args, dev, pk):
     res = bench_extra("linear", lambda: pj.linear(xg, wg), args.steps, args.warmup, 2.0 * m_rows * n_out * d_model / 1e12,
                       "TFLOP/s", pk["bf16_tflops"], "tensor", pk["source"])
     res["config"] = {"workload": f"QKV projection bf16 [{m_rows}, {d_model}] x [{n_out}, {d_model}]^T"}
-    print(json.dumps(res), flush=True)
+    _emit(res)
 
 
 def long_context_decode_bench(dev, rank, world, steps, warmup, pk, dist_on, context=131072):
@@ -579,5 +577,17 @@ def sharded_decode_bench(c4, dev, rank, world, steps, warmup, pk):
         return {"error": f"{type(e).__name__}: {e}"[:300]}
 
 
+def _emit(obj):
+    """The one JSON line of the run, on the process's original stdout."""
+    os.write(_REAL_STDOUT, (json.dumps(obj) + "\n").encode())
+
+
+# Libraries (NCCL's version banner, for one) write to file descriptor 1; the contract is one JSON
+# line on stdout, so everything else is sent to stderr and the line goes out through a saved copy.
+_REAL_STDOUT = 1
+
 if __name__ == "__main__":
+    _REAL_STDOUT = os.dup(1)
+    os.dup2(2, 1)
+    sys.stdout = sys.stderr
     main()
