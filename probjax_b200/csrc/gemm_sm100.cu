@@ -8,9 +8,10 @@
 // fused kernel recomputes per query tile (:143-145, :177).
 //
 // tcgen05 kernel: persistent CTAs walk 128 x 256 output tiles; a TMA producer lane fills a
-// 4-stage ring of 128 x 64 A and 256 x 64 B tiles (both K-major, 128-byte swizzle), an MMA
+// 3-stage ring of 128 x 64 A and 256 x 64 B tiles (both K-major, 128-byte swizzle), an MMA
 // lane accumulates in tensor memory (double buffered), four epilogue warps read the
-// accumulator (one 32-lane quarter each), convert and store.  A plain CUDA-core kernel covers
+// accumulator (one 32-lane quarter each), convert and write the tile through a shared-memory
+// staging buffer and TMA stores.  A plain CUDA-core kernel covers
 // fp32 inputs and shapes the tensor-map rules exclude.
 #include "pjx_common.cuh"
 #include "sm100_ptx.cuh"
@@ -23,12 +24,23 @@ namespace {
 
 using namespace sm100;
 
-constexpr int TM = 128, TN = 256, TK = 64, ST = 4;
+constexpr int TM = 128, TN = 256, TK = 64;
 constexpr int A_BYTES = TM * TK * 2, B_BYTES = TN * TK * 2;
-constexpr int G_OFF_BAR = ST * (A_BYTES + B_BYTES);
-constexpr int G_NBAR = 2 * ST + 4;
-constexpr int G_SMEM = G_OFF_BAR + G_NBAR * 8 + 16 + 1024;
+constexpr int STAGE_BYTES = TM * TN * 2;
 constexpr int G_THREADS = 192;
+
+// Two shapes of the kernel. STAGED: a 3-stage operand ring plus a staging tile, outputs leave by
+// TMA stores - for short K, where the epilogue of a tile is as long as its main loop. Otherwise a
+// 4-stage ring and stores straight from the registers, which a long main loop hides.
+template <bool STAGED>
+struct GCfg {
+  static constexpr int ST = STAGED ? 3 : 4;
+  static constexpr int OFF_STAGE = ST * (A_BYTES + B_BYTES);  // 4 blocks of 128 rows x 64 columns
+  static constexpr int OFF_BAR = OFF_STAGE + (STAGED ? STAGE_BYTES : 0);
+  static constexpr int NBAR = 2 * ST + 4 + 2;
+  static constexpr int SMEM = OFF_BAR + NBAR * 8 + 16 + 1024;
+  static_assert(SMEM <= 227 * 1024, "shared memory budget");
+};
 
 template <bool BF16>
 __device__ __forceinline__ uint32_t gpack(float lo, float hi) {
@@ -51,17 +63,21 @@ struct GemmArgs {
   int64_t M;
   int n0, n1, K;
   int32_t* status;
+  int group_m;   // row tiles per group of the tile walk
 };
 
-template <bool BF16>
+template <bool BF16, bool STAGED>
 __global__ void __launch_bounds__(G_THREADS, 1)
 gemm_tn_sm100_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b0,
-                     const __grid_constant__ CUtensorMap tm_b1, const GemmArgs g) {
+                     const __grid_constant__ CUtensorMap tm_b1, const __grid_constant__ CUtensorMap tm_c0,
+                     const __grid_constant__ CUtensorMap tm_c1, const GemmArgs g) {
+  using GC = GCfg<STAGED>;
+  constexpr int ST = GC::ST, G_OFF_BAR = GC::OFF_BAR, G_NBAR = GC::NBAR, G_OFF_STAGE = GC::OFF_STAGE;
   extern __shared__ unsigned char smem_unaligned[];
   unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_unaligned) + 1023) & ~uintptr_t(1023));
   const uint32_t sbase = smem_u32(smem);
   auto BAR = [&](int i) { return sbase + G_OFF_BAR + 8u * i; };
-  const int FULL = 0, EMPTY = ST, ACC_FULL = 2 * ST, ACC_EMPTY = 2 * ST + 2;
+  const int FULL = 0, EMPTY = ST, ACC_FULL = 2 * ST, ACC_EMPTY = 2 * ST + 2, OUT_STAGED = 2 * ST + 4, OUT_FREE = 2 * ST + 5;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + G_OFF_BAR + G_NBAR * 8);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -74,7 +90,7 @@ gemm_tn_sm100_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_cons
   // flight share a few B column tiles and at most kGroupM A row tiles, which stay in L2 while the
   // group sweeps all columns (a plain column-major walk streams all of A once per column tile,
   // out of HBM as soon as A is larger than L2).
-  constexpr int kGroupM = 16;
+  const int kGroupM = g.group_m;
   const int ncols = nt0 + nt1;
   auto decode = [&](int tile, int& which, int& m_idx, int& n_idx) {
     const int grp = tile / (kGroupM * ncols);
@@ -88,7 +104,7 @@ gemm_tn_sm100_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_cons
   };
 
   if (threadIdx.x == 0) {
-    for (int i = 0; i < G_NBAR; ++i) mbar_init(BAR(i), (i >= ACC_EMPTY) ? 128u : 1u);
+    for (int i = 0; i < G_NBAR; ++i) mbar_init(BAR(i), (i >= ACC_EMPTY && i <= OUT_STAGED) ? 128u : 1u);
     *abort_flag = 0;
     fence_barrier_init();
   }
@@ -166,6 +182,50 @@ gemm_tn_sm100_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_cons
       tc_fence_after();
       const int64_t row = (int64_t)m_idx * TM + quarter * 32 + lane;
       const uint32_t taddr = tmem + (static_cast<uint32_t>(quarter * 32) << 16) + acc * TN;
+      if constexpr (STAGED) {
+        // Output through shared memory: every thread converts its row and writes it into the staging
+        // tile in the tensor map's 128-byte-swizzled layout; one thread hands the tile to TMA stores,
+        // which clip rows past M and columns past N. Stores straight from the registers touch 32
+        // separate rows per instruction and made short-K products epilogue-bound.
+        if (local > 0) {  // the previous tile's stores have read the staging tile
+          ok = mbar_wait(BAR(OUT_FREE), (local - 1) & 1, abort_flag);
+          ok = __all_sync(0xffffffffu, ok);
+          if (!ok) break;
+        }
+        const int r_in = quarter * 32 + lane;
+        const uint32_t stage = sbase + G_OFF_STAGE;
+#pragma unroll 2
+        for (int c = 0; c < TN / 32; ++c) {
+          float accv[32];
+          tmem_ld32f(taddr + c * 32, accv);
+          tmem_wait_ld();
+          const uint32_t rbase = stage + (c >> 1) * (TM * 128) + r_in * 128;
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const uint32_t unit = static_cast<uint32_t>((c & 1) * 4 + i) ^ static_cast<uint32_t>(r_in & 7);
+            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};\n" ::"r"(rbase + unit * 16),
+                         "r"(gpack<BF16>(accv[8 * i + 0], accv[8 * i + 1])), "r"(gpack<BF16>(accv[8 * i + 2], accv[8 * i + 3])),
+                         "r"(gpack<BF16>(accv[8 * i + 4], accv[8 * i + 5])), "r"(gpack<BF16>(accv[8 * i + 6], accv[8 * i + 7]))
+                         : "memory");
+          }
+        }
+        tc_fence_before();
+        mbar_arrive(BAR(ACC_EMPTY + acc));  // the accumulator is free for the tile after next
+        fence_proxy_async();
+        mbar_arrive(BAR(OUT_STAGED));
+        if (threadIdx.x == 64) {
+          if (mbar_wait(BAR(OUT_STAGED), local & 1, abort_flag)) {
+            const CUtensorMap* tc = which ? &tm_c1 : &tm_c0;
+#pragma unroll
+            for (int blk = 0; blk < TN / 64; ++blk)
+              if (n_idx * TN + blk * 64 < N) tma_store_2d(tc, stage + blk * (TM * 128), n_idx * TN + blk * 64, m_idx * TM);
+            tma_store_commit();
+            tma_store_wait_read();
+          }
+          mbar_arrive(BAR(OUT_FREE));
+        }
+        continue;
+      }
       const bool vec_ok = (N % 8 == 0) && ((reinterpret_cast<uintptr_t>(Cout) & 15) == 0);
 #pragma unroll 2
       for (int c = 0; c < TN / 32; ++c) {
@@ -327,19 +387,34 @@ int launch_gemm_tn2(const void* A, const void* B0, void* C0, int N0, const void*
     }
     GemmArgs g;
     g.c0 = C0; g.c1 = C1; g.M = M; g.n0 = N0; g.n1 = N1; g.K = K; g.status = status;
+    uintptr_t cal = reinterpret_cast<uintptr_t>(C0);
+    if (N1) cal |= reinterpret_cast<uintptr_t>(C1);
+    // Short K: a tile's epilogue is as long as its main loop, so the outputs go through shared memory
+    // and TMA stores (needs row pitches that are multiples of 16 bytes). Long K hides the direct stores
+    // and prefers the fourth operand stage.
+    const bool staged = K < 1536 && (N0 % 8 == 0) && (N1 % 8 == 0) && (cal & 15) == 0;
+    CUtensorMap tc0 = ta, tc1 = ta;
+    if (staged) {
+      if ((rc = make_tmap_2d(&tc0, C0, dtype, M, N0, TM))) return rc;
+      tc1 = tc0;
+      if (N1 && (rc = make_tmap_2d(&tc1, C1, dtype, M, N1, TM))) return rc;
+    }
+    g.group_m = 16;  // 16 to 32 measure alike on B200; 4 and 64 lose 3-6 %
     const int64_t tiles = ((M + TM - 1) / TM) * ((N0 + TN - 1) / TN + (N1 + TN - 1) / TN);
     int dev = 0, sms = 148;
     if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
     const unsigned grid = (unsigned)(tiles < sms ? tiles : sms);
-    if (dtype == PJX_BF16) {
-      auto kern = gemm_tn_sm100_kernel<true>;
-      if ((rc = check_cuda(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, G_SMEM), "cudaFuncSetAttribute(projection)"))) return rc;
-      kern<<<grid, G_THREADS, G_SMEM, stream>>>(ta, tb0, tb1, g);
-    } else {
-      auto kern = gemm_tn_sm100_kernel<false>;
-      if ((rc = check_cuda(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, G_SMEM), "cudaFuncSetAttribute(projection)"))) return rc;
-      kern<<<grid, G_THREADS, G_SMEM, stream>>>(ta, tb0, tb1, g);
-    }
+    auto launch = [&](auto kern, int smem) -> int {
+      int r = check_cuda(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem), "cudaFuncSetAttribute(projection)");
+      if (r) return r;
+      kern<<<grid, G_THREADS, smem, stream>>>(ta, tb0, tb1, tc0, tc1, g);
+      return PJX_OK;
+    };
+    if (dtype == PJX_BF16)
+      rc = staged ? launch(gemm_tn_sm100_kernel<true, true>, GCfg<true>::SMEM) : launch(gemm_tn_sm100_kernel<true, false>, GCfg<false>::SMEM);
+    else
+      rc = staged ? launch(gemm_tn_sm100_kernel<false, true>, GCfg<true>::SMEM) : launch(gemm_tn_sm100_kernel<false, false>, GCfg<false>::SMEM);
+    if (rc) return rc;
     count_launch();
     return check_cuda(cudaGetLastError(), "projection (tcgen05) launch");
   }
