@@ -53,6 +53,36 @@ def peaks():
         return dict(FALLBACK_PEAKS, bf16_tflops_sustained=1400.0, source="fallback")
 
 
+PREFILL_PROFILE = "profiles/attn_fwd_sm100_prefill_b2_s4096.md"
+
+
+def profiled_prefill_traffic(batch):
+    """DRAM read + write bytes per launch of the headline kernel, from the tracked ncu summary
+    of the B=2 case (last capture column), scaled with the batch; None if the file is absent."""
+    import re
+
+    try:
+        text = open(os.path.join(ROOT, PREFILL_PROFILE)).read()
+        tot = 0.0
+        for name in ("dram__bytes_read.sum", "dram__bytes_write.sum"):
+            row = re.search(r"\| `" + re.escape(name) + r"` \|(.*)\|", text).group(1)
+            tot += float(re.findall(r"([0-9.]+) MB", row)[-1]) * 1e6
+        return tot * batch / 2.0
+    except Exception:
+        return None
+
+
+def rounded(obj, digits=4):
+    """Floats to `digits` significant digits (keeps the JSON line short)."""
+    if isinstance(obj, float):
+        return float(f"{obj:.{digits}g}") if obj == obj and abs(obj) != float("inf") else obj
+    if isinstance(obj, dict):
+        return {k: rounded(v, digits) for k, v in obj.items()}
+    if isinstance(obj, (list, tuple)):
+        return [rounded(v, digits) for v in obj]
+    return obj
+
+
 def prefill_flops(B, Hq, Lq, Lkv, D, Dv, causal):
     if causal:  # sum over rows of (i + 1) keys, rows beyond Lkv see Lkv keys
         pairs = sum(min(i + 1, Lkv) for i in range(Lq))
@@ -183,44 +213,56 @@ def cpu_baseline(budget_s=12.0, threads=None):
                       f"{dt:.1f} s, torch CPU fp32 restatement of the reference's XLA path"}
 
 
+WORKLOAD = "GQA prefill fwd bf16 B{b} Hq32 Hkv8 S4096 D128 non-causal (per GPU)"
+
+
 def run_reference(args, rank):
-    """--impl reference: the reference's CPU attention path on the host cores."""
+    """--impl reference: the reference's CPU attention path on the host cores, on the
+    same workload as the GPU arm: one step = the whole batch, same warm-up count."""
     if rank != 0:
         return
     import oracle
 
     threads = os.cpu_count() or 1
     torch.set_num_threads(threads)
-    c = oracle.make_config(2, B=1)
-    for _ in range(min(args.warmup, 1)):
-        oracle.xla_attention(c["q"], c["k"], c["v"], sm_scale=c["sm_scale"])
+    c = oracle.make_config(2, B=args.batch)
+
+    def step():
+        for b in range(args.batch):  # one batch row at a time bounds the fp32 score memory
+            oracle.xla_attention(c["q"][b:b + 1], c["k"][b:b + 1], c["v"][b:b + 1], sm_scale=c["sm_scale"])
+
+    for _ in range(args.warmup):
+        step()
     t0 = time.perf_counter()
     for _ in range(args.steps):
-        oracle.xla_attention(c["q"], c["k"], c["v"], sm_scale=c["sm_scale"])
+        step()
     dt = time.perf_counter() - t0
-    fl = prefill_flops(1, C2["Hq"], C2["S"], C2["S"], C2["D"], C2["D"], False) * args.steps
+    fl = prefill_flops(args.batch, C2["Hq"], C2["S"], C2["S"], C2["D"], C2["D"], False) * args.steps
     val = fl / dt / 1e12
-    sample = "each step = 1 of 4 batch rows of the workload (B=1 Hq=32 Hkv=8 S=4096 D=128, non-causal)"
+    sample = f"each step = the whole workload (B={args.batch}), {threads} threads"
     _emit({
         "impl": "reference", "metric": "attn_fwd_tflops", "value": val, "unit": "TFLOP/s", "n_gpus": args.gpus,
-        "steps": args.steps, "warmup": min(args.warmup, 1), "ms_per_step": dt / args.steps * 1e3,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt / args.steps * 1e3,
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-        "config": {"workload": "GQA prefill fwd bf16 B4 Hq32 Hkv8 S4096 D128 non-causal", "sample": sample},
+        "config": {"workload": WORKLOAD.format(b=args.batch)},
         "cpu_baseline": {"value": val, "unit": "TFLOP/s", "cores": threads, "kind": "port", "sample": sample},
         "e2e": {"value": val, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
-        "note": "oracle port of probjax's XLA CPU attention path (the reference needs jax, not installable offline)",
+        "note": "oracle port of probjax's XLA CPU path (the reference needs jax, not installable offline)",
     })
 
 
-def bench_extra(name, fn, steps, warmup, work, unit, peak, bound, pk_note):
-    """Time one secondary configuration; returns a small dict (never raises)."""
+def bench_extra(name, fn, steps, warmup, work, unit, peak, bound, pk_note, profile=None):
+    """Time one secondary configuration; returns a small dict (never raises).  `profile`
+    names the tracked ncu summary of the kernel behind the number."""
     try:
         ms = time_steps(fn, steps, warmup) / steps
         ach = work / (ms * 1e-3)
-        return {"ms": ms, "value": ach, "unit": unit, "roofline": {"bound": bound, "achieved": ach, "peak": peak,
-                                                                   "unit": unit, "frac": ach / peak, "of": pk_note}}
+        out = {"ms": ms, "value": ach, "unit": unit, "bound": bound, "frac": ach / peak}
+        if profile:
+            out["profile"] = profile
+        return out
     except Exception as e:  # keep the headline line alive
-        return {"error": f"{type(e).__name__}: {e}"[:300]}
+        return {"error": f"{type(e).__name__}: {e}"[:200]}
 
 
 def main():
@@ -314,22 +356,35 @@ def main():
            "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
            "call": "probjax_b200.attention_forward on pinned host tensors (pjx_attn_fwd_host)"}
 
+    # one-shot parity of the headline result: batch row 0 against the oracle (outside every timed region)
+    try:
+        got0 = step()[0:1].float().cpu()
+        want0 = oracle.xla_attention(c["q"][0:1], c["k"][0:1], c["v"][0:1], sm_scale=sc).float()
+        parity = float((got0 - want0).abs().max())
+        del got0, want0
+    except Exception as e:
+        parity = f"{type(e).__name__}: {e}"[:120]
+    alg_bytes = sum(t.numel() * t.element_size() for t in (q, k, v)) + q.numel() * q.element_size()
     out = {
         "metric": "attn_fwd_tflops", "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "bf16", "data": "synthetic",
-        "config": {"workload": f"GQA prefill fwd bf16 B{args.batch} Hq32 Hkv8 S4096 D128 non-causal (per GPU)",
+        "config": {"workload": WORKLOAD.format(b=args.batch),
                    "l2": "inputs+outputs 335 MB per step exceed the 126 MB L2; no flush needed",
                    "parallelism": f"batch-sharded x{world}, no collective" if world > 1 else "single GPU"},
         "roofline": {"bound": "tensor", "achieved": per_gpu, "peak": pk["bf16_tflops"], "unit": "TFLOP/s",
                      "frac": per_gpu / pk["bf16_tflops"],
-                     # DRAM bytes per launch from the ncu capture summarised under profiles/ (135 MB at B=2,
-                     # proportional to the batch)
-                     "traffic": 67.5e6 * args.batch, "traffic_unit": "bytes per launch (ncu dram read+write, scaled from B=2)",
+                     # measured DRAM bytes per launch of this kernel: the ncu capture of the B=2 case, scaled
+                     # with the batch (traffic grows in proportion); the algorithmic bytes beside it
+                     "traffic": profiled_prefill_traffic(args.batch), "traffic_source": PREFILL_PROFILE,
+                     "algorithmic_bytes": alg_bytes,
                      "of": f"{pk['source']} burst bf16 peak", "kernel": "attn_fwd_sm100_kernel<128,128,128,2,2,bf16>",
                      "frac_of_sustained": per_gpu / pk["bf16_tflops_sustained"]},
         "e2e": e2e, "gpu_launches": int(launches_per_step * args.steps), "clocks": clocks,
+        "parity_max_abs_err": parity,
     }
+    if isinstance(parity, float) and not parity <= 2e-2:
+        raise SystemExit(f"headline result differs from the oracle: max-abs error {parity}")
 
     # ------------------------------------------------- other configurations
     if not args.skip_extras:
@@ -338,7 +393,7 @@ def main():
         fl_c = prefill_flops(C2["B"], C2["Hq"], C2["S"], C2["S"], C2["D"], C2["D"], True)
         extras["prefill_causal"] = bench_extra(
             "causal", lambda: pj.attention_forward(q, k, v, causal=True, sm_scale=sc), xs, xw, fl_c / 1e12,
-            "TFLOP/s", pk["bf16_tflops"], "tensor", pk["source"])
+            "TFLOP/s", pk["bf16_tflops"], "tensor", pk["source"], PREFILL_PROFILE)
         try:  # sliding window of 1024 keys (the band form of the mask): keys j with i-1023 <= j <= i
             win = 1024
             rows = torch.arange(C2["S"], dtype=torch.float64)
@@ -354,7 +409,7 @@ def main():
             g_b = torch.randn_like(o_b)
             extras["backward"] = bench_extra(
                 "bwd", lambda: pj.attention_backward(q, k, v, o_b, lse_b, g_b, sm_scale=sc), xs, xw,
-                2.5 * flops / 1e12, "TFLOP/s", pk["bf16_tflops"], "tensor", pk["source"])
+                2.5 * flops / 1e12, "TFLOP/s", pk["bf16_tflops"], "tensor", pk["source"], "profiles/bwd_sm100_b2_s4096.md")
             o_c, lse_c = pj.attention_forward(q, k, v, causal=True, sm_scale=sc, return_lse=True)
             extras["backward_causal"] = bench_extra(
                 "bwd_causal", lambda: pj.attention_backward(q, k, v, o_c, lse_c, g_b, causal=True, sm_scale=sc), xs, xw,
@@ -369,7 +424,7 @@ def main():
             wg = (torch.randn((n_out, d_model), device=dev) / 64).bfloat16()
             extras["qkv_projection"] = bench_extra(
                 "linear", lambda: pj.linear(xg, wg), xs, xw, 2.0 * m_rows * n_out * d_model / 1e12, "TFLOP/s",
-                pk["bf16_tflops"], "tensor", pk["source"])
+                pk["bf16_tflops"], "tensor", pk["source"], "profiles/gemm_tn_sm100_qkv_projection.md")
             del xg, wg
         except Exception as e:
             extras["qkv_projection"] = {"error": str(e)[:300]}
@@ -392,7 +447,8 @@ def main():
             fl3 = 4.0 * 16 * 1024 * 64 * float(c3["kv_lengths"].sum())
             extras["masked_bias"] = bench_extra(
                 "c3", lambda: pj.attention_forward(q3, k3, v3, kv_lengths=l3, bias=b3, sm_scale=c3["sm_scale"]), xs, xw,
-                fl3 / 1e12, "TFLOP/s", pk["bf16_tflops"], "tensor", pk["source"])
+                fl3 / 1e12, "TFLOP/s", pk["bf16_tflops"], "tensor", pk["source"],
+                "profiles/attn_fwd_sm100_masked_bias_b8_s1024.md")
             by3 = 2 * q3.numel() * 2 + 2 * 16 * 64 * 2 * float(c3["kv_lengths"].sum()) + 4.0 * 16 * 1024 * float(c3["kv_lengths"].max())
             if "ms" in extras["masked_bias"]:
                 extras["masked_bias"]["hbm_gbs"] = by3 / (extras["masked_bias"]["ms"] * 1e-3) / 1e9
@@ -405,7 +461,8 @@ def main():
             fl5 = 2.0 * 8 * 2048 * 512 * 16 * 256 + prefill_flops(8, 16, 2048, 2048, 192, 128, True)
             extras["latent"] = bench_extra(
                 "c5", lambda: pj.mla(q5, ch5, wk5, wv5, mask=pj.CausalMask(), sm_scale=c5["sm_scale"]), xs, xw,
-                fl5 / 1e12, "TFLOP/s", pk["bf16_tflops"], "tensor", pk["source"])
+                fl5 / 1e12, "TFLOP/s", pk["bf16_tflops"], "tensor", pk["source"],
+                "profiles/attn_fwd_sm100_latent_b2_s2048.md")
             del q5, ch5
         except Exception as e:
             extras["latent"] = {"error": str(e)[:300]}
@@ -416,12 +473,25 @@ def main():
                 by4 = 4096.0 * float(c4["kv_lengths"].sum()) + 2 * q4.numel() * 2 + 16 * 32 * 4
                 extras[tag] = bench_extra(
                     tag, lambda: pj.decode_forward(q4, k4, v4, kv_lengths=l4, sm_scale=c4["sm_scale"], return_lse=True),
-                    xs, xw, by4 / 1e9, "GB/s", pk["hbm_gbs"], "hbm", pk["source"])
-                if "roofline" in extras[tag]:
-                    extras[tag]["roofline"]["frac_of_nominal_8TBs"] = extras[tag]["value"] / 8000.0
+                    xs, xw, by4 / 1e9, "GB/s", pk["hbm_gbs"], "hbm", pk["source"], "profiles/decode_splitkv_b4_32k.md")
+                if "value" in extras[tag]:
+                    extras[tag]["frac_of_nominal_8TBs"] = extras[tag]["value"] / 8000.0
+                if full and "value" in extras[tag]:
+                    # the decode half of the metric, repeated where the driver keeps it
+                    out["roofline"]["decode_32k_gbs"] = extras[tag]["value"]
+                    out["roofline"]["decode_32k_frac"] = extras[tag]["frac"]
                 if dist_on and full:
-                    extras["decode_32k_seq_sharded"] = sharded_decode_bench(c4, dev, rank, world, xs, xw, pk)
+                    ref4 = pj.decode_forward(q4, k4, v4, kv_lengths=l4, sm_scale=c4["sm_scale"], return_lse=True)
+                    sh = sharded_decode_bench(c4, ref4, dev, rank, world, xs, xw, pk)
+                    extras["decode_32k_seq_sharded"] = sh
+                    if "value" in sh.get("fused", {}) and "value" in extras[tag]:
+                        out["roofline"]["decode_sharded_gbs"] = sh["fused"]["value"]
+                        out["roofline"]["decode_sharded_eff"] = sh["fused"]["value"] / (world * extras[tag]["value"])
+                        out["roofline"]["decode_sharded_max_abs_err"] = sh["fused"]["max_abs_err"]
+                    del ref4
                 del q4, k4, v4
+        except SystemExit:
+            raise
         except Exception as e:
             extras["decode"] = {"error": str(e)[:300]}
         try:  # the all-32768 decode over a paged cache (pages of 256 keys, shuffled in the pool)
@@ -438,11 +508,14 @@ def main():
             by4p = 4096.0 * float(c4["kv_lengths"].sum()) + 2 * q4.numel() * 2 + 16 * 32 * 4
             extras["decode_32k_paged"] = bench_extra(
                 "decode_paged", lambda: pj.decode_paged(q4, kp, vp, permd, l4, sm_scale=c4["sm_scale"]), xs, xw,
-                by4p / 1e9, "GB/s", pk["hbm_gbs"], "hbm", pk["source"])
+                by4p / 1e9, "GB/s", pk["hbm_gbs"], "hbm", pk["source"], "profiles/decode_splitkv_b4_32k.md")
             del kp, vp
         except Exception as e:
             extras["decode_32k_paged"] = {"error": str(e)[:300]}
         extras["decode_128k"] = long_context_decode_bench(dev, rank, world, xs, xw, pk, dist_on)
+        if dist_on and "value" in extras["decode_128k"]:
+            out["roofline"]["decode_128k_sharded_gbs"] = extras["decode_128k"]["value"]
+            out["roofline"]["decode_128k_sharded_max_abs_err"] = extras["decode_128k"].get("max_abs_err")
         out["extras"] = extras
 
     if rank == 0 and not args.skip_cpu and world == 1:
@@ -450,6 +523,7 @@ def main():
             out["cpu_baseline"] = cpu_baseline()
         except Exception as e:
             out["cpu_baseline"] = {"error": str(e)[:300]}
+    failed = [f"{k}: {v['parity_failure']}" for k, v in _walk(out.get("extras", {})) if "parity_failure" in v]
     if rank == 0:
         _emit(out)
     if dist_on:
@@ -457,6 +531,16 @@ def main():
 
         dist.barrier()
         dist.destroy_process_group()
+    if failed:
+        raise SystemExit("parity failure: " + "; ".join(failed))
+
+
+def _walk(d, prefix=""):
+    """(path, dict) for every dict nested in d."""
+    for k, v in d.items():
+        if isinstance(v, dict):
+            yield prefix + k, v
+            yield from _walk(v, prefix + k + ".")
 
 
 def only_decode(args, dev, pk):
@@ -507,46 +591,76 @@ def only_linear(args, dev, pk):
     _emit(res)
 
 
+def _parity(o, lse, ref_o, ref_lse, tol_o=2e-2, tol_lse=1e-3):
+    """max-abs errors of (o, lse) against a reference pair, and whether they pass the bounds."""
+    eo = float((o.float() - ref_o.float()).abs().max())
+    el = float((lse.float() - ref_lse.float()).abs().max())
+    res = {"max_abs_err": eo, "lse_err": el}
+    if not (eo <= tol_o and el <= tol_lse):
+        res["parity_failure"] = f"o {eo:.3e} lse {el:.3e}"
+    return res
+
+
 def long_context_decode_bench(dev, rank, world, steps, warmup, pk, dist_on, context=131072):
     """The decode geometry of configuration 4 at a 128k context (device-generated
     N(0,1) cache, all keys valid): on one GPU the whole cache, on N GPUs the KV
     sequence sharded with the fused exchange.  At 8 GPUs each rank still streams 16k
-    keys per sequence, so the fixed cost of the exchange is amortised."""
+    keys per sequence, so the fixed cost of the exchange is amortised.  With N > 1 the
+    sharded result is compared (outside the timed region) with the one-GPU decode over
+    the concatenation of all ranks' shards, which every rank regenerates from the seeds."""
     import probjax_b200 as pj
     from probjax_b200 import dist as pjd
 
     try:
         B, Hq, Hkv, D, page = 16, 32, 8, 128, 256
         local = context // world
-        g = torch.Generator(device=dev).manual_seed(1234 + rank)
         q = torch.randn((B, 1, Hq, D), generator=torch.Generator(device=dev).manual_seed(99), device=dev).bfloat16()
-        k = torch.randn((B, local, Hkv, D), generator=g, device=dev, dtype=torch.float16).bfloat16()
-        v = torch.randn((B, local, Hkv, D), generator=g, device=dev, dtype=torch.float16).bfloat16()
+        # every rank holds the whole cache (8.6 GB) for the check; its own shard is a slice of it
+        k_all = torch.empty((B, context, Hkv, D), device=dev, dtype=torch.bfloat16)
+        v_all = torch.empty_like(k_all)
+        for r in range(world):
+            g = torch.Generator(device=dev).manual_seed(1234 + r)
+            k_all[:, r * local:(r + 1) * local] = torch.randn((B, local, Hkv, D), generator=g, device=dev, dtype=torch.float16)
+            v_all[:, r * local:(r + 1) * local] = torch.randn((B, local, Hkv, D), generator=g, device=dev, dtype=torch.float16)
+        k = k_all[:, rank * local:(rank + 1) * local].contiguous() if dist_on else k_all
+        v = v_all[:, rank * local:(rank + 1) * local].contiguous() if dist_on else v_all
         lens = torch.full((B,), context, dtype=torch.int32)
         sc = 1.0 / (D ** 0.5)
+        ll = lens.to(dev)
+        check = {}
         if dist_on:
             fn = pjd.FusedShardedDecoder(q, k, v, lens, page=page, sm_scale=sc)
+            ref = pj.decode_forward(q, k_all, v_all, kv_lengths=ll, sm_scale=sc, return_lse=True)
+            o, lse = fn(return_lse=True)
+            fn.check_status()
+            check = _parity(o, lse, ref[0], ref[1])
+            del ref
         else:
-            ll = lens.to(dev)
 
             def fn():
                 return pj.decode_forward(q, k, v, kv_lengths=ll, sm_scale=sc, return_lse=True)
 
+        if dist_on:
+            del k_all, v_all
         ms = max_over_ranks(time_steps(fn, steps, warmup, dist_on), dist_on) / steps
+        if dist_on:
+            fn.check_status()
         by = 4096.0 * B * context
         ach = by / (ms * 1e-3) / 1e9
-        return {"ms": ms, "value": ach, "unit": "GB/s aggregate", "context": context, "n_gpus": world,
-                "roofline": {"bound": "hbm", "achieved": ach / world, "peak": pk["hbm_gbs"], "unit": "GB/s per GPU",
-                             "frac": ach / world / pk["hbm_gbs"], "of": pk["source"]}}
+        return dict({"ms": ms, "value": ach, "unit": "GB/s aggregate", "context": context, "n_gpus": world,
+                     "bound": "hbm", "frac": ach / world / pk["hbm_gbs"]}, **check)
     except Exception as e:
         return {"error": f"{type(e).__name__}: {e}"[:300]}
 
 
-def sharded_decode_bench(c4, dev, rank, world, steps, warmup, pk):
+def sharded_decode_bench(c4, ref, dev, rank, world, steps, warmup, pk):
     """Decode at 32k context with the KV sequence block-cyclically sharded over
     the ranks.  Timed three ways: the fused exchange (peer stores and flags inside
     the kernels), NCCL all-gathers between the kernels, and the latter as one CUDA
-    graph per step."""
+    graph per step.  Outside the timed region every rank compares each variant's
+    (o, lse) with `ref`, the one-GPU decode over the unsharded cache, and a few
+    sequences of the fused result with the oracle."""
+    import oracle
     from probjax_b200 import dist as pjd
 
     out = {}
@@ -565,10 +679,21 @@ def sharded_decode_bench(c4, dev, rank, world, steps, warmup, pk):
                     dec = pjd.ShardedDecoder(q4, kl, vl, lens, page=page, sm_scale=c4["sm_scale"],
                                              use_graph=(mode == "nccl_graph"))
                 ms = max_over_ranks(time_steps(dec, steps * 5, warmup, True), True) / (steps * 5)
+                o, lse = dec(return_lse=True)
+                torch.cuda.synchronize(dev)
+                if mode == "fused":
+                    dec.check_status()
                 ach = by / (ms * 1e-3) / 1e9
-                out[mode] = {"ms": ms, "value": ach, "unit": "GB/s aggregate",
-                             "roofline": {"bound": "hbm", "achieved": ach / world, "peak": pk["hbm_gbs"],
-                                          "unit": "GB/s per GPU", "frac": ach / world / pk["hbm_gbs"], "of": pk["source"]}}
+                out[mode] = dict({"ms": ms, "value": ach, "unit": "GB/s aggregate", "bound": "hbm",
+                                  "frac": ach / world / pk["hbm_gbs"]}, **_parity(o, lse, ref[0], ref[1]))
+                if mode == "fused":  # two sequences against the CPU oracle as well
+                    want, want_lse = oracle.xla_attention(c4["q"][:2], c4["k"][:2], c4["v"][:2], kv_lengths=lens[:2],
+                                                          sm_scale=c4["sm_scale"], return_lse=True)
+                    vs_oracle = _parity(o[:2].cpu(), lse[:2].cpu(), want, want_lse)
+                    out[mode]["oracle_max_abs_err"] = vs_oracle["max_abs_err"]
+                    out[mode]["oracle_lse_err"] = vs_oracle["lse_err"]
+                    if "parity_failure" in vs_oracle:
+                        out[mode]["parity_failure"] = "vs oracle " + vs_oracle["parity_failure"]
             except Exception as e:
                 out[mode] = {"error": f"{type(e).__name__}: {e}"[:300]}
         out["page"] = page
@@ -579,7 +704,7 @@ def sharded_decode_bench(c4, dev, rank, world, steps, warmup, pk):
 
 def _emit(obj):
     """The one JSON line of the run, on the process's original stdout."""
-    os.write(_REAL_STDOUT, (json.dumps(obj) + "\n").encode())
+    os.write(_REAL_STDOUT, (json.dumps(rounded(obj), separators=(",", ":")) + "\n").encode())
 
 
 # Libraries (NCCL's version banner, for one) write to file descriptor 1; the contract is one JSON

@@ -187,7 +187,8 @@ int pjx_attn_decode_default_split_len(int B, int Hkv, int capacity);
  *     pjx_attn_decode_splitkv).  o is written in `dtype`.
  *   - It calls no cudaMalloc / cudaFree and no allocating library routine.
  *   - The first call on each device looks up the array's device address; make
- *     that first call before starting any stream capture.
+ *     that first call before starting any stream capture.  The address is kept
+ *     for the life of the process: it does not survive a cudaDeviceReset.
  *   - All calls share the array.  Nothing in it needs clearing between calls,
  *     but two calls whose kernels overlap on the GPU (different streams or
  *     threads) corrupt each other: order them on one stream.
@@ -202,11 +203,22 @@ size_t pjx_attn_decode_static_scratch_bytes(void);
  * Decode step with the KV sequence sharded over `world` GPUs (one process per
  * GPU).  Each rank passes its own shard (`k_local`, `v_local`, `local_lengths` =
  * valid tokens this rank holds per sequence) and the replicated q; every rank
- * gets the full result.  The exchange is fused into the kernels: after the local
- * split-KV pass a kernel writes this rank's (o, lse) partial straight into every
- * rank's exchange buffer with peer stores over NVLink and raises a flag; a second
- * kernel waits (bounded, about two seconds, then PJX_ERR_DEVICE_TIMEOUT in
- * `status`) for all ranks' flags and combines the partials out of local memory.
+ * gets the full result.  The exchange is fused into the kernels.  When the split
+ * kernel's grid fits on the GPU at once (the default split length makes it so for
+ * up to 296 (sequence, kv head) pairs) the whole step is ONE launch: the last CTA of
+ * each (sequence, kv head) to finish combines the head's splits, writes the rank's
+ * (o, lse) partial straight into every rank's exchange buffer with peer stores over
+ * NVLink, raises that head's flag there, waits (bounded, about two seconds, then
+ * PJX_ERR_DEVICE_TIMEOUT in `status`) for the same head's flag of every rank and
+ * combines the partials out of local memory.  Larger grids use three launches
+ * (split kernel, publish with one flag per rank, gather + combine) with the same
+ * bounded wait.  Only stores cross NVLink; every load is local.
+ *
+ * Exchange buffer of one rank, N = B * Lq * Hq (identical on every rank):
+ *   2 x { float o[world][N][Dv]; float lse[world][N]; }   halves alternate with step parity
+ *   uint32 rank_flags[16]; uint32 counter;                (three-launch form)
+ *   (padding to 16 bytes) uint32 unit_flags[world][N]; uint32 unit_counters[N];  (one-launch form)
+ * Flags hold the step number of the last partial published.
  * It generalises the split combine of attention_splitkv.py:236-250 across GPUs;
  * the reference itself never shards the sequence axis (probjax/nn/sharding.py:70, 97).
  *

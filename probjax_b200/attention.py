@@ -60,13 +60,50 @@ def check_status(device=None) -> None:
 
 
 def _scratch_bytes(device, tag: str, nbytes: int) -> torch.Tensor:
-    """A cached, growing device byte buffer (decode partials, projections, staging)."""
-    key = (torch.device(device).index or 0, tag)
+    """A cached, growing device byte buffer (decode partials, projections, staging), one per
+    (device, CUDA stream, purpose): calls issued on different streams never share scratch, and a
+    buffer that is outgrown is only dropped by the stream that owns it, whose earlier kernels
+    are ordered before anything that reuses the memory."""
+    device = torch.device(device)
+    key = (device.index or 0, _stream(device), tag)
     buf = _scratch.get(key)
     if buf is None or buf.numel() < nbytes:
         buf = torch.empty(max(int(nbytes), 256), dtype=torch.uint8, device=device)
         _scratch[key] = buf
     return buf
+
+
+def _check_call(q, k, v, *, bias=None, kv_lengths=None, o=None, lse=None, d_o=None, what="attention"):
+    """Shape, dtype and device agreement of the tensors of one kernel call.  The C ABI takes
+    sizes from q, k and v and indexes every other buffer with them, so a mismatch here would
+    read or write past an allocation; the reference raises at trace time for the same mistakes."""
+    for name, t in (("q", q), ("k", k), ("v", v)):
+        if t.dim() != 4:
+            raise ValueError(f"{what}: {name} must be rank 4 [B, T, H, D], got shape {tuple(t.shape)}")
+    if q.dtype not in _DTYPES:
+        raise ValueError(f"unsupported dtype {q.dtype}; expected float32, bfloat16 or float16")
+    if k.dtype != q.dtype or v.dtype != q.dtype:
+        raise ValueError(f"{what}: q, k and v must share a dtype, got {q.dtype}, {k.dtype}, {v.dtype}")
+    if k.device != q.device or v.device != q.device:
+        raise ValueError(f"{what}: q, k and v must live on one device, got {q.device}, {k.device}, {v.device}")
+    B, Lq, Hq, D = q.shape
+    Lkv, Hkv = k.shape[1], k.shape[2]
+    if tuple(k.shape) != (B, Lkv, Hkv, D):
+        raise ValueError(f"{what}: k must be [B={B}, Lkv, Hkv, D={D}], got {tuple(k.shape)}")
+    if tuple(v.shape[:3]) != (B, Lkv, Hkv):
+        raise ValueError(f"{what}: v must be [B={B}, Lkv={Lkv}, Hkv={Hkv}, Dv], got {tuple(v.shape)}")
+    _gqa_group(Hq, Hkv)
+    Dv = v.shape[3]
+    if bias is not None:
+        if bias.dim() != 4 or tuple(bias.shape[-2:]) != (Lq, Lkv) or bias.shape[0] not in (1, B) \
+                or bias.shape[1] not in (1, Hq):
+            raise ValueError(f"{what}: bias must be [B|1, H|1, Lq={Lq}, Lkv={Lkv}], got {tuple(bias.shape)}")
+    if kv_lengths is not None and kv_lengths.numel() != B:
+        raise ValueError(f"{what}: kv_lengths must hold B={B} entries, got {kv_lengths.numel()}")
+    for name, t, shape in (("o", o, (B, Lq, Hq, Dv)), ("d_o", d_o, (B, Lq, Hq, Dv)), ("lse", lse, (B, Hq, Lq))):
+        if t is not None and tuple(t.shape) != shape:
+            raise ValueError(f"{what}: {name} must be {shape}, got {tuple(t.shape)}")
+    return B, Lq, Lkv, Hq, Hkv, D, Dv
 
 
 def _as_tensor(x):
@@ -133,10 +170,11 @@ def attention_forward(q, k, v, *, causal=False, band=None, kv_lengths=None, bias
     _require_gpu()
     band_lo, band_hi = _band_args(causal, band)
     q, k, v = _as_tensor(q), _as_tensor(k), _as_tensor(v)
-    if q.dtype not in _DTYPES:
-        raise ValueError(f"unsupported dtype {q.dtype}; expected float32, bfloat16 or float16")
-    B, Lq, Hq, D = q.shape
-    Lkv, Hkv, Dv = k.shape[1], k.shape[2], v.shape[3]
+    if q.is_cuda != k.is_cuda or q.is_cuda != v.is_cuda:
+        raise ValueError("q, k and v must live on the same side (all CUDA or all host)")
+    B, Lq, Lkv, Hq, Hkv, D, Dv = _check_call(
+        q, k, v, bias=None if bias is None else _as_tensor(bias),
+        kv_lengths=None if kv_lengths is None else _as_tensor(kv_lengths), what="attention_forward")
     if impl not in _IMPL:
         raise ValueError(f"implementation must be one of {sorted(x for x in _IMPL if x)} or None, got {impl!r}")
     on_device = q.is_cuda
@@ -191,10 +229,14 @@ def attention_backward(q, k, v, o, lse, d_o, *, causal=False, band=None, kv_leng
     _require_gpu()
     band_lo, band_hi = _band_args(causal, band)
     dev = q.device
+    B, Lq, Lkv, Hq, Hkv, D, Dv = _check_call(
+        q, k, v, bias=None if bias is None else _as_tensor(bias),
+        kv_lengths=None if kv_lengths is None else _as_tensor(kv_lengths), o=o, lse=lse, d_o=d_o,
+        what="attention_backward")
+    if o.dtype != q.dtype or d_o.dtype != q.dtype or o.device != dev or d_o.device != dev or lse.device != dev:
+        raise ValueError("attention_backward: o and d_o must have q's dtype, and o, d_o, lse its device")
     q, k, v, o, d_o = (x.contiguous() for x in (q, k, v, o, d_o))
     lse = lse.contiguous().float()
-    B, Lq, Hq, D = q.shape
-    Lkv, Hkv, Dv = k.shape[1], k.shape[2], v.shape[3]
     dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
     kvl = None if kv_lengths is None else _as_tensor(kv_lengths).to(device=dev, dtype=torch.int32).contiguous()
     bs = hs = 0
@@ -226,11 +268,15 @@ def attention_jvp(q, k, v, lse, tq=None, tk=None, tv=None, *, causal=False, band
     _require_gpu()
     band_lo, band_hi = _band_args(causal, band)
     dev = q.device
+    B, Lq, Lkv, Hq, Hkv, D, Dv = _check_call(
+        q, k, v, bias=None if bias is None else _as_tensor(bias),
+        kv_lengths=None if kv_lengths is None else _as_tensor(kv_lengths), lse=lse, what="attention_jvp")
+    for name, t, like in (("tq", tq, q), ("tk", tk, k), ("tv", tv, v)):
+        if t is not None and (tuple(t.shape) != tuple(like.shape) or t.device != dev):
+            raise ValueError(f"attention_jvp: {name} must match its primal's shape {tuple(like.shape)} and device")
     q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
     tq, tk, tv = (None if t is None else t.to(q.dtype).contiguous() for t in (tq, tk, tv))
     lse = lse.contiguous().float()
-    B, Lq, Hq, D = q.shape
-    Lkv, Hkv, Dv = k.shape[1], k.shape[2], v.shape[3]
     t_o = torch.empty((B, Lq, Hq, Dv), dtype=q.dtype, device=dev)
     kvl = None if kv_lengths is None else _as_tensor(kv_lengths).to(device=dev, dtype=torch.int32).contiguous()
     bs = hs = 0
@@ -305,14 +351,14 @@ def decode_forward(q, k_cache, v_cache, *, kv_lengths=None, sm_scale, split_len=
     if not q.is_cuda:
         raise ValueError("decode_forward takes CUDA tensors")
     dev = q.device
+    B, Lq, cap, Hq, Hkv, D, Dv = _check_call(
+        q, k_cache, v_cache, kv_lengths=None if kv_lengths is None else _as_tensor(kv_lengths), what="decode_forward")
     q, k_cache, v_cache = q.contiguous(), k_cache.contiguous(), v_cache.contiguous()
-    B, Lq, Hq, D = q.shape
-    cap, Hkv, Dv = k_cache.shape[1], k_cache.shape[2], v_cache.shape[3]
     L = _lib.lib()
     o = torch.empty((B, Lq, Hq, Dv), dtype=torch.float32 if partial_f32 else q.dtype, device=dev)
     lse = torch.empty((B, Hq, Lq), dtype=torch.float32, device=dev) if return_lse else None
     kvl = None if kv_lengths is None else _as_tensor(kv_lengths).to(device=dev, dtype=torch.int32).contiguous()
-    need = L.pjx_attn_decode_workspace_bytes(B, Lq, Hq, Hkv, Dv, cap, int(split_len)) if Hq % Hkv == 0 else 0
+    need = L.pjx_attn_decode_workspace_bytes(B, Lq, Hq, Hkv, Dv, cap, int(split_len))
     ws = _scratch_bytes(dev, "decode", need)
     with torch.cuda.device(dev):
         rc = L.pjx_attn_decode_splitkv(_ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(kvl), _ptr(o), _ptr(lse),

@@ -141,9 +141,18 @@ def decode_paged(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, bl
     if not q.is_cuda:
         raise ValueError("decode_paged takes CUDA tensors")
     dev = q.device
+    if q.dim() != 4 or k_pool.dim() != 4 or v_pool.dim() != 4:
+        raise ValueError("decode_paged: q must be [B, Lq, Hq, D] and the pools [num_pages, page_size, Hkv, D]")
+    if k_pool.dtype != q.dtype or v_pool.dtype != q.dtype or k_pool.device != dev or v_pool.device != dev:
+        raise ValueError("decode_paged: q and the page pools must share a dtype and a device")
     q, k_pool, v_pool = q.contiguous(), k_pool.contiguous(), v_pool.contiguous()
     B, Lq, Hq, D = q.shape
     page_size, Hkv, Dv = k_pool.shape[1], k_pool.shape[2], v_pool.shape[3]
+    if k_pool.shape[3] != D or tuple(v_pool.shape[:3]) != tuple(k_pool.shape[:3]):
+        raise ValueError(f"decode_paged: pools must be [P, page, Hkv, D={D}] / [P, page, Hkv, Dv], got "
+                         f"{tuple(k_pool.shape)} and {tuple(v_pool.shape)}")
+    if Hq % Hkv != 0:
+        raise ValueError(f"query heads ({Hq}) must be a multiple of key/value heads ({Hkv})")
     bt = torch.as_tensor(block_table).to(device=dev, dtype=torch.int32).contiguous()
     if bt.dim() != 2 or bt.shape[0] != B:
         raise ValueError(f"block_table must be [B={B}, max_pages], got {tuple(bt.shape)}")
@@ -151,10 +160,12 @@ def decode_paged(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, bl
     if sm_scale is None:
         sm_scale = 1.0 / math.sqrt(D)
     kvl = torch.as_tensor(kv_lengths).to(device=dev, dtype=torch.int32).contiguous()
+    if kvl.numel() != B:
+        raise ValueError(f"decode_paged: kv_lengths must hold B={B} entries, got {kvl.numel()}")
     L = _lib.lib()
     o = torch.empty((B, Lq, Hq, Dv), dtype=q.dtype, device=dev)
     lse = torch.empty((B, Hq, Lq), dtype=torch.float32, device=dev) if return_lse else None
-    need = L.pjx_attn_decode_workspace_bytes(B, Lq, Hq, Hkv, Dv, max_pages * page_size, int(split_len)) if Hq % Hkv == 0 else 0
+    need = L.pjx_attn_decode_workspace_bytes(B, Lq, Hq, Hkv, Dv, max_pages * page_size, int(split_len))
     ws = _scratch_bytes(dev, "decode", need)
     with torch.cuda.device(dev):
         rc = L.pjx_attn_decode_paged(_ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(bt), _ptr(kvl), _ptr(o), _ptr(lse), B, Lq, Hq,

@@ -85,7 +85,15 @@ __device__ __forceinline__ uint32_t swz(int r, int c) {
   return static_cast<uint32_t>(r * (HD * 2) + ((c ^ (r & 7)) << 4));
 }
 
-template <typename T, int HD, bool PAGED>
+__device__ __forceinline__ void st_release_sys_u32(uint32_t* p, uint32_t v) {
+  asm volatile("st.release.sys.global.u32 [%0], %1;\n" ::"l"(p), "r"(v) : "memory");
+}
+
+// FUSED (sequence-sharded decode, whole grid co-resident): the last CTA of each (batch, kv
+// head) to finish combines the head's splits, stores the rank's partial into every rank's
+// exchange buffer, raises the head's flag there, waits (bounded) for the same head's flags of
+// all ranks and writes the final result -- the whole exchange inside this one launch.
+template <typename T, int HD, bool PAGED, bool FUSED>
 __global__ void __launch_bounds__(NTHR, 2) decode_splitkv_kernel(const DecodeParams p) {
   constexpr int CH = HD / 8;               // 16-byte chunks per row
   constexpr int TILE_BYTES = BK * HD * 2;  // one K or V tile
@@ -97,9 +105,11 @@ __global__ void __launch_bounds__(NTHR, 2) decode_splitkv_kernel(const DecodePar
   int len = p.capacity;
   if (p.kv_lengths) len = max(0, min(len, p.kv_lengths[b]));
   const int start = split * p.split_len;
-  if (start >= len) return;  // nothing to do; the combine never reads this split
+  // nothing to do; the combine never reads this split (in the fused exchange split 0 always
+  // runs, so that a head without keys still publishes its empty partial)
+  if (start >= len && !(FUSED && split == 0)) return;
   const int end = min(len, start + p.split_len);
-  const int n_tiles = (end - start + BK - 1) / BK;
+  const int n_tiles = max(0, (end - start + BK - 1) / BK);
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int G = p.Hq / p.Hkv;
@@ -311,6 +321,128 @@ __global__ void __launch_bounds__(NTHR, 2) decode_splitkv_kernel(const DecodePar
     p.o_part[(part + r) * HD + d] = lall > 0.f ? o / lall : 0.f;
     if (d == 0) p.lse_part[part + r] = lall > 0.f ? mall + log2f(lall) : -INFINITY;
   }
+
+  if constexpr (FUSED) {
+    const int64_t N = (int64_t)p.B * p.Lq * p.Hq;
+    const size_t half = exchange_record_floats(p.ex_world, N, HD);
+    const size_t uf_off = exchange_unit_flags_offset(p.ex_world, N, HD);
+    const int unit = b * p.Hkv + hk;
+    unsigned char* mine = p.ex_buf[p.ex_rank];
+    uint32_t* counters = reinterpret_cast<uint32_t*>(mine + uf_off) + (size_t)p.ex_world * N;
+    const int ns = max(1, (len + p.split_len - 1) / p.split_len);  // CTAs of this head that run
+    __shared__ int s_last;
+    __shared__ float s_w[16][kMaxExchangeRanks];  // per packed row: weight of every rank's partial
+    __shared__ float s_inv[16], s_lse[16];
+    __threadfence();  // this CTA's partial is visible device-wide before it is counted
+    __syncthreads();
+    if (tid == 0) {
+      const uint32_t prev = atomicAdd(counters + unit, 1u);
+      s_last = (prev == (uint32_t)(ns - 1));
+      if (s_last) counters[unit] = 0;  // ready for the next step (the next launch on this stream)
+    }
+    __syncthreads();
+    if (!s_last) return;
+    __threadfence();
+
+    // ---- this rank's partial of the head: exact combine of its splits ----
+    const int64_t pbase = ((int64_t)b * p.Hkv + hk) * p.num_splits;
+    const size_t par = (p.ex_step & 1) * half;
+    if (tid < p.rows) {
+      float m = -INFINITY;
+      for (int s = 0; s < ns; ++s) m = fmaxf(m, __ldcg(p.lse_part + (pbase + s) * p.rows + tid));
+      const float msafe = (m == -INFINITY) ? 0.f : m;
+      float denom = 0.f;
+      for (int s = 0; s < ns; ++s) denom += exp2f(__ldcg(p.lse_part + (pbase + s) * p.rows + tid) - msafe);
+      s_inv[tid] = denom > 0.f ? 1.f / denom : 0.f;
+      s_lse[tid] = msafe;  // base 2
+      const float lse_nat = denom > 0.f ? (msafe + log2f(denom)) * kLn2 : INFINITY;
+      const int g = tid / p.Lq, t = tid % p.Lq;
+      const int64_t n = ((int64_t)b * p.Lq + t) * p.Hq + hk * G + g;
+      const size_t l_off = par + (size_t)p.ex_world * N * HD + (size_t)p.ex_rank * N + n;
+      for (int q = 0; q < p.ex_world; ++q) reinterpret_cast<float*>(p.ex_buf[q])[l_off] = lse_nat;
+    }
+    __syncthreads();
+    for (int idx = tid; idx < p.rows * (HD / 4); idx += NTHR) {
+      const int r = idx / (HD / 4), d4 = idx % (HD / 4);
+      float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+      for (int s = 0; s < ns; ++s) {
+        const float w = exp2f(__ldcg(p.lse_part + (pbase + s) * p.rows + r) - s_lse[r]);
+        const float4 x = __ldcg(reinterpret_cast<const float4*>(p.o_part + ((pbase + s) * p.rows + r) * HD) + d4);
+        acc.x = fmaf(w, x.x, acc.x);
+        acc.y = fmaf(w, x.y, acc.y);
+        acc.z = fmaf(w, x.z, acc.z);
+        acc.w = fmaf(w, x.w, acc.w);
+      }
+      const float inv = s_inv[r];
+      acc.x *= inv; acc.y *= inv; acc.z *= inv; acc.w *= inv;
+      const int g = r / p.Lq, t = r % p.Lq;
+      const int64_t n = ((int64_t)b * p.Lq + t) * p.Hq + hk * G + g;
+      const size_t o_off = par + ((size_t)p.ex_rank * N + n) * HD;
+      for (int q = 0; q < p.ex_world; ++q) reinterpret_cast<float4*>(reinterpret_cast<float*>(p.ex_buf[q]) + o_off)[d4] = acc;
+    }
+    __syncthreads();  // the CTA's stores are ordered before thread 0's fence (cumulativity)
+    if (tid == 0) {
+      __threadfence_system();
+      for (int q = 0; q < p.ex_world; ++q)
+        st_release_sys_u32(reinterpret_cast<uint32_t*>(p.ex_buf[q] + uf_off) + (size_t)p.ex_rank * N + unit, p.ex_step);
+    }
+
+    // ---- wait for the same head's partials of all ranks (bounded), then combine them ----
+    if (tid < p.ex_world) {
+      const volatile uint32_t* flag = reinterpret_cast<const volatile uint32_t*>(mine + uf_off) + (size_t)tid * N + unit;
+      const long long t0 = clock64();
+      while (static_cast<int32_t>(*flag - p.ex_step) < 0) {
+        if (clock64() - t0 > 4000000000LL) {  // about two seconds: a peer never published
+          if (p.status) atomicExch(p.status, (int)PJX_ERR_DEVICE_TIMEOUT);
+          break;
+        }
+      }
+      __threadfence_system();  // acquire: the peer's records are visible after its flag
+    }
+    __syncthreads();
+    const float* o_parts = reinterpret_cast<const float*>(mine) + par;
+    const float* lse_parts = o_parts + (size_t)p.ex_world * N * HD;
+    if (tid < p.rows) {
+      const int g = tid / p.Lq, t = tid % p.Lq;
+      const int64_t n = ((int64_t)b * p.Lq + t) * p.Hq + hk * G + g;
+      float m = -INFINITY;
+      for (int q = 0; q < p.ex_world; ++q) {
+        const float x = __ldcg(lse_parts + (size_t)q * N + n);
+        if (x != INFINITY) m = fmaxf(m, x);  // +inf marks a rank without keys
+      }
+      const float msafe = (m == -INFINITY) ? 0.f : m;
+      float denom = 0.f;
+      for (int q = 0; q < p.ex_world; ++q) {
+        const float x = __ldcg(lse_parts + (size_t)q * N + n);
+        const float w = (x == INFINITY) ? 0.f : expf(x - msafe);
+        s_w[tid][q] = w;
+        denom += w;
+      }
+      s_inv[tid] = denom > 0.f ? 1.f / denom : 0.f;
+      if (p.lse) p.lse[((int64_t)b * p.Hq + hk * G + g) * p.Lq + t] = denom > 0.f ? msafe + logf(denom) : INFINITY;
+    }
+    __syncthreads();
+    T* o = static_cast<T*>(p.o);
+    for (int idx = tid; idx < p.rows * (HD / 4); idx += NTHR) {
+      const int r = idx / (HD / 4), d4 = idx % (HD / 4);
+      const int g = r / p.Lq, t = r % p.Lq;
+      const int64_t n = ((int64_t)b * p.Lq + t) * p.Hq + hk * G + g;
+      float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+      for (int q = 0; q < p.ex_world; ++q) {
+        const float w = s_w[r][q];
+        const float4 x = __ldcg(reinterpret_cast<const float4*>(o_parts + ((size_t)q * N + n) * HD) + d4);
+        acc.x = fmaf(w, x.x, acc.x);
+        acc.y = fmaf(w, x.y, acc.y);
+        acc.z = fmaf(w, x.z, acc.z);
+        acc.w = fmaf(w, x.w, acc.w);
+      }
+      const float inv = s_inv[r];
+      uint2 out;
+      out.x = pack2<T>(acc.x * inv, acc.y * inv);
+      out.y = pack2<T>(acc.z * inv, acc.w * inv);
+      *reinterpret_cast<uint2*>(o + n * HD + d4 * 4) = out;
+    }
+  }
 }
 
 // One CTA per packed row (b, kv head, r): exact combine of the valid splits.
@@ -389,10 +521,6 @@ __global__ void combine_parts_kernel(const float* __restrict__ o_parts, const fl
 // Buffers are double buffered by step parity: a rank can run at most one step
 // ahead of a peer, because its next combine needs that peer's next flag.
 // ---------------------------------------------------------------------------
-__device__ __forceinline__ void st_release_sys_u32(uint32_t* p, uint32_t v) {
-  asm volatile("st.release.sys.global.u32 [%0], %1;\n" ::"l"(p), "r"(v) : "memory");
-}
-
 __global__ void publish_partials_kernel(const DecodeParams p) {
   const int r = blockIdx.x, hk = blockIdx.y, b = blockIdx.z;
   int len = p.capacity;
@@ -489,11 +617,28 @@ __global__ void gather_combine_kernel(const DecodeParams p) {
   }
 }
 
+// CTAs of the split kernel that one device holds at once (2 per SM unless the driver says otherwise).
+template <typename T, int HD>
+int coresident_ctas_t(int* out) {
+  constexpr int smem = NSTAGE * 2 * BK * HD * 2;
+  auto kern = decode_splitkv_kernel<T, HD, false, true>;
+  int rc = check_cuda(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem),
+                      "cudaFuncSetAttribute(decode)");
+  if (rc) return rc;
+  int dev = 0, sms = 0, per_sm = 0;
+  if ((rc = check_cuda(cudaGetDevice(&dev), "cudaGetDevice"))) return rc;
+  if ((rc = check_cuda(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev), "SM count"))) return rc;
+  if ((rc = check_cuda(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, NTHR, smem), "occupancy query"))) return rc;
+  *out = sms * per_sm;
+  return PJX_OK;
+}
+
 template <typename T, int HD>
 int launch_decode_t(const DecodeParams& p, cudaStream_t stream) {
   constexpr int smem = NSTAGE * 2 * BK * HD * 2;
   static_assert(smem >= (NWARP * 16 * HD + 2 * NWARP * 16) * 4, "merge scratch must fit in the ring");
-  auto kern = p.block_table ? decode_splitkv_kernel<T, HD, true> : decode_splitkv_kernel<T, HD, false>;
+  auto kern = p.block_table ? decode_splitkv_kernel<T, HD, true, false>
+                            : (p.ex_fused ? decode_splitkv_kernel<T, HD, false, true> : decode_splitkv_kernel<T, HD, false, false>);
   int rc = check_cuda(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem),
                       "cudaFuncSetAttribute(decode)");
   if (rc) return rc;
@@ -501,7 +646,7 @@ int launch_decode_t(const DecodeParams& p, cudaStream_t stream) {
   kern<<<grid, NTHR, smem, stream>>>(p);
   count_launch();
   rc = check_cuda(cudaGetLastError(), "decode launch");
-  if (rc) return rc;
+  if (rc || p.ex_fused) return rc;
   dim3 cgrid(p.rows, p.Hkv, p.B);
   const int cthr = p.Dv >= 128 ? 128 : 64;
   if (p.ex_world > 0) {
@@ -531,6 +676,11 @@ bool decode_fast_supported(const DecodeParams& p, int dtype) {
   if (p.D != p.Dv || (p.D != 64 && p.D != 128)) return false;
   if (p.rows > 16) return false;
   return true;
+}
+
+int decode_coresident_ctas(int dtype, int D, int* out) {
+  if (dtype == PJX_BF16) return D == 128 ? coresident_ctas_t<__nv_bfloat16, 128>(out) : coresident_ctas_t<__nv_bfloat16, 64>(out);
+  return D == 128 ? coresident_ctas_t<__half, 128>(out) : coresident_ctas_t<__half, 64>(out);
 }
 
 int launch_decode(const DecodeParams& p, int dtype, cudaStream_t stream) {
@@ -634,6 +784,9 @@ int pjx_attn_decode_splitkv_static(const void* q, const void* k_cache, const voi
   if (B < 0 || Lq < 0 || capacity < 0 || Hq < 1 || Hkv < 1 || D < 1 || Dv < 1)
     return fail(PJX_ERR_BAD_ARG, "negative or zero dimension (B=%d Lq=%d capacity=%d Hq=%d Hkv=%d D=%d Dv=%d)", B, Lq, capacity, Hq, Hkv, D, Dv);
   if (Hq % Hkv != 0) return fail(PJX_ERR_BAD_ARG, "query heads %d must be a multiple of kv heads %d", Hq, Hkv);
+  if (capacity >= PJX_BAND_NO_UPPER) return fail(PJX_ERR_UNSUPPORTED, "decode: cache capacity must be below 2^30 (got %d)", capacity);
+  if (B > 65535 || Hkv > 65535)
+    return fail(PJX_ERR_UNSUPPORTED, "decode: at most 65535 sequences and 65535 kv heads per call (got B=%d, Hkv=%d)", B, Hkv);
   if (B == 0 || Lq == 0) return PJX_OK;
   if (!q || !k_cache || !v_cache || !o) return fail(PJX_ERR_BAD_ARG, "q, k_cache, v_cache and o must not be null");
   DecodeParams p;

@@ -52,6 +52,7 @@ struct HostPipe {
   cudaStream_t in = nullptr, out = nullptr;
   cudaEvent_t start = nullptr, finish = nullptr, up[kHostEvents] = {}, done[kHostEvents] = {};
   bool ready = false;
+  std::mutex busy;  // held for a whole host-buffer call: the events and copy streams are not re-entrant
 };
 std::mutex g_pipe_mu;
 HostPipe g_pipes[64];
@@ -158,8 +159,8 @@ int pjx_linear(const void* x, const void* w, void* y, int64_t M, int N, int K, i
 int pjx_attn_decode_default_split_len(int B, int Hkv, int capacity) {
   // Measured on B200 (B=16, Hkv=8, caches of 4k..32k keys): CTAs that stream at least
   // ~2048 keys amortise their pipeline fill and merge; more than ~3.5 waves of the 296
-  // CTA slots (2 per SM) buys nothing. Small problems get shorter splits so that one
-  // wave is still filled.
+  // CTA slots (2 per SM) buys nothing. Small problems get a whole number of CTAs per
+  // (batch, kv head) that fits one wave: a partial second wave costs more than the idle slots.
   if (B < 1 || Hkv < 1 || capacity < 1) return 64;
   const double total = (double)B * Hkv * capacity;
   const double slots = 148.0 * 2;
@@ -167,11 +168,24 @@ int pjx_attn_decode_default_split_len(int B, int Hkv, int capacity) {
   const double len_waves = total / (slots * 3.5);
   double len = len_fill < 2048.0 ? len_fill : 2048.0;
   if (len_waves > len) len = len_waves;
+  const long units = (long)B * Hkv;
+  if (len_fill < 2048.0 && units <= (long)slots) {
+    const long per_unit = (long)slots / units;  // >= 1
+    len = (double)((capacity + per_unit - 1) / per_unit);
+  }
   long l64 = ((long)len + 63) / 64 * 64;
   if (l64 < 256) l64 = 256;
   const long cap64 = ((long)capacity + 63) / 64 * 64;
   if (l64 > cap64) l64 = cap64;
   return (int)l64;
+}
+
+// Limits every decode entry point shares: index arithmetic in int and a (split, kv head, batch) grid.
+static int decode_limits(int B, int Hkv, int capacity) {
+  if (capacity >= PJX_BAND_NO_UPPER) return fail(PJX_ERR_UNSUPPORTED, "decode: cache capacity must be below 2^30 (got %d)", capacity);
+  if (B > 65535 || Hkv > 65535)
+    return fail(PJX_ERR_UNSUPPORTED, "decode: at most 65535 sequences and 65535 kv heads per call (got B=%d, Hkv=%d)", B, Hkv);
+  return PJX_OK;
 }
 
 static int decode_geometry(int B, int Hkv, int capacity, int split_len, int* out_len, int* out_splits) {
@@ -198,6 +212,7 @@ int pjx_attn_decode_splitkv(const void* q, const void* k_cache, const void* v_ca
                             size_t workspace_bytes, void* stream) {
   int rc = validate_common(q, k_cache, v_cache, o, B, Lq, capacity, Hq, Hkv, D, Dv, dtype);
   if (rc) return rc;
+  if ((rc = decode_limits(B, Hkv, capacity))) return rc;
   if (B == 0 || Lq == 0) return PJX_OK;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   DecodeParams p;
@@ -237,6 +252,7 @@ int pjx_attn_decode_paged(const void* q, const void* k_pool, const void* v_pool,
   const int capacity = max_pages * page_size;
   int rc = validate_common(q, k_pool, v_pool, o, B, Lq, capacity, Hq, Hkv, D, Dv, dtype);
   if (rc) return rc;
+  if ((rc = decode_limits(B, Hkv, capacity))) return rc;
   if (B == 0 || Lq == 0) return PJX_OK;
   if (!block_table || !kv_lengths) return fail(PJX_ERR_BAD_ARG, "paged decode needs a block table and key lengths");
   DecodeParams p;
@@ -280,6 +296,7 @@ int pjx_attn_decode_sharded(const void* q, const void* k_local, const void* v_lo
     if (!exchange_buffers[i] || (reinterpret_cast<uintptr_t>(exchange_buffers[i]) & 15))
       return fail(PJX_ERR_BAD_ARG, "exchange buffer of rank %d is null or not 16-byte aligned", i);
   if (step == 0) return fail(PJX_ERR_BAD_ARG, "step counts from 1 and must grow by one per call");
+  if ((rc = decode_limits(B, Hkv, capacity_local))) return rc;
   if (B == 0 || Lq == 0) return PJX_OK;
   DecodeParams p;
   p.q = q; p.k = k_local; p.v = v_local; p.kv_lengths = local_lengths; p.o = o; p.lse = lse;
@@ -292,6 +309,12 @@ int pjx_attn_decode_sharded(const void* q, const void* k_local, const void* v_lo
   if (!decode_fast_supported(p, dtype) || !aligned || capacity_local == 0)
     return fail(PJX_ERR_UNSUPPORTED,
                 "the sharded decode takes bf16/fp16, D = Dv in {64,128}, (Hq/Hkv)*Lq <= 16, a non-empty local cache and 16-byte aligned q/k/v");
+  if (split_len == 0 && (int64_t)B * Hkv <= 296) {
+    // one wave of CTAs whatever the cache length: the exchange then runs inside the split kernel
+    const int per_unit = 296 / (B * Hkv);
+    int len = ((capacity_local + per_unit - 1) / per_unit + 63) / 64 * 64;
+    split_len = len < 256 ? 256 : len;
+  }
   if ((rc = decode_geometry(B, Hkv, capacity_local, split_len, &p.split_len, &p.num_splits))) return rc;
   const size_t need = pjx_attn_decode_workspace_bytes(B, Lq, Hq, Hkv, Dv, capacity_local, p.split_len);
   if (!workspace || workspace_bytes < need)
@@ -300,6 +323,11 @@ int pjx_attn_decode_sharded(const void* q, const void* k_local, const void* v_lo
   p.o_part = static_cast<float*>(workspace);
   p.lse_part = reinterpret_cast<float*>(static_cast<char*>(workspace) + align_up(parts * Dv * sizeof(float)));
   p.ex_world = world; p.ex_rank = rank; p.ex_step = step; p.status = status;
+  // The one-kernel exchange has CTAs wait for peers while they hold their SM slots, so it is
+  // only used when every CTA of the grid is resident at once; larger grids take three kernels.
+  int slots = 0;
+  if ((rc = decode_coresident_ctas(dtype, D, &slots))) return rc;
+  p.ex_fused = ((int64_t)p.num_splits * Hkv * B <= slots) && (reinterpret_cast<uintptr_t>(o) & 7) == 0;
   for (int i = 0; i < world; ++i) p.ex_buf[i] = static_cast<unsigned char*>(exchange_buffers[i]);
   return launch_decode(p, dtype, static_cast<cudaStream_t>(stream));
 }
@@ -382,6 +410,9 @@ int pjx_attn_fwd_host(const void* q, const void* k, const void* v, void* o, floa
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   HostPipe* hp = nullptr;
   if ((rc = host_pipe(&hp))) return rc;
+  // One call at a time per device: a second host thread waits here (the call synchronises before
+  // it returns anyway, so nothing is lost by serialising).
+  std::lock_guard<std::mutex> one_call(hp->busy);
   const size_t es = dtype_size(dtype);
   char* base = static_cast<char*>(staging);
   size_t off = 0;

@@ -84,8 +84,11 @@ struct DecodeParams {
   // rank publishes its partial into all ranks' exchange buffers and then combines
   // the partials of all ranks. Buffer layout (identical on every rank), N = B*Lq*Hq:
   //   2 x { float o[world][N][Dv]; float lse[world][N]; }   (double buffered by step parity)
-  //   uint32 flags[16]; uint32 counter;
+  //   uint32 flags[16]; uint32 counter;          (per-rank flags of the three-kernel exchange)
+  //   uint32 unit_flags[world][N];               (per (rank, batch, kv head) flags of the one-kernel exchange)
+  //   uint32 unit_counters[N];                   (split CTAs of a (batch, kv head) that have finished)
   int ex_world = 0, ex_rank = 0;
+  int ex_fused = 0;  // 1: the split kernel's last CTA of each (batch, kv head) exchanges and combines
   uint32_t ex_step = 0;
   unsigned char* ex_buf[16] = {};
   int32_t* status = nullptr;
@@ -125,8 +128,13 @@ struct BwdParams {
 
 constexpr int kMaxExchangeRanks = 16;
 __host__ __device__ inline size_t exchange_record_floats(int world, int64_t n_rows, int Dv) { return (size_t)world * n_rows * (Dv + 1); }
+// byte offset of unit_flags inside an exchange buffer (16-byte aligned)
+__host__ __device__ inline size_t exchange_unit_flags_offset(int world, int64_t n_rows, int Dv) {
+  const size_t head = 2 * exchange_record_floats(world, n_rows, Dv) * sizeof(float) + (kMaxExchangeRanks + 1) * sizeof(uint32_t);
+  return (head + 15) / 16 * 16;
+}
 inline size_t exchange_buffer_bytes(int world, int64_t n_rows, int Dv) {
-  return 2 * exchange_record_floats(world, n_rows, Dv) * sizeof(float) + (kMaxExchangeRanks + 1) * sizeof(uint32_t);
+  return exchange_unit_flags_offset(world, n_rows, Dv) + (size_t)(world + 1) * n_rows * sizeof(uint32_t);
 }
 
 // ---------------------------------------------------------------------------
@@ -148,6 +156,8 @@ bool bwd_sm100_supported(const BwdParams& p, const char** why);
 int launch_bwd_sm100(const BwdParams& p, cudaStream_t stream);
 bool decode_fast_supported(const DecodeParams& p, int dtype);
 int launch_decode(const DecodeParams& p, int dtype, cudaStream_t stream);
+// CTAs of the split-KV kernel (dtype, head width D) that the current device holds at once.
+int decode_coresident_ctas(int dtype, int D, int* out);
 int launch_combine_parts(const float* o_parts, const float* lse_parts, int n_parts, int64_t n_rows,
                          int Dv, void* o, float* lse, int dtype, cudaStream_t stream);
 // C[M, N] = A[M, K] . B[N, K]^T, all row-major, fp32 accumulation, C in `dtype`.

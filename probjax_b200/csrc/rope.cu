@@ -59,8 +59,9 @@ struct Vec16<__half> : Vec16Half<__half2, __half> {};
 // once per (position, pair) and not once per element.
 constexpr int kVecsPerThread = 8;
 
+// x and y may be the same buffer (in-place rotation), so neither is declared restrict.
 template <typename T>
-__global__ void rope_kernel(const T* __restrict__ x, T* __restrict__ y, const float* __restrict__ positions, float offset,
+__global__ void rope_kernel(const T* x, T* y, const float* __restrict__ positions, float offset,
                             int64_t outer, int T_len, int H, int D, int rotary_dim, float neg_log2_base_2_over_rot) {
   constexpr int N = Vec16<T>::N;
   const int units_per_vec = D / N;

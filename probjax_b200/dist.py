@@ -51,6 +51,27 @@ def shard_cache(cache: torch.Tensor, rank: int, world: int, page: int) -> torch.
     return cache.index_select(1, mine).contiguous()
 
 
+def exchange_layout(B: int, Lq: int, Hq: int, Dv: int, world: int) -> dict:
+    """Offsets inside one rank's exchange buffer of ``pjx_attn_decode_sharded`` (the layout
+    the header documents), ``N = B * Lq * Hq`` records per rank:
+
+    ``o(parity, rank)`` / ``lse(parity, rank)``: float32 element offsets of rank ``rank``'s
+    ``[N, Dv]`` partial outputs and ``[N]`` natural-log LSEs in the half used by steps of that
+    parity; ``rank_flags`` / ``unit_flags`` / ``unit_counters``: uint32 element offsets of the
+    per-rank flags, the per-(rank, batch, kv head) flags ``[world, N]`` and the split counters."""
+    N = B * Lq * Hq
+    half = world * N * (Dv + 1)
+    head_bytes = 2 * half * 4 + (16 + 1) * 4
+    uf = (head_bytes + 15) // 16 * 16
+    return {
+        "N": N, "half": half,
+        "o": lambda parity, rank: parity * half + rank * N * Dv,
+        "lse": lambda parity, rank: parity * half + world * N * Dv + rank * N,
+        "rank_flags": 2 * half, "unit_flags": uf // 4, "unit_counters": uf // 4 + world * N,
+        "bytes": uf + (world + 1) * N * 4,
+    }
+
+
 def decode_sharded(q, k_local, v_local, kv_lengths, *, page: int, sm_scale: float, group=None,
                    return_lse: bool = False, _local_fn=None, _combine_fn=None):
     """Decode step with the KV sequence split across ``group``.

@@ -205,6 +205,62 @@ def test_missing_peer_is_reported_not_waited_for_forever():
     assert_close(o, None, want, None, torch.bfloat16, "after a timed-out exchange")
 
 
+def test_sharded_decode_rank0_of_two_with_the_peer_record_prefilled():
+    """The two-rank exchange on one GPU, without one launch waiting for another: rank 1's partial
+    (its own split-KV decode over its shard) and its flags are written into rank 0's exchange
+    buffer by the test, then rank 0 runs its sharded step; the result must equal the oracle over
+    the whole cache.  Covers both exchange forms: the one-kernel form (small grid) and the
+    three-kernel form (a grid larger than one wave of CTAs), on two steps of opposite parity."""
+    import ctypes
+
+    import oracle
+    from probjax_b200 import _lib, decode_forward
+    from probjax_b200 import dist as pjd
+
+    L = _lib.lib()
+    d = dev()
+    for (B, cap, page, split_len) in ((3, 2048, 128, 0), (5, 4096, 256, 64)):
+        c = oracle.make_config(4, B=B, cap=cap)
+        c["kv_lengths"][0] = 7  # rank 1 holds nothing of this sequence
+        Hq, Hkv, D = c["q"].shape[2], c["k"].shape[2], c["q"].shape[3]
+        want, want_lse = oracle.xla_attention(c["q"], c["k"], c["v"], kv_lengths=c["kv_lengths"], sm_scale=c["sm_scale"],
+                                              return_lse=True)
+        q = c["q"].to(d)
+        shards = [(pjd.shard_cache(c["k"], r, 2, page).to(d), pjd.shard_cache(c["v"], r, 2, page).to(d),
+                   pjd.local_lengths(c["kv_lengths"], r, 2, page).to(d)) for r in range(2)]
+        o1, lse1 = decode_forward(q, shards[1][0], shards[1][1], kv_lengths=shards[1][2], sm_scale=c["sm_scale"],
+                                  return_lse=True, partial_f32=True)
+        lay = pjd.exchange_layout(B, 1, Hq, D, 2)
+        assert lay["bytes"] <= L.pjx_attn_decode_sharded_buffer_bytes(B, 1, Hq, D, 2)
+        mine = torch.zeros(L.pjx_attn_decode_sharded_buffer_bytes(B, 1, Hq, D, 2), dtype=torch.uint8, device=d)
+        peer = torch.zeros_like(mine)  # rank 0's stores to rank 1 land here and are not looked at
+        f32, u32 = mine.view(torch.float32), mine.view(torch.int32)
+        k0, v0, l0 = shards[0]
+        ws = torch.empty(L.pjx_attn_decode_workspace_bytes(B, 1, Hq, Hkv, D, k0.shape[1], split_len), dtype=torch.uint8, device=d)
+        o = torch.empty(B, 1, Hq, D, dtype=torch.bfloat16, device=d)
+        lse = torch.empty(B, Hq, 1, dtype=torch.float32, device=d)
+        status = torch.zeros(1, dtype=torch.int32, device=d)
+        ptrs = (ctypes.c_void_p * 2)(mine.data_ptr(), peer.data_ptr())
+        stream = torch.cuda.current_stream(d).cuda_stream
+        N = lay["N"]
+        for step in (1, 2):
+            par = step & 1
+            f32[lay["o"](par, 1): lay["o"](par, 1) + N * D] = o1.reshape(-1)
+            f32[lay["lse"](par, 1): lay["lse"](par, 1) + N] = lse1.permute(0, 2, 1).reshape(-1)  # rows in [B, Lq, Hq] order
+            u32[lay["rank_flags"] + 1] = step
+            u32[lay["unit_flags"] + N: lay["unit_flags"] + 2 * N] = step
+            o.zero_()
+            rc = L.pjx_attn_decode_sharded(q.data_ptr(), k0.data_ptr(), v0.data_ptr(), l0.data_ptr(), o.data_ptr(),
+                                           lse.data_ptr(), B, 1, Hq, Hkv, D, D, k0.shape[1], _lib.PJX_BF16, c["sm_scale"],
+                                           split_len, ws.data_ptr(), ws.numel(), 0, 2, ptrs, step, status.data_ptr(), stream)
+            assert rc == 0, _lib.last_error()
+            assert L.pjx_read_status(status.data_ptr(), stream) == 0
+            assert_close(o, lse, want, want_lse, torch.bfloat16, f"sharded rank 0 of 2, B={B} step {step}")
+        # rank 0 stored its own partial and flags into the peer's buffer as well
+        pu32 = peer.view(torch.int32)
+        assert int(pu32[lay["rank_flags"]]) == 2 or bool((pu32[lay["unit_flags"]: lay["unit_flags"] + B * Hkv] == 2).all())
+
+
 def test_decode_cache_steps_match_causal_attention():
     """A ragged batch decoded token by token through DecodeCache (append kernel + split-KV
     decode) equals attention over each sequence's prefix (the reference's decode branch,

@@ -330,3 +330,42 @@ def test_dense_lowered_masks_and_biases_follow_the_reference_predicates():
     assert torch.equal(add[0, 0], want)
     lm2, res2 = M.split_mask(M.CausalMask(), 1, 6, 6)
     assert res2 is None and lm2.causal
+
+
+def test_raw_wrappers_reject_mismatched_tensors_before_the_library_call():
+    """The C ABI takes every size from q, k and v; the host wrapper must refuse tensors that
+    disagree with them (the reference raises a shape error at trace time for the same calls)."""
+    import torch
+    from probjax_b200 import attention as A
+
+    q = torch.zeros(2, 8, 4, 16)
+    k = torch.zeros(2, 12, 2, 16)
+    v = torch.zeros(2, 12, 2, 24)
+    assert A._check_call(q, k, v) == (2, 8, 12, 4, 2, 16, 24)
+    bad = [
+        dict(k=torch.zeros(2, 12, 2, 8)),                    # head width differs from q
+        dict(k=torch.zeros(3, 12, 2, 16)),                   # batch differs
+        dict(v=torch.zeros(2, 10, 2, 24)),                   # v shorter than k
+        dict(v=torch.zeros(2, 12, 1, 24)),                   # v head count differs from k
+        dict(k=torch.zeros(2, 12, 3, 16), v=torch.zeros(2, 12, 3, 24)),  # 4 query heads over 3 kv heads
+        dict(k=k.half()),                                    # dtype differs
+        dict(bias=torch.zeros(1, 4, 8, 11)),                 # bias key axis
+        dict(bias=torch.zeros(3, 4, 8, 12)),                 # bias batch axis neither 1 nor B
+        dict(bias=torch.zeros(4, 8, 12)),                    # bias rank
+        dict(kv_lengths=torch.zeros(1, dtype=torch.int32)),  # fewer lengths than batch rows
+        dict(o=torch.zeros(2, 8, 4, 16)),                    # o must carry v's width
+        dict(d_o=torch.zeros(2, 8, 2, 24)),
+        dict(lse=torch.zeros(2, 8, 4)),                      # lse is [B, Hq, Lq]
+        dict(q=torch.zeros(8, 4, 16)),                       # rank 3
+    ]
+    for kw in bad:
+        args = dict(q=q, k=k, v=v)
+        args.update(kw)
+        qq, kk, vv = args.pop("q"), args.pop("k"), args.pop("v")
+        with pytest.raises(ValueError):
+            A._check_call(qq, kk, vv, **args)
+    # every raw wrapper goes through the validator before it touches the library
+    import inspect
+
+    for fn in (A.attention_forward, A.attention_backward, A.attention_jvp, A.decode_forward):
+        assert "_check_call(" in inspect.getsource(fn), fn.__name__
