@@ -209,8 +209,7 @@ def cpu_baseline(budget_s=12.0, threads=None):
     dt = time.perf_counter() - t0
     fl = prefill_flops(done, C2["Hq"], C2["S"], C2["S"], C2["D"], C2["D"], False)
     return {"value": fl / dt / 1e12, "unit": "TFLOP/s", "cores": threads, "kind": "port",
-            "sample": f"{done} of {C2['B']} batch rows of the workload (B={done} Hq=32 Hkv=8 S=4096 D=128, non-causal), "
-                      f"{dt:.1f} s, torch CPU fp32 restatement of the reference's XLA path"}
+            "sample": f"{done} of {C2['B']} batch rows of the workload, {dt:.1f} s, torch fp32 port of the XLA path"}
 
 
 WORKLOAD = "GQA prefill fwd bf16 B{b} Hq32 Hkv8 S4096 D128 non-causal (per GPU)"
@@ -258,8 +257,8 @@ def bench_extra(name, fn, steps, warmup, work, unit, peak, bound, pk_note, profi
         ms = time_steps(fn, steps, warmup) / steps
         ach = work / (ms * 1e-3)
         out = {"ms": ms, "value": ach, "unit": unit, "bound": bound, "frac": ach / peak}
-        if profile:
-            out["profile"] = profile
+        if profile:  # file under profiles/ (without the .md) that holds the ncu summary of this kernel
+            out["profile"] = os.path.splitext(os.path.basename(profile))[0]
         return out
     except Exception as e:  # keep the headline line alive
         return {"error": f"{type(e).__name__}: {e}"[:200]}
@@ -354,7 +353,7 @@ def main():
     d2h = q.numel() * q.element_size()
     e2e = {"value": flops * world / (ms_e2e * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": ms_e2e,
            "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
-           "call": "probjax_b200.attention_forward on pinned host tensors (pjx_attn_fwd_host)"}
+           "call": "attention_forward on pinned host tensors (pjx_attn_fwd_host)"}
 
     # one-shot parity of the headline result: batch row 0 against the oracle (outside every timed region)
     try:
@@ -370,7 +369,7 @@ def main():
         "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "bf16", "data": "synthetic",
         "config": {"workload": WORKLOAD.format(b=args.batch),
-                   "l2": "inputs+outputs 335 MB per step exceed the 126 MB L2; no flush needed",
+                   "l2": "335 MB of inputs+outputs per step exceed the 126 MB L2: no flush",
                    "parallelism": f"batch-sharded x{world}, no collective" if world > 1 else "single GPU"},
         "roofline": {"bound": "tensor", "achieved": per_gpu, "peak": pk["bf16_tflops"], "unit": "TFLOP/s",
                      "frac": per_gpu / pk["bf16_tflops"],
@@ -378,7 +377,7 @@ def main():
                      # with the batch (traffic grows in proportion); the algorithmic bytes beside it
                      "traffic": profiled_prefill_traffic(args.batch), "traffic_source": PREFILL_PROFILE,
                      "algorithmic_bytes": alg_bytes,
-                     "of": f"{pk['source']} burst bf16 peak", "kernel": "attn_fwd_sm100_kernel<128,128,128,2,2,bf16>",
+                     "of": f"{pk['source']} burst peak", "kernel": "attn_fwd_sm100_kernel<128,128,128,2,2,bf16>",
                      "frac_of_sustained": per_gpu / pk["bf16_tflops_sustained"]},
         "e2e": e2e, "gpu_launches": int(launches_per_step * args.steps), "clocks": clocks,
         "parity_max_abs_err": parity,
@@ -434,7 +433,7 @@ def main():
             fl1 = prefill_flops(2, 4, 256, 256, 64, 64, True)
             extras["fp32_causal_small"] = bench_extra(
                 "c1", lambda: pj.attention_forward(q1, k1, v1, causal=True, sm_scale=c1["sm_scale"]), xs * 5, xw,
-                fl1 / 1e12, "TFLOP/s", 72.0, "fp32 FMA (nominal, for scale only)", "nominal")
+                fl1 / 1e12, "TFLOP/s", 72.0, "fp32 FMA nominal", "nominal")
             got = pj.attention_forward(q1, k1, v1, causal=True, sm_scale=c1["sm_scale"]).cpu()
             want = oracle.xla_attention(c1["q"], c1["k"], c1["v"], causal=True, sm_scale=c1["sm_scale"])
             extras["fp32_causal_small"]["max_abs_error_vs_oracle"] = float((got - want).abs().max())

@@ -96,6 +96,63 @@ int pjx_attn_fwd_band(const void* q, const void* k, const void* v, void* o, floa
                       void* stream);
 
 /*
+ * Structured masks and score modifiers, evaluated element by element inside the kernels from
+ * O(B T) / O(H T) data: no [Lq, Lkv] tensor is ever built.  A NULL pointer / zero switches a
+ * field off; an all-zero struct (or a NULL struct pointer) is "no modifiers".
+ *
+ * Replaces the per-tile evaluation of the reference's mask / bias classes inside its kernels
+ * (probjax/nn/pallas_kernels/attention_mask_bias.py; applied at kernels/attention.py:456-481):
+ *
+ *   seg_q, seg_k     int32 [Bs, Lq] / [Bs, Lkv] (Bs in {1, B}; *_batch_stride in elements, 0 =
+ *                    shared): key j is visible to query i iff seg_q[b,i] == seg_k[b,j].
+ *                    SameSegmentMask 1537-1565, BlockDiagonalMask 871-893 (AND the causal band:
+ *                    BlockDiagonalCausalMask 984-1008).  SeqLenMask 1239-1323 and
+ *                    MarginalizationMask 1671-1699, both of the form (a_i & a_j) | i == j for a
+ *                    per-token keep vector a, are the ids "0 where a, else -(t+1)".
+ *   row_kv_limit     int32 [Bs, Lq]: visible iff j < row_kv_limit[b,i] (KeyPaddingMask 1132-1234,
+ *                    whose lengths are per query row).
+ *   prefix_len       int32 [B]: keys j < prefix_len[b] are visible to every row, OR-ed with the
+ *                    band (PrefixLMMask 785-809 with the causal band).
+ *   rel_bias         float32 [Hr, Lq + Lkv - 1] (Hr in {1, Hq}; head stride in elements, 0 =
+ *                    shared): score += rel_bias[h, (j - i) + Lq - 1].  Any bias of the head and the
+ *                    relative position: T5RelativePositionBias 2453, LearnedRelativePositionBias
+ *                    2521 (bucket look-up done per distance by the caller), ConstantBias 1781.
+ *   alibi_slopes     float32 [Hq] with alibi_mode 1: score -= slope[h] * max(i - j, 0)
+ *                    (CausalAlibiBias 2230-2247); mode 2: score -= slope[h] * |i - j|
+ *                    (SymmetricAlibiBias 2355-2372, DistanceDecayBias 2387-2406).
+ *   head_scale       float32 [Hq]: score *= head_scale[h] (PerHeadScaleBias 2606).
+ *   softcap          > 0: score = softcap * tanh(score / softcap) (SoftCappingBias 2564-2582).
+ *
+ * "score" is sm_scale * q.k; every term is a delta on that same value and the deltas add up, as
+ * SumBias 553-579 defines the sum of modifiers; the dense `bias` argument adds on top.  The
+ * backward and forward-mode entry points multiply dS by d(modified score)/d(score), the `grad`
+ * methods of the two non-additive classes (2590-2601, 2637-2650).
+ */
+typedef struct pjx_score_mod {
+  const int32_t* seg_q;
+  const int32_t* seg_k;
+  int64_t seg_q_batch_stride, seg_k_batch_stride;
+  const int32_t* row_kv_limit;
+  int64_t row_kv_limit_batch_stride;
+  const int32_t* prefix_len;
+  const float* rel_bias;
+  int64_t rel_bias_head_stride;
+  const float* alibi_slopes;
+  int32_t alibi_mode;
+  const float* head_scale;
+  float softcap;
+} pjx_score_mod;
+
+/* pjx_attn_fwd_band with score modifiers (mod may be NULL).  16-bit inputs with head shapes the
+ * tcgen05 kernel takes run on it with the modifiers evaluated in its softmax warps; other calls
+ * run the exact-fp32 kernel. */
+int pjx_attn_fwd_mod(const void* q, const void* k, const void* v, void* o, float* lse,
+                     const int32_t* kv_lengths, const float* bias, int64_t bias_batch_stride,
+                     int64_t bias_head_stride, int B, int Lq, int Lkv, int Hq, int Hkv, int D, int Dv,
+                     int dtype, int band_lo, int band_hi, float sm_scale, const pjx_score_mod* mod,
+                     int impl, int32_t* status, void* stream);
+
+/*
  * Backward of pjx_attn_fwd: dq, dk, dv from q, k, v, o, d_o and the forward's
  * natural-log lse, for the same masks and bias (the bias itself gets no gradient
  * here).  First correct path: exact fp32 arithmetic on CUDA cores for every dtype.
@@ -127,6 +184,14 @@ int pjx_attn_bwd_band(const void* q, const void* k, const void* v, const void* o
                       int band_lo, int band_hi, float sm_scale, int impl, void* workspace,
                       size_t workspace_bytes, int32_t* status, void* stream);
 size_t pjx_attn_bwd_workspace_bytes(int B, int Lq, int Hq);
+/* pjx_attn_bwd_band with score modifiers (mod may be NULL).  With modifiers the CUDA-core kernels
+ * run; `dbias` cannot be combined with head_scale / softcap. */
+int pjx_attn_bwd_mod(const void* q, const void* k, const void* v, const void* o, const float* lse,
+                     const void* d_o, void* dq, void* dk, void* dv, const int32_t* kv_lengths,
+                     const float* bias, int64_t bias_batch_stride, int64_t bias_head_stride,
+                     float* dbias, int B, int Lq, int Lkv, int Hq, int Hkv, int D, int Dv, int dtype,
+                     int band_lo, int band_hi, float sm_scale, const pjx_score_mod* mod, int impl,
+                     void* workspace, size_t workspace_bytes, int32_t* status, void* stream);
 
 /*
  * Forward-mode derivative of pjx_attn_fwd_band: the tangent t_o of o for tangents tq, tk, tv of
@@ -141,6 +206,12 @@ int pjx_attn_jvp_band(const void* q, const void* k, const void* v, const void* t
                       const float* bias, int64_t bias_batch_stride, int64_t bias_head_stride, int B,
                       int Lq, int Lkv, int Hq, int Hkv, int D, int Dv, int dtype, int band_lo,
                       int band_hi, float sm_scale, void* stream);
+/* The same with score modifiers (mod may be NULL). */
+int pjx_attn_jvp_mod(const void* q, const void* k, const void* v, const void* tq, const void* tk,
+                     const void* tv, const float* lse, void* t_o, const int32_t* kv_lengths,
+                     const float* bias, int64_t bias_batch_stride, int64_t bias_head_stride, int B,
+                     int Lq, int Lkv, int Hq, int Hkv, int D, int Dv, int dtype, int band_lo,
+                     int band_hi, float sm_scale, const pjx_score_mod* mod, void* stream);
 
 /*
  * Split-KV decode forward over a KV cache with per-sequence valid lengths,
@@ -328,6 +399,14 @@ int pjx_mla_fwd(const void* q, const void* cache, const void* wk, const void* wv
                 void* workspace, size_t workspace_bytes, int32_t* status, void* stream);
 size_t pjx_mla_workspace_bytes(int B, int S, int H, int Dqk, int Dv, int R, int dtype,
                                int has_projections);
+/* pjx_mla_fwd with the band form of the mask and score modifiers (mod may be NULL): the masks and
+ * biases `mla` shares with `mha` (latent_attention.py:636-766 takes the same mask / bias objects). */
+int pjx_mla_fwd_mod(const void* q, const void* cache, const void* wk, const void* wv, void* o,
+                    float* lse, const int32_t* kv_lengths, const float* bias,
+                    int64_t bias_batch_stride, int64_t bias_head_stride, int B, int Lq, int S, int H,
+                    int Dqk, int Dv, int R, int dtype, int band_lo, int band_hi, float sm_scale,
+                    const pjx_score_mod* mod, int impl, void* workspace, size_t workspace_bytes,
+                    int32_t* status, void* stream);
 
 /*
  * The forward with HOST buffers: copies q, k, v (and kv_lengths, bias) to the

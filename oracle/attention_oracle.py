@@ -100,7 +100,8 @@ class _Mods:
     ``-inf`` (:236-246 bias, :247-273 mask, :269-271 padded keys).
     """
 
-    def __init__(self, *, causal, kv_lengths, keep, bias, q_len, kv_len, kv_pad):
+    def __init__(self, *, causal, kv_lengths, keep, bias, q_len, kv_len, kv_pad, score_fn=None):
+        self.score_fn = score_fn
         self.causal = bool(causal)
         self.kv_lengths = None if kv_lengths is None else _as_t(kv_lengths, torch.int64).reshape(-1)
         self.keep = None if keep is None else _as_t(keep, torch.bool)
@@ -116,6 +117,7 @@ class _Mods:
             or self.keep is not None
             or self.bias is not None
             or self.kv_padded
+            or self.score_fn is not None
         )
 
     @staticmethod
@@ -130,6 +132,10 @@ class _Mods:
     def apply(self, s, q0, bq, k0, kc):
         if not self.any:
             return s
+        if self.score_fn is not None:
+            # a bias object is a function of the scaled scores, the head and the absolute indices
+            # (attention_xla.py:236-246 calls ``self.bias(s_bh, h, span_q, span_k, data=chunk)``)
+            s = self.score_fn(s, q0 + torch.arange(bq), k0 + torch.arange(kc))
         if self.bias is not None:
             s = s + self._window(self.bias, q0, bq, k0, kc)
         keep = None
@@ -238,13 +244,16 @@ def xla_attention(
     block_q: int | None = None,
     block_k: int | None = None,
     return_lse: bool = False,
+    score_fn=None,
 ):
     """Restatement of ``xla_attention`` (attention_xla.py:601-721), forward only.
 
     ``q [B,Lq,Hq,D]``, ``k [B,Lkv,Hkv,D]``, ``v [B,Lkv,Hkv,Dv]``.  The mask is
     given structurally (``causal``: ``CausalMask``; ``kv_lengths [B]``:
     ``KVLenMask``) and/or as a dense boolean ``keep [B|1,H|1,Q,K]``; ``bias`` is
-    a dense additive ``[B|1,H|1,Q,K]`` array (``DenseBias``).  Output has
+    a dense additive ``[B|1,H|1,Q,K]`` array (``DenseBias``); ``score_fn(s, q_idx, k_idx)``
+    stands for a non-dense bias object: it maps the scaled scores ``s [B,Hq,q,k]`` of the
+    rows ``q_idx`` and keys ``k_idx`` to modified scores (:236-246).  Output has
     ``q``'s dtype; the optional LSE is natural log ``[B,Hq,Lq]`` fp32 with
     ``+inf`` for rows without a valid key (:417-420).
     """
@@ -281,7 +290,7 @@ def xla_attention(
     kt, vt = to_bhtd(k, kv_pad), to_bhtd(v, kv_pad)
     mods = _Mods(
         causal=causal, kv_lengths=kv_lengths, keep=keep, bias=bias,
-        q_len=q_len, kv_len=kv_len, kv_pad=kv_pad,
+        q_len=q_len, kv_len=kv_len, kv_pad=kv_pad, score_fn=score_fn,
     )
     if strategy == "dense":
         o5, lse = _dense_forward(q5, kt, vt, mods, sm_scale)

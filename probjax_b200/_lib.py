@@ -20,6 +20,22 @@ IMPL_AUTO, IMPL_GENERIC, IMPL_SM100 = 0, 1, 2
 
 _vp, _i, _i64, _f, _sz = C.c_void_p, C.c_int, C.c_int64, C.c_float, C.c_size_t
 
+class ScoreMod(C.Structure):
+    """``pjx_score_mod`` of the header, field by field."""
+
+    _fields_ = [
+        ("seg_q", _vp), ("seg_k", _vp), ("seg_q_batch_stride", _i64), ("seg_k_batch_stride", _i64),
+        ("row_kv_limit", _vp), ("row_kv_limit_batch_stride", _i64),
+        ("prefix_len", _vp),
+        ("rel_bias", _vp), ("rel_bias_head_stride", _i64),
+        ("alibi_slopes", _vp), ("alibi_mode", C.c_int32),
+        ("head_scale", _vp),
+        ("softcap", _f),
+    ]
+
+
+_modp = C.POINTER(ScoreMod)
+
 # name -> (restype, argtypes); mirrors include/pjx_attention.h declaration by declaration.
 SIGNATURES = {
     "pjx_version": (_i, []),
@@ -29,6 +45,14 @@ SIGNATURES = {
                           _i, _i, _i, _i, _i, _i, _i, _i, _i, _f, _i, _vp, _vp]),
     "pjx_attn_fwd_band": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64,
                                _i, _i, _i, _i, _i, _i, _i, _i, _i, _i, _f, _i, _vp, _vp]),
+    "pjx_attn_fwd_mod": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64,
+                              _i, _i, _i, _i, _i, _i, _i, _i, _i, _i, _f, _modp, _i, _vp, _vp]),
+    "pjx_attn_bwd_mod": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _vp,
+                              _i, _i, _i, _i, _i, _i, _i, _i, _i, _i, _f, _modp, _i, _vp, _sz, _vp, _vp]),
+    "pjx_attn_jvp_mod": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64,
+                              _i, _i, _i, _i, _i, _i, _i, _i, _i, _i, _f, _modp, _vp]),
+    "pjx_mla_fwd_mod": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64,
+                             _i, _i, _i, _i, _i, _i, _i, _i, _i, _i, _f, _modp, _i, _vp, _sz, _vp, _vp]),
     "pjx_attn_bwd_band": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _vp,
                                _i, _i, _i, _i, _i, _i, _i, _i, _i, _i, _f, _i, _vp, _sz, _vp, _vp]),
     "pjx_attn_jvp_band": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64,

@@ -20,7 +20,8 @@ import numpy as np
 import torch
 
 from . import _lib
-from .masks import AttentionBias, AttentionMask, NoMask, lower_bias, lower_dense, lower_mask, split_mask
+from .masks import (AttentionBias, AttentionMask, LoweredBias, LoweredMask, NoMask, lower_bias, lower_bias_structured,
+                    lower_dense, lower_mask, split_mask)
 
 _DTYPES = {torch.float32: _lib.PJX_F32, torch.bfloat16: _lib.PJX_BF16, torch.float16: _lib.PJX_F16}
 _IMPL = {None: _lib.IMPL_AUTO, "b200": _lib.IMPL_AUTO, "b200:generic": _lib.IMPL_GENERIC,
@@ -139,6 +140,58 @@ def _gqa_group(hq: int, hkv: int) -> int:
     return hq // hkv
 
 
+class ScoreMods:
+    """The ``pjx_score_mod`` argument of one call: the structured part of a lowered mask and bias
+    (segment ids, per-row key limits, prefix lengths, relative-position table, ALiBi slopes, per-head
+    scale, soft cap) as device tensors plus the C struct that points at them.  Keeps the tensors
+    alive for as long as the object lives."""
+
+    def __init__(self, lm: LoweredMask | None = None, lb: LoweredBias | None = None, device=None):
+        import ctypes
+
+        self.device = torch.device(device)
+        self._keep = []
+        st = _lib.ScoreMod()
+
+        def put(t, dtype):
+            t = torch.as_tensor(t).to(device=self.device, dtype=dtype).contiguous()
+            self._keep.append(t)
+            return t
+
+        if lm is not None:
+            if lm.seg_q is not None:
+                sq, sk = put(lm.seg_q, torch.int32), put(lm.seg_k, torch.int32)
+                st.seg_q, st.seg_k = sq.data_ptr(), sk.data_ptr()
+                st.seg_q_batch_stride = 0 if sq.shape[0] == 1 else sq.stride(0)
+                st.seg_k_batch_stride = 0 if sk.shape[0] == 1 else sk.stride(0)
+            if lm.row_kv_limit is not None:
+                rl = put(lm.row_kv_limit, torch.int32)
+                st.row_kv_limit = rl.data_ptr()
+                st.row_kv_limit_batch_stride = 0 if rl.shape[0] == 1 else rl.stride(0)
+            if lm.prefix_len is not None:
+                st.prefix_len = put(lm.prefix_len, torch.int32).data_ptr()
+        if lb is not None:
+            if lb.rel_bias is not None:
+                rb = put(lb.rel_bias, torch.float32)
+                st.rel_bias = rb.data_ptr()
+                st.rel_bias_head_stride = 0 if rb.shape[0] == 1 else rb.stride(0)
+            if lb.alibi_slopes is not None:
+                st.alibi_slopes = put(lb.alibi_slopes, torch.float32).data_ptr()
+                st.alibi_mode = int(lb.alibi_mode)
+            if lb.head_scale is not None:
+                st.head_scale = put(lb.head_scale, torch.float32).data_ptr()
+            st.softcap = float(lb.softcap)
+        self.struct = st
+        self.active = bool(self._keep) or st.softcap > 0
+        self.nbytes = sum(t.numel() * t.element_size() for t in self._keep)
+        self._ref = ctypes.byref(st)
+
+    @staticmethod
+    def arg(mods):
+        """The pointer to pass for ``mods`` (``None`` = a null pointer)."""
+        return None if mods is None or not mods.active else mods._ref
+
+
 # ---------------------------------------------------------------------------
 # Raw calls (rank-4 tensors, structural mask)
 # ---------------------------------------------------------------------------
@@ -160,8 +213,8 @@ def _band_args(causal, band):
 
 
 def attention_forward(q, k, v, *, causal=False, band=None, kv_lengths=None, bias=None, sm_scale=1.0,
-                      return_lse=False, impl=None, out=None, lse_out=None):
-    """One ``pjx_attn_fwd_band`` call. ``q [B,Lq,Hq,D]``, ``k [B,Lkv,Hkv,D]``,
+                      return_lse=False, impl=None, out=None, lse_out=None, mods: ScoreMods | None = None):
+    """One ``pjx_attn_fwd_mod`` call. ``q [B,Lq,Hq,D]``, ``k [B,Lkv,Hkv,D]``,
     ``v [B,Lkv,Hkv,Dv]``; CUDA tensors stay on the device, host tensors use the
     host-buffer entry point.  ``band = (lo, hi)`` limits query ``i`` to keys
     ``i + lo .. i + hi`` (``None`` leaves a side open; ``causal`` is ``(None, 0)``).
@@ -194,12 +247,15 @@ def attention_forward(q, k, v, *, causal=False, band=None, kv_lengths=None, bias
             bs = 0 if bt.shape[0] == 1 else bt.stride(0)
             hs = 0 if bt.shape[1] == 1 else bt.stride(1)
         with torch.cuda.device(dev):
-            rc = L.pjx_attn_fwd_band(_ptr(q), _ptr(k), _ptr(v), _ptr(o), _ptr(lse), _ptr(kvl), _ptr(bt), bs, hs,
-                                     B, Lq, Lkv, Hq, Hkv, D, Dv, _DTYPES[q.dtype], band_lo, band_hi,
-                                     float(sm_scale), _IMPL[impl], _ptr(_status_word(dev)), _stream(dev))
+            rc = L.pjx_attn_fwd_mod(_ptr(q), _ptr(k), _ptr(v), _ptr(o), _ptr(lse), _ptr(kvl), _ptr(bt), bs, hs,
+                                    B, Lq, Lkv, Hq, Hkv, D, Dv, _DTYPES[q.dtype], band_lo, band_hi,
+                                    float(sm_scale), ScoreMods.arg(mods), _IMPL[impl], _ptr(_status_word(dev)),
+                                    _stream(dev))
         _lib.check(rc)
         return (o, lse) if return_lse else o
     # host buffers
+    if ScoreMods.arg(mods) is not None:
+        raise NotImplementedError("the host-buffer entry point takes no structured masks or score modifiers")
     is_causal = band_lo == _BAND_NO_LOWER and band_hi == 0
     if not is_causal and (band_lo != _BAND_NO_LOWER or band_hi != _BAND_NO_UPPER):
         raise NotImplementedError("the host-buffer entry point takes no mask band other than the causal one")
@@ -222,8 +278,8 @@ def attention_forward(q, k, v, *, causal=False, band=None, kv_lengths=None, bias
 
 
 def attention_backward(q, k, v, o, lse, d_o, *, causal=False, band=None, kv_lengths=None, bias=None,
-                       sm_scale=1.0, impl=None, bias_grad=False):
-    """One ``pjx_attn_bwd_band`` call on CUDA tensors: ``(dq, dk, dv)`` for the forward
+                       sm_scale=1.0, impl=None, bias_grad=False, mods: ScoreMods | None = None):
+    """One ``pjx_attn_bwd_mod`` call on CUDA tensors: ``(dq, dk, dv)`` for the forward
     that produced ``o`` and ``lse`` from the same arguments; with ``bias_grad`` also the
     gradient of the dense bias (float32, the bias' shape)."""
     _require_gpu()
@@ -253,17 +309,17 @@ def attention_backward(q, k, v, o, lse, d_o, *, causal=False, band=None, kv_leng
     L = _lib.lib()
     ws = _scratch_bytes(dev, "bwd", L.pjx_attn_bwd_workspace_bytes(B, Lq, Hq))
     with torch.cuda.device(dev):
-        rc = L.pjx_attn_bwd_band(_ptr(q), _ptr(k), _ptr(v), _ptr(o), _ptr(lse), _ptr(d_o), _ptr(dq), _ptr(dk),
-                                 _ptr(dv), _ptr(kvl), _ptr(bt), bs, hs, _ptr(dbias), B, Lq, Lkv, Hq, Hkv, D, Dv,
-                                 _DTYPES[q.dtype], band_lo, band_hi, float(sm_scale), _IMPL[impl], _ptr(ws),
-                                 ws.numel(), _ptr(_status_word(dev)), _stream(dev))
+        rc = L.pjx_attn_bwd_mod(_ptr(q), _ptr(k), _ptr(v), _ptr(o), _ptr(lse), _ptr(d_o), _ptr(dq), _ptr(dk),
+                                _ptr(dv), _ptr(kvl), _ptr(bt), bs, hs, _ptr(dbias), B, Lq, Lkv, Hq, Hkv, D, Dv,
+                                _DTYPES[q.dtype], band_lo, band_hi, float(sm_scale), ScoreMods.arg(mods), _IMPL[impl],
+                                _ptr(ws), ws.numel(), _ptr(_status_word(dev)), _stream(dev))
     _lib.check(rc)
     return (dq, dk, dv, dbias) if bias_grad else (dq, dk, dv)
 
 
 def attention_jvp(q, k, v, lse, tq=None, tk=None, tv=None, *, causal=False, band=None, kv_lengths=None, bias=None,
-                  sm_scale=1.0):
-    """One ``pjx_attn_jvp_band`` call on CUDA tensors: the tangent of ``o`` for tangents
+                  sm_scale=1.0, mods: ScoreMods | None = None):
+    """One ``pjx_attn_jvp_mod`` call on CUDA tensors: the tangent of ``o`` for tangents
     ``tq, tk, tv`` (``None`` = zero) of the forward that produced ``lse``."""
     _require_gpu()
     band_lo, band_hi = _band_args(causal, band)
@@ -286,9 +342,9 @@ def attention_jvp(q, k, v, lse, tq=None, tk=None, tv=None, *, causal=False, band
         bs = 0 if bt.shape[0] == 1 else bt.stride(0)
         hs = 0 if bt.shape[1] == 1 else bt.stride(1)
     with torch.cuda.device(dev):
-        rc = _lib.lib().pjx_attn_jvp_band(_ptr(q), _ptr(k), _ptr(v), _ptr(tq), _ptr(tk), _ptr(tv), _ptr(lse), _ptr(t_o),
-                                          _ptr(kvl), _ptr(bt), bs, hs, B, Lq, Lkv, Hq, Hkv, D, Dv, _DTYPES[q.dtype],
-                                          band_lo, band_hi, float(sm_scale), _stream(dev))
+        rc = _lib.lib().pjx_attn_jvp_mod(_ptr(q), _ptr(k), _ptr(v), _ptr(tq), _ptr(tk), _ptr(tv), _ptr(lse), _ptr(t_o),
+                                         _ptr(kvl), _ptr(bt), bs, hs, B, Lq, Lkv, Hq, Hkv, D, Dv, _DTYPES[q.dtype],
+                                         band_lo, band_hi, float(sm_scale), ScoreMods.arg(mods), _stream(dev))
     _lib.check(rc)
     return t_o
 
@@ -299,12 +355,12 @@ class _AttentionFunction(torch.autograd.Function):
     its kernels the same way, kernels/attention.py:3156-3270)."""
 
     @staticmethod
-    def forward(ctx, q, k, v, band, kv_lengths, bias, sm_scale, impl):
+    def forward(ctx, q, k, v, band, kv_lengths, bias, sm_scale, impl, mods=None):
         o, lse = attention_forward(q, k, v, band=band, kv_lengths=kv_lengths, bias=bias, sm_scale=sm_scale,
-                                   return_lse=True, impl=impl)
+                                   return_lse=True, impl=impl, mods=mods)
         ctx.save_for_backward(q, k, v, o, lse)
         ctx.save_for_forward(q, k, v, lse)
-        ctx.args = (band, kv_lengths, bias, sm_scale, impl)
+        ctx.args = (band, kv_lengths, bias, sm_scale, impl, mods)
         ctx.mark_non_differentiable(lse)
         return o, lse
 
@@ -312,20 +368,21 @@ class _AttentionFunction(torch.autograd.Function):
     def jvp(ctx, tq, tk, tv, *_):
         # forward-mode: the reference's diff_mode="forward" path (kernels/attention.py:3303-3330)
         q, k, v, lse = ctx.saved_tensors
-        band, kv_lengths, bias, sm_scale, _impl = ctx.args
-        t_o = attention_jvp(q, k, v, lse, tq, tk, tv, band=band, kv_lengths=kv_lengths, bias=bias, sm_scale=sm_scale)
+        band, kv_lengths, bias, sm_scale, _impl, mods = ctx.args
+        t_o = attention_jvp(q, k, v, lse, tq, tk, tv, band=band, kv_lengths=kv_lengths, bias=bias, sm_scale=sm_scale,
+                            mods=mods)
         return t_o, None
 
     @staticmethod
     def backward(ctx, d_o, _d_lse):
         q, k, v, o, lse = ctx.saved_tensors
-        band, kv_lengths, bias, sm_scale, impl = ctx.args
+        band, kv_lengths, bias, sm_scale, impl, mods = ctx.args
         want_dbias = bias is not None and ctx.needs_input_grad[5]
         # a forced tensor-core forward does not force the tensor-core backward, which takes fewer shapes
         grads = attention_backward(q, k, v, o, lse, d_o, band=band, kv_lengths=kv_lengths, bias=bias, sm_scale=sm_scale,
-                                   impl=impl if impl == "b200:generic" else None, bias_grad=want_dbias)
+                                   impl=impl if impl == "b200:generic" else None, bias_grad=want_dbias, mods=mods)
         dbias = grads[3].to(bias.dtype) if want_dbias else None
-        return grads[0], grads[1], grads[2], None, None, dbias, None, None
+        return grads[0], grads[1], grads[2], None, None, dbias, None, None, None
 
 
 def _wants_grad(*tensors) -> bool:
@@ -439,6 +496,39 @@ def _apply_q_limit(out, lse, q_limit):
     return out, lse
 
 
+def masks_DenseBias(t):
+    from .masks import DenseBias
+
+    return DenseBias(t)
+
+
+def _fold_low_rank(q, k, v, terms, sm_scale: float):
+    """``LowRankBias`` terms as extra feature columns of q and k: ``sm_scale (q' . k') = sm_scale q.k +
+    scale qf.kf`` with both factors multiplied by ``sqrt(scale / sm_scale)`` and cast to the input dtype,
+    as the reference folds them (layers/attention.py:1602-1639).  The factors are per query head, so
+    K / V heads are repeated to the query head count first."""
+    if sm_scale <= 0:
+        raise ValueError("LowRankBias requires a positive sm_scale")
+    B, Lq, Hq, _ = q.shape
+    Lkv, Hkv = k.shape[1], k.shape[2]
+    if Hkv != Hq:
+        k, v = k.repeat_interleave(Hq // Hkv, dim=2), v.repeat_interleave(Hq // Hkv, dim=2)
+    q_extra, k_extra = [], []
+    for t in terms:
+        if Lq > t.query_factors.shape[1]:
+            raise ValueError(f"q_len={Lq} exceeds maximum {t.query_factors.shape[1]}")
+        if Lkv > t.key_factors.shape[1]:
+            raise ValueError(f"kv_len={Lkv} exceeds maximum {t.key_factors.shape[1]}")
+        if t.query_factors.shape[0] not in (1, Hq):
+            raise ValueError(f"factor head count {t.query_factors.shape[0]} cannot broadcast to {Hq}")
+        f = math.sqrt(t.scale / sm_scale)
+        qf = (t.query_factors[:, :Lq].to(q.device).float() * f).to(q.dtype)  # [H|1, Lq, r]
+        kf = (t.key_factors[:, :Lkv].to(q.device).float() * f).to(q.dtype)
+        q_extra.append(qf.permute(1, 0, 2)[None].expand(B, Lq, Hq, qf.shape[-1]))
+        k_extra.append(kf.permute(1, 0, 2)[None].expand(B, Lkv, Hq, kf.shape[-1]))
+    return torch.cat([q, *q_extra], dim=-1), torch.cat([k, *k_extra], dim=-1), v
+
+
 def mha(q, k, v, mask: AttentionMask | None = None, bias: AttentionBias | None = None, rng=None,
         sm_scale: float = 1.0, block_sizes=None, backward_pass_impl: str = "auto", num_warps=None,
         num_stages: int = 2, grid=None, interpret: bool = False, debug: bool = False,
@@ -458,24 +548,34 @@ def mha(q, k, v, mask: AttentionMask | None = None, bias: AttentionBias | None =
     if interpret:
         raise NotImplementedError("interpret mode belongs to the Pallas kernels; this library runs CUDA only")
     B, Lq = q.shape[0], q.shape[1]
+    # What the kernels take natively: a band, key lengths, a query limit, and -- evaluated per element
+    # from O(B T) / O(H T) data -- segment ids, per-row key limits, a prefix, relative-position tables,
+    # ALiBi slopes, a per-head scale and a soft cap.  Only what is left (or / xor / not compositions)
+    # is densified into the additive bias.
     lm, residual = split_mask(mask, B, Lq, k.shape[1])
-    if residual is None:
-        bt = lower_bias(bias, B, q.shape[2], Lq, k.shape[1])
-    else:  # mask classes without a native form: their dense -inf tensor rides on the bias
-        bt = lower_dense(residual, bias, B, q.shape[2], Lq, k.shape[1])
+    lb = lower_bias_structured(bias, B, q.shape[2], Lq, k.shape[1])
+    if lb.low_rank:
+        q, k, v = _fold_low_rank(q, k, v, lb.low_rank, float(sm_scale))
+    bt = lb.dense
+    if residual is not None:  # mask classes without a native form: their dense -inf tensor rides on the bias
+        bt = lower_dense(residual, None if bt is None else masks_DenseBias(bt), B, q.shape[2], Lq, k.shape[1])
+    mods = ScoreMods(lm, lb, q.device) if (lm.structured or lb.structured) and q.is_cuda else None
+    if (lm.structured or lb.structured) and not q.is_cuda:
+        raise NotImplementedError("structured masks and score modifiers take CUDA tensors")
     if _wants_grad(q, k, v, bt):
         # differentiation always runs the regular kernels (attention_splitkv.py:253-272)
         if not q.is_cuda:
             raise NotImplementedError("differentiable attention takes CUDA tensors")
         if lm.q_limit is not None:
             raise NotImplementedError("gradients under a query-length mask are not implemented")
-        out, lse = _AttentionFunction.apply(q, k, v, lm.band, lm.kv_lengths, bt, float(sm_scale), implementation)
+        out, lse = _AttentionFunction.apply(q, k, v, lm.band, lm.kv_lengths, bt, float(sm_scale), implementation, mods)
         res = (out, lse) if return_lse else out
-    elif use_splitkv(q, k, causal=lm.banded, bias=bt, q_limit=lm.q_limit, dropout_rate=dropout_rate, split_kv=split_kv):
+    elif mods is None and use_splitkv(q, k, causal=lm.banded, bias=bt, q_limit=lm.q_limit, dropout_rate=dropout_rate,
+                                      split_kv=split_kv):
         res = decode_forward(q, k, v, kv_lengths=lm.kv_lengths, sm_scale=sm_scale, return_lse=return_lse)
     else:
         res = attention_forward(q, k, v, band=lm.band, kv_lengths=lm.kv_lengths, bias=bt, sm_scale=sm_scale,
-                                return_lse=return_lse, impl=implementation)
+                                return_lse=return_lse, impl=implementation, mods=mods)
     out, lse = res if return_lse else (res, None)
     out, lse = _apply_q_limit(out, lse, lm.q_limit)
     return (out, lse) if return_lse else out
@@ -523,21 +623,65 @@ def flex_attention(query, key, value, mask: AttentionMask | None = None, bias: A
     return out
 
 
+def _dense_arrays_as_bias(mask, bias, batch_shape, heads, q_len, kv_len):
+    """Dense ``mask`` (boolean, True = keep) / ``bias`` arrays broadcastable to
+    ``[*batch, H, Q, K]`` (the Flax convention, layers/attention.py:1293-1319) as one
+    ``DenseBias`` ``[B|1, H|1, Q, K]`` with ``-inf`` where masked."""
+    from .masks import DenseBias
+
+    nb = len(batch_shape)
+    total = None
+    for arr, is_mask in ((mask, True), (bias, False)):
+        if arr is None:
+            continue
+        t = _as_tensor(arr)
+        if t.dim() > nb + 3:
+            raise ValueError(f"mask / bias rank {t.dim()} exceeds [*batch, H, Q, K] (rank {nb + 3})")
+        t = t.reshape((1,) * (nb + 3 - t.dim()) + tuple(t.shape))
+        lead = tuple(t.shape[:nb])
+        if any(d != 1 for d in lead):
+            t = t.expand(tuple(batch_shape) + tuple(t.shape[nb:]))
+        t = t.reshape((-1,) + tuple(t.shape[nb:]))  # [B|1, H|1, Q|1, K|1]
+        if t.shape[1] not in (1, heads):
+            raise ValueError(f"cannot broadcast mask / bias head dim {t.shape[1]} to {heads}")
+        t = t.expand(t.shape[0], t.shape[1], q_len, kv_len)
+        if is_mask:
+            t = torch.zeros(t.shape, dtype=torch.float32, device=t.device).masked_fill_(~t.bool(), float("-inf"))
+        else:
+            t = t.float()
+        total = t if total is None else total + t.to(total.device)
+    return None if total is None else DenseBias(total.contiguous())
+
+
 def dot_product_attention(query, key, value, mask=None, bias=None, dropout_rng=None, dropout_rate: float = 0.0,
                           broadcast_dropout: bool = False, deterministic=True, dtype=None, precision=None,
                           module=None, sm_scale: Optional[float] = None, enable_gqa: bool = False,
                           implementation: str | None = None):
     """``dot_product_attention`` (layers/attention.py:1205-1221): the default
     ``attention_fn`` of ``MultiHeadAttention``.  Like Flax, K/V may carry fewer
-    heads than Q.  Mask / bias must be the mask / bias objects of
-    :mod:`probjax_b200.masks` (dense arrays belong to the Flax einsum path of the
-    reference, which has no counterpart here)."""
+    heads than Q.  ``mask`` / ``bias`` are mask / bias objects of
+    :mod:`probjax_b200.masks` or, as on the reference's Flax path (1293-1319), dense arrays
+    broadcastable to ``[*batch, H, Q, K]`` (boolean keep-mask, additive bias); arrays become one
+    dense additive tensor for the kernels.  Rows whose keys are all masked come out as zeros
+    (the kernel convention), where the Flax einsum would average the values."""
     if module is not None or precision is not None:
         raise NotImplementedError("sowing (module=) and explicit precision belong to the Flax einsum path")
-    if mask is not None and not isinstance(mask, AttentionMask):
-        raise NotImplementedError("dense mask arrays are not supported; pass an AttentionMask object")
-    if bias is not None and not isinstance(bias, AttentionBias):
-        raise NotImplementedError("dense bias arrays are not supported; wrap them in DenseBias")
+    arrays = (mask is not None and not isinstance(mask, AttentionMask)) or \
+             (bias is not None and not isinstance(bias, AttentionBias))
+    if arrays:
+        query, key = _as_tensor(query), _as_tensor(key)
+        if query.dim() < 3:
+            raise ValueError("dense mask / bias arrays need query of rank >= 3 [..., T, H, D]")
+        arr_mask = None if isinstance(mask, AttentionMask) else mask
+        arr_bias = None if isinstance(bias, AttentionBias) else bias
+        dense = _dense_arrays_as_bias(arr_mask, arr_bias, tuple(query.shape[:-3]), query.shape[-2], query.shape[-3],
+                                      key.shape[-3])
+        if isinstance(bias, AttentionBias):
+            from .masks import SumBias
+
+            dense = SumBias(bias, dense)
+        mask = mask if isinstance(mask, AttentionMask) else None
+        bias = dense
     return flex_attention(query, key, value, mask=mask, bias=bias, dropout_rng=dropout_rng,
                           dropout_rate=dropout_rate, deterministic=deterministic, dtype=dtype,
                           sm_scale=sm_scale, enable_gqa=True, implementation=implementation)
@@ -639,10 +783,15 @@ def mla(q, cache, wk=None, wv=None, *, mask=None, bias=None, rng=None, sm_scale:
     dev = q.device
     B, Lq, S = q.shape[0], q.shape[1], cache.shape[1]
     Dv = R if wv is None else wv.shape[1]
-    lm = lower_mask(mask, B, Lq, S)
-    if lm.banded and not lm.causal:
-        raise NotImplementedError("mla takes no mask band other than the causal one")
-    bt = lower_bias(bias, B, H, Lq, S)
+    # the same masks and biases as mha (latent_attention.py:636-766 shares its mask / bias machinery)
+    lm, residual = split_mask(mask, B, Lq, S)
+    lb = lower_bias_structured(bias, B, H, Lq, S)
+    if lb.low_rank:
+        raise NotImplementedError("mla does not fold LowRankBias terms (the latent has no per-head key columns)")
+    bt = lb.dense
+    if residual is not None:
+        bt = lower_dense(residual, None if bt is None else masks_DenseBias(bt), B, H, Lq, S)
+    mods = ScoreMods(lm, lb, dev) if (lm.structured or lb.structured) else None
     q, cache = q.contiguous(), cache.contiguous()
     wk = None if wk is None else wk.to(dev).contiguous()
     wv = None if wv is None else wv.to(dev).contiguous()
@@ -659,7 +808,8 @@ def mla(q, cache, wk=None, wv=None, *, mask=None, bias=None, rng=None, sm_scale:
             vmat = torch.matmul(cache, wv.reshape(H * Dv, R).t()).view(B, S, H, Dv)
         else:
             kmat = vmat = cache[:, :, None, :]  # one shared KV head
-        out, lse = _AttentionFunction.apply(q, kmat, vmat, lm.band, lm.kv_lengths, bt, float(sm_scale), implementation)
+        out, lse = _AttentionFunction.apply(q, kmat, vmat, lm.band, lm.kv_lengths, bt, float(sm_scale), implementation,
+                                            mods)
         return (out, lse) if return_lse else out
     o = torch.empty((B, Lq, H, Dv), dtype=q.dtype, device=dev)
     lse = torch.empty((B, H, Lq), dtype=torch.float32, device=dev) if return_lse else None
@@ -672,10 +822,12 @@ def mla(q, cache, wk=None, wv=None, *, mask=None, bias=None, rng=None, sm_scale:
     L = _lib.lib()
     need = L.pjx_mla_workspace_bytes(B, S, H, Dqk, Dv, R, _DTYPES[q.dtype], int(wk is not None))
     ws = _scratch_bytes(dev, "mla", need)
+    band_lo, band_hi = _band_args(False, lm.band)
     with torch.cuda.device(dev):
-        rc = L.pjx_mla_fwd(_ptr(q), _ptr(cache), _ptr(wk), _ptr(wv), _ptr(o), _ptr(lse), _ptr(kvl), _ptr(bt), bs, hs,
-                           B, Lq, S, H, Dqk, Dv, R, _DTYPES[q.dtype], int(lm.causal), float(sm_scale),
-                           _IMPL[implementation], _ptr(ws), ws.numel(), _ptr(_status_word(dev)), _stream(dev))
+        rc = L.pjx_mla_fwd_mod(_ptr(q), _ptr(cache), _ptr(wk), _ptr(wv), _ptr(o), _ptr(lse), _ptr(kvl), _ptr(bt), bs, hs,
+                               B, Lq, S, H, Dqk, Dv, R, _DTYPES[q.dtype], band_lo, band_hi, float(sm_scale),
+                               ScoreMods.arg(mods), _IMPL[implementation], _ptr(ws), ws.numel(),
+                               _ptr(_status_word(dev)), _stream(dev))
     _lib.check(rc)
     o, lse = _apply_q_limit(o, lse, lm.q_limit)
     return (o, lse) if return_lse else o

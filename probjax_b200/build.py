@@ -81,6 +81,40 @@ def build(force: bool = False, verbose: bool = False) -> Path:
     return LIB
 
 
+FFI_LIB = PKG / "libpjx_ffi.so"
+
+
+def jax_include_dir():
+    """jaxlib's XLA FFI header directory, or None when jax is not installed."""
+    try:
+        import jax.ffi
+
+        inc = jax.ffi.include_dir()
+    except Exception:
+        return None
+    return inc if os.path.exists(os.path.join(inc, "xla", "ffi", "api", "ffi.h")) else None
+
+
+def build_ffi(include_dir: str | None = None) -> Path | None:
+    """Compiles ``csrc/ffi_shim.cc`` (the XLA FFI handlers over the C ABI) into ``libpjx_ffi.so``.
+    Needs jaxlib's headers: returns None, building nothing, where they are absent."""
+    include_dir = include_dir or jax_include_dir()
+    if include_dir is None:
+        return None
+    build()
+    cxx = shutil.which("g++") or "g++"
+    cuda_inc = os.path.join(os.path.dirname(os.path.dirname(_nvcc())), "include")
+    cmd = [cxx, "-std=c++17", "-O2", "-shared", "-fPIC", "-I", include_dir, "-I", str(INCLUDE), "-I", cuda_inc,
+           str(CSRC / "ffi_shim.cc"), "-L", str(PKG), "-lpjx_attention", "-L", os.path.join(os.path.dirname(cuda_inc), "lib64"),
+           "-lcudart", "-Wl,-rpath,$ORIGIN", "-o", str(FFI_LIB)]
+    res = subprocess.run(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
+    if res.returncode != 0:
+        raise RuntimeError(f"ffi shim build failed:\n{res.stdout}")
+    return FFI_LIB
+
+
 if __name__ == "__main__":
     path = build(force="--force" in sys.argv, verbose="-v" in sys.argv)
     print(path)
+    if "--ffi" in sys.argv:
+        print(build_ffi() or "jaxlib headers not found: the FFI shim was not built")

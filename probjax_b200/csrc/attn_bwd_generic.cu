@@ -113,6 +113,9 @@ __device__ __forceinline__ void tile_p_ds(const BwdParams& p, const Tiles& t, in
     dp[1][1] = fmaf(a1, v1, dp[1][1]);
   }
   const float* bias = p.bias ? p.bias + (int64_t)b * p.bias_bs + (int64_t)h * p.bias_hs : nullptr;
+  const bool has_mod = p.mod.on != 0;
+  ScoreModView mv = {};
+  if (has_mod) mv = view_of(p.mod, b, h, p.Lq);
 #pragma unroll
   for (int i = 0; i < 2; ++i) {
     const int r = ty * 2 + i, qi = q0 + r;
@@ -121,11 +124,17 @@ __device__ __forceinline__ void tile_p_ds(const BwdParams& p, const Tiles& t, in
     for (int c = 0; c < 2; ++c) {
       const int col = tx + 16 * c, kj = k0 + col;
       float x = s[i][c] * p.sm_scale;
+      float dsds = 1.f;  // d(modified score) / d(scaled score)
+      bool keep = kj <= qi + p.band_hi && kj >= qi + p.band_lo;
+      if (has_mod && qi < p.Lq && kj < kv_len) {
+        x = mod_score<true>(mv, x, qi, kj, &dsds);
+        keep = mod_keep(mv, keep, qi, kj);
+      }
       if (bias && qi < p.Lq && kj < p.Lkv) x += bias[(int64_t)qi * p.Lkv + kj];
-      const bool keep = qi < p.Lq && kj < kv_len && kj <= qi + p.band_hi && kj >= qi + p.band_lo && lse != INFINITY;
+      keep = keep && qi < p.Lq && kj < kv_len && lse != INFINITY;
       const float pr = keep ? exp2f((x - lse) * kLog2e) : 0.f;
       t.Ps[r * (T + 1) + col] = pr;
-      t.dSs[r * (T + 1) + col] = pr * (dp[i][c] - delta);
+      t.dSs[r * (T + 1) + col] = pr * (dp[i][c] - delta) * dsds;
     }
   }
 }
@@ -139,8 +148,9 @@ __global__ void __launch_bounds__(NT) bwd_dq_kernel(const BwdParams p) {
   const int hk = h / (p.Hq / p.Hkv);
   int kv_len = p.Lkv;
   if (p.kv_lengths) kv_len = max(0, min(kv_len, p.kv_lengths[b]));
-  const int kv_end = max(0, min(kv_len, min(q0 + T, p.Lq) + p.band_hi));  // keys past the band of the tile's last row
-  const int kv_begin = (max(0, q0 + p.band_lo) / T) * T;                  // keys before the band of its first row
+  int kv_end = max(0, min(kv_len, min(q0 + T, p.Lq) + p.band_hi));  // keys past the band of the tile's last row
+  const int kv_begin = (max(0, q0 + p.band_lo) / T) * T;             // keys before the band of its first row
+  if (p.mod.prefix_len) kv_end = max(kv_end, min(kv_len, p.mod.prefix_len[b]));  // prefix keys: visible to every row
   const int64_t qstride = (int64_t)p.Hq * p.D, ostride = (int64_t)p.Hq * p.Dv;
   const int64_t kstride = (int64_t)p.Hkv * p.D, vstride = (int64_t)p.Hkv * p.Dv;
   const T_* q = static_cast<const T_*>(p.q) + ((int64_t)b * p.Lq * p.Hq + h) * p.D;
@@ -231,8 +241,9 @@ __global__ void __launch_bounds__(NT) bwd_dkdv_kernel(const BwdParams p) {
     load_rows<T_>(t.Ks, t.Dp, k, kstride, k0, kv_len, p.D);
     load_rows<T_>(t.Vs, t.Dvp, v, vstride, k0, kv_len, p.Dv);
     // queries outside [first key - band_hi, last key - band_lo] never see a key of this tile
-    const int q_first = (max(0, k0 - p.band_hi) / T) * T;
+    int q_first = (max(0, k0 - p.band_hi) / T) * T;
     const int q_end = min(p.Lq, k0 + T - p.band_lo);
+    if (p.mod.prefix_len && k0 < p.mod.prefix_len[b]) q_first = 0;  // a prefix key is seen by every row
     for (int g = 0; g < G; ++g) {
       const int h = hk * G + g;
       const T_* q = static_cast<const T_*>(p.q) + ((int64_t)b * p.Lq * p.Hq + h) * p.D;
@@ -354,6 +365,7 @@ struct JvpParams {
   int B, Lq, Lkv, Hq, Hkv, D, Dv;
   int band_lo, band_hi;
   float sm_scale;
+  ScoreMod mod;
 };
 
 inline size_t jvp_smem_bytes(int D, int Dv) {
@@ -388,8 +400,14 @@ __global__ void __launch_bounds__(NT) jvp_kernel(const JvpParams p) {
   const int hk = h / (p.Hq / p.Hkv);
   int kv_len = p.Lkv;
   if (p.kv_lengths) kv_len = max(0, min(kv_len, p.kv_lengths[b]));
-  const int kv_end = max(0, min(kv_len, min(q0 + T, p.Lq) + p.band_hi));
+  int kv_end = max(0, min(kv_len, min(q0 + T, p.Lq) + p.band_hi));
   const int kv_begin = (max(0, q0 + p.band_lo) / T) * T;
+  const bool has_mod = p.mod.on != 0;
+  ScoreModView mv = {};
+  if (has_mod) {
+    mv = view_of(p.mod, b, h, p.Lq);
+    kv_end = max(kv_end, min(kv_len, mv.prefix));
+  }
   const int64_t qstride = (int64_t)p.Hq * p.D, ostride = (int64_t)p.Hq * p.Dv;
   const int64_t kstride = (int64_t)p.Hkv * p.D, vstride = (int64_t)p.Hkv * p.Dv;
   const int64_t qoff = ((int64_t)b * p.Lq * p.Hq + h) * p.D;
@@ -444,10 +462,16 @@ __global__ void __launch_bounds__(NT) jvp_kernel(const JvpParams p) {
       for (int c = 0; c < 2; ++c) {
         const int col = tx + 16 * c, kj = k0 + col;
         float x = s[i][c] * p.sm_scale;
+        float dsds = 1.f;
+        bool keep = kj <= qi + p.band_hi && kj >= qi + p.band_lo;
+        if (has_mod && qi < p.Lq && kj < kv_len) {
+          x = mod_score<true>(mv, x, qi, kj, &dsds);
+          keep = mod_keep(mv, keep, qi, kj);
+        }
         if (bias && qi < p.Lq && kj < p.Lkv) x += bias[(int64_t)qi * p.Lkv + kj];
-        const bool keep = qi < p.Lq && kj < kv_len && kj <= qi + p.band_hi && kj >= qi + p.band_lo && lse != INFINITY;
+        keep = keep && qi < p.Lq && kj < kv_len && lse != INFINITY;
         const float pr = keep ? exp2f((x - lse) * kLog2e) : 0.f;
-        const float pd = keep ? pr * ds[i][c] * p.sm_scale : 0.f;
+        const float pd = keep ? pr * ds[i][c] * p.sm_scale * dsds : 0.f;
         part += pd;
         Ps[r * (T + 1) + col] = Elem<T_>::round(pr);
         PDs[r * (T + 1) + col] = Elem<T_>::round(pd);
@@ -521,6 +545,24 @@ int pjx_attn_bwd_band(const void* q, const void* k, const void* v, const void* o
                       int64_t bias_batch_stride, int64_t bias_head_stride, float* dbias, int B, int Lq, int Lkv, int Hq,
                       int Hkv, int D, int Dv, int dtype, int band_lo, int band_hi, float sm_scale, int impl,
                       void* workspace, size_t workspace_bytes, int32_t* status, void* stream) {
+  return pjx_attn_bwd_mod(q, k, v, o, lse, d_o, dq, dk, dv, kv_lengths, bias, bias_batch_stride, bias_head_stride, dbias,
+                          B, Lq, Lkv, Hq, Hkv, D, Dv, dtype, band_lo, band_hi, sm_scale, nullptr, impl, workspace,
+                          workspace_bytes, status, stream);
+}
+
+int pjx_attn_bwd_mod(const void* q, const void* k, const void* v, const void* o, const float* lse, const void* d_o,
+                     void* dq, void* dk, void* dv, const int32_t* kv_lengths, const float* bias,
+                     int64_t bias_batch_stride, int64_t bias_head_stride, float* dbias, int B, int Lq, int Lkv, int Hq,
+                     int Hkv, int D, int Dv, int dtype, int band_lo, int band_hi, float sm_scale,
+                     const pjx_score_mod* mod, int impl, void* workspace, size_t workspace_bytes, int32_t* status,
+                     void* stream) {
+  ScoreMod smod;
+  {
+    int rcm = convert_score_mod(mod, &smod);
+    if (rcm) return rcm;
+  }
+  if (dbias && smod.nonlinear())
+    return fail(PJX_ERR_UNSUPPORTED, "backward: the bias gradient is not computed together with head_scale / softcap");
   if (impl != PJX_IMPL_AUTO && impl != PJX_IMPL_GENERIC && impl != PJX_IMPL_SM100)
     return fail(PJX_ERR_BAD_ARG, "impl must be 0 (auto), 1 (generic) or 2 (tcgen05), got %d", impl);
   if (dtype != PJX_F32 && dtype != PJX_BF16 && dtype != PJX_F16)
@@ -551,6 +593,7 @@ int pjx_attn_bwd_band(const void* q, const void* k, const void* v, const void* o
   p.sm_scale = sm_scale;
   p.dtype = dtype;
   p.status = status;
+  p.mod = smod;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   if (dbias) {
     if (!bias) return fail(PJX_ERR_BAD_ARG, "backward: dbias given without a bias");
@@ -568,7 +611,11 @@ int pjx_attn_bwd_band(const void* q, const void* k, const void* v, const void* o
     return check_cuda(cudaMemsetAsync(dv, 0, (size_t)B * Lkv * Hkv * Dv * dtype_size(dtype), st), "clear dv");
   }
   const char* why = nullptr;
-  const bool tc_ok = bwd_sm100_supported(p, &why);
+  bool tc_ok = bwd_sm100_supported(p, &why);
+  if (tc_ok && smod.on) {
+    tc_ok = false;
+    why = "score modifiers are evaluated by the CUDA-core backward only";
+  }
   if (impl == PJX_IMPL_SM100 && !tc_ok) return fail(PJX_ERR_UNSUPPORTED, "tcgen05 backward: %s", why);
   p.use_sm100 = impl != PJX_IMPL_GENERIC && tc_ok;
   switch (dtype) {
@@ -591,6 +638,20 @@ int pjx_attn_jvp_band(const void* q, const void* k, const void* v, const void* t
                       const float* lse, void* t_o, const int32_t* kv_lengths, const float* bias,
                       int64_t bias_batch_stride, int64_t bias_head_stride, int B, int Lq, int Lkv, int Hq, int Hkv,
                       int D, int Dv, int dtype, int band_lo, int band_hi, float sm_scale, void* stream) {
+  return pjx_attn_jvp_mod(q, k, v, tq, tk, tv, lse, t_o, kv_lengths, bias, bias_batch_stride, bias_head_stride, B, Lq, Lkv,
+                          Hq, Hkv, D, Dv, dtype, band_lo, band_hi, sm_scale, nullptr, stream);
+}
+
+int pjx_attn_jvp_mod(const void* q, const void* k, const void* v, const void* tq, const void* tk, const void* tv,
+                     const float* lse, void* t_o, const int32_t* kv_lengths, const float* bias,
+                     int64_t bias_batch_stride, int64_t bias_head_stride, int B, int Lq, int Lkv, int Hq, int Hkv,
+                     int D, int Dv, int dtype, int band_lo, int band_hi, float sm_scale, const pjx_score_mod* mod,
+                     void* stream) {
+  ScoreMod smod;
+  {
+    int rcm = convert_score_mod(mod, &smod);
+    if (rcm) return rcm;
+  }
   if (dtype != PJX_F32 && dtype != PJX_BF16 && dtype != PJX_F16)
     return fail(PJX_ERR_BAD_ARG, "dtype must be float32, bfloat16 or float16 (got code %d)", dtype);
   if (B < 0 || Lq < 0 || Lkv < 0 || Hq < 1 || Hkv < 1 || D < 1 || Dv < 1)
@@ -608,6 +669,7 @@ int pjx_attn_jvp_band(const void* q, const void* k, const void* v, const void* t
   p.band_lo = band_lo < PJX_BAND_NO_LOWER ? PJX_BAND_NO_LOWER : (band_lo > PJX_BAND_NO_UPPER ? PJX_BAND_NO_UPPER : band_lo);
   p.band_hi = band_hi > PJX_BAND_NO_UPPER ? PJX_BAND_NO_UPPER : (band_hi < PJX_BAND_NO_LOWER ? PJX_BAND_NO_LOWER : band_hi);
   p.sm_scale = sm_scale;
+  p.mod = smod;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   switch (dtype) {
     case PJX_F32: return launch_jvp<float>(p, st);

@@ -89,6 +89,15 @@ __device__ __forceinline__ void st_release_sys_u32(uint32_t* p, uint32_t v) {
   asm volatile("st.release.sys.global.u32 [%0], %1;\n" ::"l"(p), "r"(v) : "memory");
 }
 
+__device__ __forceinline__ void st_volatile_v4(uint4* p, uint4 v) {
+  asm volatile("st.volatile.global.v4.u32 [%0], {%1, %2, %3, %4};\n" ::"l"(p), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+}
+__device__ __forceinline__ uint4 ld_volatile_v4(const uint4* p) {
+  uint4 v;
+  asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];\n" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
+  return v;
+}
+
 // FUSED (sequence-sharded decode, whole grid co-resident): the last CTA of each (batch, kv
 // head) to finish combines the head's splits, stores the rank's partial into every rank's
 // exchange buffer, raises the head's flag there, waits (bounded) for the same head's flags of
@@ -323,16 +332,17 @@ __global__ void __launch_bounds__(NTHR, 2) decode_splitkv_kernel(const DecodePar
   }
 
   if constexpr (FUSED) {
+    // Exchange in "data + flag" words (the low-latency protocol collectives libraries use for small
+    // messages): every value crosses NVLink inside a 16-byte store {v0, step, v1, step}, so a value is
+    // valid exactly when the step number beside it is this step's -- no fence, no separate flag, one
+    // one-way trip.  Only stores go to peers; all polling is on this GPU's own memory.
     const int64_t N = (int64_t)p.B * p.Lq * p.Hq;
-    const size_t half = exchange_record_floats(p.ex_world, N, HD);
-    const size_t uf_off = exchange_unit_flags_offset(p.ex_world, N, HD);
     const int unit = b * p.Hkv + hk;
     unsigned char* mine = p.ex_buf[p.ex_rank];
-    uint32_t* counters = reinterpret_cast<uint32_t*>(mine + uf_off) + (size_t)p.ex_world * N;
+    uint32_t* counters = reinterpret_cast<uint32_t*>(mine + exchange_unit_flags_offset(p.ex_world, N, HD)) + (size_t)p.ex_world * N;
+    const size_t ll_off = exchange_ll_offset(p.ex_world, N, HD);
     const int ns = max(1, (len + p.split_len - 1) / p.split_len);  // CTAs of this head that run
     __shared__ int s_last;
-    __shared__ float s_w[16][kMaxExchangeRanks];  // per packed row: weight of every rank's partial
-    __shared__ float s_inv[16], s_lse[16];
     __threadfence();  // this CTA's partial is visible device-wide before it is counted
     __syncthreads();
     if (tid == 0) {
@@ -344,104 +354,98 @@ __global__ void __launch_bounds__(NTHR, 2) decode_splitkv_kernel(const DecodePar
     if (!s_last) return;
     __threadfence();
 
-    // ---- this rank's partial of the head: exact combine of its splits ----
     const int64_t pbase = ((int64_t)b * p.Hkv + hk) * p.num_splits;
-    const size_t par = (p.ex_step & 1) * half;
-    if (tid < p.rows) {
-      float m = -INFINITY;
-      for (int s = 0; s < ns; ++s) m = fmaxf(m, __ldcg(p.lse_part + (pbase + s) * p.rows + tid));
-      const float msafe = (m == -INFINITY) ? 0.f : m;
-      float denom = 0.f;
-      for (int s = 0; s < ns; ++s) denom += exp2f(__ldcg(p.lse_part + (pbase + s) * p.rows + tid) - msafe);
-      s_inv[tid] = denom > 0.f ? 1.f / denom : 0.f;
-      s_lse[tid] = msafe;  // base 2
-      const float lse_nat = denom > 0.f ? (msafe + log2f(denom)) * kLn2 : INFINITY;
-      const int g = tid / p.Lq, t = tid % p.Lq;
-      const int64_t n = ((int64_t)b * p.Lq + t) * p.Hq + hk * G + g;
-      const size_t l_off = par + (size_t)p.ex_world * N * HD + (size_t)p.ex_rank * N + n;
-      for (int q = 0; q < p.ex_world; ++q) reinterpret_cast<float*>(p.ex_buf[q])[l_off] = lse_nat;
-    }
-    __syncthreads();
+    const uint32_t step = p.ex_step;
+    const int par = step & 1;
+    // LL region of one rank: [2 parities][world][N] records of (HD / 2 + 1) 16-byte lines:
+    // HD / 2 lines of two output values each, then one line holding the natural-log LSE.
+    constexpr int LINES = HD / 2 + 1;
+    auto line_of = [&](unsigned char* base, int src_rank, int64_t n, int line) {
+      return reinterpret_cast<uint4*>(base + ll_off) + ((((size_t)par * p.ex_world + src_rank) * N + n) * LINES + line);
+    };
+    T* o = static_cast<T*>(p.o);
+    bool timed_out = false;
     for (int idx = tid; idx < p.rows * (HD / 4); idx += NTHR) {
       const int r = idx / (HD / 4), d4 = idx % (HD / 4);
+      const int g = r / p.Lq, t = r % p.Lq;
+      const int64_t n = ((int64_t)b * p.Lq + t) * p.Hq + hk * G + g;
+      // ---- this rank's partial of the row: exact combine of its splits (base-2 LSEs) ----
+      float m = -INFINITY;
+      for (int s = 0; s < ns; ++s) m = fmaxf(m, __ldcg(p.lse_part + (pbase + s) * p.rows + r));
+      const float msafe = (m == -INFINITY) ? 0.f : m;
+      float denom = 0.f;
       float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
       for (int s = 0; s < ns; ++s) {
-        const float w = exp2f(__ldcg(p.lse_part + (pbase + s) * p.rows + r) - s_lse[r]);
+        const float w = exp2f(__ldcg(p.lse_part + (pbase + s) * p.rows + r) - msafe);
         const float4 x = __ldcg(reinterpret_cast<const float4*>(p.o_part + ((pbase + s) * p.rows + r) * HD) + d4);
+        denom += w;
         acc.x = fmaf(w, x.x, acc.x);
         acc.y = fmaf(w, x.y, acc.y);
         acc.z = fmaf(w, x.z, acc.z);
         acc.w = fmaf(w, x.w, acc.w);
       }
-      const float inv = s_inv[r];
+      const float inv = denom > 0.f ? 1.f / denom : 0.f;
       acc.x *= inv; acc.y *= inv; acc.z *= inv; acc.w *= inv;
-      const int g = r / p.Lq, t = r % p.Lq;
-      const int64_t n = ((int64_t)b * p.Lq + t) * p.Hq + hk * G + g;
-      const size_t o_off = par + ((size_t)p.ex_rank * N + n) * HD;
-      for (int q = 0; q < p.ex_world; ++q) reinterpret_cast<float4*>(reinterpret_cast<float*>(p.ex_buf[q]) + o_off)[d4] = acc;
-    }
-    __syncthreads();  // the CTA's stores are ordered before thread 0's fence (cumulativity)
-    if (tid == 0) {
-      __threadfence_system();
-      for (int q = 0; q < p.ex_world; ++q)
-        st_release_sys_u32(reinterpret_cast<uint32_t*>(p.ex_buf[q] + uf_off) + (size_t)p.ex_rank * N + unit, p.ex_step);
-    }
-
-    // ---- wait for the same head's partials of all ranks (bounded), then combine them ----
-    if (tid < p.ex_world) {
-      const volatile uint32_t* flag = reinterpret_cast<const volatile uint32_t*>(mine + uf_off) + (size_t)tid * N + unit;
+      const float my_lse = denom > 0.f ? (msafe + log2f(denom)) * kLn2 : INFINITY;  // natural log, +inf = no keys
+      // ---- publish to every peer ----
+      const uint4 l0 = make_uint4(__float_as_uint(acc.x), step, __float_as_uint(acc.y), step);
+      const uint4 l1 = make_uint4(__float_as_uint(acc.z), step, __float_as_uint(acc.w), step);
+      const uint4 ll = make_uint4(__float_as_uint(my_lse), step, 0u, step);
+      for (int q = 0; q < p.ex_world; ++q) {
+        if (q == p.ex_rank) continue;
+        st_volatile_v4(line_of(p.ex_buf[q], p.ex_rank, n, 2 * d4), l0);
+        st_volatile_v4(line_of(p.ex_buf[q], p.ex_rank, n, 2 * d4 + 1), l1);
+        if (d4 == 0) st_volatile_v4(line_of(p.ex_buf[q], p.ex_rank, n, HD / 2), ll);
+      }
+      // ---- gather the peers' partials of the same row (bounded wait) and combine ----
+      float lse_q[kMaxExchangeRanks];
+      float mx = (my_lse == INFINITY) ? -INFINITY : my_lse;
       const long long t0 = clock64();
-      while (static_cast<int32_t>(*flag - p.ex_step) < 0) {
-        if (clock64() - t0 > 4000000000LL) {  // about two seconds: a peer never published
-          if (p.status) atomicExch(p.status, (int)PJX_ERR_DEVICE_TIMEOUT);
-          break;
+      for (int q = 0; q < p.ex_world; ++q) {
+        if (q == p.ex_rank) {
+          lse_q[q] = my_lse;
+          continue;
+        }
+        uint4 v = ld_volatile_v4(line_of(mine, q, n, HD / 2));
+        while (!timed_out && (v.y != step || v.w != step)) {
+          if (clock64() - t0 > 4000000000LL) timed_out = true;  // about two seconds: a peer never published
+          v = ld_volatile_v4(line_of(mine, q, n, HD / 2));
+        }
+        lse_q[q] = timed_out ? INFINITY : __uint_as_float(v.x);
+        if (lse_q[q] != INFINITY) mx = fmaxf(mx, lse_q[q]);
+      }
+      const float mxs = (mx == -INFINITY) ? 0.f : mx;
+      float den = 0.f;
+      float4 out4 = make_float4(0.f, 0.f, 0.f, 0.f);
+      for (int q = 0; q < p.ex_world; ++q) {
+        const float w = (lse_q[q] == INFINITY) ? 0.f : expf(lse_q[q] - mxs);
+        den += w;
+        float4 x = acc;
+        if (q != p.ex_rank) {
+          uint4 a = ld_volatile_v4(line_of(mine, q, n, 2 * d4));
+          uint4 c = ld_volatile_v4(line_of(mine, q, n, 2 * d4 + 1));
+          while (!timed_out && (a.y != step || a.w != step || c.y != step || c.w != step)) {
+            if (clock64() - t0 > 4000000000LL) timed_out = true;
+            a = ld_volatile_v4(line_of(mine, q, n, 2 * d4));
+            c = ld_volatile_v4(line_of(mine, q, n, 2 * d4 + 1));
+          }
+          x = make_float4(__uint_as_float(a.x), __uint_as_float(a.z), __uint_as_float(c.x), __uint_as_float(c.z));
+        }
+        if (w != 0.f) {  // a rank without keys contributes nothing (its record may hold anything finite or not)
+          out4.x = fmaf(w, x.x, out4.x);
+          out4.y = fmaf(w, x.y, out4.y);
+          out4.z = fmaf(w, x.z, out4.z);
+          out4.w = fmaf(w, x.w, out4.w);
         }
       }
-      __threadfence_system();  // acquire: the peer's records are visible after its flag
+      const float dinv = den > 0.f ? 1.f / den : 0.f;
+      uint2 packed;
+      packed.x = pack2<T>(out4.x * dinv, out4.y * dinv);
+      packed.y = pack2<T>(out4.z * dinv, out4.w * dinv);
+      *reinterpret_cast<uint2*>(o + n * HD + d4 * 4) = packed;
+      if (p.lse && d4 == 0) p.lse[((int64_t)b * p.Hq + hk * G + g) * p.Lq + t] = den > 0.f ? mxs + logf(den) : INFINITY;
     }
-    __syncthreads();
-    const float* o_parts = reinterpret_cast<const float*>(mine) + par;
-    const float* lse_parts = o_parts + (size_t)p.ex_world * N * HD;
-    if (tid < p.rows) {
-      const int g = tid / p.Lq, t = tid % p.Lq;
-      const int64_t n = ((int64_t)b * p.Lq + t) * p.Hq + hk * G + g;
-      float m = -INFINITY;
-      for (int q = 0; q < p.ex_world; ++q) {
-        const float x = __ldcg(lse_parts + (size_t)q * N + n);
-        if (x != INFINITY) m = fmaxf(m, x);  // +inf marks a rank without keys
-      }
-      const float msafe = (m == -INFINITY) ? 0.f : m;
-      float denom = 0.f;
-      for (int q = 0; q < p.ex_world; ++q) {
-        const float x = __ldcg(lse_parts + (size_t)q * N + n);
-        const float w = (x == INFINITY) ? 0.f : expf(x - msafe);
-        s_w[tid][q] = w;
-        denom += w;
-      }
-      s_inv[tid] = denom > 0.f ? 1.f / denom : 0.f;
-      if (p.lse) p.lse[((int64_t)b * p.Hq + hk * G + g) * p.Lq + t] = denom > 0.f ? msafe + logf(denom) : INFINITY;
-    }
-    __syncthreads();
-    T* o = static_cast<T*>(p.o);
-    for (int idx = tid; idx < p.rows * (HD / 4); idx += NTHR) {
-      const int r = idx / (HD / 4), d4 = idx % (HD / 4);
-      const int g = r / p.Lq, t = r % p.Lq;
-      const int64_t n = ((int64_t)b * p.Lq + t) * p.Hq + hk * G + g;
-      float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-      for (int q = 0; q < p.ex_world; ++q) {
-        const float w = s_w[r][q];
-        const float4 x = __ldcg(reinterpret_cast<const float4*>(o_parts + ((size_t)q * N + n) * HD) + d4);
-        acc.x = fmaf(w, x.x, acc.x);
-        acc.y = fmaf(w, x.y, acc.y);
-        acc.z = fmaf(w, x.z, acc.z);
-        acc.w = fmaf(w, x.w, acc.w);
-      }
-      const float inv = s_inv[r];
-      uint2 out;
-      out.x = pack2<T>(acc.x * inv, acc.y * inv);
-      out.y = pack2<T>(acc.z * inv, acc.w * inv);
-      *reinterpret_cast<uint2*>(o + n * HD + d4 * 4) = out;
-    }
+    if (timed_out && p.status) atomicExch(p.status, (int)PJX_ERR_DEVICE_TIMEOUT);
   }
 }
 

@@ -44,8 +44,14 @@ __global__ void __launch_bounds__(NT) attn_fwd_generic_kernel(const FwdParams p)
   int kv_len = p.Lkv;
   if (p.kv_lengths) kv_len = max(0, min(kv_len, p.kv_lengths[b]));
   // keys outside [first query + band_lo, last query + band_hi] of the tile are masked for all its rows
-  const int kv_end = max(0, min(kv_len, min(q0 + BM, p.Lq) + p.band_hi));
+  int kv_end = max(0, min(kv_len, min(q0 + BM, p.Lq) + p.band_hi));
   const int kv_begin = (max(0, q0 + p.band_lo) / BN) * BN;
+  const bool has_mod = p.mod.on != 0;
+  ScoreModView mv = {};
+  if (has_mod) {
+    mv = view_of(p.mod, b, h, p.Lq);
+    kv_end = max(kv_end, min(kv_len, mv.prefix));  // prefix keys are visible to every row
+  }
 
   for (int idx = tid; idx < BM * D; idx += NT) {
     int r = idx / D, d = idx - r * D;
@@ -111,8 +117,13 @@ __global__ void __launch_bounds__(NT) attn_fwd_generic_kernel(const FwdParams p)
       for (int c = 0; c < 4; ++c) {
         const int kj = k0 + tx + 16 * c;
         float x = s[i][c] * c1;
+        bool keep = kj <= qi + p.band_hi && kj >= qi + p.band_lo;
+        if (has_mod && qi < p.Lq && kj < kv_len) {
+          x = mod_score<true>(mv, s[i][c] * p.sm_scale, qi, kj, nullptr) * kLog2e;
+          keep = mod_keep(mv, keep, qi, kj);
+        }
         if (bias && qi < p.Lq && kj < p.Lkv) x = fmaf(bias[(int64_t)qi * p.Lkv + kj], kLog2e, x);
-        const bool keep = (kj < kv_len) && kj <= qi + p.band_hi && kj >= qi + p.band_lo;
+        keep = keep && (kj < kv_len);
         x = keep ? x : -INFINITY;
         s[i][c] = x;
         tmax = fmaxf(tmax, x);

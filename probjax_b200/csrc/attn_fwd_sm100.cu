@@ -135,12 +135,17 @@ __device__ __forceinline__ void exp_pack_store(const float (&s)[BN], float2 cs2,
 // row + band_hi) instead of the causal flag.  The KV loop then starts at the first tile that
 // any row of the CTA can see; a query tile whose band begins later meets leading tiles it
 // masks completely, which leaves its running state untouched.
-template <int DQK, int DV, int BN, int KST, int VST, bool BF16, int BIAS, bool BAND>
+//
+// MOD (implies BAND): structured masks and score modifiers (score_mod.cuh) are evaluated by the
+// softmax threads on every tile: the scaled score of (row, key) is passed through the modifiers
+// and the mask part decides per element; no tile beyond the band / prefix range is visited.
+template <int DQK, int DV, int BN, int KST, int VST, bool BF16, int BIAS, bool BAND, bool MOD = false>
 __global__ void __launch_bounds__(NTHREADS, 1)
 attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                       const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_b,
                       const __grid_constant__ CUtensorMap tm_o, const FwdParams p, const int order_w) {
   constexpr bool HAS_BIAS = BIAS != 0;
+  static_assert(!MOD || (BAND && BIAS != 2), "the modifier variant builds on the band variant without staged bias");
   using C = Cfg<DQK, DV, BN, KST, VST, BIAS == 2>;
   extern __shared__ unsigned char smem_unaligned[];
   unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_unaligned) + 1023) & ~uintptr_t(1023));
@@ -192,8 +197,17 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
       const int qs = q0 + t * BM;
       lo_t[t] = hi_t[t] = 0;
       if (qs < p.Lq) {
-        const int end = max(0, min(kv_len, min(qs + BM, p.Lq) + p.band_hi));
-        const int begin = max(0, qs + p.band_lo);
+        int end = max(0, min(kv_len, min(qs + BM, p.Lq) + p.band_hi));
+        int begin = max(0, qs + p.band_lo);
+        if constexpr (MOD) {
+          if (p.mod.prefix_len) {  // prefix keys are visible to every row
+            const int pre = min(kv_len, p.mod.prefix_len[b]);
+            if (pre > 0) {
+              end = max(end, pre);
+              begin = 0;
+            }
+          }
+        }
         if (begin < end) {
           lo_t[t] = begin / BN;
           hi_t[t] = (end + BN - 1) / BN;
@@ -396,7 +410,14 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
     if (BIAS == 1 && row_ok) bias_row = p.bias + (int64_t)b * p.bias_bs + (int64_t)h * p.bias_hs + (int64_t)row * p.Lkv;
     const bool bias_vec = BIAS == 1 && (p.Lkv % 4 == 0) && ((reinterpret_cast<uintptr_t>(p.bias) & 15) == 0) &&
                           (p.bias_bs % 4 == 0) && (p.bias_hs % 4 == 0);
-    const float cs = HAS_BIAS ? 1.f : c1;
+    const float cs = (HAS_BIAS || MOD) ? 1.f : c1;
+    ScoreModView mv = {};
+    int my_seg = 0, my_limit = 0x7fffffff;
+    if constexpr (MOD) {
+      mv = view_of(p.mod, b, h, p.Lq);
+      if (row_ok && mv.seg_q) my_seg = mv.seg_q[row];
+      if (row_ok && mv.row_limit) my_limit = mv.row_limit[row];
+    }
 
     float m_ref = -INFINITY, l = 0.f;
     bool ok = true;
@@ -410,7 +431,9 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
       constexpr int NCH = BN / 32;
       const int k0 = (j_base + j) * BN;
       bool need_mask;
-      if constexpr (BAND) {
+      if constexpr (MOD) {
+        need_mask = true;
+      } else if constexpr (BAND) {
         need_mask = (k0 + BN > kv_len) || (k0 + BN - 1 > q0 + t * BM + p.band_hi) ||
                     (k0 < q0 + t * BM + BM - 1 + p.band_lo);
       } else {
@@ -424,6 +447,18 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
       tmem_wait_ld();
       PJX_TRACE_AT(t, j, 2);
 
+      if constexpr (MOD) {
+        // scaled score -> modifiers -> exp2 domain; a dense bias (BIAS == 1) is added below on top
+        const bool plain = !HAS_BIAS;
+#pragma unroll
+        for (int i = 0; i < BN; ++i) {
+          const int key = k0 + i;
+          const float sc = s[i] * p.sm_scale;
+          const float md = (row_ok && key < kv_len) ? mod_score<false>(mv, sc, row, key, nullptr) : sc;
+          // the bias branch multiplies by c1 = sm_scale * log2(e) itself: hand it md / sm_scale
+          s[i] = plain ? md * kLog2e : md / p.sm_scale;
+        }
+      }
       if constexpr (BIAS == 2) {
         ok = mbar_wait(BAR(B_FULL + t), j & 1, abort_flag);
         ok = __all_sync(0xffffffffu, ok);
@@ -472,7 +507,11 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
         for (int i = 0; i < BN; ++i) {
           const int key = k0 + i;
           bool keep;
-          if constexpr (BAND) {
+          if constexpr (MOD) {
+            keep = (key <= row + p.band_hi && key >= row + p.band_lo) || key < mv.prefix;
+            keep = keep && key < kv_len && key < my_limit;
+            if (mv.seg_k) keep = keep && (key < kv_len ? __ldg(mv.seg_k + key) == my_seg : false);
+          } else if constexpr (BAND) {
             keep = key < kv_len && key <= row + p.band_hi && key >= row + p.band_lo;
           } else {
             keep = key < kv_len && (!p.causal || key <= row);
@@ -656,7 +695,7 @@ bool bias_can_be_staged(const FwdParams& p) {
          p.bias_bs % 4 == 0;
 }
 
-template <int DQK, int DV, int BN, int KST, int VST, bool BF16, int BIAS, bool BAND = false>
+template <int DQK, int DV, int BN, int KST, int VST, bool BF16, int BIAS, bool BAND = false, bool MOD = false>
 int launch_one(const FwdParams& p, int dtype, cudaStream_t stream) {
   using C = Cfg<DQK, DV, BN, KST, VST, BIAS == 2>;
   CUtensorMap tq, tk, tv, tb;
@@ -671,7 +710,7 @@ int launch_one(const FwdParams& p, int dtype, cudaStream_t stream) {
   }
   CUtensorMap to;
   if ((rc = make_tmap_blhd(&to, p.o, dtype, p.B, p.Lq, p.Hq, DV, BM))) return rc;
-  auto kern = attn_fwd_sm100_kernel<DQK, DV, BN, KST, VST, BF16, BIAS, BAND>;
+  auto kern = attn_fwd_sm100_kernel<DQK, DV, BN, KST, VST, BF16, BIAS, BAND, MOD>;
   if ((rc = check_cuda(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES),
                        "cudaFuncSetAttribute(sm100 fwd)")))
     return rc;
@@ -685,6 +724,10 @@ int launch_one(const FwdParams& p, int dtype, cudaStream_t stream) {
 
 template <int DQK, int DV, int BN, int KST, int VST, bool BF16>
 int launch_cfg(const FwdParams& p, int dtype, cudaStream_t stream) {
+  if (p.mod.on) {
+    if (!p.bias) return launch_one<DQK, DV, BN, KST, VST, BF16, 0, true, true>(p, dtype, stream);
+    return launch_one<DQK, DV, BN, KST, VST, BF16, 1, true, true>(p, dtype, stream);
+  }
   if (p.banded()) {
     if (!p.bias) return launch_one<DQK, DV, BN, KST, VST, BF16, 0, true>(p, dtype, stream);
     return launch_one<DQK, DV, BN, KST, VST, BF16, 1, true>(p, dtype, stream);
@@ -698,7 +741,7 @@ int launch_by_shape(const FwdParams& p, int dtype, cudaStream_t stream) {
   if (p.D == 128 && p.Dv == 128) return launch_cfg<128, 128, 128, 2, 2, BF16>(p, dtype, stream);
   if (p.D == 64 && p.Dv == 64) {
     // with a bias that TMA can address, two K/V stages leave room for the staged bias tiles
-    if (bias_can_be_staged(p) && !p.banded()) return launch_one<64, 64, 128, 2, 2, BF16, 2>(p, dtype, stream);
+    if (bias_can_be_staged(p) && !p.banded() && !p.mod.on) return launch_one<64, 64, 128, 2, 2, BF16, 2>(p, dtype, stream);
     return launch_cfg<64, 64, 128, 3, 3, BF16>(p, dtype, stream);
   }
   if (p.D == 192 && p.Dv == 128) return launch_cfg<192, 128, 128, 2, 1, BF16>(p, dtype, stream);

@@ -44,6 +44,34 @@ int validate_common(const void* q, const void* k, const void* v, const void* o, 
   return PJX_OK;
 }
 
+}  // namespace
+
+// Validates a caller's pjx_score_mod and converts it to the kernels' form (null: no modifiers).
+int convert_score_mod(const pjx_score_mod* m, ScoreMod* out) {
+  *out = ScoreMod();
+  if (!m) return PJX_OK;
+  if ((m->seg_q == nullptr) != (m->seg_k == nullptr))
+    return fail(PJX_ERR_BAD_ARG, "score modifiers: seg_q and seg_k come together (ids of the query rows and of the keys)");
+  if (m->seg_q_batch_stride < 0 || m->seg_k_batch_stride < 0 || m->row_kv_limit_batch_stride < 0 || m->rel_bias_head_stride < 0)
+    return fail(PJX_ERR_BAD_ARG, "score modifiers: strides must be non-negative");
+  if (m->alibi_mode < 0 || m->alibi_mode > 2 || ((m->alibi_mode != 0) != (m->alibi_slopes != nullptr)))
+    return fail(PJX_ERR_BAD_ARG, "score modifiers: alibi_mode is 1 (causal) or 2 (symmetric) with slopes, 0 without");
+  if (!(m->softcap >= 0.f)) return fail(PJX_ERR_BAD_ARG, "score modifiers: softcap must be positive (0 = off)");
+  out->seg_q = m->seg_q; out->seg_k = m->seg_k;
+  out->seg_q_bs = m->seg_q_batch_stride; out->seg_k_bs = m->seg_k_batch_stride;
+  out->row_kv_limit = m->row_kv_limit; out->row_limit_bs = m->row_kv_limit_batch_stride;
+  out->prefix_len = m->prefix_len;
+  out->rel_bias = m->rel_bias; out->rel_hs = m->rel_bias_head_stride;
+  out->alibi_slopes = m->alibi_slopes; out->alibi_mode = m->alibi_mode;
+  out->head_scale = m->head_scale;
+  out->softcap = m->softcap;
+  out->on = (out->seg_q || out->row_kv_limit || out->prefix_len || out->rel_bias || out->alibi_slopes ||
+             out->head_scale || out->softcap > 0.f) ? 1 : 0;
+  return PJX_OK;
+}
+
+namespace {
+
 // Streams and events of the host-buffer call, one set per device, created on first use.
 constexpr int kHostChunks = 8;        // batch chunks of the host-buffer pipeline
 constexpr int kHostQueryChunks = 4;   // query-row chunks inside a batch chunk
@@ -108,8 +136,18 @@ int pjx_attn_fwd_band(const void* q, const void* k, const void* v, void* o, floa
                       const float* bias, int64_t bias_batch_stride, int64_t bias_head_stride, int B, int Lq, int Lkv,
                       int Hq, int Hkv, int D, int Dv, int dtype, int band_lo, int band_hi, float sm_scale, int impl,
                       int32_t* status, void* stream) {
+  return pjx_attn_fwd_mod(q, k, v, o, lse, kv_lengths, bias, bias_batch_stride, bias_head_stride, B, Lq, Lkv, Hq, Hkv, D,
+                          Dv, dtype, band_lo, band_hi, sm_scale, nullptr, impl, status, stream);
+}
+
+int pjx_attn_fwd_mod(const void* q, const void* k, const void* v, void* o, float* lse, const int32_t* kv_lengths,
+                     const float* bias, int64_t bias_batch_stride, int64_t bias_head_stride, int B, int Lq, int Lkv,
+                     int Hq, int Hkv, int D, int Dv, int dtype, int band_lo, int band_hi, float sm_scale,
+                     const pjx_score_mod* mod, int impl, int32_t* status, void* stream) {
   int rc = validate_common(q, k, v, o, B, Lq, Lkv, Hq, Hkv, D, Dv, dtype);
   if (rc) return rc;
+  ScoreMod sm;
+  if ((rc = convert_score_mod(mod, &sm))) return rc;
   if (impl != PJX_IMPL_AUTO && impl != PJX_IMPL_GENERIC && impl != PJX_IMPL_SM100)
     return fail(PJX_ERR_BAD_ARG, "impl must be 0 (auto), 1 (generic) or 2 (tcgen05), got %d", impl);
   if (bias && (bias_batch_stride < 0 || bias_head_stride < 0))
@@ -129,6 +167,7 @@ int pjx_attn_fwd_band(const void* q, const void* k, const void* v, void* o, floa
   p.causal = p.band_hi == 0 && p.band_lo == PJX_BAND_NO_LOWER;
   p.sm_scale = sm_scale;
   p.status = status;
+  p.mod = sm;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   if (impl == PJX_IMPL_SM100) return launch_fwd_sm100(p, dtype, st);
   if (impl == PJX_IMPL_AUTO && fwd_sm100_supported(p, dtype, nullptr)) return launch_fwd_sm100(p, dtype, st);
@@ -351,6 +390,16 @@ int pjx_mla_fwd(const void* q, const void* cache, const void* wk, const void* wv
                 const int32_t* kv_lengths, const float* bias, int64_t bias_batch_stride, int64_t bias_head_stride,
                 int B, int Lq, int S, int H, int Dqk, int Dv, int R, int dtype, int causal, float sm_scale, int impl,
                 void* workspace, size_t workspace_bytes, int32_t* status, void* stream) {
+  return pjx_mla_fwd_mod(q, cache, wk, wv, o, lse, kv_lengths, bias, bias_batch_stride, bias_head_stride, B, Lq, S, H,
+                         Dqk, Dv, R, dtype, PJX_BAND_NO_LOWER, causal ? 0 : PJX_BAND_NO_UPPER, sm_scale, nullptr, impl,
+                         workspace, workspace_bytes, status, stream);
+}
+
+int pjx_mla_fwd_mod(const void* q, const void* cache, const void* wk, const void* wv, void* o, float* lse,
+                    const int32_t* kv_lengths, const float* bias, int64_t bias_batch_stride, int64_t bias_head_stride,
+                    int B, int Lq, int S, int H, int Dqk, int Dv, int R, int dtype, int band_lo, int band_hi,
+                    float sm_scale, const pjx_score_mod* mod, int impl, void* workspace, size_t workspace_bytes,
+                    int32_t* status, void* stream) {
   // probjax/nn/pallas_kernels/kernels/latent_attention.py:668-696
   if ((wk == nullptr) != (wv == nullptr))
     return fail(PJX_ERR_BAD_ARG, "provide both wk and wv (materialized) or neither (absorbed); mixing the two is not supported");
@@ -363,8 +412,8 @@ int pjx_mla_fwd(const void* q, const void* cache, const void* wk, const void* wv
   if (!q || !cache || !o) return fail(PJX_ERR_BAD_ARG, "mla: null buffer");
   if (!wk) {
     // K = V = latent, one shared KV head (latent_attention.py:604-607).
-    return pjx_attn_fwd(q, cache, cache, o, lse, kv_lengths, bias, bias_batch_stride, bias_head_stride, B, Lq, S, H,
-                        1, R, R, dtype, causal, sm_scale, impl, status, stream);
+    return pjx_attn_fwd_mod(q, cache, cache, o, lse, kv_lengths, bias, bias_batch_stride, bias_head_stride, B, Lq, S,
+                            H, 1, R, R, dtype, band_lo, band_hi, sm_scale, mod, impl, status, stream);
   }
   const size_t need = pjx_mla_workspace_bytes(B, S, H, Dqk, Dv, R, dtype, 1);
   if (!workspace || workspace_bytes < need)
@@ -375,8 +424,8 @@ int pjx_mla_fwd(const void* q, const void* cache, const void* wk, const void* wv
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   int rc;
   if ((rc = launch_gemm_tn2(cache, wk, kmat, H * Dqk, wv, vmat, H * Dv, (int64_t)B * S, R, dtype, impl, status, st))) return rc;
-  return pjx_attn_fwd(q, kmat, vmat, o, lse, kv_lengths, bias, bias_batch_stride, bias_head_stride, B, Lq, S, H, H,
-                      Dqk, Dv, dtype, causal, sm_scale, impl, status, stream);
+  return pjx_attn_fwd_mod(q, kmat, vmat, o, lse, kv_lengths, bias, bias_batch_stride, bias_head_stride, B, Lq, S, H, H,
+                          Dqk, Dv, dtype, band_lo, band_hi, sm_scale, mod, impl, status, stream);
 }
 
 size_t pjx_attn_fwd_host_staging_bytes(int bias_batch, int bias_heads, int has_lse, int B, int Lq, int Lkv, int Hq,

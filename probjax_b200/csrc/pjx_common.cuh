@@ -8,6 +8,7 @@
 #include <stdint.h>
 
 #include "../../include/pjx_attention.h"
+#include "score_mod.cuh"
 
 namespace pjx {
 
@@ -63,6 +64,7 @@ struct FwdParams {
   int band_lo = PJX_BAND_NO_LOWER, band_hi = PJX_BAND_NO_UPPER;
   float sm_scale;
   int32_t* status;  // device status word or null
+  ScoreMod mod;     // structured masks / score modifiers (mod.on == 0: none)
 
   bool banded() const { return !causal && (band_lo > PJX_BAND_NO_LOWER || band_hi < PJX_BAND_NO_UPPER); }
 };
@@ -85,8 +87,9 @@ struct DecodeParams {
   // the partials of all ranks. Buffer layout (identical on every rank), N = B*Lq*Hq:
   //   2 x { float o[world][N][Dv]; float lse[world][N]; }   (double buffered by step parity)
   //   uint32 flags[16]; uint32 counter;          (per-rank flags of the three-kernel exchange)
-  //   uint32 unit_flags[world][N];               (per (rank, batch, kv head) flags of the one-kernel exchange)
+  //   uint32 unit_flags[world][N];               (reserved)
   //   uint32 unit_counters[N];                   (split CTAs of a (batch, kv head) that have finished)
+  //   uint4 ll[2][world][N][Dv / 2 + 1];         (one-kernel exchange: values travelling with their step number)
   int ex_world = 0, ex_rank = 0;
   int ex_fused = 0;  // 1: the split kernel's last CTA of each (batch, kv head) exchanges and combines
   uint32_t ex_step = 0;
@@ -124,6 +127,7 @@ struct BwdParams {
   int dtype = PJX_F32;
   int32_t* status = nullptr;  // device status word or null
   bool use_sm100 = false;     // dQ and dK/dV by the tcgen05 kernels instead of the CUDA-core ones
+  ScoreMod mod;               // structured masks / score modifiers (CUDA-core kernels only)
 };
 
 constexpr int kMaxExchangeRanks = 16;
@@ -133,14 +137,21 @@ __host__ __device__ inline size_t exchange_unit_flags_offset(int world, int64_t 
   const size_t head = 2 * exchange_record_floats(world, n_rows, Dv) * sizeof(float) + (kMaxExchangeRanks + 1) * sizeof(uint32_t);
   return (head + 15) / 16 * 16;
 }
+// byte offset of the data+flag region of the one-kernel exchange (16-byte aligned):
+// [2 parities][world][n_rows] records of (Dv / 2 + 1) 16-byte lines {v0, step, v1, step}
+__host__ __device__ inline size_t exchange_ll_offset(int world, int64_t n_rows, int Dv) {
+  const size_t off = exchange_unit_flags_offset(world, n_rows, Dv) + (size_t)(world + 1) * n_rows * sizeof(uint32_t);
+  return (off + 15) / 16 * 16;
+}
 inline size_t exchange_buffer_bytes(int world, int64_t n_rows, int Dv) {
-  return exchange_unit_flags_offset(world, n_rows, Dv) + (size_t)(world + 1) * n_rows * sizeof(uint32_t);
+  return exchange_ll_offset(world, n_rows, Dv) + (size_t)2 * world * n_rows * (Dv / 2 + 1) * 16;
 }
 
 // ---------------------------------------------------------------------------
 // Error plumbing (host)
 // ---------------------------------------------------------------------------
 int fail(int status, const char* fmt, ...);
+int convert_score_mod(const pjx_score_mod* m, ScoreMod* out);
 int check_cuda(cudaError_t e, const char* what);
 void count_launch(int n = 1);
 

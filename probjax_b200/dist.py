@@ -53,23 +53,42 @@ def shard_cache(cache: torch.Tensor, rank: int, world: int, page: int) -> torch.
 
 def exchange_layout(B: int, Lq: int, Hq: int, Dv: int, world: int) -> dict:
     """Offsets inside one rank's exchange buffer of ``pjx_attn_decode_sharded`` (the layout
-    the header documents), ``N = B * Lq * Hq`` records per rank:
+    the header documents), ``N = B * Lq * Hq`` records per rank.
 
-    ``o(parity, rank)`` / ``lse(parity, rank)``: float32 element offsets of rank ``rank``'s
-    ``[N, Dv]`` partial outputs and ``[N]`` natural-log LSEs in the half used by steps of that
-    parity; ``rank_flags`` / ``unit_flags`` / ``unit_counters``: uint32 element offsets of the
-    per-rank flags, the per-(rank, batch, kv head) flags ``[world, N]`` and the split counters."""
+    Three-launch form: ``o(parity, rank)`` / ``lse(parity, rank)`` are float32 element offsets of
+    rank ``rank``'s ``[N, Dv]`` partial outputs and ``[N]`` natural-log LSEs in the half used by
+    steps of that parity; ``rank_flags`` the uint32 element offset of the per-rank flags.
+
+    One-launch form: ``ll(parity, rank)`` is the offset, in 16-byte lines, of rank ``rank``'s ``N``
+    records of ``lines`` lines each: ``Dv / 2`` lines ``{o[2i], step, o[2i+1], step}`` and one line
+    ``{lse, step, 0, step}`` (values as their float32 bit patterns)."""
     N = B * Lq * Hq
     half = world * N * (Dv + 1)
     head_bytes = 2 * half * 4 + (16 + 1) * 4
     uf = (head_bytes + 15) // 16 * 16
+    ll = (uf + (world + 1) * N * 4 + 15) // 16 * 16
+    lines = Dv // 2 + 1
     return {
-        "N": N, "half": half,
+        "N": N, "half": half, "lines": lines,
         "o": lambda parity, rank: parity * half + rank * N * Dv,
         "lse": lambda parity, rank: parity * half + world * N * Dv + rank * N,
-        "rank_flags": 2 * half, "unit_flags": uf // 4, "unit_counters": uf // 4 + world * N,
-        "bytes": uf + (world + 1) * N * 4,
+        "rank_flags": 2 * half, "unit_counters": uf // 4 + world * N,
+        "ll": lambda parity, rank: ll // 16 + (parity * world + rank) * N * lines,
+        "bytes": ll + 2 * world * N * lines * 16,
     }
+
+
+def ll_records(o: torch.Tensor, lse: torch.Tensor, step: int) -> torch.Tensor:
+    """``[N, Dv]`` float32 partial outputs and ``[N]`` LSEs as the int32 ``[N, Dv / 2 + 1, 4]`` lines of
+    the one-launch exchange for step ``step`` (what a rank's kernel stores into its peers)."""
+    N, Dv = o.shape
+    rec = torch.full((N, Dv // 2 + 1, 4), int(step), dtype=torch.int32, device=o.device)
+    bits = o.contiguous().view(torch.int32).view(N, Dv // 2, 2)
+    rec[:, : Dv // 2, 0] = bits[:, :, 0]
+    rec[:, : Dv // 2, 2] = bits[:, :, 1]
+    rec[:, Dv // 2, 0] = lse.contiguous().view(torch.int32)
+    rec[:, Dv // 2, 2] = 0
+    return rec
 
 
 def decode_sharded(q, k_local, v_local, kv_lengths, *, page: int, sm_scale: float, group=None,

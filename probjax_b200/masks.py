@@ -432,12 +432,119 @@ class LowRankBias(AttentionBias):
         return (self.scale * torch.einsum("hqr,hkr->hqk", qf, kf))[None]
 
 
+class IdentityBias(AttentionBias):
+    """Leaves the scores as they are (attention_mask_bias.py, ``IdentityBias``)."""
+
+    def dense(self, q_len, kv_len, *, batch_size=1, num_heads=1):
+        return torch.zeros((1, 1, q_len, kv_len), dtype=torch.float32)
+
+
+def _t5_bucket(relative_position, *, num_buckets: int, max_distance: int, bidirectional: bool):
+    """T5 log-bucketing of ``k - q`` (attention_mask_bias.py:2417-2449)."""
+    import math
+
+    rp = -relative_position.to(torch.int64)
+    if bidirectional:
+        half = num_buckets // 2
+        sign_bucket = (rp < 0).to(torch.int64) * half
+        rp = rp.abs()
+        nb = half
+    else:
+        sign_bucket = torch.zeros_like(rp)
+        rp = rp.clamp_min(0)
+        nb = num_buckets
+    max_exact = nb // 2
+    is_small = rp < max_exact
+    rp_f = rp.to(torch.float32)
+    val_large = max_exact + (torch.log(rp_f.clamp_min(1.0) / max_exact) / math.log(max_distance / max_exact)
+                             * (nb - max_exact))
+    val_large = val_large.to(torch.int64).clamp_max(nb - 1)
+    return torch.where(is_small, rp, val_large) + sign_bucket
+
+
+class _RelativeBias(AttentionBias):
+    """Biases that depend on the head and on ``k - q`` only: ``table(rel) -> [H|1, len(rel)]``."""
+
+    def table(self, rel):
+        raise NotImplementedError
+
+    def relative_table(self, q_len, kv_len):
+        """``[H|1, q_len + kv_len - 1]`` float32: entry ``(j - i) + q_len - 1`` is the bias of ``(i, j)``."""
+        rel = torch.arange(-(q_len - 1), kv_len, dtype=torch.int64)
+        return self.table(rel).float()
+
+    def dense(self, q_len, kv_len, *, batch_size=1, num_heads=1):
+        rel = _idx(kv_len)[None, :].to(torch.int64) - _idx(q_len)[:, None].to(torch.int64)
+        return self.table(rel.reshape(-1)).float().reshape(-1, q_len, kv_len)[None]
+
+
+class T5RelativePositionBias(_RelativeBias):
+    """``table[h, bucket(k - q)]`` with T5's bucketing (attention_mask_bias.py:2453-2517)."""
+
+    def __init__(self, bias_table, *, num_buckets: int, max_distance: int = 128, bidirectional: bool = True):
+        bt = torch.as_tensor(bias_table)
+        bt = bt[None] if bt.dim() == 1 else bt
+        if bt.dim() != 2:
+            raise ValueError("bias_table must have shape [H|1, num_buckets]")
+        if bt.shape[-1] != int(num_buckets):
+            raise ValueError("bias_table last dim must equal num_buckets")
+        self.bias_table, self.num_buckets = bt, int(num_buckets)
+        self.max_distance, self.bidirectional = int(max_distance), bool(bidirectional)
+
+    def table(self, rel):
+        buckets = _t5_bucket(rel, num_buckets=self.num_buckets, max_distance=self.max_distance,
+                             bidirectional=self.bidirectional)
+        return self.bias_table.cpu()[:, buckets]
+
+
+class LearnedRelativePositionBias(_RelativeBias):
+    """``table[h, clip(k - q, -M, M) + M]`` (attention_mask_bias.py:2521-2560)."""
+
+    def __init__(self, table, *, max_distance: int):
+        t = torch.as_tensor(table)
+        t = t[None] if t.dim() == 1 else t
+        if t.dim() != 2:
+            raise ValueError("table must have shape [H|1, 2*max_distance+1]")
+        if t.shape[-1] != 2 * int(max_distance) + 1:
+            raise ValueError("table last dim must be 2*max_distance+1")
+        self.tab, self.max_distance = t, int(max_distance)
+
+    def table(self, rel):
+        return self.tab.cpu()[:, rel.clamp(-self.max_distance, self.max_distance) + self.max_distance]
+
+
+class SoftCappingBias(AttentionBias):
+    """``softcap * tanh(scores / softcap)`` (attention_mask_bias.py:2564-2601).  Not additive: it has
+    no dense form; the kernels evaluate it (and its derivative ``1 - tanh^2``) on the scores."""
+
+    def __init__(self, softcap: float = 20.0):
+        if softcap <= 0:
+            raise ValueError("softcap must be > 0")
+        self.softcap = float(softcap)
+
+
+class PerHeadScaleBias(AttentionBias):
+    """``scores * scale[h]`` (attention_mask_bias.py:2606-2650).  Not additive, no dense form."""
+
+    def __init__(self, scales):
+        s = torch.as_tensor(scales, dtype=torch.float32)
+        s = s[None] if s.dim() == 0 else s
+        if s.dim() != 1:
+            raise ValueError("scales must be shape [H|1]")
+        self.scales = s
+
+
 @dataclass
 class LoweredMask:
     band_lo: Optional[int] = None     # key j visible to query i iff i + band_lo <= j (None: no bound)
     band_hi: Optional[int] = None     # ... and j <= i + band_hi (None: no bound)
     kv_lengths: Optional[Any] = None  # int32 tensor [B] or None
     q_limit: Optional[int] = None     # query rows >= q_limit see no key
+    # evaluated inside the kernels from O(B T) data (pjx_score_mod):
+    seg_q: Optional[Any] = None         # int32 [Bs, Lq]: key j visible iff seg_q[b, i] == seg_k[b, j]
+    seg_k: Optional[Any] = None         # int32 [Bs, Lkv]
+    row_kv_limit: Optional[Any] = None  # int32 [Bs, Lq]: key j visible iff j < row_kv_limit[b, i]
+    prefix_len: Optional[Any] = None    # int32 [B]: keys j < prefix_len[b] visible to every row (OR with the band)
 
     @property
     def causal(self) -> bool:
@@ -451,6 +558,11 @@ class LoweredMask:
     @property
     def banded(self) -> bool:
         return self.band_lo is not None or self.band_hi is not None
+
+    @property
+    def structured(self) -> bool:
+        """Carries data the kernels evaluate per element (segments, row limits, prefix)."""
+        return self.seg_q is not None or self.row_kv_limit is not None or self.prefix_len is not None
 
 
 def _merge_lowered(a: LoweredMask, b: LoweredMask) -> LoweredMask:
@@ -467,7 +579,27 @@ def _merge_lowered(a: LoweredMask, b: LoweredMask) -> LoweredMask:
         out.kv_lengths = a.kv_lengths if a.kv_lengths is not None else b.kv_lengths
     limits = [x for x in (a.q_limit, b.q_limit) if x is not None]
     out.q_limit = min(limits) if limits else None
+    # one pair of segment ids, one set of row limits, one prefix; the prefix is OR-ed with the band, so
+    # it cannot be merged with a band that comes from another mask: (A | P) & C != (A & C) | P
+    for name in ("seg_q", "seg_k", "row_kv_limit", "prefix_len"):
+        x, y = getattr(a, name), getattr(b, name)
+        if x is not None and y is not None:
+            raise _MergeConflict(f"two masks with {name} data")
+        setattr(out, name, x if x is not None else y)
+    if (a.prefix_len is not None and b.banded) or (b.prefix_len is not None and a.banded):
+        raise _MergeConflict("a prefix mask cannot be AND-ed with another band natively")
     return out
+
+
+class _MergeConflict(NotImplementedError):
+    """Two natively lowered masks whose AND has no native form."""
+
+
+def _token_ids(keep, length):
+    """Segment ids for masks of the form ``(a_i & a_j) | i == j``: 0 where ``a``, else a negative id of
+    the token's own, so that equality of ids is the mask."""
+    t = torch.arange(length, dtype=torch.int32)
+    return torch.where(keep[..., :length], torch.zeros((), dtype=torch.int32), -(t + 1))
 
 
 def split_mask(mask, batch: int, q_len: int, kv_len: int):
@@ -480,8 +612,12 @@ def split_mask(mask, batch: int, q_len: int, kv_len: int):
     if isinstance(mask, ComposeMask) and mask.op == "and":
         la, ra = split_mask(mask.lhs, batch, q_len, kv_len)
         lb, rb = split_mask(mask.rhs, batch, q_len, kv_len)
+        try:
+            merged = _merge_lowered(la, lb)
+        except _MergeConflict:  # keep the left side native, the whole right side goes dense
+            merged, rb = la, mask.rhs
         residual = ra if rb is None else (rb if ra is None else ComposeMask("and", ra, rb))
-        return _merge_lowered(la, lb), residual
+        return merged, residual
     return LoweredMask(), mask
 
 
@@ -512,16 +648,139 @@ def lower_mask(mask, batch: int, q_len: int, kv_len: int) -> LoweredMask:
             out.q_limit = max(int(mask.q_length), 0)
         return out
     if isinstance(mask, KeyPaddingMask):
-        lengths = mask.lengths.reshape(-1)
-        if q_len == 1 and lengths.shape[0] == batch:
+        lengths = mask.lengths
+        if q_len == 1 and lengths.dim() == 1 and lengths.shape[0] == batch:
             return LoweredMask(kv_lengths=lengths.to(torch.int32))
+        # per query row (the reference lays 1-D data out as (1, T, 1, 1), attention_mask_bias.py:1175-1204)
+        if lengths.dim() == 1 and lengths.shape[0] in (1, q_len):
+            return LoweredMask(row_kv_limit=lengths.to(torch.int32).expand(q_len).reshape(1, q_len).contiguous())
+        if lengths.dim() == 2 and lengths.shape[0] in (1, batch) and lengths.shape[1] == q_len:
+            return LoweredMask(row_kv_limit=lengths.to(torch.int32).contiguous())
         raise NotImplementedError(
-            "KeyPaddingMask gives key lengths per query row; only the one-query-row decode form "
-            "lowers to the kernels (use KVLenMask for per-batch key lengths)"
+            "KeyPaddingMask gives key lengths per query row: pass [Lq] or [B, Lq] lengths "
+            "(use KVLenMask for per-batch key lengths)"
         )
+    if isinstance(mask, BlockDiagonalMask):  # also BlockDiagonalCausalMask, SameSegmentMask
+        qids = mask.query_block_ids
+        kids = mask.key_block_ids if mask.key_block_ids is not None else qids
+        qids = (qids if qids.dim() == 2 else qids[None])[:, :q_len].to(torch.int32).contiguous()
+        kids = (kids if kids.dim() == 2 else kids[None])[:, :kv_len].to(torch.int32).contiguous()
+        if qids.shape[1] != q_len or kids.shape[1] != kv_len or qids.shape[0] not in (1, batch) \
+                or kids.shape[0] not in (1, batch):
+            raise ValueError(f"segment ids {tuple(qids.shape)} / {tuple(kids.shape)} do not cover "
+                             f"[B|1, {q_len}] / [B|1, {kv_len}]")
+        return LoweredMask(seg_q=qids, seg_k=kids, band_hi=0 if isinstance(mask, BlockDiagonalCausalMask) else None)
+    if isinstance(mask, SeqLenMask):
+        lengths = mask.seq_lengths.reshape(-1).cpu()
+        if lengths.shape[0] != batch:
+            raise ValueError(f"SeqLenMask holds {lengths.shape[0]} lengths for a batch of {batch}")
+        n = max(q_len, kv_len)
+        ids = _token_ids(torch.arange(n)[None, :] < lengths[:, None], n)
+        return LoweredMask(seg_q=ids[:, :q_len].contiguous(), seg_k=ids[:, :kv_len].contiguous())
+    if isinstance(mask, MarginalizationMask):
+        keep = mask.mask.cpu()
+        keep = keep if keep.dim() == 2 else keep[None]
+        n = max(q_len, kv_len)
+        if keep.shape[1] < n or keep.shape[0] not in (1, batch):
+            raise ValueError(f"MarginalizationMask data {tuple(keep.shape)} does not cover [B|1, {n}]")
+        ids = _token_ids(keep, n)
+        return LoweredMask(seg_q=ids[:, :q_len].contiguous(), seg_k=ids[:, :kv_len].contiguous())
+    if isinstance(mask, PrefixLMMask):
+        pl = mask.prefix_lengths.reshape(-1).to(torch.int32)
+        if pl.shape[0] not in (1, batch):
+            raise ValueError(f"PrefixLMMask holds {pl.shape[0]} lengths for a batch of {batch}")
+        return LoweredMask(band_hi=0, prefix_len=pl.expand(batch).contiguous())
     if isinstance(mask, ComposeMask) and mask.op == "and":
         return _merge_lowered(lower_mask(mask.lhs, batch, q_len, kv_len), lower_mask(mask.rhs, batch, q_len, kv_len))
     raise NotImplementedError(f"mask {type(mask).__name__} is not implemented by the sm_100a kernels")
+
+
+@dataclass
+class LoweredBias:
+    """A bias expression as the kernels take it: one dense tensor (or none) plus the modifiers
+    evaluated per element from O(H T) data."""
+
+    dense: Optional[Any] = None         # float32 [B|1, H|1, Q, K]
+    rel_bias: Optional[Any] = None      # float32 [H|1, Q + K - 1]
+    alibi_slopes: Optional[Any] = None  # float32 [H]
+    alibi_mode: int = 0                 # 1: -slope * relu(i - j), 2: -slope * |i - j|
+    head_scale: Optional[Any] = None    # float32 [H]
+    softcap: float = 0.0
+    low_rank: tuple = ()                # LowRankBias terms, for the caller to fold into Q / K
+
+    @property
+    def structured(self) -> bool:
+        return (self.rel_bias is not None or self.alibi_slopes is not None or self.head_scale is not None
+                or self.softcap > 0)
+
+
+def _bias_terms(bias):
+    if bias is None:
+        return []
+    if isinstance(bias, SumBias):
+        return _bias_terms(bias.lhs) + _bias_terms(bias.rhs)
+    return [bias]
+
+
+def lower_bias_structured(bias, batch: int, heads: int, q_len: int, kv_len: int) -> LoweredBias:
+    """A (sum of) bias objects as a :class:`LoweredBias`: nothing of size ``Q x K`` is built except for
+    ``DenseBias`` terms, which already are that tensor."""
+    out = LoweredBias()
+    low_rank = []
+    for term in _bias_terms(bias):
+        if isinstance(term, IdentityBias):
+            continue
+        if isinstance(term, DenseBias):
+            term.dense(q_len, kv_len, batch_size=batch, num_heads=heads)  # shape validation
+            d = term.bias.float()
+            out.dense = d if out.dense is None else out.dense + d.to(out.dense.device)
+            continue
+        if isinstance(term, LowRankBias):
+            low_rank.append(term)
+            continue
+        if isinstance(term, SoftCappingBias):
+            if out.softcap > 0:
+                raise NotImplementedError("two soft-capping terms in one bias sum")
+            out.softcap = term.softcap
+            continue
+        if isinstance(term, PerHeadScaleBias):
+            if out.head_scale is not None:
+                raise NotImplementedError("two per-head scale terms in one bias sum")
+            if term.scales.shape[0] not in (1, heads):
+                raise ValueError(f"Cannot broadcast {term.scales.shape[0]} head scales to {heads} heads")
+            out.head_scale = term.scales.float().expand(heads).contiguous()
+            continue
+        slopes = mode = None
+        if isinstance(term, CausalAlibiBias):
+            slopes, mode = _alibi_slopes(heads), 1
+        elif isinstance(term, SymmetricAlibiBias):
+            slopes, mode = _alibi_slopes(heads), 2
+        elif isinstance(term, DistanceDecayBias):
+            slopes, mode = torch.full((heads,), term.alpha, dtype=torch.float32), 2
+        if slopes is not None and out.alibi_slopes is None:
+            out.alibi_slopes, out.alibi_mode = slopes, mode
+            continue
+        # everything else that depends on (head, j - i) only goes into the relative-position table
+        if slopes is not None:
+            rel = torch.arange(-(q_len - 1), kv_len, dtype=torch.float32)
+            dist = (-rel).clamp_min(0) if mode == 1 else rel.abs()
+            tab = -(slopes[:, None] * dist[None, :])
+        elif isinstance(term, ConstantBias):
+            tab = torch.full((1, q_len + kv_len - 1), term.value, dtype=torch.float32)
+        elif isinstance(term, _RelativeBias):
+            tab = term.relative_table(q_len, kv_len)
+            if tab.shape[0] not in (1, heads):
+                raise ValueError(f"Cannot broadcast a bias table of {tab.shape[0]} heads to {heads}")
+        else:
+            raise NotImplementedError(f"bias {type(term).__name__} is not implemented by the sm_100a kernels")
+        if out.rel_bias is None:
+            out.rel_bias = tab
+        else:  # [1, n] + [H, n] broadcasts
+            out.rel_bias = out.rel_bias + tab
+    out.low_rank = tuple(low_rank)
+    if out.rel_bias is not None:
+        out.rel_bias = out.rel_bias.contiguous()
+    return out
 
 
 def lower_bias(bias, batch: int, heads: int, q_len: int, kv_len: int):

@@ -248,7 +248,8 @@ def test_sharded_decode_rank0_of_two_with_the_peer_record_prefilled():
             f32[lay["o"](par, 1): lay["o"](par, 1) + N * D] = o1.reshape(-1)
             f32[lay["lse"](par, 1): lay["lse"](par, 1) + N] = lse1.permute(0, 2, 1).reshape(-1)  # rows in [B, Lq, Hq] order
             u32[lay["rank_flags"] + 1] = step
-            u32[lay["unit_flags"] + N: lay["unit_flags"] + 2 * N] = step
+            rec = pjd.ll_records(o1.reshape(N, D), lse1.permute(0, 2, 1).reshape(-1), step)
+            u32[lay["ll"](par, 1) * 4: (lay["ll"](par, 1) + N * lay["lines"]) * 4] = rec.reshape(-1)
             o.zero_()
             rc = L.pjx_attn_decode_sharded(q.data_ptr(), k0.data_ptr(), v0.data_ptr(), l0.data_ptr(), o.data_ptr(),
                                            lse.data_ptr(), B, 1, Hq, Hkv, D, D, k0.shape[1], _lib.PJX_BF16, c["sm_scale"],
@@ -256,9 +257,10 @@ def test_sharded_decode_rank0_of_two_with_the_peer_record_prefilled():
             assert rc == 0, _lib.last_error()
             assert L.pjx_read_status(status.data_ptr(), stream) == 0
             assert_close(o, lse, want, want_lse, torch.bfloat16, f"sharded rank 0 of 2, B={B} step {step}")
-        # rank 0 stored its own partial and flags into the peer's buffer as well
+        # rank 0 stored its own partial into the peer's buffer as well, under the step number
         pu32 = peer.view(torch.int32)
-        assert int(pu32[lay["rank_flags"]]) == 2 or bool((pu32[lay["unit_flags"]: lay["unit_flags"] + B * Hkv] == 2).all())
+        sent = pu32[lay["ll"](0, 0) * 4: (lay["ll"](0, 0) + N * lay["lines"]) * 4].view(N, lay["lines"], 4)
+        assert int(pu32[lay["rank_flags"]]) == 2 or bool((sent[:, :, 1] == 2).all() and (sent[:, :, 3] == 2).all())
 
 
 def test_decode_cache_steps_match_causal_attention():

@@ -46,6 +46,27 @@ def test_default_scale_rank3_and_extra_batch_dims():
     assert_close(got.reshape(6, 20, 4, 16), None, want, None, torch.float32, "rank 5")
 
 
+def test_dot_product_attention_takes_dense_mask_and_bias_arrays():
+    """The Flax-style call (layers/attention.py:1293-1319): boolean mask and additive bias given as
+    arrays broadcastable to [*batch, H, Q, K], with extra batch dimensions and fewer K/V heads."""
+    d = dev()
+    q = randn((2, 3, 24, 4, 16), torch.float32, 1)
+    k, v = randn((2, 3, 30, 2, 16), torch.float32, 2), randn((2, 3, 30, 2, 16), torch.float32, 3)
+    g = torch.Generator().manual_seed(4)
+    keep = torch.rand((2, 3, 1, 24, 30), generator=g) > 0.3   # per batch element, shared by the heads
+    keep[..., 0] = True                                      # every row keeps at least one key
+    bias = randn((4, 24, 30), torch.float32, 5)               # per head, shared by the batch
+    got = pj.dot_product_attention(q.to(d), k.to(d), v.to(d), mask=keep.to(d), bias=bias.to(d))
+    want, _ = oracle_fwd(q.reshape(6, 24, 4, 16), k.reshape(6, 30, 2, 16), v.reshape(6, 30, 2, 16),
+                         keep=keep.reshape(6, 1, 24, 30), bias=bias[None], sm_scale=0.25)
+    assert got.shape == q.shape
+    assert_close(got.reshape(6, 24, 4, 16), None, want, None, torch.float32, "dense arrays")
+    # an array bias together with a mask object
+    got = pj.dot_product_attention(q[0].to(d), k[0].to(d), v[0].to(d), mask=pj.CausalMask(), bias=bias.to(d))
+    want, _ = oracle_fwd(q[0], k[0], v[0], causal=True, bias=bias[None], sm_scale=0.25)
+    assert_close(got, None, want, None, torch.float32, "array bias with a mask object")
+
+
 def test_mha_defaults_and_padding_mask():
     d = dev()
     q, k, v = (randn((1, 50, 2, 24), torch.float32, s) for s in (1, 2, 3))

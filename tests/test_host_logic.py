@@ -323,11 +323,83 @@ def test_dense_lowered_masks_and_biases_follow_the_reference_predicates():
     both = M.SumBias(M.ConstantBias(1.5), M.DistanceDecayBias(1.0)).dense(6, 7)
     assert torch.allclose(both[0, 0], 1.5 - (i - j).abs().float())
     # an AND-expression keeps its native part native
-    lm, residual = M.split_mask(M.CausalMask() & M.SameSegmentMask(ids_q) & M.KVLenMask(torch.tensor([5])), 1, 6, 6)
-    assert lm.causal and lm.kv_lengths.tolist() == [5] and isinstance(residual, M.SameSegmentMask)
+    lm, residual = M.split_mask(M.CausalMask() & M.NotMask(M.SameSegmentMask(ids_q)) & M.KVLenMask(torch.tensor([5])), 1, 6, 6)
+    assert lm.causal and lm.kv_lengths.tolist() == [5] and isinstance(residual, M.NotMask)
     add = M.lower_dense(residual, M.ConstantBias(2.0), 1, 2, 6, 6)
-    want = torch.where(ids_q[:, None] == ids_q[None, :], torch.tensor(2.0), torch.tensor(-math.inf))
+    want = torch.where(ids_q[:, None] != ids_q[None, :], torch.tensor(2.0), torch.tensor(-math.inf))
     assert torch.equal(add[0, 0], want)
+
+
+def test_structured_lowering_of_masks_and_biases():
+    """Masks and biases the kernels evaluate per element lower to O(B T) / O(H T) data whose meaning
+    equals the classes' dense definitions (attention_mask_bias.py)."""
+    import torch
+    from probjax_b200 import masks as M
+
+    b, t = 2, 9
+    i, j = torch.arange(t)[:, None], torch.arange(t)[None, :]
+
+    def keep_of(lm):  # the kernels' rule, evaluated densely
+        band = torch.ones(t, t, dtype=torch.bool)
+        if lm.band_lo is not None:
+            band &= j >= i + lm.band_lo
+        if lm.band_hi is not None:
+            band &= j <= i + lm.band_hi
+        out = band[None].expand(b, t, t).clone()
+        if lm.prefix_len is not None:
+            out |= j[None] < lm.prefix_len[:, None, None]
+        if lm.seg_q is not None:
+            out &= lm.seg_q.expand(b, t)[:, :, None] == lm.seg_k.expand(b, t)[:, None, :]
+        if lm.row_kv_limit is not None:
+            out &= j[None] < lm.row_kv_limit.expand(b, t)[:, :, None]
+        if lm.kv_lengths is not None:
+            out &= j[None] < lm.kv_lengths[:, None, None]
+        return out
+
+    g = torch.Generator().manual_seed(3)
+    seg = torch.randint(0, 3, (b, t), generator=g)
+    tok = torch.rand((b, t), generator=g) > 0.4
+    for mask in (M.SameSegmentMask(seg, seg.flip(1)), M.BlockDiagonalMask(seg[0]), M.BlockDiagonalCausalMask(seg),
+                 M.SeqLenMask(torch.tensor([9, 4])), M.MarginalizationMask(tok), M.PrefixLMMask(torch.tensor([3, 0])),
+                 M.PrefixLMMask(torch.tensor([2, 5])) & M.KVLenMask(torch.tensor([7, 9])),
+                 M.SameSegmentMask(seg) & M.CausalLocalWindowMask(3)):
+        lm, residual = M.split_mask(mask, b, t, t)
+        assert residual is None and lm.structured, type(mask).__name__
+        assert torch.equal(keep_of(lm), mask.dense(t, t, batch_size=b)[:, 0]), type(mask).__name__
+    rows = torch.randint(1, t + 1, (t,), generator=g)
+    lm = M.lower_mask(M.KeyPaddingMask(rows), b, t, t)
+    assert torch.equal(keep_of(lm)[1], j < rows[:, None])
+    # a prefix cannot be merged with a band from another mask: that part goes dense
+    lm, residual = M.split_mask(M.PrefixLMMask(torch.tensor([3, 5])) & M.LocalWindowMask(2, 2), b, t, t)
+    assert lm.prefix_len is not None and isinstance(residual, M.LocalWindowMask)
+    # two segment masks: one native, one dense
+    lm, residual = M.split_mask(M.SameSegmentMask(seg) & M.MarginalizationMask(tok), b, t, t)
+    assert lm.seg_q is not None and isinstance(residual, M.MarginalizationMask)
+
+    heads = 4
+    rel = (j - i)
+    t5 = M.T5RelativePositionBias(torch.randn(heads, 8, generator=g), num_buckets=8, max_distance=16)
+    lr = M.LearnedRelativePositionBias(torch.randn(1, 7, generator=g), max_distance=3)
+    assert torch.equal(lr.dense(t, t)[0, 0], lr.tab[0][rel.clamp(-3, 3) + 3])
+    for bias in (t5, lr, M.ConstantBias(0.25), M.SumBias(M.CausalAlibiBias(), M.SymmetricAlibiBias()),
+                 M.SumBias(M.DistanceDecayBias(0.5), M.SumBias(t5, M.ConstantBias(-1.0)))):
+        lb = M.lower_bias_structured(bias, b, heads, t, t)
+        assert lb.dense is None and lb.structured
+        total = torch.zeros(heads, t, t)
+        if lb.rel_bias is not None:
+            assert lb.rel_bias.shape[1] == 2 * t - 1
+            total = total + lb.rel_bias.expand(heads, -1)[:, (rel + t - 1).reshape(-1)].reshape(heads, t, t)
+        if lb.alibi_slopes is not None:
+            dist = (i - j).clamp_min(0) if lb.alibi_mode == 1 else (i - j).abs()
+            total = total - lb.alibi_slopes[:, None, None] * dist
+        want = bias.dense(t, t, batch_size=1, num_heads=heads)[0].expand(heads, t, t)
+        assert torch.allclose(total, want, atol=1e-6), type(bias).__name__
+    lb = M.lower_bias_structured(M.SumBias(M.SoftCappingBias(5.0), M.PerHeadScaleBias(torch.tensor([2.0]))), b, heads, t, t)
+    assert lb.softcap == 5.0 and lb.head_scale.tolist() == [2.0] * heads
+    # T5 buckets (attention_mask_bias.py:2417-2449), 8 buckets, bidirectional: 4 per sign, distances 0 and 1
+    # exact, then 2 + floor(2 ln(d / 2) / ln 8) capped at 3; keys after the query use buckets 4..7
+    bk = M._t5_bucket(torch.tensor([0, -1, -3, -4, -100, 1, 3, 100]), num_buckets=8, max_distance=16, bidirectional=True)
+    assert bk.tolist() == [0, 1, 2, 2, 3, 5, 6, 7]
     lm2, res2 = M.split_mask(M.CausalMask(), 1, 6, 6)
     assert res2 is None and lm2.causal
 
@@ -369,3 +441,32 @@ def test_raw_wrappers_reject_mismatched_tensors_before_the_library_call():
 
     for fn in (A.attention_forward, A.attention_backward, A.attention_jvp, A.decode_forward):
         assert "_check_call(" in inspect.getsource(fn), fn.__name__
+
+
+def test_ffi_shim_is_consistent_and_compiles_without_jaxlib(tmp_path):
+    """The XLA FFI shim cannot run here (no jaxlib), but its gate must hold: the file compiles to an
+    object that only says why it is empty, every handler symbol it defines is one the Python side
+    registers, and every C function it forwards to is declared in the header."""
+    import re
+    import shutil
+    import subprocess
+
+    from probjax_b200 import build as B
+    from probjax_b200 import jax_ffi
+
+    src = (B.CSRC / "ffi_shim.cc").read_text()
+    defined = re.findall(r"XLA_FFI_DEFINE_HANDLER_SYMBOL\(\s*(\w+)", src)
+    assert sorted(defined) == sorted(jax_ffi.TARGETS)
+    header = (B.INCLUDE / "pjx_attention.h").read_text()
+    for fn in set(re.findall(r"\b(pjx_[a-z0-9_]+)\(", src)) - {"pjx_ffi_unavailable"}:
+        assert re.search(r"\b" + fn + r"\(", header), f"{fn} is not declared in pjx_attention.h"
+    assert not jax_ffi.available() or B.jax_include_dir()
+    if B.jax_include_dir() is None:
+        assert B.build_ffi() is None
+        obj = tmp_path / "ffi_shim.o"
+        gxx = shutil.which("g++")
+        res = subprocess.run([gxx, "-std=c++17", "-c", "-fPIC", "-I", str(B.INCLUDE), str(B.CSRC / "ffi_shim.cc"),
+                              "-o", str(obj)], capture_output=True, text=True)
+        assert res.returncode == 0, res.stderr
+        syms = subprocess.run(["nm", "-g", str(obj)], capture_output=True, text=True).stdout
+        assert "pjx_ffi_unavailable" in syms
