@@ -279,6 +279,10 @@ def main():
                     help="time only the backward of the headline shape on --batch rows (profiling captures)")
     ap.add_argument("--only-linear", action="store_true",
                     help="time only the fused QKV projection of the headline shape (profiling captures)")
+    ap.add_argument("--only-masked-bias", action="store_true",
+                    help="time only the masked + biased configuration on --batch batch rows (profiling captures)")
+    ap.add_argument("--only-latent", action="store_true",
+                    help="time only the latent-attention configuration on --batch batch rows (profiling captures)")
     ap.add_argument("--kernel", default=None, choices=[None, "b200:generic", "b200:tcgen05"],
                     help="force one forward kernel for the headline (default: the library's own choice)")
     args = ap.parse_args()
@@ -316,6 +320,12 @@ def main():
         return
     if args.only_linear:
         only_linear(args, dev, pk)
+        return
+    if args.only_masked_bias:
+        only_masked_bias(args, dev, pk)
+        return
+    if args.only_latent:
+        only_latent(args, dev, pk)
         return
 
     # ---------------------------------------------------------------- headline
@@ -587,6 +597,40 @@ def only_linear(args, dev, pk):
     res = bench_extra("linear", lambda: pj.linear(xg, wg), args.steps, args.warmup, 2.0 * m_rows * n_out * d_model / 1e12,
                       "TFLOP/s", pk["bf16_tflops"], "tensor", pk["source"])
     res["config"] = {"workload": f"QKV projection bf16 [{m_rows}, {d_model}] x [{n_out}, {d_model}]^T"}
+    _emit(res)
+
+
+def only_masked_bias(args, dev, pk):
+    """The masked + biased configuration (bf16 B8 H16 S1024 D64, per-batch key lengths, fp32 bias
+    [1,16,1024,1024]) on `--batch` batch rows, nothing else: the command profiling captures of the
+    staged-bias instantiation of the forward kernel run."""
+    import oracle
+    import probjax_b200 as pj
+
+    c3 = oracle.make_config(3, B=args.batch)
+    q3, k3, v3 = c3["q"].to(dev), c3["k"].to(dev), c3["v"].to(dev)
+    l3, b3 = c3["kv_lengths"].to(dev), c3["bias"].to(dev)
+    fl3 = 4.0 * 16 * 1024 * 64 * float(c3["kv_lengths"].sum())
+    res = bench_extra("c3", lambda: pj.attention_forward(q3, k3, v3, kv_lengths=l3, bias=b3, sm_scale=c3["sm_scale"]),
+                      args.steps, args.warmup, fl3 / 1e12, "TFLOP/s", pk["bf16_tflops"], "tensor", pk["source"])
+    res["config"] = {"workload": f"masked + biased attention bf16 B{args.batch} H16 S1024 D64, fp32 bias [1,16,1024,1024]",
+                     "kv_lengths": c3["kv_lengths"].tolist()}
+    _emit(res)
+
+
+def only_latent(args, dev, pk):
+    """The latent-attention configuration (bf16 H16 S2048 causal, rank 512 + 64 rotary) on `--batch`
+    batch rows, nothing else: the command profiling captures of the (192,128) instantiation of the
+    forward kernel and of the up-projection GEMM at K = 576 run."""
+    import oracle
+    import probjax_b200 as pj
+
+    c5 = oracle.make_config(5, B=args.batch)
+    q5, ch5, wk5, wv5 = c5["q"].to(dev), c5["cache"].to(dev), c5["wk"].to(dev), c5["wv"].to(dev)
+    fl5 = 2.0 * args.batch * 2048 * 512 * 16 * 256 + prefill_flops(args.batch, 16, 2048, 2048, 192, 128, True)
+    res = bench_extra("c5", lambda: pj.mla(q5, ch5, wk5, wv5, mask=pj.CausalMask(), sm_scale=c5["sm_scale"]), args.steps,
+                      args.warmup, fl5 / 1e12, "TFLOP/s", pk["bf16_tflops"], "tensor", pk["source"])
+    res["config"] = {"workload": f"latent attention bf16 B{args.batch} H16 S2048 causal, rank 512 + 64 rotary"}
     _emit(res)
 
 

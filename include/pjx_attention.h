@@ -309,6 +309,18 @@ int pjx_attn_decode_sharded(const void* q, const void* k_local, const void* v_lo
                             int world, void* const* exchange_buffers, uint32_t step, int32_t* status,
                             void* stream);
 size_t pjx_attn_decode_sharded_buffer_bytes(int B, int Lq, int Hq, int Dv, int world);
+/* The same with this rank's share of the cache held in pages (the format of
+ * pjx_attn_decode_paged): k_pool / v_pool [num_pages, page_size, Hkv, D|Dv], block_table int32
+ * [B, max_pages] naming the local pages of every sequence in order, local_lengths the valid tokens
+ * this rank holds.  The workspace is sized with capacity = max_pages * page_size.  No counterpart
+ * in the reference (contiguous caches, no sequence sharding). */
+int pjx_attn_decode_sharded_paged(const void* q, const void* k_pool, const void* v_pool,
+                                  const int32_t* block_table, const int32_t* local_lengths, void* o,
+                                  float* lse, int B, int Lq, int Hq, int Hkv, int D, int Dv,
+                                  int page_size, int max_pages, int dtype, float sm_scale,
+                                  int split_len, void* workspace, size_t workspace_bytes, int rank,
+                                  int world, void* const* exchange_buffers, uint32_t step,
+                                  int32_t* status, void* stream);
 
 /*
  * Exact combine of n_parts normalised partial results, each with its natural-
@@ -368,6 +380,24 @@ int pjx_kv_cache_append(void* k_cache, void* v_cache, const void* k_new, const v
  */
 int pjx_linear(const void* x, const void* w, void* y, int64_t M, int N, int K, int dtype, int impl,
                int32_t* status, void* stream);
+
+/* pjx_linear on a column block of wider matrices: row i of x starts at x + i * x_row_pitch and row i
+ * of y at y + i * y_row_pitch (pitches in elements).  One call per head applies a per-head weight
+ * to a [.., H, K] activation without gathering it, e.g. the value up-projection folded onto the
+ * output of absorbed latent attention, einsum("...qhr,hdr->...qhd")
+ * (probjax/nn/layers/latent_attention.py:468-474). */
+int pjx_linear_strided(const void* x, int64_t x_row_pitch, const void* w, void* y, int64_t y_row_pitch,
+                       int64_t M, int N, int K, int dtype, int impl, int32_t* status, void* stream);
+
+/*
+ * Root-mean-square normalisation of the rows of x [rows, width]: y = x * rsqrt(mean(x^2) + eps) *
+ * scale (float32 [width] or NULL = ones), arithmetic in float32, y in `dtype` (may alias x).
+ *
+ * Replaces the `nnx.RMSNorm(kv_lora_rank)` the latent-attention layer applies to the encoded latent
+ * before it is cached (probjax/nn/layers/latent_attention.py:313-319, 435-438).
+ */
+int pjx_rms_norm(const void* x, const float* scale, void* y, int64_t rows, int width, float eps,
+                 int dtype, void* stream);
 
 /*
  * Interleaved rotary position embedding of x [outer, T, H, D] into y (may alias x): pairs

@@ -27,6 +27,7 @@ SOURCES = [
     "attn_decode.cu",
     "kv_cache.cu",
     "rope.cu",
+    "rmsnorm.cu",
     "gemm_sm100.cu",
 ]
 

@@ -641,8 +641,9 @@ template <typename T, int HD>
 int launch_decode_t(const DecodeParams& p, cudaStream_t stream) {
   constexpr int smem = NSTAGE * 2 * BK * HD * 2;
   static_assert(smem >= (NWARP * 16 * HD + 2 * NWARP * 16) * 4, "merge scratch must fit in the ring");
-  auto kern = p.block_table ? decode_splitkv_kernel<T, HD, true, false>
-                            : (p.ex_fused ? decode_splitkv_kernel<T, HD, false, true> : decode_splitkv_kernel<T, HD, false, false>);
+  auto kern = p.block_table
+                  ? (p.ex_fused ? decode_splitkv_kernel<T, HD, true, true> : decode_splitkv_kernel<T, HD, true, false>)
+                  : (p.ex_fused ? decode_splitkv_kernel<T, HD, false, true> : decode_splitkv_kernel<T, HD, false, false>);
   int rc = check_cuda(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem),
                       "cudaFuncSetAttribute(decode)");
   if (rc) return rc;

@@ -18,7 +18,8 @@
 
 namespace pjx {
 
-int make_tmap_2d(CUtensorMap* m, const void* base, int dtype, int64_t rows, int64_t cols, int box_rows);
+int make_tmap_2d(CUtensorMap* m, const void* base, int dtype, int64_t rows, int64_t cols, int box_rows,
+                 int64_t pitch = 0);
 
 namespace {
 
@@ -271,7 +272,8 @@ gemm_tn_sm100_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_cons
 // CUDA-core fallback: 64 x 64 tile, 16-wide K slices, 4 x 4 outputs per thread.
 template <typename T>
 __global__ void __launch_bounds__(256) gemm_tn_simt_kernel(const T* __restrict__ A, const T* __restrict__ Bm,
-                                                          T* __restrict__ Cout, int64_t M, int N, int K) {
+                                                          T* __restrict__ Cout, int64_t M, int N, int K, int64_t lda,
+                                                          int64_t ldc) {
   __shared__ float As[16][65], Bs[16][65];
   const int tid = threadIdx.x, tx = tid & 15, ty = tid >> 4;
   const int64_t m0 = (int64_t)blockIdx.y * 64;
@@ -282,7 +284,7 @@ __global__ void __launch_bounds__(256) gemm_tn_simt_kernel(const T* __restrict__
       const int r = idx >> 4, kk = idx & 15;
       const int64_t gm = m0 + r;
       const int gn = n0 + r;
-      As[kk][r] = (gm < M && k0 + kk < K) ? Elem<T>::to_f(A[gm * K + k0 + kk]) : 0.f;
+      As[kk][r] = (gm < M && k0 + kk < K) ? Elem<T>::to_f(A[gm * lda + k0 + kk]) : 0.f;
       Bs[kk][r] = (gn < N && k0 + kk < K) ? Elem<T>::to_f(Bm[(int64_t)gn * K + k0 + kk]) : 0.f;
     }
     __syncthreads();
@@ -307,7 +309,7 @@ __global__ void __launch_bounds__(256) gemm_tn_simt_kernel(const T* __restrict__
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
       const int gn = n0 + tx + 16 * j;
-      if (gn < N) Cout[gm * N + gn] = Elem<T>::from_f(acc[i][j]);
+      if (gn < N) Cout[gm * ldc + gn] = Elem<T>::from_f(acc[i][j]);
     }
   }
 }
@@ -328,22 +330,24 @@ EncodeTiledFn encode_fn2() {
 }
 
 template <typename T>
-int launch_simt(const void* A, const void* Bm, void* C, int64_t M, int N, int K, cudaStream_t stream) {
+int launch_simt(const void* A, const void* Bm, void* C, int64_t M, int N, int K, int64_t lda, int64_t ldc,
+                cudaStream_t stream) {
   dim3 grid((N + 63) / 64, (unsigned)((M + 63) / 64));
   gemm_tn_simt_kernel<T><<<grid, 256, 0, stream>>>(static_cast<const T*>(A), static_cast<const T*>(Bm),
-                                                   static_cast<T*>(C), M, N, K);
+                                                   static_cast<T*>(C), M, N, K, lda, ldc);
   count_launch();
   return check_cuda(cudaGetLastError(), "projection (CUDA-core) launch");
 }
 
 }  // namespace
 
-// Row-major [rows, cols] 16-bit matrix, box = 64 columns x box_rows rows.
-int make_tmap_2d(CUtensorMap* m, const void* base, int dtype, int64_t rows, int64_t cols, int box_rows) {
+// Row-major [rows, cols] 16-bit matrix with a row pitch of `pitch` elements (0 = cols),
+// box = 64 columns x box_rows rows.
+int make_tmap_2d(CUtensorMap* m, const void* base, int dtype, int64_t rows, int64_t cols, int box_rows, int64_t pitch) {
   EncodeTiledFn fn = encode_fn2();
   if (!fn) return fail(PJX_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
   cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
-  cuuint64_t strides[1] = {(cuuint64_t)cols * 2};
+  cuuint64_t strides[1] = {(cuuint64_t)(pitch ? pitch : cols) * 2};
   cuuint32_t box[2] = {64, (cuuint32_t)box_rows};
   cuuint32_t estr[2] = {1, 1};
   CUresult r = fn(m, dtype == PJX_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2,
@@ -355,11 +359,12 @@ int make_tmap_2d(CUtensorMap* m, const void* base, int dtype, int64_t rows, int6
 
 namespace {
 
-int simt_by_dtype(const void* A, const void* Bm, void* C, int64_t M, int N, int K, int dtype, cudaStream_t stream) {
+int simt_by_dtype(const void* A, const void* Bm, void* C, int64_t M, int N, int K, int64_t lda, int64_t ldc, int dtype,
+                  cudaStream_t stream) {
   switch (dtype) {
-    case PJX_F32: return launch_simt<float>(A, Bm, C, M, N, K, stream);
-    case PJX_BF16: return launch_simt<__nv_bfloat16>(A, Bm, C, M, N, K, stream);
-    case PJX_F16: return launch_simt<__half>(A, Bm, C, M, N, K, stream);
+    case PJX_F32: return launch_simt<float>(A, Bm, C, M, N, K, lda, ldc, stream);
+    case PJX_BF16: return launch_simt<__nv_bfloat16>(A, Bm, C, M, N, K, lda, ldc, stream);
+    case PJX_F16: return launch_simt<__half>(A, Bm, C, M, N, K, lda, ldc, stream);
   }
   return fail(PJX_ERR_BAD_ARG, "unknown dtype %d", dtype);
 }
@@ -367,18 +372,24 @@ int simt_by_dtype(const void* A, const void* Bm, void* C, int64_t M, int N, int 
 }  // namespace
 
 int launch_gemm_tn2(const void* A, const void* B0, void* C0, int N0, const void* B1, void* C1, int N1, int64_t M,
-                    int K, int dtype, int impl, int32_t* status, cudaStream_t stream) {
+                    int K, int dtype, int impl, int32_t* status, cudaStream_t stream, int64_t lda, int64_t ldc) {
   if (M == 0 || (N0 == 0 && N1 == 0)) return PJX_OK;
+  if (lda == 0) lda = K;
+  const bool c_strided = ldc != 0 && ldc != N0;
+  if (c_strided && N1) return fail(PJX_ERR_BAD_ARG, "a row pitch for C is taken for one product only");
+  if (ldc == 0) ldc = N0;
   uintptr_t al = reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(B0);
   if (N1) al |= reinterpret_cast<uintptr_t>(B1);
-  const bool tc_ok = (dtype == PJX_BF16 || dtype == PJX_F16) && K % 8 == 0 && K >= 64 && (al & 15) == 0 &&
-                     M <= 2147483647LL - TM;
+  bool tc_ok = (dtype == PJX_BF16 || dtype == PJX_F16) && K % 8 == 0 && K >= 64 && (al & 15) == 0 &&
+               M <= 2147483647LL - TM && lda % 8 == 0;
+  // a pitched C leaves through TMA stores only (the direct stores assume dense rows)
+  if (c_strided && !(ldc % 8 == 0 && N0 % 8 == 0 && (reinterpret_cast<uintptr_t>(C0) & 15) == 0)) tc_ok = false;
   if (impl == PJX_IMPL_SM100 && !tc_ok)
     return fail(PJX_ERR_UNSUPPORTED, "tcgen05 projection needs 16-bit inputs, K %% 8 == 0, K >= 64 and 16-byte aligned operands");
   if (impl != PJX_IMPL_GENERIC && tc_ok) {
     CUtensorMap ta, tb0, tb1;
     int rc;
-    if ((rc = make_tmap_2d(&ta, A, dtype, M, K, TM))) return rc;
+    if ((rc = make_tmap_2d(&ta, A, dtype, M, K, TM, lda))) return rc;
     if ((rc = make_tmap_2d(&tb0, B0, dtype, N0, K, 128))) return rc;
     if (N1) {
       if ((rc = make_tmap_2d(&tb1, B1, dtype, N1, K, 128))) return rc;
@@ -392,10 +403,10 @@ int launch_gemm_tn2(const void* A, const void* B0, void* C0, int N0, const void*
     // Short K: a tile's epilogue is as long as its main loop, so the outputs go through shared memory
     // and TMA stores (needs row pitches that are multiples of 16 bytes). Long K hides the direct stores
     // and prefers the fourth operand stage.
-    const bool staged = K < 1536 && (N0 % 8 == 0) && (N1 % 8 == 0) && (cal & 15) == 0;
+    const bool staged = (K < 1536 || c_strided) && (N0 % 8 == 0) && (N1 % 8 == 0) && (cal & 15) == 0;
     CUtensorMap tc0 = ta, tc1 = ta;
     if (staged) {
-      if ((rc = make_tmap_2d(&tc0, C0, dtype, M, N0, TM))) return rc;
+      if ((rc = make_tmap_2d(&tc0, C0, dtype, M, N0, TM, ldc))) return rc;
       tc1 = tc0;
       if (N1 && (rc = make_tmap_2d(&tc1, C1, dtype, M, N1, TM))) return rc;
     }
@@ -418,9 +429,9 @@ int launch_gemm_tn2(const void* A, const void* B0, void* C0, int N0, const void*
     count_launch();
     return check_cuda(cudaGetLastError(), "projection (tcgen05) launch");
   }
-  int rc = simt_by_dtype(A, B0, C0, M, N0, K, dtype, stream);
+  int rc = simt_by_dtype(A, B0, C0, M, N0, K, lda, ldc, dtype, stream);
   if (rc || !N1) return rc;
-  return simt_by_dtype(A, B1, C1, M, N1, K, dtype, stream);
+  return simt_by_dtype(A, B1, C1, M, N1, K, lda, N1, dtype, stream);
 }
 
 int launch_gemm_tn(const void* A, const void* Bm, void* C, int64_t M, int N, int K, int dtype, int impl,

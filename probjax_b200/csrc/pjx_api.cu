@@ -195,6 +195,20 @@ int pjx_linear(const void* x, const void* w, void* y, int64_t M, int N, int K, i
   return launch_gemm_tn2(x, w, y, N, nullptr, nullptr, 0, M, K, dtype, impl, status, static_cast<cudaStream_t>(stream));
 }
 
+int pjx_linear_strided(const void* x, int64_t x_row_pitch, const void* w, void* y, int64_t y_row_pitch, int64_t M, int N,
+                       int K, int dtype, int impl, int32_t* status, void* stream) {
+  if (dtype != PJX_F32 && dtype != PJX_BF16 && dtype != PJX_F16)
+    return fail(PJX_ERR_BAD_ARG, "dtype must be float32, bfloat16 or float16 (got code %d)", dtype);
+  if (M < 0 || N < 0 || K < 1) return fail(PJX_ERR_BAD_ARG, "linear: negative dimension or K < 1");
+  if (x_row_pitch < K || y_row_pitch < N) return fail(PJX_ERR_BAD_ARG, "linear: a row pitch is shorter than its row");
+  if (impl != PJX_IMPL_AUTO && impl != PJX_IMPL_GENERIC && impl != PJX_IMPL_SM100)
+    return fail(PJX_ERR_BAD_ARG, "impl must be 0 (auto), 1 (generic) or 2 (tcgen05), got %d", impl);
+  if (M == 0 || N == 0) return PJX_OK;
+  if (!x || !w || !y) return fail(PJX_ERR_BAD_ARG, "linear: null buffer");
+  return launch_gemm_tn2(x, w, y, N, nullptr, nullptr, 0, M, K, dtype, impl, status, static_cast<cudaStream_t>(stream),
+                         x_row_pitch, y_row_pitch);
+}
+
 int pjx_attn_decode_default_split_len(int B, int Hkv, int capacity) {
   // Measured on B200 (B=16, Hkv=8, caches of 4k..32k keys): CTAs that stream at least
   // ~2048 keys amortise their pipeline fill and merge; more than ~3.5 waves of the 296
@@ -321,11 +335,12 @@ size_t pjx_attn_decode_sharded_buffer_bytes(int B, int Lq, int Hq, int Dv, int w
   return align_up(exchange_buffer_bytes(world, (int64_t)B * Lq * Hq, Dv));
 }
 
-int pjx_attn_decode_sharded(const void* q, const void* k_local, const void* v_local, const int32_t* local_lengths,
-                            void* o, float* lse, int B, int Lq, int Hq, int Hkv, int D, int Dv, int capacity_local,
-                            int dtype, float sm_scale, int split_len, void* workspace, size_t workspace_bytes,
-                            int rank, int world, void* const* exchange_buffers, uint32_t step, int32_t* status,
-                            void* stream) {
+// Shared body of the two sharded entry points (contiguous local cache, or local pages).
+static int decode_sharded_impl(const void* q, const void* k_local, const void* v_local, const int32_t* block_table,
+                               int page_size, int max_pages, const int32_t* local_lengths, void* o, float* lse, int B,
+                               int Lq, int Hq, int Hkv, int D, int Dv, int capacity_local, int dtype, float sm_scale,
+                               int split_len, void* workspace, size_t workspace_bytes, int rank, int world,
+                               void* const* exchange_buffers, uint32_t step, int32_t* status, void* stream) {
   int rc = validate_common(q, k_local, v_local, o, B, Lq, capacity_local, Hq, Hkv, D, Dv, dtype);
   if (rc) return rc;
   if (world < 1 || world > kMaxExchangeRanks || rank < 0 || rank >= world)
@@ -343,6 +358,7 @@ int pjx_attn_decode_sharded(const void* q, const void* k_local, const void* v_lo
   p.rows = (Hq / Hkv) * Lq;
   p.sm_scale = sm_scale;
   p.o_is_f32 = 0;
+  p.block_table = block_table; p.page_size = page_size; p.max_pages = max_pages;
   const bool aligned =
       ((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(k_local) | reinterpret_cast<uintptr_t>(v_local)) & 15) == 0;
   if (!decode_fast_supported(p, dtype) || !aligned || capacity_local == 0)
@@ -369,6 +385,31 @@ int pjx_attn_decode_sharded(const void* q, const void* k_local, const void* v_lo
   p.ex_fused = ((int64_t)p.num_splits * Hkv * B <= slots) && (reinterpret_cast<uintptr_t>(o) & 7) == 0;
   for (int i = 0; i < world; ++i) p.ex_buf[i] = static_cast<unsigned char*>(exchange_buffers[i]);
   return launch_decode(p, dtype, static_cast<cudaStream_t>(stream));
+}
+
+int pjx_attn_decode_sharded(const void* q, const void* k_local, const void* v_local, const int32_t* local_lengths,
+                            void* o, float* lse, int B, int Lq, int Hq, int Hkv, int D, int Dv, int capacity_local,
+                            int dtype, float sm_scale, int split_len, void* workspace, size_t workspace_bytes,
+                            int rank, int world, void* const* exchange_buffers, uint32_t step, int32_t* status,
+                            void* stream) {
+  return decode_sharded_impl(q, k_local, v_local, nullptr, 0, 0, local_lengths, o, lse, B, Lq, Hq, Hkv, D, Dv,
+                             capacity_local, dtype, sm_scale, split_len, workspace, workspace_bytes, rank, world,
+                             exchange_buffers, step, status, stream);
+}
+
+int pjx_attn_decode_sharded_paged(const void* q, const void* k_pool, const void* v_pool, const int32_t* block_table,
+                                  const int32_t* local_lengths, void* o, float* lse, int B, int Lq, int Hq, int Hkv,
+                                  int D, int Dv, int page_size, int max_pages, int dtype, float sm_scale, int split_len,
+                                  void* workspace, size_t workspace_bytes, int rank, int world,
+                                  void* const* exchange_buffers, uint32_t step, int32_t* status, void* stream) {
+  if (page_size < 64 || page_size % 64 != 0)
+    return fail(PJX_ERR_BAD_ARG, "page_size must be a positive multiple of 64 (got %d)", page_size);
+  if (max_pages < 1 || (int64_t)max_pages * page_size >= PJX_BAND_NO_UPPER)
+    return fail(PJX_ERR_BAD_ARG, "max_pages * page_size must be positive and below 2^30");
+  if (!block_table || !local_lengths) return fail(PJX_ERR_BAD_ARG, "paged decode needs a block table and key lengths");
+  return decode_sharded_impl(q, k_pool, v_pool, block_table, page_size, max_pages, local_lengths, o, lse, B, Lq, Hq, Hkv,
+                             D, Dv, max_pages * page_size, dtype, sm_scale, split_len, workspace, workspace_bytes, rank,
+                             world, exchange_buffers, step, status, stream);
 }
 
 int pjx_attn_combine(const float* o_parts, const float* lse_parts, int n_parts, int64_t n_rows, int Dv, void* o,

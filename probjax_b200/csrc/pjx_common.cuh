@@ -175,7 +175,9 @@ int launch_combine_parts(const float* o_parts, const float* lse_parts, int n_par
 int launch_gemm_tn(const void* A, const void* Bm, void* C, int64_t M, int N, int K, int dtype,
                    int impl, cudaStream_t stream);
 // Two products sharing A in one launch: C0 = A . B0^T [M, N0], C1 = A . B1^T [M, N1] (N1 may be 0).
+// `lda` / `ldc` are row pitches of A and C0 in elements (0 = dense rows); a pitched C0 excludes C1.
 int launch_gemm_tn2(const void* A, const void* B0, void* C0, int N0, const void* B1, void* C1, int N1,
-                    int64_t M, int K, int dtype, int impl, int32_t* status, cudaStream_t stream);
+                    int64_t M, int K, int dtype, int impl, int32_t* status, cudaStream_t stream,
+                    int64_t lda = 0, int64_t ldc = 0);
 
 }  // namespace pjx

@@ -233,7 +233,12 @@ class FusedShardedDecoder:
     number of times.  ``decoder.q`` holds the queries of the step.
     """
 
-    def __init__(self, q, k_local, v_local, kv_lengths, *, page: int, sm_scale: float, group=None):
+    def __init__(self, q, k_local, v_local, kv_lengths, *, page: int, sm_scale: float, group=None,
+                 block_table=None):
+        """``block_table`` (``int32 [B, max_pages]``) switches to a paged local cache: ``k_local`` /
+        ``v_local`` are then page pools ``[num_pages, page_size, Hkv, D]`` and row ``b`` of the table
+        names, in order, the pool pages that hold this rank's share of sequence ``b`` (the pool page
+        size is the cache's own and must be a multiple of 64; ``page`` stays the sharding granule)."""
         import ctypes
 
         from . import _lib
@@ -245,7 +250,14 @@ class FusedShardedDecoder:
         self.q, self.k, self.v = q.contiguous(), k_local.contiguous(), v_local.contiguous()
         dev = q.device
         B, Lq, Hq, D = q.shape
-        self.cap, Hkv, Dv = self.k.shape[1], self.k.shape[2], self.v.shape[3]
+        self.block_table = None
+        if block_table is not None:
+            self.block_table = torch.as_tensor(block_table).to(device=dev, dtype=torch.int32).contiguous()
+            if self.block_table.dim() != 2 or self.block_table.shape[0] != B:
+                raise ValueError(f"block_table must be [B={B}, max_pages], got {tuple(self.block_table.shape)}")
+            self.pool_page = self.k.shape[1]
+        self.cap = self.k.shape[1] if block_table is None else self.block_table.shape[1] * self.k.shape[1]
+        Hkv, Dv = self.k.shape[2], self.v.shape[3]
         self.shape = (B, Lq, Hq, Hkv, D, Dv)
         self.out = torch.empty((B, Lq, Hq, Dv), dtype=q.dtype, device=dev)
         self.lse = torch.empty((B, Hq, Lq), dtype=torch.float32, device=dev)
@@ -281,11 +293,19 @@ class FusedShardedDecoder:
 
         B, Lq, Hq, Hkv, D, Dv = self.shape
         self.step += 1
-        rc = self._L.pjx_attn_decode_sharded(
-            self.q.data_ptr(), self.k.data_ptr(), self.v.data_ptr(), self.lens.data_ptr(), self.out.data_ptr(),
-            self.lse.data_ptr(), B, Lq, Hq, Hkv, D, Dv, self.cap, self._dt, self.sm_scale, 0,
-            self.ws.data_ptr(), self.ws.numel(), self.rank, self.world, self._ptrs, self.step,
-            self._status.data_ptr(), torch.cuda.current_stream(self.q.device).cuda_stream)
+        stream = torch.cuda.current_stream(self.q.device).cuda_stream
+        if self.block_table is not None:
+            rc = self._L.pjx_attn_decode_sharded_paged(
+                self.q.data_ptr(), self.k.data_ptr(), self.v.data_ptr(), self.block_table.data_ptr(),
+                self.lens.data_ptr(), self.out.data_ptr(), self.lse.data_ptr(), B, Lq, Hq, Hkv, D, Dv, self.pool_page,
+                self.block_table.shape[1], self._dt, self.sm_scale, 0, self.ws.data_ptr(), self.ws.numel(), self.rank,
+                self.world, self._ptrs, self.step, self._status.data_ptr(), stream)
+        else:
+            rc = self._L.pjx_attn_decode_sharded(
+                self.q.data_ptr(), self.k.data_ptr(), self.v.data_ptr(), self.lens.data_ptr(), self.out.data_ptr(),
+                self.lse.data_ptr(), B, Lq, Hq, Hkv, D, Dv, self.cap, self._dt, self.sm_scale, 0,
+                self.ws.data_ptr(), self.ws.numel(), self.rank, self.world, self._ptrs, self.step,
+                self._status.data_ptr(), stream)
         _lib.check(rc)
         return (self.out, self.lse) if return_lse else self.out
 

@@ -263,6 +263,33 @@ def test_sharded_decode_rank0_of_two_with_the_peer_record_prefilled():
         assert int(pu32[lay["rank_flags"]]) == 2 or bool((sent[:, :, 1] == 2).all() and (sent[:, :, 3] == 2).all())
 
 
+def test_sharded_decode_over_a_paged_local_cache():
+    """The sharded step with this rank's share held in shuffled pool pages (one rank, exchange with
+    itself): bit-identical to the same step over the contiguous local cache, right against the oracle."""
+    c = oracle.make_config(4, B=4, cap=2048)
+    c["kv_lengths"][1] = 100
+    d = dev()
+    q, k, v = c["q"].to(d), c["k"].to(d), c["v"].to(d)
+    page = 128
+    B, cap = k.shape[0], k.shape[1]
+    mp = cap // page
+    perm = torch.randperm(B * mp, generator=torch.Generator().manual_seed(3)).view(B, mp).to(torch.int32)
+    kp = torch.empty((B * mp, page) + tuple(k.shape[2:]), dtype=k.dtype, device=d)
+    vp = torch.empty_like(kp)
+    kp[perm.view(-1).long().to(d)] = k.view(B * mp, page, *k.shape[2:])
+    vp[perm.view(-1).long().to(d)] = v.view(B * mp, page, *v.shape[2:])
+    dense = pjd.FusedShardedDecoder(q, k, v, c["kv_lengths"], page=page, sm_scale=c["sm_scale"])
+    paged = pjd.FusedShardedDecoder(q, kp, vp, c["kv_lengths"], page=page, sm_scale=c["sm_scale"], block_table=perm)
+    for _ in range(2):
+        o1, l1 = dense(return_lse=True)
+        o2, l2 = paged(return_lse=True)
+    dense.check_status()
+    paged.check_status()
+    assert torch.equal(o1, o2) and torch.equal(l1, l2)
+    want, want_lse = oracle_fwd(c["q"], c["k"], c["v"], kv_lengths=c["kv_lengths"], sm_scale=c["sm_scale"])
+    assert_close(o2, l2, want, want_lse, torch.bfloat16, "paged sharded decode")
+
+
 def test_decode_cache_steps_match_causal_attention():
     """A ragged batch decoded token by token through DecodeCache (append kernel + split-KV
     decode) equals attention over each sequence's prefix (the reference's decode branch,

@@ -252,3 +252,68 @@ def test_linear_projection(dtype, m, n, k):
     assert got.shape == (2, m // 2, n)
     tol = 1e-5 if dtype == torch.float32 else 2e-2
     assert float((got.double().cpu() - want).abs().max()) <= tol
+
+
+def _layer_reference(layer, x_q, x_kv, *, causal):
+    """float64 restatement of the layer's forward (layers/latent_attention.py:424-481, 640-709) on the
+    layer's own (rounded) weights."""
+    f = lambda t: None if t is None else t.detach().double().cpu()
+    wkv_a, wq, wk, wv, wo = f(layer.wkv_a), f(layer.wq), f(layer.wk), f(layer.wv), f(layer.wo)
+    x_q, x_kv = x_q.double(), x_kv.double()
+    latent = x_kv @ wkv_a.t()
+    if layer.latent_norm_scale is not None:
+        latent = latent * torch.rsqrt((latent ** 2).mean(-1, keepdim=True) + layer.eps) * f(layer.latent_norm_scale)
+    h, dqk = layer.num_heads, layer.qk_head_dim
+    q = (x_q @ wq.t()).reshape(x_q.shape[0], x_q.shape[1], h, dqk)
+    if layer.mode == "materialized":
+        key = torch.einsum("bsr,hdr->bshd", latent, wk)
+        val = torch.einsum("bsr,hdr->bshd", latent, wv)
+    else:
+        key = val = latent[:, :, None, :].expand(-1, -1, h, -1)
+    s = torch.einsum("bqhd,bkhd->bhqk", q, key) / math.sqrt(dqk)
+    if causal:
+        s = s.masked_fill(~torch.tril(torch.ones(s.shape[-2], s.shape[-1], dtype=torch.bool)), -math.inf)
+    attn = torch.einsum("bhqk,bkhd->bqhd", torch.softmax(s, -1), val)
+    if layer.mode == "absorbed" and wv is not None:
+        attn = torch.einsum("bqhr,hdr->bqhd", attn, wv)
+    return attn.reshape(attn.shape[0], attn.shape[1], -1) @ wo.t()
+
+
+@pytest.mark.parametrize("mode,kw", [("materialized", dict(qk_head_dim=128, v_head_dim=128)),
+                                     ("absorbed", dict(v_head_dim=64)),
+                                     ("absorbed", dict(value_projection=False))])
+def test_latent_attention_layer_steps(mode, kw):
+    """The layer around the latent kernel: encoder + RMS norm, query projection, attention, the value
+    projection folded onto the absorbed output, output projection -- every step a kernel of the library."""
+    from probjax_b200.latent_layer import MultiHeadLatentAttention
+
+    d = dev()
+    layer = MultiHeadLatentAttention(4, 256, kv_lora_rank=128, mode=mode, out_features=192, device=d, seed=3, **kw)
+    x = randn((2, 200, 256), torch.bfloat16, 9)
+    n0 = pj._lib.launch_count()
+    got = layer(x.to(d), mask=pj.CausalMask())
+    assert pj._lib.launch_count() - n0 >= 5  # encoder, norm, query projection, attention, output projection
+    pj.check_status(d)
+    want = _layer_reference(layer, x, x, causal=True)
+    rel = float((got.double().cpu() - want).norm() / want.norm())
+    assert got.shape == (2, 200, 192) and rel <= 2e-2, f"{mode} {kw}: relative error {rel:.3e}"
+
+
+def test_rms_norm_and_per_head_linear():
+    from probjax_b200.latent_layer import per_head_linear, rms_norm
+
+    d = dev()
+    for dtype, width, tol in ((torch.float32, 100, 1e-5), (torch.bfloat16, 512, 1e-2), (torch.float16, 576, 2e-3)):
+        x = randn((7, 33, width), dtype, 1)
+        scale = torch.rand(width, generator=torch.Generator().manual_seed(2)) + 0.5
+        got = rms_norm(x.to(d), scale.to(d), eps=1e-6)
+        want = x.double() * torch.rsqrt((x.double() ** 2).mean(-1, keepdim=True) + 1e-6) * scale.double()
+        assert float((got.double().cpu() - want).abs().max()) <= tol * float(want.abs().max())
+        assert torch.equal(rms_norm(x.to(d)), rms_norm(x.to(d), torch.ones(width)))
+    for dtype, (h, n, k), tol in ((torch.bfloat16, (3, 128, 512), 2e-2), (torch.float32, (2, 24, 40), 1e-5),
+                                  (torch.float16, (4, 72, 64), 5e-3)):
+        x, w = randn((5, 31, h, k), dtype, 3), (randn((h, n, k), dtype, 4).float() / math.sqrt(k)).to(dtype)
+        got = per_head_linear(x.to(d), w.to(d))
+        want = torch.einsum("bqhk,hnk->bqhn", x.double(), w.double())
+        rel = float((got.double().cpu() - want).norm() / want.norm())
+        assert got.shape == (5, 31, h, n) and rel <= tol, (dtype, rel)
