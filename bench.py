@@ -521,6 +521,17 @@ def main():
             del kp, vp
         except Exception as e:
             extras["decode_32k_paged"] = {"error": str(e)[:300]}
+        try:  # decode step of absorbed latent attention: 16 heads over a 576-wide latent cache of 32768 keys
+            Bl, Hl, Rl, Sl = 16, 16, 576, 32768
+            gl = torch.Generator(device=dev).manual_seed(5)
+            ql = torch.randn((Bl, 1, Hl, Rl), generator=gl, device=dev).bfloat16()
+            cl = (torch.randn((Bl, Sl, Rl), generator=gl, device=dev) * 0.5).bfloat16()
+            extras["latent_decode_32k"] = bench_extra(
+                "latent_decode", lambda: pj.mla_decode(ql, cl, sm_scale=Rl ** -0.5), xs, xw,
+                (cl.numel() * 2 + 2 * ql.numel() * 2) / 1e9, "GB/s", pk["hbm_gbs"], "hbm", pk["source"])
+            del ql, cl
+        except Exception as e:
+            extras["latent_decode_32k"] = {"error": str(e)[:200]}
         extras["decode_128k"] = long_context_decode_bench(dev, rank, world, xs, xw, pk, dist_on)
         if dist_on and "value" in extras["decode_128k"]:
             out["roofline"]["decode_128k_sharded_gbs"] = extras["decode_128k"]["value"]

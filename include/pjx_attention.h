@@ -439,6 +439,23 @@ int pjx_mla_fwd_mod(const void* q, const void* cache, const void* wk, const void
                     int32_t* status, void* stream);
 
 /*
+ * Decode step of absorbed latent attention: q [B, Lq, H, R] over the latent cache [B, capacity, R]
+ * with K = V = cache, per-sequence valid lengths, split along the keys and combined exactly.  Every
+ * latent tile is read once and used for both products (half the bytes of a decode that streams K
+ * and V), and the latent may be 128, 256, 512 or 576 wide (512 + 64 rotary columns); Lq <= 16.
+ * o [B, Lq, H, R] in `dtype`; lse [B, H, Lq] natural log or NULL.
+ *
+ * Replaces the `mla_fwd_absorbed` primitive (probjax/nn/pallas_kernels/kernels/
+ * latent_attention.py:204-244, 604-607) at decode time, where the reference's own split-KV rule
+ * (kernels/attention.py:2653-2689) does not reach the latent kernel.
+ */
+int pjx_mla_decode_absorbed(const void* q, const void* cache, const int32_t* kv_lengths, void* o,
+                            float* lse, int B, int Lq, int H, int R, int capacity, int dtype,
+                            float sm_scale, int split_len, void* workspace, size_t workspace_bytes,
+                            void* stream);
+size_t pjx_mla_decode_workspace_bytes(int B, int Lq, int H, int R, int capacity, int split_len);
+
+/*
  * The forward with HOST buffers: copies q, k, v (and kv_lengths, bias) to the
  * device staging area, runs pjx_attn_fwd, copies o (and lse) back, and
  * synchronises the stream before returning.  The batch is processed in chunks so

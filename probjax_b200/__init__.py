@@ -18,10 +18,12 @@ from .attention import (  # noqa: F401
     mha,
     mha_flash,
     mla,
+    mla_decode,
     splitkv_forward,
     use_splitkv,
 )
 from .cache import DecodeCache, decode_paged, linear, rope_interleaved  # noqa: F401
+from .latent_layer import MultiHeadLatentAttention, per_head_linear, rms_norm  # noqa: F401
 from .dispatch import b200_attention_or_none, device_attention_defaults  # noqa: F401
 from .masks import (  # noqa: F401
     AttentionBias,
@@ -36,19 +38,24 @@ from .masks import (  # noqa: F401
     ConstantBias,
     DenseBias,
     DistanceDecayBias,
+    IdentityBias,
     KeyPaddingMask,
     KVLenMask,
+    LearnedRelativePositionBias,
     LocalWindowMask,
     LowRankBias,
     MarginalizationMask,
     NoMask,
     NotMask,
+    PerHeadScaleBias,
     PrefixLMMask,
     QKVLengthMask,
     SameSegmentMask,
     SeqLenMask,
+    SoftCappingBias,
     SumBias,
     SymmetricAlibiBias,
+    T5RelativePositionBias,
 )
 
 __version__ = "0.1.0"

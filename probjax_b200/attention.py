@@ -425,6 +425,50 @@ def decode_forward(q, k_cache, v_cache, *, kv_lengths=None, sm_scale, split_len=
     return (o, lse) if return_lse else o
 
 
+def mla_decode(q, cache, *, kv_lengths=None, sm_scale=None, split_len=0, return_lse=False):
+    """One ``pjx_mla_decode_absorbed`` call on CUDA tensors: the decode step of absorbed latent
+    attention, ``q [B, Lq, H, R]`` over ``cache [B, S, R]`` with ``K = V = cache`` (``Lq <= 16``,
+    latent width 128 / 256 / 512 / 576, bf16 or fp16)."""
+    _require_gpu()
+    if not q.is_cuda or q.dim() != 4 or cache.dim() != 3:
+        raise ValueError("mla_decode takes CUDA tensors q [B, Lq, H, R] and cache [B, S, R]")
+    if cache.dtype != q.dtype or cache.device != q.device or cache.shape[0] != q.shape[0] or cache.shape[2] != q.shape[3]:
+        raise ValueError(f"mla_decode: cache {tuple(cache.shape)} {cache.dtype} does not match q {tuple(q.shape)} {q.dtype}")
+    if q.dtype not in _DTYPES:
+        raise ValueError(f"unsupported dtype {q.dtype}; expected float32, bfloat16 or float16")
+    dev = q.device
+    q, cache = q.contiguous(), cache.contiguous()
+    B, Lq, H, R = q.shape
+    S = cache.shape[1]
+    if sm_scale is None:
+        sm_scale = 1.0 / math.sqrt(R)
+    kvl = None if kv_lengths is None else _as_tensor(kv_lengths).to(device=dev, dtype=torch.int32).contiguous()
+    if kvl is not None and kvl.numel() != B:
+        raise ValueError(f"mla_decode: kv_lengths must hold B={B} entries, got {kvl.numel()}")
+    L = _lib.lib()
+    o = torch.empty((B, Lq, H, R), dtype=q.dtype, device=dev)
+    lse = torch.empty((B, H, Lq), dtype=torch.float32, device=dev) if return_lse else None
+    ws = _scratch_bytes(dev, "mla_decode", L.pjx_mla_decode_workspace_bytes(B, Lq, H, R, S, int(split_len)))
+    with torch.cuda.device(dev):
+        rc = L.pjx_mla_decode_absorbed(_ptr(q), _ptr(cache), _ptr(kvl), _ptr(o), _ptr(lse), B, Lq, H, R, S,
+                                       _DTYPES[q.dtype], float(sm_scale), int(split_len), _ptr(ws), ws.numel(), _stream(dev))
+    _lib.check(rc)
+    return (o, lse) if return_lse else o
+
+
+def _latent_decode_applies(q, cache, wk, lm, bt, mods) -> bool:
+    """Absorbed call that is a decode step the latent kernel takes: few query tokens, no mask but
+    key lengths, no bias; always for latents wider than the regular kernels' head widths."""
+    if wk is not None or bt is not None or mods is not None or lm.banded or lm.q_limit is not None:
+        return False
+    if q.dtype not in (torch.bfloat16, torch.float16) or cache.shape[2] not in (128, 256, 512, 576):
+        return False
+    Lq, H = q.shape[1], q.shape[2]
+    if Lq > 16 or not any(H % g == 0 for g in range(1, 16 // Lq + 1)):
+        return False
+    return cache.shape[2] > 256 or cache.shape[1] >= _SPLITKV_MIN_KV_LEN
+
+
 def combine_partials(o_parts, lse_parts, *, out_dtype=None):
     """``pjx_attn_combine``: ``o_parts [P, N, Dv]`` fp32, ``lse_parts [P, N]`` natural
     log (``+inf`` = no keys) -> ``(o [N, Dv], lse [N])``."""
@@ -811,6 +855,8 @@ def mla(q, cache, wk=None, wv=None, *, mask=None, bias=None, rng=None, sm_scale:
         out, lse = _AttentionFunction.apply(q, kmat, vmat, lm.band, lm.kv_lengths, bt, float(sm_scale), implementation,
                                             mods)
         return (out, lse) if return_lse else out
+    if _latent_decode_applies(q, cache, wk, lm, bt, mods):
+        return mla_decode(q, cache, kv_lengths=lm.kv_lengths, sm_scale=sm_scale, return_lse=return_lse)
     o = torch.empty((B, Lq, H, Dv), dtype=q.dtype, device=dev)
     lse = torch.empty((B, H, Lq), dtype=torch.float32, device=dev) if return_lse else None
     kvl = None if lm.kv_lengths is None else lm.kv_lengths.to(device=dev, dtype=torch.int32).contiguous()

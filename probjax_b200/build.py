@@ -25,6 +25,7 @@ SOURCES = [
     "attn_bwd_sm100.cu",
     "attn_fwd_sm100.cu",
     "attn_decode.cu",
+    "attn_decode_latent.cu",
     "kv_cache.cu",
     "rope.cu",
     "rmsnorm.cu",

@@ -420,6 +420,71 @@ int pjx_attn_combine(const float* o_parts, const float* lse_parts, int n_parts, 
   return launch_combine_parts(o_parts, lse_parts, n_parts, n_rows, Dv, o, lse, dtype, static_cast<cudaStream_t>(stream));
 }
 
+// Row groups of the absorbed latent decode: the largest number of heads per group that divides H
+// and keeps heads x query tokens within the 16 rows of one tensor-core operand.
+static int latent_heads_per_group(int H, int Lq) {
+  if (Lq < 1 || Lq > 16) return 0;
+  for (int g = 16 / Lq; g >= 1; --g)
+    if (H % g == 0) return g;
+  return 0;
+}
+
+static int latent_decode_split_len(int B, int groups, int capacity, int split_len) {
+  if (split_len != 0) return split_len;
+  // one CTA per SM (148): a whole number of CTAs per (sequence, row group) that fills one wave
+  const int64_t units = (int64_t)B * groups;
+  const int64_t per_unit = units >= 148 ? 1 : 148 / units;
+  int64_t len = ((capacity + per_unit - 1) / per_unit + 63) / 64 * 64;
+  if (len < 256) len = 256;
+  return (int)len;
+}
+
+size_t pjx_mla_decode_workspace_bytes(int B, int Lq, int H, int R, int capacity, int split_len) {
+  const int gh = latent_heads_per_group(H, Lq);
+  if (B < 1 || H < 1 || R < 1 || capacity < 1 || gh == 0) return 0;
+  const int groups = H / gh;
+  const int len = latent_decode_split_len(B, groups, capacity, split_len);
+  if (len < 64 || len % 64) return 0;
+  const size_t ns = ((size_t)capacity + len - 1) / len;
+  const size_t parts = (size_t)B * groups * ns * gh * Lq;
+  return align_up(parts * R * sizeof(float)) + align_up(parts * sizeof(float));
+}
+
+int pjx_mla_decode_absorbed(const void* q, const void* cache, const int32_t* kv_lengths, void* o, float* lse, int B,
+                            int Lq, int H, int R, int capacity, int dtype, float sm_scale, int split_len,
+                            void* workspace, size_t workspace_bytes, void* stream) {
+  if (B < 0 || Lq < 0 || H < 1 || R < 1 || capacity < 0) return fail(PJX_ERR_BAD_ARG, "mla decode: bad dimension");
+  int rc = decode_limits(B, H, capacity);
+  if (rc) return rc;
+  if (B == 0 || Lq == 0) return PJX_OK;
+  if (!q || !cache || !o) return fail(PJX_ERR_BAD_ARG, "mla decode: null buffer");
+  const int gh = latent_heads_per_group(H, Lq);
+  const bool aligned = ((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(cache)) & 15) == 0;
+  if (gh == 0 || !decode_latent_supported(R, dtype) || !aligned || capacity == 0)
+    return fail(PJX_ERR_UNSUPPORTED,
+                "the absorbed latent decode takes bf16/fp16, a latent width of 128, 256, 512 or 576, at most 16 query "
+                "tokens, a non-empty cache and 16-byte aligned q / cache");
+  DecodeParams p;
+  p.q = q; p.k = cache; p.v = cache; p.kv_lengths = kv_lengths; p.o = o; p.lse = lse;
+  p.B = B; p.Lq = Lq; p.Hq = H; p.Hkv = H / gh; p.D = R; p.Dv = R; p.capacity = capacity;
+  p.rows = gh * Lq;
+  p.sm_scale = sm_scale;
+  p.o_is_f32 = 0;
+  p.split_len = latent_decode_split_len(B, p.Hkv, capacity, split_len);
+  if (p.split_len < 64 || p.split_len % 64 != 0)
+    return fail(PJX_ERR_BAD_ARG, "split_len must be a positive multiple of 64 (got %d)", p.split_len);
+  p.num_splits = (capacity + p.split_len - 1) / p.split_len;
+  const size_t need = pjx_mla_decode_workspace_bytes(B, Lq, H, R, capacity, p.split_len);
+  if (!workspace || workspace_bytes < need)
+    return fail(PJX_ERR_WORKSPACE, "mla decode workspace: need %zu bytes, got %zu", need, workspace ? workspace_bytes : (size_t)0);
+  const size_t parts = (size_t)B * p.Hkv * p.num_splits * p.rows;
+  p.o_part = static_cast<float*>(workspace);
+  p.lse_part = reinterpret_cast<float*>(static_cast<char*>(workspace) + align_up(parts * R * sizeof(float)));
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if ((rc = launch_decode_latent_splits(p, dtype, st))) return rc;
+  return launch_decode_combine(p, dtype, st);
+}
+
 size_t pjx_mla_workspace_bytes(int B, int S, int H, int Dqk, int Dv, int R, int dtype, int has_projections) {
   (void)R;
   if (!has_projections) return 0;

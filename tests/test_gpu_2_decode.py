@@ -390,3 +390,34 @@ def test_paged_cache_decode_equals_contiguous_decode(dtype, d, page):
     with pytest.raises(ValueError, match="multiple of 64"):
         pj.decode_paged(q.to(dev()), k_pool[:, :48].contiguous().to(dev()), v_pool[:, :48].contiguous().to(dev()),
                         perm.to(torch.int32), lens, sm_scale=sc)
+
+
+@pytest.mark.parametrize("R,H,Lq,dtype", [(576, 16, 1, torch.bfloat16), (512, 16, 1, torch.float16), (576, 8, 2, torch.bfloat16),
+                                          (256, 5, 3, torch.bfloat16), (128, 32, 1, torch.bfloat16), (576, 6, 4, torch.float16)])
+def test_absorbed_latent_decode(R, H, Lq, dtype):
+    """Decode step of absorbed latent attention (K = V = latent) at real latent widths, ragged
+    lengths and a cache tail full of NaN: every row against the oracle's absorbed form
+    (latent_attention.py:604-607), through ``mla`` (routing) and the raw call (several split lengths)."""
+    d = dev()
+    B, S = 5, 1500
+    q = randn((B, Lq, H, R), dtype, 1)
+    cache = (randn((B, S, R), torch.float32, 2) * 0.5).to(dtype)
+    lens = torch.tensor([1500, 1, 777, 64, 0], dtype=torch.int32)
+    sc = 1 / math.sqrt(R)
+    shared = cache[:, :, None, :]
+    want, want_lse = oracle.xla_attention(q, shared, shared, kv_lengths=lens, sm_scale=sc, return_lse=True)
+    poisoned = cache.clone()
+    for b in range(B):
+        poisoned[b, int(lens[b]):] = float("nan")
+    got, lse = pj.mla(q.to(d), poisoned.to(d), mask=pj.KVLenMask(lens), sm_scale=sc, return_lse=True)
+    assert_close(got, lse, want, want_lse, dtype, f"absorbed latent decode R={R} H={H} Lq={Lq}")
+    for split_len in (64, 256, 1536):
+        got2, lse2 = pj.mla_decode(q.to(d), poisoned.to(d), kv_lengths=lens.to(d), sm_scale=sc, split_len=split_len,
+                                   return_lse=True)
+        assert_close(got2, lse2, want, want_lse, dtype, f"split_len {split_len}")
+    # no lengths: the whole cache
+    got3 = pj.mla_decode(q.to(d), cache.to(d), sm_scale=sc)
+    want3 = oracle.xla_attention(q, shared, shared, sm_scale=sc)
+    assert_close(got3, None, want3, None, dtype, "whole cache")
+    again = pj.mla_decode(q.to(d), cache.to(d), sm_scale=sc)
+    assert torch.equal(got3, again)  # bit-repeatable
