@@ -471,7 +471,7 @@ def main():
             extras["latent"] = bench_extra(
                 "c5", lambda: pj.mla(q5, ch5, wk5, wv5, mask=pj.CausalMask(), sm_scale=c5["sm_scale"]), xs, xw,
                 fl5 / 1e12, "TFLOP/s", pk["bf16_tflops"], "tensor", pk["source"],
-                "profiles/attn_fwd_sm100_latent_b2_s2048.md")
+                "profiles/attn_fwd_sm100_latent_b4_s2048.md")
             del q5, ch5
         except Exception as e:
             extras["latent"] = {"error": str(e)[:300]}
