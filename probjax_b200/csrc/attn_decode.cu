@@ -51,28 +51,17 @@ __device__ __forceinline__ uint4 ld_volatile_v4(const uint4* p) {
   return v;
 }
 
-// FUSED (sequence-sharded decode, whole grid co-resident): the last CTA of each (batch, kv
-// head) to finish combines the head's splits, stores the rank's partial into every rank's
-// exchange buffer, raises the head's flag there, waits (bounded) for the same head's flags of
-// all ranks and writes the final result -- the whole exchange inside this one launch.
-template <typename T, int HD, bool PAGED, bool FUSED>
-__global__ void __launch_bounds__(NTHR, 2) decode_splitkv_kernel(const DecodeParams p) {
+// Streams keys [start, end) of (batch b, kv head hk) and writes the partial result -- O normalised by
+// its own sum and a base-2 LSE per packed query row -- at row offset `part` of the partial arrays.
+// Every thread of the CTA takes part; on return the shared memory is free again.
+template <typename T, int HD, bool PAGED>
+__device__ __forceinline__ void stream_segment(const DecodeParams& p, unsigned char* smem_raw, int b, int hk, int start,
+                                               int end, int64_t part) {
   constexpr int CH = HD / 8;               // 16-byte chunks per row
   constexpr int TILE_BYTES = BK * HD * 2;  // one K or V tile
   constexpr int KS = HD / 16;              // k-steps of the score product
   constexpr int NT_O = HD / 8;             // output n-tiles
-  extern __shared__ __align__(128) unsigned char smem_raw[];
-
-  const int split = blockIdx.x, hk = blockIdx.y, b = blockIdx.z;
-  int len = p.capacity;
-  if (p.kv_lengths) len = max(0, min(len, p.kv_lengths[b]));
-  const int start = split * p.split_len;
-  // nothing to do; the combine never reads this split (in the fused exchange split 0 always
-  // runs, so that a head without keys still publishes its empty partial)
-  if (start >= len && !(FUSED && split == 0)) return;
-  const int end = min(len, start + p.split_len);
   const int n_tiles = max(0, (end - start + BK - 1) / BK);
-
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int G = p.Hq / p.Hkv;
   // contiguous cache: the sequence's rows; paged cache: the pool (rows are found per tile)
@@ -266,7 +255,6 @@ __global__ void __launch_bounds__(NTHR, 2) decode_splitkv_kernel(const DecodePar
   }
   __syncthreads();
 
-  const int64_t part = (((int64_t)b * p.Hkv + hk) * p.num_splits + split) * p.rows;
   for (int idx = tid; idx < p.rows * HD; idx += NTHR) {
     const int r = idx / HD, d = idx % HD;
     float mall = -INFINITY;
@@ -283,6 +271,29 @@ __global__ void __launch_bounds__(NTHR, 2) decode_splitkv_kernel(const DecodePar
     p.o_part[(part + r) * HD + d] = lall > 0.f ? o / lall : 0.f;
     if (d == 0) p.lse_part[part + r] = lall > 0.f ? mall + log2f(lall) : -INFINITY;
   }
+
+  __syncthreads();  // the merge scratch is shared memory the next segment's tiles will land in
+}
+
+// FUSED (sequence-sharded decode, whole grid co-resident): the last CTA of each (batch, kv
+// head) to finish combines the head's splits, stores the rank's partial into every rank's
+// exchange buffer, raises the head's flag there, waits (bounded) for the same head's flags of
+// all ranks and writes the final result -- the whole exchange inside this one launch.
+template <typename T, int HD, bool PAGED, bool FUSED>
+__global__ void __launch_bounds__(NTHR, 2) decode_splitkv_kernel(const DecodeParams p) {
+  extern __shared__ __align__(128) unsigned char smem_raw[];
+  const int split = blockIdx.x, hk = blockIdx.y, b = blockIdx.z;
+  int len = p.capacity;
+  if (p.kv_lengths) len = max(0, min(len, p.kv_lengths[b]));
+  const int start = split * p.split_len;
+  // nothing to do; the combine never reads this split (in the fused exchange split 0 always
+  // runs, so that a head without keys still publishes its empty partial)
+  if (start >= len && !(FUSED && split == 0)) return;
+  const int end = min(len, start + p.split_len);
+  stream_segment<T, HD, PAGED>(p, smem_raw, b, hk, start, end,
+                               (((int64_t)b * p.Hkv + hk) * p.num_splits + split) * p.rows);
+  [[maybe_unused]] const int tid = threadIdx.x;
+  [[maybe_unused]] const int G = p.Hq / p.Hkv;
 
   if constexpr (FUSED) {
     // Exchange in "data + flag" words (the low-latency protocol collectives libraries use for small
@@ -773,7 +784,7 @@ int pjx_attn_decode_splitkv_static(const void* q, const void* k_cache, const voi
   if (!decode_fast_supported(p, dtype) || !aligned || capacity == 0)
     return fail(PJX_ERR_UNSUPPORTED,
                 "the allocation-free decode takes bf16/fp16, D = Dv in {64,128}, (Hq/Hkv)*Lq <= 16, capacity > 0 and 16-byte aligned q/k/v");
-  if (split_len == 0) split_len = pjx_attn_decode_default_split_len(B, Hkv, capacity);
+  if (split_len == 0) split_len = decode_default_split_len(B, Hkv, capacity, kv_lengths != nullptr);
   if (split_len < 64 || split_len % 64 != 0)
     return fail(PJX_ERR_BAD_ARG, "split_len must be a positive multiple of 64 (got %d)", split_len);
   p.split_len = split_len;

@@ -108,6 +108,39 @@ int host_pipe(HostPipe** out) {
 }
 
 }  // namespace
+
+// Split length for split_len = 0.  Measured on B200 (B=16, Hkv=8, caches of 4k..32k keys, two CTAs per
+// SM = 296 slots):
+//  * all sequences full (no lengths given): a whole number of CTAs per (sequence, kv head) that fits ONE
+//    wave streams fastest at every cache length (32k keys: 16384-key splits 7.08 TB/s, 4096-key splits
+//    6.69; a partly filled last wave costs 5-6 %, and the idle 13 % of the slots cost nothing, the kernel
+//    being bound by HBM);
+//  * lengths given: sequences may be ragged, and then a CTA that owns a long split of a long sequence
+//    is the straggler (one CTA cannot pull much more than its fair share of the bandwidth): splits of about
+//    4096 keys in several waves balance best (ragged 1k..32k: 6.47 TB/s against 5.0 with 16384-key splits);
+//  * small problems (fewer keys than one wave of 2048-key CTAs): one wave either way.
+int decode_default_split_len(int B, int Hkv, int capacity, bool ragged) {
+  if (B < 1 || Hkv < 1 || capacity < 1) return 64;
+  const double total = (double)B * Hkv * capacity;
+  const double slots = 148.0 * 2;
+  const double len_fill = total / slots;
+  const long units = (long)B * Hkv;
+  double len;
+  if (units <= (long)slots && (!ragged || len_fill < 2048.0)) {
+    const long per_unit = (long)slots / units;  // >= 1
+    len = (double)((capacity + per_unit - 1) / per_unit);
+  } else {
+    const double len_waves = total / (slots * 3.5);
+    len = len_fill < 2048.0 ? len_fill : 2048.0;
+    if (len_waves > len) len = len_waves;
+  }
+  long l64 = ((long)len + 63) / 64 * 64;
+  if (l64 < 256) l64 = 256;
+  const long cap64 = ((long)capacity + 63) / 64 * 64;
+  if (l64 > cap64) l64 = cap64;
+  return (int)l64;
+}
+
 }  // namespace pjx
 
 using namespace pjx;
@@ -210,27 +243,7 @@ int pjx_linear_strided(const void* x, int64_t x_row_pitch, const void* w, void* 
 }
 
 int pjx_attn_decode_default_split_len(int B, int Hkv, int capacity) {
-  // Measured on B200 (B=16, Hkv=8, caches of 4k..32k keys): CTAs that stream at least
-  // ~2048 keys amortise their pipeline fill and merge; more than ~3.5 waves of the 296
-  // CTA slots (2 per SM) buys nothing. Small problems get a whole number of CTAs per
-  // (batch, kv head) that fits one wave: a partial second wave costs more than the idle slots.
-  if (B < 1 || Hkv < 1 || capacity < 1) return 64;
-  const double total = (double)B * Hkv * capacity;
-  const double slots = 148.0 * 2;
-  const double len_fill = total / slots;
-  const double len_waves = total / (slots * 3.5);
-  double len = len_fill < 2048.0 ? len_fill : 2048.0;
-  if (len_waves > len) len = len_waves;
-  const long units = (long)B * Hkv;
-  if (len_fill < 2048.0 && units <= (long)slots) {
-    const long per_unit = (long)slots / units;  // >= 1
-    len = (double)((capacity + per_unit - 1) / per_unit);
-  }
-  long l64 = ((long)len + 63) / 64 * 64;
-  if (l64 < 256) l64 = 256;
-  const long cap64 = ((long)capacity + 63) / 64 * 64;
-  if (l64 > cap64) l64 = cap64;
-  return (int)l64;
+  return decode_default_split_len(B, Hkv, capacity, true);
 }
 
 // Limits every decode entry point shares: index arithmetic in int and a (split, kv head, batch) grid.
@@ -241,8 +254,9 @@ static int decode_limits(int B, int Hkv, int capacity) {
   return PJX_OK;
 }
 
-static int decode_geometry(int B, int Hkv, int capacity, int split_len, int* out_len, int* out_splits) {
-  if (split_len == 0) split_len = pjx_attn_decode_default_split_len(B, Hkv, capacity);
+static int decode_geometry(int B, int Hkv, int capacity, int split_len, int* out_len, int* out_splits,
+                           bool ragged = true) {
+  if (split_len == 0) split_len = decode_default_split_len(B, Hkv, capacity, ragged);
   if (split_len < 64 || split_len % 64 != 0)
     return fail(PJX_ERR_BAD_ARG, "split_len must be a positive multiple of 64 (got %d)", split_len);
   *out_len = split_len;
@@ -250,13 +264,37 @@ static int decode_geometry(int B, int Hkv, int capacity, int split_len, int* out
   return PJX_OK;
 }
 
-size_t pjx_attn_decode_workspace_bytes(int B, int Lq, int Hq, int Hkv, int Dv, int capacity, int split_len) {
-  int len, ns;
-  if (B < 1 || Hkv < 1 || Hq < 1 || Lq < 1 || Dv < 1 || Hq % Hkv) return 0;
-  if (decode_geometry(B, Hkv, capacity, split_len, &len, &ns)) return 0;
-  const size_t rows = (size_t)(Hq / Hkv) * Lq;
-  const size_t parts = (size_t)B * Hkv * ns * rows;
+static size_t decode_partial_bytes(size_t parts, int Dv) {
   return align_up(parts * Dv * sizeof(float)) + align_up(parts * sizeof(float));
+}
+
+size_t pjx_attn_decode_workspace_bytes(int B, int Lq, int Hq, int Hkv, int Dv, int capacity, int split_len) {
+  if (B < 1 || Hkv < 1 || Hq < 1 || Lq < 1 || Dv < 1 || Hq % Hkv) return 0;
+  const size_t rows = (size_t)(Hq / Hkv) * Lq;
+  size_t need = 0;
+  for (int ragged = 0; ragged < 2; ++ragged) {  // split_len = 0: enough for either default
+    int len, ns;
+    if (decode_geometry(B, Hkv, capacity, split_len, &len, &ns, ragged != 0)) return 0;
+    const size_t n = decode_partial_bytes((size_t)B * Hkv * ns * rows, Dv);
+    if (n > need) need = n;
+  }
+  return need;
+}
+
+// Points p at its partial arrays in `workspace` for fixed splits of `split_len` keys (0 = choose).
+static int decode_place_partials(DecodeParams& p, int dtype, int split_len, void* workspace, size_t workspace_bytes,
+                                 bool allow_flat) {
+  (void)dtype; (void)allow_flat;
+  int rc;
+  if ((rc = decode_geometry(p.B, p.Hkv, p.capacity, split_len, &p.split_len, &p.num_splits, p.kv_lengths != nullptr)))
+    return rc;
+  const size_t parts = (size_t)p.B * p.Hkv * p.num_splits * p.rows;
+  const size_t need = decode_partial_bytes(parts, p.Dv);
+  if (!workspace || workspace_bytes < need)
+    return fail(PJX_ERR_WORKSPACE, "decode workspace: need %zu bytes, got %zu", need, workspace ? workspace_bytes : (size_t)0);
+  p.o_part = static_cast<float*>(workspace);
+  p.lse_part = reinterpret_cast<float*>(static_cast<char*>(workspace) + align_up(parts * p.Dv * sizeof(float)));
+  return PJX_OK;
 }
 
 int pjx_attn_decode_splitkv(const void* q, const void* k_cache, const void* v_cache, const int32_t* kv_lengths,
@@ -284,13 +322,7 @@ int pjx_attn_decode_splitkv(const void* q, const void* k_cache, const void* v_ca
     return pjx_attn_fwd(q, k_cache, v_cache, o, lse, kv_lengths, nullptr, 0, 0, B, Lq, capacity, Hq, Hkv, D, Dv,
                         dtype, 0, sm_scale, PJX_IMPL_GENERIC, nullptr, stream);
   }
-  if ((rc = decode_geometry(B, Hkv, capacity, split_len, &p.split_len, &p.num_splits))) return rc;
-  const size_t need = pjx_attn_decode_workspace_bytes(B, Lq, Hq, Hkv, Dv, capacity, p.split_len);
-  if (!workspace || workspace_bytes < need)
-    return fail(PJX_ERR_WORKSPACE, "decode workspace: need %zu bytes, got %zu", need, workspace ? workspace_bytes : (size_t)0);
-  const size_t parts = (size_t)B * Hkv * p.num_splits * p.rows;
-  p.o_part = static_cast<float*>(workspace);
-  p.lse_part = reinterpret_cast<float*>(static_cast<char*>(workspace) + align_up(parts * Dv * sizeof(float)));
+  if ((rc = decode_place_partials(p, dtype, split_len, workspace, workspace_bytes, true))) return rc;
   return launch_decode(p, dtype, st);
 }
 
@@ -320,13 +352,7 @@ int pjx_attn_decode_paged(const void* q, const void* k_pool, const void* v_pool,
   if (!decode_fast_supported(p, dtype) || !aligned || capacity == 0)
     return fail(PJX_ERR_UNSUPPORTED,
                 "the paged decode takes bf16/fp16, D = Dv in {64,128}, (Hq/Hkv)*Lq <= 16, at least one page and 16-byte aligned q/k/v");
-  if ((rc = decode_geometry(B, Hkv, capacity, split_len, &p.split_len, &p.num_splits))) return rc;
-  const size_t need = pjx_attn_decode_workspace_bytes(B, Lq, Hq, Hkv, Dv, capacity, p.split_len);
-  if (!workspace || workspace_bytes < need)
-    return fail(PJX_ERR_WORKSPACE, "decode workspace: need %zu bytes, got %zu", need, workspace ? workspace_bytes : (size_t)0);
-  const size_t parts = (size_t)B * Hkv * p.num_splits * p.rows;
-  p.o_part = static_cast<float*>(workspace);
-  p.lse_part = reinterpret_cast<float*>(static_cast<char*>(workspace) + align_up(parts * Dv * sizeof(float)));
+  if ((rc = decode_place_partials(p, dtype, split_len, workspace, workspace_bytes, true))) return rc;
   return launch_decode(p, dtype, static_cast<cudaStream_t>(stream));
 }
 

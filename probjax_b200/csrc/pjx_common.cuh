@@ -167,6 +167,8 @@ bool bwd_sm100_supported(const BwdParams& p, const char** why);
 int launch_bwd_sm100(const BwdParams& p, cudaStream_t stream);
 bool decode_fast_supported(const DecodeParams& p, int dtype);
 int launch_decode(const DecodeParams& p, int dtype, cudaStream_t stream);
+// Split length chosen for split_len = 0; `ragged`: per-sequence lengths are given (see pjx_api.cu).
+int decode_default_split_len(int B, int Hkv, int capacity, bool ragged);
 // CTAs of the split-KV kernel (dtype, head width D) that the current device holds at once.
 int decode_coresident_ctas(int dtype, int D, int* out);
 int launch_decode_combine(const DecodeParams& p, int dtype, cudaStream_t stream);
