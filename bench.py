@@ -693,8 +693,8 @@ def long_context_decode_bench(dev, rank, world, steps, warmup, pk, dist_on, cont
             del ref
         else:
 
-            def fn():
-                return pj.decode_forward(q, k, v, kv_lengths=ll, sm_scale=sc, return_lse=True)
+            def fn():  # every sequence is full: no lengths
+                return pj.decode_forward(q, k, v, sm_scale=sc, return_lse=True)
 
         if dist_on:
             del k_all, v_all

@@ -843,13 +843,15 @@ def mla(q, cache, wk=None, wv=None, *, mask=None, bias=None, rng=None, sm_scale:
         raise ValueError("q, cache, wk and wv must share a dtype")
     if _wants_grad(q, cache, wk, wv):
         # Differentiation goes through the materialized K and V and the regular attention kernels, as
-        # in the reference (latent_attention.py:554-585); the up-projections and their gradients are
-        # plain library matrix products here.
+        # in the reference (latent_attention.py:554-585); the up-projections and their gradients run
+        # on the projection kernel (pjx_linear) as well.
         if lm.q_limit is not None:
             raise NotImplementedError("gradients under a query-length mask are not implemented")
         if wk is not None:
-            kmat = torch.matmul(cache, wk.reshape(H * Dqk, R).t()).view(B, S, H, Dqk)
-            vmat = torch.matmul(cache, wv.reshape(H * Dv, R).t()).view(B, S, H, Dv)
+            from .cache import linear_autograd
+
+            kmat = linear_autograd(cache, wk.reshape(H * Dqk, R)).view(B, S, H, Dqk)
+            vmat = linear_autograd(cache, wv.reshape(H * Dv, R)).view(B, S, H, Dv)
         else:
             kmat = vmat = cache[:, :, None, :]  # one shared KV head
         out, lse = _AttentionFunction.apply(q, kmat, vmat, lm.band, lm.kv_lengths, bt, float(sm_scale), implementation,

@@ -132,6 +132,33 @@ def linear(x: torch.Tensor, weight: torch.Tensor, *, implementation: str | None 
     return y.view(*x.shape[:-1], w.shape[0])
 
 
+class _LinearFunction(torch.autograd.Function):
+    """``linear`` with its gradients computed by the same kernel: ``dx = dy . w`` and ``dw = dy^T . x`` are
+    again products of the ``A . B^T`` form once the second operand is transposed (a copy)."""
+
+    @staticmethod
+    def forward(ctx, x, weight):
+        ctx.save_for_backward(x, weight)
+        return linear(x, weight)
+
+    @staticmethod
+    def backward(ctx, dy):
+        x, weight = ctx.saved_tensors
+        dx = dw = None
+        dy2 = dy.reshape(-1, dy.shape[-1]).to(x.dtype)
+        if ctx.needs_input_grad[0]:
+            dx = linear(dy2, weight.t().contiguous()).reshape(x.shape)          # [M, N] . [K, N]^T
+        if ctx.needs_input_grad[1]:
+            x2 = x.reshape(-1, x.shape[-1])
+            dw = linear(dy2.t().contiguous(), x2.t().contiguous())              # [N, M] . [K, M]^T
+        return dx, dw
+
+
+def linear_autograd(x: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:
+    """:func:`linear` that records itself for reverse-mode differentiation (both gradients on ``pjx_linear``)."""
+    return _LinearFunction.apply(x, weight)
+
+
 def decode_paged(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, block_table: torch.Tensor, kv_lengths,
                  *, sm_scale: float | None = None, split_len: int = 0, return_lse: bool = False):
     """Split-KV decode over a paged cache (``pjx_attn_decode_paged``): ``k_pool`` / ``v_pool``

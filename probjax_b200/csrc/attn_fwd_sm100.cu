@@ -27,6 +27,8 @@
 // Every barrier wait is bounded: on expiry the role raises the CTA abort flag,
 // all roles drain, tensor memory is freed and the status word gets
 // PJX_ERR_DEVICE_TIMEOUT.
+#include <cstdlib>
+
 #include "pjx_common.cuh"
 #include "sm100_ptx.cuh"
 
@@ -738,7 +740,7 @@ int launch_one(const FwdParams& p, int dtype, cudaStream_t stream) {
   dim3 grid((unsigned)(((p.Lq + 2 * BM - 1) / (2 * BM)) * (int64_t)p.Hq * p.B));
   // triangular work (an upper bound on the keys only): heavy-first order in blocks of 16 pairs
   int order_w = (p.band_hi < PJX_BAND_NO_UPPER && p.band_lo == PJX_BAND_NO_LOWER) ? 16 : 1;
-  if (BIAS != 0 && p.bias_bs == 0 && p.B > 1) order_w = 0;  // batch-fastest: the batch shares the bias tiles
+  if (BIAS != 0 && p.bias_bs == 0 && p.B > 1 && getenv("PJX_BIAS_ORDER")) order_w = 0;  // experiment
   kern<<<grid, NTHREADS, C::SMEM_BYTES, stream>>>(tq, tk, tv, tb, to, p, order_w);
   count_launch();
   return check_cuda(cudaGetLastError(), "sm100 forward launch");
