@@ -119,18 +119,31 @@ __global__ void __launch_bounds__(LTHR, 1) decode_latent_kernel(const DecodePara
     const int key0 = start + t * LBK;
 
     // ---- 1. scores of keys 8 warp .. 8 warp + 7 ----
-    float s[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll 4
-    for (int kp = 0; kp < R / 32; ++kp) {  // two 16-wide steps per iteration
-      uint32_t b0, b1, b2, b3;
-      ldsm_x4(tile + lswz(warp * 8 + (lane & 7), kp * 4 + (lane >> 3), C::ROW_BYTES), b0, b1, b2, b3);
-      uint32_t a[4], a2[4];
-      const int arow = ((lane >> 3) & 1) * 8 + (lane & 7);
-      ldsm_x4(sbase + C::OFF_Q + lswz(arow, kp * 4 + (lane >> 4), C::ROW_BYTES), a[0], a[1], a[2], a[3]);
-      ldsm_x4(sbase + C::OFF_Q + lswz(arow, kp * 4 + 2 + (lane >> 4), C::ROW_BYTES), a2[0], a2[1], a2[2], a2[3]);
-      mma16816<T>(s, a, b0, b1);
-      mma16816<T>(s, a2, b2, b3);
+    // four independent accumulators: one chain of R / 16 dependent tensor-core steps would run at the
+    // latency of a step, not at its issue rate
+    float sa[4][4];
+#pragma unroll
+    for (int c = 0; c < 4; ++c)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) sa[c][e] = 0.f;
+    const int arow = ((lane >> 3) & 1) * 8 + (lane & 7);
+    static_assert((R / 32) % 2 == 0, "the score loop takes four 16-wide steps per iteration");
+#pragma unroll 2
+    for (int kp = 0; kp < R / 32; kp += 2) {  // four 16-wide steps per iteration, one per accumulator
+#pragma unroll
+      for (int u = 0; u < 2; ++u) {
+        uint32_t b0, b1, b2, b3;
+        ldsm_x4(tile + lswz(warp * 8 + (lane & 7), (kp + u) * 4 + (lane >> 3), C::ROW_BYTES), b0, b1, b2, b3);
+        uint32_t a[4], a2[4];
+        ldsm_x4(sbase + C::OFF_Q + lswz(arow, (kp + u) * 4 + (lane >> 4), C::ROW_BYTES), a[0], a[1], a[2], a[3]);
+        ldsm_x4(sbase + C::OFF_Q + lswz(arow, (kp + u) * 4 + 2 + (lane >> 4), C::ROW_BYTES), a2[0], a2[1], a2[2], a2[3]);
+        mma16816<T>(sa[2 * u], a, b0, b1);
+        mma16816<T>(sa[2 * u + 1], a2, b2, b3);
+      }
     }
+    float s[4];
+#pragma unroll
+    for (int e = 0; e < 4; ++e) s[e] = (sa[0][e] + sa[1][e]) + (sa[2][e] + sa[3][e]);
     float tmax[2] = {-INFINITY, -INFINITY};
 #pragma unroll
     for (int e = 0; e < 4; ++e) {

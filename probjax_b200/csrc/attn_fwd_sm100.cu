@@ -27,8 +27,6 @@
 // Every barrier wait is bounded: on expiry the role raises the CTA abort flag,
 // all roles drain, tensor memory is freed and the status word gets
 // PJX_ERR_DEVICE_TIMEOUT.
-#include <cstdlib>
-
 #include "pjx_common.cuh"
 #include "sm100_ptx.cuh"
 
@@ -87,7 +85,7 @@ struct Cfg {
   static constexpr int BIAS_TILE_BYTES = BIAS_STAGED ? (BN / 32) * BM * 128 : 0;
   static constexpr int OFF_BIAS = OFF_V + VST * V_TILE_BYTES;
   static constexpr int OFF_BAR = OFF_BIAS + 2 * BIAS_TILE_BYTES;
-  static constexpr int N_BAR = 2 + 2 * KST + 2 * VST + 6 + 8 + 2 + 1;
+  static constexpr int N_BAR = 2 + 2 * KST + 2 * VST + 6 + 4 + 2 + 1;
   static constexpr int SMEM_BYTES = OFF_BAR + N_BAR * 8 + 16 + 1024;  // + alignment slack
   static constexpr int TMEM_USED = 2 * BN + 2 * DV;
   static constexpr int TMEM_COLS = TMEM_USED <= 128 ? 128 : (TMEM_USED <= 256 ? 256 : 512);
@@ -163,12 +161,9 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
   const int S_FULL = V_EMPTY + VST;       // [2]
   const int P_FULL = S_FULL + 2;          // [2]
   const int O_FULL = P_FULL + 2;          // [2]
-  // The staged bias tile of a query tile is handed over in two halves of 64 keys, each with its own
-  // pair of barriers: the producer refills the first half for the next KV step while the softmax
-  // threads are still working on the second half and on the exponentials of this step.
-  const int B_FULL = O_FULL + 2;          // [2 tiles][2 halves] staged bias half landed
-  const int B_EMPTY = B_FULL + 4;         // [2][2] staged bias half consumed (128 arrivals)
-  const int O_STAGED = B_EMPTY + 4;       // [2] output tile written to shared memory (128 arrivals)
+  const int B_FULL = O_FULL + 2;          // [2] staged bias tile landed
+  const int B_EMPTY = B_FULL + 2;         // [2] staged bias tile consumed (128 arrivals)
+  const int O_STAGED = B_EMPTY + 2;       // [2] output tile written to shared memory (128 arrivals)
   const int V_CLEAN = O_STAGED + 2;       // rows past the valid length cleared in the last V tile (32 arrivals)
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + C::OFF_BAR + C::N_BAR * 8);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
@@ -179,25 +174,14 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
   // block therefore start first and its short ones fill the gaps (a block of 16 pairs gets
   // within a few per cent of a global longest-first order), while the CTAs in flight still
   // share few K/V heads, which keeps their tiles in the near L2 partition.
-  // order_w == 0 (a bias shared by the batch): the batch index runs fastest, so the CTAs that need
-  // the same bias tiles run at the same time and the tiles come out of L2 for all but the first.
   const int n_bh = p.Hq * p.B;
   const int n_qt = (p.Lq + 2 * BM - 1) / (2 * BM);
-  int qt, h, b;
-  if (order_w == 0) {
-    b = blockIdx.x % p.B;
-    const int rest = blockIdx.x / p.B;
-    qt = n_qt - 1 - rest % n_qt;
-    h = rest / n_qt;
-  } else {
-    const int blk = blockIdx.x / (order_w * n_qt);
-    const int rem = blockIdx.x - blk * (order_w * n_qt);
-    const int wc = min(order_w, n_bh - blk * order_w);
-    qt = n_qt - 1 - rem / wc;
-    const int bh = blk * order_w + rem % wc;
-    h = bh % p.Hq;
-    b = bh / p.Hq;
-  }
+  const int blk = blockIdx.x / (order_w * n_qt);
+  const int rem = blockIdx.x - blk * (order_w * n_qt);
+  const int wc = min(order_w, n_bh - blk * order_w);
+  const int qt = n_qt - 1 - rem / wc;
+  const int bh = blk * order_w + rem % wc;
+  const int h = bh % p.Hq, b = bh / p.Hq;
   const int hk = h / (p.Hq / p.Hkv);
   const int q0 = qt * 2 * BM;
 
@@ -314,17 +298,13 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
 #pragma unroll
           for (int t = 0; t < 2; ++t) {
             if (j >= n_t[t]) continue;
-#pragma unroll
-            for (int hf = 0; hf < 2; ++hf) {
-              okb = okb && mbar_wait(BAR(B_EMPTY + 2 * t + hf), (j & 1) ^ 1, abort_flag);
-              if (!okb) break;
-              mbar_arrive_expect_tx(BAR(B_FULL + 2 * t + hf), C::BIAS_TILE_BYTES / 2);
-#pragma unroll
-              for (int c = hf * (BN / 64); c < (hf + 1) * (BN / 64); ++c)
-                tma_load_4d(sbase + C::OFF_BIAS + t * C::BIAS_TILE_BYTES + c * BM * 128, &tm_b, BAR(B_FULL + 2 * t + hf),
-                            (j_base + j) * BN + c * 32, q0 + t * BM, p.bias_hs ? h : 0, p.bias_bs ? b : 0);
-            }
+            okb = mbar_wait(BAR(B_EMPTY + t), (j & 1) ^ 1, abort_flag);
             if (!okb) break;
+            mbar_arrive_expect_tx(BAR(B_FULL + t), C::BIAS_TILE_BYTES);
+#pragma unroll
+            for (int c = 0; c < BN / 32; ++c)
+              tma_load_4d(sbase + C::OFF_BIAS + t * C::BIAS_TILE_BYTES + c * BM * 128, &tm_b, BAR(B_FULL + t),
+                          (j_base + j) * BN + c * 32, q0 + t * BM, p.bias_hs ? h : 0, p.bias_bs ? b : 0);
           }
           if (!okb) break;
         }
@@ -480,14 +460,12 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
         }
       }
       if constexpr (BIAS == 2) {
+        ok = mbar_wait(BAR(B_FULL + t), j & 1, abort_flag);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
         const uint32_t brow = sbase + C::OFF_BIAS + t * C::BIAS_TILE_BYTES + r_in * 128;
 #pragma unroll
         for (int c = 0; c < NCH; ++c) {
-          if (c % (NCH / 2) == 0) {  // a half of the tile begins: wait for it
-            ok = mbar_wait(BAR(B_FULL + 2 * t + c / (NCH / 2)), j & 1, abort_flag);
-            ok = __all_sync(0xffffffffu, ok);
-            if (!ok) break;
-          }
 #pragma unroll
           for (int i = 0; i < 8; ++i) {
             float4 bv;
@@ -499,9 +477,8 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
             s[c * 32 + 4 * i + 2] = fmaf(bv.z, kLog2e, s[c * 32 + 4 * i + 2] * c1);
             s[c * 32 + 4 * i + 3] = fmaf(bv.w, kLog2e, s[c * 32 + 4 * i + 3] * c1);
           }
-          if (c % (NCH / 2) == NCH / 2 - 1) mbar_arrive(BAR(B_EMPTY + 2 * t + c / (NCH / 2)));  // half consumed
         }
-        if (!ok) break;
+        mbar_arrive(BAR(B_EMPTY + t));
       } else if constexpr (BIAS == 1) {
 #pragma unroll
         for (int c = 0; c < NCH; ++c) {
@@ -739,8 +716,7 @@ int launch_one(const FwdParams& p, int dtype, cudaStream_t stream) {
     return rc;
   dim3 grid((unsigned)(((p.Lq + 2 * BM - 1) / (2 * BM)) * (int64_t)p.Hq * p.B));
   // triangular work (an upper bound on the keys only): heavy-first order in blocks of 16 pairs
-  int order_w = (p.band_hi < PJX_BAND_NO_UPPER && p.band_lo == PJX_BAND_NO_LOWER) ? 16 : 1;
-  if (BIAS != 0 && p.bias_bs == 0 && p.B > 1 && getenv("PJX_BIAS_ORDER")) order_w = 0;  // experiment
+  const int order_w = (p.band_hi < PJX_BAND_NO_UPPER && p.band_lo == PJX_BAND_NO_LOWER) ? 16 : 1;
   kern<<<grid, NTHREADS, C::SMEM_BYTES, stream>>>(tq, tk, tv, tb, to, p, order_w);
   count_launch();
   return check_cuda(cudaGetLastError(), "sm100 forward launch");
