@@ -685,7 +685,7 @@ def long_context_decode_bench(dev, rank, world, steps, warmup, pk, dist_on, cont
         ll = lens.to(dev)
         check = {}
         if dist_on:
-            fn = pjd.FusedShardedDecoder(q, k, v, lens, page=page, sm_scale=sc)
+            fn = pjd.FusedShardedDecoder(q, k, v, lens, page=page, sm_scale=sc, overlap_steps=True)
             ref = pj.decode_forward(q, k_all, v_all, kv_lengths=ll, sm_scale=sc, return_lse=True)
             o, lse = fn(return_lse=True)
             fn.check_status()
@@ -727,17 +727,19 @@ def sharded_decode_bench(c4, ref, dev, rank, world, steps, warmup, pk):
         q4 = c4["q"].to(dev)
         lens = c4["kv_lengths"]
         by = 4096.0 * float(lens.sum())
-        for mode in ("fused", "nccl", "nccl_graph"):
+        for mode in ("fused", "fused_serial", "nccl", "nccl_graph"):
             try:
-                if mode == "fused":  # peer stores + flags inside the kernels, no library collective
-                    dec = pjd.FusedShardedDecoder(q4, kl, vl, lens, page=page, sm_scale=c4["sm_scale"])
+                if mode.startswith("fused"):  # peer stores inside the kernel, no library collective; "fused" lets
+                    # a step stream its cache while the previous step's exchange drains, "fused_serial" does not
+                    dec = pjd.FusedShardedDecoder(q4, kl, vl, lens, page=page, sm_scale=c4["sm_scale"],
+                                                  overlap_steps=(mode == "fused"))
                 else:
                     dec = pjd.ShardedDecoder(q4, kl, vl, lens, page=page, sm_scale=c4["sm_scale"],
                                              use_graph=(mode == "nccl_graph"))
                 ms = max_over_ranks(time_steps(dec, steps * 5, warmup, True), True) / (steps * 5)
                 o, lse = dec(return_lse=True)
                 torch.cuda.synchronize(dev)
-                if mode == "fused":
+                if mode.startswith("fused"):
                     dec.check_status()
                 ach = by / (ms * 1e-3) / 1e9
                 out[mode] = dict({"ms": ms, "value": ach, "unit": "GB/s aggregate", "bound": "hbm",

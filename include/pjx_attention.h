@@ -300,14 +300,22 @@ size_t pjx_attn_decode_static_scratch_bytes(void);
  *                     same list.
  *   step              1, 2, 3, ... : every rank must make the same sequence of calls
  *                     with the same step numbers.
+ *   flags             0, or PJX_DECODE_OVERLAP_PREVIOUS: the one-launch form is started as a
+ *                     programmatic dependent launch and streams its cache while the kernel
+ *                     launched just before it on `stream` is still finishing (it waits for that
+ *                     kernel before it writes anything).  Set it only when that previous kernel
+ *                     does not write this call's q, caches, lengths or block table -- e.g. it is
+ *                     the previous step's call of this function, whose exchange then overlaps the
+ *                     next step's streaming.
  *   o, lse            as pjx_attn_decode_splitkv (o in `dtype`).
  */
+#define PJX_DECODE_OVERLAP_PREVIOUS 1
 int pjx_attn_decode_sharded(const void* q, const void* k_local, const void* v_local,
                             const int32_t* local_lengths, void* o, float* lse, int B, int Lq, int Hq,
                             int Hkv, int D, int Dv, int capacity_local, int dtype, float sm_scale,
                             int split_len, void* workspace, size_t workspace_bytes, int rank,
-                            int world, void* const* exchange_buffers, uint32_t step, int32_t* status,
-                            void* stream);
+                            int world, void* const* exchange_buffers, uint32_t step, int flags,
+                            int32_t* status, void* stream);
 size_t pjx_attn_decode_sharded_buffer_bytes(int B, int Lq, int Hq, int Dv, int world);
 /* The same with this rank's share of the cache held in pages (the format of
  * pjx_attn_decode_paged): k_pool / v_pool [num_pages, page_size, Hkv, D|Dv], block_table int32
@@ -319,7 +327,7 @@ int pjx_attn_decode_sharded_paged(const void* q, const void* k_pool, const void*
                                   float* lse, int B, int Lq, int Hq, int Hkv, int D, int Dv,
                                   int page_size, int max_pages, int dtype, float sm_scale,
                                   int split_len, void* workspace, size_t workspace_bytes, int rank,
-                                  int world, void* const* exchange_buffers, uint32_t step,
+                                  int world, void* const* exchange_buffers, uint32_t step, int flags,
                                   int32_t* status, void* stream);
 
 /*

@@ -67,9 +67,9 @@ SIGNATURES = {
     "pjx_attn_decode_splitkv_static": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _f, _i, _vp]),
     "pjx_attn_decode_static_scratch_bytes": (_sz, []),
     "pjx_attn_decode_sharded": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _f, _i, _vp, _sz,
-                                     _i, _i, _vp, C.c_uint32, _vp, _vp]),
+                                     _i, _i, _vp, C.c_uint32, _i, _vp, _vp]),
     "pjx_attn_decode_sharded_paged": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _i, _f, _i,
-                                           _vp, _sz, _i, _i, _vp, C.c_uint32, _vp, _vp]),
+                                           _vp, _sz, _i, _i, _vp, C.c_uint32, _i, _vp, _vp]),
     "pjx_attn_decode_sharded_buffer_bytes": (_sz, [_i, _i, _i, _i, _i]),
     "pjx_linear": (_i, [_vp, _vp, _vp, _i64, _i, _i, _i, _i, _vp, _vp]),
     "pjx_linear_strided": (_i, [_vp, _i64, _vp, _vp, _i64, _i64, _i, _i, _i, _i, _vp, _vp]),

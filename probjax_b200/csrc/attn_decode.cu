@@ -229,6 +229,11 @@ __device__ __forceinline__ void stream_segment(const DecodeParams& p, unsigned c
 
   // ---- merge the four warps ----
   cp_async_wait<0>();
+  // Overlapped launch (ex_overlap): this grid may have started while the kernel before it on the stream
+  // was still running.  Everything up to here only read this call's inputs; from here on the kernel writes
+  // memory the previous kernel may still be reading (partials, counters, exchange records), so it waits
+  // for that kernel to have completed.  Without the launch attribute the instruction does nothing.
+  if (p.ex_overlap) asm volatile("griddepcontrol.wait;\n" ::: "memory");
   __syncthreads();  // every warp is done with the ring: reuse it as fp32 scratch
   float* sm_o = reinterpret_cast<float*>(smem_raw);          // [NWARP][16][HD]
   float* sm_m = sm_o + NWARP * 16 * HD;                       // [NWARP][16]
@@ -290,6 +295,8 @@ __global__ void __launch_bounds__(NTHR, 2) decode_splitkv_kernel(const DecodePar
   // runs, so that a head without keys still publishes its empty partial)
   if (start >= len && !(FUSED && split == 0)) return;
   const int end = min(len, start + p.split_len);
+  // let the next kernel on the stream (launched with the same attribute) start as SM slots free up
+  if (FUSED && p.ex_overlap) asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");
   stream_segment<T, HD, PAGED>(p, smem_raw, b, hk, start, end,
                                (((int64_t)b * p.Hkv + hk) * p.num_splits + split) * p.rows);
   [[maybe_unused]] const int tid = threadIdx.x;
@@ -612,6 +619,21 @@ int launch_decode_t(const DecodeParams& p, cudaStream_t stream) {
                       "cudaFuncSetAttribute(decode)");
   if (rc) return rc;
   dim3 grid(p.num_splits, p.Hkv, p.B);
+  if (p.ex_fused && p.ex_overlap) {  // programmatic dependent launch: see the kernel's griddepcontrol.wait
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = dim3(NTHR);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    rc = check_cuda(cudaLaunchKernelEx(&cfg, kern, p), "decode launch (overlapped)");
+    count_launch();
+    return rc;
+  }
   kern<<<grid, NTHR, smem, stream>>>(p);
   count_launch();
   rc = check_cuda(cudaGetLastError(), "decode launch");

@@ -366,8 +366,9 @@ static int decode_sharded_impl(const void* q, const void* k_local, const void* v
                                int page_size, int max_pages, const int32_t* local_lengths, void* o, float* lse, int B,
                                int Lq, int Hq, int Hkv, int D, int Dv, int capacity_local, int dtype, float sm_scale,
                                int split_len, void* workspace, size_t workspace_bytes, int rank, int world,
-                               void* const* exchange_buffers, uint32_t step, int32_t* status, void* stream) {
+                               void* const* exchange_buffers, uint32_t step, int flags, int32_t* status, void* stream) {
   int rc = validate_common(q, k_local, v_local, o, B, Lq, capacity_local, Hq, Hkv, D, Dv, dtype);
+  if (flags & ~PJX_DECODE_OVERLAP_PREVIOUS) return fail(PJX_ERR_BAD_ARG, "unknown flag bits 0x%x", flags);
   if (rc) return rc;
   if (world < 1 || world > kMaxExchangeRanks || rank < 0 || rank >= world)
     return fail(PJX_ERR_BAD_ARG, "rank %d / world %d out of range (at most %d ranks)", rank, world, kMaxExchangeRanks);
@@ -409,6 +410,7 @@ static int decode_sharded_impl(const void* q, const void* k_local, const void* v
   int slots = 0;
   if ((rc = decode_coresident_ctas(dtype, D, &slots))) return rc;
   p.ex_fused = ((int64_t)p.num_splits * Hkv * B <= slots) && (reinterpret_cast<uintptr_t>(o) & 7) == 0;
+  p.ex_overlap = (flags & PJX_DECODE_OVERLAP_PREVIOUS) ? 1 : 0;  // only the one-launch form uses it
   for (int i = 0; i < world; ++i) p.ex_buf[i] = static_cast<unsigned char*>(exchange_buffers[i]);
   return launch_decode(p, dtype, static_cast<cudaStream_t>(stream));
 }
@@ -416,18 +418,19 @@ static int decode_sharded_impl(const void* q, const void* k_local, const void* v
 int pjx_attn_decode_sharded(const void* q, const void* k_local, const void* v_local, const int32_t* local_lengths,
                             void* o, float* lse, int B, int Lq, int Hq, int Hkv, int D, int Dv, int capacity_local,
                             int dtype, float sm_scale, int split_len, void* workspace, size_t workspace_bytes,
-                            int rank, int world, void* const* exchange_buffers, uint32_t step, int32_t* status,
-                            void* stream) {
+                            int rank, int world, void* const* exchange_buffers, uint32_t step, int flags,
+                            int32_t* status, void* stream) {
   return decode_sharded_impl(q, k_local, v_local, nullptr, 0, 0, local_lengths, o, lse, B, Lq, Hq, Hkv, D, Dv,
                              capacity_local, dtype, sm_scale, split_len, workspace, workspace_bytes, rank, world,
-                             exchange_buffers, step, status, stream);
+                             exchange_buffers, step, flags, status, stream);
 }
 
 int pjx_attn_decode_sharded_paged(const void* q, const void* k_pool, const void* v_pool, const int32_t* block_table,
                                   const int32_t* local_lengths, void* o, float* lse, int B, int Lq, int Hq, int Hkv,
                                   int D, int Dv, int page_size, int max_pages, int dtype, float sm_scale, int split_len,
                                   void* workspace, size_t workspace_bytes, int rank, int world,
-                                  void* const* exchange_buffers, uint32_t step, int32_t* status, void* stream) {
+                                  void* const* exchange_buffers, uint32_t step, int flags, int32_t* status,
+                                  void* stream) {
   if (page_size < 64 || page_size % 64 != 0)
     return fail(PJX_ERR_BAD_ARG, "page_size must be a positive multiple of 64 (got %d)", page_size);
   if (max_pages < 1 || (int64_t)max_pages * page_size >= PJX_BAND_NO_UPPER)
@@ -435,7 +438,7 @@ int pjx_attn_decode_sharded_paged(const void* q, const void* k_pool, const void*
   if (!block_table || !local_lengths) return fail(PJX_ERR_BAD_ARG, "paged decode needs a block table and key lengths");
   return decode_sharded_impl(q, k_pool, v_pool, block_table, page_size, max_pages, local_lengths, o, lse, B, Lq, Hq, Hkv,
                              D, Dv, max_pages * page_size, dtype, sm_scale, split_len, workspace, workspace_bytes, rank,
-                             world, exchange_buffers, step, status, stream);
+                             world, exchange_buffers, step, flags, status, stream);
 }
 
 int pjx_attn_combine(const float* o_parts, const float* lse_parts, int n_parts, int64_t n_rows, int Dv, void* o,

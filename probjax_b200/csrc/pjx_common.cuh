@@ -92,6 +92,7 @@ struct DecodeParams {
   //   uint4 ll[2][world][N][Dv / 2 + 1];         (one-kernel exchange: values travelling with their step number)
   int ex_world = 0, ex_rank = 0;
   int ex_fused = 0;  // 1: the split kernel's last CTA of each (batch, kv head) exchanges and combines
+  int ex_overlap = 0;  // 1 (with ex_fused): may start before the previous kernel on the stream has finished
   uint32_t ex_step = 0;
   unsigned char* ex_buf[16] = {};
   int32_t* status = nullptr;

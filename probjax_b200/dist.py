@@ -234,8 +234,12 @@ class FusedShardedDecoder:
     """
 
     def __init__(self, q, k_local, v_local, kv_lengths, *, page: int, sm_scale: float, group=None,
-                 block_table=None):
-        """``block_table`` (``int32 [B, max_pages]``) switches to a paged local cache: ``k_local`` /
+                 block_table=None, overlap_steps: bool = False):
+        """``overlap_steps``: consecutive calls are issued back to back on one stream and nothing
+        between them writes ``q``, the caches or the lengths (``PJX_DECODE_OVERLAP_PREVIOUS``): a step
+        then streams its cache while the previous step's exchange is still draining.
+
+        ``block_table`` (``int32 [B, max_pages]``) switches to a paged local cache: ``k_local`` /
         ``v_local`` are then page pools ``[num_pages, page_size, Hkv, D]`` and row ``b`` of the table
         names, in order, the pool pages that hold this rank's share of sequence ``b`` (the pool page
         size is the cache's own and must be a multiple of 64; ``page`` stays the sharding granule)."""
@@ -247,6 +251,7 @@ class FusedShardedDecoder:
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
         self.rank = dist.get_rank(group) if dist.is_initialized() else 0
         self.page, self.sm_scale = page, float(sm_scale)
+        self.flags = 1 if overlap_steps else 0
         self.q, self.k, self.v = q.contiguous(), k_local.contiguous(), v_local.contiguous()
         dev = q.device
         B, Lq, Hq, D = q.shape
@@ -299,12 +304,12 @@ class FusedShardedDecoder:
                 self.q.data_ptr(), self.k.data_ptr(), self.v.data_ptr(), self.block_table.data_ptr(),
                 self.lens.data_ptr(), self.out.data_ptr(), self.lse.data_ptr(), B, Lq, Hq, Hkv, D, Dv, self.pool_page,
                 self.block_table.shape[1], self._dt, self.sm_scale, 0, self.ws.data_ptr(), self.ws.numel(), self.rank,
-                self.world, self._ptrs, self.step, self._status.data_ptr(), stream)
+                self.world, self._ptrs, self.step, self.flags, self._status.data_ptr(), stream)
         else:
             rc = self._L.pjx_attn_decode_sharded(
                 self.q.data_ptr(), self.k.data_ptr(), self.v.data_ptr(), self.lens.data_ptr(), self.out.data_ptr(),
                 self.lse.data_ptr(), B, Lq, Hq, Hkv, D, Dv, self.cap, self._dt, self.sm_scale, 0,
-                self.ws.data_ptr(), self.ws.numel(), self.rank, self.world, self._ptrs, self.step,
+                self.ws.data_ptr(), self.ws.numel(), self.rank, self.world, self._ptrs, self.step, self.flags,
                 self._status.data_ptr(), stream)
         _lib.check(rc)
         return (self.out, self.lse) if return_lse else self.out

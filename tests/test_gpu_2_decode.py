@@ -189,7 +189,7 @@ def test_missing_peer_is_reported_not_waited_for_forever():
     status = torch.zeros(1, dtype=torch.int32, device=d)
     stream = torch.cuda.current_stream(d).cuda_stream
     rc = L.pjx_attn_decode_sharded(q.data_ptr(), k.data_ptr(), v.data_ptr(), None, o.data_ptr(), None, b, 1, hq, hkv, dd, dd,
-                                   cap, _lib.PJX_BF16, 0.1, 0, ws.data_ptr(), ws.numel(), 0, 2, ptrs, 1, status.data_ptr(), stream)
+                                   cap, _lib.PJX_BF16, 0.1, 0, ws.data_ptr(), ws.numel(), 0, 2, ptrs, 1, 0, status.data_ptr(), stream)
     assert rc == 0
     assert L.pjx_read_status(status.data_ptr(), stream) == _lib.PJX_ERR_DEVICE_TIMEOUT
     with pytest.raises(_lib.KernelTimeout):
@@ -199,7 +199,7 @@ def test_missing_peer_is_reported_not_waited_for_forever():
     mine.zero_()
     one = (ctypes.c_void_p * 1)(mine.data_ptr())
     rc = L.pjx_attn_decode_sharded(q.data_ptr(), k.data_ptr(), v.data_ptr(), None, o.data_ptr(), None, b, 1, hq, hkv, dd, dd,
-                                   cap, _lib.PJX_BF16, 0.1, 0, ws.data_ptr(), ws.numel(), 0, 1, one, 1, status.data_ptr(), stream)
+                                   cap, _lib.PJX_BF16, 0.1, 0, ws.data_ptr(), ws.numel(), 0, 1, one, 1, 0, status.data_ptr(), stream)
     assert rc == 0 and L.pjx_read_status(status.data_ptr(), stream) == 0
     want, _ = oracle_fwd(q, k, v, sm_scale=0.1)
     assert_close(o, None, want, None, torch.bfloat16, "after a timed-out exchange")
@@ -253,7 +253,7 @@ def test_sharded_decode_rank0_of_two_with_the_peer_record_prefilled():
             o.zero_()
             rc = L.pjx_attn_decode_sharded(q.data_ptr(), k0.data_ptr(), v0.data_ptr(), l0.data_ptr(), o.data_ptr(),
                                            lse.data_ptr(), B, 1, Hq, Hkv, D, D, k0.shape[1], _lib.PJX_BF16, c["sm_scale"],
-                                           split_len, ws.data_ptr(), ws.numel(), 0, 2, ptrs, step, status.data_ptr(), stream)
+                                           split_len, ws.data_ptr(), ws.numel(), 0, 2, ptrs, step, 0, status.data_ptr(), stream)
             assert rc == 0, _lib.last_error()
             assert L.pjx_read_status(status.data_ptr(), stream) == 0
             assert_close(o, lse, want, want_lse, torch.bfloat16, f"sharded rank 0 of 2, B={B} step {step}")
@@ -280,12 +280,18 @@ def test_sharded_decode_over_a_paged_local_cache():
     vp[perm.view(-1).long().to(d)] = v.view(B * mp, page, *v.shape[2:])
     dense = pjd.FusedShardedDecoder(q, k, v, c["kv_lengths"], page=page, sm_scale=c["sm_scale"])
     paged = pjd.FusedShardedDecoder(q, kp, vp, c["kv_lengths"], page=page, sm_scale=c["sm_scale"], block_table=perm)
+    # steps that may start while the previous step's kernel is still finishing (programmatic dependent launch)
+    chained = pjd.FusedShardedDecoder(q, k, v, c["kv_lengths"], page=page, sm_scale=c["sm_scale"], overlap_steps=True)
     for _ in range(2):
         o1, l1 = dense(return_lse=True)
         o2, l2 = paged(return_lse=True)
+    for _ in range(20):
+        o3, l3 = chained(return_lse=True)
     dense.check_status()
     paged.check_status()
+    chained.check_status()
     assert torch.equal(o1, o2) and torch.equal(l1, l2)
+    assert torch.equal(o1, o3) and torch.equal(l1, l3)
     want, want_lse = oracle_fwd(c["q"], c["k"], c["v"], kv_lengths=c["kv_lengths"], sm_scale=c["sm_scale"])
     assert_close(o2, l2, want, want_lse, torch.bfloat16, "paged sharded decode")
 
