@@ -143,7 +143,8 @@ template <int DQK, int DV, int BN, int KST, int VST, bool BF16, int BIAS, bool B
 __global__ void __launch_bounds__(NTHREADS, 1)
 attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                       const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_b,
-                      const __grid_constant__ CUtensorMap tm_o, const FwdParams p, const int order_w) {
+                      const __grid_constant__ CUtensorMap tm_o, const FwdParamsCore p, const int order_w,
+                      const ScoreMod smod) {
   constexpr bool HAS_BIAS = BIAS != 0;
   static_assert(!MOD || (BAND && BIAS != 2), "the modifier variant builds on the band variant without staged bias");
   using C = Cfg<DQK, DV, BN, KST, VST, BIAS == 2>;
@@ -200,8 +201,8 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
         int end = max(0, min(kv_len, min(qs + BM, p.Lq) + p.band_hi));
         int begin = max(0, qs + p.band_lo);
         if constexpr (MOD) {
-          if (p.mod.prefix_len) {  // prefix keys are visible to every row
-            const int pre = min(kv_len, p.mod.prefix_len[b]);
+          if (smod.prefix_len) {  // prefix keys are visible to every row
+            const int pre = min(kv_len, smod.prefix_len[b]);
             if (pre > 0) {
               end = max(end, pre);
               begin = 0;
@@ -414,7 +415,7 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
     ScoreModView mv = {};
     int my_seg = 0, my_limit = 0x7fffffff;
     if constexpr (MOD) {
-      mv = view_of(p.mod, b, h, p.Lq);
+      mv = view_of(smod, b, h, p.Lq);
       if (row_ok && mv.seg_q) my_seg = mv.seg_q[row];
       if (row_ok && mv.row_limit) my_limit = mv.row_limit[row];
     }
@@ -717,7 +718,7 @@ int launch_one(const FwdParams& p, int dtype, cudaStream_t stream) {
   dim3 grid((unsigned)(((p.Lq + 2 * BM - 1) / (2 * BM)) * (int64_t)p.Hq * p.B));
   // triangular work (an upper bound on the keys only): heavy-first order in blocks of 16 pairs
   const int order_w = (p.band_hi < PJX_BAND_NO_UPPER && p.band_lo == PJX_BAND_NO_LOWER) ? 16 : 1;
-  kern<<<grid, NTHREADS, C::SMEM_BYTES, stream>>>(tq, tk, tv, tb, to, p, order_w);
+  kern<<<grid, NTHREADS, C::SMEM_BYTES, stream>>>(tq, tk, tv, tb, to, static_cast<const FwdParamsCore&>(p), order_w, p.mod);
   count_launch();
   return check_cuda(cudaGetLastError(), "sm100 forward launch");
 }
