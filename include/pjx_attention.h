@@ -122,6 +122,12 @@ int pjx_attn_fwd_band(const void* q, const void* k, const void* v, void* o, floa
  *                    (SymmetricAlibiBias 2355-2372, DistanceDecayBias 2387-2406).
  *   head_scale       float32 [Hq]: score *= head_scale[h] (PerHeadScaleBias 2606).
  *   softcap          > 0: score = softcap * tanh(score / softcap) (SoftCappingBias 2564-2582).
+ *   dropout_rate,    attention dropout with the reference's counter hash (`_dropout_mask_counter`,
+ *   dropout_seed     probjax/nn/pallas_kernels/kernels/attention.py:116-148): probability (b, h, i, j) is
+ *                    dropped iff hash(seed, b, h, i, j) * 2^-32 < rate, survivors are scaled by
+ *                    1 / (1 - rate), after the row sum has been taken (497-505); the backward and the
+ *                    forward-mode entry points regenerate the same mask from the same seed.  The seed is
+ *                    the folded key of `_rng_seed_from_key` (151-159).
  *
  * "score" is sm_scale * q.k; every term is a delta on that same value and the deltas add up, as
  * SumBias 553-579 defines the sum of modifiers; the dense `bias` argument adds on top.  The
@@ -141,6 +147,8 @@ typedef struct pjx_score_mod {
   int32_t alibi_mode;
   const float* head_scale;
   float softcap;
+  float dropout_rate;
+  uint32_t dropout_seed;
 } pjx_score_mod;
 
 /* pjx_attn_fwd_band with score modifiers (mod may be NULL).  16-bit inputs with head shapes the

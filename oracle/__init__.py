@@ -22,5 +22,7 @@ from .attention_oracle import (  # noqa: F401
     materialize_kv,
     rope_interleaved,
     auto_strategy,
+    counter_dropout_scale,
+    rng_seed_from_key,
 )
 from .inputs import make_config  # noqa: F401

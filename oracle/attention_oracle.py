@@ -93,6 +93,43 @@ def dense_formula(q, k, v, *, sm_scale, keep=None, bias=None):
 # ---------------------------------------------------------------------------
 
 
+def rng_seed_from_key(key) -> int:
+    """The 32-bit seed the kernels take, folded from the words of a PRNG key as
+    ``_rng_seed_from_key`` does (probjax/nn/pallas_kernels/kernels/attention.py:151-159)."""
+    words = [int(w) & 0xFFFFFFFF for w in (key if hasattr(key, "__iter__") else [key])]
+    seed = words[0]
+    if len(words) > 1:
+        seed ^= (words[1] * 0x9E3779B9) & 0xFFFFFFFF
+        for i in range(2, len(words)):
+            seed ^= (words[i] * ((0x85EBCA6B + i) & 0xFFFFFFFF)) & 0xFFFFFFFF
+    return seed & 0xFFFFFFFF
+
+
+def counter_dropout_scale(seed: int, batch: int, heads: int, q_idx, k_idx, rate: float):
+    """Multiplier ``0`` (dropped) or ``1 / (1 - rate)`` of every probability ``[B, H, q, k]``:
+    restatement of ``_dropout_mask_counter`` (kernels/attention.py:116-148) in uint32 arithmetic,
+    and of ``drop_scale`` on the XLA path (attention_xla.py:280-305)."""
+    import numpy as np
+
+    with np.errstate(over="ignore"):
+        b = np.arange(batch, dtype=np.uint32)[:, None, None, None]
+        h = np.arange(heads, dtype=np.uint32)[None, :, None, None]
+        q = np.asarray(q_idx, dtype=np.uint32)[None, None, :, None]
+        k = np.asarray(k_idx, dtype=np.uint32)[None, None, None, :]
+        x = np.uint32(seed) ^ (b * np.uint32(0x85EBCA6B))
+        x = x ^ (h * np.uint32(0xC2B2AE35))
+        x = x ^ (q * np.uint32(0x27D4EB2F))
+        x = x ^ (k * np.uint32(0x165667B1))
+        x = x ^ (x >> np.uint32(16))
+        x = x * np.uint32(0x7FEB352D)
+        x = x ^ (x >> np.uint32(15))
+        x = x * np.uint32(0x846CA68B)
+        x = x ^ (x >> np.uint32(16))
+    u = x.astype(np.float32) * np.float32(1.0 / float(2 ** 32))
+    dropped = u < np.float32(rate)
+    return torch.from_numpy(np.where(dropped, np.float32(0.0), np.float32(1.0 / (1.0 - rate))).astype(np.float32))
+
+
 class _Mods:
     """Score modifiers on a ``[B, Hq, bq, kc]`` tile (attention_xla.py:171-279).
 
@@ -100,8 +137,9 @@ class _Mods:
     ``-inf`` (:236-246 bias, :247-273 mask, :269-271 padded keys).
     """
 
-    def __init__(self, *, causal, kv_lengths, keep, bias, q_len, kv_len, kv_pad, score_fn=None):
+    def __init__(self, *, causal, kv_lengths, keep, bias, q_len, kv_len, kv_pad, score_fn=None, dropout=None):
         self.score_fn = score_fn
+        self.dropout = dropout  # (seed, rate) of the counter-hash dropout, or None
         self.causal = bool(causal)
         self.kv_lengths = None if kv_lengths is None else _as_t(kv_lengths, torch.int64).reshape(-1)
         self.keep = None if keep is None else _as_t(keep, torch.bool)
@@ -156,6 +194,13 @@ class _Mods:
             s = torch.where(keep, s, torch.tensor(-math.inf))
         return s
 
+    def drop_scale(self, shape, q0, bq, k0, kc):
+        """attention_xla.py:280-305: per-probability multiplier of a tile, or None."""
+        if self.dropout is None:
+            return None
+        seed, rate = self.dropout
+        return counter_dropout_scale(seed, shape[0], shape[1], q0 + torch.arange(bq), k0 + torch.arange(kc), rate)
+
     def tile_is_dead(self, q0, bq, k0):
         """Static tile skipping of the tiled strategy (attention_xla.py:318-331,
         373-377): a causal tile whose first key lies past its last query."""
@@ -191,6 +236,9 @@ def _dense_forward(q5, k, v, mods, sm_scale):
     l_safe = torch.where(nonempty, l_, torch.ones_like(l_))
     p = p / l_safe[..., None]
     lse = torch.where(nonempty, m + torch.log(l_safe), torch.tensor(math.inf))
+    drop = mods.drop_scale(p.shape, 0, q_len, 0, kv_len)  # after the normaliser (attention_xla.py:14-15)
+    if drop is not None:
+        p = p * drop
     return _pv(p, v, hkv), lse
 
 
@@ -219,6 +267,9 @@ def _tiled_forward(q5, k, v, mods, sm_scale, bq, kc):
             corr = torch.exp(m - m_safe)
             p = torch.exp(s - m_safe[..., None])
             l_ = l_ * corr + p.sum(dim=-1)
+            drop = mods.drop_scale(p.shape, q0, bq, k0, kc)
+            if drop is not None:
+                p = p * drop
             o = o * corr.reshape(b, hkv, g, bq)[..., None] + _pv(p, vj, hkv)
             m = m_new
         nonempty = l_ > 0
@@ -245,6 +296,7 @@ def xla_attention(
     block_k: int | None = None,
     return_lse: bool = False,
     score_fn=None,
+    dropout=None,
 ):
     """Restatement of ``xla_attention`` (attention_xla.py:601-721), forward only.
 
@@ -253,7 +305,8 @@ def xla_attention(
     ``KVLenMask``) and/or as a dense boolean ``keep [B|1,H|1,Q,K]``; ``bias`` is
     a dense additive ``[B|1,H|1,Q,K]`` array (``DenseBias``); ``score_fn(s, q_idx, k_idx)``
     stands for a non-dense bias object: it maps the scaled scores ``s [B,Hq,q,k]`` of the
-    rows ``q_idx`` and keys ``k_idx`` to modified scores (:236-246).  Output has
+    rows ``q_idx`` and keys ``k_idx`` to modified scores (:236-246); ``dropout = (seed, rate)``
+    is the counter-hash dropout (:14-15, 280-305).  Output has
     ``q``'s dtype; the optional LSE is natural log ``[B,Hq,Lq]`` fp32 with
     ``+inf`` for rows without a valid key (:417-420).
     """
@@ -290,7 +343,7 @@ def xla_attention(
     kt, vt = to_bhtd(k, kv_pad), to_bhtd(v, kv_pad)
     mods = _Mods(
         causal=causal, kv_lengths=kv_lengths, keep=keep, bias=bias,
-        q_len=q_len, kv_len=kv_len, kv_pad=kv_pad, score_fn=score_fn,
+        q_len=q_len, kv_len=kv_len, kv_pad=kv_pad, score_fn=score_fn, dropout=dropout,
     )
     if strategy == "dense":
         o5, lse = _dense_forward(q5, kt, vt, mods, sm_scale)

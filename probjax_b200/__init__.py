@@ -19,6 +19,7 @@ from .attention import (  # noqa: F401
     mha_flash,
     mla,
     mla_decode,
+    rng_seed_from_key,
     splitkv_forward,
     use_splitkv,
 )

@@ -31,6 +31,8 @@ class ScoreMod(C.Structure):
         ("alibi_slopes", _vp), ("alibi_mode", C.c_int32),
         ("head_scale", _vp),
         ("softcap", _f),
+        ("dropout_rate", _f),
+        ("dropout_seed", C.c_uint32),
     ]
 
 

@@ -146,7 +146,8 @@ class ScoreMods:
     scale, soft cap) as device tensors plus the C struct that points at them.  Keeps the tensors
     alive for as long as the object lives."""
 
-    def __init__(self, lm: LoweredMask | None = None, lb: LoweredBias | None = None, device=None):
+    def __init__(self, lm: LoweredMask | None = None, lb: LoweredBias | None = None, device=None,
+                 dropout_rate: float = 0.0, dropout_seed: int = 0):
         import ctypes
 
         self.device = torch.device(device)
@@ -181,8 +182,12 @@ class ScoreMods:
             if lb.head_scale is not None:
                 st.head_scale = put(lb.head_scale, torch.float32).data_ptr()
             st.softcap = float(lb.softcap)
+        if not 0.0 <= dropout_rate < 1.0:
+            raise ValueError(f"dropout_rate must be in [0, 1), got {dropout_rate}")
+        st.dropout_rate = float(dropout_rate)
+        st.dropout_seed = int(dropout_seed) & 0xFFFFFFFF
         self.struct = st
-        self.active = bool(self._keep) or st.softcap > 0
+        self.active = bool(self._keep) or st.softcap > 0 or st.dropout_rate > 0
         self.nbytes = sum(t.numel() * t.element_size() for t in self._keep)
         self._ref = ctypes.byref(st)
 
@@ -540,6 +545,37 @@ def _apply_q_limit(out, lse, q_limit):
     return out, lse
 
 
+def rng_seed_from_key(rng) -> int:
+    """The 32-bit dropout seed from ``rng``: an int, or the words of a PRNG key (a sequence, array or
+    tensor of integers) folded as the reference folds them (kernels/attention.py:151-159)."""
+    if isinstance(rng, torch.Tensor):
+        rng = rng.reshape(-1).tolist()
+    elif isinstance(rng, np.ndarray):
+        rng = rng.reshape(-1).tolist()
+    words = [int(w) & 0xFFFFFFFF for w in (rng if isinstance(rng, (list, tuple)) else [rng])]
+    if not words:
+        raise ValueError("empty PRNG key")
+    seed = words[0]
+    if len(words) > 1:
+        seed ^= (words[1] * 0x9E3779B9) & 0xFFFFFFFF
+        for i in range(2, len(words)):
+            seed ^= (words[i] * ((0x85EBCA6B + i) & 0xFFFFFFFF)) & 0xFFFFFFFF
+    return seed & 0xFFFFFFFF
+
+
+def _dropout_args(rng, dropout_rate, dropout_impl):
+    """(rate, seed) of an attention call, with the reference's checks (attention_xla.py:637-641)."""
+    if not dropout_rate > 0:
+        return 0.0, 0
+    if not dropout_rate < 1:
+        raise ValueError(f"dropout_rate must be in [0, 1), got {dropout_rate}")
+    if rng is None:
+        raise ValueError("prng_key must be provided when dropout_rate>0")
+    if dropout_impl != "counter":
+        raise NotImplementedError(f"dropout_impl={dropout_impl!r}: only the counter-hash dropout runs in the kernels")
+    return float(dropout_rate), rng_seed_from_key(rng)
+
+
 def masks_DenseBias(t):
     from .masks import DenseBias
 
@@ -587,8 +623,7 @@ def mha(q, k, v, mask: AttentionMask | None = None, bias: AttentionBias | None =
     _gqa_group(q.shape[-2], k.shape[-2])
     if v.shape[-2] != k.shape[-2]:
         raise ValueError(f"key and value need the same number of heads, got {k.shape[-2]} and {v.shape[-2]}.")
-    if dropout_rate > 0:
-        raise NotImplementedError("attention dropout is not implemented by the sm_100a forward kernels")
+    drop_rate, drop_seed = _dropout_args(rng, dropout_rate, dropout_impl)
     if interpret:
         raise NotImplementedError("interpret mode belongs to the Pallas kernels; this library runs CUDA only")
     B, Lq = q.shape[0], q.shape[1]
@@ -603,9 +638,10 @@ def mha(q, k, v, mask: AttentionMask | None = None, bias: AttentionBias | None =
     bt = lb.dense
     if residual is not None:  # mask classes without a native form: their dense -inf tensor rides on the bias
         bt = lower_dense(residual, None if bt is None else masks_DenseBias(bt), B, q.shape[2], Lq, k.shape[1])
-    mods = ScoreMods(lm, lb, q.device) if (lm.structured or lb.structured) and q.is_cuda else None
-    if (lm.structured or lb.structured) and not q.is_cuda:
-        raise NotImplementedError("structured masks and score modifiers take CUDA tensors")
+    wants_mods = lm.structured or lb.structured or drop_rate > 0
+    mods = ScoreMods(lm, lb, q.device, drop_rate, drop_seed) if wants_mods and q.is_cuda else None
+    if wants_mods and not q.is_cuda:
+        raise NotImplementedError("structured masks, score modifiers and dropout take CUDA tensors")
     if _wants_grad(q, k, v, bt):
         # differentiation always runs the regular kernels (attention_splitkv.py:253-272)
         if not q.is_cuda:
@@ -654,9 +690,9 @@ def flex_attention(query, key, value, mask: AttentionMask | None = None, bias: A
     if key.shape[:-3] != batch_shape or value.shape[:-3] != batch_shape:
         raise ValueError(f"batch dimensions differ: {tuple(query.shape)}, {tuple(key.shape)}, {tuple(value.shape)}")
     q4, k4, v4 = (x.reshape((-1,) + tuple(x.shape[-3:])) for x in (query, key, value))
-    res = mha(q4, k4, v4, mask=mask, bias=bias, sm_scale=sm_scale, dropout_rate=active_dropout,
-              interpret=interpret, diff_mode=diff_mode, split_kv=split_kv, return_lse=return_lse,
-              implementation=implementation)
+    res = mha(q4, k4, v4, mask=mask, bias=bias, rng=dropout_rng, sm_scale=sm_scale, dropout_rate=active_dropout,
+              dropout_impl=dropout_impl, interpret=interpret, diff_mode=diff_mode, split_kv=split_kv,
+              return_lse=return_lse, implementation=implementation)
     out, lse = res if return_lse else (res, None)
     out = out.reshape(tuple(batch_shape) + tuple(out.shape[-3:]))
     if squeeze:
@@ -813,8 +849,7 @@ def mla(q, cache, wk=None, wv=None, *, mask=None, bias=None, rng=None, sm_scale:
         raise ValueError(f"wk must be {(H, Dqk, R)}, got {tuple(wk.shape)}")
     if wv is not None and (wv.shape[0] != H or wv.shape[2] != R):
         raise ValueError(f"wv must be [heads, v_head_dim, {R}], got {tuple(wv.shape)}")
-    if dropout_rate > 0:
-        raise NotImplementedError("attention dropout is not implemented by the sm_100a forward kernels")
+    drop_rate, drop_seed = _dropout_args(rng, dropout_rate, dropout_impl)
     if interpret:
         raise NotImplementedError("interpret mode belongs to the Pallas kernels; this library runs CUDA only")
     if sm_scale is None:
@@ -835,7 +870,7 @@ def mla(q, cache, wk=None, wv=None, *, mask=None, bias=None, rng=None, sm_scale:
     bt = lb.dense
     if residual is not None:
         bt = lower_dense(residual, None if bt is None else masks_DenseBias(bt), B, H, Lq, S)
-    mods = ScoreMods(lm, lb, dev) if (lm.structured or lb.structured) else None
+    mods = ScoreMods(lm, lb, dev, drop_rate, drop_seed) if (lm.structured or lb.structured or drop_rate > 0) else None
     q, cache = q.contiguous(), cache.contiguous()
     wk = None if wk is None else wk.to(dev).contiguous()
     wv = None if wv is None else wv.to(dev).contiguous()

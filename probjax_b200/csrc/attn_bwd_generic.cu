@@ -133,8 +133,11 @@ __device__ __forceinline__ void tile_p_ds(const BwdParams& p, const Tiles& t, in
       if (bias && qi < p.Lq && kj < p.Lkv) x += bias[(int64_t)qi * p.Lkv + kj];
       keep = keep && qi < p.Lq && kj < kv_len && lse != INFINITY;
       const float pr = keep ? exp2f((x - lse) * kLog2e) : 0.f;
-      t.Ps[r * (T + 1) + col] = pr;
-      t.dSs[r * (T + 1) + col] = pr * (dp[i][c] - delta) * dsds;
+      // dropout: dV sees the dropped, rescaled probabilities and dP is dropped the same way
+      // (kernels/attention.py:1038-1039); delta = rowsum(o * do) already includes it
+      const float dm = (has_mod && keep) ? mod_dropout(mv, qi, kj) : 1.f;
+      t.Ps[r * (T + 1) + col] = pr * dm;
+      t.dSs[r * (T + 1) + col] = pr * (dp[i][c] * dm - delta) * dsds;
     }
   }
 }
@@ -472,9 +475,10 @@ __global__ void __launch_bounds__(NT) jvp_kernel(const JvpParams p) {
         keep = keep && qi < p.Lq && kj < kv_len && lse != INFINITY;
         const float pr = keep ? exp2f((x - lse) * kLog2e) : 0.f;
         const float pd = keep ? pr * ds[i][c] * p.sm_scale * dsds : 0.f;
-        part += pd;
-        Ps[r * (T + 1) + col] = Elem<T_>::round(pr);
-        PDs[r * (T + 1) + col] = Elem<T_>::round(pd);
+        part += pd;  // sum of p ds without dropout: the derivative of the normaliser
+        const float dm = (has_mod && keep) ? mod_dropout(mv, qi, kj) : 1.f;
+        Ps[r * (T + 1) + col] = Elem<T_>::round(pr * dm);
+        PDs[r * (T + 1) + col] = Elem<T_>::round(pd * dm);
       }
 #pragma unroll
       for (int off = 8; off >= 1; off >>= 1) part += __shfl_xor_sync(0xffffffffu, part, off);

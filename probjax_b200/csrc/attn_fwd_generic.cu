@@ -137,8 +137,9 @@ __global__ void __launch_bounds__(NT) attn_fwd_generic_kernel(const FwdParams p)
 #pragma unroll
       for (int c = 0; c < 4; ++c) {
         const float pv = exp2f(s[i][c] - m_safe);
-        rsum += pv;
-        Ps[(ty * 4 + i) * (BN + 1) + tx + 16 * c] = Elem<T>::round(pv);
+        rsum += pv;  // the row sum is taken before dropout (kernels/attention.py:497-505)
+        const float dm = has_mod ? mod_dropout(mv, qi, k0 + tx + 16 * c) : 1.f;
+        Ps[(ty * 4 + i) * (BN + 1) + tx + 16 * c] = Elem<T>::round(pv * dm);
       }
 #pragma unroll
       for (int off = 8; off >= 1; off >>= 1) rsum += __shfl_xor_sync(0xffffffffu, rsum, off);

@@ -127,6 +127,27 @@ __device__ __forceinline__ void exp_pack_store(const float (&s)[BN], float2 cs2,
   for (int c = 0; c < BN / 64; ++c) tmem_st32(s_addr + c * 32, *reinterpret_cast<const uint32_t(*)[32]>(&pk[c * 32]));
 }
 
+// The same with a multiplier per probability applied after it has been added to the row sum
+// (dropout): dmul(i) is the multiplier of score column i.
+template <int BN, bool BF16, typename F>
+__device__ __forceinline__ void exp_pack_store_scaled(const float (&s)[BN], float2 cs2, float2 nm2, float2& sum0,
+                                                      float2& sum1, uint32_t s_addr, F dmul) {
+  uint32_t pk[BN / 2];
+#pragma unroll
+  for (int i = 0; i < BN / 2; i += 2) {
+    const float2 x0 = __ffma2_rn(make_float2(s[2 * i], s[2 * i + 1]), cs2, nm2);
+    const float2 x1 = __ffma2_rn(make_float2(s[2 * i + 2], s[2 * i + 3]), cs2, nm2);
+    const float2 p0 = make_float2(ex2_approx(x0.x), ex2_approx(x0.y));
+    const float2 p1 = make_float2(ex2_approx(x1.x), ex2_approx(x1.y));
+    sum0 = __fadd2_rn(sum0, p0);
+    sum1 = __fadd2_rn(sum1, p1);
+    pk[i] = pack16<BF16>(p0.x * dmul(2 * i), p0.y * dmul(2 * i + 1));
+    pk[i + 1] = pack16<BF16>(p1.x * dmul(2 * i + 2), p1.y * dmul(2 * i + 3));
+  }
+#pragma unroll
+  for (int c = 0; c < BN / 64; ++c) tmem_st32(s_addr + c * 32, *reinterpret_cast<const uint32_t(*)[32]>(&pk[c * 32]));
+}
+
 // BIAS: 0 = no bias, 1 = bias read by each thread from global memory, 2 = bias tiles
 // staged in shared memory by TMA (one row per thread out of global memory costs one
 // L1 transaction per lane and instruction; the staged tile is read conflict-free).
@@ -550,7 +571,14 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
       const float2 cs2 = make_float2(cs, cs), nm2 = make_float2(neg_m, neg_m);
       float2 sum0 = make_float2(0.f, 0.f), sum1 = make_float2(0.f, 0.f);
       PJX_TRACE_AT(t, j, 3);
-      exp_pack_store<BN, BF16>(s, cs2, nm2, sum0, sum1, s_addr);
+      if constexpr (MOD) {
+        if (mv.drop_rate > 0.f)
+          exp_pack_store_scaled<BN, BF16>(s, cs2, nm2, sum0, sum1, s_addr, [&](int i) { return mod_dropout(mv, row, k0 + i); });
+        else
+          exp_pack_store<BN, BF16>(s, cs2, nm2, sum0, sum1, s_addr);
+      } else {
+        exp_pack_store<BN, BF16>(s, cs2, nm2, sum0, sum1, s_addr);
+      }
       PJX_TRACE_AT(t, j, 4);
       const float lsum = (sum0.x + sum0.y) + (sum1.x + sum1.y);
 

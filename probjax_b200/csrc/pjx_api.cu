@@ -57,6 +57,8 @@ int convert_score_mod(const pjx_score_mod* m, ScoreMod* out) {
   if (m->alibi_mode < 0 || m->alibi_mode > 2 || ((m->alibi_mode != 0) != (m->alibi_slopes != nullptr)))
     return fail(PJX_ERR_BAD_ARG, "score modifiers: alibi_mode is 1 (causal) or 2 (symmetric) with slopes, 0 without");
   if (!(m->softcap >= 0.f)) return fail(PJX_ERR_BAD_ARG, "score modifiers: softcap must be positive (0 = off)");
+  if (!(m->dropout_rate >= 0.f && m->dropout_rate < 1.f))
+    return fail(PJX_ERR_BAD_ARG, "score modifiers: dropout_rate must be in [0, 1), got %g", (double)m->dropout_rate);
   out->seg_q = m->seg_q; out->seg_k = m->seg_k;
   out->seg_q_bs = m->seg_q_batch_stride; out->seg_k_bs = m->seg_k_batch_stride;
   out->row_kv_limit = m->row_kv_limit; out->row_limit_bs = m->row_kv_limit_batch_stride;
@@ -65,8 +67,10 @@ int convert_score_mod(const pjx_score_mod* m, ScoreMod* out) {
   out->alibi_slopes = m->alibi_slopes; out->alibi_mode = m->alibi_mode;
   out->head_scale = m->head_scale;
   out->softcap = m->softcap;
+  out->dropout_rate = m->dropout_rate;
+  out->dropout_seed = m->dropout_seed;
   out->on = (out->seg_q || out->row_kv_limit || out->prefix_len || out->rel_bias || out->alibi_slopes ||
-             out->head_scale || out->softcap > 0.f) ? 1 : 0;
+             out->head_scale || out->softcap > 0.f || out->dropout_rate > 0.f) ? 1 : 0;
   return PJX_OK;
 }
 

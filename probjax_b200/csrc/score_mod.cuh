@@ -18,6 +18,10 @@
 //                      DistanceDecayBias 2387 with one slope for all heads).
 //   head_scale         s += s * (head_scale[h] - 1): PerHeadScaleBias 2606.
 //   softcap            s += softcap * tanh(s / softcap) - s: SoftCappingBias 2564.
+//   dropout_rate,      counter-hash dropout (probjax/nn/pallas_kernels/kernels/attention.py:116-148,
+//   dropout_seed       497-505): probability (b, h, i, j) is dropped when a 32-bit hash of
+//                      (seed, b, h, i, j) falls below the rate, survivors are scaled by 1 / (1 - rate);
+//                      applied to the probabilities after the row sum is accumulated.
 //
 // All score terms are deltas on the scaled score s = sm_scale q.k, summed the way SumBias 553
 // sums them (every term sees the same s); a dense bias adds on top as before.  The derivative
@@ -42,6 +46,8 @@ struct ScoreMod {
   int alibi_mode = 0;
   const float* head_scale = nullptr;  // [Hq]
   float softcap = 0.f;                // > 0: on
+  float dropout_rate = 0.f;           // > 0: on
+  uint32_t dropout_seed = 0;
   int on = 0;                         // any field set
 
   __host__ __device__ bool has_mask() const { return seg_q || row_kv_limit || prefix_len; }
@@ -57,6 +63,8 @@ struct ScoreModView {
   int prefix;        // 0 when off
   float slope, hscale_m1, softcap;
   int alibi_mode;
+  float drop_rate, drop_keep;  // rate (0 = off) and 1 / (1 - rate)
+  uint32_t drop_base;          // seed mixed with the batch and head indices
 };
 
 __device__ __forceinline__ ScoreModView view_of(const ScoreMod& m, int b, int h, int Lq) {
@@ -70,7 +78,25 @@ __device__ __forceinline__ ScoreModView view_of(const ScoreMod& m, int b, int h,
   v.slope = m.alibi_slopes ? m.alibi_slopes[h] : 0.f;
   v.hscale_m1 = m.head_scale ? m.head_scale[h] - 1.f : 0.f;
   v.softcap = m.softcap;
+  v.drop_rate = m.dropout_rate;
+  v.drop_keep = m.dropout_rate > 0.f ? 1.f / (1.f - m.dropout_rate) : 1.f;
+  v.drop_base = m.dropout_seed ^ (static_cast<uint32_t>(b) * 0x85EBCA6Bu) ^ (static_cast<uint32_t>(h) * 0xC2B2AE35u);
   return v;
+}
+
+// Multiplier of probability (i, j): 0 if the counter hash drops it, 1 / (1 - rate) otherwise
+// (`_dropout_mask_counter`, kernels/attention.py:116-148: the same constants, shifts and the
+// uint32 -> float32 conversion before the comparison).
+__device__ __forceinline__ float mod_dropout(const ScoreModView& v, int i, int j) {
+  if (v.drop_rate <= 0.f) return 1.f;
+  uint32_t x = v.drop_base ^ (static_cast<uint32_t>(i) * 0x27D4EB2Fu) ^ (static_cast<uint32_t>(j) * 0x165667B1u);
+  x ^= x >> 16;
+  x *= 0x7FEB352Du;
+  x ^= x >> 15;
+  x *= 0x846CA68Bu;
+  x ^= x >> 16;
+  const float u = __uint2float_rn(x) * (1.0f / 4294967296.0f);
+  return u < v.drop_rate ? 0.f : v.drop_keep;
 }
 
 // Mask part.  `band_keep` is the band test of (i, j); the key-length test is the caller's.

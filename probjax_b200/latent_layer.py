@@ -10,8 +10,8 @@ Every step is a kernel of ``libpjx_attention.so``: ``pjx_linear`` (projections),
 ``pjx_mla_fwd_mod`` (attention, with the same mask / bias objects as ``mha``) and one
 ``pjx_linear_strided`` call per head for the value fold, which reads the ``[.., H, R]`` attention
 output in place.  Weights are torch tensors in the ``[out, in]`` layout of ``pjx_linear``; the
-module holds no training state (no dropout, no parameter initialisation policy beyond a seeded
-normal draw for tests).
+module holds no training state (no dropout plumbing -- ``mla`` itself takes ``rng`` / ``dropout_rate`` --
+and no parameter initialisation policy beyond a seeded normal draw for tests).
 """
 
 from __future__ import annotations

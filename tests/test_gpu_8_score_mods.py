@@ -255,3 +255,119 @@ def test_no_score_sized_tensor_is_allocated():
     want = oracle.xla_attention(q[:, lo:].cpu(), k[:, lo:].cpu(), v[:, lo:].cpu(), causal=True, sm_scale=0.09,
                                 bias=M.CausalAlibiBias().dense(s - lo, s - lo, num_heads=h))
     assert_close(out[:, lo:], None, want, None, torch.bfloat16, "segment + alibi at S=4096")
+
+
+def _dense_dropout_reference(q, k, v, keep, bias_fn, dense, sc, seed, rate):
+    """float64 restatement with the counter-hash dropout: probabilities are normalised over all kept
+    keys, then dropped / rescaled (kernels/attention.py:497-505)."""
+    b, s, h = q.shape[0], q.shape[1], q.shape[2]
+    ss = torch.einsum("bqhd,bkhd->bhqk", q, k) * sc
+    if bias_fn is not None:
+        ss = bias_fn(ss, torch.arange(s), torch.arange(k.shape[1]))
+    if dense is not None:
+        ss = ss + dense.double()
+    if keep is not None:
+        ss = ss.masked_fill(~keep, -math.inf)
+    mm = ss.amax(-1, keepdim=True)
+    mm = torch.where(torch.isfinite(mm), mm, torch.zeros_like(mm))
+    pp = torch.exp(ss - mm)
+    dd = pp.sum(-1, keepdim=True)
+    pp = pp / torch.where(dd > 0, dd, torch.ones_like(dd))
+    drop = oracle.counter_dropout_scale(seed, b, h, torch.arange(s), torch.arange(k.shape[1]), rate).double()
+    return torch.einsum("bhqk,bkhd->bqhd", pp * drop, v)
+
+
+@pytest.mark.parametrize("rate", [0.1, 0.5])
+def test_counter_dropout_forward_fp32_and_tcgen05(rate):
+    """Attention dropout with the reference's counter hash: the kernels regenerate the oracle's mask
+    from (seed, batch, head, row, key); the log-sum-exp is the undropped one."""
+    d = dev()
+    key = [0x1234ABCD, 0x0BADF00D]
+    seed = oracle.rng_seed_from_key(key)
+    sc = 1 / math.sqrt(D)
+    q, k, v = (randn((B, S, H, D), torch.float32, s) for s in (1, 2, 3))
+    got, lse = pj.mha(q.to(d), k.to(d), v.to(d), mask=M.CausalMask(), bias=M.CausalAlibiBias(), rng=key, sm_scale=sc,
+                      dropout_rate=rate, return_lse=True)
+    want, want_lse = oracle.xla_attention(q, k, v, causal=True, sm_scale=sc, return_lse=True, dropout=(seed, rate),
+                                          score_fn=_score_fn(M.CausalAlibiBias(), H))
+    assert_close(got, lse, want, want_lse, torch.float32, f"fp32 dropout {rate}")
+    plain = pj.mha(q.to(d), k.to(d), v.to(d), mask=M.CausalMask(), bias=M.CausalAlibiBias(), sm_scale=sc)
+    assert float((plain - got).abs().max()) > 1e-3, "dropout changed nothing"
+    # tensor-core kernel, GQA, ragged length, dropout alone (no other modifier) and through flex_attention
+    s2, h2, d2 = 200, 4, 64
+    q2, k2, v2 = randn((B, s2, h2, d2), torch.bfloat16, 4), randn((B, s2, 2, d2), torch.bfloat16, 5), randn((B, s2, 2, d2), torch.bfloat16, 6)
+    got, lse = pj.flex_attention(q2.to(d), k2.to(d), v2.to(d), dropout_rng=torch.tensor(key), dropout_rate=rate,
+                                 deterministic=False, sm_scale=0.125, enable_gqa=True, return_lse=True,
+                                 implementation="b200:tcgen05")
+    pj.check_status(d)
+    want, want_lse = oracle.xla_attention(q2, k2, v2, sm_scale=0.125, return_lse=True, dropout=(seed, rate))
+    assert_close(got, lse, want, want_lse, torch.bfloat16, f"tcgen05 dropout {rate}")
+    # deterministic=True switches it off
+    off = pj.flex_attention(q2.to(d), k2.to(d), v2.to(d), dropout_rng=key, dropout_rate=rate, deterministic=True,
+                            sm_scale=0.125, enable_gqa=True)
+    want_off = oracle.xla_attention(q2, k2, v2, sm_scale=0.125)
+    assert_close(off, None, want_off, None, torch.bfloat16, "deterministic")
+
+
+def test_counter_dropout_backward_forward_mode_and_latent():
+    """Both derivatives regenerate the mask of the forward (kernels/attention.py:1038-1039) and ``mla``
+    takes the same arguments."""
+    d = dev()
+    key, rate = 77, 0.25
+    seed = oracle.rng_seed_from_key(key)
+    mask, bias = _masks()["same_segment"], _biases()["soft_capping"]
+    keep = _dense_keep(mask, B, S)
+    sc = 1 / math.sqrt(D)
+    q, k, v = (randn((B, S, H, D), torch.float32, s) for s in (1, 2, 3))
+    g_o = randn((B, S, H, D), torch.float32, 10)
+    qd, kd, vd = (x.to(d).requires_grad_(True) for x in (q, k, v))
+    out = pj.mha(qd, kd, vd, mask=mask, bias=bias, rng=key, sm_scale=sc, dropout_rate=rate)
+    out.backward(g_o.to(d))
+    q64, k64, v64 = (x.double().requires_grad_(True) for x in (q, k, v))
+    o64 = _dense_dropout_reference(q64, k64, v64, keep, _score_fn(bias, H), None, sc, seed, rate)
+    assert float((out.detach().cpu().double() - o64.detach()).abs().max()) <= 1e-4
+    o64.backward(g_o.double())
+    for name, a, w in (("dq", qd.grad, q64.grad), ("dk", kd.grad, k64.grad), ("dv", vd.grad, v64.grad)):
+        rel = float((a.double().cpu() - w).norm() / w.norm())
+        assert rel <= 1e-4, f"dropout: {name} relative error {rel:.3e}"
+    # tensor-core backward kernels do not take modifiers: 16-bit inputs go through the exact kernels too
+    qh, kh, vh = (x.to(torch.bfloat16).to(d).requires_grad_(True) for x in (q, k, v))
+    pj.mha(qh, kh, vh, rng=key, sm_scale=sc, dropout_rate=rate).backward(g_o.to(torch.bfloat16).to(d))
+    q64b, k64b, v64b = (x.to(torch.bfloat16).double().requires_grad_(True) for x in (q, k, v))
+    _dense_dropout_reference(q64b, k64b, v64b, None, None, None, sc, seed, rate).backward(g_o.to(torch.bfloat16).double())
+    for name, a, w in (("dq", qh.grad, q64b.grad), ("dk", kh.grad, k64b.grad), ("dv", vh.grad, v64b.grad)):
+        rel = float((a.double().cpu() - w).norm() / w.norm())
+        assert rel <= 2e-2, f"bf16 dropout: {name} relative error {rel:.3e}"
+    # forward mode
+    import torch.autograd.forward_ad as fwd_ad
+
+    tq, tk, tv = (randn((B, S, H, D), torch.float32, s) for s in (21, 22, 23))
+    with fwd_ad.dual_level():
+        dual_o = pj.mha(fwd_ad.make_dual(q.to(d), tq.to(d)), fwd_ad.make_dual(k.to(d), tk.to(d)),
+                        fwd_ad.make_dual(v.to(d), tv.to(d)), mask=mask, bias=bias, rng=key, sm_scale=sc,
+                        dropout_rate=rate, diff_mode="forward")
+        t_o = fwd_ad.unpack_dual(dual_o).tangent
+    _, want_t = torch.func.jvp(lambda a, b_, c: _dense_dropout_reference(a, b_, c, keep, _score_fn(bias, H), None, sc, seed, rate),
+                               (q.double(), k.double(), v.double()), (tq.double(), tk.double(), tv.double()))
+    rel = float((t_o.double().cpu() - want_t).norm() / want_t.norm())
+    assert rel <= 1e-4, f"dropout: forward-mode relative error {rel:.3e}"
+    # latent attention: materialized K / V with the same dropout arguments
+    r = 8
+    cache, wk, wv = randn((B, S, r), torch.float32, 7), randn((H, D, r), torch.float32, 8), randn((H, D, r), torch.float32, 9)
+    got = pj.mla(q.to(d), cache.to(d), wk.to(d), wv.to(d), mask=mask, rng=key, dropout_rate=rate, sm_scale=sc)
+    kk, vv = oracle.materialize_kv(cache, wk, wv, H)
+    want = oracle.xla_attention(q, kk, vv, keep=keep, sm_scale=sc, dropout=(seed, rate))
+    assert_close(got, None, want, None, torch.float32, "mla dropout")
+
+
+def test_dropout_argument_checks():
+    """attention_xla.py:637-641: a rate without a key is an error; the materialized-mask variant
+    (a [B, H, Q, K] tensor of jax.random draws) is not built."""
+    d = dev()
+    q, k, v = (randn((1, 16, 2, 16), torch.float32, s).to(d) for s in (1, 2, 3))
+    with pytest.raises(ValueError, match="prng_key must be provided"):
+        pj.mha(q, k, v, dropout_rate=0.1)
+    with pytest.raises(NotImplementedError, match="counter-hash"):
+        pj.mha(q, k, v, rng=3, dropout_rate=0.1, dropout_impl="materialize")
+    with pytest.raises(ValueError, match=r"\[0, 1\)"):
+        pj.mha(q, k, v, rng=3, dropout_rate=1.0)

@@ -244,3 +244,55 @@ def test_config_generator_shapes():
     assert c["q"].shape == (1, 64, 16, 192) and c["cache"].shape == (1, 64, 576)
     assert c["wk"].shape == (16, 192, 576) and c["wv"].shape == (16, 128, 576)
     assert LOG2E == pytest.approx(1 / math.log(2))
+
+
+def _hash_u32(seed, b, h, q, k):
+    """`_dropout_mask_counter` (kernels/attention.py:116-148) in Python integers, one element."""
+    m = 0xFFFFFFFF
+    x = seed & m
+    x ^= (b * 0x85EBCA6B) & m
+    x ^= (h * 0xC2B2AE35) & m
+    x ^= (q * 0x27D4EB2F) & m
+    x ^= (k * 0x165667B1) & m
+    x ^= x >> 16
+    x = (x * 0x7FEB352D) & m
+    x ^= x >> 15
+    x = (x * 0x846CA68B) & m
+    x ^= x >> 16
+    return x
+
+
+# tests/test_attention_xla.py:226-237 -- counter dropout: the same mask on every strategy
+def test_counter_dropout_hash_and_seed_folding():
+    seed = oracle.rng_seed_from_key([0, 11])  # the two words of jax.random.key(11) under threefry
+    assert seed == (11 * 0x9E3779B9) & 0xFFFFFFFF
+    assert oracle.rng_seed_from_key(5) == 5
+    assert oracle.rng_seed_from_key([1, 2, 3, 4]) == (
+        1 ^ ((2 * 0x9E3779B9) & 0xFFFFFFFF) ^ ((3 * (0x85EBCA6B + 2)) & 0xFFFFFFFF) ^ ((4 * (0x85EBCA6B + 3)) & 0xFFFFFFFF))
+    rate = 0.3
+    scale = oracle.counter_dropout_scale(seed, 2, 3, torch.arange(5, 45), torch.arange(64), rate)
+    assert scale.shape == (2, 3, 40, 64) and scale.dtype == torch.float32
+    for b, h, qi, kj in [(0, 0, 0, 0), (1, 2, 39, 63), (1, 0, 7, 31), (0, 1, 20, 5)]:
+        u = np.float32(_hash_u32(seed, b, h, 5 + qi, kj)) * np.float32(2.0 ** -32)
+        want = 0.0 if u < np.float32(rate) else np.float32(1.0 / (1.0 - rate))
+        assert float(scale[b, h, qi, kj]) == float(want)
+    dropped = float((scale == 0).float().mean())
+    assert abs(dropped - rate) < 0.02, dropped
+    # every (batch, head) plane differs
+    assert not torch.equal(scale[0, 0], scale[0, 1]) and not torch.equal(scale[0, 0], scale[1, 0])
+
+
+@pytest.mark.parametrize("causal", [False, True])
+def test_counter_dropout_tiled_equals_dense(causal):
+    q, k, v = _inputs(2, 40, 56, 4, 2, 16, seed=21)
+    seed, rate = 1234567, 0.3
+    kw = dict(causal=causal, sm_scale=0.25, dropout=(seed, rate), return_lse=True)
+    a, la = oracle.xla_attention(q, k, v, strategy="dense", **kw)
+    b, lb = oracle.xla_attention(q, k, v, strategy="tiled", block_q=16, block_k=16, **kw)
+    assert _rel(a, b) < 1e-5 and torch.allclose(la, lb, atol=1e-5)
+    plain, lp = oracle.xla_attention(q, k, v, causal=causal, sm_scale=0.25, return_lse=True)
+    assert torch.allclose(la, lp, atol=1e-6)  # the normaliser ignores dropout
+    assert _rel(a, plain) > 1e-2
+    # E[dropout(p)] = p: averaged over many seeds the output approaches the undropped one
+    acc = sum(oracle.xla_attention(q, k, v, causal=causal, sm_scale=0.25, dropout=(s, rate)) for s in range(200)) / 200
+    assert _rel(acc, plain) < 0.12
