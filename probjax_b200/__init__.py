@@ -29,6 +29,7 @@ from .dispatch import b200_attention_or_none, device_attention_defaults  # noqa:
 from .masks import (  # noqa: F401
     AttentionBias,
     AttentionMask,
+    BatchedLowRankBias,
     BlockDiagonalCausalMask,
     BlockDiagonalMask,
     CausalAlibiBias,
@@ -42,6 +43,7 @@ from .masks import (  # noqa: F401
     IdentityBias,
     KeyPaddingMask,
     KVLenMask,
+    LearnedAlibiBias,
     LearnedRelativePositionBias,
     LocalWindowMask,
     LowRankBias,

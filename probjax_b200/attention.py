@@ -594,18 +594,13 @@ def _fold_low_rank(q, k, v, terms, sm_scale: float):
     if Hkv != Hq:
         k, v = k.repeat_interleave(Hq // Hkv, dim=2), v.repeat_interleave(Hq // Hkv, dim=2)
     q_extra, k_extra = [], []
-    for t in terms:
-        if Lq > t.query_factors.shape[1]:
-            raise ValueError(f"q_len={Lq} exceeds maximum {t.query_factors.shape[1]}")
-        if Lkv > t.key_factors.shape[1]:
-            raise ValueError(f"kv_len={Lkv} exceeds maximum {t.key_factors.shape[1]}")
-        if t.query_factors.shape[0] not in (1, Hq):
-            raise ValueError(f"factor head count {t.query_factors.shape[0]} cannot broadcast to {Hq}")
+    for t in terms:  # LowRankBias, BatchedLowRankBias, LearnedAlibiBias: factors [B|1, length, H|1, rank]
+        qf, kf = t.factors(Lq, Lkv, Hq)
         f = math.sqrt(t.scale / sm_scale)
-        qf = (t.query_factors[:, :Lq].to(q.device).float() * f).to(q.dtype)  # [H|1, Lq, r]
-        kf = (t.key_factors[:, :Lkv].to(q.device).float() * f).to(q.dtype)
-        q_extra.append(qf.permute(1, 0, 2)[None].expand(B, Lq, Hq, qf.shape[-1]))
-        k_extra.append(kf.permute(1, 0, 2)[None].expand(B, Lkv, Hq, kf.shape[-1]))
+        qf = (qf.to(q.device).float() * f).to(q.dtype)
+        kf = (kf.to(q.device).float() * f).to(q.dtype)
+        q_extra.append(qf.expand(B, Lq, Hq, qf.shape[-1]))
+        k_extra.append(kf.expand(B, Lkv, Hq, kf.shape[-1]))
     return torch.cat([q, *q_extra], dim=-1), torch.cat([k, *k_extra], dim=-1), v
 
 

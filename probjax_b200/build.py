@@ -3,6 +3,12 @@
 Run as ``python -m probjax_b200.build`` (add ``--force`` to rebuild, ``-v`` for
 ptxas resource usage).  The library is rebuilt only when a source is newer than
 it.  nvcc cross-compiles, so no GPU is needed to build.
+
+``--what-if N --output PATH`` builds a second library whose tcgen05 forward kernel is compiled with
+``-DPJX_EXP_VARIANT=N`` (timing experiments that remove one phase of the softmax loop: 9 no
+exponentials, 11 no P store, 12 no softmax work at all, 13 no row maximum; 1-3 a share of the
+exponentials on the FMA pipe); load it with ``PJX_ATTENTION_LIB=PATH``.  Variants 9-13 compute wrong
+results on purpose and exist only to be timed.
 """
 
 from __future__ import annotations
@@ -115,7 +121,32 @@ def build_ffi(include_dir: str | None = None) -> Path | None:
     return FFI_LIB
 
 
+def build_what_if(variant: int, output: Path) -> Path:
+    """The library with ``attn_fwd_sm100.cu`` compiled at ``-DPJX_EXP_VARIANT=variant``, linked with
+    the regular objects of every other source."""
+    build()
+    objdir = PKG / "build"
+    nvcc = _nvcc()
+    obj = objdir / f"attn_fwd_sm100_what_if_{variant}.o"
+    cmd = [nvcc, "-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-std=c++17", "-lineinfo", "-Xcompiler", "-fPIC",
+           "--expt-relaxed-constexpr", "-I", str(INCLUDE), f"-DPJX_EXP_VARIANT={variant}", "-c",
+           str(CSRC / "attn_fwd_sm100.cu"), "-o", str(obj)]
+    res = subprocess.run(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
+    if res.returncode != 0:
+        raise RuntimeError(f"nvcc failed:\n{res.stdout}")
+    objs = [str(objdir / (Path(s).stem + ".o")) for s in SOURCES if s != "attn_fwd_sm100.cu"] + [str(obj)]
+    res = subprocess.run([nvcc, "-shared", "-o", str(output), *objs, "-gencode", "arch=compute_100a,code=sm_100a"],
+                         stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
+    if res.returncode != 0:
+        raise RuntimeError(f"link failed:\n{res.stdout}")
+    return output
+
+
 if __name__ == "__main__":
+    if "--what-if" in sys.argv:
+        out = Path(sys.argv[sys.argv.index("--output") + 1]) if "--output" in sys.argv else PKG / "libpjx_what_if.so"
+        print(build_what_if(int(sys.argv[sys.argv.index("--what-if") + 1]), out))
+        sys.exit(0)
     path = build(force="--force" in sys.argv, verbose="-v" in sys.argv)
     print(path)
     if "--ffi" in sys.argv:

@@ -123,6 +123,55 @@ __device__ __forceinline__ void exp_pack_store(const float (&s)[BN], float2 cs2,
     pk[i] = pack16<BF16>(p0.x, p0.y);
     pk[i + 1] = pack16<BF16>(p1.x, p1.y);
   }
+#if PJX_EXP_VARIANT == 11
+#pragma unroll
+  for (int i = 0; i < BN / 2; ++i) asm volatile("" ::"r"(pk[i]));
+#else
+#pragma unroll
+  for (int c = 0; c < BN / 64; ++c) tmem_st32(s_addr + c * 32, *reinterpret_cast<const uint32_t(*)[32]>(&pk[c * 32]));
+#endif
+}
+
+// The same with EMU of every 4 score pairs exponentiated on the FMA pipe instead of the
+// special-function unit: x = n + f with n = round(x), f in [-0.5, 0.5]; 2^f as a degree-3
+// polynomial (max relative error 7.5e-5, far below the 16-bit rounding of P); n is added to the
+// exponent field.  x is clamped at -126, so the result is never exactly 0: only for tiles that
+// need no mask (a masked score must give exactly 0).
+#ifndef PJX_EXP_VARIANT
+#define PJX_EXP_VARIANT 0
+#endif
+template <int BN, bool BF16, int EMU>
+__device__ __forceinline__ void exp_pack_store_emu(const float (&s)[BN], float2 cs2, float2 nm2, float2& sum0,
+                                                   float2& sum1, uint32_t s_addr) {
+  uint32_t pk[BN / 2];
+  const float2 magic = make_float2(12582912.f, 12582912.f), nmagic = make_float2(-12582912.f, -12582912.f);
+  const float2 neg1 = make_float2(-1.f, -1.f);
+  const float2 c0 = make_float2(0.9999280572f, 0.9999280572f), c1 = make_float2(0.6932609677f, 0.6932609677f);
+  const float2 c2 = make_float2(0.2426111251f, 0.2426111251f), c3 = make_float2(0.0551716648f, 0.0551716648f);
+#pragma unroll
+  for (int i = 0; i < BN / 2; ++i) {
+    float2 x = __ffma2_rn(make_float2(s[2 * i], s[2 * i + 1]), cs2, nm2);
+    float2 p;
+    if ((i & 3) < EMU) {
+      x.x = fmaxf(x.x, -126.f);
+      x.y = fmaxf(x.y, -126.f);
+      const float2 r = __fadd2_rn(x, magic);
+      const float2 f = __ffma2_rn(__fadd2_rn(r, nmagic), neg1, x);
+      float2 q = __ffma2_rn(f, c3, c2);
+      q = __ffma2_rn(q, f, c1);
+      q = __ffma2_rn(q, f, c0);
+      p.x = __uint_as_float(__float_as_uint(q.x) + (__float_as_uint(r.x) << 23));
+      p.y = __uint_as_float(__float_as_uint(q.y) + (__float_as_uint(r.y) << 23));
+    } else {
+#if PJX_EXP_VARIANT == 9
+      p = x;
+#else
+      p = make_float2(ex2_approx(x.x), ex2_approx(x.y));
+#endif
+    }
+    if (i & 1) sum1 = __fadd2_rn(sum1, p); else sum0 = __fadd2_rn(sum0, p);
+    pk[i] = pack16<BF16>(p.x, p.y);
+  }
 #pragma unroll
   for (int c = 0; c < BN / 64; ++c) tmem_st32(s_addr + c * 32, *reinterpret_cast<const uint32_t(*)[32]>(&pk[c * 32]));
 }
@@ -450,6 +499,12 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
       if (!ok) break;
       tc_fence_after();
       PJX_TRACE_AT(t, j, 1);
+#if PJX_EXP_VARIANT == 12
+      l = 1.f;
+      tc_fence_before();
+      mbar_arrive(BAR(P_FULL + t));
+      continue;
+#endif
       constexpr int NCH = BN / 32;
       const int k0 = (j_base + j) * BN;
       bool need_mask;
@@ -464,9 +519,14 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
 
       // The whole row of scores in registers: all loads in flight at once.
       float s[BN];
+#if PJX_EXP_VARIANT == 10
+#pragma unroll
+      for (int i = 0; i < BN; ++i) s[i] = __int_as_float(0x3c000000 + ((i * 37 + j * 11 + lane) & 0xffff));
+#else
 #pragma unroll
       for (int c = 0; c < NCH; ++c) tmem_ld32f(s_addr + c * 32, &s[c * 32]);
       tmem_wait_ld();
+#endif
       PJX_TRACE_AT(t, j, 2);
 
       if constexpr (MOD) {
@@ -554,6 +614,9 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
         mx = fmaxf(fmaxf(fmaxf(m[0], m[1]), fmaxf(m[2], m[3])), fmaxf(fmaxf(m[4], m[5]), fmaxf(m[6], m[7])));
       }
       mx *= cs;  // cs > 0
+#if PJX_EXP_VARIANT == 13
+      mx = 4.f;
+#endif
 
       // lazy running maximum: advance only when it grew by more than 8 (base 2)
       const bool need = (mx > m_ref + 8.f) || (m_ref == -INFINITY && mx > -INFINITY);
@@ -577,7 +640,16 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
         else
           exp_pack_store<BN, BF16>(s, cs2, nm2, sum0, sum1, s_addr);
       } else {
+#if PJX_EXP_VARIANT == 0 || PJX_EXP_VARIANT >= 10
         exp_pack_store<BN, BF16>(s, cs2, nm2, sum0, sum1, s_addr);
+#elif PJX_EXP_VARIANT == 9
+        exp_pack_store_emu<BN, BF16, 0>(s, cs2, nm2, sum0, sum1, s_addr);
+#else
+        if (need_mask)
+          exp_pack_store<BN, BF16>(s, cs2, nm2, sum0, sum1, s_addr);
+        else
+          exp_pack_store_emu<BN, BF16, PJX_EXP_VARIANT>(s, cs2, nm2, sum0, sum1, s_addr);
+#endif
       }
       PJX_TRACE_AT(t, j, 4);
       const float lsum = (sum0.x + sum0.y) + (sum1.x + sum1.y);

@@ -421,15 +421,112 @@ class LowRankBias(AttentionBias):
             raise ValueError("scale must be non-negative")
         self.query_factors, self.key_factors, self.scale = qf, kf, float(scale)
 
-    def dense(self, q_len, kv_len, *, batch_size=1, num_heads=1):
+    @property
+    def rank(self) -> int:
+        return self.query_factors.shape[-1]
+
+    def factors(self, q_len, kv_len, num_heads):
+        """Factors in attention layout ``[1, length, H|1, rank]`` (attention_mask_bias.py:1974-2000)."""
         if q_len > self.query_factors.shape[1]:
             raise ValueError(f"q_len={q_len} exceeds maximum {self.query_factors.shape[1]}")
         if kv_len > self.key_factors.shape[1]:
             raise ValueError(f"kv_len={kv_len} exceeds maximum {self.key_factors.shape[1]}")
         if self.query_factors.shape[0] not in (1, num_heads):
             raise ValueError(f"Cannot broadcast factor head dim {self.query_factors.shape[0]} to {num_heads}")
-        qf, kf = self.query_factors[:, :q_len].float(), self.key_factors[:, :kv_len].float()
-        return (self.scale * torch.einsum("hqr,hkr->hqk", qf, kf))[None]
+        return self.query_factors[:, :q_len].permute(1, 0, 2)[None], self.key_factors[:, :kv_len].permute(1, 0, 2)[None]
+
+    def dense(self, q_len, kv_len, *, batch_size=1, num_heads=1):
+        qf, kf = self.factors(q_len, kv_len, num_heads)
+        return self.scale * torch.einsum("bqhr,bkhr->bhqk", qf.float(), kf.float())
+
+
+class BatchedLowRankBias(AttentionBias):
+    """Per-example factored bias ``scale * query_factors[b] @ key_factors[b]^T`` with factors
+    ``[B, length, rank]`` shared by the heads (attention_mask_bias.py:2028-2192).  Folded into extra
+    q / k columns like :class:`LowRankBias`; a query factor of length 1 broadcasts over the rows."""
+
+    def __init__(self, query_factors, key_factors, *, scale: float = 1.0):
+        qf, kf = torch.as_tensor(query_factors), torch.as_tensor(key_factors)
+        if qf.dim() != 3 or kf.dim() != 3:
+            raise ValueError("factors must have shape [B, length, rank]")
+        if qf.shape[-1] != kf.shape[-1]:
+            raise ValueError("query and key factors must have the same rank")
+        if qf.shape[0] != kf.shape[0]:
+            raise ValueError("query and key factors must have the same batch size")
+        if scale < 0:
+            raise ValueError("scale must be non-negative")
+        self.query_factors, self.key_factors, self.scale = qf, kf, float(scale)
+
+    @classmethod
+    def from_key_bias(cls, key_bias, q_len: int = 1) -> "BatchedLowRankBias":
+        """Rank-1 bias that adds ``key_bias[b, j]`` to every score of key ``j`` (2069-2083)."""
+        kb = torch.as_tensor(key_bias)
+        if kb.dim() != 2:
+            raise ValueError("key_bias must have shape [B, kv_len]")
+        return cls(torch.ones((kb.shape[0], q_len, 1), dtype=kb.dtype, device=kb.device), kb[..., None])
+
+    @property
+    def rank(self) -> int:
+        return self.query_factors.shape[-1]
+
+    def factors(self, q_len, kv_len, num_heads):
+        """``[B, length, 1, rank]`` (2089-2127): broadcast over the heads by the caller."""
+        if self.query_factors.shape[1] == 1:
+            qf = self.query_factors.expand(-1, q_len, -1)
+        elif q_len <= self.query_factors.shape[1]:
+            qf = self.query_factors[:, :q_len]
+        else:
+            raise ValueError(f"q_len={q_len} exceeds maximum {self.query_factors.shape[1]}")
+        if kv_len > self.key_factors.shape[1]:
+            raise ValueError(f"kv_len={kv_len} exceeds maximum {self.key_factors.shape[1]}")
+        return qf[:, :, None, :], self.key_factors[:, :kv_len, None, :]
+
+    def dense(self, q_len, kv_len, *, batch_size=1, num_heads=1):
+        qf, kf = self.factors(q_len, kv_len, num_heads)
+        return self.scale * torch.einsum("bqhr,bkhr->bhqk", qf.float(), kf.float())
+
+
+class LearnedAlibiBias(AttentionBias):
+    """``scores - slope[h] * ((q + query_offset) - (k + key_offset))`` with caller-owned slopes
+    ``[H|1]`` (attention_mask_bias.py:2258-2351; meant for use under a causal mask).  When the slopes
+    require a gradient it is folded into two extra q / k columns as in the reference, so the gradient
+    reaches them through dq / dk; otherwise the kernels read it from a float32 table indexed by the
+    head and ``k - q``."""
+
+    scale = 1.0
+    rank = 2
+
+    def __init__(self, slopes, *, query_offset: int = 0, key_offset: int = 0):
+        s = torch.as_tensor(slopes)
+        s = s[None] if s.dim() == 0 else s
+        if s.dim() != 1:
+            raise ValueError("slopes must have shape [H|1]")
+        self.slopes, self.query_offset, self.key_offset = s, int(query_offset), int(key_offset)
+
+    def _head_slopes(self, num_heads):
+        if self.slopes.shape[0] not in (1, num_heads):
+            raise ValueError(f"slope head count {self.slopes.shape[0]} cannot broadcast to {num_heads}")
+        return self.slopes.expand(num_heads)
+
+    def factors(self, q_len, kv_len, num_heads):
+        """``q' = (-slope * q_pos, 1)``, ``k' = (1, slope * k_pos)``: ``[1, length, H, 2]`` (2296-2321)."""
+        sl = self._head_slopes(num_heads)
+        q_pos = torch.arange(q_len, dtype=sl.dtype, device=sl.device) + self.query_offset
+        k_pos = torch.arange(kv_len, dtype=sl.dtype, device=sl.device) + self.key_offset
+        qf = torch.stack((-sl[:, None] * q_pos[None], torch.ones((num_heads, q_len), dtype=sl.dtype, device=sl.device)), -1)
+        kf = torch.stack((torch.ones((num_heads, kv_len), dtype=sl.dtype, device=sl.device), sl[:, None] * k_pos[None]), -1)
+        return qf.transpose(0, 1)[None], kf.transpose(0, 1)[None]
+
+    def relative_table(self, q_len, kv_len, num_heads):
+        """``[H, q_len + kv_len - 1]`` float32: entry ``(j - i) + q_len - 1`` is the bias of ``(i, j)``."""
+        rel = torch.arange(-(q_len - 1), kv_len, dtype=torch.float32)  # j - i
+        sl = self._head_slopes(num_heads).detach().float().cpu()
+        return sl[:, None] * (rel[None, :] - float(self.query_offset - self.key_offset))
+
+    def dense(self, q_len, kv_len, *, batch_size=1, num_heads=1):
+        tab = self.relative_table(q_len, kv_len, num_heads)
+        idx = (_idx(kv_len)[None, :] - _idx(q_len)[:, None] + (q_len - 1)).to(torch.int64)
+        return tab[:, idx][None]
 
 
 class IdentityBias(AttentionBias):
@@ -735,7 +832,10 @@ def lower_bias_structured(bias, batch: int, heads: int, q_len: int, kv_len: int)
             d = term.bias.float()
             out.dense = d if out.dense is None else out.dense + d.to(out.dense.device)
             continue
-        if isinstance(term, LowRankBias):
+        if isinstance(term, (LowRankBias, BatchedLowRankBias)) or (
+                isinstance(term, LearnedAlibiBias) and term.slopes.requires_grad):
+            if isinstance(term, BatchedLowRankBias) and term.query_factors.shape[0] not in (1, batch):
+                raise ValueError(f"Cannot broadcast factors of batch {term.query_factors.shape[0]} to {batch}")
             low_rank.append(term)
             continue
         if isinstance(term, SoftCappingBias):
@@ -767,6 +867,8 @@ def lower_bias_structured(bias, batch: int, heads: int, q_len: int, kv_len: int)
             tab = -(slopes[:, None] * dist[None, :])
         elif isinstance(term, ConstantBias):
             tab = torch.full((1, q_len + kv_len - 1), term.value, dtype=torch.float32)
+        elif isinstance(term, LearnedAlibiBias):
+            tab = term.relative_table(q_len, kv_len, heads)
         elif isinstance(term, _RelativeBias):
             tab = term.relative_table(q_len, kv_len)
             if tab.shape[0] not in (1, heads):

@@ -257,13 +257,12 @@ def test_no_score_sized_tensor_is_allocated():
     assert_close(out[:, lo:], None, want, None, torch.bfloat16, "segment + alibi at S=4096")
 
 
-def _dense_dropout_reference(q, k, v, keep, bias_fn, dense, sc, seed, rate):
+def _dense_dropout_reference(q, k, v, keep, bias_fn, dense, sc, drop):
     """float64 restatement with the counter-hash dropout: probabilities are normalised over all kept
-    keys, then dropped / rescaled (kernels/attention.py:497-505)."""
-    b, s, h = q.shape[0], q.shape[1], q.shape[2]
+    keys, then dropped / rescaled by ``drop`` (kernels/attention.py:497-505)."""
     ss = torch.einsum("bqhd,bkhd->bhqk", q, k) * sc
     if bias_fn is not None:
-        ss = bias_fn(ss, torch.arange(s), torch.arange(k.shape[1]))
+        ss = bias_fn(ss, _IDX, _IDX)
     if dense is not None:
         ss = ss + dense.double()
     if keep is not None:
@@ -273,8 +272,10 @@ def _dense_dropout_reference(q, k, v, keep, bias_fn, dense, sc, seed, rate):
     pp = torch.exp(ss - mm)
     dd = pp.sum(-1, keepdim=True)
     pp = pp / torch.where(dd > 0, dd, torch.ones_like(dd))
-    drop = oracle.counter_dropout_scale(seed, b, h, torch.arange(s), torch.arange(k.shape[1]), rate).double()
     return torch.einsum("bhqk,bkhd->bqhd", pp * drop, v)
+
+
+_IDX = torch.arange(S)
 
 
 @pytest.mark.parametrize("rate", [0.1, 0.5])
@@ -317,6 +318,7 @@ def test_counter_dropout_backward_forward_mode_and_latent():
     seed = oracle.rng_seed_from_key(key)
     mask, bias = _masks()["same_segment"], _biases()["soft_capping"]
     keep = _dense_keep(mask, B, S)
+    drop = oracle.counter_dropout_scale(seed, B, H, _IDX, _IDX, rate).double()
     sc = 1 / math.sqrt(D)
     q, k, v = (randn((B, S, H, D), torch.float32, s) for s in (1, 2, 3))
     g_o = randn((B, S, H, D), torch.float32, 10)
@@ -324,7 +326,7 @@ def test_counter_dropout_backward_forward_mode_and_latent():
     out = pj.mha(qd, kd, vd, mask=mask, bias=bias, rng=key, sm_scale=sc, dropout_rate=rate)
     out.backward(g_o.to(d))
     q64, k64, v64 = (x.double().requires_grad_(True) for x in (q, k, v))
-    o64 = _dense_dropout_reference(q64, k64, v64, keep, _score_fn(bias, H), None, sc, seed, rate)
+    o64 = _dense_dropout_reference(q64, k64, v64, keep, _score_fn(bias, H), None, sc, drop)
     assert float((out.detach().cpu().double() - o64.detach()).abs().max()) <= 1e-4
     o64.backward(g_o.double())
     for name, a, w in (("dq", qd.grad, q64.grad), ("dk", kd.grad, k64.grad), ("dv", vd.grad, v64.grad)):
@@ -334,7 +336,7 @@ def test_counter_dropout_backward_forward_mode_and_latent():
     qh, kh, vh = (x.to(torch.bfloat16).to(d).requires_grad_(True) for x in (q, k, v))
     pj.mha(qh, kh, vh, rng=key, sm_scale=sc, dropout_rate=rate).backward(g_o.to(torch.bfloat16).to(d))
     q64b, k64b, v64b = (x.to(torch.bfloat16).double().requires_grad_(True) for x in (q, k, v))
-    _dense_dropout_reference(q64b, k64b, v64b, None, None, None, sc, seed, rate).backward(g_o.to(torch.bfloat16).double())
+    _dense_dropout_reference(q64b, k64b, v64b, None, None, None, sc, drop).backward(g_o.to(torch.bfloat16).double())
     for name, a, w in (("dq", qh.grad, q64b.grad), ("dk", kh.grad, k64b.grad), ("dv", vh.grad, v64b.grad)):
         rel = float((a.double().cpu() - w).norm() / w.norm())
         assert rel <= 2e-2, f"bf16 dropout: {name} relative error {rel:.3e}"
@@ -347,7 +349,7 @@ def test_counter_dropout_backward_forward_mode_and_latent():
                         fwd_ad.make_dual(v.to(d), tv.to(d)), mask=mask, bias=bias, rng=key, sm_scale=sc,
                         dropout_rate=rate, diff_mode="forward")
         t_o = fwd_ad.unpack_dual(dual_o).tangent
-    _, want_t = torch.func.jvp(lambda a, b_, c: _dense_dropout_reference(a, b_, c, keep, _score_fn(bias, H), None, sc, seed, rate),
+    _, want_t = torch.func.jvp(lambda a, b_, c: _dense_dropout_reference(a, b_, c, keep, _score_fn(bias, H), None, sc, drop),
                                (q.double(), k.double(), v.double()), (tq.double(), tk.double(), tv.double()))
     rel = float((t_o.double().cpu() - want_t).norm() / want_t.norm())
     assert rel <= 1e-4, f"dropout: forward-mode relative error {rel:.3e}"
@@ -371,3 +373,44 @@ def test_dropout_argument_checks():
         pj.mha(q, k, v, rng=3, dropout_rate=0.1, dropout_impl="materialize")
     with pytest.raises(ValueError, match=r"\[0, 1\)"):
         pj.mha(q, k, v, rng=3, dropout_rate=1.0)
+
+
+def test_batched_low_rank_and_learned_alibi():
+    """Per-example factors (attention_mask_bias.py:2028-2192) ride on extra q / k columns; caller-owned
+    ALiBi slopes (2258-2351) are a relative-position table in the kernels, or -- when they require a
+    gradient -- two folded columns through which the gradient reaches them."""
+    d = dev()
+    sc = 1 / math.sqrt(D)
+    q, k, v = randn((B, S, H, D), torch.float32, 1), randn((B, S, 2, D), torch.float32, 2), randn((B, S, 2, D), torch.float32, 3)
+    log_m = randn((B, S), torch.float32, 4)
+    bias = M.SumBias(M.BatchedLowRankBias.from_key_bias(log_m), M.CausalAlibiBias())
+    got = pj.flex_attention(q.to(d), k.to(d), v.to(d), mask=M.CausalMask(), bias=bias, enable_gqa=True)
+    dense = log_m[:, None, None, :] + M.CausalAlibiBias().dense(S, S, num_heads=H)
+    want = oracle.xla_attention(q, k, v, causal=True, bias=dense, sm_scale=sc)
+    assert_close(got, None, want, None, torch.float32, "per-example key bias")
+    # caller-owned slopes, no gradient: in-kernel table (fp32 and tensor-core kernels)
+    slopes = torch.tensor([0.5, 0.25, 0.125, 0.0625])
+    la = M.LearnedAlibiBias(slopes, query_offset=2, key_offset=0)
+    dense = la.dense(S, S, num_heads=H)
+    got, lse = pj.mha(q.to(d), k.to(d), v.to(d), mask=M.CausalMask(), bias=la, sm_scale=sc, return_lse=True)
+    want, want_lse = oracle.xla_attention(q, k, v, causal=True, bias=dense, sm_scale=sc, return_lse=True)
+    assert_close(got, lse, want, want_lse, torch.float32, "learned alibi table")
+    qh, kh, vh = randn((B, 200, H, 64), torch.bfloat16, 5), randn((B, 200, 2, 64), torch.bfloat16, 6), randn((B, 200, 2, 64), torch.bfloat16, 7)
+    got = pj.mha(qh.to(d), kh.to(d), vh.to(d), mask=M.CausalMask(), bias=la, sm_scale=0.125, implementation="b200:tcgen05")
+    want = oracle.xla_attention(qh, kh, vh, causal=True, bias=la.dense(200, 200, num_heads=H), sm_scale=0.125)
+    assert_close(got, None, want, None, torch.bfloat16, "learned alibi table, tcgen05")
+    # slopes that require a gradient: folded, d loss / d slopes against float64 autograd
+    sl = slopes.clone().to(d).requires_grad_(True)
+    g_o = randn((B, S, H, D), torch.float32, 8)
+    out = pj.mha(q.to(d), k.to(d), v.to(d), mask=M.CausalMask(), bias=M.LearnedAlibiBias(sl), sm_scale=sc)
+    out.backward(g_o.to(d))
+    sl64 = slopes.double().requires_grad_(True)
+    pos = torch.arange(S, dtype=torch.float64)
+    s64 = torch.einsum("bqhd,bkhd->bhqk", q.double(), k.double().repeat_interleave(2, 2)) * sc
+    s64 = s64 - sl64[None, :, None, None] * (pos[:, None] - pos[None, :])
+    s64 = s64.masked_fill(~torch.tril(torch.ones(S, S, dtype=torch.bool)), -math.inf)
+    o64 = torch.einsum("bhqk,bkhd->bqhd", torch.softmax(s64, -1), v.double().repeat_interleave(2, 2))
+    assert float((out.detach().cpu().double() - o64.detach()).abs().max()) <= 1e-4
+    o64.backward(g_o.double())
+    rel = float((sl.grad.double().cpu() - sl64.grad).norm() / sl64.grad.norm())
+    assert rel <= 1e-3, f"slope gradient relative error {rel:.3e}"

@@ -470,3 +470,43 @@ def test_ffi_shim_is_consistent_and_compiles_without_jaxlib(tmp_path):
         assert res.returncode == 0, res.stderr
         syms = subprocess.run(["nm", "-g", str(obj)], capture_output=True, text=True).stdout
         assert "pjx_ffi_unavailable" in syms
+
+
+def test_low_rank_family_factors_and_dense_forms():
+    """attention_mask_bias.py:2028-2192 (per-example factors), 2258-2351 (caller-owned ALiBi slopes):
+    ``dense`` equals ``scale * qf @ kf^T`` / ``-slope ((q + qo) - (k + ko))`` and the factor layouts are
+    the ones ``flex_attention`` concatenates onto q and k."""
+    from probjax_b200 import masks as M
+
+    g = torch.Generator().manual_seed(5)
+    log_m = torch.randn((3, 10), generator=g)
+    kb = M.BatchedLowRankBias.from_key_bias(log_m)
+    qf, kf = kb.factors(7, 10, 4)
+    assert tuple(qf.shape) == (3, 7, 1, 1) and tuple(kf.shape) == (3, 10, 1, 1) and kb.rank == 1
+    d = kb.dense(7, 10, batch_size=3, num_heads=4)
+    assert torch.allclose(d.expand(3, 4, 7, 10), log_m[:, None, None, :].expand(3, 4, 7, 10))
+    with pytest.raises(ValueError, match="exceeds maximum"):
+        kb.factors(7, 11, 4)
+    with pytest.raises(ValueError, match=r"\[B, length, rank\]"):
+        M.BatchedLowRankBias(torch.zeros(3, 4), torch.zeros(3, 4))
+    with pytest.raises(ValueError, match="same batch size"):
+        M.BatchedLowRankBias(torch.zeros(2, 4, 1), torch.zeros(3, 4, 1))
+    lb = M.lower_bias_structured(kb, 3, 4, 7, 10)
+    assert lb.low_rank == (kb,) and lb.dense is None and not lb.structured
+    with pytest.raises(ValueError, match="Cannot broadcast factors of batch"):
+        M.lower_bias_structured(kb, 2, 4, 7, 10)
+
+    slopes = torch.tensor([0.5, 0.25])
+    la = M.LearnedAlibiBias(slopes, query_offset=3, key_offset=1)
+    want = -slopes[:, None, None] * ((torch.arange(6)[:, None] + 3) - (torch.arange(9)[None, :] + 1))
+    assert torch.allclose(la.dense(6, 9, num_heads=2)[0], want.float())
+    qf, kf = la.factors(6, 9, 2)
+    assert tuple(qf.shape) == (1, 6, 2, 2) and tuple(kf.shape) == (1, 9, 2, 2)
+    assert torch.allclose(torch.einsum("bqhr,bkhr->bhqk", qf, kf)[0], want)
+    lb = M.lower_bias_structured(la, 1, 2, 6, 9)  # no gradient asked for: a relative-position table
+    assert lb.low_rank == () and tuple(lb.rel_bias.shape) == (2, 14)
+    assert torch.allclose(lb.rel_bias[:, (torch.arange(9)[None, :] - torch.arange(6)[:, None]) + 5], want.float())
+    lg = M.LearnedAlibiBias(slopes.clone().requires_grad_(True))
+    assert M.lower_bias_structured(lg, 1, 2, 6, 9).low_rank == (lg,)  # folded: the gradient reaches the slopes
+    with pytest.raises(ValueError, match="cannot broadcast"):
+        M.lower_bias_structured(M.LearnedAlibiBias(torch.ones(3)), 1, 2, 6, 9)
