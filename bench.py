@@ -281,6 +281,9 @@ def main():
                     help="time only the fused QKV projection of the headline shape (profiling captures)")
     ap.add_argument("--only-masked-bias", action="store_true",
                     help="time only the masked + biased configuration on --batch batch rows (profiling captures)")
+    ap.add_argument("--only-prefill", action="store_true",
+                    help="time only the headline forward, non-causal and causal, without checking the result "
+                         "(what-if builds of the forward kernel, whose outputs are wrong on purpose)")
     ap.add_argument("--only-latent", action="store_true",
                     help="time only the latent-attention configuration on --batch batch rows (profiling captures)")
     ap.add_argument("--kernel", default=None, choices=[None, "b200:generic", "b200:tcgen05"],
@@ -323,6 +326,9 @@ def main():
         return
     if args.only_masked_bias:
         only_masked_bias(args, dev, pk)
+        return
+    if args.only_prefill:
+        only_prefill(args, dev, pk)
         return
     if args.only_latent:
         only_latent(args, dev, pk)
@@ -629,6 +635,24 @@ def only_masked_bias(args, dev, pk):
     res["config"] = {"workload": f"masked + biased attention bf16 B{args.batch} H16 S1024 D64, fp32 bias [1,16,1024,1024]",
                      "kv_lengths": c3["kv_lengths"].tolist()}
     _emit(res)
+
+
+def only_prefill(args, dev, pk):
+    """The headline forward on `--batch` batch rows, non-causal and causal, timing only: the command the
+    what-if builds of the forward kernel (`python -m probjax_b200.build --what-if N`, loaded through
+    PJX_ATTENTION_LIB) are timed with."""
+    import oracle
+    import probjax_b200 as pj
+
+    c = oracle.make_config(2, B=args.batch)
+    q, k, v = c["q"].to(dev), c["k"].to(dev), c["v"].to(dev)
+    out = {"config": {"workload": f"GQA prefill bf16 B{args.batch} Hq32 Hkv8 S4096 D128", "library": os.environ.get("PJX_ATTENTION_LIB", "in-tree")}}
+    for name, causal in (("noncausal", False), ("causal", True)):
+        fl = prefill_flops(args.batch, C2["Hq"], C2["S"], C2["S"], C2["D"], C2["D"], causal)
+        res = bench_extra(name, lambda: pj.attention_forward(q, k, v, causal=causal, sm_scale=c["sm_scale"], impl=args.kernel),
+                          args.steps, args.warmup, fl / 1e12, "TFLOP/s", pk["bf16_tflops"], "tensor", pk["source"])
+        out[name] = {"ms": res["ms"], "tflops": res["value"]}
+    _emit(out)
 
 
 def only_latent(args, dev, pk):

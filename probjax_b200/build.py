@@ -8,7 +8,8 @@ it.  nvcc cross-compiles, so no GPU is needed to build.
 ``-DPJX_EXP_VARIANT=N`` (timing experiments that remove one phase of the softmax loop: 9 no
 exponentials, 11 no P store, 12 no softmax work at all, 13 no row maximum; 1-3 a share of the
 exponentials on the FMA pipe); load it with ``PJX_ATTENTION_LIB=PATH``.  Variants 9-13 compute wrong
-results on purpose and exist only to be timed.
+results on purpose and exist only to be timed.  ``--probe`` builds ``build/probe_mma_rate``, a
+stand-alone program that times tcgen05.mma issue sequences.
 """
 
 from __future__ import annotations
@@ -142,7 +143,23 @@ def build_what_if(variant: int, output: Path) -> Path:
     return output
 
 
+def build_probe() -> Path:
+    """``csrc/probe_mma_rate.cu`` as the program ``build/probe_mma_rate`` (tcgen05.mma issue rates)."""
+    objdir = PKG / "build"
+    objdir.mkdir(exist_ok=True)
+    exe = objdir / "probe_mma_rate"
+    cmd = [_nvcc(), "-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-std=c++17", "-I", str(INCLUDE),
+           str(CSRC / "probe_mma_rate.cu"), "-o", str(exe), "-lcuda"]
+    res = subprocess.run(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
+    if res.returncode != 0:
+        raise RuntimeError(f"nvcc failed:\n{res.stdout}")
+    return exe
+
+
 if __name__ == "__main__":
+    if "--probe" in sys.argv:
+        print(build_probe())
+        sys.exit(0)
     if "--what-if" in sys.argv:
         out = Path(sys.argv[sys.argv.index("--output") + 1]) if "--output" in sys.argv else PKG / "libpjx_what_if.so"
         print(build_what_if(int(sys.argv[sys.argv.index("--what-if") + 1]), out))
