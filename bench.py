@@ -281,6 +281,8 @@ def main():
                     help="time only the fused QKV projection of the headline shape (profiling captures)")
     ap.add_argument("--only-masked-bias", action="store_true",
                     help="time only the masked + biased configuration on --batch batch rows (profiling captures)")
+    ap.add_argument("--only-latent-decode", action="store_true",
+                    help="time only the absorbed latent decode on --batch sequences (profiling captures)")
     ap.add_argument("--only-prefill", action="store_true",
                     help="time only the headline forward, non-causal and causal, without checking the result "
                          "(what-if builds of the forward kernel, whose outputs are wrong on purpose)")
@@ -329,6 +331,9 @@ def main():
         return
     if args.only_prefill:
         only_prefill(args, dev, pk)
+        return
+    if args.only_latent_decode:
+        only_latent_decode(args, dev, pk)
         return
     if args.only_latent:
         only_latent(args, dev, pk)
@@ -634,6 +639,21 @@ def only_masked_bias(args, dev, pk):
                       args.steps, args.warmup, fl3 / 1e12, "TFLOP/s", pk["bf16_tflops"], "tensor", pk["source"])
     res["config"] = {"workload": f"masked + biased attention bf16 B{args.batch} H16 S1024 D64, fp32 bias [1,16,1024,1024]",
                      "kv_lengths": c3["kv_lengths"].tolist()}
+    _emit(res)
+
+
+def only_latent_decode(args, dev, pk):
+    """The decode step of absorbed latent attention (16 heads over a 576-wide latent cache of 32768 keys)
+    on `--batch` sequences, nothing else: the command profiling captures of `decode_latent_kernel` run."""
+    import probjax_b200 as pj
+
+    Bl, Hl, Rl, Sl = args.batch, 16, 576, 32768
+    gl = torch.Generator(device=dev).manual_seed(5)
+    ql = torch.randn((Bl, 1, Hl, Rl), generator=gl, device=dev).bfloat16()
+    cl = (torch.randn((Bl, Sl, Rl), generator=gl, device=dev) * 0.5).bfloat16()
+    res = bench_extra("latent_decode", lambda: pj.mla_decode(ql, cl, sm_scale=Rl ** -0.5), args.steps, args.warmup,
+                      (cl.numel() * 2 + 2 * ql.numel() * 2) / 1e9, "GB/s", pk["hbm_gbs"], "hbm", pk["source"])
+    res["config"] = {"workload": f"absorbed latent decode bf16 B{Bl} H16 R576, 32768 keys each"}
     _emit(res)
 
 

@@ -74,10 +74,21 @@ __global__ void __launch_bounds__(LTHR, 1) decode_latent_kernel(const DecodePara
   auto load_tile = [&](int t) {
     const uint32_t dst = sbase + (t % C::NSTAGE) * C::TILE_BYTES;
     const int key0 = start + t * LBK;
-    for (int idx = tid; idx < LBK * CH; idx += LTHR) {
-      const int r = idx / CH, c = idx % CH;
+    // warp w copies rows 8w .. 8w+7, lanes take the 16-byte chunks lane, lane + 32, ... of a row: no
+    // division, and the swizzle term (r & 7) is the unrolled loop index
+    static_assert(LBK == 8 * LWARPS, "one warp per eight rows of a tile");
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const int r = warp * 8 + i;
       const bool ok = key0 + r < end;  // rows past the valid length are zero-filled, never read
-      cp_async16(dst + lswz(r, c, C::ROW_BYTES), cbase + (int64_t)(key0 + (ok ? r : 0)) * R + c * 8, ok ? 16 : 0);
+      const T* src = cbase + (int64_t)(key0 + (ok ? r : 0)) * R + lane * 8;
+      const uint32_t drow = dst + r * C::ROW_BYTES;
+#pragma unroll
+      for (int c0 = 0; c0 < CH; c0 += 32) {
+        const int c = c0 + lane;
+        if (c0 + 32 <= CH || c < CH)
+          cp_async16(drow + (((c & ~7) | ((c ^ i) & 7)) << 4), src + c0 * 8, ok ? 16 : 0);
+      }
     }
   };
 #pragma unroll
