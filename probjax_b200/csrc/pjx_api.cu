@@ -646,6 +646,8 @@ int pjx_attn_fwd_host(const void* q, const void* k, const void* v, void* o, floa
       const char* hq = static_cast<const char*>(q) + b0 * q1 + l0 * qrow;
       if (nq == 1) {
         if ((rc = check_cuda(cudaMemcpyAsync(dq + b0 * q1, hq, nb_c * q1, cudaMemcpyHostToDevice, hp->in), "copy q to device"))) return rc;
+      } else if (nb_c == 1) {  // one batch row: the block of query rows is contiguous
+        if ((rc = check_cuda(cudaMemcpyAsync(dq + b0 * q1 + l0 * qrow, hq, rows * qrow, cudaMemcpyHostToDevice, hp->in), "copy q rows to device"))) return rc;
       } else if ((rc = check_cuda(cudaMemcpy2DAsync(dq + b0 * q1 + l0 * qrow, q1, hq, q1, rows * qrow, nb_c, cudaMemcpyHostToDevice, hp->in), "copy q rows to device"))) {
         return rc;
       }
@@ -673,6 +675,8 @@ int pjx_attn_fwd_host(const void* q, const void* k, const void* v, void* o, floa
       if (nq == 1) {
         if ((rc = check_cuda(cudaMemcpyAsync(static_cast<char*>(o) + b0 * o1, dout + b0 * o1, nb_c * o1, cudaMemcpyDeviceToHost, hp->out), "copy o to host"))) return rc;
         if (lse && (rc = check_cuda(cudaMemcpyAsync(reinterpret_cast<char*>(lse) + b0 * l1, dl + b0 * l1, nb_c * l1, cudaMemcpyDeviceToHost, hp->out), "copy lse to host"))) return rc;
+      } else if (nb_c == 1) {
+        if ((rc = check_cuda(cudaMemcpyAsync(static_cast<char*>(o) + b0 * o1 + l0 * orow, dout + b0 * o1 + l0 * orow, rows * orow, cudaMemcpyDeviceToHost, hp->out), "copy o rows to host"))) return rc;
       } else if ((rc = check_cuda(cudaMemcpy2DAsync(static_cast<char*>(o) + b0 * o1 + l0 * orow, o1, dout + b0 * o1 + l0 * orow, o1, rows * orow, nb_c, cudaMemcpyDeviceToHost, hp->out), "copy o rows to host"))) {
         return rc;
       }
