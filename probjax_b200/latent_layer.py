@@ -10,8 +10,10 @@ Every step is a kernel of ``libpjx_attention.so``: ``pjx_linear`` (projections),
 ``pjx_mla_fwd_mod`` (attention, with the same mask / bias objects as ``mha``) and one
 ``pjx_linear_strided`` call per head for the value fold, which reads the ``[.., H, R]`` attention
 output in place.  Weights are torch tensors in the ``[out, in]`` layout of ``pjx_linear``; the
-module holds no training state (no dropout plumbing -- ``mla`` itself takes ``rng`` / ``dropout_rate`` --
-and no parameter initialisation policy beyond a seeded normal draw for tests).
+module's attention dropout follows the reference's resolution rules (``dropout_rate`` /
+``deterministic`` / ``keep_rngs`` at construction, ``deterministic`` / ``rng`` per call, 600-632) with a
+counter of its own standing in for the kept ``nnx`` dropout stream; there is no parameter
+initialisation policy beyond a seeded normal draw for tests.
 """
 
 from __future__ import annotations
@@ -82,11 +84,19 @@ class MultiHeadLatentAttention:
     def __init__(self, num_heads: int, in_features: int, *, kv_lora_rank: int, mode: str = "absorbed",
                  out_features: int | None = None, in_kv_features: int | None = None, qk_head_dim: int | None = None,
                  v_head_dim: int | None = None, latent_norm: bool = True, kv_encoder: bool = True,
-                 value_projection: bool = True, eps: float = 1e-6, dtype=torch.bfloat16, device=None, seed: int = 0):
+                 value_projection: bool = True, eps: float = 1e-6, dtype=torch.bfloat16, device=None, seed: int = 0,
+                 dropout_rate: float = 0.0, deterministic: bool | None = None, keep_rngs: bool = True):
         if mode not in MODES:
             raise ValueError(f"mode must be one of {MODES}, got {mode!r}")
         if num_heads <= 0 or kv_lora_rank <= 0:
             raise ValueError("num_heads and kv_lora_rank must be positive")
+        if not 0.0 <= dropout_rate < 1.0:
+            raise ValueError(f"dropout_rate must be in [0, 1), got {dropout_rate}; "
+                             "a rate of 1 or more zeroes the output and a negative rate "
+                             "biases it")
+        self.dropout_rate, self.deterministic = float(dropout_rate), deterministic
+        # the kept dropout stream: (seed, call counter) words folded into the kernels' 32-bit seed
+        self._kept_stream = [int(seed) & 0xFFFFFFFF, 0] if keep_rngs and self.dropout_rate > 0.0 else None
         if not value_projection and mode != "absorbed":
             raise ValueError("value_projection=False is only supported in absorbed mode "
                              "(K = V = C); materialized mode needs wv to form values")
@@ -136,8 +146,28 @@ class MultiHeadLatentAttention:
             latent = rms_norm(latent, self.latent_norm_scale, eps=self.eps, out=latent)
         return latent
 
+    def _resolve_dropout(self, deterministic, rng):
+        """(rate, rng) of one call (latent_attention.py:604-632)."""
+        if self.dropout_rate == 0.0:
+            return 0.0, None
+        deterministic = deterministic if deterministic is not None else self.deterministic
+        if deterministic is None:
+            raise ValueError("No `deterministic` argument was provided to "
+                             "MultiHeadLatentAttention as either a __call__ argument, "
+                             "class attribute, or nnx.flag.")
+        if deterministic:
+            return 0.0, None
+        if rng is not None:
+            return self.dropout_rate, rng
+        if self._kept_stream is not None:
+            self._kept_stream[1] += 1
+            return self.dropout_rate, list(self._kept_stream)
+        raise ValueError("'rng'/'rngs' must be provided to __call__, or the layer "
+                         "built with keep_rngs=True, when dropout is enabled")
+
     def __call__(self, inputs_q: torch.Tensor, inputs_kv: torch.Tensor | None = None, *, mask=None, bias=None,
-                 sm_scale: float | None = None) -> torch.Tensor:
+                 sm_scale: float | None = None, deterministic: bool | None = None, rng=None) -> torch.Tensor:
+        drop_rate, drop_rng = self._resolve_dropout(deterministic, rng)
         inputs_kv = inputs_q if inputs_kv is None else inputs_kv
         latent = self.encode_latent(inputs_kv) if self.kv_encoder else inputs_kv
         lead = inputs_q.shape[:-2]
@@ -145,9 +175,10 @@ class MultiHeadLatentAttention:
         lat3 = latent.reshape(-1, latent.shape[-2], self.kv_lora_rank)
         scale = 1.0 / math.sqrt(self.qk_head_dim) if sm_scale is None else float(sm_scale)
         if self.mode == "materialized":
-            attn = mla(q, lat3, self.wk, self.wv, mask=mask, bias=bias, sm_scale=scale)
+            attn = mla(q, lat3, self.wk, self.wv, mask=mask, bias=bias, sm_scale=scale, rng=drop_rng,
+                       dropout_rate=drop_rate)
         else:
-            attn = mla(q, lat3, mask=mask, bias=bias, sm_scale=scale)  # [B, Q, H, R]
+            attn = mla(q, lat3, mask=mask, bias=bias, sm_scale=scale, rng=drop_rng, dropout_rate=drop_rate)  # [B, Q, H, R]
             if self.wv is not None:  # fold W_V in, then the shared output projection (468-474)
                 attn = per_head_linear(attn, self.wv)
         out = linear(attn.reshape(attn.shape[0], attn.shape[1], self.num_heads * self.v_head_dim), self.wo)

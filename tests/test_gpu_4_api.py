@@ -299,6 +299,27 @@ def test_latent_attention_layer_steps(mode, kw):
     assert got.shape == (2, 200, 192) and rel <= 2e-2, f"{mode} {kw}: relative error {rel:.3e}"
 
 
+def test_latent_attention_layer_dropout():
+    """Dropout through the layer: off under `deterministic=True`, reproducible for a given key, different
+    from call to call on the kept stream."""
+    from probjax_b200.latent_layer import MultiHeadLatentAttention
+
+    d = dev()
+    kw = dict(kv_lora_rank=128, mode="absorbed", v_head_dim=64, out_features=192, device=d, seed=3)
+    plain = MultiHeadLatentAttention(4, 256, **kw)
+    layer = MultiHeadLatentAttention(4, 256, dropout_rate=0.2, **kw)
+    x = randn((2, 200, 256), torch.bfloat16, 9).to(d)
+    base = plain(x, mask=pj.CausalMask())
+    assert torch.equal(layer(x, mask=pj.CausalMask(), deterministic=True), base)
+    a = layer(x, mask=pj.CausalMask(), deterministic=False, rng=[3, 4])
+    b = layer(x, mask=pj.CausalMask(), deterministic=False, rng=[3, 4])
+    c = layer(x, mask=pj.CausalMask(), deterministic=False)
+    e = layer(x, mask=pj.CausalMask(), deterministic=False)
+    pj.check_status(d)
+    assert torch.equal(a, b) and not torch.equal(a, base) and not torch.equal(c, e)
+    assert float((a.float() - base.float()).abs().max()) < 1.0 and bool(torch.isfinite(a).all())
+
+
 def test_rms_norm_and_per_head_linear():
     from probjax_b200.latent_layer import per_head_linear, rms_norm
 

@@ -510,3 +510,30 @@ def test_low_rank_family_factors_and_dense_forms():
     assert M.lower_bias_structured(lg, 1, 2, 6, 9).low_rank == (lg,)  # folded: the gradient reaches the slopes
     with pytest.raises(ValueError, match="cannot broadcast"):
         M.lower_bias_structured(M.LearnedAlibiBias(torch.ones(3)), 1, 2, 6, 9)
+
+
+def test_latent_layer_dropout_resolution():
+    """tests/test_latent_attention.py:589-630 -- a rate needs an explicit `deterministic`; a kept stream
+    or a per-call key supplies the randomness; rates outside [0, 1) are rejected."""
+    from probjax_b200.latent_layer import MultiHeadLatentAttention
+
+    def layer(**kw):
+        return MultiHeadLatentAttention(2, 32, kv_lora_rank=16, dtype=torch.float32, device="cpu", **kw)
+
+    for rate in (-0.1, 1.0, 1.5):
+        with pytest.raises(ValueError, match="dropout_rate"):
+            layer(dropout_rate=rate)
+    plain = layer()
+    assert plain._resolve_dropout(None, None) == (0.0, None)  # no rate: `deterministic` is not needed
+    lay = layer(dropout_rate=0.1)
+    with pytest.raises(ValueError, match="No `deterministic` argument"):
+        lay._resolve_dropout(None, 7)  # a key alone must not switch dropout on
+    assert lay._resolve_dropout(True, 7) == (0.0, None)
+    assert lay._resolve_dropout(False, 7) == (0.1, 7)
+    lay = layer(dropout_rate=0.1, deterministic=False, seed=5)
+    a, b = lay._resolve_dropout(None, None), lay._resolve_dropout(None, None)
+    assert a[0] == b[0] == 0.1 and a[1] != b[1] and a[1][0] == 5  # the kept stream advances per call
+    lay = layer(dropout_rate=0.1, deterministic=False, keep_rngs=False)
+    with pytest.raises(ValueError, match="keep_rngs=True"):
+        lay._resolve_dropout(None, None)
+    assert lay._resolve_dropout(None, [1, 2]) == (0.1, [1, 2])
