@@ -651,9 +651,11 @@ def only_latent_decode(args, dev, pk):
     gl = torch.Generator(device=dev).manual_seed(5)
     ql = torch.randn((Bl, 1, Hl, Rl), generator=gl, device=dev).bfloat16()
     cl = (torch.randn((Bl, Sl, Rl), generator=gl, device=dev) * 0.5).bfloat16()
-    res = bench_extra("latent_decode", lambda: pj.mla_decode(ql, cl, sm_scale=Rl ** -0.5), args.steps, args.warmup,
-                      (cl.numel() * 2 + 2 * ql.numel() * 2) / 1e9, "GB/s", pk["hbm_gbs"], "hbm", pk["source"])
-    res["config"] = {"workload": f"absorbed latent decode bf16 B{Bl} H16 R576, 32768 keys each"}
+    res = bench_extra("latent_decode", lambda: pj.mla_decode(ql, cl, sm_scale=Rl ** -0.5, impl=args.kernel), args.steps,
+                      args.warmup, (cl.numel() * 2 + 2 * ql.numel() * 2) / 1e9, "GB/s", pk["hbm_gbs"], "hbm", pk["source"])
+    pj.check_status(dev)
+    res["config"] = {"workload": f"absorbed latent decode bf16 B{Bl} H16 R576, 32768 keys each",
+                     "kernel": args.kernel or "library's choice"}
     _emit(res)
 
 

@@ -469,6 +469,15 @@ int pjx_mla_decode_absorbed(const void* q, const void* cache, const int32_t* kv_
                             float* lse, int B, int Lq, int H, int R, int capacity, int dtype,
                             float sm_scale, int split_len, void* workspace, size_t workspace_bytes,
                             void* stream);
+/* The same with a choice of kernel and a status word.  impl: PJX_IMPL_AUTO, PJX_IMPL_GENERIC (the
+ * mma.sync kernel) or PJX_IMPL_SM100 (TMA + tcgen05: both products with the keys on the M axis of the
+ * MMA, the latent tile loaded once into a ring of sub-tiles; chosen by AUTO when `status` is given).
+ * `status` (device int32, may be NULL for the mma.sync kernel) receives PJX_ERR_DEVICE_TIMEOUT if
+ * a bounded wait of the tcgen05 kernel expires.  No counterpart in the reference. */
+int pjx_mla_decode_absorbed_impl(const void* q, const void* cache, const int32_t* kv_lengths, void* o,
+                                 float* lse, int B, int Lq, int H, int R, int capacity, int dtype,
+                                 float sm_scale, int split_len, int impl, void* workspace,
+                                 size_t workspace_bytes, int32_t* status, void* stream);
 size_t pjx_mla_decode_workspace_bytes(int B, int Lq, int H, int R, int capacity, int split_len);
 
 /*

@@ -84,6 +84,7 @@ SIGNATURES = {
     "pjx_mla_fwd": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64,
                          _i, _i, _i, _i, _i, _i, _i, _i, _i, _f, _i, _vp, _sz, _vp, _vp]),
     "pjx_mla_decode_absorbed": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _f, _i, _vp, _sz, _vp]),
+    "pjx_mla_decode_absorbed_impl": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _f, _i, _i, _vp, _sz, _vp, _vp]),
     "pjx_mla_decode_workspace_bytes": (_sz, [_i, _i, _i, _i, _i, _i]),
     "pjx_mla_workspace_bytes": (_sz, [_i, _i, _i, _i, _i, _i, _i, _i]),
     "pjx_attn_fwd_host": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i,

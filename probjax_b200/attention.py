@@ -430,10 +430,13 @@ def decode_forward(q, k_cache, v_cache, *, kv_lengths=None, sm_scale, split_len=
     return (o, lse) if return_lse else o
 
 
-def mla_decode(q, cache, *, kv_lengths=None, sm_scale=None, split_len=0, return_lse=False):
-    """One ``pjx_mla_decode_absorbed`` call on CUDA tensors: the decode step of absorbed latent
+def mla_decode(q, cache, *, kv_lengths=None, sm_scale=None, split_len=0, return_lse=False, impl=None):
+    """One ``pjx_mla_decode_absorbed_impl`` call on CUDA tensors: the decode step of absorbed latent
     attention, ``q [B, Lq, H, R]`` over ``cache [B, S, R]`` with ``K = V = cache`` (``Lq <= 16``,
-    latent width 128 / 256 / 512 / 576, bf16 or fp16)."""
+    latent width 128 / 256 / 512 / 576, bf16 or fp16).  ``impl``: ``None`` (the tcgen05 kernel),
+    ``"b200:generic"`` (the mma.sync kernel) or ``"b200:tcgen05"``."""
+    if impl not in _IMPL:
+        raise ValueError(f"impl must be None or one of {sorted(k for k in _IMPL if k)}")
     _require_gpu()
     if not q.is_cuda or q.dim() != 4 or cache.dim() != 3:
         raise ValueError("mla_decode takes CUDA tensors q [B, Lq, H, R] and cache [B, S, R]")
@@ -455,8 +458,9 @@ def mla_decode(q, cache, *, kv_lengths=None, sm_scale=None, split_len=0, return_
     lse = torch.empty((B, H, Lq), dtype=torch.float32, device=dev) if return_lse else None
     ws = _scratch_bytes(dev, "mla_decode", L.pjx_mla_decode_workspace_bytes(B, Lq, H, R, S, int(split_len)))
     with torch.cuda.device(dev):
-        rc = L.pjx_mla_decode_absorbed(_ptr(q), _ptr(cache), _ptr(kvl), _ptr(o), _ptr(lse), B, Lq, H, R, S,
-                                       _DTYPES[q.dtype], float(sm_scale), int(split_len), _ptr(ws), ws.numel(), _stream(dev))
+        rc = L.pjx_mla_decode_absorbed_impl(_ptr(q), _ptr(cache), _ptr(kvl), _ptr(o), _ptr(lse), B, Lq, H, R, S,
+                                            _DTYPES[q.dtype], float(sm_scale), int(split_len), _IMPL[impl], _ptr(ws),
+                                            ws.numel(), _ptr(_status_word(dev)), _stream(dev))
     _lib.check(rc)
     return (o, lse) if return_lse else o
 

@@ -33,6 +33,7 @@ SOURCES = [
     "attn_fwd_sm100.cu",
     "attn_decode.cu",
     "attn_decode_latent.cu",
+    "attn_decode_latent_sm100.cu",
     "kv_cache.cu",
     "rope.cu",
     "rmsnorm.cu",

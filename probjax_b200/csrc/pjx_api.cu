@@ -486,6 +486,13 @@ size_t pjx_mla_decode_workspace_bytes(int B, int Lq, int H, int R, int capacity,
 int pjx_mla_decode_absorbed(const void* q, const void* cache, const int32_t* kv_lengths, void* o, float* lse, int B,
                             int Lq, int H, int R, int capacity, int dtype, float sm_scale, int split_len,
                             void* workspace, size_t workspace_bytes, void* stream) {
+  return pjx_mla_decode_absorbed_impl(q, cache, kv_lengths, o, lse, B, Lq, H, R, capacity, dtype, sm_scale, split_len,
+                                      PJX_IMPL_AUTO, workspace, workspace_bytes, nullptr, stream);
+}
+
+int pjx_mla_decode_absorbed_impl(const void* q, const void* cache, const int32_t* kv_lengths, void* o, float* lse,
+                                 int B, int Lq, int H, int R, int capacity, int dtype, float sm_scale, int split_len,
+                                 int impl, void* workspace, size_t workspace_bytes, int32_t* status, void* stream) {
   if (B < 0 || Lq < 0 || H < 1 || R < 1 || capacity < 0) return fail(PJX_ERR_BAD_ARG, "mla decode: bad dimension");
   int rc = decode_limits(B, H, capacity);
   if (rc) return rc;
@@ -513,8 +520,18 @@ int pjx_mla_decode_absorbed(const void* q, const void* cache, const int32_t* kv_
   const size_t parts = (size_t)B * p.Hkv * p.num_splits * p.rows;
   p.o_part = static_cast<float*>(workspace);
   p.lse_part = reinterpret_cast<float*>(static_cast<char*>(workspace) + align_up(parts * R * sizeof(float)));
+  p.status = status;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  if ((rc = launch_decode_latent_splits(p, dtype, st))) return rc;
+  if (impl != PJX_IMPL_AUTO && impl != PJX_IMPL_GENERIC && impl != PJX_IMPL_SM100)
+    return fail(PJX_ERR_BAD_ARG, "mla decode: unknown impl %d", impl);
+  // AUTO: the tcgen05 kernel where the step streams at least 64 MiB of latent (measured 13-57 % faster there:
+  // B16 H16 R576 32k keys 4.28 against 3.78 TB/s, B64 8k keys 4.67 against 3.65, H = 128 0.76 against 1.20 ms);
+  // below that the two are within a few per cent and the mma.sync kernel has the shorter prologue
+  const bool big = (double)B * p.Hkv * capacity * R * 2.0 >= 64.0 * 1024 * 1024;
+  const bool tc = (impl == PJX_IMPL_SM100 || (impl == PJX_IMPL_AUTO && big)) && decode_latent_tc_supported(p, dtype);
+  if (impl == PJX_IMPL_SM100 && !tc)
+    return fail(PJX_ERR_UNSUPPORTED, "the tcgen05 latent decode needs a status word and a cache of fewer than 2^31 rows");
+  if ((rc = tc ? launch_decode_latent_tc_splits(p, dtype, st) : launch_decode_latent_splits(p, dtype, st))) return rc;
   return launch_decode_combine(p, dtype, st);
 }
 

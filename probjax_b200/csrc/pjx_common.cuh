@@ -183,6 +183,9 @@ int launch_decode_combine(const DecodeParams& p, int dtype, cudaStream_t stream)
 // Absorbed latent decode (K = V = cache [B, S, R]): split kernel writing the decode partial layout.
 bool decode_latent_supported(int R, int dtype);
 int launch_decode_latent_splits(const DecodeParams& p, int dtype, cudaStream_t stream);
+// The same on the tcgen05 tensor cores (attn_decode_latent_sm100.cu); needs p.status.
+bool decode_latent_tc_supported(const DecodeParams& p, int dtype);
+int launch_decode_latent_tc_splits(const DecodeParams& p, int dtype, cudaStream_t stream);
 int launch_combine_parts(const float* o_parts, const float* lse_parts, int n_parts, int64_t n_rows,
                          int Dv, void* o, float* lse, int dtype, cudaStream_t stream);
 // C[M, N] = A[M, K] . B[N, K]^T, all row-major, fp32 accumulation, C in `dtype`.

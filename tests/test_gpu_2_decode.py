@@ -417,10 +417,13 @@ def test_absorbed_latent_decode(R, H, Lq, dtype):
         poisoned[b, int(lens[b]):] = float("nan")
     got, lse = pj.mla(q.to(d), poisoned.to(d), mask=pj.KVLenMask(lens), sm_scale=sc, return_lse=True)
     assert_close(got, lse, want, want_lse, dtype, f"absorbed latent decode R={R} H={H} Lq={Lq}")
-    for split_len in (64, 256, 1536):
-        got2, lse2 = pj.mla_decode(q.to(d), poisoned.to(d), kv_lengths=lens.to(d), sm_scale=sc, split_len=split_len,
-                                   return_lse=True)
-        assert_close(got2, lse2, want, want_lse, dtype, f"split_len {split_len}")
+    pj.check_status(d)
+    for impl in ("b200:tcgen05", "b200:generic"):  # TMA + tcgen05 kernel (the default) and the mma.sync kernel
+        for split_len in (64, 256, 1536):
+            got2, lse2 = pj.mla_decode(q.to(d), poisoned.to(d), kv_lengths=lens.to(d), sm_scale=sc, split_len=split_len,
+                                       return_lse=True, impl=impl)
+            pj.check_status(d)
+            assert_close(got2, lse2, want, want_lse, dtype, f"{impl} split_len {split_len}")
     # no lengths: the whole cache
     got3 = pj.mla_decode(q.to(d), cache.to(d), sm_scale=sc)
     want3 = oracle.xla_attention(q, shared, shared, sm_scale=sc)
