@@ -549,7 +549,7 @@ def main():
         if dist_on and "value" in extras["decode_128k"]:
             out["roofline"]["decode_128k_sharded_gbs"] = extras["decode_128k"]["value"]
             out["roofline"]["decode_128k_sharded_max_abs_err"] = extras["decode_128k"].get("max_abs_err")
-        out["extras"] = extras
+        out["extras"] = compact_extras(extras, world)
 
     if rank == 0 and not args.skip_cpu and world == 1:
         try:
@@ -566,6 +566,30 @@ def main():
         dist.destroy_process_group()
     if failed:
         raise SystemExit("parity failure: " + "; ".join(failed))
+
+
+def compact_extras(extras, world):
+    """Keeps the one JSON line short enough to survive a truncated capture of stdout: the bound of an entry
+    follows from its unit and is dropped; the slower variants of the sharded decode keep their time, rate
+    and error only; a multi-GPU line keeps the entries that depend on the number of GPUs (the others are in
+    the one-GPU line of the same build)."""
+    keep_multi = ("prefill_causal", "decode_32k", "decode_ragged", "decode_32k_seq_sharded", "decode_128k")
+    out = {}
+    for name, entry in extras.items():
+        if world > 1 and name not in keep_multi:
+            continue
+        if isinstance(entry, dict):
+            entry = {k: v for k, v in entry.items() if k != "bound"}
+            if name == "decode_32k_seq_sharded":
+                for mode, res in list(entry.items()):
+                    if isinstance(res, dict):
+                        keys = ("ms", "value", "frac", "max_abs_err", "lse_err", "oracle_max_abs_err", "oracle_lse_err",
+                                "parity_failure", "error") if mode == "fused" else ("ms", "value", "max_abs_err",
+                                                                                    "parity_failure", "error")
+                        entry[mode] = {k: res[k] for k in keys if k in res}
+                entry["unit"] = "GB/s aggregate"
+        out[name] = entry
+    return out
 
 
 def _walk(d, prefix=""):

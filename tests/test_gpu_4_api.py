@@ -317,7 +317,9 @@ def test_latent_attention_layer_dropout():
     e = layer(x, mask=pj.CausalMask(), deterministic=False)
     pj.check_status(d)
     assert torch.equal(a, b) and not torch.equal(a, base) and not torch.equal(c, e)
-    assert float((a.float() - base.float()).abs().max()) < 1.0 and bool(torch.isfinite(a).all())
+    assert bool(torch.isfinite(a).all())
+    # dropout is unbiased: the difference to the deterministic output averages out
+    assert abs(float((a.float() - base.float()).mean())) < 0.05 * float(base.float().abs().mean())
 
 
 def test_rms_norm_and_per_head_linear():
