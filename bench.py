@@ -541,7 +541,8 @@ def main():
             cl = (torch.randn((Bl, Sl, Rl), generator=gl, device=dev) * 0.5).bfloat16()
             extras["latent_decode_32k"] = bench_extra(
                 "latent_decode", lambda: pj.mla_decode(ql, cl, sm_scale=Rl ** -0.5), xs, xw,
-                (cl.numel() * 2 + 2 * ql.numel() * 2) / 1e9, "GB/s", pk["hbm_gbs"], "hbm", pk["source"])
+                (cl.numel() * 2 + 2 * ql.numel() * 2) / 1e9, "GB/s", pk["hbm_gbs"], "hbm", pk["source"],
+                "profiles/decode_latent_b4_32k.md")
             del ql, cl
         except Exception as e:
             extras["latent_decode_32k"] = {"error": str(e)[:200]}
