@@ -259,9 +259,10 @@ decode_latent_tc_kernel(const __grid_constant__ CUtensorMap tm_c, const DecodePa
     // ------------------------------------------------------ MMA issuer, scores
     if (lane == 0) {
       constexpr uint32_t idesc_s = make_idesc(TK, NROW, BF16, false, false);
-      // descriptors differ only in the address field (bits 0-13, address >> 4): add to a base
+      // descriptors differ only in the address field (bits 0-13, address >> 4): add to a base.  The address is
+      // masked to the 18 bits of the field (bits above them would spill into the leading-offset field)
       const uint64_t kdesc = make_smem_desc(0, 16, 1024);
-      const uint32_t ring16 = (sbase + C::OFF_QRING) >> 4, q16 = (sbase + C::OFF_Q) >> 4;
+      const uint32_t ring16 = ((sbase + C::OFF_QRING) & 0x3FFFF) >> 4, q16 = ((sbase + C::OFF_Q) & 0x3FFFF) >> 4;
       bool ok = true;
       for (int t = 0, n = 0; t < n_tiles && ok; ++t) {
         if (t >= 2) {  // S^T[t % 2] is free once every softmax thread has written P(t - 2)
@@ -287,7 +288,7 @@ decode_latent_tc_kernel(const __grid_constant__ CUtensorMap tm_c, const DecodePa
     if (lane == 0) {
       constexpr uint32_t idesc_o = make_idesc(128, NROW, BF16, true, false);
       const uint64_t adesc = make_smem_desc(0, SUB_BYTES, 1024), bdesc = make_smem_desc(0, 16, 1024);
-      const uint32_t ring16 = (sbase + C::OFF_PRING) >> 4, p16 = (sbase + C::OFF_P) >> 4;
+      const uint32_t ring16 = ((sbase + C::OFF_PRING) & 0x3FFFF) >> 4, p16 = ((sbase + C::OFF_P) & 0x3FFFF) >> 4;
       bool ok = true;
       for (int t = 0, n = 0; t < n_tiles && ok; ++t) {
         ok = mbar_wait(BAR(P_FULL + (t & 1)), (t >> 1) & 1, abort_flag);
