@@ -35,6 +35,11 @@ namespace {
 
 using namespace sm100;
 
+// Timing experiments (python -m probjax_b200.build --what-if N): 0 = the shipped kernel.
+#ifndef PJX_EXP_VARIANT
+#define PJX_EXP_VARIANT 0
+#endif
+
 constexpr int BM = 128;          // rows per query tile (= tensor-memory lanes)
 constexpr int NTHREADS = 320;    // 10 warps
 
@@ -137,9 +142,6 @@ __device__ __forceinline__ void exp_pack_store(const float (&s)[BN], float2 cs2,
 // polynomial (max relative error 7.5e-5, far below the 16-bit rounding of P); n is added to the
 // exponent field.  x is clamped at -126, so the result is never exactly 0: only for tiles that
 // need no mask (a masked score must give exactly 0).
-#ifndef PJX_EXP_VARIANT
-#define PJX_EXP_VARIANT 0
-#endif
 template <int BN, bool BF16, int EMU>
 __device__ __forceinline__ void exp_pack_store_emu(const float (&s)[BN], float2 cs2, float2 nm2, float2& sum0,
                                                    float2& sum1, uint32_t s_addr) {
