@@ -27,6 +27,10 @@
 // Every barrier wait is bounded: on expiry the role raises the CTA abort flag,
 // all roles drain, tensor memory is freed and the status word gets
 // PJX_ERR_DEVICE_TIMEOUT.
+#include <atomic>
+#include <cstdlib>
+#include <type_traits>
+
 #include "pjx_common.cuh"
 #include "sm100_ptx.cuh"
 
@@ -211,13 +215,25 @@ __device__ __forceinline__ void exp_pack_store_scaled(const float (&s)[BN], floa
 // MOD (implies BAND): structured masks and score modifiers (score_mod.cuh) are evaluated by the
 // softmax threads on every tile: the scaled score of (row, key) is passed through the modifiers
 // and the mask part decides per element; no tile beyond the band / prefix range is visited.
-template <int DQK, int DV, int BN, int KST, int VST, bool BF16, int BIAS, bool BAND, bool MOD = false>
+//
+// SPLIT: the CTA takes one HALF of the KV tiles of its work item (two CTAs per item, blockIdx.x & 1 = the
+// half) and leaves an fp32 partial -- O normalised by its own sum, base-2 log-sum-exp -- in a workspace
+// (p.o / p.lse then point there) for `combine_halves_kernel`.  Used for the work items of a last, partly
+// filled wave of a grid of equal items: 512 items on 148 SMs are 3.46 waves and cost 4; with the last 68
+// items cut in two, 136 CTAs of half length fill that wave.
+//
+// `order_item0` packs the order block width (low 8 bits) and the index of the grid's first work item.
+template <int DQK, int DV, int BN, int KST, int VST, bool BF16, int BIAS, bool BAND, bool MOD = false, bool SPLIT = false>
 __global__ void __launch_bounds__(NTHREADS, 1)
 attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                       const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_b,
-                      const __grid_constant__ CUtensorMap tm_o, const FwdParamsCore p, const int order_w,
+                      const __grid_constant__ CUtensorMap tm_o, const FwdParamsCore p, const int order_item0,
                       const ScoreMod smod) {
   constexpr bool HAS_BIAS = BIAS != 0;
+  static_assert(!SPLIT || (!BAND && !MOD && BIAS == 0), "KV halves are built for the plain variant");
+  const int order_w = order_item0 & 0xff;
+  const int item = (order_item0 >> 8) + (SPLIT ? static_cast<int>(blockIdx.x >> 1) : static_cast<int>(blockIdx.x));
+  const int half = SPLIT ? static_cast<int>(blockIdx.x & 1) : 0;
   static_assert(!MOD || (BAND && BIAS != 2), "the modifier variant builds on the band variant without staged bias");
   using C = Cfg<DQK, DV, BN, KST, VST, BIAS == 2>;
   extern __shared__ unsigned char smem_unaligned[];
@@ -249,8 +265,8 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
   // share few K/V heads, which keeps their tiles in the near L2 partition.
   const int n_bh = p.Hq * p.B;
   const int n_qt = (p.Lq + 2 * BM - 1) / (2 * BM);
-  const int blk = blockIdx.x / (order_w * n_qt);
-  const int rem = blockIdx.x - blk * (order_w * n_qt);
+  const int blk = item / (order_w * n_qt);
+  const int rem = item - blk * (order_w * n_qt);
   const int wc = min(order_w, n_bh - blk * order_w);
   const int qt = n_qt - 1 - rem / wc;
   const int bh = blk * order_w + rem % wc;
@@ -301,6 +317,13 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
         const int lim = p.causal ? min(kv_len, min(qs + BM, p.Lq)) : kv_len;
         n_t[t] = (lim + BN - 1) / BN;
       }
+    }
+    if constexpr (SPLIT) {  // this CTA's half of the tiles (the launcher takes unmasked problems only: equal counts)
+      const int all = max(n_t[0], n_t[1]);
+      j_base = half ? all / 2 : 0;
+      const int mine = half ? all - all / 2 : all / 2;
+#pragma unroll
+      for (int t = 0; t < 2; ++t) n_t[t] = n_t[t] > 0 ? mine : 0;
     }
   }
   const int n = max(n_t[0], n_t[1]);
@@ -682,7 +705,24 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
         ok = mbar_wait(BAR(O_FULL + t), 0, abort_flag);
         ok = __all_sync(0xffffffffu, ok);
       }
-      if (ok) {
+      if (ok && SPLIT) {
+        // fp32 partial of this half: row slot = ((work item of this grid) * 2 + tile) * 128 + row in tile
+        tc_fence_after();
+        const int64_t slot = ((int64_t)(blockIdx.x >> 1) * 2 + t) * BM + r_in;
+        const int64_t slots = (int64_t)(gridDim.x >> 1) * 2 * BM;
+        float* po = static_cast<float*>(p.o) + ((int64_t)half * slots + slot) * DV;
+#pragma unroll
+        for (int c = 0; c < DV / 32; ++c) {
+          float o[32];
+          tmem_ld32f(o_addr + c * 32, o);
+          tmem_wait_ld();
+#pragma unroll
+          for (int i = 0; i < 8; ++i)
+            *reinterpret_cast<float4*>(po + c * 32 + 4 * i) =
+                make_float4(o[4 * i] * inv, o[4 * i + 1] * inv, o[4 * i + 2] * inv, o[4 * i + 3] * inv);
+        }
+        p.lse[half * slots + slot] = l > 0.f ? m_ref + log2f(l) : -INFINITY;
+      } else if (ok) {
         tc_fence_after();
         if (threadIdx.x == 320 - 128) PJX_CTA_AT(4);
         // O leaves through shared memory: every thread writes its row (16-bit, 128-byte-swizzled
@@ -798,6 +838,68 @@ bool bias_can_be_staged(const FwdParams& p) {
          p.bias_bs % 4 == 0;
 }
 
+// Merges the two KV halves of the work items `item0 ..` (SPLIT CTAs): one warp per query row.
+//   o = (w0 o0 + w1 o1) / (w0 + w1),  w = 2^(lse2 - max),  lse = (max + log2(w0 + w1)) ln 2
+// The work-item -> (batch, head, first row) mapping is the forward kernel's.
+template <typename T, int DV>
+__global__ void __launch_bounds__(256) combine_halves_kernel(const float* __restrict__ part_o, const float* __restrict__ part_lse,
+                                                            T* __restrict__ o, float* __restrict__ lse, int n_items, int item0,
+                                                            int order_w, int B, int Lq, int Hq) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int64_t slot = (int64_t)blockIdx.x * 8 + warp;  // ((item - item0) * 2 + tile) * BM + row in tile
+  const int64_t slots = (int64_t)n_items * 2 * BM;
+  if (slot >= slots) return;
+  const int item = item0 + (int)(slot / (2 * BM));
+  const int n_bh = Hq * B, n_qt = (Lq + 2 * BM - 1) / (2 * BM);
+  const int blk = item / (order_w * n_qt);
+  const int rem = item - blk * (order_w * n_qt);
+  const int wc = min(order_w, n_bh - blk * order_w);
+  const int qt = n_qt - 1 - rem / wc;
+  const int bh = blk * order_w + rem % wc;
+  const int h = bh % Hq, b = bh / Hq;
+  const int row = qt * 2 * BM + (int)(slot % (2 * BM));
+  if (row >= Lq) return;
+  const float l0 = part_lse[slot], l1 = part_lse[slots + slot];
+  const float mx = fmaxf(l0, l1);
+  const float w0 = mx == -INFINITY ? 0.f : exp2f(l0 - mx), w1 = mx == -INFINITY ? 0.f : exp2f(l1 - mx);
+  const float den = w0 + w1;
+  const float inv = den > 0.f ? 1.f / den : 0.f;
+  const float* p0 = part_o + slot * DV;
+  const float* p1 = part_o + (slots + slot) * DV;
+  T* dst = o + (((int64_t)b * Lq + row) * Hq + h) * DV;
+  static_assert(DV % 128 == 0 || DV == 64, "one or more float4 per lane");
+#pragma unroll
+  for (int c = lane * 4; c < DV; c += 128) {
+    const float4 a = *reinterpret_cast<const float4*>(p0 + c), bb = *reinterpret_cast<const float4*>(p1 + c);
+    T r[4] = {Elem<T>::from_f((w0 * a.x + w1 * bb.x) * inv), Elem<T>::from_f((w0 * a.y + w1 * bb.y) * inv),
+              Elem<T>::from_f((w0 * a.z + w1 * bb.z) * inv), Elem<T>::from_f((w0 * a.w + w1 * bb.w) * inv)};
+    *reinterpret_cast<uint2*>(dst + c) = *reinterpret_cast<const uint2*>(r);
+  }
+  if (lse && lane == 0) lse[((int64_t)b * Hq + h) * Lq + row] = den > 0.f ? (mx + log2f(den)) * kLn2 : INFINITY;
+}
+
+// The partials of the KV halves come from the stream-ordered allocator.  Its default pool hands freed memory
+// back to the driver at every synchronisation, which would make each call pay for a fresh mapping: keep it.
+void keep_pool_memory() {
+  static std::atomic<bool> done[64];
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64 || done[dev].exchange(true)) return;
+  cudaMemPool_t pool;
+  if (cudaDeviceGetDefaultMemPool(&pool, dev) == cudaSuccess) {
+    uint64_t keep = 256ull << 20;  // the partials are at most 74 items x 2 halves x 256 rows x Dv floats (< 40 MB)
+    uint64_t cur = 0;
+    if (cudaMemPoolGetAttribute(pool, cudaMemPoolAttrReleaseThreshold, &cur) == cudaSuccess && cur < keep)
+      cudaMemPoolSetAttribute(pool, cudaMemPoolAttrReleaseThreshold, &keep);
+  }
+}
+
+int sm_count() {
+  int dev = 0, v = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || v < 1)
+    v = 148;
+  return v;
+}
+
 template <int DQK, int DV, int BN, int KST, int VST, bool BF16, int BIAS, bool BAND = false, bool MOD = false>
 int launch_one(const FwdParams& p, int dtype, cudaStream_t stream) {
   using C = Cfg<DQK, DV, BN, KST, VST, BIAS == 2>;
@@ -820,6 +922,48 @@ int launch_one(const FwdParams& p, int dtype, cudaStream_t stream) {
   dim3 grid((unsigned)(((p.Lq + 2 * BM - 1) / (2 * BM)) * (int64_t)p.Hq * p.B));
   // triangular work (an upper bound on the keys only): heavy-first order in blocks of 16 pairs
   const int order_w = (p.band_hi < PJX_BAND_NO_UPPER && p.band_lo == PJX_BAND_NO_LOWER) ? 16 : 1;
+  if constexpr (BIAS == 0 && !BAND && !MOD && DQK == DV) {
+    // Equal work items (no mask, no key lengths) come in waves of one CTA per SM; a last wave that fills at
+    // most half of the SMs is cut into KV halves (two CTAs per item, fp32 partials, one small merge kernel).
+    const int64_t n_items = grid.x;
+    const int sms = sm_count();
+    const int64_t full = n_items / sms * sms;
+    const int tail = (int)(n_items - full);
+    const int n_kv = (p.Lkv + BN - 1) / BN;
+    static const bool off = getenv("PJX_FWD_SPLIT_TAIL") && atoi(getenv("PJX_FWD_SPLIT_TAIL")) == 0;
+    if (!off && !p.causal && !p.kv_lengths && tail > 0 && 2 * tail <= sms && n_kv >= 8 && n_items < (1 << 23)) {
+      const size_t slots = (size_t)tail * 2 * BM;
+      const size_t o_bytes = 2 * slots * DV * sizeof(float), l_bytes = 2 * slots * sizeof(float);
+      void* ws = nullptr;
+      keep_pool_memory();
+      if (cudaMallocAsync(&ws, o_bytes + l_bytes, stream) == cudaSuccess) {
+        if (full > 0) {
+          kern<<<dim3((unsigned)full), NTHREADS, C::SMEM_BYTES, stream>>>(tq, tk, tv, tb, to, static_cast<const FwdParamsCore&>(p),
+                                                                          order_w, p.mod);
+          count_launch();
+        }
+        auto kern_h = attn_fwd_sm100_kernel<DQK, DV, BN, KST, VST, BF16, 0, false, false, true>;
+        rc = check_cuda(cudaFuncSetAttribute(kern_h, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES),
+                        "cudaFuncSetAttribute(sm100 fwd, KV halves)");
+        if (!rc) {
+          FwdParamsCore ph = static_cast<const FwdParamsCore&>(p);
+          ph.o = ws;
+          ph.lse = reinterpret_cast<float*>(static_cast<char*>(ws) + o_bytes);
+          kern_h<<<dim3(2u * (unsigned)tail), NTHREADS, C::SMEM_BYTES, stream>>>(tq, tk, tv, tb, to, ph,
+                                                                               order_w | ((int)full << 8), p.mod);
+          count_launch();
+          using T = typename std::conditional<BF16, __nv_bfloat16, __half>::type;
+          combine_halves_kernel<T, DV><<<dim3((unsigned)((slots + 7) / 8)), 256, 0, stream>>>(
+              static_cast<const float*>(ws), ph.lse, static_cast<T*>(p.o), p.lse, tail, (int)full, order_w, p.B, p.Lq, p.Hq);
+          count_launch();
+          rc = check_cuda(cudaGetLastError(), "sm100 forward launch (with KV halves)");
+        }
+        cudaFreeAsync(ws, stream);
+        return rc;
+      }
+      (void)cudaGetLastError();  // no memory for the partials: one grid as usual
+    }
+  }
   kern<<<grid, NTHREADS, C::SMEM_BYTES, stream>>>(tq, tk, tv, tb, to, static_cast<const FwdParamsCore&>(p), order_w, p.mod);
   count_launch();
   return check_cuda(cudaGetLastError(), "sm100 forward launch");

@@ -227,3 +227,29 @@ def test_rows_past_the_valid_length_may_hold_anything(d, dv):
                                             sm_scale=sc, return_lse=True, impl="b200:tcgen05")
         assert torch.isfinite(got).all()
         assert torch.equal(got, ref) and torch.equal(lse, lse_ref)
+
+
+@pytest.mark.parametrize("dtype,d", [(torch.bfloat16, 128), (torch.float16, 64)])
+@pytest.mark.parametrize("b,h,lq,lkv", [(1, 3, 600, 1100), (2, 80, 512, 1024), (1, 2, 256, 4096)])
+def test_last_wave_cut_into_kv_halves(dtype, d, b, h, lq, lkv):
+    """Unmasked problems whose last wave of work items fills at most half of the SMs run those items as
+    two CTAs each (KV halves, fp32 partials, a merge kernel): 6, 320 = 2 x 148 + 24 and 2 work items here.
+    Output and log-sum-exp against the oracle, and bit-repeatable."""
+    q = randn((b, lq, h, d), dtype, 1)
+    k = randn((b, lkv, max(h // 2, 1), d), dtype, 2) if h % 2 == 0 else randn((b, lkv, h, d), dtype, 2)
+    v = randn(tuple(k.shape), dtype, 3)
+    sc = 1 / math.sqrt(d)
+    n0 = pj._lib.launch_count()
+    out, lse = _run(q, k, v, sm_scale=sc)
+    launches = pj._lib.launch_count() - n0
+    assert launches >= 2, "the split path was expected to launch the halves and the merge"
+    want, want_lse = oracle_fwd(q[:, :, : min(h, 6)], k[:, :, : max(min(h, 6) // (2 if h % 2 == 0 else 1), 1)],
+                                v[:, :, : max(min(h, 6) // (2 if h % 2 == 0 else 1), 1)], sm_scale=sc)
+    assert_close(out[:, :, : min(h, 6)], lse[:, : min(h, 6)], want, want_lse, dtype, f"kv halves b{b} h{h} lq{lq} lkv{lkv}")
+    if h > 6:  # the last heads too (their work items are the ones cut in two)
+        hk = k.shape[2]
+        g = h // hk
+        want, want_lse = oracle_fwd(q[:, :, -g:], k[:, :, -1:], v[:, :, -1:], sm_scale=sc)
+        assert_close(out[:, :, -g:], lse[:, -g:], want, want_lse, dtype, "kv halves, last heads")
+    again, lse2 = _run(q, k, v, sm_scale=sc)
+    assert torch.equal(out, again) and torch.equal(lse, lse2)
