@@ -29,6 +29,7 @@
 // PJX_ERR_DEVICE_TIMEOUT.
 #include <atomic>
 #include <cstdlib>
+#include <mutex>
 #include <type_traits>
 
 #include "pjx_common.cuh"
@@ -218,7 +219,7 @@ __device__ __forceinline__ void exp_pack_store_scaled(const float (&s)[BN], floa
 //
 // SPLIT: the CTA takes one HALF of the KV tiles of its work item (two CTAs per item, blockIdx.x & 1 = the
 // half) and leaves an fp32 partial -- O normalised by its own sum, base-2 log-sum-exp -- in a workspace
-// (p.o / p.lse then point there) for `combine_halves_kernel`.  Used for the work items of a last, partly
+// (p.o / p.lse then point there); the half that finishes second merges the two and writes the result.  Used for the work items of a last, partly
 // filled wave of a grid of equal items: 512 items on 148 SMs are 3.46 waves and cost 4; with the last 68
 // items cut in two, 136 CTAs of half length fill that wave.
 //
@@ -275,7 +276,9 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
   const int q0 = qt * 2 * BM;
 
   int kv_len = p.Lkv;
-  if (p.kv_lengths) kv_len = max(0, min(kv_len, p.kv_lengths[b]));
+  if constexpr (!SPLIT) {  // (a SPLIT launch has no key lengths; the field carries its arrival counters)
+    if (p.kv_lengths) kv_len = max(0, min(kv_len, p.kv_lengths[b]));
+  }
   int n_t[2];
   int j_base = 0;  // first KV tile of the loop (BAND only)
   if constexpr (BAND) {
@@ -705,23 +708,61 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
         ok = mbar_wait(BAR(O_FULL + t), 0, abort_flag);
         ok = __all_sync(0xffffffffu, ok);
       }
-      if (ok && SPLIT) {
-        // fp32 partial of this half: row slot = ((work item of this grid) * 2 + tile) * 128 + row in tile
-        tc_fence_after();
-        const int64_t slot = ((int64_t)(blockIdx.x >> 1) * 2 + t) * BM + r_in;
-        const int64_t slots = (int64_t)(gridDim.x >> 1) * 2 * BM;
-        float* po = static_cast<float*>(p.o) + ((int64_t)half * slots + slot) * DV;
+      // SPLIT: this half's fp32 partial goes to the workspace; the half that arrives second (a counter per work
+      // item and query tile) merges both and writes the final rows, so no CTA ever waits for another.
+      float ca = inv, cb = 0.f;          // final value = O_tmem * ca + other_partial * cb
+      const float* other = nullptr;
+      float lse_final = 0.f;
+      bool writes_out = true;
+      if constexpr (SPLIT) {
+        if (ok) {
+          tc_fence_after();
+          const int64_t slot = ((int64_t)(blockIdx.x >> 1) * 2 + t) * BM + r_in;
+          const int64_t slots = (int64_t)(gridDim.x >> 1) * 2 * BM;
+          float* po = static_cast<float*>(p.o) + ((int64_t)half * slots + slot) * DV;
 #pragma unroll
-        for (int c = 0; c < DV / 32; ++c) {
-          float o[32];
-          tmem_ld32f(o_addr + c * 32, o);
-          tmem_wait_ld();
+          for (int c = 0; c < DV / 32; ++c) {
+            float o[32];
+            tmem_ld32f(o_addr + c * 32, o);
+            tmem_wait_ld();
 #pragma unroll
-          for (int i = 0; i < 8; ++i)
-            *reinterpret_cast<float4*>(po + c * 32 + 4 * i) =
-                make_float4(o[4 * i] * inv, o[4 * i + 1] * inv, o[4 * i + 2] * inv, o[4 * i + 3] * inv);
+            for (int i = 0; i < 8; ++i)
+              *reinterpret_cast<float4*>(po + c * 32 + 4 * i) =
+                  make_float4(o[4 * i] * inv, o[4 * i + 1] * inv, o[4 * i + 2] * inv, o[4 * i + 3] * inv);
+          }
+          const float lse_self = l > 0.f ? m_ref + log2f(l) : -INFINITY;
+          p.lse[half * slots + slot] = lse_self;
+          __threadfence();
+          // rendezvous of the tile's 128 threads (the bias barrier of this tile is free in this variant), one
+          // counter increment, second rendezvous to hand its result round
+          volatile int* arrived = reinterpret_cast<volatile int*>(tmem_slot + 2 + t);
+          mbar_arrive(BAR(B_EMPTY + t));
+          ok = mbar_wait(BAR(B_EMPTY + t), 0, abort_flag);
+          ok = __all_sync(0xffffffffu, ok);
+          if (ok) {
+            if (r_in == 0)
+              *arrived = atomicAdd(const_cast<int32_t*>(p.kv_lengths) + (blockIdx.x >> 1) * 2 + t, 1);
+            mbar_arrive(BAR(B_EMPTY + t));
+            ok = mbar_wait(BAR(B_EMPTY + t), 1, abort_flag);
+            ok = __all_sync(0xffffffffu, ok);
+          }
+          writes_out = ok && *arrived == 1;
+          if (writes_out) {
+            __threadfence();
+            const int64_t oslot = (int64_t)(half ^ 1) * slots + slot;
+            other = static_cast<const float*>(p.o) + oslot * DV;
+            const float lse_other = p.lse[oslot];
+            const float mx = fmaxf(lse_self, lse_other);
+            const float ws = mx == -INFINITY ? 0.f : exp2f(lse_self - mx), wo = mx == -INFINITY ? 0.f : exp2f(lse_other - mx);
+            const float den = ws + wo;
+            ca = ws;  // weights of this half and of the other; the merge below is written in half order,
+            cb = wo;  // so that the result does not depend on which half arrived second
+            lse_final = den > 0.f ? (mx + log2f(den)) * kLn2 : INFINITY;
+          }
         }
-        p.lse[half * slots + slot] = l > 0.f ? m_ref + log2f(l) : -INFINITY;
+      }
+      if (ok && !writes_out) {
+        // first half to arrive: nothing more to do
       } else if (ok) {
         tc_fence_after();
         if (threadIdx.x == 320 - 128) PJX_CTA_AT(4);
@@ -730,6 +771,8 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
         // thread hands the tile to a TMA store, which clips rows past Lq. Stores straight from the
         // registers would touch 32 separate rows per instruction.
         const uint32_t stage = sbase + C::OFF_Q + t * C::Q_TILE_BYTES;
+        const float out_scale = SPLIT ? 1.f : inv;  // a merged value carries its normalisation already
+        const float iden = (ca + cb) > 0.f ? 1.f / (ca + cb) : 0.f;  // SPLIT: 1 / (sum of the halves' weights)
 #pragma unroll
         for (int c = 0; c < DV / 32; ++c) {
           float o[32];
@@ -740,16 +783,30 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
 #pragma unroll
             for (int i = 0; i < 32; ++i) o[i] = 0.f;
           }
+          if constexpr (SPLIT) {  // merged value of the two halves, the other half's partial read back from L2
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+              const float4 w = *reinterpret_cast<const float4*>(other + c * 32 + 4 * i);
+              const float ov[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+              for (int e = 0; e < 4; ++e) {
+                const float mine = __fmul_rn(__fmul_rn(o[4 * i + e], inv), ca);  // o * inv is what this half stored
+                const float theirs = __fmul_rn(ov[e], cb);
+                const float sum = half ? __fadd_rn(theirs, mine) : __fadd_rn(mine, theirs);
+                o[4 * i + e] = __fmul_rn(sum, iden);
+              }
+            }
+          }
           // columns 32c .. 32c+31 = 16-byte units 4(c%2) .. 4(c%2)+3 of the 128-byte row in block c/2
           const uint32_t rbase = stage + (c >> 1) * (BM * 128) + r_in * 128;
 #pragma unroll
           for (int i = 0; i < 4; ++i) {
             const uint32_t unit = static_cast<uint32_t>((c & 1) * 4 + i) ^ static_cast<uint32_t>(r_in & 7);
             asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};\n" ::"r"(rbase + unit * 16),
-                         "r"(pack16<BF16>(o[8 * i + 0] * inv, o[8 * i + 1] * inv)),
-                         "r"(pack16<BF16>(o[8 * i + 2] * inv, o[8 * i + 3] * inv)),
-                         "r"(pack16<BF16>(o[8 * i + 4] * inv, o[8 * i + 5] * inv)),
-                         "r"(pack16<BF16>(o[8 * i + 6] * inv, o[8 * i + 7] * inv))
+                         "r"(pack16<BF16>(o[8 * i + 0] * out_scale, o[8 * i + 1] * out_scale)),
+                         "r"(pack16<BF16>(o[8 * i + 2] * out_scale, o[8 * i + 3] * out_scale)),
+                         "r"(pack16<BF16>(o[8 * i + 4] * out_scale, o[8 * i + 5] * out_scale)),
+                         "r"(pack16<BF16>(o[8 * i + 6] * out_scale, o[8 * i + 7] * out_scale))
                          : "memory");
           }
         }
@@ -761,8 +818,13 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
           tma_store_commit();
           tma_store_wait_read();
         }
-        if (p.lse && row_ok)
-          p.lse[((int64_t)b * p.Hq + h) * p.Lq + row] = l > 0.f ? (m_ref + log2f(l)) * kLn2 : INFINITY;
+        if constexpr (SPLIT) {  // p.bias carries the caller's LSE pointer in this variant
+          float* lse_out = const_cast<float*>(p.bias);
+          if (lse_out && row_ok) lse_out[((int64_t)b * p.Hq + h) * p.Lq + row] = lse_final;
+        } else {
+          if (p.lse && row_ok)
+            p.lse[((int64_t)b * p.Hq + h) * p.Lq + row] = l > 0.f ? (m_ref + log2f(l)) * kLn2 : INFINITY;
+        }
       }
     }
   }
@@ -838,46 +900,6 @@ bool bias_can_be_staged(const FwdParams& p) {
          p.bias_bs % 4 == 0;
 }
 
-// Merges the two KV halves of the work items `item0 ..` (SPLIT CTAs): one warp per query row.
-//   o = (w0 o0 + w1 o1) / (w0 + w1),  w = 2^(lse2 - max),  lse = (max + log2(w0 + w1)) ln 2
-// The work-item -> (batch, head, first row) mapping is the forward kernel's.
-template <typename T, int DV>
-__global__ void __launch_bounds__(256) combine_halves_kernel(const float* __restrict__ part_o, const float* __restrict__ part_lse,
-                                                            T* __restrict__ o, float* __restrict__ lse, int n_items, int item0,
-                                                            int order_w, int B, int Lq, int Hq) {
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int64_t slot = (int64_t)blockIdx.x * 8 + warp;  // ((item - item0) * 2 + tile) * BM + row in tile
-  const int64_t slots = (int64_t)n_items * 2 * BM;
-  if (slot >= slots) return;
-  const int item = item0 + (int)(slot / (2 * BM));
-  const int n_bh = Hq * B, n_qt = (Lq + 2 * BM - 1) / (2 * BM);
-  const int blk = item / (order_w * n_qt);
-  const int rem = item - blk * (order_w * n_qt);
-  const int wc = min(order_w, n_bh - blk * order_w);
-  const int qt = n_qt - 1 - rem / wc;
-  const int bh = blk * order_w + rem % wc;
-  const int h = bh % Hq, b = bh / Hq;
-  const int row = qt * 2 * BM + (int)(slot % (2 * BM));
-  if (row >= Lq) return;
-  const float l0 = part_lse[slot], l1 = part_lse[slots + slot];
-  const float mx = fmaxf(l0, l1);
-  const float w0 = mx == -INFINITY ? 0.f : exp2f(l0 - mx), w1 = mx == -INFINITY ? 0.f : exp2f(l1 - mx);
-  const float den = w0 + w1;
-  const float inv = den > 0.f ? 1.f / den : 0.f;
-  const float* p0 = part_o + slot * DV;
-  const float* p1 = part_o + (slots + slot) * DV;
-  T* dst = o + (((int64_t)b * Lq + row) * Hq + h) * DV;
-  static_assert(DV % 128 == 0 || DV == 64, "one or more float4 per lane");
-#pragma unroll
-  for (int c = lane * 4; c < DV; c += 128) {
-    const float4 a = *reinterpret_cast<const float4*>(p0 + c), bb = *reinterpret_cast<const float4*>(p1 + c);
-    T r[4] = {Elem<T>::from_f((w0 * a.x + w1 * bb.x) * inv), Elem<T>::from_f((w0 * a.y + w1 * bb.y) * inv),
-              Elem<T>::from_f((w0 * a.z + w1 * bb.z) * inv), Elem<T>::from_f((w0 * a.w + w1 * bb.w) * inv)};
-    *reinterpret_cast<uint2*>(dst + c) = *reinterpret_cast<const uint2*>(r);
-  }
-  if (lse && lane == 0) lse[((int64_t)b * Hq + h) * Lq + row] = den > 0.f ? (mx + log2f(den)) * kLn2 : INFINITY;
-}
-
 // The partials of the KV halves come from the stream-ordered allocator.  Its default pool hands freed memory
 // back to the driver at every synchronisation, which would make each call pay for a fresh mapping: keep it.
 void keep_pool_memory() {
@@ -891,6 +913,32 @@ void keep_pool_memory() {
     if (cudaMemPoolGetAttribute(pool, cudaMemPoolAttrReleaseThreshold, &cur) == cudaSuccess && cur < keep)
       cudaMemPoolSetAttribute(pool, cudaMemPoolAttrReleaseThreshold, &keep);
   }
+}
+
+// A second stream per device for the halves: they do not depend on the full-length CTAs, and launched beside
+// them their CTAs take over SMs one by one as the last full wave drains, instead of waiting for all of it.
+struct SideStream {
+  cudaStream_t stream = nullptr;
+  cudaEvent_t fork = nullptr, join = nullptr;
+  std::mutex mu;  // held while one call enqueues its fork / launch / join
+};
+SideStream* side_stream() {
+  static SideStream side[64];
+  static std::mutex create_mu;
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+  SideStream& s = side[dev];
+  std::lock_guard<std::mutex> lock(create_mu);
+  if (!s.stream) {
+    if (cudaStreamCreateWithFlags(&s.stream, cudaStreamNonBlocking) != cudaSuccess ||
+        cudaEventCreateWithFlags(&s.fork, cudaEventDisableTiming) != cudaSuccess ||
+        cudaEventCreateWithFlags(&s.join, cudaEventDisableTiming) != cudaSuccess) {
+      (void)cudaGetLastError();
+      s.stream = nullptr;
+      return nullptr;
+    }
+  }
+  return &s;
 }
 
 int sm_count() {
@@ -934,29 +982,47 @@ int launch_one(const FwdParams& p, int dtype, cudaStream_t stream) {
     if (!off && !p.causal && !p.kv_lengths && tail > 0 && 2 * tail <= sms && n_kv >= 8 && n_items < (1 << 23)) {
       const size_t slots = (size_t)tail * 2 * BM;
       const size_t o_bytes = 2 * slots * DV * sizeof(float), l_bytes = 2 * slots * sizeof(float);
+      const size_t c_bytes = (size_t)tail * 2 * sizeof(int32_t);  // arrivals per (work item, query tile)
       void* ws = nullptr;
       keep_pool_memory();
-      if (cudaMallocAsync(&ws, o_bytes + l_bytes, stream) == cudaSuccess) {
-        if (full > 0) {
-          kern<<<dim3((unsigned)full), NTHREADS, C::SMEM_BYTES, stream>>>(tq, tk, tv, tb, to, static_cast<const FwdParamsCore&>(p),
-                                                                          order_w, p.mod);
-          count_launch();
-        }
+      if (cudaMallocAsync(&ws, o_bytes + l_bytes + c_bytes, stream) == cudaSuccess) {
+        int32_t* counters = reinterpret_cast<int32_t*>(static_cast<char*>(ws) + o_bytes + l_bytes);
+        rc = check_cuda(cudaMemsetAsync(counters, 0, c_bytes, stream), "clear arrival counters");
         auto kern_h = attn_fwd_sm100_kernel<DQK, DV, BN, KST, VST, BF16, 0, false, false, true>;
-        rc = check_cuda(cudaFuncSetAttribute(kern_h, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES),
-                        "cudaFuncSetAttribute(sm100 fwd, KV halves)");
+        if (!rc)
+          rc = check_cuda(cudaFuncSetAttribute(kern_h, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES),
+                          "cudaFuncSetAttribute(sm100 fwd, KV halves)");
+        SideStream* side = (!rc && full > 0) ? side_stream() : nullptr;
+        cudaStream_t hstream = stream;  // where the halves go
+        std::unique_lock<std::mutex> side_lock;
+        if (side) {
+          side_lock = std::unique_lock<std::mutex>(side->mu);
+          if (cudaEventRecord(side->fork, stream) == cudaSuccess && cudaStreamWaitEvent(side->stream, side->fork, 0) == cudaSuccess)
+            hstream = side->stream;
+          else
+            (void)cudaGetLastError();
+        }
         if (!rc) {
+          if (full > 0) {
+            kern<<<dim3((unsigned)full), NTHREADS, C::SMEM_BYTES, stream>>>(tq, tk, tv, tb, to,
+                                                                            static_cast<const FwdParamsCore&>(p), order_w, p.mod);
+            count_launch();
+          }
+          // the halves: partials and their LSE in the workspace; the fields this variant does not use carry the
+          // arrival counters (kv_lengths) and the caller's LSE pointer (bias)
           FwdParamsCore ph = static_cast<const FwdParamsCore&>(p);
           ph.o = ws;
           ph.lse = reinterpret_cast<float*>(static_cast<char*>(ws) + o_bytes);
-          kern_h<<<dim3(2u * (unsigned)tail), NTHREADS, C::SMEM_BYTES, stream>>>(tq, tk, tv, tb, to, ph,
-                                                                               order_w | ((int)full << 8), p.mod);
-          count_launch();
-          using T = typename std::conditional<BF16, __nv_bfloat16, __half>::type;
-          combine_halves_kernel<T, DV><<<dim3((unsigned)((slots + 7) / 8)), 256, 0, stream>>>(
-              static_cast<const float*>(ws), ph.lse, static_cast<T*>(p.o), p.lse, tail, (int)full, order_w, p.B, p.Lq, p.Hq);
+          ph.kv_lengths = counters;
+          ph.bias = p.lse;
+          kern_h<<<dim3(2u * (unsigned)tail), NTHREADS, C::SMEM_BYTES, hstream>>>(tq, tk, tv, tb, to, ph,
+                                                                                order_w | ((int)full << 8), p.mod);
           count_launch();
           rc = check_cuda(cudaGetLastError(), "sm100 forward launch (with KV halves)");
+          if (hstream != stream) {  // the caller's stream continues after both grids
+            if (!rc) rc = check_cuda(cudaEventRecord(side->join, hstream), "record the halves' completion");
+            if (!rc) rc = check_cuda(cudaStreamWaitEvent(stream, side->join, 0), "join the halves");
+          }
         }
         cudaFreeAsync(ws, stream);
         return rc;
