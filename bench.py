@@ -283,6 +283,10 @@ def main():
                     help="time only the masked + biased configuration on --batch batch rows (profiling captures)")
     ap.add_argument("--only-latent-decode", action="store_true",
                     help="time only the absorbed latent decode on --batch sequences (profiling captures)")
+    ap.add_argument("--only-waves", action="store_true",
+                    help="time the unmasked forward on 8 .. 512 equal work items (256 query rows x 4096 keys each): "
+                         "the staircase of waves and what cutting the last wave into KV halves buys "
+                         "(PJX_FWD_SPLIT_TAIL=0 switches the halves off)")
     ap.add_argument("--only-prefill", action="store_true",
                     help="time only the headline forward, non-causal and causal, without checking the result "
                          "(what-if builds of the forward kernel, whose outputs are wrong on purpose)")
@@ -328,6 +332,9 @@ def main():
         return
     if args.only_masked_bias:
         only_masked_bias(args, dev, pk)
+        return
+    if args.only_waves:
+        only_waves(args, dev, pk)
         return
     if args.only_prefill:
         only_prefill(args, dev, pk)
@@ -682,6 +689,28 @@ def only_latent_decode(args, dev, pk):
     res["config"] = {"workload": f"absorbed latent decode bf16 B{Bl} H16 R576, 32768 keys each",
                      "kernel": args.kernel or "library's choice"}
     _emit(res)
+
+
+def only_waves(args, dev, pk):
+    """Unmasked bf16 forward, one work item (256 query rows x 4096 keys, D = 128) per query head, for head counts
+    around the multiples of the SM count: time per call and launches per call."""
+    import probjax_b200 as pj
+    from probjax_b200 import _lib
+
+    g = torch.Generator(device=dev).manual_seed(0)
+    k = torch.randn((1, 4096, 8, 128), device=dev, generator=g).bfloat16()
+    v = torch.randn((1, 4096, 8, 128), device=dev, generator=g).bfloat16()
+    out = {"config": {"workload": "GQA forward bf16, Lq 256 per head, Lkv 4096, Hkv 8, D 128, unmasked",
+                      "kv_halves": os.environ.get("PJX_FWD_SPLIT_TAIL", "1") != "0"}, "items_us_launches": []}
+    for items in (8, 72, 144, 152, 216, 296, 304, 368, 440, 512):
+        q = torch.randn((1, 256, items, 128), device=dev, generator=g).bfloat16()
+        n0 = _lib.launch_count()
+        pj.attention_forward(q, k, v, sm_scale=0.088)
+        launches = _lib.launch_count() - n0
+        ms = time_steps(lambda: pj.attention_forward(q, k, v, sm_scale=0.088), args.steps, args.warmup) / args.steps
+        out["items_us_launches"].append([items, ms * 1e3, launches])
+    pj.check_status(dev)
+    _emit(out)
 
 
 def only_prefill(args, dev, pk):
