@@ -1057,7 +1057,7 @@ int launch_by_shape(const FwdParams& p, int dtype, cudaStream_t stream) {
     if (bias_can_be_staged(p) && !p.banded() && !p.mod.on) return launch_one<64, 64, 128, 2, 2, BF16, 2>(p, dtype, stream);
     return launch_cfg<64, 64, 128, 3, 3, BF16>(p, dtype, stream);
   }
-  if (p.D == 192 && p.Dv == 128) return launch_cfg<192, 128, 128, 2, 1, BF16>(p, dtype, stream);
+  if (p.D == 192 && p.Dv == 128) return launch_cfg<192, 128, 128, 1, 2, BF16>(p, dtype, stream);
   return fail(PJX_ERR_UNSUPPORTED, "tcgen05 forward: head dims (%d, %d) not built", p.D, p.Dv);
 }
 
