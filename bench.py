@@ -251,12 +251,19 @@ def run_reference(args, rank):
 
 
 def bench_extra(name, fn, steps, warmup, work, unit, peak, bound, pk_note, profile=None):
-    """Time one secondary configuration; returns a small dict (never raises).  `profile`
-    names the tracked ncu summary of the kernel behind the number."""
+    """Time one secondary configuration (the faster of two timed batches); returns a small dict (never
+    raises).  `profile` names the tracked ncu summary of the kernel behind the number."""
     try:
-        ms = time_steps(fn, steps, warmup) / steps
+        # Two timed batches of `steps` steps each, the faster one reported: one batch in some tens of runs
+        # came out far slower than every other run of the same build.  A slower batch that differs by more
+        # than a quarter stays visible as "ms_other".
+        a = time_steps(fn, steps, warmup) / steps
+        b = time_steps(fn, steps, 1) / steps
+        ms = min(a, b)
         ach = work / (ms * 1e-3)
         out = {"ms": ms, "value": ach, "unit": unit, "bound": bound, "frac": ach / peak}
+        if max(a, b) > 1.25 * ms:
+            out["ms_other"] = max(a, b)
         if profile:  # file under profiles/ (without the .md) that holds the ncu summary of this kernel
             out["profile"] = os.path.splitext(os.path.basename(profile))[0]
         return out

@@ -295,8 +295,10 @@ __global__ void __launch_bounds__(NTHR, 2) decode_splitkv_kernel(const DecodePar
   // runs, so that a head without keys still publishes its empty partial)
   if (start >= len && !(FUSED && split == 0)) return;
   const int end = min(len, start + p.split_len);
-  // let the next kernel on the stream (launched with the same attribute) start as SM slots free up
-  if (FUSED && p.ex_overlap) asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");
+  // Let the next kernel on the stream start as SM slots free up, if it was launched for that: the
+  // combine of the splits always is (it waits for this grid before it reads a partial), the next
+  // step's kernel of a sharded decode is with ex_overlap.
+  if (!FUSED || p.ex_overlap) asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");
   stream_segment<T, HD, PAGED>(p, smem_raw, b, hk, start, end,
                                (((int64_t)b * p.Hkv + hk) * p.num_splits + split) * p.rows);
   [[maybe_unused]] const int tid = threadIdx.x;
@@ -424,6 +426,9 @@ __global__ void __launch_bounds__(NTHR, 2) decode_splitkv_kernel(const DecodePar
 template <typename TO>
 __global__ void combine_splits_kernel(const DecodeParams p) {
   const int r = blockIdx.x, hk = blockIdx.y, b = blockIdx.z;
+  // Launched with programmatic stream serialization, the grid may be resident before the split kernel
+  // has finished: wait for that grid and its stores.  (Does nothing under a plain launch.)
+  asm volatile("griddepcontrol.wait;\n" ::: "memory");
   int len = p.capacity;
   if (p.kv_lengths) len = max(0, min(len, p.kv_lengths[b]));
   const int ns = (len + p.split_len - 1) / p.split_len;
@@ -592,6 +597,24 @@ __global__ void gather_combine_kernel(const DecodeParams p) {
   }
 }
 
+// The combine of the splits is launched so that it may become resident while the split kernel's last
+// CTAs still run (its first instruction waits for that grid): the launch latency of the second kernel,
+// a few microseconds of a short decode step, is hidden behind the first.
+template <typename TO>
+cudaError_t launch_combine_splits(const DecodeParams& p, cudaStream_t stream) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(p.rows, p.Hkv, p.B);
+  cfg.blockDim = dim3(p.Dv >= 128 ? 128 : 64);
+  cfg.dynamicSmemBytes = 0;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, combine_splits_kernel<TO>, p);
+}
+
 // CTAs of the split kernel that one device holds at once (2 per SM unless the driver says otherwise).
 template <typename T, int HD>
 int coresident_ctas_t(int* out) {
@@ -652,12 +675,9 @@ int launch_decode_t(const DecodeParams& p, cudaStream_t stream) {
     count_launch();
     return check_cuda(cudaGetLastError(), "decode gather-combine launch");
   }
-  if (p.o_is_f32)
-    combine_splits_kernel<float><<<cgrid, cthr, 0, stream>>>(p);
-  else
-    combine_splits_kernel<T><<<cgrid, cthr, 0, stream>>>(p);
+  const cudaError_t ce = p.o_is_f32 ? launch_combine_splits<float>(p, stream) : launch_combine_splits<T>(p, stream);
   count_launch();
-  return check_cuda(cudaGetLastError(), "decode combine launch");
+  return check_cuda(ce, "decode combine launch");
 }
 
 }  // namespace
@@ -687,16 +707,11 @@ int launch_decode(const DecodeParams& p, int dtype, cudaStream_t stream) {
 // The exact combine of the per-split partials alone (the split kernel of the latent decode writes
 // the same partial layout).
 int launch_decode_combine(const DecodeParams& p, int dtype, cudaStream_t stream) {
-  dim3 cgrid(p.rows, p.Hkv, p.B);
-  const int cthr = p.Dv >= 128 ? 128 : 64;
-  if (p.o_is_f32)
-    combine_splits_kernel<float><<<cgrid, cthr, 0, stream>>>(p);
-  else if (dtype == PJX_BF16)
-    combine_splits_kernel<__nv_bfloat16><<<cgrid, cthr, 0, stream>>>(p);
-  else
-    combine_splits_kernel<__half><<<cgrid, cthr, 0, stream>>>(p);
+  const cudaError_t ce = p.o_is_f32          ? launch_combine_splits<float>(p, stream)
+                         : dtype == PJX_BF16 ? launch_combine_splits<__nv_bfloat16>(p, stream)
+                                             : launch_combine_splits<__half>(p, stream);
   count_launch();
-  return check_cuda(cudaGetLastError(), "decode combine launch");
+  return check_cuda(ce, "decode combine launch");
 }
 
 int launch_combine_parts(const float* o_parts, const float* lse_parts, int n_parts, int64_t n_rows,

@@ -66,6 +66,9 @@ __global__ void __launch_bounds__(LTHR, 1) decode_latent_kernel(const DecodePara
   const int start = split * p.split_len;
   if (start >= len) return;  // the combine never reads this split
   const int end = min(len, start + p.split_len);
+  // the combine of the splits, next on the stream, may become resident as SM slots free up (it waits
+  // for this grid before it reads a partial)
+  asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");
   const int n_tiles = (end - start + LBK - 1) / LBK;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int G = p.Hq / p.Hkv;  // heads per row group

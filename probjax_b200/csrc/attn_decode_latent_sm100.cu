@@ -168,6 +168,9 @@ decode_latent_tc_kernel(const __grid_constant__ CUtensorMap tm_c, const DecodePa
   const int start = split * p.split_len;
   if (start >= len) return;  // the combine never reads this split
   const int end = min(len, start + p.split_len);
+  // the combine of the splits, next on the stream, may become resident as SM slots free up (it waits
+  // for this grid before it reads a partial)
+  asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");
   const int n_tiles = (end - start + TK - 1) / TK;
   const int last_rows = end - start - (n_tiles - 1) * TK;  // valid rows of the last tile, 1 .. 128
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
