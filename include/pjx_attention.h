@@ -437,6 +437,13 @@ int pjx_rope_interleaved(const void* x, void* y, const float* positions, float o
  *
  *   q [B, Lq, H, Dqk]  cache [B, S, R]  wk [H, Dqk, R]  wv [H, Dv, R]  o [B, Lq, H, Dv]
  *   workspace: pjx_mla_workspace_bytes(...) bytes; holds K = C.wk^T and V = C.wv^T.
+ *
+ * Without projections the call is multi-query attention of head width R.  Up to R = 256 the
+ * regular forward kernels take it.  At R = 512 and 576 (bf16 / fp16, no bias, no score modifiers,
+ * a mask without a lower band edge: none, causal, bottom-right causal, key lengths) every query
+ * token runs as a one-token sequence of the absorbed latent decode kernels, whose partials live in
+ * the workspace (pjx_mla_workspace_bytes with has_projections = 0); other calls at those widths
+ * return PJX_ERR_UNSUPPORTED.
  */
 int pjx_mla_fwd(const void* q, const void* cache, const void* wk, const void* wv, void* o,
                 float* lse, const int32_t* kv_lengths, const float* bias,

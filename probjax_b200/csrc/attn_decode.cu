@@ -425,14 +425,14 @@ __global__ void __launch_bounds__(NTHR, 2) decode_splitkv_kernel(const DecodePar
 // One CTA per packed row (b, kv head, r): exact combine of the valid splits.
 template <typename TO>
 __global__ void combine_splits_kernel(const DecodeParams p) {
-  const int r = blockIdx.x, hk = blockIdx.y, b = blockIdx.z;
+  const int r = blockIdx.x, hk = blockIdx.y;
   // Launched with programmatic stream serialization, the grid may be resident before the split kernel
   // has finished: wait for that grid and its stores.  (Does nothing under a plain launch.)
   asm volatile("griddepcontrol.wait;\n" ::: "memory");
-  int len = p.capacity;
-  if (p.kv_lengths) len = max(0, min(len, p.kv_lengths[b]));
+  const DecodeSeq sq = decode_seq(p, blockIdx.z);
+  const int len = sq.len;
   const int ns = (len + p.split_len - 1) / p.split_len;
-  const int64_t base = ((int64_t)b * p.Hkv + hk) * p.num_splits;
+  const int64_t base = ((int64_t)blockIdx.z * p.Hkv + hk) * p.num_splits;
   float m = -INFINITY;
   for (int s = 0; s < ns; ++s) m = fmaxf(m, p.lse_part[(base + s) * p.rows + r]);
   const float msafe = (m == -INFINITY) ? 0.f : m;
@@ -442,7 +442,7 @@ __global__ void combine_splits_kernel(const DecodeParams p) {
   const int G = p.Hq / p.Hkv;
   const int g = r / p.Lq, t = r % p.Lq;
   const int h = hk * G + g;
-  TO* o = static_cast<TO*>(p.o) + (((int64_t)b * p.Lq + t) * p.Hq + h) * p.Dv;
+  TO* o = static_cast<TO*>(p.o) + ((sq.q_b * p.Lq + t) * p.Hq + h) * p.Dv;
   for (int d = threadIdx.x; d < p.Dv; d += blockDim.x) {
     float acc = 0.f;
     for (int s = 0; s < ns; ++s) {
@@ -452,7 +452,7 @@ __global__ void combine_splits_kernel(const DecodeParams p) {
     o[d] = Elem<TO>::from_f(acc * inv);
   }
   if (p.lse && threadIdx.x == 0)
-    p.lse[((int64_t)b * p.Hq + h) * p.Lq + t] = denom > 0.f ? (msafe + log2f(denom)) * kLn2 : INFINITY;
+    p.lse[decode_lse_index(p, sq, h, t)] = denom > 0.f ? (msafe + log2f(denom)) * kLn2 : INFINITY;
 }
 
 // Combine of n_parts partials laid out [n_parts, n_rows, Dv] with natural-log LSEs.

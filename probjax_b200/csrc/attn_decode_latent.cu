@@ -60,9 +60,9 @@ __global__ void __launch_bounds__(LTHR, 1) decode_latent_kernel(const DecodePara
   const uint32_t sbase = smem_u32(smem_raw);
   float* red = reinterpret_cast<float*>(smem_raw + C::OFF_RED);
 
-  const int split = blockIdx.x, grp = blockIdx.y, b = blockIdx.z;
-  int len = p.capacity;
-  if (p.kv_lengths) len = max(0, min(len, p.kv_lengths[b]));
+  const int split = blockIdx.x, grp = blockIdx.y;
+  const DecodeSeq sq = decode_seq(p, blockIdx.z);
+  const int b = sq.cache_b, len = sq.len;
   const int start = split * p.split_len;
   if (start >= len) return;  // the combine never reads this split
   const int end = min(len, start + p.split_len);
@@ -108,7 +108,7 @@ __global__ void __launch_bounds__(LTHR, 1) decode_latent_kernel(const DecodePara
       uint4 v = make_uint4(0u, 0u, 0u, 0u);
       if (r < p.rows) {
         const int g = r / p.Lq, t = r % p.Lq;
-        v = *reinterpret_cast<const uint4*>(q + (((int64_t)b * p.Lq + t) * p.Hq + grp * G + g) * R + c * 8);
+        v = *reinterpret_cast<const uint4*>(q + ((sq.q_b * p.Lq + t) * p.Hq + grp * G + g) * R + c * 8);
       }
       *reinterpret_cast<uint4*>(smem_raw + C::OFF_Q + lswz(r, c, C::ROW_BYTES)) = v;
     }
@@ -255,7 +255,7 @@ __global__ void __launch_bounds__(LTHR, 1) decode_latent_kernel(const DecodePara
     lsum[0] += red[LWARPS * 16 + w * 16 + row_lo];
     lsum[1] += red[LWARPS * 16 + w * 16 + row_lo + 8];
   }
-  const int64_t part = (((int64_t)b * p.Hkv + grp) * p.num_splits + split) * p.rows;
+  const int64_t part = (((int64_t)blockIdx.z * p.Hkv + grp) * p.num_splits + split) * p.rows;
 #pragma unroll
   for (int h = 0; h < 2; ++h) {
     const int r = row_lo + 8 * h;

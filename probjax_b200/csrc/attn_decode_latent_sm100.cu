@@ -162,9 +162,9 @@ decode_latent_tc_kernel(const __grid_constant__ CUtensorMap tm_c, const DecodePa
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   float* red = reinterpret_cast<float*>(smem + C::OFF_RED);
 
-  const int split = blockIdx.x, grp = blockIdx.y, b = blockIdx.z;
-  int len = p.capacity;
-  if (p.kv_lengths) len = max(0, min(len, p.kv_lengths[b]));
+  const int split = blockIdx.x, grp = blockIdx.y;
+  const DecodeSeq sq = decode_seq(p, blockIdx.z);
+  const int b = sq.cache_b, len = sq.len;
   const int start = split * p.split_len;
   if (start >= len) return;  // the combine never reads this split
   const int end = min(len, start + p.split_len);
@@ -195,7 +195,7 @@ decode_latent_tc_kernel(const __grid_constant__ CUtensorMap tm_c, const DecodePa
       uint4 v = make_uint4(0u, 0u, 0u, 0u);
       if (r < p.rows) {
         const int g = r / p.Lq, t = r % p.Lq;
-        v = *reinterpret_cast<const uint4*>(q + (((int64_t)b * p.Lq + t) * p.Hq + grp * G + g) * R + c * 8);
+        v = *reinterpret_cast<const uint4*>(q + ((sq.q_b * p.Lq + t) * p.Hq + grp * G + g) * R + c * 8);
       }
       const int sub = c >> 3, ch = c & 7;
       *reinterpret_cast<uint4*>(smem + C::OFF_Q + sub * 2048 + r * 128 + ((ch ^ (r & 7)) << 4)) = v;
@@ -429,7 +429,7 @@ decode_latent_tc_kernel(const __grid_constant__ CUtensorMap tm_c, const DecodePa
           inv[h] = ls > 0.f ? 1.f / ls : 0.f;
           if (h == kl) lsum_mine = ls;
         }
-        const int64_t part = (((int64_t)b * p.Hkv + grp) * p.num_splits + split) * p.rows;
+        const int64_t part = (((int64_t)blockIdx.z * p.Hkv + grp) * p.num_splits + split) * p.rows;
 #pragma unroll
         for (int m = 0; m < NBLK; ++m) {
           float o[NROW];
@@ -463,7 +463,7 @@ template <bool BF16, int R>
 int launch_tc_t(const DecodeParams& p, int dtype, cudaStream_t stream) {
   using C = TCfg<R>;
   CUtensorMap tm;
-  int rc = make_tmap_2d(&tm, p.k, dtype, (int64_t)p.B * p.capacity, R, TK, 0);
+  int rc = make_tmap_2d(&tm, p.k, dtype, decode_cache_rows(p) * p.capacity, R, TK, 0);
   if (rc) return rc;
   auto kern = decode_latent_tc_kernel<BF16, R>;
   rc = check_cuda(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM),
@@ -491,7 +491,7 @@ int launch_tc_r(const DecodeParams& p, int dtype, cudaStream_t stream) {
 // bounded waits and a cache whose 2-D view [B * capacity, R] a tensor map can address.
 bool decode_latent_tc_supported(const DecodeParams& p, int dtype) {
   return (dtype == PJX_BF16 || dtype == PJX_F16) && (p.D == 128 || p.D == 256 || p.D == 512 || p.D == 576) &&
-         p.status != nullptr && p.rows <= NROW && (int64_t)p.B * p.capacity < (1LL << 31) &&
+         p.status != nullptr && p.rows <= NROW && decode_cache_rows(p) * p.capacity < (1LL << 31) &&
          (reinterpret_cast<uintptr_t>(p.k) & 15) == 0;
 }
 

@@ -535,9 +535,90 @@ int pjx_mla_decode_absorbed_impl(const void* q, const void* cache, const int32_t
   return launch_decode_combine(p, dtype, st);
 }
 
+// ---------------------------------------------------------------------------
+// Absorbed latent attention over many query tokens at latent widths the regular
+// forward kernels do not take (R = 512, 576): every query token becomes a
+// one-token sequence of the latent decode kernels -- its 16 heads are the 16 rows
+// of the tensor-core operand, its keys are the cache row's keys up to its band
+// limit -- and the tokens are walked in chunks so that the partials stay small.
+// ---------------------------------------------------------------------------
+static constexpr int kAbsorbedPrefillSeqs = 2048;  // one-token sequences per launch (rounded to whole batch rows)
+
+static int absorbed_prefill_chunk(int B, int Lq) {
+  int t = kAbsorbedPrefillSeqs / (B < 1 ? 1 : B);
+  if (t < 1) t = 1;
+  return t < Lq ? t : Lq;
+}
+
+static size_t absorbed_prefill_parts(int B, int H) {
+  const int gh = latent_heads_per_group(H, 1);
+  if (gh == 0 || B < 1) return 0;
+  size_t units = (size_t)B * (kAbsorbedPrefillSeqs / B < 1 ? 1 : kAbsorbedPrefillSeqs / B) * (H / gh);
+  if (units < 148) units = 148;  // fewer units are cut into at most 148 splits in all
+  return units * gh;
+}
+
+static bool absorbed_prefill_applies(int H, int R, int dtype, int band_lo, const float* bias, const pjx_score_mod* mod,
+                                     const void* q, const void* cache) {
+  if (R <= 256 || !decode_latent_supported(R, dtype) || latent_heads_per_group(H, 1) == 0) return false;
+  if (bias || mod || band_lo > PJX_BAND_NO_LOWER) return false;
+  return ((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(cache)) & 15) == 0;
+}
+
+static int absorbed_prefill(const void* q, const void* cache, const int32_t* kv_lengths, void* o, float* lse, int B,
+                            int Lq, int S, int H, int R, int dtype, int band_hi, float sm_scale, int impl,
+                            void* workspace, size_t workspace_bytes, int32_t* status, cudaStream_t st) {
+  int rc = decode_limits(B, H, S);
+  if (rc) return rc;
+  if (S == 0) return fail(PJX_ERR_UNSUPPORTED, "absorbed latent attention at this width needs a non-empty cache");
+  const int gh = latent_heads_per_group(H, 1);
+  const size_t parts_max = absorbed_prefill_parts(B, H);
+  const size_t need = align_up(parts_max * R * sizeof(float)) + align_up(parts_max * sizeof(float));
+  if (!workspace || workspace_bytes < need)
+    return fail(PJX_ERR_WORKSPACE, "mla workspace: need %zu bytes, got %zu", need, workspace ? workspace_bytes : (size_t)0);
+  DecodeParams p;
+  p.q = q; p.k = cache; p.v = cache; p.kv_lengths = kv_lengths; p.o = o; p.lse = lse;
+  p.Lq = 1; p.Hq = H; p.Hkv = H / gh; p.D = R; p.Dv = R; p.capacity = S;
+  p.rows = gh;
+  p.sm_scale = sm_scale;
+  p.o_is_f32 = 0;
+  p.status = status;
+  p.o_part = static_cast<float*>(workspace);
+  p.lse_part = reinterpret_cast<float*>(static_cast<char*>(workspace) + align_up(parts_max * R * sizeof(float)));
+  p.seq_total = Lq;
+  // key j is visible to token t iff j <= t + band_hi
+  p.seq_visible = band_hi >= S ? S : (band_hi < -Lq ? -Lq : band_hi + 1);
+  const int chunk = absorbed_prefill_chunk(B, Lq);
+  for (int t0 = 0; t0 < Lq; t0 += chunk) {
+    p.seq_first = t0;
+    p.seq_tokens = Lq - t0 < chunk ? Lq - t0 : chunk;
+    p.B = B * p.seq_tokens;
+    // keys this chunk can see at most: no split reaches beyond them
+    int cap = S;
+    if (t0 + p.seq_tokens - 1 + p.seq_visible < cap) cap = t0 + p.seq_tokens - 1 + p.seq_visible;
+    if (cap < 1) cap = 1;
+    p.split_len = latent_decode_split_len(p.B, p.Hkv, cap, 0);
+    p.num_splits = (cap + p.split_len - 1) / p.split_len;
+    if ((size_t)p.B * p.Hkv * p.num_splits * p.rows > parts_max)
+      return fail(PJX_ERR_WORKSPACE, "absorbed latent attention: partials of a chunk exceed the workspace");
+    const bool big = (double)p.B * p.Hkv * cap * R * 2.0 >= 64.0 * 1024 * 1024;
+    const bool tc = (impl == PJX_IMPL_SM100 || (impl == PJX_IMPL_AUTO && big)) && decode_latent_tc_supported(p, dtype);
+    if (impl == PJX_IMPL_SM100 && !tc)
+      return fail(PJX_ERR_UNSUPPORTED, "the tcgen05 latent decode needs a status word and a cache of fewer than 2^31 rows");
+    if ((rc = tc ? launch_decode_latent_tc_splits(p, dtype, st) : launch_decode_latent_splits(p, dtype, st))) return rc;
+    if ((rc = launch_decode_combine(p, dtype, st))) return rc;
+  }
+  return PJX_OK;
+}
+
 size_t pjx_mla_workspace_bytes(int B, int S, int H, int Dqk, int Dv, int R, int dtype, int has_projections) {
-  (void)R;
-  if (!has_projections) return 0;
+  (void)S;
+  if (!has_projections) {
+    // absorbed attention at the wide latents runs through the latent decode kernels and keeps their partials here
+    if (R <= 256 || !decode_latent_supported(R, dtype)) return 0;
+    const size_t parts = absorbed_prefill_parts(B, H);
+    return parts ? align_up(parts * R * sizeof(float)) + align_up(parts * sizeof(float)) : 0;
+  }
   const size_t es = dtype_size(dtype);
   return align_up((size_t)B * S * H * Dqk * es) + align_up((size_t)B * S * H * Dv * es);
 }
@@ -568,6 +649,9 @@ int pjx_mla_fwd_mod(const void* q, const void* cache, const void* wk, const void
   if (!q || !cache || !o) return fail(PJX_ERR_BAD_ARG, "mla: null buffer");
   if (!wk) {
     // K = V = latent, one shared KV head (latent_attention.py:604-607).
+    if (absorbed_prefill_applies(H, R, dtype, band_lo, bias, mod, q, cache))
+      return absorbed_prefill(q, cache, kv_lengths, o, lse, B, Lq, S, H, R, dtype, band_hi, sm_scale, impl, workspace,
+                              workspace_bytes, status, static_cast<cudaStream_t>(stream));
     return pjx_attn_fwd_mod(q, cache, cache, o, lse, kv_lengths, bias, bias_batch_stride, bias_head_stride, B, Lq, S,
                             H, 1, R, R, dtype, band_lo, band_hi, sm_scale, mod, impl, status, stream);
   }

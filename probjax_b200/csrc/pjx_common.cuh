@@ -108,7 +108,46 @@ struct DecodeParams {
   // j % page_size. page_size is a multiple of the 64-key tile, capacity = max_pages * page_size.
   const int32_t* block_table = nullptr;
   int page_size = 0, max_pages = 0;
+  // Prefill rows through the latent decode kernels (seq_tokens > 0): grid z walks B x seq_tokens
+  // one-token sequences.  Sequence z reads cache row z / seq_tokens, is query token
+  // t = seq_first + z % seq_tokens of seq_total, and sees the keys below t + seq_visible (and below
+  // the cache row's valid length); its partials are indexed by z, its output by (cache row, t).
+  int seq_tokens = 0, seq_first = 0, seq_total = 0, seq_visible = 0;
 };
+
+// What grid index z of a decode launch stands for (see DecodeParams::seq_tokens).
+struct DecodeSeq {
+  int cache_b;   // batch row of the cache and of kv_lengths
+  int64_t q_b;   // row of q / o counted in blocks of Lq tokens
+  int len;       // valid keys
+};
+
+// Batch rows the cache of a decode launch holds.
+inline int64_t decode_cache_rows(const DecodeParams& p) { return p.seq_tokens > 0 ? p.B / p.seq_tokens : p.B; }
+
+#ifdef __CUDACC__
+__device__ __forceinline__ DecodeSeq decode_seq(const DecodeParams& p, int z) {
+  DecodeSeq s;
+  s.cache_b = z;
+  s.q_b = z;
+  int lim = p.capacity;
+  if (p.seq_tokens > 0) {
+    s.cache_b = z / p.seq_tokens;
+    const int t = p.seq_first + z % p.seq_tokens;
+    s.q_b = (int64_t)s.cache_b * p.seq_total + t;
+    lim = max(0, min(p.capacity, t + p.seq_visible));
+  }
+  s.len = p.kv_lengths ? max(0, min(lim, p.kv_lengths[s.cache_b])) : lim;
+  return s;
+}
+
+// Index of the LSE of (sequence, head, token of the launch) in the caller's [B, Hq, Lq] array.
+__device__ __forceinline__ int64_t decode_lse_index(const DecodeParams& p, const DecodeSeq& s, int h, int t) {
+  if (p.seq_tokens > 0)
+    return ((int64_t)s.cache_b * p.Hq + h) * p.seq_total + (s.q_b - (int64_t)s.cache_b * p.seq_total);
+  return ((int64_t)s.cache_b * p.Hq + h) * p.Lq + t;
+}
+#endif
 
 // Parameter block of the backward kernels
 struct BwdParams {

@@ -398,6 +398,42 @@ def test_paged_cache_decode_equals_contiguous_decode(dtype, d, page):
                         perm.to(torch.int32), lens, sm_scale=sc)
 
 
+@pytest.mark.parametrize("R,H,dtype", [(576, 16, torch.bfloat16), (512, 32, torch.float16), (576, 6, torch.bfloat16)])
+@pytest.mark.parametrize("mask", ["none", "causal", "bottom_right", "causal+lengths"])
+def test_absorbed_latent_attention_over_many_tokens(R, H, dtype, mask):
+    """Absorbed latent attention (K = V = latent, latent_attention.py:604-607) at the wide latents with
+    hundreds of query tokens: every token runs as a one-token sequence of the latent decode kernels.
+    Output and LSE against the oracle on the shared cache; keys past the valid lengths hold NaN."""
+    d = dev()
+    B, S = 3, 700
+    Lq = 333 if mask == "bottom_right" else S
+    q = randn((B, Lq, H, R), dtype, 5)
+    cache = (randn((B, S, R), torch.float32, 6) * 0.5).to(dtype)
+    sc = 1 / math.sqrt(R)
+    lens, m = None, None
+    keep = None
+    if mask == "causal":
+        m = pj.CausalMask()
+        keep = m.dense(Lq, S, batch_size=B, num_heads=1)
+    elif mask == "bottom_right":
+        m = pj.CausalFromBottomRightMask(Lq, S)
+        keep = m.dense(Lq, S, batch_size=B, num_heads=1)
+    elif mask == "causal+lengths":
+        lens = torch.tensor([700, 0, 129], dtype=torch.int32)
+        m = pj.ComposeMask("and", pj.CausalMask(), pj.KVLenMask(lens))
+        keep = pj.CausalMask().dense(Lq, S, batch_size=B, num_heads=1)
+    shared = cache[:, :, None, :]
+    want, want_lse = oracle.xla_attention(q, shared, shared, keep=keep, kv_lengths=lens, sm_scale=sc, return_lse=True)
+    poisoned = cache.clone()
+    if lens is not None:
+        for b in range(B):
+            poisoned[b, int(lens[b]):] = float("nan")
+    for impl in (None, "b200:tcgen05", "b200:generic"):
+        got, lse = pj.mla(q.to(d), poisoned.to(d), mask=m, sm_scale=sc, return_lse=True, implementation=impl)
+        pj.check_status(d)
+        assert_close(got, lse, want, want_lse, dtype, f"absorbed latent attention R={R} H={H} {mask} impl={impl}")
+
+
 @pytest.mark.parametrize("R,H,Lq,dtype", [(576, 16, 1, torch.bfloat16), (512, 16, 1, torch.float16), (576, 8, 2, torch.bfloat16),
                                           (256, 5, 3, torch.bfloat16), (128, 32, 1, torch.bfloat16), (576, 6, 4, torch.float16)])
 def test_absorbed_latent_decode(R, H, Lq, dtype):
