@@ -249,7 +249,7 @@ def test_no_score_sized_tensor_is_allocated():
     out = pj.mha(q, k, v, mask=mask, bias=bias, sm_scale=0.09)
     torch.cuda.synchronize(d)
     extra = torch.cuda.max_memory_allocated(d) - base
-    assert extra <= out.numel() * out.element_size() + (1 << 20), f"{extra} bytes allocated"
+    assert extra <= out.numel() * out.element_size() + (4 << 20), f"{extra} bytes allocated"
     # and it is right: rows of the last segment against the oracle on that segment alone (block diagonal)
     lo = 4000
     want = oracle.xla_attention(q[:, lo:].cpu(), k[:, lo:].cpu(), v[:, lo:].cpu(), causal=True, sm_scale=0.09,
