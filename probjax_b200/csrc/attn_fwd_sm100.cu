@@ -214,8 +214,10 @@ __device__ __forceinline__ void exp_pack_store_scaled(const float (&s)[BN], floa
 // masks completely, which leaves its running state untouched.
 //
 // MOD (implies BAND): structured masks and score modifiers (score_mod.cuh) are evaluated by the
-// softmax threads on every tile: the scaled score of (row, key) is passed through the modifiers
-// and the mask part decides per element; no tile beyond the band / prefix range is visited.
+// softmax threads: level 1 holds the masks only (segment ids, per-row key limits, prefix), level 2
+// also passes the scaled score of (row, key) through the score terms and applies dropout.  No tile
+// beyond the band / prefix range is visited; under a segment mask the launcher also gives every
+// query tile the key range its ids can match, so tiles outside the range are skipped.
 //
 // SPLIT: the CTA takes one HALF of the KV tiles of its work item (two CTAs per item, blockIdx.x & 1 = the
 // half) and leaves an fp32 partial -- O normalised by its own sum, base-2 log-sum-exp -- in a workspace
@@ -224,7 +226,7 @@ __device__ __forceinline__ void exp_pack_store_scaled(const float (&s)[BN], floa
 // items cut in two, 136 CTAs of half length fill that wave.
 //
 // `order_item0` packs the order block width (low 8 bits) and the index of the grid's first work item.
-template <int DQK, int DV, int BN, int KST, int VST, bool BF16, int BIAS, bool BAND, bool MOD = false, bool SPLIT = false>
+template <int DQK, int DV, int BN, int KST, int VST, bool BF16, int BIAS, bool BAND, int MOD = 0, bool SPLIT = false>
 __global__ void __launch_bounds__(NTHREADS, 1)
 attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                       const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_b,
@@ -291,6 +293,11 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
         int end = max(0, min(kv_len, min(qs + BM, p.Lq) + p.band_hi));
         int begin = max(0, qs + p.band_lo);
         if constexpr (MOD) {
+          if (smod.q_tile_range) {  // keys that can share a segment with a row of this tile
+            const int32_t* r = smod.q_tile_range + ((int64_t)b * smod.q_tile_range_bs + qs / BM) * 2;
+            begin = max(begin, r[0]);
+            end = min(end, r[1]);
+          }
           if (smod.prefix_len) {  // prefix keys are visible to every row
             const int pre = min(kv_len, smod.prefix_len[b]);
             if (pre > 0) {
@@ -508,14 +515,19 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
     if (BIAS == 1 && row_ok) bias_row = p.bias + (int64_t)b * p.bias_bs + (int64_t)h * p.bias_hs + (int64_t)row * p.Lkv;
     const bool bias_vec = BIAS == 1 && (p.Lkv % 4 == 0) && ((reinterpret_cast<uintptr_t>(p.bias) & 15) == 0) &&
                           (p.bias_bs % 4 == 0) && (p.bias_hs % 4 == 0);
-    const float cs = (HAS_BIAS || MOD) ? 1.f : c1;
     ScoreModView mv = {};
     int my_seg = 0, my_limit = 0x7fffffff;
+    bool mod_terms = false;  // a modifier changes the scores (not only the mask)
+    bool seg_vec = false;    // the key-side segment ids can be read four at a time
     if constexpr (MOD) {
       mv = view_of(smod, b, h, p.Lq);
       if (row_ok && mv.seg_q) my_seg = mv.seg_q[row];
       if (row_ok && mv.row_limit) my_limit = mv.row_limit[row];
+      if constexpr (MOD == 2) mod_terms = mv.hscale_m1 != 0.f || mv.softcap > 0.f || mv.rel != nullptr || mv.alibi_mode != 0;
+      seg_vec = mv.seg_k != nullptr && (reinterpret_cast<uintptr_t>(mv.seg_k) & 15) == 0;
     }
+    // scores reach the exponential already in the exp2 domain when a bias or a score modifier was applied
+    const float cs = (HAS_BIAS || (MOD == 2 && mod_terms)) ? 1.f : c1;
 
     float m_ref = -INFINITY, l = 0.f;
     bool ok = true;
@@ -535,8 +547,9 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
       constexpr int NCH = BN / 32;
       const int k0 = (j_base + j) * BN;
       bool need_mask;
-      if constexpr (MOD) {
-        need_mask = true;
+      if constexpr (MOD) {  // band, lengths, per-row limits and the prefix; the segment test comes after it
+        need_mask = (k0 + BN > kv_len) || (k0 + BN - 1 > q0 + t * BM + p.band_hi) ||
+                    (k0 < q0 + t * BM + BM - 1 + p.band_lo) || mv.row_limit != nullptr || mv.prefix > 0;
       } else if constexpr (BAND) {
         need_mask = (k0 + BN > kv_len) || (k0 + BN - 1 > q0 + t * BM + p.band_hi) ||
                     (k0 < q0 + t * BM + BM - 1 + p.band_lo);
@@ -556,7 +569,7 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
 #endif
       PJX_TRACE_AT(t, j, 2);
 
-      if constexpr (MOD) {
+      if (MOD == 2 && mod_terms) {
         // scaled score -> modifiers -> exp2 domain; a dense bias (BIAS == 1) is added below on top
         const bool plain = !HAS_BIAS;
 #pragma unroll
@@ -619,13 +632,51 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
           if constexpr (MOD) {
             keep = (key <= row + p.band_hi && key >= row + p.band_lo) || key < mv.prefix;
             keep = keep && key < kv_len && key < my_limit;
-            if (mv.seg_k) keep = keep && (key < kv_len ? __ldg(mv.seg_k + key) == my_seg : false);
           } else if constexpr (BAND) {
             keep = key < kv_len && key <= row + p.band_hi && key >= row + p.band_lo;
           } else {
             keep = key < kv_len && (!p.causal || key <= row);
           }
           s[i] = keep ? s[i] : -INFINITY;
+        }
+      }
+      if constexpr (MOD) {
+        if (mv.seg_k) {
+          // Same-segment test, one load per warp and tile: lane L reads the ids of keys k0 + 4 L .. + 3, and
+          // for every distinct row id in the warp four ballots give the 128 keep bits of the rows that carry
+          // it.  A row whose bits are all set (the tile lies inside its segment) has nothing to mask.  Keys
+          // at and past kv_len are masked above: every tile that holds one needs the mask.
+          static_assert(BN == 128, "four keys per lane");
+          int4 g = make_int4(0, 0, 0, 0);
+          if (seg_vec && k0 + BN <= p.Lkv) {
+            g = __ldg(reinterpret_cast<const int4*>(mv.seg_k + k0) + lane);
+          } else {
+            const int kk = k0 + 4 * lane;
+            if (kk + 0 < p.Lkv) g.x = __ldg(mv.seg_k + kk + 0);
+            if (kk + 1 < p.Lkv) g.y = __ldg(mv.seg_k + kk + 1);
+            if (kk + 2 < p.Lkv) g.z = __ldg(mv.seg_k + kk + 2);
+            if (kk + 3 < p.Lkv) g.w = __ldg(mv.seg_k + kk + 3);
+          }
+          uint32_t bits0 = 0, bits1 = 0, bits2 = 0, bits3 = 0;
+          uint32_t remaining = 0xffffffffu;
+          while (remaining) {  // warp-uniform
+            const int v = __shfl_sync(0xffffffffu, my_seg, __ffs(remaining) - 1);
+            const uint32_t b0 = __ballot_sync(0xffffffffu, g.x == v), b1 = __ballot_sync(0xffffffffu, g.y == v);
+            const uint32_t b2 = __ballot_sync(0xffffffffu, g.z == v), b3 = __ballot_sync(0xffffffffu, g.w == v);
+            if (my_seg == v) {
+              bits0 = b0; bits1 = b1; bits2 = b2; bits3 = b3;
+            }
+            remaining &= ~__ballot_sync(0xffffffffu, my_seg == v);
+          }
+          if ((bits0 & bits1 & bits2 & bits3) != 0xffffffffu) {
+#pragma unroll
+            for (int i = 0; i < BN / 4; ++i) {
+              s[4 * i + 0] = (bits0 >> i) & 1u ? s[4 * i + 0] : -INFINITY;
+              s[4 * i + 1] = (bits1 >> i) & 1u ? s[4 * i + 1] : -INFINITY;
+              s[4 * i + 2] = (bits2 >> i) & 1u ? s[4 * i + 2] : -INFINITY;
+              s[4 * i + 3] = (bits3 >> i) & 1u ? s[4 * i + 3] : -INFINITY;
+            }
+          }
         }
       }
 
@@ -661,7 +712,7 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
       const float2 cs2 = make_float2(cs, cs), nm2 = make_float2(neg_m, neg_m);
       float2 sum0 = make_float2(0.f, 0.f), sum1 = make_float2(0.f, 0.f);
       PJX_TRACE_AT(t, j, 3);
-      if constexpr (MOD) {
+      if constexpr (MOD == 2) {
         if (mv.drop_rate > 0.f)
           exp_pack_store_scaled<BN, BF16>(s, cs2, nm2, sum0, sum1, s_addr, [&](int i) { return mod_dropout(mv, row, k0 + i); });
         else
@@ -947,7 +998,51 @@ int sm_count() {
   return v;
 }
 
-template <int DQK, int DV, int BN, int KST, int VST, bool BF16, int BIAS, bool BAND = false, bool MOD = false>
+// Key range per tile of 128 query rows under a segment mask (ScoreMod::q_tile_range): one CTA per
+// (tile, batch row of the ids).
+__global__ void __launch_bounds__(128) seg_tile_range_kernel(const int32_t* __restrict__ seg_q, const int32_t* __restrict__ seg_k,
+                                                             int64_t sq_bs, int64_t sk_bs, int Lq, int Lkv,
+                                                             int32_t* __restrict__ out) {
+  __shared__ int red[4][2];
+  const int tile = blockIdx.x, bs = blockIdx.y, tid = threadIdx.x;
+  const int32_t* sq = seg_q + (int64_t)bs * sq_bs;
+  const int32_t* sk = seg_k + (int64_t)bs * sk_bs;
+  auto block_min_max = [&](int& lo, int& hi) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      lo = min(lo, __shfl_xor_sync(0xffffffffu, lo, o));
+      hi = max(hi, __shfl_xor_sync(0xffffffffu, hi, o));
+    }
+    __syncthreads();  // the previous round's values have been read
+    if ((tid & 31) == 0) {
+      red[tid >> 5][0] = lo;
+      red[tid >> 5][1] = hi;
+    }
+    __syncthreads();
+    lo = min(min(red[0][0], red[1][0]), min(red[2][0], red[3][0]));
+    hi = max(max(red[0][1], red[1][1]), max(red[2][1], red[3][1]));
+  };
+  const int row = tile * 128 + tid;
+  int smin = 0x7fffffff, smax = (int)0x80000000;
+  if (row < Lq) smin = smax = sq[row];
+  block_min_max(smin, smax);
+  int first = 0x7fffffff, last = -1;
+  for (int j = tid; j < Lkv; j += 128) {
+    const int s = sk[j];
+    if (s >= smin && s <= smax) {
+      first = min(first, j);
+      last = max(last, j);
+    }
+  }
+  block_min_max(first, last);
+  if (tid == 0) {
+    int32_t* r = out + ((int64_t)bs * gridDim.x + tile) * 2;
+    r[0] = last < 0 ? 0 : first;
+    r[1] = last + 1;
+  }
+}
+
+template <int DQK, int DV, int BN, int KST, int VST, bool BF16, int BIAS, bool BAND = false, int MOD = 0>
 int launch_one(const FwdParams& p, int dtype, cudaStream_t stream) {
   using C = Cfg<DQK, DV, BN, KST, VST, BIAS == 2>;
   CUtensorMap tq, tk, tv, tb;
@@ -1037,6 +1132,30 @@ int launch_one(const FwdParams& p, int dtype, cudaStream_t stream) {
       (void)cudaGetLastError();  // no memory for the partials: one grid as usual
     }
   }
+  if constexpr (MOD) {
+    // Segment masks: the KV loop of a query tile is cut to the keys whose ids can match (worth a small
+    // kernel of its own from a few KV tiles on; without memory for the ranges every tile is visited).
+    if (p.mod.seg_q && p.mod.seg_k && !p.mod.prefix_len && p.Lkv > 2 * BN) {
+      const int tiles = (p.Lq + BM - 1) / BM;
+      const int nb = (p.mod.seg_q_bs == 0 && p.mod.seg_k_bs == 0) ? 1 : p.B;
+      void* ranges = nullptr;
+      keep_pool_memory();
+      if (nb <= 65535 && cudaMallocAsync(&ranges, (size_t)nb * tiles * 2 * sizeof(int32_t), stream) == cudaSuccess) {
+        seg_tile_range_kernel<<<dim3(tiles, nb), 128, 0, stream>>>(p.mod.seg_q, p.mod.seg_k, p.mod.seg_q_bs, p.mod.seg_k_bs,
+                                                                   p.Lq, p.Lkv, static_cast<int32_t*>(ranges));
+        count_launch();
+        ScoreMod mod = p.mod;
+        mod.q_tile_range = static_cast<const int32_t*>(ranges);
+        mod.q_tile_range_bs = nb == 1 ? 0 : tiles;
+        kern<<<grid, NTHREADS, C::SMEM_BYTES, stream>>>(tq, tk, tv, tb, to, static_cast<const FwdParamsCore&>(p), order_w, mod);
+        count_launch();
+        rc = check_cuda(cudaGetLastError(), "sm100 forward launch (segment ranges)");
+        cudaFreeAsync(ranges, stream);
+        return rc;
+      }
+      (void)cudaGetLastError();
+    }
+  }
   kern<<<grid, NTHREADS, C::SMEM_BYTES, stream>>>(tq, tk, tv, tb, to, static_cast<const FwdParamsCore&>(p), order_w, p.mod);
   count_launch();
   return check_cuda(cudaGetLastError(), "sm100 forward launch");
@@ -1045,8 +1164,14 @@ int launch_one(const FwdParams& p, int dtype, cudaStream_t stream) {
 template <int DQK, int DV, int BN, int KST, int VST, bool BF16>
 int launch_cfg(const FwdParams& p, int dtype, cudaStream_t stream) {
   if (p.mod.on) {
-    if (!p.bias) return launch_one<DQK, DV, BN, KST, VST, BF16, 0, true, true>(p, dtype, stream);
-    return launch_one<DQK, DV, BN, KST, VST, BF16, 1, true, true>(p, dtype, stream);
+    // level 1: masks only (segments, per-row limits, prefix); level 2: score terms and dropout as well
+    const bool terms = p.mod.rel_bias || p.mod.alibi_slopes || p.mod.head_scale || p.mod.softcap > 0.f || p.mod.dropout_rate > 0.f;
+    if (!terms) {
+      if (!p.bias) return launch_one<DQK, DV, BN, KST, VST, BF16, 0, true, 1>(p, dtype, stream);
+      return launch_one<DQK, DV, BN, KST, VST, BF16, 1, true, 1>(p, dtype, stream);
+    }
+    if (!p.bias) return launch_one<DQK, DV, BN, KST, VST, BF16, 0, true, 2>(p, dtype, stream);
+    return launch_one<DQK, DV, BN, KST, VST, BF16, 1, true, 2>(p, dtype, stream);
   }
   if (p.banded()) {
     if (!p.bias) return launch_one<DQK, DV, BN, KST, VST, BF16, 0, true>(p, dtype, stream);

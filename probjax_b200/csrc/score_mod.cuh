@@ -49,6 +49,13 @@ struct ScoreMod {
   float dropout_rate = 0.f;           // > 0: on
   uint32_t dropout_seed = 0;
   int on = 0;                         // any field set
+  // Filled by the tcgen05 forward's launcher, not by callers: for every tile of 128 query rows the
+  // range [first, last + 1) of keys whose segment id lies between the smallest and the largest id
+  // of the tile's rows -- no key outside it can match a row of the tile, so the KV loop skips the
+  // tiles outside (what the reference's block-sparse `index_offset` lists do for its kernels,
+  // kernels/attention.py:1485-1566).  [Bs, tiles, 2]; batch stride in tiles (0 = shared).
+  const int32_t* q_tile_range = nullptr;
+  int64_t q_tile_range_bs = 0;
 
   __host__ __device__ bool has_mask() const { return seg_q || row_kv_limit || prefix_len; }
   __host__ __device__ bool nonlinear() const { return head_scale || softcap > 0.f; }

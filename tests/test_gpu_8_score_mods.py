@@ -121,6 +121,43 @@ def test_every_mask_fp32_and_tcgen05(name):
     assert_close(got, lse, want, want_lse, torch.bfloat16, f"tcgen05 {name}")
 
 
+@pytest.mark.parametrize("name", ["block_diagonal", "block_diagonal_causal", "same_segment", "marginalization", "seq_len",
+                                  "unsorted_ids", "many_segments_with_lengths"])
+def test_segment_masks_skip_key_tiles(name):
+    """Segment masks over several KV tiles on the tensor-core kernel, where the KV loop of a query tile is cut
+    to the keys whose ids can match: sorted ids (block diagonal), ids in reverse order on the key side, ids
+    that give dropped tokens a segment of their own, ids in random order that differ per sequence, and 16
+    short segments under key lengths.  Keys outside the ranges hold NaN where that is well defined."""
+    d = dev()
+    b, s, h, hk, dd = 2, 1000, 4, 2, 64
+    g = torch.Generator().manual_seed(77)
+    lens = None
+    if name == "unsorted_ids":
+        mask = M.SameSegmentMask(torch.randint(0, 5, (b, s), generator=g).to(torch.int32))
+    elif name == "many_segments_with_lengths":
+        seg = (torch.arange(s) // 64).to(torch.int32)[None].expand(b, s).contiguous()
+        lens = torch.tensor([s, 391], dtype=torch.int32)
+        mask = M.ComposeMask("and", M.BlockDiagonalCausalMask(seg), M.KVLenMask(lens))
+    else:
+        mask = _masks(b, s)[name]
+    q, k, v = randn((b, s, h, dd), torch.bfloat16, 4), randn((b, s, hk, dd), torch.bfloat16, 5), randn((b, s, hk, dd), torch.bfloat16, 6)
+    want, want_lse = _want(q, k, v, mask, None, 0.125, h)
+    kd, vd = k.clone(), v.clone()
+    if lens is not None:
+        for i in range(b):
+            kd[i, int(lens[i]):] = float("nan")
+            vd[i, int(lens[i]):] = float("nan")
+    got, lse = pj.mha(q.to(d), kd.to(d), vd.to(d), mask=mask, sm_scale=0.125, return_lse=True, implementation="b200:tcgen05")
+    pj.check_status(d)
+    assert_close(got, lse, want, want_lse, torch.bfloat16, f"tcgen05 {name} over several KV tiles")
+    if name in ("block_diagonal_causal", "same_segment"):  # with a bias expression on top
+        bias = M.SumBias(M.CausalAlibiBias(), M.SoftCappingBias(3.0))
+        got, lse = pj.mha(q.to(d), k.to(d), v.to(d), mask=mask, bias=bias, sm_scale=0.125, return_lse=True,
+                          implementation="b200:tcgen05")
+        want, want_lse = _want(q, k, v, mask, bias, 0.125, h)
+        assert_close(got, lse, want, want_lse, torch.bfloat16, f"tcgen05 {name} + bias over several KV tiles")
+
+
 @pytest.mark.parametrize("name", list(_biases()))
 def test_every_bias_fp32_and_tcgen05(name):
     d = dev()
