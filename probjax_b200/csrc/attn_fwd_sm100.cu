@@ -518,16 +518,22 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
     ScoreModView mv = {};
     int my_seg = 0, my_limit = 0x7fffffff;
     bool mod_terms = false;  // a modifier changes the scores (not only the mask)
+    [[maybe_unused]] int mod_kind = 0;
     bool seg_vec = false;    // the key-side segment ids can be read four at a time
     if constexpr (MOD) {
       mv = view_of(smod, b, h, p.Lq);
       if (row_ok && mv.seg_q) my_seg = mv.seg_q[row];
       if (row_ok && mv.row_limit) my_limit = mv.row_limit[row];
-      if constexpr (MOD == 2) mod_terms = mv.hscale_m1 != 0.f || mv.softcap > 0.f || mv.rel != nullptr || mv.alibi_mode != 0;
+      if constexpr (MOD == 2) {  // which score terms are on: head scale 1, soft cap 2, relative table 4, ALiBi 8 / 16
+        mod_kind = (mv.hscale_m1 != 0.f ? 1 : 0) | (mv.softcap > 0.f ? 2 : 0) | (mv.rel != nullptr ? 4 : 0) | (mv.alibi_mode << 3);
+        mod_terms = mod_kind != 0;
+      }
       seg_vec = mv.seg_k != nullptr && (reinterpret_cast<uintptr_t>(mv.seg_k) & 15) == 0;
     }
     // scores reach the exponential already in the exp2 domain when a bias or a score modifier was applied
-    const float cs = (HAS_BIAS || (MOD == 2 && mod_terms)) ? 1.f : c1;
+    // (a positive per-head scale alone is folded into that multiplier: the row maximum is taken before it)
+    const bool hs_fold = MOD == 2 && !HAS_BIAS && mod_kind == 1 && mv.hscale_m1 > -1.f;
+    const float cs = HAS_BIAS ? 1.f : hs_fold ? c1 * (1.f + mv.hscale_m1) : (MOD == 2 && mod_terms) ? 1.f : c1;
 
     float m_ref = -INFINITY, l = 0.f;
     bool ok = true;
@@ -570,15 +576,63 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
       PJX_TRACE_AT(t, j, 2);
 
       if (MOD == 2 && mod_terms) {
-        // scaled score -> modifiers -> exp2 domain; a dense bias (BIAS == 1) is added below on top
+        // scaled score -> modifiers -> exp2 domain; a dense bias (BIAS == 1) is added below on top.
+        // One term alone (the usual case) has a loop of its own with no test per element; the values
+        // written for rows past Lq and keys past kv_len are never used (not stored / masked below).
         const bool plain = !HAS_BIAS;
+        if (plain && (mod_kind == 8 || mod_kind == 16)) {  // ALiBi: s - slope * distance
+          // float arithmetic throughout (an integer-to-float conversion per element runs at a quarter of
+          // the rate); a tile on one side of the diagonal has a distance that is linear in the key
+          const float sl2 = mv.slope * kLog2e;
+          const int d0 = row - k0;  // row - key at the tile's first key
+          const float d0f = (float)d0;
+          if (d0 >= BN - 1) {  // every key at or before the row
+            const float base = -sl2 * d0f;
 #pragma unroll
-        for (int i = 0; i < BN; ++i) {
-          const int key = k0 + i;
-          const float sc = s[i] * p.sm_scale;
-          const float md = (row_ok && key < kv_len) ? mod_score<false>(mv, sc, row, key, nullptr) : sc;
-          // the bias branch multiplies by c1 = sm_scale * log2(e) itself: hand it md / sm_scale
-          s[i] = plain ? md * kLog2e : md / p.sm_scale;
+            for (int i = 0; i < BN; ++i) s[i] = fmaf(s[i], c1, fmaf(sl2, (float)i, base));
+          } else if (d0 <= 0) {  // every key at or after the row: no penalty (causal form) or slope * (key - row)
+            const float sl = mod_kind == 8 ? 0.f : sl2;
+            const float base = sl * d0f;
+#pragma unroll
+            for (int i = 0; i < BN; ++i) s[i] = fmaf(s[i], c1, fmaf(-sl, (float)i, base));
+          } else if (mod_kind == 8) {
+#pragma unroll
+            for (int i = 0; i < BN; ++i) s[i] = fmaf(s[i], c1, -sl2 * fmaxf(d0f - (float)i, 0.f));
+          } else {
+#pragma unroll
+            for (int i = 0; i < BN; ++i) s[i] = fmaf(s[i], c1, -sl2 * fabsf(d0f - (float)i));
+          }
+        } else if (plain && mod_kind == 1) {  // per-head scale: folded into the multiplier of the exponential if positive
+          if (!hs_fold) {
+            const float c = c1 * (1.f + mv.hscale_m1);
+#pragma unroll
+            for (int i = 0; i < BN; ++i) s[i] *= c;
+          }
+        } else if (plain && mod_kind == 2) {  // soft cap: cap * tanh(s / cap)
+          const float a = p.sm_scale / mv.softcap, c = mv.softcap * kLog2e;
+#pragma unroll
+          for (int i = 0; i < BN; ++i) {
+            float th;
+            asm("tanh.approx.f32 %0, %1;" : "=f"(th) : "f"(s[i] * a));
+            s[i] = c * th;
+          }
+        } else if (plain && mod_kind == 4) {  // relative-position table
+          const bool inside = row_ok && k0 + BN <= p.Lkv;
+          const float* rel0 = mv.rel + (k0 - row);
+#pragma unroll
+          for (int i = 0; i < BN; ++i) {
+            const float r = (inside || (row_ok && k0 + i < p.Lkv)) ? __ldg(rel0 + i) : 0.f;
+            s[i] = fmaf(s[i], c1, r * kLog2e);
+          }
+        } else {
+#pragma unroll
+          for (int i = 0; i < BN; ++i) {
+            const int key = k0 + i;
+            const float sc = s[i] * p.sm_scale;
+            const float md = (row_ok && key < kv_len) ? mod_score<false>(mv, sc, row, key, nullptr) : sc;
+            // the bias branch multiplies by c1 = sm_scale * log2(e) itself: hand it md / sm_scale
+            s[i] = plain ? md * kLog2e : md / p.sm_scale;
+          }
         }
       }
       if constexpr (BIAS == 2) {
