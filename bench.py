@@ -437,6 +437,20 @@ def main():
                 "TFLOP/s", pk["bf16_tflops"], "tensor", pk["source"])
         except Exception as e:
             extras["prefill_window_1024"] = {"error": str(e)[:300]}
+        try:  # structured masks and score terms evaluated inside the kernel, through the mask / bias objects:
+            # packed sequences (8 segments of 512 tokens, causal inside each) and causal attention with ALiBi
+            seg = (torch.arange(C2["S"], device=dev) // 512).to(torch.int32)[None]
+            m_seg = pj.BlockDiagonalCausalMask(seg)
+            extras["prefill_packed_8x512_causal"] = bench_extra(
+                "packed", lambda: pj.mha(q, k, v, mask=m_seg, sm_scale=sc), xs, xw,
+                8 * prefill_flops(C2["B"], C2["Hq"], 512, 512, C2["D"], C2["D"], True) / 1e12,
+                "TFLOP/s", pk["bf16_tflops"], "tensor", pk["source"])
+            m_c, b_al = pj.CausalMask(), pj.CausalAlibiBias()
+            extras["prefill_causal_alibi"] = bench_extra(
+                "alibi", lambda: pj.mha(q, k, v, mask=m_c, bias=b_al, sm_scale=sc), xs, xw, fl_c / 1e12,
+                "TFLOP/s", pk["bf16_tflops"], "tensor", pk["source"])
+        except Exception as e:
+            extras["prefill_packed_8x512_causal"] = {"error": str(e)[:300]}
         try:  # backward of the headline shape (tcgen05 dQ and dK/dV kernels + the delta kernel);
             # FLOPs counted as 2.5 x the forward (five products), although the split design computes seven
             o_b, lse_b = pj.attention_forward(q, k, v, sm_scale=sc, return_lse=True)
