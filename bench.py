@@ -599,7 +599,7 @@ def main():
 
 def compact_extras(extras, world):
     """Keeps the one JSON line short enough to survive a truncated capture of stdout: the bound of an entry
-    follows from its unit and is dropped; the slower variants of the sharded decode keep their time, rate
+    follows from its unit and is dropped, and so is the unit where it is the line's own (TFLOP/s); the slower variants of the sharded decode keep their time, rate
     and error only; a multi-GPU line keeps the entries that depend on the number of GPUs (the others are in
     the one-GPU line of the same build)."""
     keep_multi = ("prefill_causal", "decode_32k", "decode_ragged", "decode_32k_seq_sharded", "decode_128k")
@@ -608,7 +608,8 @@ def compact_extras(extras, world):
         if world > 1 and name not in keep_multi:
             continue
         if isinstance(entry, dict):
-            entry = {k: v for k, v in entry.items() if k != "bound"}
+            entry = {k: v for k, v in entry.items()
+                     if k not in ("bound", "frac_of_nominal_8TBs") and not (k == "unit" and v == "TFLOP/s")}
             if name == "decode_32k_seq_sharded":
                 for mode, res in list(entry.items()):
                     if isinstance(res, dict):

@@ -140,6 +140,9 @@ def _gqa_group(hq: int, hkv: int) -> int:
     return hq // hkv
 
 
+_constant_copies: dict = {}  # (id of a library constant, device, dtype) -> (the constant, its device copy)
+
+
 class ScoreMods:
     """The ``pjx_score_mod`` argument of one call: the structured part of a lowered mask and bias
     (segment ids, per-row key limits, prefix lengths, relative-position table, ALiBi slopes, per-head
@@ -155,7 +158,16 @@ class ScoreMods:
         st = _lib.ScoreMod()
 
         def put(t, dtype):
-            t = torch.as_tensor(t).to(device=self.device, dtype=dtype).contiguous()
+            if getattr(t, "_pjx_constant", False):
+                # a constant of the library (ALiBi slopes): one device copy per device, not one pageable
+                # upload -- which waits for the stream -- per call
+                key = (id(t), self.device.index or 0, dtype)
+                hit = _constant_copies.get(key)
+                if hit is None:
+                    hit = _constant_copies[key] = (t, t.to(device=self.device, dtype=dtype).contiguous())
+                t = hit[1]
+            else:
+                t = torch.as_tensor(t).to(device=self.device, dtype=dtype).contiguous()
             self._keep.append(t)
             return t
 

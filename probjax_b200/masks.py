@@ -26,6 +26,7 @@ keys around each query row (``i + lo <= j <= i + hi``; the causal mask is the ba
 
 from __future__ import annotations
 
+import functools
 from dataclasses import dataclass
 from typing import Any, Optional
 
@@ -370,9 +371,22 @@ class SumBias(AttentionBias):
         return a.float().cpu() + b.float().cpu() if a.device != b.device else a.float() + b.float()
 
 
+def _library_constant(t):
+    """Marks a tensor the library computed from Python scalars alone: its device copy may be cached
+    (nobody else holds it, so nobody can change it)."""
+    t._pjx_constant = True
+    return t
+
+
+@functools.lru_cache(maxsize=64)
 def _alibi_slopes(num_heads):
     # attention_mask_bias.py:2223-2227: slope(h) = 2^-(h+1)
-    return torch.exp2(-(torch.arange(num_heads, dtype=torch.float32) + 1.0))
+    return _library_constant(torch.exp2(-(torch.arange(num_heads, dtype=torch.float32) + 1.0)))
+
+
+@functools.lru_cache(maxsize=64)
+def _constant_slopes(num_heads, value):
+    return _library_constant(torch.full((num_heads,), value, dtype=torch.float32))
 
 
 class CausalAlibiBias(AttentionBias):
@@ -856,7 +870,7 @@ def lower_bias_structured(bias, batch: int, heads: int, q_len: int, kv_len: int)
         elif isinstance(term, SymmetricAlibiBias):
             slopes, mode = _alibi_slopes(heads), 2
         elif isinstance(term, DistanceDecayBias):
-            slopes, mode = torch.full((heads,), term.alpha, dtype=torch.float32), 2
+            slopes, mode = _constant_slopes(heads, float(term.alpha)), 2
         if slopes is not None and out.alibi_slopes is None:
             out.alibi_slopes, out.alibi_mode = slopes, mode
             continue
