@@ -554,8 +554,9 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
       const int k0 = (j_base + j) * BN;
       bool need_mask;
       if constexpr (MOD) {  // band, lengths, per-row limits and the prefix; the segment test comes after it
-        need_mask = (k0 + BN > kv_len) || (k0 + BN - 1 > q0 + t * BM + p.band_hi) ||
-                    (k0 < q0 + t * BM + BM - 1 + p.band_lo) || mv.row_limit != nullptr || mv.prefix > 0;
+        const bool band_cut = (k0 + BN - 1 > q0 + t * BM + p.band_hi) || (k0 < q0 + t * BM + BM - 1 + p.band_lo);
+        // (a tile inside the prefix is visible whatever the band says; a row limit matters to the rows it cuts)
+        need_mask = (k0 + BN > kv_len) || (band_cut && k0 + BN > mv.prefix) || my_limit < k0 + BN;
       } else if constexpr (BAND) {
         need_mask = (k0 + BN > kv_len) || (k0 + BN - 1 > q0 + t * BM + p.band_hi) ||
                     (k0 < q0 + t * BM + BM - 1 + p.band_lo);
