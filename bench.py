@@ -299,6 +299,10 @@ def main():
                          "(what-if builds of the forward kernel, whose outputs are wrong on purpose)")
     ap.add_argument("--only-latent", action="store_true",
                     help="time only the latent-attention configuration on --batch batch rows (profiling captures)")
+    ap.add_argument("--only-modifier", default=None,
+                    choices=["band", "row_limits", "one_segment", "packed_8x512", "head_scale", "causal_alibi", "soft_cap"],
+                    help="time only the headline shape on --batch rows under one structured mask or score term "
+                         "(profiling captures of the forward kernel's band / modifier variants)")
     ap.add_argument("--kernel", default=None, choices=[None, "b200:generic", "b200:tcgen05"],
                     help="force one forward kernel for the headline (default: the library's own choice)")
     args = ap.parse_args()
@@ -345,6 +349,9 @@ def main():
         return
     if args.only_prefill:
         only_prefill(args, dev, pk)
+        return
+    if args.only_modifier:
+        only_modifier(args, dev, pk)
         return
     if args.only_latent_decode:
         only_latent_decode(args, dev, pk)
@@ -751,6 +758,48 @@ def only_prefill(args, dev, pk):
                           args.steps, args.warmup, fl / 1e12, "TFLOP/s", pk["bf16_tflops"], "tensor", pk["source"])
         out[name] = {"ms": res["ms"], "tflops": res["value"]}
     _emit(out)
+
+
+def only_modifier(args, dev, pk):
+    """The headline shape on `--batch` batch rows under one structured mask or score term, with the mask data
+    on the device: `band` is a band that never cuts (the band variant of the kernel with nothing to mask),
+    `row_limits` per-row key limits that never cut and `one_segment` a single segment (the mask-only
+    modifier level), `head_scale` a positive per-head scale (the full level with no work per element)."""
+    import oracle
+    import probjax_b200 as pj
+
+    c = oracle.make_config(2, B=args.batch)
+    q, k, v = c["q"].to(dev), c["k"].to(dev), c["v"].to(dev)
+    S, H, sc = C2["S"], C2["Hq"], c["sm_scale"]
+    causal = False
+    kw = {}
+    if args.only_modifier == "band":
+        def fn():
+            return pj.attention_forward(q, k, v, band=(-(1 << 20), 1 << 20), sm_scale=sc)
+    else:
+        if args.only_modifier == "row_limits":
+            kw = dict(mask=pj.KeyPaddingMask(torch.full((S,), S, dtype=torch.int32, device=dev)))
+        elif args.only_modifier == "one_segment":
+            kw = dict(mask=pj.SameSegmentMask(torch.zeros((1, S), dtype=torch.int32, device=dev)))
+        elif args.only_modifier == "packed_8x512":
+            kw = dict(mask=pj.BlockDiagonalCausalMask((torch.arange(S, device=dev) // 512).to(torch.int32)[None]))
+        elif args.only_modifier == "head_scale":
+            kw = dict(bias=pj.PerHeadScaleBias(torch.linspace(0.5, 1.5, H, device=dev)))
+        elif args.only_modifier == "causal_alibi":
+            kw, causal = dict(mask=pj.CausalMask(), bias=pj.CausalAlibiBias()), True
+        elif args.only_modifier == "soft_cap":
+            kw = dict(bias=pj.SoftCappingBias(30.0))
+
+        def fn():
+            return pj.mha(q, k, v, sm_scale=sc, **kw)
+
+    if args.only_modifier == "packed_8x512":
+        fl = 8 * prefill_flops(args.batch, H, 512, 512, C2["D"], C2["D"], True)
+    else:
+        fl = prefill_flops(args.batch, H, S, S, C2["D"], C2["D"], causal)
+    res = bench_extra(args.only_modifier, fn, args.steps, args.warmup, fl / 1e12, "TFLOP/s", pk["bf16_tflops"], "tensor", pk["source"])
+    _emit({"config": {"workload": f"GQA prefill bf16 B{args.batch} Hq32 Hkv8 S4096 D128, {args.only_modifier}"},
+           "ms": res.get("ms"), "tflops": res.get("value"), "error": res.get("error")})
 
 
 def only_latent(args, dev, pk):
