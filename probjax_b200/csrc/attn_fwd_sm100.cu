@@ -82,7 +82,7 @@ __device__ __forceinline__ float fmax3(float a, float b, float c) {
   return y;
 }
 
-template <int DQK, int DV, int BN, int KST, int VST, bool BIAS_STAGED = false>
+template <int DQK, int DV, int BN, int KST, int VST, bool BIAS_STAGED = false, bool REL_STAGED = false>
 struct Cfg {
   static constexpr int Q_SUB = DQK / 64, V_SUB = DV / 64;
   static constexpr int Q_TILE_BYTES = Q_SUB * BM * 128;
@@ -94,8 +94,14 @@ struct Cfg {
   // staged bias: per query tile one fp32 [128 rows x BN keys] tile as BN/32 boxes of 128 x 32 (128-byte rows)
   static constexpr int BIAS_TILE_BYTES = BIAS_STAGED ? (BN / 32) * BM * 128 : 0;
   static constexpr int OFF_BIAS = OFF_V + VST * V_TILE_BYTES;
-  static constexpr int OFF_BAR = OFF_BIAS + 2 * BIAS_TILE_BYTES;
-  static constexpr int N_BAR = 2 + 2 * KST + 2 * VST + 6 + 4 + 2 + 1;
+  // window of a relative-position table that one (query tile, KV tile) pair uses: 2 BM - 1 entries, double
+  // buffered per query tile.  Only the instantiation that reads it reserves it: at (128,128) these 4 KB
+  // push the CTA from the 196 KB shared-memory configuration to the 228 KB one, and the 32 KB of L1 that
+  // takes away made every variant that spills 12-20 % slower when all of them carried it.
+  static constexpr int REL_BYTES = REL_STAGED ? 2 * 2 * (2 * BM) * 4 : 0;
+  static constexpr int OFF_REL = OFF_BIAS + 2 * BIAS_TILE_BYTES;
+  static constexpr int OFF_BAR = OFF_REL + REL_BYTES;
+  static constexpr int N_BAR = 2 + 2 * KST + 2 * VST + 6 + 4 + 2 + 1 + 2;
   static constexpr int SMEM_BYTES = OFF_BAR + N_BAR * 8 + 16 + 1024;  // + alignment slack
   static constexpr int TMEM_USED = 2 * BN + 2 * DV;
   static constexpr int TMEM_COLS = TMEM_USED <= 128 ? 128 : (TMEM_USED <= 256 ? 256 : 512);
@@ -215,7 +221,9 @@ __device__ __forceinline__ void exp_pack_store_scaled(const float (&s)[BN], floa
 //
 // MOD (implies BAND): structured masks and score modifiers (score_mod.cuh) are evaluated by the
 // softmax threads: level 1 holds the masks only (segment ids, per-row key limits, prefix), level 2
-// also passes the scaled score of (row, key) through the score terms and applies dropout.  No tile
+// also passes the scaled score of (row, key) through the score terms and applies dropout, level 3 is
+// the masks and a relative-position table alone (every path that shares an instantiation costs the
+// others registers: with the table's path inside level 2 its other terms ran 12-20 % slower).  No tile
 // beyond the band / prefix range is visited; under a segment mask the launcher also gives every
 // query tile the key range its ids can match, so tiles outside the range are skipped.
 //
@@ -238,7 +246,7 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
   const int item = (order_item0 >> 8) + (SPLIT ? static_cast<int>(blockIdx.x >> 1) : static_cast<int>(blockIdx.x));
   const int half = SPLIT ? static_cast<int>(blockIdx.x & 1) : 0;
   static_assert(!MOD || (BAND && BIAS != 2), "the modifier variant builds on the band variant without staged bias");
-  using C = Cfg<DQK, DV, BN, KST, VST, BIAS == 2>;
+  using C = Cfg<DQK, DV, BN, KST, VST, BIAS == 2, MOD == 3>;
   extern __shared__ unsigned char smem_unaligned[];
   unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_unaligned) + 1023) & ~uintptr_t(1023));
   const uint32_t sbase = smem_u32(smem);
@@ -257,6 +265,7 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
   const int B_EMPTY = B_FULL + 2;         // [2] staged bias tile consumed (128 arrivals)
   const int O_STAGED = B_EMPTY + 2;       // [2] output tile written to shared memory (128 arrivals)
   const int V_CLEAN = O_STAGED + 2;       // rows past the valid length cleared in the last V tile (32 arrivals)
+  [[maybe_unused]] const int REL_SYNC = V_CLEAN + 1;  // [2] table window of a query tile staged (128 arrivals)
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + C::OFF_BAR + C::N_BAR * 8);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
@@ -524,7 +533,7 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
       mv = view_of(smod, b, h, p.Lq);
       if (row_ok && mv.seg_q) my_seg = mv.seg_q[row];
       if (row_ok && mv.row_limit) my_limit = mv.row_limit[row];
-      if constexpr (MOD == 2) {  // which score terms are on: head scale 1, soft cap 2, relative table 4, ALiBi 8 / 16
+      if constexpr (MOD >= 2) {  // which score terms are on: head scale 1, soft cap 2, relative table 4, ALiBi 8 / 16
         mod_kind = (mv.hscale_m1 != 0.f ? 1 : 0) | (mv.softcap > 0.f ? 2 : 0) | (mv.rel != nullptr ? 4 : 0) | (mv.alibi_mode << 3);
         mod_terms = mod_kind != 0;
       }
@@ -533,7 +542,7 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
     // scores reach the exponential already in the exp2 domain when a bias or a score modifier was applied
     // (a positive per-head scale alone is folded into that multiplier: the row maximum is taken before it)
     const bool hs_fold = MOD == 2 && !HAS_BIAS && mod_kind == 1 && mv.hscale_m1 > -1.f;
-    const float cs = HAS_BIAS ? 1.f : hs_fold ? c1 * (1.f + mv.hscale_m1) : (MOD == 2 && mod_terms) ? 1.f : c1;
+    const float cs = HAS_BIAS ? 1.f : hs_fold ? c1 * (1.f + mv.hscale_m1) : (MOD >= 2 && mod_terms) ? 1.f : c1;
 
     float m_ref = -INFINITY, l = 0.f;
     bool ok = true;
@@ -617,14 +626,6 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
             asm("tanh.approx.f32 %0, %1;" : "=f"(th) : "f"(s[i] * a));
             s[i] = c * th;
           }
-        } else if (plain && mod_kind == 4) {  // relative-position table
-          const bool inside = row_ok && k0 + BN <= p.Lkv;
-          const float* rel0 = mv.rel + (k0 - row);
-#pragma unroll
-          for (int i = 0; i < BN; ++i) {
-            const float r = (inside || (row_ok && k0 + i < p.Lkv)) ? __ldg(rel0 + i) : 0.f;
-            s[i] = fmaf(s[i], c1, r * kLog2e);
-          }
         } else {
 #pragma unroll
           for (int i = 0; i < BN; ++i) {
@@ -635,6 +636,27 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
             s[i] = plain ? md * kLog2e : md / p.sm_scale;
           }
         }
+      }
+      if constexpr (MOD == 3 && C::REL_BYTES > 0) {  // a relative-position table alone, no dense bias
+        // The 128 x 128 scores of a tile pair use 2 BM - 1 consecutive entries, table[key - row]: the tile's
+        // 128 softmax threads stage them (times log2 e) in shared memory, meet at a bounded barrier, and row
+        // r reads entry BM - 1 - r + i for key i -- consecutive lanes read consecutive words.  Two buffers
+        // per query tile: a thread writes the buffer of tile j + 2 only after the barrier of tile j + 1,
+        // which every thread reaches after its reads of tile j.
+        static_assert(BN == BM, "the window is laid out for square tile pairs");
+        float* win = reinterpret_cast<float*>(smem + C::OFF_REL) + (t * 2 + (j & 1)) * (2 * BM);
+        const int base = k0 - (q0 + t * BM) - (BM - 1);  // win[x] = table[base + x]
+        for (int x = r_in; x < 2 * BM - 1; x += BM) {
+          const int idx = base + x;
+          win[x] = (idx > -p.Lq && idx < p.Lkv) ? __ldg(mv.rel + idx) * kLog2e : 0.f;
+        }
+        mbar_arrive(BAR(REL_SYNC + t));
+        ok = mbar_wait(BAR(REL_SYNC + t), j & 1, abort_flag);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
+        const float* mine = win + (BM - 1 - r_in);
+#pragma unroll
+        for (int i = 0; i < BN; ++i) s[i] = fmaf(s[i], c1, mine[i]);
       }
       if constexpr (BIAS == 2) {
         ok = mbar_wait(BAR(B_FULL + t), j & 1, abort_flag);
@@ -1099,7 +1121,7 @@ __global__ void __launch_bounds__(128) seg_tile_range_kernel(const int32_t* __re
 
 template <int DQK, int DV, int BN, int KST, int VST, bool BF16, int BIAS, bool BAND = false, int MOD = 0>
 int launch_one(const FwdParams& p, int dtype, cudaStream_t stream) {
-  using C = Cfg<DQK, DV, BN, KST, VST, BIAS == 2>;
+  using C = Cfg<DQK, DV, BN, KST, VST, BIAS == 2, MOD == 3>;
   CUtensorMap tq, tk, tv, tb;
   int rc;
   if ((rc = make_tmap_blhd(&tq, p.q, dtype, p.B, p.Lq, p.Hq, DQK, BM))) return rc;
@@ -1221,6 +1243,9 @@ int launch_cfg(const FwdParams& p, int dtype, cudaStream_t stream) {
   if (p.mod.on) {
     // level 1: masks only (segments, per-row limits, prefix); level 2: score terms and dropout as well
     const bool terms = p.mod.rel_bias || p.mod.alibi_slopes || p.mod.head_scale || p.mod.softcap > 0.f || p.mod.dropout_rate > 0.f;
+    // level 3: a relative-position table as the only score term and no dense bias (the table's window is staged)
+    if (p.mod.rel_bias && !p.mod.alibi_slopes && !p.mod.head_scale && !(p.mod.softcap > 0.f) && !(p.mod.dropout_rate > 0.f) && !p.bias)
+      return launch_one<DQK, DV, BN, KST, VST, BF16, 0, true, 3>(p, dtype, stream);
     if (!terms) {
       if (!p.bias) return launch_one<DQK, DV, BN, KST, VST, BF16, 0, true, 1>(p, dtype, stream);
       return launch_one<DQK, DV, BN, KST, VST, BF16, 1, true, 1>(p, dtype, stream);

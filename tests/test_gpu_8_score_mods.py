@@ -158,6 +158,25 @@ def test_segment_masks_skip_key_tiles(name):
         assert_close(got, lse, want, want_lse, torch.bfloat16, f"tcgen05 {name} + bias over several KV tiles")
 
 
+@pytest.mark.parametrize("lq,lkv,causal", [(700, 700, False), (500, 900, False), (640, 640, True), (130, 1000, False)])
+def test_relative_table_over_several_kv_tiles(lq, lkv, causal):
+    """A relative-position bias alone on the tensor-core kernel over many KV tiles (the kernel stages the
+    window of the table that a tile pair uses in shared memory, two buffers in turn), rectangular problems
+    included: table entries from -(Lq - 1) to Lkv - 1."""
+    d = dev()
+    b, h, hk, dd = 2, 4, 2, 64
+    g = torch.Generator().manual_seed(5)
+    bias = M.T5RelativePositionBias(torch.randn((h, 16), generator=g), num_buckets=16, max_distance=64)
+    mask = M.CausalMask() if causal else None
+    q, k, v = randn((b, lq, h, dd), torch.bfloat16, 7), randn((b, lkv, hk, dd), torch.bfloat16, 8), randn((b, lkv, hk, dd), torch.bfloat16, 9)
+    dense = bias.dense(lq, lkv, batch_size=1, num_heads=h)
+    keep = None if mask is None else mask.dense(lq, lkv, batch_size=b, num_heads=1)
+    want, want_lse = oracle.xla_attention(q, k, v, keep=keep, bias=dense, sm_scale=0.125, return_lse=True)
+    got, lse = pj.mha(q.to(d), k.to(d), v.to(d), mask=mask, bias=bias, sm_scale=0.125, return_lse=True, implementation="b200:tcgen05")
+    pj.check_status(d)
+    assert_close(got, lse, want, want_lse, torch.bfloat16, f"tcgen05 T5 table Lq={lq} Lkv={lkv} causal={causal}")
+
+
 @pytest.mark.parametrize("name", list(_biases()))
 def test_every_bias_fp32_and_tcgen05(name):
     d = dev()
