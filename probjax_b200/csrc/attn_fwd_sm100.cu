@@ -94,11 +94,11 @@ struct Cfg {
   // staged bias: per query tile one fp32 [128 rows x BN keys] tile as BN/32 boxes of 128 x 32 (128-byte rows)
   static constexpr int BIAS_TILE_BYTES = BIAS_STAGED ? (BN / 32) * BM * 128 : 0;
   static constexpr int OFF_BIAS = OFF_V + VST * V_TILE_BYTES;
-  // window of a relative-position table that one (query tile, KV tile) pair uses: 2 BM - 1 entries, double
-  // buffered per query tile.  Only the instantiation that reads it reserves it: at (128,128) these 4 KB
-  // push the CTA from the 196 KB shared-memory configuration to the 228 KB one, and the 32 KB of L1 that
-  // takes away made every variant that spills 12-20 % slower when all of them carried it.
-  static constexpr int REL_BYTES = REL_STAGED ? 2 * 2 * (2 * BM) * 4 : 0;
+  // window of a relative-position table that one (query tile, KV tile) pair uses: 2 BM - 1 entries per query
+  // tile, one buffer each.  Only the instantiation that reads it reserves it, and only 2 KB: at (128,128) a
+  // double-buffered 4 KB pushed the CTA from the 196 KB shared-memory configuration to the 228 KB one, and
+  // the 32 KB of L1 that takes away made every variant that spills 12-20 % slower when all of them carried it.
+  static constexpr int REL_BYTES = REL_STAGED ? 2 * (2 * BM) * 4 : 0;
   static constexpr int OFF_REL = OFF_BIAS + 2 * BIAS_TILE_BYTES;
   static constexpr int OFF_BAR = OFF_REL + REL_BYTES;
   static constexpr int N_BAR = 2 + 2 * KST + 2 * VST + 6 + 4 + 2 + 1 + 2;
@@ -640,23 +640,29 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
       if constexpr (MOD == 3 && C::REL_BYTES > 0) {  // a relative-position table alone, no dense bias
         // The 128 x 128 scores of a tile pair use 2 BM - 1 consecutive entries, table[key - row]: the tile's
         // 128 softmax threads stage them (times log2 e) in shared memory, meet at a bounded barrier, and row
-        // r reads entry BM - 1 - r + i for key i -- consecutive lanes read consecutive words.  Two buffers
-        // per query tile: a thread writes the buffer of tile j + 2 only after the barrier of tile j + 1,
-        // which every thread reaches after its reads of tile j.
+        // r reads entry BM - 1 - r + i for key i -- consecutive lanes read consecutive words.  One buffer per
+        // query tile and two phases of one barrier per KV tile: "window written" (waited for at once) and
+        // "window read" (arrived at after the reads, waited for a whole tile later, before the next write).
         static_assert(BN == BM, "the window is laid out for square tile pairs");
-        float* win = reinterpret_cast<float*>(smem + C::OFF_REL) + (t * 2 + (j & 1)) * (2 * BM);
+        float* win = reinterpret_cast<float*>(smem + C::OFF_REL) + t * (2 * BM);
+        if (j > 0) {
+          ok = mbar_wait(BAR(REL_SYNC + t), 1, abort_flag);
+          ok = __all_sync(0xffffffffu, ok);
+          if (!ok) break;
+        }
         const int base = k0 - (q0 + t * BM) - (BM - 1);  // win[x] = table[base + x]
         for (int x = r_in; x < 2 * BM - 1; x += BM) {
           const int idx = base + x;
           win[x] = (idx > -p.Lq && idx < p.Lkv) ? __ldg(mv.rel + idx) * kLog2e : 0.f;
         }
         mbar_arrive(BAR(REL_SYNC + t));
-        ok = mbar_wait(BAR(REL_SYNC + t), j & 1, abort_flag);
+        ok = mbar_wait(BAR(REL_SYNC + t), 0, abort_flag);
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
         const float* mine = win + (BM - 1 - r_in);
 #pragma unroll
         for (int i = 0; i < BN; ++i) s[i] = fmaf(s[i], c1, mine[i]);
+        mbar_arrive(BAR(REL_SYNC + t));
       }
       if constexpr (BIAS == 2) {
         ok = mbar_wait(BAR(B_FULL + t), j & 1, abort_flag);
