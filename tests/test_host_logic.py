@@ -59,6 +59,13 @@ def test_abi_validation_without_a_gpu(built_lib):
     # absorbed form needs Dqk == R
     rc = L.pjx_mla_fwd(1, 1, None, None, 1, None, None, None, 0, 0, 1, 4, 4, 2, 16, 8, 8, 1, 0, 1.0, 0, None, 0, None, None)
     assert rc == _lib.PJX_ERR_BAD_ARG and "qk_head_dim == kv_lora_rank" in _lib.last_error()
+    # absorbed form at the wide latents: partials of the latent decode kernels live in the workspace
+    assert L.pjx_mla_workspace_bytes(8, 2048, 16, 128, 128, 128, 1, 0) == 0
+    need = L.pjx_mla_workspace_bytes(8, 2048, 16, 576, 576, 576, 1, 0)
+    assert need >= 2048 * 16 * 577 * 4
+    rc = L.pjx_mla_fwd(16, 16, None, None, 16, None, None, None, 0, 0, 8, 2048, 2048, 16, 576, 576, 576, 1, 1, 1.0, 0,
+                       None, 0, None, None)
+    assert rc == _lib.PJX_ERR_WORKSPACE and "mla workspace" in _lib.last_error()
     # decode workspace query and split-length rule
     assert L.pjx_attn_decode_default_split_len(16, 8, 32768) % 64 == 0
     need = L.pjx_attn_decode_workspace_bytes(16, 1, 32, 8, 128, 32768, 1024)
